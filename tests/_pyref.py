@@ -1,0 +1,75 @@
+"""Independent pure-Python / float64 restatements used to cross-check the C oracle.
+
+``loss_two_term`` is the left-tree-layer-1 specialisation of the inside recurrence
+(pcfg_loss.cu:149-213 with max_left == 1: of the four (j, b) combinations only
+"no left child, j=0" and "leaf left child, j=1" are ever finite), written with torch in
+float64 so autograd gives an independent gradient.  ``loss_bruteforce`` enumerates every
+derivation explicitly.
+"""
+import itertools
+import math
+
+import torch
+
+NEG = float("-inf")
+
+
+def _lse(xs):
+    """-inf-safe logsumexp of a list of 0-d tensors (torch.logsumexp gives NaN grads on all -inf)."""
+    fin = [x for x in xs if x.item() != NEG]
+    if not fin:
+        return torch.tensor(NEG, dtype=torch.float64)
+    return torch.logsumexp(torch.stack(fin), 0)
+
+
+def loss_two_term(match, links, m, n):
+    """S[0][0] for one sentence; match [L,T], links [L,2,L] float64 tensors (may require grad)."""
+    M = m // 2  # main-chain nodes a = 2*ai+1 < m
+    last = (m - 2) // 2
+    S = [[torch.tensor(NEG, dtype=torch.float64) for _ in range(n + 2)] for _ in range(M)]
+    S[last][n - 1] = match[m - 1, n - 1]
+    for t in range(n - 2, -1, -1):
+        for ai in range(M):
+            a = 2 * ai + 1
+            terms = []
+            for ci in range(ai + 1, M):
+                c = 2 * ci + 1
+                terms.append(links[a, 0, c] + S[ci][t + 1] + match[a, t])
+                if a >= 3 and t + 1 < n:
+                    terms.append(links[a, 1, c] + S[ci][t + 2] + match[a - 1, t] + match[a, t + 1])
+            S[ai][t] = _lse(terms)
+    return S[0][0]
+
+
+def loss_bruteforce(match, links, m, n):
+    """log of the sum over all derivations, enumerated one by one (tiny m only)."""
+    M = m // 2
+    mains = [2 * i + 1 for i in range(M)]
+    if mains[-1] != m - 1:
+        return NEG
+    inner = mains[1:-1]
+    total = []
+    for r in range(len(inner) + 1):
+        for sub in itertools.combinations(inner, r):
+            chain = [1] + list(sub) + [m - 1]
+            k = len(chain)
+            # nodes chain[1..k-2] may take a leaf left child; node 1 and the last node cannot
+            for uses in itertools.product([0, 1], repeat=max(k - 2, 0)):
+                use = [0] + list(uses) + [0]
+                if sum(use) + k != n:
+                    continue
+                lp, t = 0.0, 0
+                for i, a in enumerate(chain):
+                    if use[i]:
+                        lp += float(match[a - 1, t])
+                        t += 1
+                    lp += float(match[a, t])
+                    t += 1
+                    if i + 1 < k:
+                        lp += float(links[a, use[i], chain[i + 1]])
+                if lp != NEG and not math.isnan(lp):
+                    total.append(lp)
+    if not total:
+        return NEG
+    mx = max(total)
+    return mx + math.log(sum(math.exp(x - mx) for x in total))
