@@ -1,0 +1,117 @@
+/*
+ * libpcfgnat — C ABI of the B200 (sm_100a) kernels for PCFG-NAT's structured loss and
+ * decoding path.  Plain pointers and sizes only; every pointer is a DEVICE pointer unless
+ * marked "host".  The caller owns all memory (inputs, outputs, scratch); the library
+ * keeps no state between calls, launches on the stream it is given and never
+ * synchronises or calls exit().  Each entry point replaces the reference interface cited
+ * beside it (paths relative to the reference project root).
+ *
+ * Conventions shared by all entry points
+ *   B            sentences in the batch
+ *   L            graph length ("prelen"), padded to the batch maximum
+ *   T            target length ("tarlen"), padded to the batch maximum
+ *   max_left     links.size(2) - 1 = 2^left_tree_layer - 1; only max_left == 1 is
+ *                implemented (every published configuration uses left_tree_layer 1)
+ *   Mc, Lt       main-chain / local-tree slots: Mc = (L-2)/(max_left+1)+1, Lt = L-Mc
+ *   output_length[b] = m_b graph nodes in use, target_length[b] = n_b target tokens
+ *   status       optional device int (may be NULL) the kernels OR PCFGNAT_STATUS_* bits
+ *                into; the caller zeroes it and reads it when it wants to
+ *   stream       a cudaStream_t passed as void*
+ * Return value: PCFGNAT_OK or a negative PCFGNAT_ERR_* code (argument checks and launch
+ * errors; asynchronous faults surface on the caller's next synchronisation).
+ */
+#ifndef PCFGNAT_H_
+#define PCFGNAT_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PCFGNAT_OK 0
+#define PCFGNAT_ERR_INVALID_ARGUMENT (-1) /* null pointer, negative or inconsistent size */
+#define PCFGNAT_ERR_UNSUPPORTED (-2)      /* max_left != 1, unsupported dtype */
+#define PCFGNAT_ERR_CUDA (-3)             /* a CUDA runtime call or launch failed */
+#define PCFGNAT_ERR_WORKSPACE (-4)        /* scratch buffer too small */
+#define PCFGNAT_ERR_TOO_LARGE (-5)        /* shape beyond what the kernels index */
+
+/* bits OR-ed into *status by the kernels */
+#define PCFGNAT_STATUS_BAD_LENGTH 1 /* a sentence with m_b or n_b out of range was skipped */
+#define PCFGNAT_STATUS_BAD_TRACE 2  /* a back-trace left the tables and was cut short */
+#define PCFGNAT_STATUS_BAD_INDEX 4  /* a gather index outside [0, V) produced NaN */
+#define PCFGNAT_STATUS_TIMEOUT 8    /* a bounded device-side wait ran out */
+
+#define PCFGNAT_DTYPE_F32 0
+#define PCFGNAT_DTYPE_F16 1
+
+int pcfgnat_version(void);
+const char *pcfgnat_error_string(int code);
+
+/* Inside pass.  Replaces pcfg_loss() (fs_plugins/custom_ops/pcfg_loss.cu:379-401, kernels
+ * :85-224 and :263-349).  match_all [B][L][T] f32, links [B][L][max_left+1][L] f32,
+ * lengths int64.  Writes every cell of S [B][Mc][T+2] and, when C is not NULL, of
+ * C [B][Lt][T+2][max_left+2] (fill value -inf); loss_b = S[b][0][0].  S is bit-identical
+ * to the reference kernel's table (same reduction order, expf/logf, no fast-math). */
+int pcfgnat_loss_fwd(const float *match_all, const float *links, const int64_t *output_length,
+                     const int64_t *target_length, int B, int L, int T, int max_left, float *S, float *C,
+                     int *status, void *stream);
+
+/* Outside pass + gradients.  Replaces pcfg_loss_backward()
+ * (fs_plugins/custom_ops/pcfg_loss_backward.cu:654-721, seven kernels :29-603).
+ * grad_output [B] f32, S from pcfgnat_loss_fwd.  S_grad [B][Mc][T+2] is scratch.
+ * Writes every cell of match_all_grad [B][L][T] and links_grad [B][L][max_left+1][L]. */
+int pcfgnat_loss_bwd(const float *grad_output, const float *S, const float *match_all, const float *links,
+                     const int64_t *output_length, const int64_t *target_length, int B, int L, int T, int max_left,
+                     float *S_grad, float *match_all_grad, float *links_grad, int *status, void *stream);
+
+/* Forward and backward in one call, as CUDAPCFGLossFunc.forward always runs them
+ * (fs_plugins/custom_ops/pcfg_loss.py:63-74).  workspace holds S and S_grad
+ * (pcfgnat_loss_workspace_bytes); loss [B] f32 receives S[b][0][0]; gradients are for
+ * grad_output == 1. */
+size_t pcfgnat_loss_workspace_bytes(int B, int L, int T, int max_left);
+int pcfgnat_loss_fwd_bwd(const float *match_all, const float *links, const int64_t *output_length,
+                         const int64_t *target_length, int B, int L, int T, int max_left, void *workspace,
+                         size_t workspace_bytes, float *loss, float *match_all_grad, float *links_grad, int *status,
+                         void *stream);
+
+/* Best tree for glancing training.  Replaces pcfg_best_tree()
+ * (fs_plugins/custom_ops/pcfg_best_tree.cu:333-360, kernels :65-197 and :240-301).
+ * S from pcfgnat_loss_fwd; tree [B][L] int64: target index emitted by each node, -1 if
+ * unused.  Bit-exact with the reference including arg-max tie-breaking. */
+int pcfgnat_best_tree(const float *S, const float *match_all, const float *links, const int64_t *output_length,
+                      const int64_t *target_length, int B, int L, int T, int max_left, int64_t *tree, int *status,
+                      void *stream);
+
+/* Viterbi tables.  Replaces pcfg_viterbi() (fs_plugins/custom_ops/pcfg_viterbi.cu:272-301,
+ * kernels :23-140 and :178-241).  ob_lprob [B][L] f32; writes every cell of S f32 and
+ * R, Lt, Mt int64, all [B][L][L/4] (fills: -inf, 0).  Bit-exact with the reference. */
+int pcfgnat_viterbi(const float *ob_lprob, const float *links, const int64_t *output_length, int B, int L,
+                    int max_left, float *S, int64_t *R, int64_t *Lt, int64_t *Mt, int *status, void *stream);
+
+/* Back-trace on the device.  Replaces the host function viterbi_decoding()
+ * (fs_plugins/custom_ops/pcfg_loss.cpp:12-73).  Traces [B][L][Q] int64, tokens [B][L]
+ * int64, left_tree_mask [mask_dim][mask_dim] int64 (non-zero = not allowed).  Writes
+ * out_tokens [B][cap] int64 (pad_index beyond the sentence) and out_count [B] int64. */
+int pcfgnat_viterbi_backtrace(const int64_t *pred_length, const int64_t *output_length, const int64_t *Lt,
+                              const int64_t *R, const int64_t *Mt, const int64_t *tokens,
+                              const int64_t *left_tree_mask, int mask_dim, int64_t pad_index, int B, int L, int Q,
+                              int cap, int64_t *out_tokens, int64_t *out_count, int *status, void *stream);
+
+/* log-softmax over the vocabulary + gather of selected columns, optional in-place
+ * softmax for the backward.  Replaces logsoftmax_gather()
+ * (fs_plugins/custom_ops/logsoftmax_gather.cu:295-359, kernel :240-292).
+ * logits [rows][V] contiguous, f32 or f16 (PCFGNAT_DTYPE_*); select_idx int64 addressed as
+ * select_idx[(r / rows_per_batch) * stride_b + (r % rows_per_batch) * stride_l + s * stride_s]
+ * (element strides, so the reference's stride-0 expand of the targets needs no copy);
+ * selected [rows][slen] f32.  With require_gradient != 0 the logits are overwritten by
+ * the softmax probabilities. */
+int pcfgnat_logsoftmax_gather(void *logits, int dtype, const int64_t *select_idx, int64_t stride_b, int64_t stride_l,
+                              int64_t stride_s, int64_t rows, int64_t rows_per_batch, int V, int slen,
+                              int require_gradient, float *selected, int *status, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PCFGNAT_H_ */

@@ -7,4 +7,4 @@ fallback: operators raise if the library or a GPU is missing.
 """
 __version__ = "0.1.0"
 
-from . import support_tree, synthetic  # noqa: F401
+from . import sharding, support_tree, synthetic  # noqa: F401

@@ -1,0 +1,120 @@
+// extern "C" entry points declared in include/pcfgnat.h: argument checks, then launch.
+#include "common.cuh"
+
+using namespace pcfgnat;
+
+namespace {
+
+inline bool bad_dims(int B, int L, int T) { return B < 0 || L < 2 || T < 1; }
+
+inline size_t align256(size_t x) { return (x + 255) / 256 * 256; }
+
+}  // namespace
+
+extern "C" {
+
+int pcfgnat_version(void) { return 100; }
+
+const char *pcfgnat_error_string(int code) {
+    switch (code) {
+        case PCFGNAT_OK: return "ok";
+        case PCFGNAT_ERR_INVALID_ARGUMENT: return "invalid argument (null pointer, negative or inconsistent size)";
+        case PCFGNAT_ERR_UNSUPPORTED: return "unsupported configuration (only max_left == 1; dtypes f32/f16)";
+        case PCFGNAT_ERR_CUDA: return "a CUDA runtime call or kernel launch failed";
+        case PCFGNAT_ERR_WORKSPACE: return "workspace too small";
+        case PCFGNAT_ERR_TOO_LARGE: return "shape too large for the kernels";
+        default: return "unknown error code";
+    }
+}
+
+int pcfgnat_loss_fwd(const float *match_all, const float *links, const int64_t *output_length,
+                     const int64_t *target_length, int B, int L, int T, int max_left, float *S, float *C, int *status,
+                     void *stream) {
+    if (max_left != 1) return PCFGNAT_ERR_UNSUPPORTED;
+    if (bad_dims(B, L, T)) return PCFGNAT_ERR_INVALID_ARGUMENT;
+    if (B && (!match_all || !links || !output_length || !target_length || !S)) return PCFGNAT_ERR_INVALID_ARGUMENT;
+    return launch_loss_fwd(match_all, links, output_length, target_length, B, L, T, S, C, nullptr, status,
+                           static_cast<cudaStream_t>(stream));
+}
+
+int pcfgnat_loss_bwd(const float *grad_output, const float *S, const float *match_all, const float *links,
+                     const int64_t *output_length, const int64_t *target_length, int B, int L, int T, int max_left,
+                     float *S_grad, float *match_all_grad, float *links_grad, int *status, void *stream) {
+    if (max_left != 1) return PCFGNAT_ERR_UNSUPPORTED;
+    if (bad_dims(B, L, T)) return PCFGNAT_ERR_INVALID_ARGUMENT;
+    if (B && (!grad_output || !S || !match_all || !links || !output_length || !target_length || !S_grad ||
+              !match_all_grad || !links_grad))
+        return PCFGNAT_ERR_INVALID_ARGUMENT;
+    return launch_loss_bwd(grad_output, S, match_all, links, output_length, target_length, B, L, T, S_grad,
+                           match_all_grad, links_grad, status, static_cast<cudaStream_t>(stream));
+}
+
+size_t pcfgnat_loss_workspace_bytes(int B, int L, int T, int max_left) {
+    if (max_left != 1 || bad_dims(B, L, T)) return 0;
+    const size_t table = align256((size_t)B * main_slots(L, 1) * (T + 2) * sizeof(float));
+    return 2 * table;  // S and S_grad
+}
+
+int pcfgnat_loss_fwd_bwd(const float *match_all, const float *links, const int64_t *output_length,
+                         const int64_t *target_length, int B, int L, int T, int max_left, void *workspace,
+                         size_t workspace_bytes, float *loss, float *match_all_grad, float *links_grad, int *status,
+                         void *stream) {
+    if (max_left != 1) return PCFGNAT_ERR_UNSUPPORTED;
+    if (bad_dims(B, L, T)) return PCFGNAT_ERR_INVALID_ARGUMENT;
+    if (B && (!match_all || !links || !output_length || !target_length || !workspace || !loss || !match_all_grad ||
+              !links_grad))
+        return PCFGNAT_ERR_INVALID_ARGUMENT;
+    const size_t need = pcfgnat_loss_workspace_bytes(B, L, T, max_left);
+    if (workspace_bytes < need) return PCFGNAT_ERR_WORKSPACE;
+    if (reinterpret_cast<uintptr_t>(workspace) % 16) return PCFGNAT_ERR_INVALID_ARGUMENT;
+    float *S = static_cast<float *>(workspace);
+    float *G = reinterpret_cast<float *>(static_cast<char *>(workspace) + need / 2);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int rc = launch_loss_fwd(match_all, links, output_length, target_length, B, L, T, S, nullptr, loss, status, st);
+    if (rc) return rc;
+    return launch_loss_bwd(nullptr, S, match_all, links, output_length, target_length, B, L, T, G, match_all_grad,
+                           links_grad, status, st);
+}
+
+int pcfgnat_best_tree(const float *S, const float *match_all, const float *links, const int64_t *output_length,
+                      const int64_t *target_length, int B, int L, int T, int max_left, int64_t *tree, int *status,
+                      void *stream) {
+    if (max_left != 1) return PCFGNAT_ERR_UNSUPPORTED;
+    if (bad_dims(B, L, T)) return PCFGNAT_ERR_INVALID_ARGUMENT;
+    if (B && (!S || !match_all || !links || !output_length || !target_length || !tree))
+        return PCFGNAT_ERR_INVALID_ARGUMENT;
+    return launch_best_tree(S, match_all, links, output_length, target_length, B, L, T, tree, status,
+                            static_cast<cudaStream_t>(stream));
+}
+
+int pcfgnat_viterbi(const float *ob_lprob, const float *links, const int64_t *output_length, int B, int L,
+                    int max_left, float *S, int64_t *R, int64_t *Lt, int64_t *Mt, int *status, void *stream) {
+    if (max_left != 1) return PCFGNAT_ERR_UNSUPPORTED;
+    if (B < 0 || L < 8) return PCFGNAT_ERR_INVALID_ARGUMENT;
+    if (B && (!ob_lprob || !links || !output_length || !S || !R || !Lt || !Mt)) return PCFGNAT_ERR_INVALID_ARGUMENT;
+    return launch_viterbi(ob_lprob, links, output_length, B, L, S, R, Lt, Mt, status,
+                          static_cast<cudaStream_t>(stream));
+}
+
+int pcfgnat_viterbi_backtrace(const int64_t *pred_length, const int64_t *output_length, const int64_t *Lt,
+                              const int64_t *R, const int64_t *Mt, const int64_t *tokens,
+                              const int64_t *left_tree_mask, int mask_dim, int64_t pad_index, int B, int L, int Q,
+                              int cap, int64_t *out_tokens, int64_t *out_count, int *status, void *stream) {
+    if (B < 0 || L < 1 || Q < 1 || cap < 0 || mask_dim < 1) return PCFGNAT_ERR_INVALID_ARGUMENT;
+    if (B && (!pred_length || !output_length || !Lt || !R || !Mt || !tokens || !left_tree_mask || !out_count ||
+              (cap && !out_tokens)))
+        return PCFGNAT_ERR_INVALID_ARGUMENT;
+    return launch_backtrace(pred_length, output_length, Lt, R, Mt, tokens, left_tree_mask, mask_dim, pad_index, B, L,
+                            Q, cap, out_tokens, out_count, status, static_cast<cudaStream_t>(stream));
+}
+
+int pcfgnat_logsoftmax_gather(void *logits, int dtype, const int64_t *select_idx, int64_t stride_b, int64_t stride_l,
+                              int64_t stride_s, int64_t rows, int64_t rows_per_batch, int V, int slen,
+                              int require_gradient, float *selected, int *status, void *stream) {
+    if (rows < 0 || rows_per_batch < 1 || V < 1 || slen < 0) return PCFGNAT_ERR_INVALID_ARGUMENT;
+    if (rows && (!logits || (slen && (!select_idx || !selected)))) return PCFGNAT_ERR_INVALID_ARGUMENT;
+    return launch_logsoftmax_gather(logits, dtype, select_idx, stride_b, stride_l, stride_s, rows, rows_per_batch, V,
+                                    slen, require_gradient, selected, status, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

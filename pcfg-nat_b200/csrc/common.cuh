@@ -1,0 +1,48 @@
+// Shared helpers of the sm_100a kernels behind include/pcfgnat.h.
+#pragma once
+#include <cuda_runtime.h>
+#include <math_constants.h>
+#include <stdint.h>
+
+#include "../../include/pcfgnat.h"
+
+namespace pcfgnat {
+
+constexpr int kLanes = 4;          // virtual reduction lanes per tree node; the reduction order of the
+                                   // sum-semiring tables and all arg-max tie-breaks are defined on them
+constexpr int kMaxRows = 256;      // main-chain rows per CTA pass (x kLanes threads)
+constexpr int kSmemLimit = 227 * 1024;
+
+__host__ __device__ inline int main_slots(int L, int ml) { return (L - 2) / (ml + 1) + 1; }
+
+// Number of main-chain nodes a = 2*ai+1 that are < m (max_left == 1).
+__host__ __device__ inline int main_nodes_below(int m) { return m / 2; }
+
+__device__ __forceinline__ float neg_inf() { return -CUDART_INF_F; }
+
+__device__ __forceinline__ bool lengths_ok(int m, int n, int L, int T) { return m >= 2 && m <= L && n >= 1 && n <= T; }
+
+__device__ __forceinline__ void flag(int *status, int bit) {
+    if (status) atomicOr(status, bit);
+}
+
+inline int cuda_rc(cudaError_t e) { return e == cudaSuccess ? PCFGNAT_OK : PCFGNAT_ERR_CUDA; }
+
+// Host-side launchers shared between the translation units.
+int launch_loss_fwd(const float *match_all, const float *links, const int64_t *ol, const int64_t *tl, int B, int L,
+                    int T, float *S, float *C, float *loss, int *status, cudaStream_t st);
+int launch_loss_bwd(const float *grad_output, const float *S, const float *match_all, const float *links,
+                    const int64_t *ol, const int64_t *tl, int B, int L, int T, float *S_grad, float *mg, float *lg,
+                    int *status, cudaStream_t st);
+int launch_best_tree(const float *S, const float *match_all, const float *links, const int64_t *ol, const int64_t *tl,
+                     int B, int L, int T, int64_t *tree, int *status, cudaStream_t st);
+int launch_viterbi(const float *ob, const float *links, const int64_t *ol, int B, int L, float *S, int64_t *R,
+                   int64_t *Lt, int64_t *Mt, int *status, cudaStream_t st);
+int launch_backtrace(const int64_t *pred, const int64_t *ol, const int64_t *Lt, const int64_t *R, const int64_t *Mt,
+                     const int64_t *tokens, const int64_t *mask, int mask_dim, int64_t pad, int B, int L, int Q,
+                     int cap, int64_t *out, int64_t *cnt, int *status, cudaStream_t st);
+int launch_logsoftmax_gather(void *logits, int dtype, const int64_t *sel, int64_t sb, int64_t sl, int64_t ss,
+                             int64_t rows, int64_t rpb, int V, int slen, int req_grad, float *selected, int *status,
+                             cudaStream_t st);
+
+}  // namespace pcfgnat

@@ -1,0 +1,411 @@
+"""Drop-in for ``fs_plugins/custom_ops/pcfg_loss.py`` of PCFG-NAT on top of libpcfgnat.so.
+
+Same five public operators with the same positional signatures and return structure
+(fs_plugins/custom_ops/pcfg_loss.py:85, :117, :142, :181, :183-184):
+
+    cuda_pcfg_loss(match_all, links, output_length, target_length)           -> loss [B]
+    cuda_pcfg_best_tree(match_all, links, output_length, target_length)      -> (tree [B,L] i64, loss [B])
+    cuda_pcfg_viterbi(ob_lprob, links, output_length)                        -> (scores [B,L/4], R, L, M)
+    dag_logsoftmax_gather_inplace(word_ins_out, select_idx)                  -> (word_ins_out, selected f32)
+    viterbi_decoding(pred_length, output_length, L_trace, R_trace, M_trace,
+                     unreduced_tokens, left_tree_mask, pad_index)            -> float32 [B, maxlen]
+
+and ``get_pcfg_kernel()`` returning an object with the six extension-level functions an
+unmodified reference wrapper calls (fs_plugins/custom_ops/pcfg_loss.cpp:75-82).
+
+The host side only validates arguments, allocates outputs with torch and hands raw
+device pointers to the C ABI on the caller's current CUDA stream.  There is no CPU path:
+every operator raises when CUDA or the library is unavailable.
+
+Known, deliberate differences from the reference:
+* only ``max_left == 1`` (left_tree_layer 1) and float32 tables are implemented;
+* ``config`` values 1..4 all run the kernels (the reference silently skips its launches for
+  2..4, pcfg_loss_backward.cu:694-697); other values raise the reference's message;
+* ``viterbi_decoding`` right-pads ragged batches (the reference raises for them,
+  pcfg_loss.cpp:66-69) and also accepts CUDA tensors, in which case nothing is copied to
+  the host except the per-sentence counts;
+* outputs are produced on the tensors' own device and current stream (the reference
+  always launches on the legacy default stream 0, pcfg_loss.cu:395).
+"""
+import torch
+from torch.autograd import Function
+
+from .. import _cabi
+
+_status = {}
+_kernel_shim = None
+
+
+def _require_cuda():
+    if not torch.cuda.is_available():
+        # same condition and wording as the reference loader (pcfg_loss.py:20-21)
+        raise RuntimeError("You need GPU to use the custom cuda operations")
+
+
+def _stream(dev):
+    return torch.cuda.current_stream(dev).cuda_stream
+
+
+def _status_ptr(dev):
+    """Per-device int32 word the kernels OR PCFGNAT_STATUS_* bits into."""
+    key = dev.index if dev.index is not None else torch.cuda.current_device()
+    t = _status.get(key)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=dev)
+        _status[key] = t
+    return t.data_ptr()
+
+
+def read_status(device=None, reset=True):
+    """Returns the PCFGNAT_STATUS_* bits recorded on ``device`` (synchronises)."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    key = dev.index if dev.index is not None else torch.cuda.current_device()
+    t = _status.get(key)
+    if t is None:
+        return 0
+    v = int(t.item())
+    if reset:
+        t.zero_()
+    return v
+
+
+def _check_config(config):
+    if not (1 <= int(config) <= 4):
+        raise RuntimeError("config should be 1~4")
+
+
+def _f32_cuda(t, name, ndim):
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor")
+    if t.dim() != ndim:
+        raise RuntimeError(f"{name} dim != {ndim}")
+    if t.dtype != torch.float32:
+        raise RuntimeError(f"{name} must be float32 (got {t.dtype}); the DP tables are fp32 only")
+    return t.contiguous()
+
+
+def _lengths(t, name, B, dev):
+    if not isinstance(t, torch.Tensor) or t.dim() != 1 or t.shape[0] != B:
+        raise RuntimeError(f"{name} must be a 1-d tensor of batch size {B}")
+    return t.to(device=dev, dtype=torch.int64).contiguous()
+
+
+def _loss_args(match_all, links, output_length, target_length):
+    match_all = _f32_cuda(match_all, "match_all", 3)
+    links = _f32_cuda(links, "links", 4)
+    B, L, T = match_all.shape
+    if links.shape[0] != B or links.shape[1] != L or links.shape[3] != L:
+        raise RuntimeError("links must be [batch, prelen, max_left+1, prelen] matching match_all")
+    if links.device != match_all.device:
+        raise RuntimeError("match_all and links must be on the same device")
+    max_left = links.shape[2] - 1
+    if max_left != 1:
+        raise RuntimeError(f"only max_left == 1 (left_tree_layer 1) is implemented, got max_left = {max_left}")
+    if L < 2 or T < 1:
+        raise RuntimeError("prelen must be >= 2 and tarlen >= 1")
+    dev = match_all.device
+    return match_all, links, _lengths(output_length, "output_length", B, dev), _lengths(target_length, "target_length", B, dev), B, L, T, max_left
+
+
+def table_shapes(B, L, T, max_left):
+    Mc = (L - 2) // (max_left + 1) + 1
+    return (B, Mc, T + 2), (B, L - Mc, T + 2, max_left + 2)
+
+
+class _Kernel:
+    """Extension-level API: the functions of the reference's pybind module (pcfg_loss.cpp:75-82)."""
+
+    @staticmethod
+    def pcfg_loss(match_all, links, output_length, target_length, config=1, want_c=True):
+        """Inside tables (S [B,Mc,T+2], C [B,Lt,T+2,max_left+2]); replaces pcfg_loss (pcfg_loss.cu:379-401)."""
+        _require_cuda()
+        ma, lk, ol, tl, B, L, T, ml = _loss_args(match_all, links, output_length, target_length)
+        sS, sC = table_shapes(B, L, T, ml)
+        with torch.cuda.device(ma.device):
+            S = torch.empty(sS, dtype=torch.float32, device=ma.device)
+            C = torch.empty(sC, dtype=torch.float32, device=ma.device) if want_c else None
+            rc = _cabi.lib().pcfgnat_loss_fwd(ma.data_ptr(), lk.data_ptr(), ol.data_ptr(), tl.data_ptr(), B, L, T, ml,
+                                              S.data_ptr(), C.data_ptr() if want_c else None, _status_ptr(ma.device),
+                                              _stream(ma.device))
+        _cabi.check(rc, "pcfgnat_loss_fwd")
+        return S, C
+
+    @staticmethod
+    def pcfg_loss_backward(grad_output, S, C, match_all, links, output_length, target_length, config=1):
+        """(match_all_grad, links_grad); replaces pcfg_loss_backward (pcfg_loss_backward.cu:654-721).
+        ``C`` is accepted for signature parity; the leaf entries it would supply are read from
+        ``match_all`` directly."""
+        _require_cuda()
+        _check_config(config)
+        ma, lk, ol, tl, B, L, T, ml = _loss_args(match_all, links, output_length, target_length)
+        sS, _ = table_shapes(B, L, T, ml)
+        S = _f32_cuda(S, "S", 3)
+        if tuple(S.shape) != sS:
+            raise RuntimeError(f"S must have shape {sS}")
+        go = grad_output.to(device=ma.device, dtype=torch.float32).contiguous()
+        if go.shape != (B,):
+            raise RuntimeError("grad_output must be [batch]")
+        with torch.cuda.device(ma.device):
+            G = torch.empty(sS, dtype=torch.float32, device=ma.device)
+            mg = torch.empty_like(ma)
+            lg = torch.empty_like(lk)
+            rc = _cabi.lib().pcfgnat_loss_bwd(go.data_ptr(), S.data_ptr(), ma.data_ptr(), lk.data_ptr(), ol.data_ptr(),
+                                              tl.data_ptr(), B, L, T, ml, G.data_ptr(), mg.data_ptr(), lg.data_ptr(),
+                                              _status_ptr(ma.device), _stream(ma.device))
+        _cabi.check(rc, "pcfgnat_loss_bwd")
+        return mg, lg
+
+    @staticmethod
+    def pcfg_loss_fwd_bwd(match_all, links, output_length, target_length):
+        """Fused forward + backward for grad_output == 1: (loss [B], match_all_grad, links_grad)."""
+        _require_cuda()
+        ma, lk, ol, tl, B, L, T, ml = _loss_args(match_all, links, output_length, target_length)
+        l = _cabi.lib()
+        nbytes = l.pcfgnat_loss_workspace_bytes(B, L, T, ml)
+        with torch.cuda.device(ma.device):
+            ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=ma.device)
+            loss = torch.empty(B, dtype=torch.float32, device=ma.device)
+            mg = torch.empty_like(ma)
+            lg = torch.empty_like(lk)
+            rc = l.pcfgnat_loss_fwd_bwd(ma.data_ptr(), lk.data_ptr(), ol.data_ptr(), tl.data_ptr(), B, L, T, ml,
+                                        ws.data_ptr(), nbytes, loss.data_ptr(), mg.data_ptr(), lg.data_ptr(),
+                                        _status_ptr(ma.device), _stream(ma.device))
+        _cabi.check(rc, "pcfgnat_loss_fwd_bwd")
+        return loss, mg, lg
+
+    @staticmethod
+    def pcfg_best_tree(S, C, match_all, links, output_length, target_length, config=1):
+        """tree [B, L] int64; replaces pcfg_best_tree (pcfg_best_tree.cu:333-360).  ``C`` is accepted
+        for signature parity and not read."""
+        _require_cuda()
+        _check_config(config)
+        ma, lk, ol, tl, B, L, T, ml = _loss_args(match_all, links, output_length, target_length)
+        sS, _ = table_shapes(B, L, T, ml)
+        S = _f32_cuda(S, "S", 3)
+        if tuple(S.shape) != sS:
+            raise RuntimeError(f"S must have shape {sS}")
+        with torch.cuda.device(ma.device):
+            tree = torch.empty((B, L), dtype=torch.int64, device=ma.device)
+            rc = _cabi.lib().pcfgnat_best_tree(S.data_ptr(), ma.data_ptr(), lk.data_ptr(), ol.data_ptr(), tl.data_ptr(),
+                                               B, L, T, ml, tree.data_ptr(), _status_ptr(ma.device), _stream(ma.device))
+        _cabi.check(rc, "pcfgnat_best_tree")
+        return tree
+
+    @staticmethod
+    def pcfg_viterbi(ob_lprob, links, output_length, config=1):
+        """(S, R, L, M) of shape [B, L, L//4]; replaces pcfg_viterbi (pcfg_viterbi.cu:272-301)."""
+        _require_cuda()
+        _check_config(config)
+        ob = _f32_cuda(ob_lprob, "ob_lprob", 2)
+        lk = _f32_cuda(links, "links", 4)
+        B, L = ob.shape
+        if lk.shape[0] != B or lk.shape[1] != L or lk.shape[3] != L or lk.device != ob.device:
+            raise RuntimeError("links must be [batch, prelen, max_left+1, prelen] on ob_lprob's device")
+        ml = lk.shape[2] - 1
+        if ml != 1:
+            raise RuntimeError(f"only max_left == 1 (left_tree_layer 1) is implemented, got max_left = {ml}")
+        if L < 8:
+            raise RuntimeError("prelen must be >= 8 (the tables have prelen // 4 length columns)")
+        ol = _lengths(output_length, "output_length", B, ob.device)
+        Q = L // 4
+        with torch.cuda.device(ob.device):
+            S = torch.empty((B, L, Q), dtype=torch.float32, device=ob.device)
+            R = torch.empty((B, L, Q), dtype=torch.int64, device=ob.device)
+            Lt = torch.empty_like(R)
+            Mt = torch.empty_like(R)
+            rc = _cabi.lib().pcfgnat_viterbi(ob.data_ptr(), lk.data_ptr(), ol.data_ptr(), B, L, ml, S.data_ptr(),
+                                             R.data_ptr(), Lt.data_ptr(), Mt.data_ptr(), _status_ptr(ob.device),
+                                             _stream(ob.device))
+        _cabi.check(rc, "pcfgnat_viterbi")
+        return S, R, Lt, Mt
+
+    @staticmethod
+    def logsoftmax_gather(word_ins_out, select_idx, require_gradient):
+        """selected [B, L, slen] f32; overwrites ``word_ins_out`` with softmax probabilities when
+        ``require_gradient``; replaces logsoftmax_gather (logsoftmax_gather.cu:295-359)."""
+        _require_cuda()
+        if not word_ins_out.is_cuda:
+            raise RuntimeError("word_ins_out must be a CUDA tensor")
+        if not select_idx.is_cuda:
+            raise RuntimeError("select_idx must be a CUDA tensor")
+        if word_ins_out.dim() != 3:
+            raise RuntimeError("word_ins_out dim != 3")
+        if select_idx.dim() != 3:
+            raise RuntimeError("select_idx dim != 3")
+        B, L, V = word_ins_out.shape
+        if select_idx.shape[0] != B:
+            raise RuntimeError("batch size not match")
+        if select_idx.shape[1] != L:
+            raise RuntimeError("prelen size not match")
+        if select_idx.dtype != torch.int64:
+            raise RuntimeError("select_idx should be long")
+        if not word_ins_out.is_contiguous():
+            raise RuntimeError("word_ins_out is not contiguous")
+        if word_ins_out.dtype == torch.float32:
+            dt = 0
+        elif word_ins_out.dtype == torch.float16:
+            dt = 1
+        else:
+            raise RuntimeError(f"logsoftmax_gather not implemented for '{word_ins_out.dtype}'")
+        slen = select_idx.shape[2]
+        sb, sl, ss = select_idx.stride()
+        dev = word_ins_out.device
+        with torch.cuda.device(dev):
+            selected = torch.empty((B, L, slen), dtype=torch.float32, device=dev)
+            rc = _cabi.lib().pcfgnat_logsoftmax_gather(word_ins_out.data_ptr(), dt, select_idx.data_ptr(), sb, sl, ss,
+                                                       B * L, L, V, slen, int(bool(require_gradient)),
+                                                       selected.data_ptr(), _status_ptr(dev), _stream(dev))
+        _cabi.check(rc, "pcfgnat_logsoftmax_gather")
+        return selected
+
+    @staticmethod
+    def viterbi_decoding_device(pred_length, output_length, L_trace, R_trace, M_trace, unreduced_tokens,
+                                left_tree_mask, pad_index):
+        """Device back-trace: (tokens [B, L] int64 padded with pad_index, count [B] int64), no host sync."""
+        _require_cuda()
+        dev = L_trace.device if L_trace.is_cuda else torch.device("cuda", torch.cuda.current_device())
+        i64 = lambda t: t.to(device=dev, dtype=torch.int64).contiguous()
+        Lt, R, Mt = i64(L_trace), i64(R_trace), i64(M_trace)
+        if Lt.dim() != 3 or R.shape != Lt.shape or Mt.shape != Lt.shape:
+            raise RuntimeError("L_trace, R_trace, M_trace must be [batch, prelen, prelen//4] and agree")
+        B, L, Q = Lt.shape
+        pl, ol, tk, mk = i64(pred_length), i64(output_length), i64(unreduced_tokens), i64(left_tree_mask)
+        if pl.shape != (B,) or ol.shape != (B,) or tk.shape != (B, L):
+            raise RuntimeError("pred_length/output_length must be [batch], unreduced_tokens [batch, prelen]")
+        if mk.dim() != 2 or mk.shape[0] != mk.shape[1]:
+            raise RuntimeError("left_tree_mask must be square")
+        with torch.cuda.device(dev):
+            out = torch.empty((B, L), dtype=torch.int64, device=dev)
+            cnt = torch.empty((B,), dtype=torch.int64, device=dev)
+            rc = _cabi.lib().pcfgnat_viterbi_backtrace(pl.data_ptr(), ol.data_ptr(), Lt.data_ptr(), R.data_ptr(),
+                                                       Mt.data_ptr(), tk.data_ptr(), mk.data_ptr(), mk.shape[0],
+                                                       int(pad_index), B, L, Q, L, out.data_ptr(), cnt.data_ptr(),
+                                                       _status_ptr(dev), _stream(dev))
+        _cabi.check(rc, "pcfgnat_viterbi_backtrace")
+        return out, cnt
+
+    @staticmethod
+    def viterbi_decoding(pred_length, output_length, L_trace, R_trace, M_trace, unreduced_tokens, left_tree_mask,
+                         pad_index):
+        """float32 [B, maxlen] padded with pad_index on the device of ``pred_length``;
+        replaces the host function viterbi_decoding (pcfg_loss.cpp:12-73)."""
+        out, cnt = _Kernel.viterbi_decoding_device(pred_length, output_length, L_trace, R_trace, M_trace,
+                                                   unreduced_tokens, left_tree_mask, pad_index)
+        maxlen = int(cnt.max().item()) if cnt.numel() else 0
+        return out[:, :maxlen].to(dtype=torch.float32, device=pred_length.device)
+
+
+def get_pcfg_kernel():
+    """The extension object of the reference loader (pcfg_loss.py:18-47); nothing is JIT-compiled here."""
+    global _kernel_shim
+    _require_cuda()
+    if _kernel_shim is None:
+        _cabi.lib()  # raises LibraryMissing with build instructions; never falls back
+        _kernel_shim = _Kernel()
+    return _kernel_shim
+
+
+class CUDAPCFGLossFunc(Function):
+    """loss_b = S[b, 0, 0]; gradients are computed eagerly in forward for grad_output == 1 and
+    scaled in backward, as in the reference (pcfg_loss.py:49-85)."""
+    config = 1
+
+    @staticmethod
+    def forward(ctx, match_all, links, output_length, target_length):
+        k = get_pcfg_kernel()
+        need_grad = ctx.needs_input_grad[0] or ctx.needs_input_grad[1]
+        if need_grad:
+            loss, mg, lg = k.pcfg_loss_fwd_bwd(match_all, links, output_length, target_length)
+            ctx.save_for_backward(mg, lg)
+            return loss
+        S, _ = k.pcfg_loss(match_all, links, output_length, target_length, CUDAPCFGLossFunc.config, want_c=False)
+        return S[:, 0, 0].clone()
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        if not (ctx.needs_input_grad[0] or ctx.needs_input_grad[1]):
+            return None, None, None, None
+        mg, lg = ctx.saved_tensors
+        B = mg.shape[0]
+        return mg * grad_output.view(B, 1, 1), lg * grad_output.view(B, 1, 1, 1), None, None
+
+
+cuda_pcfg_loss = CUDAPCFGLossFunc.apply
+
+
+class CUDAPCFGBestTreeFunc(Function):
+    """(tree, S[:, 0, 0]) — no gradient (pcfg_loss.py:89-117)."""
+    config = 1
+
+    @staticmethod
+    def forward(ctx, match_all, links, output_length, target_length):
+        k = get_pcfg_kernel()
+        S, _ = k.pcfg_loss(match_all, links, output_length, target_length, CUDAPCFGBestTreeFunc.config, want_c=False)
+        tree = k.pcfg_best_tree(S, None, match_all, links, output_length, target_length, CUDAPCFGBestTreeFunc.config)
+        ctx.mark_non_differentiable(tree)
+        return tree, S[:, 0, 0].clone()
+
+    @staticmethod
+    def backward(ctx, *grads):
+        return None, None, None, None
+
+
+cuda_pcfg_best_tree = CUDAPCFGBestTreeFunc.apply
+
+
+class CUDAPCFGViterbiFunc(Function):
+    """(S[:, 1, :], R, L, M) — no gradient (pcfg_loss.py:119-142)."""
+    config = 1
+
+    @staticmethod
+    def forward(ctx, ob_lprob, links, output_length):
+        S, R, Lt, Mt = get_pcfg_kernel().pcfg_viterbi(ob_lprob, links, output_length, CUDAPCFGViterbiFunc.config)
+        ctx.mark_non_differentiable(R, Lt, Mt)
+        return S[:, 1, :].clone(), R, Lt, Mt
+
+    @staticmethod
+    def backward(ctx, *grads):
+        return None, None, None
+
+
+cuda_pcfg_viterbi = CUDAPCFGViterbiFunc.apply
+
+
+class DagLogsoftmaxGatherFunc(Function):
+    """log-softmax + gather with the logits buffer reused for the backward: forward overwrites
+    ``word_ins_out`` with softmax probabilities when it needs a gradient; backward turns that
+    buffer into the logits gradient in place, once (pcfg_loss.py:144-181)."""
+
+    @staticmethod
+    def forward(ctx, word_ins_out, select_idx):
+        need_grad = ctx.needs_input_grad[0]
+        selected = get_pcfg_kernel().logsoftmax_gather(word_ins_out, select_idx, need_grad)
+        ctx.mark_dirty(word_ins_out)
+        ctx.set_materialize_grads(False)
+        if need_grad:
+            ctx.save_for_backward(word_ins_out, select_idx)
+            ctx.has_backward = False
+        return word_ins_out, selected
+
+    @staticmethod
+    def backward(ctx, grad_word_ins_out, grad_output):
+        if not ctx.needs_input_grad[0]:
+            return None, None
+        assert grad_word_ins_out is None, "Cannot reuse word_ins_out after logsoftmax_gather"
+        if grad_output is None:
+            return None, None
+        assert not ctx.has_backward, "Cannot backward twice in logsoftmax_gather"
+        ctx.has_backward = True
+        probs, idx = ctx.saved_tensors
+        # d logits = -p * sum_s g_s + scatter(g): done in the saved buffer
+        probs.mul_(grad_output.sum(-1, keepdim=True).neg_().to(probs.dtype))
+        probs.scatter_add_(-1, idx, grad_output.to(probs.dtype))
+        return probs, None
+
+
+dag_logsoftmax_gather_inplace = DagLogsoftmaxGatherFunc.apply
+
+
+def viterbi_decoding(pred_length, output_length, L_trace, R_trace, M_trace, unreduced_tokens, left_tree_mask, pad_index):
+    return get_pcfg_kernel().viterbi_decoding(pred_length, output_length, L_trace, R_trace, M_trace, unreduced_tokens,
+                                              left_tree_mask, pad_index)

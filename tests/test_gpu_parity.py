@@ -1,0 +1,373 @@
+"""GPU parity tests: the CUDA kernels, called through the C ABI (ctypes -> libpcfgnat.so), against
+the CPU oracle on the same seeded inputs, against the golden outputs of the reference kernels and,
+when the reference build is present next to the oracle, against the reference kernels live.
+
+Tolerances (from the parity contract): loss 1e-4 relative, gradients 1e-3 relative, Viterbi and
+best-tree indices bit-exact including tie-breaks.  The inside table is additionally required to be
+bit-identical to the reference kernel's table (GPU vs GPU), because best-tree compares sums of it.
+"""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from conftest import golden_path
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+def _g(name):
+    p = golden_path(name)
+    if not os.path.isfile(p):
+        pytest.skip(f"{name} not recorded yet")
+    return np.load(p)
+
+
+def _cu(x, dtype=None):
+    t = torch.as_tensor(np.ascontiguousarray(x)).to(DEV)
+    return t if dtype is None else t.to(dtype)
+
+
+def _bits(x):
+    return np.ascontiguousarray(x).view(np.int32)
+
+
+def _loss_inputs(syn, w, seed):
+    b = syn.make_batch(w, seed=seed)
+    return b, syn.reference_match_all(b)
+
+
+def _rel_close(a, b, rtol, atol=0.0):
+    a, b = np.asarray(a, np.float64), np.asarray(b, np.float64)
+    assert np.array_equal(np.isfinite(a), np.isfinite(b))
+    fin = np.isfinite(a)
+    err = np.abs(a[fin] - b[fin])
+    assert (err <= atol + rtol * np.abs(b[fin])).all(), float(err.max())
+
+
+CASES = [
+    ("tiny", dict(batch=2, vocab=100, hidden=8, fixed_graph=32, fixed_target=10), 0),
+    ("ragged", dict(batch=7, vocab=100, hidden=8, src_min=2, src_max=21), 1),
+    ("mid", dict(batch=4, vocab=100, hidden=8, src_min=30, src_max=40), 2),
+    ("wide", dict(batch=2, vocab=100, hidden=8, fixed_graph=256, fixed_target=40), 3),
+    ("global_links", dict(batch=2, vocab=100, hidden=8, fixed_graph=400, fixed_target=30), 4),
+]
+
+
+@pytest.mark.parametrize("name,kw,seed", CASES)
+def test_loss_forward_against_oracle(ops, syn, name, kw, seed):
+    b, ma = _loss_inputs(syn, syn.Workload(name, emissions="logits", **kw), seed)
+    k = ops.get_pcfg_kernel()
+    S, C = k.pcfg_loss(ma.to(DEV), b.links.to(DEV), b.output_length.to(DEV), b.target_length.to(DEV), 1)
+    So, Co = oracle.pcfg_loss(ma.numpy(), b.links.numpy(), b.output_length.numpy(), b.target_length.numpy())
+    _rel_close(S.cpu().numpy(), So, 1e-5, 1e-5)
+    assert np.array_equal(_bits(C.cpu().numpy()), _bits(Co))
+    _rel_close(S[:, 0, 0].cpu().numpy(), So[:, 0, 0], 1e-4)
+    loss = ops.cuda_pcfg_loss(ma.to(DEV), b.links.to(DEV), b.output_length.to(DEV), b.target_length.to(DEV))
+    assert np.array_equal(_bits(loss.cpu().numpy()), _bits(S[:, 0, 0].cpu().numpy()))
+
+
+@pytest.mark.parametrize("name,kw,seed", CASES)
+def test_loss_backward_against_oracle(ops, syn, name, kw, seed):
+    b, ma = _loss_inputs(syn, syn.Workload(name, emissions="logits", **kw), seed)
+    ol, tl = b.output_length.numpy(), b.target_length.numpy()
+    So, Co = oracle.pcfg_loss(ma.numpy(), b.links.numpy(), ol, tl)
+    go = np.linspace(0.5, 2.0, b.B).astype(np.float32)
+    mgo, lgo = oracle.pcfg_loss_backward(go, So, Co, ma.numpy(), b.links.numpy(), ol, tl)
+    k = ops.get_pcfg_kernel()
+    S, C = k.pcfg_loss(ma.to(DEV), b.links.to(DEV), b.output_length.to(DEV), b.target_length.to(DEV), 1)
+    mg, lg = k.pcfg_loss_backward(_cu(go), S, C, ma.to(DEV), b.links.to(DEV), b.output_length.to(DEV),
+                                  b.target_length.to(DEV), 1)
+    np.testing.assert_allclose(mg.cpu().numpy(), mgo, rtol=1e-3, atol=2e-6)
+    np.testing.assert_allclose(lg.cpu().numpy(), lgo, rtol=1e-3, atol=2e-6)
+    # fused entry point and the autograd wrapper give the same gradients (scaled by grad_output)
+    mat = ma.to(DEV).requires_grad_(True)
+    lkt = b.links.to(DEV).requires_grad_(True)
+    loss = ops.cuda_pcfg_loss(mat, lkt, b.output_length.to(DEV), b.target_length.to(DEV))
+    fin = torch.isfinite(loss)
+    (loss[fin] * _cu(go)[fin]).sum().backward()
+    fin_np = fin.cpu().numpy()
+    np.testing.assert_allclose(mat.grad.cpu().numpy()[fin_np], mgo[fin_np], rtol=1e-3, atol=2e-6)
+    np.testing.assert_allclose(lkt.grad.cpu().numpy()[fin_np], lgo[fin_np], rtol=1e-3, atol=2e-6)
+
+
+@pytest.mark.parametrize("name,kw,seed", CASES)
+def test_best_tree_bit_exact_on_shared_tables(ops, syn, name, kw, seed):
+    b, ma = _loss_inputs(syn, syn.Workload(name, emissions="logits", **kw), seed)
+    ol, tl = b.output_length.numpy(), b.target_length.numpy()
+    So, Co = oracle.pcfg_loss(ma.numpy(), b.links.numpy(), ol, tl)
+    want = oracle.pcfg_best_tree(So, Co, ma.numpy(), b.links.numpy(), ol, tl)
+    got = ops.get_pcfg_kernel().pcfg_best_tree(_cu(So), _cu(Co), ma.to(DEV), b.links.to(DEV), b.output_length.to(DEV),
+                                               b.target_length.to(DEV), 1)
+    np.testing.assert_array_equal(got.cpu().numpy(), want)
+
+
+def test_best_tree_tie_breaking(ops):
+    # all transitions and emissions equal: every arg-max is a tie, so the result is decided by the
+    # reference's lane order (0, 2, 1, 3), then smallest right child, then "no left child" first
+    B, L, T = 1, 40, 9
+    ma = np.zeros((B, L, T), np.float32)
+    ma[0, :, T - 1] = -np.inf
+    ma[0, L - 1, T - 1] = 0.0
+    lk = np.full((B, L, 2, L), -np.inf, np.float32)
+    for a in range(1, L - 1, 2):
+        lk[0, a, 0, a + 2::2] = -1.0
+        if a >= 3:
+            lk[0, a, 1, a + 2::2] = -1.0
+    ol, tl = np.array([L]), np.array([T])
+    So, Co = oracle.pcfg_loss(ma, lk, ol, tl)
+    So = np.where(np.isfinite(So), np.float32(-3.0), So)  # flatten the table: exact ties everywhere
+    want = oracle.pcfg_best_tree(So, Co, ma, lk, ol, tl)
+    got = ops.get_pcfg_kernel().pcfg_best_tree(_cu(So), None, _cu(ma), _cu(lk), _cu(ol), _cu(tl), 1)
+    np.testing.assert_array_equal(got.cpu().numpy(), want)
+    assert (want >= 0).sum() >= 2
+
+
+@pytest.mark.parametrize("name", ["ref_loss_tiny.npz", "ref_loss_ragged.npz", "ref_loss_mid.npz"])
+def test_loss_against_reference_golden(ops, name):
+    g = _g(name)
+    k = ops.get_pcfg_kernel()
+    ma, lk, ol, tl = _cu(g["match_all"]), _cu(g["links"]), _cu(g["output_length"]), _cu(g["target_length"])
+    S, C = k.pcfg_loss(ma, lk, ol, tl, 1)
+    assert np.array_equal(_bits(S.cpu().numpy()), _bits(g["S"]))  # bit-identical to the reference kernel
+    assert np.array_equal(_bits(C.cpu().numpy()), _bits(g["C"]))
+    mg, lg = k.pcfg_loss_backward(torch.ones(len(ol), device=DEV), S, C, ma, lk, ol, tl, 1)
+    np.testing.assert_allclose(mg.cpu().numpy(), g["match_all_grad"], rtol=1e-3, atol=2e-6)
+    np.testing.assert_allclose(lg.cpu().numpy(), g["links_grad"], rtol=1e-3, atol=2e-6)
+    tree, loss = ops.cuda_pcfg_best_tree(ma, lk, ol, tl)
+    np.testing.assert_array_equal(tree.cpu().numpy(), g["tree"])
+    assert np.array_equal(_bits(loss.cpu().numpy()), _bits(g["S"][:, 0, 0]))
+
+
+VCASES = [
+    ("v_ragged", dict(batch=6, vocab=80, hidden=8, src_min=2, src_max=20), 0),
+    ("v_mid", dict(batch=3, vocab=80, hidden=8, src_min=40, src_max=60), 1),
+    ("v_global_links", dict(batch=2, vocab=80, hidden=8, fixed_graph=400), 2),
+]
+
+
+def _viterbi_inputs(syn, name, kw, seed):
+    b = syn.make_batch(syn.Workload(name, emissions="logits", kind="viterbi", **kw), seed=seed)
+    ob, tok = torch.log_softmax(b.logits, -1).max(-1)
+    return b, ob.contiguous(), tok.contiguous()
+
+
+@pytest.mark.parametrize("name,kw,seed", VCASES)
+def test_viterbi_bit_exact_against_oracle(ops, syn, name, kw, seed):
+    b, ob, tok = _viterbi_inputs(syn, name, kw, seed)
+    S, R, Lt, Mt = ops.get_pcfg_kernel().pcfg_viterbi(ob.to(DEV), b.links.to(DEV), b.output_length.to(DEV), 1)
+    So, Ro, Lo, Mo = oracle.pcfg_viterbi(ob.numpy(), b.links.numpy(), b.output_length.numpy())
+    assert np.array_equal(_bits(S.cpu().numpy()), _bits(So))
+    np.testing.assert_array_equal(R.cpu().numpy(), Ro)
+    np.testing.assert_array_equal(Lt.cpu().numpy(), Lo)
+    np.testing.assert_array_equal(Mt.cpu().numpy(), Mo)
+    scores, R2, L2, M2 = ops.cuda_pcfg_viterbi(ob.to(DEV), b.links.to(DEV), b.output_length.to(DEV))
+    assert np.array_equal(_bits(scores.cpu().numpy()), _bits(So[:, 1, :]))
+    # length-penalised arg-max as the model does it, then the back-trace on the device
+    sc = scores / torch.arange(b.L // 4, device=DEV).unsqueeze(0)
+    sc.masked_fill_(sc.isnan(), float("-inf"))
+    pred = sc[:, 1:].max(-1)[1] + 1
+    mask = b.left_tree_mask.long()
+    want = oracle.viterbi_decoding(pred.cpu().numpy(), b.output_length.numpy(), Lo, Ro, Mo, tok.numpy(), mask.numpy(), 1)
+    got = ops.viterbi_decoding(pred, b.output_length.to(DEV), L2, R2, M2, tok.to(DEV), mask.to(DEV), 1)
+    assert got.dtype == torch.float32 and got.is_cuda
+    np.testing.assert_array_equal(got.cpu().numpy(), want)
+    # the reference call pattern: traces moved to the host first
+    got_cpu = ops.viterbi_decoding(pred.cpu(), b.output_length, L2.cpu(), R2.cpu(), M2.cpu(), tok, mask, 1)
+    assert not got_cpu.is_cuda
+    np.testing.assert_array_equal(got_cpu.numpy(), want)
+
+
+@pytest.mark.parametrize("name", ["ref_viterbi_ragged.npz", "ref_viterbi_mid.npz"])
+def test_viterbi_against_reference_golden(ops, name):
+    g = _g(name)
+    S, R, Lt, Mt = ops.get_pcfg_kernel().pcfg_viterbi(_cu(g["ob_lprob"]), _cu(g["links"]), _cu(g["output_length"]), 1)
+    assert np.array_equal(_bits(S.cpu().numpy()), _bits(g["S"]))
+    np.testing.assert_array_equal(R.cpu().numpy(), g["R"])
+    np.testing.assert_array_equal(Lt.cpu().numpy(), g["L"])
+    np.testing.assert_array_equal(Mt.cpu().numpy(), g["M"])
+
+
+def test_backtrace_against_reference_host_golden(ops):
+    g = np.load(golden_path("host_viterbi_decoding.npz"))
+    got = ops.viterbi_decoding(_cu(g["pred_length"]), _cu(g["output_length"]), _cu(g["L"]), _cu(g["R"]), _cu(g["M"]),
+                               _cu(g["tokens"]), _cu(g["left_tree_mask"].astype(np.int64)), 1)
+    np.testing.assert_array_equal(got.cpu().numpy().astype(np.int64), g["decoded"])
+
+
+@pytest.mark.parametrize("dtype,atol", [(torch.float32, 2e-5), (torch.float16, 2e-5)])
+@pytest.mark.parametrize("V", [1000, 40000, 997])
+def test_logsoftmax_gather_against_oracle(ops, dtype, atol, V):
+    g = torch.Generator().manual_seed(V)
+    B, L, slen = 2, 6, 11
+    x = (torch.randn(B, L, V, generator=g) * 3).to(dtype)
+    tgt = torch.randint(0, V, (B, slen), generator=g)
+    sel_idx = tgt[:, None, :].expand(-1, L, -1)  # stride-0 expand, as the criterion passes it
+    want, probs = oracle.logsoftmax_gather(x.float().numpy(), sel_idx.numpy(), True)
+    k = ops.get_pcfg_kernel()
+    xc = x.to(DEV).clone()
+    got = k.logsoftmax_gather(xc, sel_idx.to(DEV), False)
+    np.testing.assert_allclose(got.cpu().numpy(), want, atol=atol + 1e-4)
+    assert torch.equal(xc.cpu(), x)  # untouched without require_gradient
+    got2 = k.logsoftmax_gather(xc, sel_idx.to(DEV), True)
+    np.testing.assert_allclose(got2.cpu().numpy(), want, atol=atol + 1e-4)
+    np.testing.assert_allclose(xc.float().cpu().numpy(), probs, atol=1e-6 if dtype == torch.float32 else 1e-3,
+                               rtol=1e-4 if dtype == torch.float32 else 2e-3)
+
+
+def test_logsoftmax_gather_reference_golden_and_autograd(ops):
+    g = _g("ref_logsoftmax_gather.npz")
+    k = ops.get_pcfg_kernel()
+    sel_idx = _cu(g["targets"])[:, None, :].expand(-1, 8, -1)
+    for tag, dt in (("f32", torch.float32), ("f16", torch.float16)):
+        x = _cu(g["logits"]).to(dt).contiguous()
+        got = k.logsoftmax_gather(x, sel_idx, True)
+        np.testing.assert_allclose(got.cpu().numpy(), g[f"selected_{tag}_1"], atol=1e-4)
+        np.testing.assert_allclose(x.float().cpu().numpy(), g[f"probs_{tag}"], atol=1e-3 if dt == torch.float16 else 1e-6,
+                                   rtol=1e-3)
+    # autograd through the in-place function equals autograd through log_softmax + gather
+    x0 = _cu(g["logits"])
+    w = torch.randn(2, 8, 10, device=DEV, generator=torch.Generator(DEV).manual_seed(0))
+    xa = x0.clone().requires_grad_(True)
+    (torch.log_softmax(xa, -1).gather(2, sel_idx) * w).sum().backward()
+    xb = x0.clone().requires_grad_(True)
+    _, sel = ops.dag_logsoftmax_gather_inplace(xb * 1.0, sel_idx)
+    (sel * w).sum().backward()
+    np.testing.assert_allclose(xb.grad.cpu().numpy(), xa.grad.cpu().numpy(), atol=1e-5)
+
+
+def test_invalid_sentences_are_skipped_not_faulted(ops, syn):
+    b, ma = _loss_inputs(syn, syn.Workload("bad", batch=4, vocab=50, hidden=8, src_min=4, src_max=6,
+                                           emissions="logits"), 9)
+    ol = b.output_length.clone()
+    tl = b.target_length.clone()
+    ol[1] = b.L + 5  # more nodes than the graph holds
+    tl[2] = 0  # empty target
+    ops.read_status(DEV)
+    mat, lkt = ma.to(DEV).requires_grad_(True), b.links.to(DEV).requires_grad_(True)
+    loss = ops.cuda_pcfg_loss(mat, lkt, ol.to(DEV), tl.to(DEV))
+    assert torch.isinf(loss[1]) and torch.isinf(loss[2]) and torch.isfinite(loss[0]) and torch.isfinite(loss[3])
+    loss[[0, 3]].sum().backward()
+    assert float(mat.grad[1].abs().sum()) == 0.0 and float(lkt.grad[2].abs().sum()) == 0.0
+    tree, _ = ops.cuda_pcfg_best_tree(ma.to(DEV), b.links.to(DEV), ol.to(DEV), tl.to(DEV))
+    assert (tree[1] == -1).all() and (tree[2] == -1).all()
+    assert ops.read_status(DEV) & 1  # PCFGNAT_STATUS_BAD_LENGTH
+    # odd graph length: node m-1 is a leaf; the oracle restates what the reference does with it
+    ol2 = b.output_length.clone()
+    ol2[0] -= 1
+    ol2[3] -= 1
+    lp = torch.log_softmax(b.logits, -1)
+    ma2 = lp.gather(2, b.targets[:, None, :].expand(-1, b.L, -1)).contiguous()
+    syn.eos_mask_(ma2, ol2, b.target_length)
+    S, C = ops.get_pcfg_kernel().pcfg_loss(ma2.to(DEV), b.links.to(DEV), ol2.to(DEV), b.target_length.to(DEV), 1)
+    So, Co = oracle.pcfg_loss(ma2.numpy(), b.links.numpy(), ol2.numpy(), b.target_length.numpy())
+    _rel_close(S.cpu().numpy(), So, 1e-5, 1e-5)
+    mg, lg = ops.get_pcfg_kernel().pcfg_loss_backward(torch.ones(4, device=DEV), S, C, ma2.to(DEV), b.links.to(DEV),
+                                                      ol2.to(DEV), b.target_length.to(DEV), 1)
+    mgo, lgo = oracle.pcfg_loss_backward(np.ones(4, np.float32), So, Co, ma2.numpy(), b.links.numpy(), ol2.numpy(),
+                                         b.target_length.numpy())
+    np.testing.assert_allclose(mg.cpu().numpy(), mgo, rtol=1e-3, atol=2e-6)
+    np.testing.assert_allclose(lg.cpu().numpy(), lgo, rtol=1e-3, atol=2e-6)
+    want = oracle.pcfg_best_tree(So, Co, ma2.numpy(), b.links.numpy(), ol2.numpy(), b.target_length.numpy())
+    got = ops.get_pcfg_kernel().pcfg_best_tree(_cu(So), None, ma2.to(DEV), b.links.to(DEV), ol2.to(DEV),
+                                               b.target_length.to(DEV), 1)
+    np.testing.assert_array_equal(got.cpu().numpy(), want)
+
+
+def test_argument_errors(ops):
+    k = ops.get_pcfg_kernel()
+    ma = torch.zeros(1, 10, 3, device=DEV)
+    with pytest.raises(RuntimeError, match="max_left"):
+        k.pcfg_loss(ma, torch.zeros(1, 10, 4, 10, device=DEV), torch.tensor([10]), torch.tensor([3]), 1)
+    with pytest.raises(RuntimeError, match="float32"):
+        k.pcfg_loss(ma.double(), torch.zeros(1, 10, 2, 10, device=DEV), torch.tensor([10]), torch.tensor([3]), 1)
+    with pytest.raises(RuntimeError, match="config should be 1~4"):
+        k.pcfg_viterbi(torch.zeros(1, 16, device=DEV), torch.zeros(1, 16, 2, 16, device=DEV), torch.tensor([16]), 7)
+    with pytest.raises(RuntimeError, match="select_idx should be long"):
+        k.logsoftmax_gather(torch.zeros(1, 2, 5, device=DEV), torch.zeros(1, 2, 1, device=DEV, dtype=torch.int32), False)
+    with pytest.raises(RuntimeError, match="not contiguous"):
+        k.logsoftmax_gather(torch.zeros(1, 5, 2, device=DEV).transpose(1, 2), torch.zeros(1, 2, 1, device=DEV, dtype=torch.long), False)
+
+
+# ---- full-size workloads: properties that need no oracle run ---------------------------------------------------
+
+@pytest.mark.parametrize("wname", ["glance", "long_seq"])
+def test_full_size_properties(ops, syn, wname):
+    w = syn.WORKLOADS[wname]
+    b = syn.make_batch(syn.Workload(w.name, batch=w.batch, vocab=64, hidden=8, fixed_graph=w.fixed_graph,
+                                    fixed_target=w.fixed_target, emissions="logits"), seed=0)
+    ma = syn.reference_match_all(b).to(DEV).requires_grad_(True)
+    lk = b.links.to(DEV).requires_grad_(True)
+    ol, tl = b.output_length.to(DEV), b.target_length.to(DEV)
+    loss = ops.cuda_pcfg_loss(ma, lk, ol, tl)
+    assert torch.isfinite(loss).all()
+    loss.sum().backward()
+    n = int(b.target_length[0])
+    # posterior marginals: each target position is emitted by exactly one node
+    torch.testing.assert_close(ma.grad.sum(1)[:, :n], torch.ones(b.B, n, device=DEV), rtol=0, atol=2e-3)
+    # expected number of binary rule uses = expected number of main-chain nodes used - 1
+    used_main = ma.grad[:, 1::2, :].sum((1, 2))
+    torch.testing.assert_close(lk.grad.sum((1, 2, 3)), used_main - 1, rtol=0, atol=5e-3)
+    tree, loss2 = ops.cuda_pcfg_best_tree(ma.detach(), lk.detach(), ol, tl)
+    assert torch.equal(loss2, loss.detach())
+    t = tree.cpu().numpy()
+    for i in range(b.B):
+        used = t[i][t[i] >= 0]
+        assert used.tolist() == list(range(n))
+        assert t[i, 1] == 0 and t[i, int(b.output_length[i]) - 1] == n - 1
+
+
+def test_full_size_viterbi_properties(ops, syn):
+    b = syn.make_batch(syn.Workload("v64", batch=64, vocab=64, hidden=8, src_min=10, src_max=60, emissions="logits",
+                                    kind="viterbi"), seed=0)
+    ob, tok = torch.log_softmax(b.logits, -1).max(-1)
+    tok = torch.arange(b.L)[None, :].expand(b.B, -1).contiguous() + 100
+    scores, R, Lt, Mt = ops.cuda_pcfg_viterbi(ob.to(DEV), b.links.to(DEV), b.output_length.to(DEV))
+    sc = scores / torch.arange(b.L // 4, device=DEV).unsqueeze(0)
+    sc.masked_fill_(sc.isnan(), float("-inf"))
+    pred = sc[:, 1:].max(-1)[1] + 1
+    out = ops.viterbi_decoding(pred, b.output_length.to(DEV), Lt, R, Mt, tok.to(DEV), b.left_tree_mask.long().to(DEV), 1)
+    out = out.cpu().numpy()
+    for i in range(b.B):
+        row = out[i][out[i] != 1]
+        assert len(row) == int(pred[i]) and row[0] == 101 and row[-1] == 100 + int(b.output_length[i]) - 1
+        assert (np.diff(row) > 0).all()
+
+
+# ---- live comparison with the reference kernels (only where the reference build travelled along) ------------------
+
+def _ref():
+    from oracle.build_ref import load_ref, ref_so_path
+
+    if not os.path.isfile(ref_so_path()):
+        pytest.skip("reference extension not built")
+    return load_ref()
+
+
+@pytest.mark.parametrize("seed", [10, 11, 12])
+def test_live_against_reference_kernels(ops, syn, seed):
+    ref = _ref()
+    # graph length <= 256 keeps every reference launch at one row segment per sentence (no
+    # dependence on co-resident blocks in its spin-waits)
+    w = syn.Workload("live", batch=8, vocab=120, hidden=8, src_min=6, src_max=64, emissions="logits")
+    b, ma = _loss_inputs(syn, w, seed)
+    ma_d, lk_d = ma.to(DEV), b.links.to(DEV)
+    ol, tl = b.output_length.to(DEV), b.target_length.to(DEV)
+    k = ops.get_pcfg_kernel()
+    Sr, Cr = ref.pcfg_loss(ma_d, lk_d, ol, tl, 1)
+    S, C = k.pcfg_loss(ma_d, lk_d, ol, tl, 1)
+    assert torch.equal(S.view(torch.int32), Sr.view(torch.int32))
+    assert torch.equal(C.view(torch.int32), Cr.view(torch.int32))
+    mgr, lgr = ref.pcfg_loss_backward(torch.ones(b.B, device=DEV), Sr, Cr, ma_d, lk_d, ol, tl, 1)
+    mg, lg = k.pcfg_loss_backward(torch.ones(b.B, device=DEV), S, C, ma_d, lk_d, ol, tl, 1)
+    torch.testing.assert_close(mg, mgr, rtol=1e-3, atol=2e-6)
+    torch.testing.assert_close(lg, lgr, rtol=1e-3, atol=2e-6)
+    assert torch.equal(k.pcfg_best_tree(S, C, ma_d, lk_d, ol, tl, 1), ref.pcfg_best_tree(Sr, Cr, ma_d, lk_d, ol, tl, 1))
+    ob = torch.log_softmax(b.logits, -1).max(-1)[0].to(DEV)
+    for x, y in zip(k.pcfg_viterbi(ob, lk_d, ol, 1), ref.pcfg_viterbi(ob, lk_d, ol, 1)):
+        assert torch.equal(x.view(torch.int32) if x.dtype == torch.float32 else x,
+                           y.view(torch.int32) if y.dtype == torch.float32 else y)
