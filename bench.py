@@ -1,0 +1,302 @@
+"""Benchmark of the PCFG-NAT structured-loss hot path on B200.
+
+    python bench.py --gpus N --steps K --warmup W            # this implementation
+    python bench.py --impl reference ...                     # the path on the host CPU cores
+
+One "step" is one pass of the hot path over one training-shaped batch (workload
+``train_batch``: ~90 sentences, graph length 4 x source length <= 160, vocabulary 40 000,
+hidden 512, fp16 decoder states and projection weights, fp32 DP tables):
+
+    emissions  match[b, node, t] = log P(y_t | node)    fused projection + log-softmax + gather
+                                                         (+ the criterion's EOS masking)
+    loss       S[b] and d S[b] / d match, d S[b] / d links   inside + outside pass
+    scalar     -(S_b / n_b).mean() with invalid sentences masked and counted
+
+Inputs are seeded synthetic tensors of the named shapes (the WMT batches the reference
+trains on are not available offline).  With N > 1 every rank runs its own batch (weak
+scaling, as under data-parallel training); the only collective is the 3-float all-reduce
+of the loss statistics.  One JSON line is printed by rank 0.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+import __graft_entry__ as entry  # noqa: E402
+
+METRIC = "pcfg_loss_fwd_bwd_sentences_per_s"
+UNIT = "sentences/s"
+KERNELS_PER_STEP = 7  # sort_targets, proj, proj_merge, proj_poison_bad_targets, loss_fwd, outside, grad
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="train_batch")
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--cpu-sample", type=int, default=8, help="sentences in the CPU-baseline sample")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(p):
+        d = json.load(open(p))
+        return {"tflops": float(d["bf16_tflops"]), "gbs": float(d["hbm_gbs"]), "source": "measured"}
+    return {"tflops": 1590.0, "gbs": 6650.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.index), "-lms", "100"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.thread.join(timeout=5)
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            if len(r) < 9:
+                continue
+            try:
+                sm.append(float(r[1]))
+                mx.append(float(r[2]))
+            except ValueError:
+                continue
+            for name, v in zip(names, r[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def algorithmic(batch):
+    """Algorithmic work of one step from the unpadded sentence lengths."""
+    V, H = batch.weight.shape
+    rows = int(batch.output_length.sum())
+    flops_proj = 2.0 * rows * H * V
+    L_b = batch.output_length.double()
+    n_b = batch.target_length.double()
+    bytes_dp = float((8.0 * L_b * (n_b + 2.0 * L_b)).sum())  # read match + links, write both gradients
+    return {"rows": rows, "rows_padded": batch.B * batch.L, "proj_flops": flops_proj,
+            "proj_flops_padded": 2.0 * batch.B * batch.L * H * V, "dp_bytes": bytes_dp}
+
+
+def run_ours(a):
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: the product has no CPU path (use --impl reference for the CPU baseline)")
+    import torch.distributed as dist
+
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    pkg = entry.load_package()
+    import importlib
+
+    ops = importlib.import_module("pcfg_nat_b200.custom_ops.pcfg_loss")
+    k = ops.get_pcfg_kernel()
+    syn, sharding = pkg.synthetic, pkg.sharding
+
+    batch = syn.make_batch(a.workload, seed=a.seed + rank)  # every rank its own batch: weak scaling
+    alg = algorithmic(batch)
+    # host copies in pinned memory (end-to-end leg) and device-resident copies (kernel leg)
+    host = {"hidden": batch.hidden, "links": batch.links, "targets": batch.targets, "ol": batch.output_length,
+            "tl": batch.target_length}
+    host = {n: t.contiguous().pin_memory() for n, t in host.items()}
+    devt = {n: t.to(dev, non_blocking=True) for n, t in host.items()}
+    weight = batch.weight.to(dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)  # > 126 MB L2
+    h2d = sum(t.numel() * t.element_size() for t in host.values())
+    loss_host = torch.empty(3, dtype=torch.float32).pin_memory()
+
+    def step(t):
+        out = k.proj_logsoftmax_gather(t["hidden"], weight, t["targets"], t["ol"], t["tl"])
+        loss, mg, lg = k.pcfg_loss_fwd_bwd(out["match"], t["links"], t["ol"], t["tl"])
+        stats = sharding.local_loss_stats(loss, t["tl"])
+        if world > 1:
+            dist.all_reduce(stats)
+        return stats, mg, lg
+
+    def timed(n_steps, e2e, probe_proj=False):
+        """Per-step CUDA-event timing on the launching stream with an L2 flush between steps."""
+        times, proj_times = [], []
+        for _ in range(n_steps):
+            flush.fill_(1)
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            if e2e:
+                t = {n: h.to(dev, non_blocking=True) for n, h in host.items()}
+                stats, _, _ = step(t)
+                loss_host.copy_(stats, non_blocking=True)
+            elif probe_proj:
+                ps, pe = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                ps.record()
+                out = k.proj_logsoftmax_gather(devt["hidden"], weight, devt["targets"], devt["ol"], devt["tl"])
+                pe.record()
+                loss, mg, lg = k.pcfg_loss_fwd_bwd(out["match"], devt["links"], devt["ol"], devt["tl"])
+                stats = sharding.local_loss_stats(loss, devt["tl"])
+                if world > 1:
+                    dist.all_reduce(stats)
+                proj_times.append((ps, pe))
+            else:
+                step(devt)
+            e.record()
+            times.append((s, e))
+        torch.cuda.synchronize()
+        return [s.elapsed_time(e) for s, e in times], [s.elapsed_time(e) for s, e in proj_times]
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    timed(max(a.warmup, 3), False)
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    sync_all()
+    step_ms, proj_ms = timed(a.steps, False, probe_proj=True)
+    sync_all()
+    clocks = sampler.stop() if rank == 0 else None
+    timed(3, True)
+    sync_all()
+    e2e_ms, _ = timed(a.steps, True)
+    sync_all()
+    status = ops.read_status(dev)
+
+    tot = torch.tensor([sum(step_ms), sum(e2e_ms), sum(proj_ms)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(tot, op=dist.ReduceOp.MAX)
+    tot = tot.tolist()
+    sentences = batch.B * world  # same batch size on every rank
+    value = sentences * a.steps / (tot[0] / 1e3)
+    e2e_value = sentences * a.steps / (tot[1] / 1e3)
+    pk = peaks()
+    proj_avg_s = (tot[2] / a.steps) / 1e3
+    achieved = alg["proj_flops"] / proj_avg_s / 1e12
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": a.steps, "warmup": max(a.warmup, 3),
+        "ms_per_step": tot[0] / a.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f16 projection inputs, f32 accumulation and DP tables", "data": "synthetic",
+        "config": {"workload": a.workload, "sentences_per_gpu": batch.B, "graph_len_max": batch.L,
+                   "target_len_max": batch.T, "vocab": int(weight.shape[0]), "hidden": int(weight.shape[1]),
+                   "left_tree_layer": 1, "target_tokens_per_gpu": int(batch.target_length.sum()),
+                   "l2": "flushed between timed steps (256 MB write)", "parallelism": f"sentence-sharded x{world}"},
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 12,
+                "ms_per_step": tot[1] / a.steps},
+        "gpu_launches": KERNELS_PER_STEP * a.steps,
+        "roofline": {"bound": "tensor", "kernel": "proj_kernel (+ its 3 helper launches)", "achieved": achieved,
+                     "peak": pk["tflops"], "unit": "TFLOP/s", "frac": achieved / pk["tflops"],
+                     "peak_source": pk["source"] + " (burst bf16 GEMM)", "traffic": None,
+                     "ms_per_launch": proj_avg_s * 1e3, "flops_per_launch": alg["proj_flops"],
+                     "achieved_padded_rows": alg["proj_flops_padded"] / proj_avg_s / 1e12},
+        "dp": {"ms_per_step": (tot[0] - tot[2]) / a.steps, "algorithmic_bytes": alg["dp_bytes"],
+               "achieved_gbs": alg["dp_bytes"] / ((tot[0] - tot[2]) / a.steps / 1e3) / 1e9, "hbm_peak_gbs": pk["gbs"]},
+        "clocks": clocks, "device_status": status,
+    }
+    if rank == 0:
+        if world == 1 and not a.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline(a, batch)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def cpu_baseline(a, batch=None, steps=1):
+    """The same step on the host cores: the C oracle (a port of the reference kernels; the reference
+    has no CPU implementation of this path) with OpenMP over sentences, and torch's CPU GEMM for
+    the projection, on a bounded sample of the workload's sentences."""
+    import numpy as np
+
+    import oracle
+
+    pkg = entry.load_package()
+    syn = pkg.synthetic
+    if batch is None:
+        batch = syn.make_batch(a.workload, seed=a.seed)
+    n = min(a.cpu_sample, batch.B)
+    sub = batch.select(list(range(n)))
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    oracle.lib()
+    best = None
+    for _ in range(max(steps, 1)):
+        t0 = time.perf_counter()
+        logits = sub.hidden.float().reshape(-1, sub.hidden.shape[-1]) @ sub.weight.float().t()
+        lp = torch.log_softmax(logits, -1).view(n, sub.L, -1)
+        match = lp.gather(2, sub.targets[:, None, :].expand(-1, sub.L, -1)).contiguous()
+        syn.eos_mask_(match, sub.output_length, sub.target_length)
+        m_np, l_np = match.numpy(), sub.links.numpy()
+        ol, tl = sub.output_length.numpy(), sub.target_length.numpy()
+        S, C = oracle.pcfg_loss(m_np, l_np, ol, tl)
+        oracle.pcfg_loss_backward(np.ones(n, np.float32), S, C, m_np, l_np, ol, tl)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    return {"value": n / best, "unit": UNIT, "cores": cores, "kind": "port",
+            "sample": f"first {n} of {batch.B} sentences of {a.workload} (projection with torch CPU fp32 GEMM, "
+                      f"log-softmax + gather, C oracle loss forward + backward); best of {max(steps, 1)} passes, "
+                      f"{best:.3f} s per pass"}
+
+
+def run_reference(a):
+    rank = int(os.environ.get("RANK", 0))
+    if rank != 0:
+        return
+    cb = cpu_baseline(a, None, steps=max(1, min(a.steps, 3)))
+    line = {"impl": "reference", "metric": METRIC, "value": cb["value"], "unit": UNIT, "n_gpus": a.gpus,
+            "steps": a.steps, "warmup": a.warmup, "ms_per_step": None, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32 on the CPU", "data": "synthetic",
+            "config": {"workload": a.workload}, "cpu_baseline": cb,
+            "e2e": {"value": cb["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+if __name__ == "__main__":
+    args = parse()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)

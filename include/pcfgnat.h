@@ -111,6 +111,26 @@ int pcfgnat_logsoftmax_gather(void *logits, int dtype, const int64_t *select_idx
                               int64_t stride_s, int64_t rows, int64_t rows_per_batch, int V, int slen,
                               int require_gradient, float *selected, int *status, void *stream);
 
+/* Fused output projection + log-softmax + target gather / row max on the tensor cores; the
+ * [rows, V] logits are never written to memory.  New entry point: it stands in for the chain
+ * output_projection (fs_plugins/models/glat_decomposed_with_link_two_hands_tri_pcfg.py:237, a
+ * cuBLAS GEMM inside nn.Linear) -> logsoftmax_gather (fs_plugins/custom_ops/logsoftmax_gather.cu:295-359)
+ * on the training / glancing side, and output_projection -> log_softmax(-1).max(-1)
+ * (models/...pcfg.py:414-415) on the decoding side.
+ * hidden [B*L][H] f16, weight [V][H] f16 (both 16-byte aligned, H a multiple of 64, H <= 512);
+ * targets [B][T] int64 or NULL.  Outputs, each optional (NULL = not wanted):
+ *   match     [B*L][T] f32  log P(target t | row); with output_length and target_length given
+ *                           the criterion's EOS masking is applied
+ *                           (fs_plugins/criterions/nat_pcfg_loss.py:112-115)
+ *   max_lprob [B*L]    f32  max_v log P(v | row),   argmax [B*L] int64 its index
+ *   lse       [B*L]    f32  log-sum-exp of the row's logits
+ * workspace: pcfgnat_proj_workspace_bytes(B, L, T, V) bytes, 16-byte aligned. */
+size_t pcfgnat_proj_workspace_bytes(int B, int L, int T, int V);
+int pcfgnat_proj_logsoftmax_gather(const void *hidden, const void *weight, const int64_t *targets,
+                                   const int64_t *output_length, const int64_t *target_length, int B, int L, int T,
+                                   int V, int H, float *match, float *max_lprob, int64_t *argmax, float *lse,
+                                   void *workspace, size_t workspace_bytes, int *status, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

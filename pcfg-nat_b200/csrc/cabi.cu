@@ -117,4 +117,22 @@ int pcfgnat_logsoftmax_gather(void *logits, int dtype, const int64_t *select_idx
                                     slen, require_gradient, selected, status, static_cast<cudaStream_t>(stream));
 }
 
+size_t pcfgnat_proj_workspace_bytes(int B, int L, int T, int V) {
+    if (B < 0 || L < 1 || T < 0 || V < 1) return 0;
+    return proj_workspace_bytes(B, L, T, V);
+}
+
+int pcfgnat_proj_logsoftmax_gather(const void *hidden, const void *weight, const int64_t *targets,
+                                   const int64_t *output_length, const int64_t *target_length, int B, int L, int T,
+                                   int V, int H, float *match, float *max_lprob, int64_t *argmax, float *lse,
+                                   void *workspace, size_t workspace_bytes, int *status, void *stream) {
+    if (B < 0 || L < 1 || T < 0 || V < 1 || H < 1) return PCFGNAT_ERR_INVALID_ARGUMENT;
+    if ((long long)B * L > (1ll << 30)) return PCFGNAT_ERR_TOO_LARGE;
+    if (B && (!hidden || !weight || !workspace)) return PCFGNAT_ERR_INVALID_ARGUMENT;
+    if (match && (!targets || T < 1)) return PCFGNAT_ERR_INVALID_ARGUMENT;
+    if ((output_length == nullptr) != (target_length == nullptr)) return PCFGNAT_ERR_INVALID_ARGUMENT;
+    return launch_proj(hidden, weight, targets, output_length, target_length, B, L, T, V, H, match, max_lprob, argmax,
+                       lse, workspace, workspace_bytes, status, static_cast<cudaStream_t>(stream));
+}
+
 }  // extern "C"

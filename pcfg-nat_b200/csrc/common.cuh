@@ -45,4 +45,9 @@ int launch_logsoftmax_gather(void *logits, int dtype, const int64_t *sel, int64_
                              int64_t rows, int64_t rpb, int V, int slen, int req_grad, float *selected, int *status,
                              cudaStream_t st);
 
+size_t proj_workspace_bytes(int B, int L, int T, int V);
+int launch_proj(const void *hidden, const void *weight, const int64_t *targets, const int64_t *ol, const int64_t *tl,
+                int B, int L, int T, int V, int H, float *match, float *max_lprob, int64_t *argmax, float *lse,
+                void *workspace, size_t ws_bytes, int *status, cudaStream_t st);
+
 }  // namespace pcfgnat

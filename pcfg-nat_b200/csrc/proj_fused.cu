@@ -1,0 +1,527 @@
+// Fused output projection + log-softmax + target gather / row max (the only dense contraction
+// of the path, so the only tensor-core kernel).
+//
+// Replaces, without ever writing the [rows, V] logits to HBM:
+//   logits = output_projection(features)                (models/glat_decomposed_with_link_two_hands_tri_pcfg.py:237)
+//   match  = logsoftmax_gather(logits, targets)         (fs_plugins/custom_ops/logsoftmax_gather.cu:240-292)
+//   lprob, token = logits.log_softmax(-1).max(-1)       (models/...pcfg.py:414-415)
+//
+// Shape of the kernel (sm_100a only: tcgen05 tensor cores, TMEM accumulators, TMA):
+//   * one CTA per (128-row tile of the decoder states, contiguous range of 256-wide vocabulary
+//     tiles).  The 128 x H fp16 state tile stays resident in shared memory (H <= 512: 128 KB),
+//     the projection matrix streams through a 3-stage ring of 256 x 64 fp16 tiles (32 KB each);
+//   * warp 0 drives TMA (cp.async.bulk.tensor, 128-byte swizzle, no multicast), warp 1 issues
+//     tcgen05.mma 128x256x16 (fp16 in, fp32 accumulate) into one of two 256-column TMEM
+//     accumulators, warps 2-5 are the epilogue: each thread owns one row, reads its
+//     accumulator with tcgen05.ld and keeps an online (max, sum-exp), the running arg-max and
+//     the raw logits of this row's targets, while the MMA warp already fills the other
+//     accumulator;
+//   * a second, tiny kernel merges the per-range partials: lse, match = logit - lse (with the
+//     criterion's EOS masking fused if lengths are given), max log-prob and arg-max.
+// Every wait on an mbarrier is bounded; on expiry the CTA records PCFGNAT_STATUS_TIMEOUT, stops
+// issuing work, and still frees its tensor memory.
+#include <cuda.h>
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+
+namespace pcfgnat {
+
+namespace {
+
+constexpr int BM = 128;        // rows per CTA (TMEM lanes)
+constexpr int BN = 256;        // vocabulary columns per MMA tile (TMEM columns per accumulator)
+constexpr int BK = 64;         // K elements per smem tile row: 64 fp16 = 128 B = one swizzle span
+constexpr int UK = 16;         // K per tcgen05.mma for 16-bit inputs
+constexpr int NSTAGE = 3;      // W ring depth
+constexpr int KC_MAX = 8;      // H <= 512
+constexpr int A_CHUNK_BYTES = BM * BK * 2;  // 16 KB
+constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KB
+constexpr int PROJ_THREADS = 192;           // 6 warps
+constexpr uint32_t kSpinLimit = 1u << 22;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+// tcgen05 instruction descriptor, kind::f16: D = F32 (bits 4-5 = 1), A = B = F16 (0), both K-major (0),
+// N >> 3 at bits 17-22, M >> 4 at bits 24-28.
+constexpr uint32_t kIdesc = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+
+struct Partial {  // per (vocabulary range, row)
+    float m, s, best;
+    int best_idx;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("{ .reg .b64 st; mbarrier.arrive.shared::cta.b64 st, [%0]; }" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("{ .reg .b64 st; mbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1; }" ::"r"(bar), "r"(bytes)
+                 : "memory");
+}
+// Bounded wait: returns false when the limit ran out or another role already gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+    for (uint32_t it = 0; it < kSpinLimit; ++it) {
+        uint32_t ok;
+        asm volatile(
+            "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.b32 %0, 1, 0, p; }"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (ok) return true;
+        if (it > 32) __nanosleep(128);
+        if ((it & 255u) == 255u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
+        : "memory");
+}
+
+// K-major, 128-byte-swizzled operand tile: rows at 128 B pitch, 8-row groups 1024 B apart.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
+    return (uint64_t)((saddr >> 4) & 0x3FFFu) | (1ull << 16) /* leading byte offset (unused with swizzle) */
+           | (64ull << 32)                                   /* stride byte offset 1024 B >> 4 */
+           | (1ull << 46)                                    /* descriptor version of sm_100 */
+           | (2ull << 61);                                   /* SWIZZLE_128B */
+}
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "l"(da), "l"(db), "r"(kIdesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float *v) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; i++) v[i] = __uint_as_float(r[i]);
+}
+
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// ---------------------------------------------------------------------------------------
+// target lists sorted by token id, one per sentence
+// ---------------------------------------------------------------------------------------
+__global__ void sort_targets_kernel(const int64_t *__restrict__ targets, int T, int V, int *stok, int *sslot,
+                                    int *status) {
+    const int b = blockIdx.x;
+    const int64_t *tg = targets + (size_t)b * T;
+    for (int s = threadIdx.x; s < T; s += blockDim.x) {
+        int64_t mine = tg[s];
+        const bool bad = mine < 0 || mine >= V;
+        if (bad) flag(status, PCFGNAT_STATUS_BAD_INDEX);
+        const int64_t key = bad ? (int64_t)INT_MAX : mine;
+        int rank = 0;
+        for (int j = 0; j < T; j++) {
+            int64_t o = tg[j];
+            if (o < 0 || o >= V) o = INT_MAX;
+            rank += (o < key) || (o == key && j < s);
+        }
+        stok[(size_t)b * T + rank] = (int)key;
+        sslot[(size_t)b * T + rank] = s;
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// main kernel
+// ---------------------------------------------------------------------------------------
+template <bool WANT_ARGMAX>
+__global__ void __launch_bounds__(PROJ_THREADS, 1)
+    proj_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, int N, int V,
+                int KC, int L, int T, int tiles_per_split, const int *__restrict__ stok,
+                const int *__restrict__ sslot, float *match, Partial *partials, int *status) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t bars[2 * NSTAGE + 1 + 4];
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int abort_flag_s;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row0 = blockIdx.x * BM;
+    const int split = blockIdx.y;
+    const int n_tiles_total = (V + BN - 1) / BN;
+    const int t_begin = split * tiles_per_split;
+    const int t_end = min(n_tiles_total, t_begin + tiles_per_split);
+    const int n_tiles = t_end - t_begin;  // >= 1 by construction of the grid
+
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    const uint32_t smem_a = smem_u32(smem);
+    const uint32_t smem_b = smem_a + KC_MAX * A_CHUNK_BYTES;
+    const uint32_t bar_full = smem_u32(&bars[0]);             // [NSTAGE]
+    const uint32_t bar_empty = smem_u32(&bars[NSTAGE]);       // [NSTAGE]
+    const uint32_t bar_a = smem_u32(&bars[2 * NSTAGE]);       // A tile landed
+    const uint32_t bar_tfull = smem_u32(&bars[2 * NSTAGE + 1]);   // [2] accumulator ready
+    const uint32_t bar_tempty = smem_u32(&bars[2 * NSTAGE + 3]);  // [2] accumulator drained
+    volatile int *abort_flag = &abort_flag_s;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < NSTAGE; i++) {
+            mbar_init(bar_full + 8 * i, 1);
+            mbar_init(bar_empty + 8 * i, 1);
+        }
+        mbar_init(bar_a, 1);
+        for (int i = 0; i < 2; i++) {
+            mbar_init(bar_tfull + 8 * i, 1);
+            mbar_init(bar_tempty + 8 * i, 4);  // one arrival per epilogue warp
+        }
+        abort_flag_s = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
+                     "r"(2 * BN)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            mbar_expect_tx(bar_a, (uint32_t)KC * A_CHUNK_BYTES);
+            for (int kc = 0; kc < KC; kc++) tma_load_2d(smem_a + kc * A_CHUNK_BYTES, &map_a, bar_a, kc * BK, row0);
+            uint32_t it = 0;
+            bool ok = true;
+            for (int t = t_begin; t < t_end && ok; t++) {
+                for (int kc = 0; kc < KC; kc++, it++) {
+                    const uint32_t st = it % NSTAGE, ph = (it / NSTAGE) & 1;
+                    if (!mbar_wait(bar_empty + 8 * st, ph ^ 1, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                    mbar_expect_tx(bar_full + 8 * st, B_STAGE_BYTES);
+                    tma_load_2d(smem_b + st * B_STAGE_BYTES, &map_w, bar_full + 8 * st, kc * BK, t * BN);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer ------------------------------
+        if (lane == 0) {
+            bool ok = mbar_wait(bar_a, 0, abort_flag);
+            uint32_t it = 0;
+            for (int t = 0; t < n_tiles && ok; t++) {
+                const uint32_t buf = t & 1, use = t >> 1;
+                if (!mbar_wait(bar_tempty + 8 * buf, (use & 1) ^ 1, abort_flag)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t d = tmem_base + buf * BN;
+                for (int kc = 0; kc < KC; kc++, it++) {
+                    const uint32_t st = it % NSTAGE, ph = (it / NSTAGE) & 1;
+                    if (!mbar_wait(bar_full + 8 * st, ph, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint64_t da = umma_desc(smem_a + kc * A_CHUNK_BYTES);
+                    const uint64_t db = umma_desc(smem_b + st * B_STAGE_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / UK; k++)  // +32 B along K inside the swizzle span = +2 in the address field
+                        umma_f16(d, da + 2 * k, db + 2 * k, (kc | k) != 0);
+                    umma_commit(bar_empty + 8 * st);  // frees the W stage when these MMAs have read it
+                }
+                if (ok) umma_commit(bar_tfull + 8 * buf);
+            }
+        }
+    } else {
+        // ------------------------------ epilogue: one row per thread ------------------------------
+        const int sub = warp & 3;  // TMEM sub-partition this warp may read
+        const int row = row0 + sub * 32 + lane;
+        const bool row_ok = row < N;
+        const int sent = row_ok ? row / L : 0;
+        const int *my_tok = stok ? stok + (size_t)sent * T : nullptr;
+        const int *my_slot = stok ? sslot + (size_t)sent * T : nullptr;
+        float *my_out = match ? match + (size_t)row * T : nullptr;
+        int p = 0;
+        if (my_tok) {  // first target at or after this CTA's first column
+            const int c_first = t_begin * BN;
+            int lo = 0, hi = T;
+            while (lo < hi) {
+                int mid = (lo + hi) >> 1;
+                if (__ldg(my_tok + mid) < c_first) lo = mid + 1; else hi = mid;
+            }
+            p = lo;
+        }
+        float m = -CUDART_INF_F, s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+        float best = -CUDART_INF_F;
+        int best_idx = 0;
+        bool ok = true;
+        for (int t = 0; t < n_tiles && ok; t++) {
+            const uint32_t buf = t & 1, use = t >> 1;
+            if (!mbar_wait(bar_tfull + 8 * buf, use & 1, abort_flag)) {
+                ok = false;
+                break;
+            }
+            tc_fence_after();
+            const int tile_col0 = (t_begin + t) * BN;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; c++) {
+                float v[32];
+                __syncwarp();  // the gather loop below may leave the lanes diverged; tcgen05.ld is warp-collective
+                tmem_ld32(tmem_base + ((uint32_t)(sub * 32) << 16) + buf * BN + c * 32, v);
+                const int col0 = tile_col0 + c * 32;
+                if (col0 + 32 > V) {
+#pragma unroll
+                    for (int i = 0; i < 32; i++)
+                        if (col0 + i >= V) v[i] = -CUDART_INF_F;
+                }
+                float cmax = v[0];
+#pragma unroll
+                for (int i = 1; i < 32; i++) cmax = fmaxf(cmax, v[i]);
+                if (cmax > m) {
+                    const float f = ex2((m - cmax) * kLog2e);  // 0 on the first chunk (m = -inf)
+                    s0 *= f, s1 *= f, s2 *= f, s3 *= f;
+                    m = cmax;
+                }
+                if (WANT_ARGMAX && cmax > best) {
+                    best = cmax;
+                    int idx = 31;
+#pragma unroll
+                    for (int i = 30; i >= 0; i--) idx = (v[i] == cmax) ? i : idx;
+                    best_idx = col0 + idx;
+                }
+                if (m > -CUDART_INF_F) {
+                    const float nm = -m * kLog2e;
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4) {
+                        s0 += ex2(fmaf(v[i], kLog2e, nm));
+                        s1 += ex2(fmaf(v[i + 1], kLog2e, nm));
+                        s2 += ex2(fmaf(v[i + 2], kLog2e, nm));
+                        s3 += ex2(fmaf(v[i + 3], kLog2e, nm));
+                    }
+                }
+                if (my_tok) {
+                    while (p < T) {
+                        const int tk = __ldg(my_tok + p);
+                        if (tk >= col0 + 32) break;
+                        const int idx = tk - col0;
+                        if (idx >= 0 && row_ok) {
+                            float val = v[0];
+#pragma unroll
+                            for (int i = 1; i < 32; i++) val = (idx == i) ? v[i] : val;
+                            my_out[__ldg(my_slot + p)] = val;  // raw logit; the merge kernel subtracts lse
+                        }
+                        p++;
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
+        }
+        if (row_ok && ok) {
+            Partial pr;
+            pr.m = m;
+            pr.s = (s0 + s1) + (s2 + s3);
+            pr.best = best;
+            pr.best_idx = best_idx;
+            partials[(size_t)split * N + row] = pr;
+        }
+    }
+    if (*abort_flag && threadIdx.x == 0) flag(status, PCFGNAT_STATUS_TIMEOUT);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// merge of the per-range partials
+// ---------------------------------------------------------------------------------------
+__global__ void proj_merge_kernel(const Partial *__restrict__ partials, int n_splits, int N, int L, int T,
+                                  const int *__restrict__ stok, const int64_t *__restrict__ ol,
+                                  const int64_t *__restrict__ tl, float *match, float *max_lprob, int64_t *argmax,
+                                  float *lse_out) {
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (warp >= N) return;
+    const int row = warp;
+    float m = -CUDART_INF_F, best = -CUDART_INF_F;
+    int best_idx = 0;
+    for (int sp = 0; sp < n_splits; sp++) {
+        Partial p = partials[(size_t)sp * N + row];
+        m = fmaxf(m, p.m);
+        if (p.best > best) {  // ranges are visited in increasing column order: first maximum wins
+            best = p.best;
+            best_idx = p.best_idx;
+        }
+    }
+    float s = 0.f;
+    for (int sp = 0; sp < n_splits; sp++) {
+        Partial p = partials[(size_t)sp * N + row];
+        if (p.s > 0.f) s += p.s * exp2f((p.m - m) * kLog2e);
+    }
+    const float lse = m + log2f(s) * kLn2;
+    if (lane == 0) {
+        if (lse_out) lse_out[row] = lse;
+        if (max_lprob) max_lprob[row] = best - lse;
+        if (argmax) argmax[row] = best_idx;
+    }
+    if (match) {
+        const int b = row / L, l = row % L;
+        int eos_col = -1;
+        bool keep_eos = true;
+        if (ol && tl) {  // criterion's EOS masking (criterions/nat_pcfg_loss.py:112-115)
+            eos_col = (int)tl[b] - 1;
+            keep_eos = l == (int)ol[b] - 1;
+        }
+        float *out = match + (size_t)row * T;
+        for (int t = lane; t < T; t += 32) {
+            float v = out[t] - lse;
+            if (t == eos_col && !keep_eos) v = -CUDART_INF_F;
+            out[t] = v;
+        }
+    }
+}
+
+// rows whose target id is out of range get NaN (they were never gathered)
+__global__ void proj_poison_bad_targets_kernel(const int *__restrict__ stok, const int *__restrict__ sslot, int B,
+                                               int L, int T, float *match) {
+    const int b = blockIdx.x;
+    for (int p = T - 1; p >= 0 && stok[(size_t)b * T + p] == INT_MAX; p--) {
+        const int slot = sslot[(size_t)b * T + p];
+        for (int l = threadIdx.x; l < L; l += blockDim.x) match[((size_t)b * L + l) * T + slot] = CUDART_NAN_F;
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            return nullptr;
+        fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// [rows][K] fp16 row-major, box = 64 (K) x box_rows, 128-byte swizzle, out-of-bounds reads give zeros.
+bool make_map(CUtensorMap *map, const void *base, uint64_t rows, uint64_t K, uint32_t box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {K, rows};
+    cuuint64_t strides[1] = {K * 2};
+    cuuint32_t box[2] = {BK, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(base), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+struct Plan {
+    int row_tiles, n_tiles, splits, tiles_per_split;
+};
+
+Plan make_plan(int N, int V) {
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    Plan p;
+    p.row_tiles = (N + BM - 1) / BM;
+    p.n_tiles = (V + BN - 1) / BN;
+    int want = sms / p.row_tiles;  // vocabulary ranges per row tile so that one wave fills the GPU
+    if (want < 1) want = 1;
+    if (want > p.n_tiles) want = p.n_tiles;
+    p.tiles_per_split = (p.n_tiles + want - 1) / want;
+    p.splits = (p.n_tiles + p.tiles_per_split - 1) / p.tiles_per_split;
+    return p;
+}
+
+}  // namespace
+
+size_t proj_workspace_bytes(int B, int L, int T, int V) {
+    const int N = B * L;
+    Plan p = make_plan(N > 0 ? N : 1, V > 0 ? V : 1);
+    size_t lists = ((size_t)2 * B * (T > 0 ? T : 0) * sizeof(int) + 255) / 256 * 256;
+    size_t parts = ((size_t)p.splits * N * sizeof(Partial) + 255) / 256 * 256;
+    return lists + parts + 256;
+}
+
+int launch_proj(const void *hidden, const void *weight, const int64_t *targets, const int64_t *ol, const int64_t *tl,
+                int B, int L, int T, int V, int H, float *match, float *max_lprob, int64_t *argmax, float *lse,
+                void *workspace, size_t ws_bytes, int *status, cudaStream_t st) {
+    const int N = B * L;
+    if (N == 0) return PCFGNAT_OK;
+    if (H % BK != 0 || H > KC_MAX * BK) return PCFGNAT_ERR_UNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(hidden) | reinterpret_cast<uintptr_t>(weight)) % 16) return PCFGNAT_ERR_INVALID_ARGUMENT;
+    if (ws_bytes < proj_workspace_bytes(B, L, T, V) || reinterpret_cast<uintptr_t>(workspace) % 16)
+        return PCFGNAT_ERR_WORKSPACE;
+    const bool gather = match != nullptr && targets != nullptr && T > 0;
+    Plan p = make_plan(N, V);
+    char *ws = static_cast<char *>(workspace);
+    int *stok = reinterpret_cast<int *>(ws);
+    int *sslot = stok + (size_t)B * T;
+    size_t lists = ((size_t)2 * B * (T > 0 ? T : 0) * sizeof(int) + 255) / 256 * 256;
+    Partial *partials = reinterpret_cast<Partial *>(ws + lists);
+
+    CUtensorMap map_a, map_w;
+    if (!make_map(&map_a, hidden, (uint64_t)N, (uint64_t)H, BM) || !make_map(&map_w, weight, (uint64_t)V, (uint64_t)H, BN))
+        return PCFGNAT_ERR_CUDA;
+    if (gather) sort_targets_kernel<<<B, 128, 0, st>>>(targets, T, V, stok, sslot, status);
+    const size_t smem = (size_t)KC_MAX * A_CHUNK_BYTES + (size_t)NSTAGE * B_STAGE_BYTES + 1024;
+    dim3 grid(p.row_tiles, p.splits);
+    const bool want_arg = max_lprob != nullptr || argmax != nullptr;
+    cudaError_t e;
+    if (want_arg) {
+        auto k = proj_kernel<true>;
+        e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return PCFGNAT_ERR_CUDA;
+        k<<<grid, PROJ_THREADS, smem, st>>>(map_a, map_w, N, V, H / BK, L, T, p.tiles_per_split, gather ? stok : nullptr,
+                                            gather ? sslot : nullptr, gather ? match : nullptr, partials, status);
+    } else {
+        auto k = proj_kernel<false>;
+        e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return PCFGNAT_ERR_CUDA;
+        k<<<grid, PROJ_THREADS, smem, st>>>(map_a, map_w, N, V, H / BK, L, T, p.tiles_per_split, gather ? stok : nullptr,
+                                            gather ? sslot : nullptr, gather ? match : nullptr, partials, status);
+    }
+    if (cudaGetLastError() != cudaSuccess) return PCFGNAT_ERR_CUDA;
+    const int warps_per_block = 8;
+    proj_merge_kernel<<<(N + warps_per_block - 1) / warps_per_block, warps_per_block * 32, 0, st>>>(
+        partials, p.splits, N, L, T, gather ? stok : nullptr, ol, tl, gather ? match : nullptr, max_lprob, argmax, lse);
+    if (gather) proj_poison_bad_targets_kernel<<<B, 128, 0, st>>>(stok, sslot, B, L, T, match);
+    return cuda_rc(cudaGetLastError());
+}
+
+}  // namespace pcfgnat

@@ -259,6 +259,63 @@ class _Kernel:
         return selected
 
     @staticmethod
+    def proj_logsoftmax_gather(hidden, weight, targets=None, output_length=None, target_length=None,
+                               want_max=False, want_lse=False):
+        """Fused output projection + log-softmax + gather / row max on the tensor cores.
+
+        hidden [B, L, H] f16, weight [V, H] f16, targets [B, T] int64 or None.  Returns a dict with
+        ``match`` [B, L, T] f32 = log P(target | node) when targets are given (EOS-masked as the
+        criterion does, criterions/nat_pcfg_loss.py:112-115, when both lengths are given),
+        ``max_lprob`` [B, L] f32 and ``argmax`` [B, L] int64 when ``want_max``, ``lse`` [B, L] f32 when
+        ``want_lse``.  Stands in for output_projection -> logsoftmax_gather / log_softmax().max()
+        (models/glat_decomposed_with_link_two_hands_tri_pcfg.py:237, :414-415) without materialising
+        the [B, L, V] logits."""
+        _require_cuda()
+        if not (hidden.is_cuda and weight.is_cuda) or hidden.device != weight.device:
+            raise RuntimeError("hidden and weight must be CUDA tensors on the same device")
+        if hidden.dtype != torch.float16 or weight.dtype != torch.float16:
+            raise RuntimeError("hidden and weight must be float16")
+        if hidden.dim() != 3 or weight.dim() != 2 or weight.shape[1] != hidden.shape[2]:
+            raise RuntimeError("hidden must be [batch, prelen, H] and weight [V, H]")
+        B, L, H = hidden.shape
+        V = weight.shape[0]
+        if H % 64 != 0 or H > 512:
+            raise RuntimeError(f"H must be a multiple of 64 and at most 512, got {H}")
+        hidden, weight = hidden.contiguous(), weight.contiguous()
+        dev = hidden.device
+        T = 0
+        if targets is not None:
+            if targets.dim() != 2 or targets.shape[0] != B:
+                raise RuntimeError("targets must be [batch, tarlen]")
+            targets = targets.to(device=dev, dtype=torch.int64).contiguous()
+            T = targets.shape[1]
+        if (output_length is None) != (target_length is None):
+            raise RuntimeError("give both output_length and target_length (EOS masking) or neither")
+        ol = _lengths(output_length, "output_length", B, dev) if output_length is not None else None
+        tl = _lengths(target_length, "target_length", B, dev) if target_length is not None else None
+        l = _cabi.lib()
+        nbytes = l.pcfgnat_proj_workspace_bytes(B, L, T, V)
+        out = {}
+        with torch.cuda.device(dev):
+            ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=dev)
+            match = torch.empty((B, L, T), dtype=torch.float32, device=dev) if T else None
+            mx = torch.empty((B, L), dtype=torch.float32, device=dev) if want_max else None
+            am = torch.empty((B, L), dtype=torch.int64, device=dev) if want_max else None
+            lse = torch.empty((B, L), dtype=torch.float32, device=dev) if want_lse else None
+            ptr = lambda t: t.data_ptr() if t is not None else None
+            rc = l.pcfgnat_proj_logsoftmax_gather(hidden.data_ptr(), weight.data_ptr(), ptr(targets), ptr(ol), ptr(tl),
+                                                  B, L, T, V, H, ptr(match), ptr(mx), ptr(am), ptr(lse), ws.data_ptr(),
+                                                  nbytes, _status_ptr(dev), _stream(dev))
+        _cabi.check(rc, "pcfgnat_proj_logsoftmax_gather")
+        if match is not None:
+            out["match"] = match
+        if want_max:
+            out["max_lprob"], out["argmax"] = mx, am
+        if want_lse:
+            out["lse"] = lse
+        return out
+
+    @staticmethod
     def viterbi_decoding_device(pred_length, output_length, L_trace, R_trace, M_trace, unreduced_tokens,
                                 left_tree_mask, pad_index):
         """Device back-trace: (tokens [B, L] int64 padded with pad_index, count [B] int64), no host sync."""
@@ -404,6 +461,13 @@ class DagLogsoftmaxGatherFunc(Function):
 
 
 dag_logsoftmax_gather_inplace = DagLogsoftmaxGatherFunc.apply
+
+
+def proj_logsoftmax_gather(hidden, weight, targets=None, output_length=None, target_length=None, want_max=False,
+                           want_lse=False):
+    """See ``_Kernel.proj_logsoftmax_gather`` (no gradient is defined for this operator yet)."""
+    return get_pcfg_kernel().proj_logsoftmax_gather(hidden, weight, targets, output_length, target_length, want_max,
+                                                    want_lse)
 
 
 def viterbi_decoding(pred_length, output_length, L_trace, R_trace, M_trace, unreduced_tokens, left_tree_mask, pad_index):

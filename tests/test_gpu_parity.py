@@ -371,3 +371,76 @@ def test_live_against_reference_kernels(ops, syn, seed):
     for x, y in zip(k.pcfg_viterbi(ob, lk_d, ol, 1), ref.pcfg_viterbi(ob, lk_d, ol, 1)):
         assert torch.equal(x.view(torch.int32) if x.dtype == torch.float32 else x,
                            y.view(torch.int32) if y.dtype == torch.float32 else y)
+
+
+# ---- fused projection + log-softmax + gather / max (tensor cores) ------------------------------------------------
+
+def _proj_reference(hidden, weight, targets):
+    """fp32 torch reference on the GPU: same fp16 values, fp32 accumulation."""
+    logits = hidden.float().reshape(-1, hidden.shape[-1]) @ weight.float().t()
+    lse = torch.logsumexp(logits, -1)
+    lp = logits - lse[:, None]
+    mx, am = lp.max(-1)
+    B, L = hidden.shape[:2]
+    match = lp.view(B, L, -1).gather(2, targets[:, None, :].expand(-1, L, -1)) if targets is not None else None
+    top2 = logits.topk(2, -1)[0]
+    return match, mx.view(B, L), am.view(B, L), lse.view(B, L), (top2[:, 0] - top2[:, 1]).view(B, L)
+
+
+PROJ_CASES = [
+    # B, L, T, V, H, hidden_std
+    (2, 32, 10, 1000, 64, 1.0),       # tiny: one partial row tile, vocabulary split over many CTAs
+    (3, 100, 17, 5000, 128, 1.0),     # rows and vocabulary both ragged against the tile sizes
+    (1, 240, 12, 40000, 512, 1.0),    # batch-1 decode shape
+    (6, 160, 40, 40000, 512, 0.02),   # training-shaped slice
+    (4, 256, 64, 40000, 512, 1.0),    # glancing-shaped slice
+]
+
+
+@pytest.mark.parametrize("B,L,T,V,H,std", PROJ_CASES)
+def test_fused_projection_against_torch(ops, syn, B, L, T, V, H, std):
+    g = torch.Generator().manual_seed(B * 1000 + L)
+    hidden = (torch.randn(B, L, H, generator=g) * std).half().to(DEV)
+    weight = (torch.randn(V, H, generator=g) * 0.02).half().to(DEV)
+    targets = torch.randint(0, V, (B, T), generator=g).to(DEV)
+    targets[:, 0] = V - 1  # last vocabulary column (inside the ragged last tile)
+    targets[:, 1] = targets[:, 2]  # repeated target
+    ops.read_status(DEV)
+    out = ops.proj_logsoftmax_gather(hidden, weight, targets, want_max=True, want_lse=True)
+    match, mx, am, lse, margin = _proj_reference(hidden, weight, targets)
+    # fp16 inputs, fp32 accumulation on both sides: only summation order differs
+    torch.testing.assert_close(out["lse"], lse, rtol=0, atol=2e-3)
+    torch.testing.assert_close(out["match"], match, rtol=0, atol=2e-3)
+    torch.testing.assert_close(out["max_lprob"], mx, rtol=0, atol=2e-3)
+    clear = margin > 1e-3  # arg-max must agree wherever the top-2 margin exceeds the tolerance
+    assert torch.equal(out["argmax"][clear], am[clear])
+    if std >= 1.0:
+        assert clear.float().mean() > 0.9
+    assert ops.read_status(DEV) == 0
+    # gather-only and max-only variants, EOS masking fused
+    ol = torch.full((B,), L, device=DEV)
+    tl = torch.full((B,), T, device=DEV)
+    ol[0] = L - 2
+    tl[0] = max(T - 3, 2)
+    out2 = ops.proj_logsoftmax_gather(hidden, weight, targets, ol, tl)
+    want = syn.eos_mask_(match.clone(), ol.cpu(), tl.cpu())
+    fin = torch.isfinite(want)
+    assert torch.equal(fin, torch.isfinite(out2["match"]))
+    torch.testing.assert_close(out2["match"][fin], want[fin], rtol=0, atol=2e-3)
+    out3 = ops.proj_logsoftmax_gather(hidden, weight, want_max=True)
+    assert torch.equal(out3["argmax"], out["argmax"]) and torch.equal(out3["max_lprob"], out["max_lprob"])
+
+
+def test_fused_projection_flags_bad_targets(ops):
+    g = torch.Generator().manual_seed(0)
+    hidden = torch.randn(1, 16, 64, generator=g).half().to(DEV)
+    weight = torch.randn(300, 64, generator=g).half().to(DEV)
+    targets = torch.tensor([[5, 300, 7, -1]], device=DEV)
+    ops.read_status(DEV)
+    out = ops.proj_logsoftmax_gather(hidden, weight, targets)
+    m = out["match"]
+    assert torch.isnan(m[0, :, 1]).all() and torch.isnan(m[0, :, 3]).all()
+    assert torch.isfinite(m[0, :, 0]).all() and torch.isfinite(m[0, :, 2]).all()
+    assert ops.read_status(DEV) & 4
+    with pytest.raises(RuntimeError, match="multiple of 64"):
+        ops.proj_logsoftmax_gather(hidden[:, :, :48].contiguous(), weight[:, :48].contiguous(), targets)
