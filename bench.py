@@ -40,7 +40,7 @@ KERNELS_PER_STEP = 7  # sort_targets, proj, proj_merge, proj_poison_bad_targets,
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="train_batch")
@@ -59,52 +59,66 @@ def peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
-         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-         "clocks_event_reasons.sw_power_cap")
+    """Samples SM clock and throttle reasons through NVML (read-only) in a thread while the timed
+    region runs; only samples taken between mark_begin() and mark_end() are reported."""
+    REASONS = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20, "sw_power_cap": 0x4}
 
-    def __init__(self, index):
-        self.index, self.rows, self.proc = index, [], None
+    def __init__(self, index, period_s=0.002):
+        self.index, self.period, self.rows = index, period_s, []
+        self.stop_flag, self.active, self.thread, self.err = False, False, None, None
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-i", str(self.index), "-lms", "100"], stdout=subprocess.PIPE,
-                                         stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
-            self.thread.start()
-        except OSError:
-            self.proc = None
+            import pynvml
 
-    def _read(self):
-        for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            pynvml.nvmlInit()
+            vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+            phys = self.index
+            if vis:
+                try:
+                    phys = int(vis.split(",")[self.index])
+                except (ValueError, IndexError):
+                    phys = self.index
+            self.nv, self.h = pynvml, pynvml.nvmlDeviceGetHandleByIndex(phys)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+        except Exception as e:  # NVML missing: report it, do not fail the benchmark
+            self.err = repr(e)
+            return
+        self.thread = threading.Thread(target=self._loop, daemon=True)
+        self.thread.start()
+
+    def _loop(self):
+        nv = self.nv
+        while not self.stop_flag:
+            try:
+                mhz = nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)
+                why = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                if self.active:
+                    self.rows.append((float(mhz), int(why)))
+            except Exception as e:
+                self.err = repr(e)
+                return
+            time.sleep(self.period)
+
+    def mark_begin(self):
+        self.active = True
+
+    def mark_end(self):
+        self.active = False
 
     def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        self.thread.join(timeout=5)
-        sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        self.stop_flag = True
+        if self.thread is not None:
+            self.thread.join(timeout=5)
+        if not self.rows:
+            return {"sm_mhz": None, "sm_max_mhz": getattr(self, "max_mhz", None), "samples": 0,
+                    "reasons": [], "note": self.err or "no sample fell inside the timed region"}
+        sm = [r[0] for r in self.rows]
+        bits = 0
         for r in self.rows:
-            if len(r) < 9:
-                continue
-            try:
-                sm.append(float(r[1]))
-                mx.append(float(r[2]))
-            except ValueError:
-                continue
-            for name, v in zip(names, r[5:9]):
-                if v.lower().startswith("active"):
-                    reasons.add(name)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+            bits |= r[1]
+        return {"sm_mhz": statistics.median(sm), "sm_min_mhz": min(sm), "sm_max_mhz": self.max_mhz, "samples": len(sm),
+                "reasons": sorted(n for n, b in self.REASONS.items() if bits & b)}
 
 
 def algorithmic(batch):
@@ -197,8 +211,10 @@ def run_ours(a):
     if rank == 0:
         sampler.start()
     sync_all()
+    sampler.mark_begin()
     step_ms, proj_ms = timed(a.steps, False, probe_proj=True)
     sync_all()
+    sampler.mark_end()
     clocks = sampler.stop() if rank == 0 else None
     timed(3, True)
     sync_all()
