@@ -76,6 +76,20 @@ int pcfgnat_loss_fwd_bwd(const float *match_all, const float *links, const int64
                          size_t workspace_bytes, float *loss, float *match_all_grad, float *links_grad, int *status,
                          void *stream);
 
+/* The same forward + backward for hosts that cannot hand over scratch memory (a binding that only
+ * holds device pointers owned by another framework, or a process whose device memory all belongs
+ * to its own arena so that no library may call cudaMalloc).  It has no counterpart in the
+ * reference.  The two DP tables live in a fixed PCFGNAT_STATIC_SCRATCH_BYTES array inside the
+ * library's device image (held on every GPU that loads the library, until exit); shapes with
+ * 2 * roundup256(B * Mc * (T+2) * 4) above that are refused with PCFGNAT_ERR_TOO_LARGE.  The call
+ * allocates nothing.  All calls on a device share the array: calls that may overlap on the GPU
+ * race and must be serialised by the caller.  The first call on each device looks up the array's
+ * address and should come before any stream capture on that device. */
+#define PCFGNAT_STATIC_SCRATCH_BYTES (8u << 20)
+int pcfgnat_loss_fwd_bwd_static(const float *match_all, const float *links, const int64_t *output_length,
+                                const int64_t *target_length, int B, int L, int T, int max_left, float *loss,
+                                float *match_all_grad, float *links_grad, int *status, void *stream);
+
 /* Best tree for glancing training.  Replaces pcfg_best_tree()
  * (fs_plugins/custom_ops/pcfg_best_tree.cu:333-360, kernels :65-197 and :240-301).
  * S from pcfgnat_loss_fwd; tree [B][L] int64: target index emitted by each node, -1 if

@@ -17,6 +17,7 @@ SIGNATURES = {
     "pcfgnat_loss_bwd": (c_int, [c_void] * 6 + [c_int] * 4 + [c_void] * 5),
     "pcfgnat_loss_workspace_bytes": (c_size, [c_int] * 4),
     "pcfgnat_loss_fwd_bwd": (c_int, [c_void] * 4 + [c_int] * 4 + [c_void, c_size] + [c_void] * 5),
+    "pcfgnat_loss_fwd_bwd_static": (c_int, [c_void] * 4 + [c_int] * 4 + [c_void] * 5),
     "pcfgnat_best_tree": (c_int, [c_void] * 5 + [c_int] * 4 + [c_void] * 3),
     "pcfgnat_viterbi": (c_int, [c_void] * 3 + [c_int] * 3 + [c_void] * 6),
     "pcfgnat_viterbi_backtrace": (c_int, [c_void] * 7 + [c_int, c_i64] + [c_int] * 4 + [c_void] * 4),
