@@ -1,7 +1,43 @@
 // extern "C" entry points declared in include/pcfgnat.h: argument checks, then launch.
 #include "common.cuh"
 
+#include <mutex>
+
 using namespace pcfgnat;
+
+namespace pcfgnat {
+
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) is sticky per (function, device); remember what
+// was set so that steady-state launches make no driver call for it.
+cudaError_t ensure_dynamic_smem_for(const void *kernel, size_t bytes) {
+    constexpr int kSlots = 64, kDevs = 16;
+    struct Entry {
+        const void *fn;
+        int bytes[kDevs];
+    };
+    static Entry table[kSlots] = {};
+    static std::mutex mu;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    std::lock_guard<std::mutex> lock(mu);
+    Entry *slot = nullptr;
+    for (int i = 0; i < kSlots; i++) {
+        if (table[i].fn == kernel || table[i].fn == nullptr) {
+            slot = &table[i];
+            break;
+        }
+    }
+    if (slot && slot->fn == kernel && dev >= 0 && dev < kDevs && slot->bytes[dev] >= (int)bytes) return cudaSuccess;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e == cudaSuccess && slot && dev >= 0 && dev < kDevs) {
+        slot->fn = kernel;
+        slot->bytes[dev] = (int)bytes;
+    }
+    return e;
+}
+
+}  // namespace pcfgnat
 
 namespace {
 

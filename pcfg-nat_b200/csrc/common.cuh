@@ -28,6 +28,15 @@ __device__ __forceinline__ void flag(int *status, int bit) {
 
 inline int cuda_rc(cudaError_t e) { return e == cudaSuccess ? PCFGNAT_OK : PCFGNAT_ERR_CUDA; }
 
+// Raises a kernel's dynamic shared-memory limit, remembering per device the largest value already
+// set so that the steady state costs no driver call (the attribute is sticky per function and device).
+cudaError_t ensure_dynamic_smem_for(const void *kernel, size_t bytes);  // cabi.cu; keyed by (function, device)
+
+template <class Kernel>
+inline cudaError_t ensure_dynamic_smem(Kernel kernel, size_t bytes) {
+    return ensure_dynamic_smem_for(reinterpret_cast<const void *>(kernel), bytes);
+}
+
 // Host-side launchers shared between the translation units.
 int launch_loss_fwd(const float *match_all, const float *links, const int64_t *ol, const int64_t *tl, int B, int L,
                     int T, float *S, float *C, float *loss, int *status, cudaStream_t st);

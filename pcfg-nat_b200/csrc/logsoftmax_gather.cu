@@ -131,7 +131,7 @@ int launch_typed(T *logits, const int64_t *sel, int64_t sb, int64_t sl, int64_t 
     cudaError_t e;
     if (row_bytes <= (size_t)kSmemLimit - 2048) {
         auto k = logsoftmax_gather_kernel<T, true>;
-        e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)row_bytes);
+        e = ensure_dynamic_smem(k, row_bytes);
         if (e != cudaSuccess) return PCFGNAT_ERR_CUDA;
         int per_sm = (int)(((size_t)kSmemLimit) / (row_bytes + 1024));
         if (per_sm < 1) per_sm = 1;

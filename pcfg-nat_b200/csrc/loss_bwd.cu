@@ -98,20 +98,31 @@ __global__ void __launch_bounds__(kMaxRows *kLanes)
                 const bool f1 = !isinf(sc1), f2 = !isinf(sc2);
                 const int c = 2 * ci + 1;
                 if (f1 || f2) {
-                    for (int ai = x; ai < ci; ai += kLanes) {
-                        const float g = ga[ai];
-                        if (g == 0.f) continue;
-                        float l0, l1;
-                        if (SMEM_LINKS) {
-                            l0 = lt0[ci * lk_stride + ai];
-                            l1 = lt1[ci * lk_stride + ai];
-                        } else {
-                            l0 = __ldg(lkb + ((size_t)(2 * ai + 1) * 2 + 0) * L + c);
-                            l1 = __ldg(lkb + ((size_t)(2 * ai + 1) * 2 + 1) * L + c);
+                    // 4 parents per trip so that several expf are in flight (summation order is free here)
+                    float p0[4] = {0.f, 0.f, 0.f, 0.f}, p1[4] = {0.f, 0.f, 0.f, 0.f};
+                    for (int base = x; base < ci; base += 4 * kLanes) {
+#pragma unroll
+                        for (int u = 0; u < 4; u++) {
+                            const int ai = base + u * kLanes;
+                            const bool in = ai < ci;
+                            const int aa = in ? ai : 0;
+                            const float g = in ? ga[aa] : 0.f;
+                            float l0, l1;
+                            if (SMEM_LINKS) {
+                                l0 = lt0[ci * lk_stride + aa];
+                                l1 = lt1[ci * lk_stride + aa];
+                            } else {
+                                l0 = __ldg(lkb + ((size_t)(2 * aa + 1) * 2 + 0) * L + c);
+                                l1 = __ldg(lkb + ((size_t)(2 * aa + 1) * 2 + 1) * L + c);
+                            }
+                            if (g != 0.f) {
+                                if (f1) p0[u] += g * expf((l0 + sc1) + q0[aa]);
+                                if (f2) p1[u] += g * expf((l1 + sc2) + q1[aa]);
+                            }
                         }
-                        if (f1) acc0 += g * expf((l0 + sc1) + q0[ai]);
-                        if (f2) acc1 += g * expf((l1 + sc2) + q1[ai]);
                     }
+                    acc0 = (p0[0] + p0[1]) + (p0[2] + p0[3]);
+                    acc1 = (p1[0] + p1[1]) + (p1[2] + p1[3]);
                 }
             }
             acc0 += __shfl_down_sync(0xffffffffu, acc0, 2, kLanes);
@@ -274,14 +285,14 @@ int launch_loss_bwd(const float *grad_output, const float *S, const float *match
     cudaError_t e;
     if (smem_cols + smem_links <= (size_t)kSmemLimit - 1024) {
         auto k = outside_kernel<true>;
-        e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(smem_cols + smem_links));
+        e = ensure_dynamic_smem(k, smem_cols + smem_links);
         if (e != cudaSuccess) return PCFGNAT_ERR_CUDA;
         k<<<grid, block, smem_cols + smem_links, st>>>(grad_output, S, match_all, links, ol, tl, L, T, S_grad, status,
                                                        Mc, col_stride, lk_stride);
     } else {
         if (smem_cols > (size_t)kSmemLimit - 1024) return PCFGNAT_ERR_TOO_LARGE;
         auto k = outside_kernel<false>;
-        e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_cols);
+        e = ensure_dynamic_smem(k, smem_cols);
         if (e != cudaSuccess) return PCFGNAT_ERR_CUDA;
         k<<<grid, block, smem_cols, st>>>(grad_output, S, match_all, links, ol, tl, L, T, S_grad, status, Mc,
                                           col_stride, lk_stride);
@@ -290,7 +301,7 @@ int launch_loss_bwd(const float *grad_output, const float *S, const float *match
     const int npairs = (L + 1) / 2;
     const size_t gsm = (size_t)kGradWarps * 2 * T * sizeof(float);
     if (gsm > (size_t)kSmemLimit - 1024) return PCFGNAT_ERR_TOO_LARGE;
-    e = cudaFuncSetAttribute(grad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gsm);
+    e = ensure_dynamic_smem(grad_kernel, gsm);
     if (e != cudaSuccess) return PCFGNAT_ERR_CUDA;
     dim3 ggrid((npairs + kGradWarps - 1) / kGradWarps, B);
     grad_kernel<<<ggrid, kGradWarps * 32, gsm, st>>>(S, S_grad, match_all, links, ol, tl, L, T, mg, lg, Mc);

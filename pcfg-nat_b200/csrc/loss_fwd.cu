@@ -38,17 +38,32 @@ struct LinksInGlobal {
 
 __device__ __forceinline__ float clean(float t) { return isnan(t) ? neg_inf() : t; }
 
-// One dependent step of the recurrence for the rows this thread owns.
+// One dependent step of the recurrence for the row this thread owns.  The loop over the lane's
+// right children is unrolled by kUnroll so that several loads and expf are in flight; children
+// past the end contribute -inf terms, i.e. exp() = +0, which leaves max and sum bit-unchanged, and
+// the additions still happen in increasing child order, t0 before t1.
+constexpr int kUnroll = 4;
+
 template <class Links>
 __device__ __forceinline__ float inside_row(const Links &lk, int ai, int x, int Mb, const float *S1, const float *S2,
                                             float ma0, float ma1, float ml, bool has_leaf) {
     float mx = neg_inf();
-    for (int ci = ai + x; ci < Mb; ci += kLanes) {
-        float t0 = clean((lk.k0(ai, ci) + S1[ci]) + ma0);
-        if (t0 > mx) mx = t0;
-        if (has_leaf) {
-            float t1 = clean(((lk.k1(ai, ci) + S2[ci]) + ml) + ma1);
-            if (t1 > mx) mx = t1;
+    for (int base = ai + x; base < Mb; base += kLanes * kUnroll) {
+        float t0[kUnroll], t1[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; u++) {
+            const int ci = base + kLanes * u;
+            const bool in = ci < Mb;
+            const int cc = in ? ci : ai;
+            const float a = clean((lk.k0(ai, cc) + S1[cc]) + ma0);
+            const float b = clean(((lk.k1(ai, cc) + S2[cc]) + ml) + ma1);
+            t0[u] = in ? a : neg_inf();
+            t1[u] = (in && has_leaf) ? b : neg_inf();
+        }
+#pragma unroll
+        for (int u = 0; u < kUnroll; u++) {
+            if (t0[u] > mx) mx = t0[u];
+            if (t1[u] > mx) mx = t1[u];
         }
     }
     // max over the 4 lanes of the row (order-free), then broadcast lane 0's value
@@ -61,12 +76,22 @@ __device__ __forceinline__ float inside_row(const Links &lk, int ai, int x, int 
     }
     float sum = 0.f;
     if (!isinf(mx)) {
-        for (int ci = ai + x; ci < Mb; ci += kLanes) {
-            float t0 = clean(((lk.k0(ai, ci) + S1[ci]) + ma0) - mx);
-            sum += expf(t0);
-            if (has_leaf) {
-                float t1 = clean((((lk.k1(ai, ci) + S2[ci]) + ml) + ma1) - mx);
-                sum += expf(t1);
+        for (int base = ai + x; base < Mb; base += kLanes * kUnroll) {
+            float e0[kUnroll], e1[kUnroll];
+#pragma unroll
+            for (int u = 0; u < kUnroll; u++) {
+                const int ci = base + kLanes * u;
+                const bool in = ci < Mb;
+                const int cc = in ? ci : ai;
+                const float a = clean(((lk.k0(ai, cc) + S1[cc]) + ma0) - mx);
+                const float b = clean((((lk.k1(ai, cc) + S2[cc]) + ml) + ma1) - mx);
+                e0[u] = expf(in ? a : neg_inf());
+                e1[u] = expf((in && has_leaf) ? b : neg_inf());
+            }
+#pragma unroll
+            for (int u = 0; u < kUnroll; u++) {
+                sum += e0[u];
+                sum += e1[u];
             }
         }
     }
@@ -198,14 +223,14 @@ int launch_loss_fwd(const float *match_all, const float *links, const int64_t *o
     cudaError_t e;
     if (smem_cols + smem_links <= (size_t)kSmemLimit - 1024) {
         auto k = loss_fwd_kernel<true>;
-        e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(smem_cols + smem_links));
+        e = ensure_dynamic_smem(k, smem_cols + smem_links);
         if (e != cudaSuccess) return PCFGNAT_ERR_CUDA;
         k<<<grid, block, smem_cols + smem_links, st>>>(match_all, links, ol, tl, L, T, S, C, loss, status, Mc, Lt,
                                                        col_stride, lk_stride);
     } else {
         if (smem_cols > (size_t)kSmemLimit - 1024) return PCFGNAT_ERR_TOO_LARGE;
         auto k = loss_fwd_kernel<false>;
-        e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_cols);
+        e = ensure_dynamic_smem(k, smem_cols);
         if (e != cudaSuccess) return PCFGNAT_ERR_CUDA;
         k<<<grid, block, smem_cols, st>>>(match_all, links, ol, tl, L, T, S, C, loss, status, Mc, Lt, col_stride,
                                           lk_stride);

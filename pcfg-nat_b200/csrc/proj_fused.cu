@@ -7,16 +7,19 @@
 //   lprob, token = logits.log_softmax(-1).max(-1)       (models/...pcfg.py:414-415)
 //
 // Shape of the kernel (sm_100a only: tcgen05 tensor cores, TMEM accumulators, TMA):
-//   * one CTA per (128-row tile of the decoder states, contiguous range of 256-wide vocabulary
-//     tiles).  The 128 x H fp16 state tile stays resident in shared memory (H <= 512: 128 KB),
-//     the projection matrix streams through a 3-stage ring of 256 x 64 fp16 tiles (32 KB each);
+//   * the work is the grid of (128-row tile of the decoder states) x (256-wide vocabulary tile)
+//     units, flattened row-tile-major and cut into one contiguous range per CTA, one CTA per SM, so
+//     that every SM gets the same number of units whatever the number of rows.  A range crosses
+//     at most a few row tiles ("segments"); per segment the 128 x H fp16 state tile is loaded once
+//     and stays resident in shared memory (H <= 512: 128 KB) while the projection matrix streams
+//     through a 3-stage ring of 256 x 64 fp16 tiles (32 KB each);
 //   * warp 0 drives TMA (cp.async.bulk.tensor, 128-byte swizzle, no multicast), warp 1 issues
 //     tcgen05.mma 128x256x16 (fp16 in, fp32 accumulate) into one of two 256-column TMEM
-//     accumulators, warps 2-5 are the epilogue: each thread owns one row, reads its
-//     accumulator with tcgen05.ld and keeps an online (max, sum-exp), the running arg-max and
-//     the raw logits of this row's targets, while the MMA warp already fills the other
-//     accumulator;
-//   * a second, tiny kernel merges the per-range partials: lse, match = logit - lse (with the
+//     accumulators, warps 2-9 are the epilogue: two warps per TMEM sub-partition, each thread owns
+//     one row and one 128-column half of the tile, reads it with tcgen05.ld and keeps an online
+//     (max, sum-exp), the running arg-max and the raw logits of this row's targets, while the
+//     MMA warp already fills the other accumulator;
+//   * a second, tiny kernel merges the per-segment partials: lse, match = logit - lse (with the
 //     criterion's EOS masking fused if lengths are given), max log-prob and arg-max.
 // Every wait on an mbarrier is bounded; on expiry the CTA records PCFGNAT_STATUS_TIMEOUT, stops
 // issuing work, and still frees its tensor memory.
@@ -37,7 +40,9 @@ constexpr int NSTAGE = 3;      // W ring depth
 constexpr int KC_MAX = 8;      // H <= 512
 constexpr int A_CHUNK_BYTES = BM * BK * 2;  // 16 KB
 constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KB
-constexpr int PROJ_THREADS = 192;           // 6 warps
+constexpr int EPI_WARPS = 8;                // two per TMEM sub-partition
+constexpr int PROJ_THREADS = 32 * (2 + EPI_WARPS);
+constexpr int HALF_COLS = BN / 2;           // columns of a tile owned by one epilogue thread
 constexpr uint32_t kSpinLimit = 1u << 22;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
@@ -46,9 +51,20 @@ constexpr float kLn2 = 0.6931471805599453f;
 // N >> 3 at bits 17-22, M >> 4 at bits 24-28.
 constexpr uint32_t kIdesc = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 
-struct Partial {  // per (vocabulary range, row)
+struct Partial {  // per (CTA, segment, column half, row)
     float m, s, best;
     int best_idx;
+};
+
+// Flattened schedule: unit u = row_tile * n_tiles + vocab_tile; CTA g owns [begin(g), begin(g + 1)).
+struct Plan {
+    int row_tiles, n_tiles, ctas, max_seg;
+    long long units, q, rem;  // the first `rem` CTAs own q + 1 units, the others q
+    __host__ __device__ long long begin(int g) const { return (long long)g * q + (g < rem ? g : rem); }
+    __host__ __device__ int cta_of(long long u) const {
+        const long long big = rem * (q + 1);
+        return u < big ? (int)(u / (q + 1)) : (int)(rem + (u - big) / q);
+    }
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -158,30 +174,28 @@ __global__ void sort_targets_kernel(const int64_t *__restrict__ targets, int T, 
 // ---------------------------------------------------------------------------------------
 template <bool WANT_ARGMAX>
 __global__ void __launch_bounds__(PROJ_THREADS, 1)
-    proj_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, int N, int V,
-                int KC, int L, int T, int tiles_per_split, const int *__restrict__ stok,
-                const int *__restrict__ sslot, float *match, Partial *partials, int *status) {
+    proj_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, const Plan plan,
+                int N, int V, int KC, int L, int T, const int *__restrict__ stok, const int *__restrict__ sslot,
+                float *match, Partial *partials, int *status) {
     extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t bars[2 * NSTAGE + 1 + 4];
+    __shared__ __align__(8) uint64_t bars[2 * NSTAGE + 2 + 4];
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag_s;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int row0 = blockIdx.x * BM;
-    const int split = blockIdx.y;
-    const int n_tiles_total = (V + BN - 1) / BN;
-    const int t_begin = split * tiles_per_split;
-    const int t_end = min(n_tiles_total, t_begin + tiles_per_split);
-    const int n_tiles = t_end - t_begin;  // >= 1 by construction of the grid
+    const int g = blockIdx.x;
+    const long long u_begin = plan.begin(g), u_end = plan.begin(g + 1);
+    const int NT = plan.n_tiles;
 
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const uint32_t smem_a = smem_u32(smem);
     const uint32_t smem_b = smem_a + KC_MAX * A_CHUNK_BYTES;
-    const uint32_t bar_full = smem_u32(&bars[0]);             // [NSTAGE]
-    const uint32_t bar_empty = smem_u32(&bars[NSTAGE]);       // [NSTAGE]
-    const uint32_t bar_a = smem_u32(&bars[2 * NSTAGE]);       // A tile landed
-    const uint32_t bar_tfull = smem_u32(&bars[2 * NSTAGE + 1]);   // [2] accumulator ready
-    const uint32_t bar_tempty = smem_u32(&bars[2 * NSTAGE + 3]);  // [2] accumulator drained
+    const uint32_t bar_full = smem_u32(&bars[0]);                 // [NSTAGE] W stage landed
+    const uint32_t bar_empty = smem_u32(&bars[NSTAGE]);           // [NSTAGE] W stage consumed
+    const uint32_t bar_a = smem_u32(&bars[2 * NSTAGE]);           // state tile landed
+    const uint32_t bar_a_free = smem_u32(&bars[2 * NSTAGE + 1]);  // all MMAs of the segment have read it
+    const uint32_t bar_tfull = smem_u32(&bars[2 * NSTAGE + 2]);   // [2] accumulator ready
+    const uint32_t bar_tempty = smem_u32(&bars[2 * NSTAGE + 4]);  // [2] accumulator drained
     volatile int *abort_flag = &abort_flag_s;
 
     if (threadIdx.x == 0) {
@@ -190,9 +204,10 @@ __global__ void __launch_bounds__(PROJ_THREADS, 1)
             mbar_init(bar_empty + 8 * i, 1);
         }
         mbar_init(bar_a, 1);
+        mbar_init(bar_a_free, 1);
         for (int i = 0; i < 2; i++) {
             mbar_init(bar_tfull + 8 * i, 1);
-            mbar_init(bar_tempty + 8 * i, 4);  // one arrival per epilogue warp
+            mbar_init(bar_tempty + 8 * i, EPI_WARPS);  // one arrival per epilogue warp
         }
         abort_flag_s = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -211,145 +226,176 @@ __global__ void __launch_bounds__(PROJ_THREADS, 1)
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
         if (lane == 0) {
-            mbar_expect_tx(bar_a, (uint32_t)KC * A_CHUNK_BYTES);
-            for (int kc = 0; kc < KC; kc++) tma_load_2d(smem_a + kc * A_CHUNK_BYTES, &map_a, bar_a, kc * BK, row0);
-            uint32_t it = 0;
+            uint32_t it = 0, seg = 0;
             bool ok = true;
-            for (int t = t_begin; t < t_end && ok; t++) {
-                for (int kc = 0; kc < KC; kc++, it++) {
-                    const uint32_t st = it % NSTAGE, ph = (it / NSTAGE) & 1;
-                    if (!mbar_wait(bar_empty + 8 * st, ph ^ 1, abort_flag)) {
-                        ok = false;
-                        break;
+            long long u = u_begin;
+            while (u < u_end && ok) {
+                const int rt = (int)(u / NT);
+                const long long seg_end = min(u_end, (long long)(rt + 1) * NT);
+                // the previous segment's MMAs must have finished reading the resident state tile
+                if (seg > 0 && !mbar_wait(bar_a_free, (seg - 1) & 1, abort_flag)) break;
+                mbar_expect_tx(bar_a, (uint32_t)KC * A_CHUNK_BYTES);
+                for (int kc = 0; kc < KC; kc++) tma_load_2d(smem_a + kc * A_CHUNK_BYTES, &map_a, bar_a, kc * BK, rt * BM);
+                for (; u < seg_end && ok; u++) {
+                    const int t = (int)(u - (long long)rt * NT);
+                    for (int kc = 0; kc < KC; kc++, it++) {
+                        const uint32_t st = it % NSTAGE, ph = (it / NSTAGE) & 1;
+                        if (!mbar_wait(bar_empty + 8 * st, ph ^ 1, abort_flag)) {
+                            ok = false;
+                            break;
+                        }
+                        mbar_expect_tx(bar_full + 8 * st, B_STAGE_BYTES);
+                        tma_load_2d(smem_b + st * B_STAGE_BYTES, &map_w, bar_full + 8 * st, kc * BK, t * BN);
                     }
-                    mbar_expect_tx(bar_full + 8 * st, B_STAGE_BYTES);
-                    tma_load_2d(smem_b + st * B_STAGE_BYTES, &map_w, bar_full + 8 * st, kc * BK, t * BN);
                 }
+                seg++;
             }
         }
     } else if (warp == 1) {
         // ------------------------------ MMA issuer ------------------------------
         if (lane == 0) {
-            bool ok = mbar_wait(bar_a, 0, abort_flag);
-            uint32_t it = 0;
-            for (int t = 0; t < n_tiles && ok; t++) {
-                const uint32_t buf = t & 1, use = t >> 1;
-                if (!mbar_wait(bar_tempty + 8 * buf, (use & 1) ^ 1, abort_flag)) {
-                    ok = false;
-                    break;
-                }
-                tc_fence_after();
-                const uint32_t d = tmem_base + buf * BN;
-                for (int kc = 0; kc < KC; kc++, it++) {
-                    const uint32_t st = it % NSTAGE, ph = (it / NSTAGE) & 1;
-                    if (!mbar_wait(bar_full + 8 * st, ph, abort_flag)) {
+            uint32_t it = 0, seg = 0, tile = 0;
+            bool ok = true;
+            long long u = u_begin;
+            while (u < u_end && ok) {
+                const int rt = (int)(u / NT);
+                const long long seg_end = min(u_end, (long long)(rt + 1) * NT);
+                if (!mbar_wait(bar_a, seg & 1, abort_flag)) break;
+                for (; u < seg_end && ok; u++, tile++) {
+                    const uint32_t buf = tile & 1, use = tile >> 1;
+                    if (!mbar_wait(bar_tempty + 8 * buf, (use & 1) ^ 1, abort_flag)) {
                         ok = false;
                         break;
                     }
                     tc_fence_after();
-                    const uint64_t da = umma_desc(smem_a + kc * A_CHUNK_BYTES);
-                    const uint64_t db = umma_desc(smem_b + st * B_STAGE_BYTES);
+                    const uint32_t d = tmem_base + buf * BN;
+                    for (int kc = 0; kc < KC; kc++, it++) {
+                        const uint32_t st = it % NSTAGE, ph = (it / NSTAGE) & 1;
+                        if (!mbar_wait(bar_full + 8 * st, ph, abort_flag)) {
+                            ok = false;
+                            break;
+                        }
+                        tc_fence_after();
+                        const uint64_t da = umma_desc(smem_a + kc * A_CHUNK_BYTES);
+                        const uint64_t db = umma_desc(smem_b + st * B_STAGE_BYTES);
 #pragma unroll
-                    for (int k = 0; k < BK / UK; k++)  // +32 B along K inside the swizzle span = +2 in the address field
-                        umma_f16(d, da + 2 * k, db + 2 * k, (kc | k) != 0);
-                    umma_commit(bar_empty + 8 * st);  // frees the W stage when these MMAs have read it
+                        for (int k = 0; k < BK / UK; k++)  // +32 B along K inside the swizzle span = +2 in the address field
+                            umma_f16(d, da + 2 * k, db + 2 * k, (kc | k) != 0);
+                        umma_commit(bar_empty + 8 * st);  // frees the W stage when these MMAs have read it
+                    }
+                    if (ok) umma_commit(bar_tfull + 8 * buf);
                 }
-                if (ok) umma_commit(bar_tfull + 8 * buf);
+                if (ok) umma_commit(bar_a_free);
+                seg++;
             }
         }
     } else {
-        // ------------------------------ epilogue: one row per thread ------------------------------
-        const int sub = warp & 3;  // TMEM sub-partition this warp may read
-        const int row = row0 + sub * 32 + lane;
-        const bool row_ok = row < N;
-        const int sent = row_ok ? row / L : 0;
-        const int *my_tok = stok ? stok + (size_t)sent * T : nullptr;
-        const int *my_slot = stok ? sslot + (size_t)sent * T : nullptr;
-        float *my_out = match ? match + (size_t)row * T : nullptr;
-        int p = 0;
-        if (my_tok) {  // first target at or after this CTA's first column
-            const int c_first = t_begin * BN;
-            int lo = 0, hi = T;
-            while (lo < hi) {
-                int mid = (lo + hi) >> 1;
-                if (__ldg(my_tok + mid) < c_first) lo = mid + 1; else hi = mid;
-            }
-            p = lo;
-        }
-        float m = -CUDART_INF_F, s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
-        float best = -CUDART_INF_F;
-        int best_idx = 0;
+        // ------------------ epilogue: one row and one 128-column half per thread ------------------
+        const int ew = warp - 2;
+        const int sub = warp & 3;  // TMEM sub-partition (lanes 32*sub ..) this warp may read
+        const int half = ew >> 2;  // which 128 columns of each 256-wide tile
+        uint32_t tile = 0, seg = 0;
         bool ok = true;
-        for (int t = 0; t < n_tiles && ok; t++) {
-            const uint32_t buf = t & 1, use = t >> 1;
-            if (!mbar_wait(bar_tfull + 8 * buf, use & 1, abort_flag)) {
-                ok = false;
-                break;
+        long long u = u_begin;
+        while (u < u_end && ok) {
+            const int rt = (int)(u / NT);
+            const long long seg_end = min(u_end, (long long)(rt + 1) * NT);
+            const int row = rt * BM + sub * 32 + lane;
+            const bool row_ok = row < N;
+            const int sent = row_ok ? row / L : 0;
+            const int *my_tok = stok ? stok + (size_t)sent * T : nullptr;
+            const int *my_slot = stok ? sslot + (size_t)sent * T : nullptr;
+            float *my_out = match ? match + (size_t)row * T : nullptr;
+            int p = 0;
+            if (my_tok) {  // first target at or after this segment's first column
+                const int c_first = (int)(u - (long long)rt * NT) * BN;
+                int lo = 0, hi = T;
+                while (lo < hi) {
+                    int mid = (lo + hi) >> 1;
+                    if (__ldg(my_tok + mid) < c_first) lo = mid + 1; else hi = mid;
+                }
+                p = lo;
             }
-            tc_fence_after();
-            const int tile_col0 = (t_begin + t) * BN;
+            float m = -CUDART_INF_F, s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+            float best = -CUDART_INF_F;
+            int best_idx = 0;
+            for (; u < seg_end && ok; u++, tile++) {
+                const uint32_t buf = tile & 1, use = tile >> 1;
+                if (!mbar_wait(bar_tfull + 8 * buf, use & 1, abort_flag)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const int tile_col0 = (int)(u - (long long)rt * NT) * BN + half * HALF_COLS;
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; c++) {
-                float v[32];
-                __syncwarp();  // the gather loop below may leave the lanes diverged; tcgen05.ld is warp-collective
-                tmem_ld32(tmem_base + ((uint32_t)(sub * 32) << 16) + buf * BN + c * 32, v);
-                const int col0 = tile_col0 + c * 32;
-                if (col0 + 32 > V) {
+                for (int c = 0; c < HALF_COLS / 32; c++) {
+                    float v[32];
+                    __syncwarp();  // the gather loop below may leave the lanes diverged; tcgen05.ld is warp-collective
+                    tmem_ld32(tmem_base + ((uint32_t)(sub * 32) << 16) + buf * BN + half * HALF_COLS + c * 32, v);
+                    const int col0 = tile_col0 + c * 32;
+                    if (col0 + 32 > V) {
 #pragma unroll
-                    for (int i = 0; i < 32; i++)
-                        if (col0 + i >= V) v[i] = -CUDART_INF_F;
-                }
-                float cmax = v[0];
-#pragma unroll
-                for (int i = 1; i < 32; i++) cmax = fmaxf(cmax, v[i]);
-                if (cmax > m) {
-                    const float f = ex2((m - cmax) * kLog2e);  // 0 on the first chunk (m = -inf)
-                    s0 *= f, s1 *= f, s2 *= f, s3 *= f;
-                    m = cmax;
-                }
-                if (WANT_ARGMAX && cmax > best) {
-                    best = cmax;
-                    int idx = 31;
-#pragma unroll
-                    for (int i = 30; i >= 0; i--) idx = (v[i] == cmax) ? i : idx;
-                    best_idx = col0 + idx;
-                }
-                if (m > -CUDART_INF_F) {
-                    const float nm = -m * kLog2e;
-#pragma unroll
-                    for (int i = 0; i < 32; i += 4) {
-                        s0 += ex2(fmaf(v[i], kLog2e, nm));
-                        s1 += ex2(fmaf(v[i + 1], kLog2e, nm));
-                        s2 += ex2(fmaf(v[i + 2], kLog2e, nm));
-                        s3 += ex2(fmaf(v[i + 3], kLog2e, nm));
+                        for (int i = 0; i < 32; i++)
+                            if (col0 + i >= V) v[i] = -CUDART_INF_F;
                     }
-                }
-                if (my_tok) {
-                    while (p < T) {
-                        const int tk = __ldg(my_tok + p);
-                        if (tk >= col0 + 32) break;
-                        const int idx = tk - col0;
-                        if (idx >= 0 && row_ok) {
-                            float val = v[0];
+                    float w16[16];  // tree max
 #pragma unroll
-                            for (int i = 1; i < 32; i++) val = (idx == i) ? v[i] : val;
-                            my_out[__ldg(my_slot + p)] = val;  // raw logit; the merge kernel subtracts lse
+                    for (int i = 0; i < 16; i++) w16[i] = fmaxf(v[i], v[i + 16]);
+#pragma unroll
+                    for (int i = 0; i < 8; i++) w16[i] = fmaxf(w16[i], w16[i + 8]);
+#pragma unroll
+                    for (int i = 0; i < 4; i++) w16[i] = fmaxf(w16[i], w16[i + 4]);
+                    const float cmax = fmaxf(fmaxf(w16[0], w16[2]), fmaxf(w16[1], w16[3]));
+                    if (cmax > m) {
+                        const float f = ex2((m - cmax) * kLog2e);  // 0 on the first chunk (m = -inf)
+                        s0 *= f, s1 *= f, s2 *= f, s3 *= f;
+                        m = cmax;
+                    }
+                    if (WANT_ARGMAX && cmax > best) {
+                        best = cmax;
+                        int idx = 31;
+#pragma unroll
+                        for (int i = 30; i >= 0; i--) idx = (v[i] == cmax) ? i : idx;
+                        best_idx = col0 + idx;
+                    }
+                    if (m > -CUDART_INF_F) {
+                        const float nm = -m * kLog2e;
+#pragma unroll
+                        for (int i = 0; i < 32; i += 4) {
+                            s0 += ex2(fmaf(v[i], kLog2e, nm));
+                            s1 += ex2(fmaf(v[i + 1], kLog2e, nm));
+                            s2 += ex2(fmaf(v[i + 2], kLog2e, nm));
+                            s3 += ex2(fmaf(v[i + 3], kLog2e, nm));
                         }
-                        p++;
+                    }
+                    if (my_tok) {
+                        while (p < T) {  // targets are sorted; those below col0 belong to the other half
+                            const int tk = __ldg(my_tok + p);
+                            if (tk >= col0 + 32) break;
+                            const int idx = tk - col0;
+                            if (idx >= 0 && row_ok) {
+                                float val = v[0];
+#pragma unroll
+                                for (int i = 1; i < 32; i++) val = (idx == i) ? v[i] : val;
+                                my_out[__ldg(my_slot + p)] = val;  // raw logit; the merge kernel subtracts lse
+                            }
+                            p++;
+                        }
                     }
                 }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
-        }
-        if (row_ok && ok) {
-            Partial pr;
-            pr.m = m;
-            pr.s = (s0 + s1) + (s2 + s3);
-            pr.best = best;
-            pr.best_idx = best_idx;
-            partials[(size_t)split * N + row] = pr;
+            if (ok) {
+                Partial pr;
+                pr.m = m;
+                pr.s = (s0 + s1) + (s2 + s3);
+                pr.best = best;
+                pr.best_idx = best_idx;
+                partials[(((size_t)g * plan.max_seg + seg) * 2 + half) * BM + sub * 32 + lane] = pr;
+            }
+            seg++;
         }
     }
     if (*abort_flag && threadIdx.x == 0) flag(status, PCFGNAT_STATUS_TIMEOUT);
@@ -362,29 +408,38 @@ __global__ void __launch_bounds__(PROJ_THREADS, 1)
 }
 
 // ---------------------------------------------------------------------------------------
-// merge of the per-range partials
+// merge of the per-segment partials
 // ---------------------------------------------------------------------------------------
-__global__ void proj_merge_kernel(const Partial *__restrict__ partials, int n_splits, int N, int L, int T,
-                                  const int *__restrict__ stok, const int64_t *__restrict__ ol,
-                                  const int64_t *__restrict__ tl, float *match, float *max_lprob, int64_t *argmax,
-                                  float *lse_out) {
+__global__ void proj_merge_kernel(const Partial *__restrict__ partials, const Plan plan, int N, int L, int T,
+                                  const int64_t *__restrict__ ol, const int64_t *__restrict__ tl, float *match,
+                                  float *max_lprob, int64_t *argmax, float *lse_out) {
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (warp >= N) return;
-    const int row = warp;
+    const int row = warp, rt = row / BM, r_in = row % BM;
+    const long long u0 = (long long)rt * plan.n_tiles, u1 = u0 + plan.n_tiles - 1;
+    const int g_lo = plan.cta_of(u0), g_hi = plan.cta_of(u1);
     float m = -CUDART_INF_F, best = -CUDART_INF_F;
     int best_idx = 0;
-    for (int sp = 0; sp < n_splits; sp++) {
-        Partial p = partials[(size_t)sp * N + row];
-        m = fmaxf(m, p.m);
-        if (p.best > best) {  // ranges are visited in increasing column order: first maximum wins
-            best = p.best;
-            best_idx = p.best_idx;
+    // partial slots in increasing column order: CTA by CTA, inside a CTA half 0 and half 1 interleave per
+    // tile, so the first maximum over slots is resolved by comparing the recorded column index
+    for (int g = g_lo; g <= g_hi; g++) {
+        const int seg = rt - (int)(plan.begin(g) / plan.n_tiles);
+        for (int h = 0; h < 2; h++) {
+            const Partial p = partials[(((size_t)g * plan.max_seg + seg) * 2 + h) * BM + r_in];
+            m = fmaxf(m, p.m);
+            if (p.best > best || (p.best == best && p.best_idx < best_idx)) {
+                best = p.best;
+                best_idx = p.best_idx;
+            }
         }
     }
     float s = 0.f;
-    for (int sp = 0; sp < n_splits; sp++) {
-        Partial p = partials[(size_t)sp * N + row];
-        if (p.s > 0.f) s += p.s * exp2f((p.m - m) * kLog2e);
+    for (int g = g_lo; g <= g_hi; g++) {
+        const int seg = rt - (int)(plan.begin(g) / plan.n_tiles);
+        for (int h = 0; h < 2; h++) {
+            const Partial p = partials[(((size_t)g * plan.max_seg + seg) * 2 + h) * BM + r_in];
+            if (p.s > 0.f) s += p.s * exp2f((p.m - m) * kLog2e);
+        }
     }
     const float lse = m + log2f(s) * kLn2;
     if (lane == 0) {
@@ -449,22 +504,19 @@ bool make_map(CUtensorMap *map, const void *base, uint64_t rows, uint64_t K, uin
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-struct Plan {
-    int row_tiles, n_tiles, splits, tiles_per_split;
-};
-
 Plan make_plan(int N, int V) {
     int dev = 0, sms = 148;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (sms < 1) sms = 148;
     Plan p;
     p.row_tiles = (N + BM - 1) / BM;
     p.n_tiles = (V + BN - 1) / BN;
-    int want = sms / p.row_tiles;  // vocabulary ranges per row tile so that one wave fills the GPU
-    if (want < 1) want = 1;
-    if (want > p.n_tiles) want = p.n_tiles;
-    p.tiles_per_split = (p.n_tiles + want - 1) / want;
-    p.splits = (p.n_tiles + p.tiles_per_split - 1) / p.tiles_per_split;
+    p.units = (long long)p.row_tiles * p.n_tiles;
+    p.ctas = (int)(p.units < sms ? p.units : sms);
+    p.q = p.units / p.ctas;
+    p.rem = p.units % p.ctas;
+    const long long per_cta = p.q + (p.rem ? 1 : 0);
+    p.max_seg = (int)((per_cta + p.n_tiles - 1) / p.n_tiles) + 1;
     return p;
 }
 
@@ -474,7 +526,7 @@ size_t proj_workspace_bytes(int B, int L, int T, int V) {
     const int N = B * L;
     Plan p = make_plan(N > 0 ? N : 1, V > 0 ? V : 1);
     size_t lists = ((size_t)2 * B * (T > 0 ? T : 0) * sizeof(int) + 255) / 256 * 256;
-    size_t parts = ((size_t)p.splits * N * sizeof(Partial) + 255) / 256 * 256;
+    size_t parts = ((size_t)p.ctas * p.max_seg * 2 * BM * sizeof(Partial) + 255) / 256 * 256;
     return lists + parts + 256;
 }
 
@@ -500,26 +552,25 @@ int launch_proj(const void *hidden, const void *weight, const int64_t *targets, 
         return PCFGNAT_ERR_CUDA;
     if (gather) sort_targets_kernel<<<B, 128, 0, st>>>(targets, T, V, stok, sslot, status);
     const size_t smem = (size_t)KC_MAX * A_CHUNK_BYTES + (size_t)NSTAGE * B_STAGE_BYTES + 1024;
-    dim3 grid(p.row_tiles, p.splits);
     const bool want_arg = max_lprob != nullptr || argmax != nullptr;
     cudaError_t e;
     if (want_arg) {
         auto k = proj_kernel<true>;
-        e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        e = ensure_dynamic_smem(k, smem);
         if (e != cudaSuccess) return PCFGNAT_ERR_CUDA;
-        k<<<grid, PROJ_THREADS, smem, st>>>(map_a, map_w, N, V, H / BK, L, T, p.tiles_per_split, gather ? stok : nullptr,
-                                            gather ? sslot : nullptr, gather ? match : nullptr, partials, status);
+        k<<<p.ctas, PROJ_THREADS, smem, st>>>(map_a, map_w, p, N, V, H / BK, L, T, gather ? stok : nullptr,
+                                              gather ? sslot : nullptr, gather ? match : nullptr, partials, status);
     } else {
         auto k = proj_kernel<false>;
-        e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        e = ensure_dynamic_smem(k, smem);
         if (e != cudaSuccess) return PCFGNAT_ERR_CUDA;
-        k<<<grid, PROJ_THREADS, smem, st>>>(map_a, map_w, N, V, H / BK, L, T, p.tiles_per_split, gather ? stok : nullptr,
-                                            gather ? sslot : nullptr, gather ? match : nullptr, partials, status);
+        k<<<p.ctas, PROJ_THREADS, smem, st>>>(map_a, map_w, p, N, V, H / BK, L, T, gather ? stok : nullptr,
+                                              gather ? sslot : nullptr, gather ? match : nullptr, partials, status);
     }
     if (cudaGetLastError() != cudaSuccess) return PCFGNAT_ERR_CUDA;
     const int warps_per_block = 8;
     proj_merge_kernel<<<(N + warps_per_block - 1) / warps_per_block, warps_per_block * 32, 0, st>>>(
-        partials, p.splits, N, L, T, gather ? stok : nullptr, ol, tl, gather ? match : nullptr, max_lprob, argmax, lse);
+        partials, p, N, L, T, ol, tl, gather ? match : nullptr, max_lprob, argmax, lse);
     if (gather) proj_poison_bad_targets_kernel<<<B, 128, 0, st>>>(stok, sslot, B, L, T, match);
     return cuda_rc(cudaGetLastError());
 }

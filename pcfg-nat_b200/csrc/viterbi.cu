@@ -220,14 +220,14 @@ int launch_viterbi(const float *ob, const float *links, const int64_t *ol, int B
     cudaError_t e;
     if (smem_cols + smem_links <= (size_t)kSmemLimit - 1024) {
         auto k = viterbi_kernel<true>;
-        e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(smem_cols + smem_links));
+        e = ensure_dynamic_smem(k, smem_cols + smem_links);
         if (e != cudaSuccess) return PCFGNAT_ERR_CUDA;
         k<<<grid, block, smem_cols + smem_links, st>>>(ob, links, ol, L, S, R, Lt, Mt, status, Mc, col_stride,
                                                        lk_stride);
     } else {
         if (smem_cols > (size_t)kSmemLimit - 1024) return PCFGNAT_ERR_TOO_LARGE;
         auto k = viterbi_kernel<false>;
-        e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_cols);
+        e = ensure_dynamic_smem(k, smem_cols);
         if (e != cudaSuccess) return PCFGNAT_ERR_CUDA;
         k<<<grid, block, smem_cols, st>>>(ob, links, ol, L, S, R, Lt, Mt, status, Mc, col_stride, lk_stride);
     }

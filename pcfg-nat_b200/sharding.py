@@ -41,7 +41,8 @@ def local_loss_stats(sentence_loss: torch.Tensor, target_length: torch.Tensor) -
     invalid = torch.isinf(sentence_loss) | torch.isnan(sentence_loss)
     s = torch.where(invalid, torch.zeros_like(sentence_loss), sentence_loss)
     tl = target_length.to(device=sentence_loss.device, dtype=sentence_loss.dtype).clamp(min=1)
-    return torch.stack([(s / tl).sum(), s.new_tensor(float(s.numel())), invalid.sum().to(s.dtype)])
+    count = torch.full((), float(s.numel()), dtype=s.dtype, device=s.device)  # a fill kernel: capturable in a CUDA graph
+    return torch.stack([(s / tl).sum(), count, invalid.sum().to(s.dtype)])
 
 
 def reduce_loss(sentence_loss: torch.Tensor, target_length: torch.Tensor, group=None):

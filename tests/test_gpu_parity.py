@@ -444,3 +444,46 @@ def test_fused_projection_flags_bad_targets(ops):
     assert ops.read_status(DEV) & 4
     with pytest.raises(RuntimeError, match="multiple of 64"):
         ops.proj_logsoftmax_gather(hidden[:, :, :48].contiguous(), weight[:, :48].contiguous(), targets)
+
+
+# ---- the fixed-shape step object (CUDA-graph replay) ---------------------------------------------------------------
+
+def test_loss_step_graph_replay_matches_eager(pkg, ops, syn):
+    import importlib
+
+    runtime = importlib.import_module("pcfg_nat_b200.runtime")
+    w = syn.Workload("step", batch=6, vocab=3000, hidden=128, src_min=5, src_max=20, hidden_std=1.0)
+    b1, b2 = syn.make_batch(w, seed=1), syn.make_batch(w, seed=2)
+    L, T = max(b1.L, b2.L), max(b1.T, b2.T)
+
+    def padded(b):
+        hid = torch.zeros(b.B, L, w.hidden, dtype=torch.float16)
+        hid[:, :b.L] = b.hidden
+        lk = torch.full((b.B, L, 2, L), float("-inf"))
+        lk[:, :b.L, :, :b.L] = b.links
+        tg = torch.ones(b.B, T, dtype=torch.long)
+        tg[:, :b.T] = b.targets
+        return hid, lk, tg, b.output_length, b.target_length
+
+    weight = b1.weight.to(DEV)
+    eager = runtime.LossStep(weight, w.batch, L, T, DEV, use_graph=False)
+    graphed = runtime.LossStep(weight, w.batch, L, T, DEV, use_graph=True)
+    for b in (b1, b2, b1):  # the graph is captured on the first batch and replayed on the others
+        args = padded(b)
+        eager.load(*args)
+        graphed.load(*[t.pin_memory() for t in args])
+        se, mge, lge, le = [t.clone() for t in eager.run()]
+        sg, mgg, lgg, lg_ = graphed.run()
+        torch.cuda.synchronize()
+        assert torch.isfinite(le).all()
+        assert torch.equal(lg_, le) and torch.equal(sg, se)
+        assert torch.equal(mgg, mge) and torch.equal(lgg, lge)
+        # and against the torch reference of the projection feeding the oracle
+        hid, lk, tg, ol, tl = args
+        lp = torch.log_softmax(hid.float() @ b1.weight.float().t(), -1)  # the step object holds b1's projection matrix
+        match = lp.gather(2, tg[:, None, :].expand(-1, L, -1)).contiguous()
+        syn.eos_mask_(match, ol, tl)
+        So, _ = oracle.pcfg_loss(match.numpy(), lk.numpy(), ol.numpy(), tl.numpy())
+        np.testing.assert_allclose(le.cpu().numpy(), So[:, 0, 0], rtol=1e-4)
+        want = -(torch.from_numpy(So[:, 0, 0]) / tl).sum()
+        assert abs(float(-se[0]) - float(want)) < 1e-3 * abs(float(want)) and int(se[1]) == w.batch
