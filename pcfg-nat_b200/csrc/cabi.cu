@@ -1,6 +1,7 @@
 // extern "C" entry points declared in include/pcfgnat.h: argument checks, then launch.
 #include "common.cuh"
 
+#include <cstdlib>
 #include <mutex>
 
 using namespace pcfgnat;
@@ -35,6 +36,16 @@ cudaError_t ensure_dynamic_smem_for(const void *kernel, size_t bytes) {
         slot->bytes[dev] = (int)bytes;
     }
     return e;
+}
+
+bool force_row_kernels() {
+    const char *v = getenv("PCFGNAT_DP_ROWS");
+    return v && v[0] == '1';
+}
+
+bool force_balanced_inside() {
+    const char *v = getenv("PCFGNAT_DP_BALANCED_INSIDE");
+    return v && v[0] == '1' && !force_row_kernels();
 }
 
 }  // namespace pcfgnat

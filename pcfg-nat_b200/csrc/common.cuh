@@ -54,6 +54,16 @@ int launch_logsoftmax_gather(void *logits, int dtype, const int64_t *sel, int64_
                              int64_t rows, int64_t rpb, int V, int slen, int req_grad, float *selected, int *status,
                              cudaStream_t st);
 
+int launch_loss_fwd_balanced(const float *match_all, const float *links, const int64_t *ol, const int64_t *tl, int B,
+                             int L, int T, float *S, float *C, float *loss, int *status, cudaStream_t st);
+int launch_outside_balanced(const float *grad_output, const float *S, const float *match_all, const float *links,
+                            const int64_t *ol, const int64_t *tl, int B, int L, int T, float *G, int *status,
+                            cudaStream_t st);
+// PCFGNAT_DP_ROWS=1 in the environment keeps the row-per-thread DP kernels for every shape (A/B runs, tests).
+bool force_row_kernels();
+// PCFGNAT_DP_BALANCED_INSIDE=1 selects the phase-balanced inside kernel where it fits (default: row-per-thread).
+bool force_balanced_inside();
+
 size_t proj_workspace_bytes(int B, int L, int T, int V);
 int launch_proj(const void *hidden, const void *weight, const int64_t *targets, const int64_t *ol, const int64_t *tl,
                 int B, int L, int T, int V, int H, float *match, float *max_lprob, int64_t *argmax, float *lse,

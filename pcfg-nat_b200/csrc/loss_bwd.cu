@@ -283,7 +283,12 @@ int launch_loss_bwd(const float *grad_output, const float *S, const float *match
     const size_t smem_links = (size_t)2 * Mc * lk_stride * sizeof(float);
     dim3 block(kLanes, rows), grid(B);
     cudaError_t e;
-    if (smem_cols + smem_links <= (size_t)kSmemLimit - 1024) {
+    int brc = PCFGNAT_ERR_UNSUPPORTED;
+    if (!force_row_kernels())  // sentences that fit shared memory: evenly spread phases (loss_balanced.cu)
+        brc = launch_outside_balanced(grad_output, S, match_all, links, ol, tl, B, L, T, S_grad, status, st);
+    if (brc != PCFGNAT_ERR_UNSUPPORTED) {
+        if (brc != PCFGNAT_OK) return brc;
+    } else if (smem_cols + smem_links <= (size_t)kSmemLimit - 1024) {
         auto k = outside_kernel<true>;
         e = ensure_dynamic_smem(k, smem_cols + smem_links);
         if (e != cudaSuccess) return PCFGNAT_ERR_CUDA;

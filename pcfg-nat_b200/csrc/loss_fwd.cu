@@ -210,6 +210,13 @@ __global__ void __launch_bounds__(kMaxRows *kLanes)
 int launch_loss_fwd(const float *match_all, const float *links, const int64_t *ol, const int64_t *tl, int B, int L,
                     int T, float *S, float *C, float *loss, int *status, cudaStream_t st) {
     if (B == 0) return PCFGNAT_OK;
+    // The phase-balanced inside kernel (loss_balanced.cu) is bit-identical but measured slower than the
+    // row-per-thread kernel below (248 vs 172 us on the training batch: it executes ~2.7x the instructions),
+    // so it is only used on request; the balanced OUTSIDE kernel is the default (74 vs 201 us).
+    if (force_balanced_inside()) {
+        const int rc = launch_loss_fwd_balanced(match_all, links, ol, tl, B, L, T, S, C, loss, status, st);
+        if (rc != PCFGNAT_ERR_UNSUPPORTED) return rc;
+    }
     const int Mc = main_slots(L, 1), Lt = L - Mc;
     int rows = (Mc + 7) / 8 * 8;
     if (rows < 8) rows = 8;

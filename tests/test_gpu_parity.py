@@ -20,6 +20,20 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
 
+@pytest.fixture(params=["default", "rows", "balanced"])
+def dp_kernel(request, monkeypatch):
+    """Runs a test once per DP kernel selection: the default (row-per-thread inside pass, phase-balanced
+    outside pass where the sentence fits shared memory), row-per-thread only (PCFGNAT_DP_ROWS=1, what
+    longer graphs get) and phase-balanced for both passes (PCFGNAT_DP_BALANCED_INSIDE=1)."""
+    monkeypatch.delenv("PCFGNAT_DP_ROWS", raising=False)
+    monkeypatch.delenv("PCFGNAT_DP_BALANCED_INSIDE", raising=False)
+    if request.param == "rows":
+        monkeypatch.setenv("PCFGNAT_DP_ROWS", "1")
+    elif request.param == "balanced":
+        monkeypatch.setenv("PCFGNAT_DP_BALANCED_INSIDE", "1")
+    return request.param
+
+
 def _g(name):
     p = golden_path(name)
     if not os.path.isfile(p):
@@ -59,7 +73,7 @@ CASES = [
 
 
 @pytest.mark.parametrize("name,kw,seed", CASES)
-def test_loss_forward_against_oracle(ops, syn, name, kw, seed):
+def test_loss_forward_against_oracle(dp_kernel, ops, syn, name, kw, seed):
     b, ma = _loss_inputs(syn, syn.Workload(name, emissions="logits", **kw), seed)
     k = ops.get_pcfg_kernel()
     S, C = k.pcfg_loss(ma.to(DEV), b.links.to(DEV), b.output_length.to(DEV), b.target_length.to(DEV), 1)
@@ -72,7 +86,7 @@ def test_loss_forward_against_oracle(ops, syn, name, kw, seed):
 
 
 @pytest.mark.parametrize("name,kw,seed", CASES)
-def test_loss_backward_against_oracle(ops, syn, name, kw, seed):
+def test_loss_backward_against_oracle(dp_kernel, ops, syn, name, kw, seed):
     b, ma = _loss_inputs(syn, syn.Workload(name, emissions="logits", **kw), seed)
     ol, tl = b.output_length.numpy(), b.target_length.numpy()
     So, Co = oracle.pcfg_loss(ma.numpy(), b.links.numpy(), ol, tl)
@@ -128,7 +142,7 @@ def test_best_tree_tie_breaking(ops):
 
 
 @pytest.mark.parametrize("name", ["ref_loss_tiny.npz", "ref_loss_ragged.npz", "ref_loss_mid.npz"])
-def test_loss_against_reference_golden(ops, name):
+def test_loss_against_reference_golden(dp_kernel, ops, name):
     g = _g(name)
     k = ops.get_pcfg_kernel()
     ma, lk, ol, tl = _cu(g["match_all"]), _cu(g["links"]), _cu(g["output_length"]), _cu(g["target_length"])
@@ -240,7 +254,7 @@ def test_logsoftmax_gather_reference_golden_and_autograd(ops):
     np.testing.assert_allclose(xb.grad.cpu().numpy(), xa.grad.cpu().numpy(), atol=1e-5)
 
 
-def test_invalid_sentences_are_skipped_not_faulted(ops, syn):
+def test_invalid_sentences_are_skipped_not_faulted(dp_kernel, ops, syn):
     b, ma = _loss_inputs(syn, syn.Workload("bad", batch=4, vocab=50, hidden=8, src_min=4, src_max=6,
                                            emissions="logits"), 9)
     ol = b.output_length.clone()
@@ -296,7 +310,7 @@ def test_argument_errors(ops):
 # ---- full-size workloads: properties that need no oracle run ---------------------------------------------------
 
 @pytest.mark.parametrize("wname", ["glance", "long_seq"])
-def test_full_size_properties(ops, syn, wname):
+def test_full_size_properties(dp_kernel, ops, syn, wname):
     w = syn.WORKLOADS[wname]
     b = syn.make_batch(syn.Workload(w.name, batch=w.batch, vocab=64, hidden=8, fixed_graph=w.fixed_graph,
                                     fixed_target=w.fixed_target, emissions="logits"), seed=0)
@@ -349,7 +363,7 @@ def _ref():
 
 
 @pytest.mark.parametrize("seed", [10, 11, 12])
-def test_live_against_reference_kernels(ops, syn, seed):
+def test_live_against_reference_kernels(dp_kernel, ops, syn, seed):
     ref = _ref()
     # graph length <= 256 keeps every reference launch at one row segment per sentence (no
     # dependence on co-resident blocks in its spin-waits)
