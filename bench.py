@@ -1,27 +1,30 @@
-"""Benchmark of the PCFG-NAT structured-loss hot path on B200.
+"""Benchmark of the PCFG-NAT structured-loss / decoding hot path on B200.
 
     python bench.py --gpus N --steps K --warmup W            # this implementation
     python bench.py --impl reference ...                     # the path on the host CPU cores
+    python bench.py --workload viterbi_b64 | viterbi_b1 | glance | long_seq | tiny_loss ...
 
-One "step" is one pass of the hot path over one training-shaped batch (workload
-``train_batch``: ~90 sentences, graph length 4 x source length <= 160, vocabulary 40 000,
-hidden 512, fp16 decoder states and projection weights, fp32 DP tables):
+The default workload ``train_batch`` is one training-shaped batch (~90 sentences, ~2.7 k target tokens,
+graph length 4 x source length <= 160, vocabulary 40 000, hidden 512, fp16 decoder states and projection
+weights, fp32 DP tables).  One "step" is one pass of the hot path over the batch:
 
-    emissions  match[b, node, t] = log P(y_t | node)    fused projection + log-softmax + gather
-                                                         (+ the criterion's EOS masking)
-    loss       S[b] and d S[b] / d match, d S[b] / d links   inside + outside pass
-    scalar     -(S_b / n_b).mean() with invalid sentences masked and counted
+    loss workloads   emissions match[b, node, t] = log P(y_t | node) (fused projection + log-softmax +
+                     gather + the criterion's EOS masking), S[b] and dS[b]/dmatch, dS[b]/dlinks (inside +
+                     outside pass), loss statistics for -(S_b / n_b).mean()
+    glance           emissions + arg-max tokens, inside table, best-tree alignment
+    viterbi_*        max log-prob / arg-max token per node, Viterbi tables, length-penalised output
+                     length, back-trace to token ids on the device
 
-Inputs are seeded synthetic tensors of the named shapes (the WMT batches the reference
-trains on are not available offline).  With N > 1 every rank runs its own batch (weak
-scaling, as under data-parallel training); the only collective is the 3-float all-reduce
-of the loss statistics.  One JSON line is printed by rank 0.
+Inputs are seeded synthetic tensors of the named shapes (the WMT batches the reference trains on are not
+available offline).  With N > 1 every rank runs its own batch (weak scaling, as under data-parallel
+training); the only collective is the 3-float all-reduce of the loss statistics (loss workloads).  One JSON
+line is printed by rank 0.
 """
 import argparse
+import importlib
 import json
 import os
 import statistics
-import subprocess
 import sys
 import threading
 import time
@@ -32,9 +35,9 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 import __graft_entry__ as entry  # noqa: E402
 
-METRIC = "pcfg_loss_fwd_bwd_sentences_per_s"
 UNIT = "sentences/s"
-KERNELS_PER_STEP = 7  # sort_targets, proj, proj_merge, proj_poison_bad_targets, loss_fwd, outside, grad
+METRICS = {"loss": "pcfg_loss_fwd_bwd_sentences_per_s", "glance": "pcfg_best_tree_sentences_per_s",
+           "viterbi": "pcfg_viterbi_decode_sentences_per_s"}
 
 
 def parse():
@@ -47,7 +50,8 @@ def parse():
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--cpu-sample", type=int, default=8, help="sentences in the CPU-baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--no-graph", action="store_true", help="enqueue the step kernel by kernel instead of replaying a CUDA graph")
+    ap.add_argument("--no-graph", action="store_true",
+                    help="enqueue the step kernel by kernel instead of replaying a CUDA graph")
     return ap.parse_args()
 
 
@@ -126,12 +130,31 @@ def algorithmic(batch):
     """Algorithmic work of one step from the unpadded sentence lengths."""
     V, H = batch.weight.shape
     rows = int(batch.output_length.sum())
-    flops_proj = 2.0 * rows * H * V
     L_b = batch.output_length.double()
     n_b = batch.target_length.double()
-    bytes_dp = float((8.0 * L_b * (n_b + 2.0 * L_b)).sum())  # read match + links, write both gradients
-    return {"rows": rows, "rows_padded": batch.B * batch.L, "proj_flops": flops_proj,
-            "proj_flops_padded": 2.0 * batch.B * batch.L * H * V, "dp_bytes": bytes_dp}
+    kind = batch.workload.kind
+    if kind == "viterbi":  # ob + links read, S + three int64 backpointer tables written
+        dp = float((4.0 * L_b + 8.0 * L_b * L_b + 28.0 * L_b * torch.floor(L_b / 4)).sum())
+    elif kind == "glance":  # match + links read, tree written
+        dp = float((4.0 * L_b * (n_b + 2.0 * L_b) + 8.0 * L_b).sum())
+    else:  # match + links read, both gradients written
+        dp = float((8.0 * L_b * (n_b + 2.0 * L_b)).sum())
+    return {"rows": rows, "rows_padded": batch.B * batch.L, "proj_flops": 2.0 * rows * H * V,
+            "proj_flops_padded": 2.0 * batch.B * batch.L * H * V, "dp_bytes": dp}
+
+
+def make_step(runtime, batch, weight, dev, use_graph):
+    """The public step object of the workload's kind and the host tensors it loads, in load() order."""
+    kind = batch.workload.kind
+    if kind == "viterbi":
+        step = runtime.DecodeStep(weight, batch.B, batch.L, batch.left_tree_mask, dev, beta=1.0, pad_index=1,
+                                  use_graph=use_graph)
+        host = (batch.hidden, batch.links, batch.output_length)
+    else:
+        cls = runtime.GlanceStep if kind == "glance" else runtime.LossStep
+        step = cls(weight, batch.B, batch.L, batch.T, dev, use_graph=use_graph)
+        host = (batch.hidden, batch.links, batch.output_length, batch.targets, batch.target_length)
+    return step, [t.contiguous().pin_memory() for t in host]
 
 
 def run_ours(a):
@@ -139,7 +162,8 @@ def run_ours(a):
     world = int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", 0))
     if not torch.cuda.is_available():
-        raise RuntimeError("bench.py needs a CUDA device: the product has no CPU path (use --impl reference for the CPU baseline)")
+        raise RuntimeError("bench.py needs a CUDA device: the product has no CPU path "
+                           "(use --impl reference for the CPU baseline)")
     import torch.distributed as dist
 
     dev = torch.device("cuda", local)
@@ -147,28 +171,27 @@ def run_ours(a):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     pkg = entry.load_package()
-    import importlib
-
     ops = importlib.import_module("pcfg_nat_b200.custom_ops.pcfg_loss")
     runtime = importlib.import_module("pcfg_nat_b200.runtime")
     k = ops.get_pcfg_kernel()
     syn = pkg.synthetic
 
     batch = syn.make_batch(a.workload, seed=a.seed + rank)  # every rank its own batch: weak scaling
+    if batch.hidden is None:
+        raise RuntimeError(f"workload {a.workload} has no decoder states; the benchmark runs the projection path")
+    kind = batch.workload.kind
     alg = algorithmic(batch)
-    # host copies in pinned memory: the end-to-end leg copies them to the device every step
-    host = [t.contiguous().pin_memory() for t in (batch.hidden, batch.links, batch.targets, batch.output_length,
-                                                  batch.target_length)]
     weight = batch.weight.to(dev)
-    # the public step object: fused projection -> loss forward+backward -> loss statistics, replayed as one CUDA graph
-    step = runtime.LossStep(weight, batch.B, batch.L, batch.T, dev, use_graph=not a.no_graph)
+    step, host = make_step(runtime, batch, weight, dev, not a.no_graph)  # host: pinned copies for the end-to-end leg
     step.load(*host)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)  # > 126 MB L2
     h2d = step.input_bytes()
-    loss_host = torch.empty(3, dtype=torch.float32).pin_memory()
+    is_loss = kind == "loss"
+    result_host = None
 
     def timed(n_steps, e2e):
         """Per-step CUDA-event timing on the launching stream with an L2 flush between steps."""
+        nonlocal result_host
         times = []
         for _ in range(n_steps):
             flush.fill_(1)
@@ -176,24 +199,32 @@ def run_ours(a):
             s.record()
             if e2e:
                 step.load(*host)
-            stats = step.run()[0]
-            if world > 1:
-                dist.all_reduce(stats)
-            if e2e:
-                loss_host.copy_(stats, non_blocking=True)
+            out = step.run()
+            if is_loss and world > 1:
+                dist.all_reduce(out[0])
+            if e2e:  # the step's result goes back to the host: loss statistics / token ids + counts / alignment
+                res = (out[0],) if is_loss else ((out[0], out[1]) if kind == "viterbi" else (out[0],))
+                if result_host is None:
+                    result_host = [torch.empty(r.shape, dtype=r.dtype).pin_memory() for r in res]
+                for h, r in zip(result_host, res):
+                    h.copy_(r, non_blocking=True)
             e.record()
             times.append((s, e))
         torch.cuda.synchronize()
         return [s.elapsed_time(e) for s, e in times]
 
     def timed_projection(n_steps):
-        """The dominant kernel on its own (the projection call: sort, proj_kernel, merge, poison), for the roofline."""
+        """The dominant kernel on its own (the projection call: proj_kernel and its helper launches)."""
         times = []
         for _ in range(n_steps):
             flush.fill_(1)
             s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             s.record()
-            k.proj_logsoftmax_gather(step.hidden, weight, step.targets, step.output_length, step.target_length)
+            if kind == "viterbi":
+                k.proj_logsoftmax_gather(step.hidden, weight, None, step.output_length, None, want_max=True)
+            else:
+                k.proj_logsoftmax_gather(step.hidden, weight, step.targets, step.output_length, step.target_length,
+                                         want_max=(kind == "glance"))
             e.record()
             times.append((s, e))
         torch.cuda.synchronize()
@@ -205,7 +236,8 @@ def run_ours(a):
             dist.barrier()
         torch.cuda.synchronize()
 
-    timed(max(a.warmup, 3), False)
+    warm = max(a.warmup, 3)
+    timed(warm, False)
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
@@ -223,6 +255,7 @@ def run_ours(a):
     proj_ms = timed_projection(a.steps)
     sync_all()
     status = ops.read_status(dev)
+    d2h = sum(h.numel() * h.element_size() for h in result_host)
 
     tot = torch.tensor([sum(step_ms), sum(e2e_ms), sum(proj_ms)], dtype=torch.float64, device=dev)
     if world > 1:
@@ -234,25 +267,28 @@ def run_ours(a):
     pk = peaks()
     proj_avg_s = (tot[2] / a.steps) / 1e3
     achieved = alg["proj_flops"] / proj_avg_s / 1e12
+    rest_ms = max(tot[0] - tot[2], 1e-9) / a.steps
     line = {
-        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": a.steps, "warmup": max(a.warmup, 3),
+        "metric": METRICS[kind], "value": value, "unit": UNIT, "n_gpus": world, "steps": a.steps, "warmup": warm,
         "ms_per_step": tot[0] / a.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f16 projection inputs, f32 accumulation and DP tables", "data": "synthetic",
         "config": {"workload": a.workload, "sentences_per_gpu": batch.B, "graph_len_max": batch.L,
                    "target_len_max": batch.T, "vocab": int(weight.shape[0]), "hidden": int(weight.shape[1]),
-                   "left_tree_layer": 1, "target_tokens_per_gpu": int(batch.target_length.sum()),
-                   "l2": "flushed between timed steps (256 MB write)", "cuda_graph": not a.no_graph, "parallelism": f"sentence-sharded x{world}"},
-        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 12,
+                   "left_tree_layer": 1, "graph_nodes_per_gpu": alg["rows"],
+                   "target_tokens_per_gpu": int(batch.target_length.sum()),
+                   "l2": "flushed between timed steps (256 MB write)", "cuda_graph": not a.no_graph,
+                   "parallelism": f"sentence-sharded x{world}"},
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": tot[1] / a.steps},
-        "gpu_launches": KERNELS_PER_STEP * a.steps,
-        "roofline": {"bound": "tensor", "kernel": "proj_kernel (+ its 3 helper launches)", "achieved": achieved,
-                     "peak": pk["tflops"], "unit": "TFLOP/s", "frac": achieved / pk["tflops"],
+        "gpu_launches": step.kernels_per_step * a.steps,
+        "roofline": {"bound": "tensor", "kernel": "proj_kernel (timed with its helper launches: row compaction, "
+                                                  "target sort, partial merge)",
+                     "achieved": achieved, "peak": pk["tflops"], "unit": "TFLOP/s", "frac": achieved / pk["tflops"],
                      "peak_source": pk["source"] + " (burst bf16 GEMM)", "traffic": None,
-                     "ms_per_launch": proj_avg_s * 1e3, "flops_per_launch": alg["proj_flops"],
-                     "achieved_padded_rows": alg["proj_flops_padded"] / proj_avg_s / 1e12},
-        "dp": {"ms_per_step": (tot[0] - tot[2]) / a.steps, "algorithmic_bytes": alg["dp_bytes"],
-               "achieved_gbs": alg["dp_bytes"] / (max(tot[0] - tot[2], 1e-9) / a.steps / 1e3) / 1e9,
-               "hbm_peak_gbs": pk["gbs"], "note": "step time minus the separately timed projection call"},
+                     "ms_per_launch": proj_avg_s * 1e3, "flops_per_launch": alg["proj_flops"]},
+        "dp": {"ms_per_step": rest_ms, "algorithmic_bytes": alg["dp_bytes"],
+               "achieved_gbs": alg["dp_bytes"] / (rest_ms / 1e3) / 1e9, "hbm_peak_gbs": pk["gbs"],
+               "note": "DP kernels: step time minus the separately timed projection call; latency-bound"},
         "clocks": clocks, "device_status": status,
     }
     if rank == 0:
@@ -264,9 +300,9 @@ def run_ours(a):
 
 
 def cpu_baseline(a, batch=None, steps=1):
-    """The same step on the host cores: the C oracle (a port of the reference kernels; the reference
-    has no CPU implementation of this path) with OpenMP over sentences, and torch's CPU GEMM for
-    the projection, on a bounded sample of the workload's sentences."""
+    """The same step on the host cores: the C oracle (a port of the reference kernels; the reference has
+    no CPU implementation of this path) with OpenMP over sentences, and torch's CPU GEMM for the
+    projection, on a bounded sample of the workload's sentences."""
     import numpy as np
 
     import oracle
@@ -275,6 +311,7 @@ def cpu_baseline(a, batch=None, steps=1):
     syn = pkg.synthetic
     if batch is None:
         batch = syn.make_batch(a.workload, seed=a.seed)
+    kind = batch.workload.kind
     n = min(a.cpu_sample, batch.B)
     sub = batch.select(list(range(n)))
     cores = os.cpu_count() or 1
@@ -285,17 +322,30 @@ def cpu_baseline(a, batch=None, steps=1):
         t0 = time.perf_counter()
         logits = sub.hidden.float().reshape(-1, sub.hidden.shape[-1]) @ sub.weight.float().t()
         lp = torch.log_softmax(logits, -1).view(n, sub.L, -1)
-        match = lp.gather(2, sub.targets[:, None, :].expand(-1, sub.L, -1)).contiguous()
-        syn.eos_mask_(match, sub.output_length, sub.target_length)
-        m_np, l_np = match.numpy(), sub.links.numpy()
-        ol, tl = sub.output_length.numpy(), sub.target_length.numpy()
-        S, C = oracle.pcfg_loss(m_np, l_np, ol, tl)
-        oracle.pcfg_loss_backward(np.ones(n, np.float32), S, C, m_np, l_np, ol, tl)
+        l_np, ol = sub.links.numpy(), sub.output_length.numpy()
+        if kind == "viterbi":
+            ob, tok = lp.max(-1)
+            S, R, Lt, Mt = oracle.pcfg_viterbi(ob.numpy(), l_np, ol)
+            sc = torch.from_numpy(S[:, 1, :]) / torch.arange(sub.L // 4).unsqueeze(0)
+            sc = torch.where(torch.isnan(sc), torch.full_like(sc, float("-inf")), sc)
+            pred = sc[:, 1:].max(-1)[1] + 1
+            oracle.viterbi_decoding(pred.numpy(), ol, Lt, R, Mt, tok.numpy(), sub.left_tree_mask.long().numpy(), 1)
+            what = "torch CPU fp32 GEMM + log-softmax + max, C oracle Viterbi tables + back-trace"
+        else:
+            match = lp.gather(2, sub.targets[:, None, :].expand(-1, sub.L, -1)).contiguous()
+            syn.eos_mask_(match, sub.output_length, sub.target_length)
+            m_np, tl = match.numpy(), sub.target_length.numpy()
+            S, C = oracle.pcfg_loss(m_np, l_np, ol, tl)
+            if kind == "glance":
+                oracle.pcfg_best_tree(S, C, m_np, l_np, ol, tl)
+                what = "torch CPU fp32 GEMM + log-softmax + gather, C oracle inside pass + best tree"
+            else:
+                oracle.pcfg_loss_backward(np.ones(n, np.float32), S, C, m_np, l_np, ol, tl)
+                what = "torch CPU fp32 GEMM + log-softmax + gather, C oracle loss forward + backward"
         dt = time.perf_counter() - t0
         best = dt if best is None else min(best, dt)
     return {"value": n / best, "unit": UNIT, "cores": cores, "kind": "port",
-            "sample": f"first {n} of {batch.B} sentences of {a.workload} (projection with torch CPU fp32 GEMM, "
-                      f"log-softmax + gather, C oracle loss forward + backward); best of {max(steps, 1)} passes, "
+            "sample": f"first {n} of {batch.B} sentences of {a.workload} ({what}); best of {max(steps, 1)} passes, "
                       f"{best:.3f} s per pass"}
 
 
@@ -303,8 +353,10 @@ def run_reference(a):
     rank = int(os.environ.get("RANK", 0))
     if rank != 0:
         return
+    pkg = entry.load_package()
+    kind = pkg.synthetic.WORKLOADS[a.workload].kind
     cb = cpu_baseline(a, None, steps=max(1, min(a.steps, 3)))
-    line = {"impl": "reference", "metric": METRIC, "value": cb["value"], "unit": UNIT, "n_gpus": a.gpus,
+    line = {"impl": "reference", "metric": METRICS[kind], "value": cb["value"], "unit": UNIT, "n_gpus": a.gpus,
             "steps": a.steps, "warmup": a.warmup, "ms_per_step": None, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32 on the CPU", "data": "synthetic",
             "config": {"workload": a.workload}, "cpu_baseline": cb,

@@ -136,6 +136,8 @@ int pcfgnat_logsoftmax_gather(void *logits, int dtype, const int64_t *select_idx
  *   match     [B*L][T] f32  log P(target t | row); with output_length and target_length given
  *                           the criterion's EOS masking is applied
  *                           (fs_plugins/criterions/nat_pcfg_loss.py:112-115)
+ * With output_length given (target_length optional) only the rows of real nodes (l < m_b) are
+ * projected; the padding rows of every output are set to zero.  Without it all B*L rows are.
  *   max_lprob [B*L]    f32  max_v log P(v | row),   argmax [B*L] int64 its index
  *   lse       [B*L]    f32  log-sum-exp of the row's logits
  * workspace: pcfgnat_proj_workspace_bytes(B, L, T, V) bytes, 16-byte aligned. */

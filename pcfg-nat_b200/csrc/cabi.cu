@@ -177,7 +177,7 @@ int pcfgnat_proj_logsoftmax_gather(const void *hidden, const void *weight, const
     if ((long long)B * L > (1ll << 30)) return PCFGNAT_ERR_TOO_LARGE;
     if (B && (!hidden || !weight || !workspace)) return PCFGNAT_ERR_INVALID_ARGUMENT;
     if (match && (!targets || T < 1)) return PCFGNAT_ERR_INVALID_ARGUMENT;
-    if ((output_length == nullptr) != (target_length == nullptr)) return PCFGNAT_ERR_INVALID_ARGUMENT;
+    if (target_length != nullptr && output_length == nullptr) return PCFGNAT_ERR_INVALID_ARGUMENT;
     return launch_proj(hidden, weight, targets, output_length, target_length, B, L, T, V, H, match, max_lprob, argmax,
                        lse, workspace, workspace_bytes, status, static_cast<cudaStream_t>(stream));
 }

@@ -7,19 +7,22 @@
 //   lprob, token = logits.log_softmax(-1).max(-1)       (models/...pcfg.py:414-415)
 //
 // Shape of the kernel (sm_100a only: tcgen05 tensor cores, TMEM accumulators, TMA):
-//   * the work is the grid of (128-row tile of the decoder states) x (256-wide vocabulary tile)
-//     units, flattened row-tile-major and cut into one contiguous range per CTA, one CTA per SM, so
-//     that every SM gets the same number of units whatever the number of rows.  A range crosses
-//     at most a few row tiles ("segments"); per segment the 128 x H fp16 state tile is loaded once
-//     and stays resident in shared memory (H <= 512: 128 KB) while the projection matrix streams
-//     through a 3-stage ring of 256 x 64 fp16 tiles (32 KB each);
-//   * warp 0 drives TMA (cp.async.bulk.tensor, 128-byte swizzle, no multicast), warp 1 issues
+//   * rows are compacted first: when the graph lengths are known, only the rows of real nodes
+//     (l < m_b) are projected; a small kernel builds the list of source rows.  Padded rows get
+//     zeros in every output;
+//   * the work is the grid of (128 compact rows) x (256-wide vocabulary tile) units, flattened
+//     row-tile-major and cut into one contiguous range per CTA, one CTA per SM, so that every SM
+//     gets the same number of units whatever the number of rows.  A range crosses at most a few
+//     row tiles ("segments"); per segment the 128 x H fp16 state tile is gathered once into shared
+//     memory (128-byte-swizzled, the layout TMA would produce; H <= 512: 128 KB) and stays resident
+//     while the projection matrix streams through a 3-stage TMA ring of 256 x 64 fp16 tiles;
+//   * warp 0 drives TMA (cp.async.bulk.tensor into this CTA only, 128-byte swizzle), warp 1 issues
 //     tcgen05.mma 128x256x16 (fp16 in, fp32 accumulate) into one of two 256-column TMEM
-//     accumulators, warps 2-9 are the epilogue: two warps per TMEM sub-partition, each thread owns
-//     one row and one 128-column half of the tile, reads it with tcgen05.ld and keeps an online
-//     (max, sum-exp), the running arg-max and the raw logits of this row's targets, while the
-//     MMA warp already fills the other accumulator;
-//   * a second, tiny kernel merges the per-segment partials: lse, match = logit - lse (with the
+//     accumulators, warps 2-9 load the state tile and are the epilogue: two warps per TMEM
+//     sub-partition, each thread owns one row and one 128-column half of the tile, reads it with
+//     tcgen05.ld and keeps an online (max, sum-exp), the running arg-max and the raw logits of this
+//     row's targets, while the MMA warp already fills the other accumulator;
+//   * a last, tiny kernel merges the per-segment partials: lse, match = logit - lse (with the
 //     criterion's EOS masking fused if lengths are given), max log-prob and arg-max.
 // Every wait on an mbarrier is bounded; on expiry the CTA records PCFGNAT_STATUS_TIMEOUT, stops
 // issuing work, and still frees its tensor memory.
@@ -57,9 +60,20 @@ struct Partial {  // per (CTA, segment, column half, row)
 };
 
 // Flattened schedule: unit u = row_tile * n_tiles + vocab_tile; CTA g owns [begin(g), begin(g + 1)).
+// Built on the device from the compact row count, so the host never needs to know it.
 struct Plan {
-    int row_tiles, n_tiles, ctas, max_seg;
+    int n_tiles, ctas, max_seg;
     long long units, q, rem;  // the first `rem` CTAs own q + 1 units, the others q
+    __host__ __device__ static Plan make(int rows, int V, int ctas, int max_seg) {
+        Plan p;
+        p.n_tiles = (V + BN - 1) / BN;
+        p.ctas = ctas;
+        p.max_seg = max_seg;
+        p.units = (long long)((rows + BM - 1) / BM) * p.n_tiles;
+        p.q = p.units / ctas;
+        p.rem = p.units % ctas;
+        return p;
+    }
     __host__ __device__ long long begin(int g) const { return (long long)g * q + (g < rem ? g : rem); }
     __host__ __device__ int cta_of(long long u) const {
         const long long big = rem * (q + 1);
@@ -147,8 +161,36 @@ __device__ __forceinline__ float ex2(float x) {
 }
 
 // ---------------------------------------------------------------------------------------
-// target lists sorted by token id, one per sentence
+// preparation: compact row list, target lists sorted by token id
 // ---------------------------------------------------------------------------------------
+// row_src[compact row] = padded row b * L + l for every real node (l < m_b; every l when no
+// lengths are given), prefix[b] = compact index of sentence b's first row, *n_rows = their count.
+__global__ void compact_rows_kernel(const int64_t *__restrict__ ol, int B, int L, int *prefix, int *row_src,
+                                    int *n_rows, int *status) {
+    __shared__ int total;
+    if (threadIdx.x == 0) {
+        int acc = 0;
+        for (int b = 0; b < B; b++) {
+            prefix[b] = acc;
+            int m = ol ? (int)ol[b] : L;
+            if (m < 0 || m > L) {
+                flag(status, PCFGNAT_STATUS_BAD_LENGTH);
+                m = m < 0 ? 0 : L;
+            }
+            acc += m;
+        }
+        prefix[B] = acc;
+        *n_rows = acc;
+        total = acc;
+    }
+    __syncthreads();
+    for (int b = 0; b < B; b++) {
+        const int lo = prefix[b], len = prefix[b + 1] - lo;
+        for (int l = threadIdx.x; l < len; l += blockDim.x) row_src[lo + l] = b * L + l;
+    }
+    (void)total;
+}
+
 __global__ void sort_targets_kernel(const int64_t *__restrict__ targets, int T, int V, int *stok, int *sslot,
                                     int *status) {
     const int b = blockIdx.x;
@@ -174,9 +216,10 @@ __global__ void sort_targets_kernel(const int64_t *__restrict__ targets, int T, 
 // ---------------------------------------------------------------------------------------
 template <bool WANT_ARGMAX>
 __global__ void __launch_bounds__(PROJ_THREADS, 1)
-    proj_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, const Plan plan,
-                int N, int V, int KC, int L, int T, const int *__restrict__ stok, const int *__restrict__ sslot,
-                float *match, Partial *partials, int *status) {
+    proj_kernel(const __grid_constant__ CUtensorMap map_w, const __half *__restrict__ hidden,
+                const int *__restrict__ row_src, const int *__restrict__ n_rows_ptr, int max_seg, int V, int KC, int L,
+                int T, const int *__restrict__ stok, const int *__restrict__ sslot, float *match, Partial *partials,
+                int *status) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t bars[2 * NSTAGE + 2 + 4];
     __shared__ uint32_t tmem_base_slot;
@@ -184,6 +227,8 @@ __global__ void __launch_bounds__(PROJ_THREADS, 1)
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = blockIdx.x;
+    const int n_rows = *n_rows_ptr;
+    const Plan plan = Plan::make(n_rows, V, gridDim.x, max_seg);
     const long long u_begin = plan.begin(g), u_end = plan.begin(g + 1);
     const int NT = plan.n_tiles;
 
@@ -192,7 +237,7 @@ __global__ void __launch_bounds__(PROJ_THREADS, 1)
     const uint32_t smem_b = smem_a + KC_MAX * A_CHUNK_BYTES;
     const uint32_t bar_full = smem_u32(&bars[0]);                 // [NSTAGE] W stage landed
     const uint32_t bar_empty = smem_u32(&bars[NSTAGE]);           // [NSTAGE] W stage consumed
-    const uint32_t bar_a = smem_u32(&bars[2 * NSTAGE]);           // state tile landed
+    const uint32_t bar_a = smem_u32(&bars[2 * NSTAGE]);           // state tile written (one arrival per loader thread)
     const uint32_t bar_a_free = smem_u32(&bars[2 * NSTAGE + 1]);  // all MMAs of the segment have read it
     const uint32_t bar_tfull = smem_u32(&bars[2 * NSTAGE + 2]);   // [2] accumulator ready
     const uint32_t bar_tempty = smem_u32(&bars[2 * NSTAGE + 4]);  // [2] accumulator drained
@@ -203,7 +248,7 @@ __global__ void __launch_bounds__(PROJ_THREADS, 1)
             mbar_init(bar_full + 8 * i, 1);
             mbar_init(bar_empty + 8 * i, 1);
         }
-        mbar_init(bar_a, 1);
+        mbar_init(bar_a, EPI_WARPS * 32);  // every loader thread arrives after fencing its own writes
         mbar_init(bar_a_free, 1);
         for (int i = 0; i < 2; i++) {
             mbar_init(bar_tfull + 8 * i, 1);
@@ -224,31 +269,21 @@ __global__ void __launch_bounds__(PROJ_THREADS, 1)
     const uint32_t tmem_base = tmem_base_slot;
 
     if (warp == 0) {
-        // ------------------------------ TMA producer ------------------------------
+        // ------------------------------ TMA producer: streams W, segment after segment ------------
         if (lane == 0) {
-            uint32_t it = 0, seg = 0;
+            uint32_t it = 0;
             bool ok = true;
-            long long u = u_begin;
-            while (u < u_end && ok) {
-                const int rt = (int)(u / NT);
-                const long long seg_end = min(u_end, (long long)(rt + 1) * NT);
-                // the previous segment's MMAs must have finished reading the resident state tile
-                if (seg > 0 && !mbar_wait(bar_a_free, (seg - 1) & 1, abort_flag)) break;
-                mbar_expect_tx(bar_a, (uint32_t)KC * A_CHUNK_BYTES);
-                for (int kc = 0; kc < KC; kc++) tma_load_2d(smem_a + kc * A_CHUNK_BYTES, &map_a, bar_a, kc * BK, rt * BM);
-                for (; u < seg_end && ok; u++) {
-                    const int t = (int)(u - (long long)rt * NT);
-                    for (int kc = 0; kc < KC; kc++, it++) {
-                        const uint32_t st = it % NSTAGE, ph = (it / NSTAGE) & 1;
-                        if (!mbar_wait(bar_empty + 8 * st, ph ^ 1, abort_flag)) {
-                            ok = false;
-                            break;
-                        }
-                        mbar_expect_tx(bar_full + 8 * st, B_STAGE_BYTES);
-                        tma_load_2d(smem_b + st * B_STAGE_BYTES, &map_w, bar_full + 8 * st, kc * BK, t * BN);
+            for (long long u = u_begin; u < u_end && ok; u++) {
+                const int t = (int)(u % NT);
+                for (int kc = 0; kc < KC; kc++, it++) {
+                    const uint32_t st = it % NSTAGE, ph = (it / NSTAGE) & 1;
+                    if (!mbar_wait(bar_empty + 8 * st, ph ^ 1, abort_flag)) {
+                        ok = false;
+                        break;
                     }
+                    mbar_expect_tx(bar_full + 8 * st, B_STAGE_BYTES);
+                    tma_load_2d(smem_b + st * B_STAGE_BYTES, &map_w, bar_full + 8 * st, kc * BK, t * BN);
                 }
-                seg++;
             }
         }
     } else if (warp == 1) {
@@ -290,19 +325,41 @@ __global__ void __launch_bounds__(PROJ_THREADS, 1)
             }
         }
     } else {
-        // ------------------ epilogue: one row and one 128-column half per thread ------------------
+        // -------- state-tile loader + epilogue: one row and one 128-column half per thread --------
         const int ew = warp - 2;
-        const int sub = warp & 3;  // TMEM sub-partition (lanes 32*sub ..) this warp may read
-        const int half = ew >> 2;  // which 128 columns of each 256-wide tile
+        const int et = ew * 32 + lane;  // 0 .. 255
+        const int sub = warp & 3;       // TMEM sub-partition (lanes 32*sub ..) this warp may read
+        const int half = ew >> 2;       // which 128 columns of each 256-wide tile
         uint32_t tile = 0, seg = 0;
         bool ok = true;
         long long u = u_begin;
         while (u < u_end && ok) {
             const int rt = (int)(u / NT);
             const long long seg_end = min(u_end, (long long)(rt + 1) * NT);
-            const int row = rt * BM + sub * 32 + lane;
-            const bool row_ok = row < N;
-            const int sent = row_ok ? row / L : 0;
+            // ---- gather the 128 x H state tile into the swizzled layout tcgen05.mma reads ----
+            if (seg > 0 && !mbar_wait(bar_a_free, (seg - 1) & 1, abort_flag)) break;
+            {
+                const int chunks_per_row = KC * 8;  // 16-byte chunks
+                const int total = BM * chunks_per_row;
+                for (int q = et; q < total; q += EPI_WARPS * 32) {
+                    const int r = q / chunks_per_row, cc = q - r * chunks_per_row;
+                    const int kc = cc >> 3, c = cc & 7;
+                    const int cr = rt * BM + r;
+                    uint4 val = make_uint4(0u, 0u, 0u, 0u);
+                    if (cr < n_rows) {
+                        const int src = __ldg(row_src + cr);
+                        val = __ldg(reinterpret_cast<const uint4 *>(hidden + (size_t)src * (KC * BK)) + cc);
+                    }
+                    uint8_t *dst = smem + kc * A_CHUNK_BYTES + (r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4);
+                    *reinterpret_cast<uint4 *>(dst) = val;
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> tensor-core reads
+                mbar_arrive(bar_a);
+            }
+            const int cr = rt * BM + sub * 32 + lane;
+            const bool row_ok = cr < n_rows;
+            const int row = row_ok ? __ldg(row_src + cr) : 0;  // padded row index b * L + l
+            const int sent = row / L;
             const int *my_tok = stok ? stok + (size_t)sent * T : nullptr;
             const int *my_slot = stok ? sslot + (size_t)sent * T : nullptr;
             float *my_out = match ? match + (size_t)row * T : nullptr;
@@ -393,7 +450,7 @@ __global__ void __launch_bounds__(PROJ_THREADS, 1)
                 pr.s = (s0 + s1) + (s2 + s3);
                 pr.best = best;
                 pr.best_idx = best_idx;
-                partials[(((size_t)g * plan.max_seg + seg) * 2 + half) * BM + sub * 32 + lane] = pr;
+                partials[(((size_t)g * max_seg + seg) * 2 + half) * BM + sub * 32 + lane] = pr;
             }
             seg++;
         }
@@ -408,25 +465,39 @@ __global__ void __launch_bounds__(PROJ_THREADS, 1)
 }
 
 // ---------------------------------------------------------------------------------------
-// merge of the per-segment partials
+// merge of the per-segment partials; one warp per padded row
 // ---------------------------------------------------------------------------------------
-__global__ void proj_merge_kernel(const Partial *__restrict__ partials, const Plan plan, int N, int L, int T,
+__global__ void proj_merge_kernel(const Partial *__restrict__ partials, const int *__restrict__ prefix,
+                                  const int *__restrict__ n_rows_ptr, int ctas, int max_seg, int N, int V, int L, int T,
                                   const int64_t *__restrict__ ol, const int64_t *__restrict__ tl, float *match,
                                   float *max_lprob, int64_t *argmax, float *lse_out) {
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (warp >= N) return;
-    const int row = warp, rt = row / BM, r_in = row % BM;
+    const int row = warp, b = row / L, l = row % L;
+    const int len_b = prefix[b + 1] - prefix[b];
+    if (l >= len_b) {  // padding row: not projected
+        if (lane == 0) {
+            if (lse_out) lse_out[row] = 0.f;
+            if (max_lprob) max_lprob[row] = 0.f;
+            if (argmax) argmax[row] = 0;
+        }
+        if (match)
+            for (int t = lane; t < T; t += 32) match[(size_t)row * T + t] = 0.f;
+        return;
+    }
+    const Plan plan = Plan::make(*n_rows_ptr, V, ctas, max_seg);
+    const int cr = prefix[b] + l, rt = cr / BM, r_in = cr % BM;
     const long long u0 = (long long)rt * plan.n_tiles, u1 = u0 + plan.n_tiles - 1;
     const int g_lo = plan.cta_of(u0), g_hi = plan.cta_of(u1);
     float m = -CUDART_INF_F, best = -CUDART_INF_F;
     int best_idx = 0;
-    // partial slots in increasing column order: CTA by CTA, inside a CTA half 0 and half 1 interleave per
-    // tile, so the first maximum over slots is resolved by comparing the recorded column index
     for (int g = g_lo; g <= g_hi; g++) {
         const int seg = rt - (int)(plan.begin(g) / plan.n_tiles);
         for (int h = 0; h < 2; h++) {
-            const Partial p = partials[(((size_t)g * plan.max_seg + seg) * 2 + h) * BM + r_in];
+            const Partial p = partials[(((size_t)g * max_seg + seg) * 2 + h) * BM + r_in];
             m = fmaxf(m, p.m);
+            // first maximum in column order: slots are not visited in column order (the two halves of a
+            // tile interleave), so equal values are resolved by the recorded column
             if (p.best > best || (p.best == best && p.best_idx < best_idx)) {
                 best = p.best;
                 best_idx = p.best_idx;
@@ -437,7 +508,7 @@ __global__ void proj_merge_kernel(const Partial *__restrict__ partials, const Pl
     for (int g = g_lo; g <= g_hi; g++) {
         const int seg = rt - (int)(plan.begin(g) / plan.n_tiles);
         for (int h = 0; h < 2; h++) {
-            const Partial p = partials[(((size_t)g * plan.max_seg + seg) * 2 + h) * BM + r_in];
+            const Partial p = partials[(((size_t)g * max_seg + seg) * 2 + h) * BM + r_in];
             if (p.s > 0.f) s += p.s * exp2f((p.m - m) * kLog2e);
         }
     }
@@ -448,7 +519,6 @@ __global__ void proj_merge_kernel(const Partial *__restrict__ partials, const Pl
         if (argmax) argmax[row] = best_idx;
     }
     if (match) {
-        const int b = row / L, l = row % L;
         int eos_col = -1;
         bool keep_eos = true;
         if (ol && tl) {  // criterion's EOS masking (criterions/nat_pcfg_loss.py:112-115)
@@ -504,31 +574,57 @@ bool make_map(CUtensorMap *map, const void *base, uint64_t rows, uint64_t K, uin
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-Plan make_plan(int N, int V) {
+// Launch geometry from the PADDED row count (an upper bound of the compact one, which only the
+// device knows): number of CTAs and the most segments a CTA's range can touch.
+struct Geometry {
+    int ctas, max_seg;
+};
+
+Geometry make_geometry(int N, int V) {
     int dev = 0, sms = 148;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (sms < 1) sms = 148;
-    Plan p;
-    p.row_tiles = (N + BM - 1) / BM;
-    p.n_tiles = (V + BN - 1) / BN;
-    p.units = (long long)p.row_tiles * p.n_tiles;
-    p.ctas = (int)(p.units < sms ? p.units : sms);
-    p.q = p.units / p.ctas;
-    p.rem = p.units % p.ctas;
-    const long long per_cta = p.q + (p.rem ? 1 : 0);
-    p.max_seg = (int)((per_cta + p.n_tiles - 1) / p.n_tiles) + 1;
-    return p;
+    const int n_tiles = (V + BN - 1) / BN;
+    const long long units = (long long)((N + BM - 1) / BM) * n_tiles;
+    Geometry g;
+    g.ctas = (int)(units < sms ? units : sms);
+    const long long per_cta = (units + g.ctas - 1) / g.ctas;
+    g.max_seg = (int)((per_cta + n_tiles - 1) / n_tiles) + 1;
+    return g;
+}
+
+struct Workspace {
+    int *stok, *sslot, *prefix, *row_src, *n_rows;
+    Partial *partials;
+    size_t bytes;
+};
+
+Workspace carve(void *base, int B, int L, int T, int V) {
+    const int N = B * L;
+    const Geometry g = make_geometry(N > 0 ? N : 1, V > 0 ? V : 1);
+    auto up = [](size_t x) { return (x + 255) / 256 * 256; };
+    char *p = static_cast<char *>(base);
+    size_t off = 0;
+    Workspace w;
+    w.stok = reinterpret_cast<int *>(p + off);
+    off += up((size_t)B * (T > 0 ? T : 0) * sizeof(int));
+    w.sslot = reinterpret_cast<int *>(p + off);
+    off += up((size_t)B * (T > 0 ? T : 0) * sizeof(int));
+    w.prefix = reinterpret_cast<int *>(p + off);
+    off += up((size_t)(B + 1) * sizeof(int));
+    w.row_src = reinterpret_cast<int *>(p + off);
+    off += up((size_t)N * sizeof(int));
+    w.n_rows = reinterpret_cast<int *>(p + off);
+    off += 256;
+    w.partials = reinterpret_cast<Partial *>(p + off);
+    off += up((size_t)g.ctas * g.max_seg * 2 * BM * sizeof(Partial));
+    w.bytes = off;
+    return w;
 }
 
 }  // namespace
 
-size_t proj_workspace_bytes(int B, int L, int T, int V) {
-    const int N = B * L;
-    Plan p = make_plan(N > 0 ? N : 1, V > 0 ? V : 1);
-    size_t lists = ((size_t)2 * B * (T > 0 ? T : 0) * sizeof(int) + 255) / 256 * 256;
-    size_t parts = ((size_t)p.ctas * p.max_seg * 2 * BM * sizeof(Partial) + 255) / 256 * 256;
-    return lists + parts + 256;
-}
+size_t proj_workspace_bytes(int B, int L, int T, int V) { return carve(nullptr, B, L, T, V).bytes; }
 
 int launch_proj(const void *hidden, const void *weight, const int64_t *targets, const int64_t *ol, const int64_t *tl,
                 int B, int L, int T, int V, int H, float *match, float *max_lprob, int64_t *argmax, float *lse,
@@ -540,38 +636,35 @@ int launch_proj(const void *hidden, const void *weight, const int64_t *targets, 
     if (ws_bytes < proj_workspace_bytes(B, L, T, V) || reinterpret_cast<uintptr_t>(workspace) % 16)
         return PCFGNAT_ERR_WORKSPACE;
     const bool gather = match != nullptr && targets != nullptr && T > 0;
-    Plan p = make_plan(N, V);
-    char *ws = static_cast<char *>(workspace);
-    int *stok = reinterpret_cast<int *>(ws);
-    int *sslot = stok + (size_t)B * T;
-    size_t lists = ((size_t)2 * B * (T > 0 ? T : 0) * sizeof(int) + 255) / 256 * 256;
-    Partial *partials = reinterpret_cast<Partial *>(ws + lists);
+    const Geometry geo = make_geometry(N, V);
+    const Workspace w = carve(workspace, B, L, T, V);
 
-    CUtensorMap map_a, map_w;
-    if (!make_map(&map_a, hidden, (uint64_t)N, (uint64_t)H, BM) || !make_map(&map_w, weight, (uint64_t)V, (uint64_t)H, BN))
-        return PCFGNAT_ERR_CUDA;
-    if (gather) sort_targets_kernel<<<B, 128, 0, st>>>(targets, T, V, stok, sslot, status);
+    CUtensorMap map_w;
+    if (!make_map(&map_w, weight, (uint64_t)V, (uint64_t)H, BN)) return PCFGNAT_ERR_CUDA;
+    compact_rows_kernel<<<1, 1024, 0, st>>>(ol, B, L, w.prefix, w.row_src, w.n_rows, status);
+    if (gather) sort_targets_kernel<<<B, 128, 0, st>>>(targets, T, V, w.stok, w.sslot, status);
     const size_t smem = (size_t)KC_MAX * A_CHUNK_BYTES + (size_t)NSTAGE * B_STAGE_BYTES + 1024;
     const bool want_arg = max_lprob != nullptr || argmax != nullptr;
-    cudaError_t e;
+    const __half *hid = static_cast<const __half *>(hidden);
     if (want_arg) {
         auto k = proj_kernel<true>;
-        e = ensure_dynamic_smem(k, smem);
-        if (e != cudaSuccess) return PCFGNAT_ERR_CUDA;
-        k<<<p.ctas, PROJ_THREADS, smem, st>>>(map_a, map_w, p, N, V, H / BK, L, T, gather ? stok : nullptr,
-                                              gather ? sslot : nullptr, gather ? match : nullptr, partials, status);
+        if (ensure_dynamic_smem(k, smem) != cudaSuccess) return PCFGNAT_ERR_CUDA;
+        k<<<geo.ctas, PROJ_THREADS, smem, st>>>(map_w, hid, w.row_src, w.n_rows, geo.max_seg, V, H / BK, L, T,
+                                                gather ? w.stok : nullptr, gather ? w.sslot : nullptr,
+                                                gather ? match : nullptr, w.partials, status);
     } else {
         auto k = proj_kernel<false>;
-        e = ensure_dynamic_smem(k, smem);
-        if (e != cudaSuccess) return PCFGNAT_ERR_CUDA;
-        k<<<p.ctas, PROJ_THREADS, smem, st>>>(map_a, map_w, p, N, V, H / BK, L, T, gather ? stok : nullptr,
-                                              gather ? sslot : nullptr, gather ? match : nullptr, partials, status);
+        if (ensure_dynamic_smem(k, smem) != cudaSuccess) return PCFGNAT_ERR_CUDA;
+        k<<<geo.ctas, PROJ_THREADS, smem, st>>>(map_w, hid, w.row_src, w.n_rows, geo.max_seg, V, H / BK, L, T,
+                                                gather ? w.stok : nullptr, gather ? w.sslot : nullptr,
+                                                gather ? match : nullptr, w.partials, status);
     }
     if (cudaGetLastError() != cudaSuccess) return PCFGNAT_ERR_CUDA;
     const int warps_per_block = 8;
     proj_merge_kernel<<<(N + warps_per_block - 1) / warps_per_block, warps_per_block * 32, 0, st>>>(
-        partials, p, N, L, T, ol, tl, gather ? match : nullptr, max_lprob, argmax, lse);
-    if (gather) proj_poison_bad_targets_kernel<<<B, 128, 0, st>>>(stok, sslot, B, L, T, match);
+        w.partials, w.prefix, w.n_rows, geo.ctas, geo.max_seg, N, V, L, T, ol, tl, gather ? match : nullptr, max_lprob,
+        argmax, lse);
+    if (gather) proj_poison_bad_targets_kernel<<<B, 128, 0, st>>>(w.stok, w.sslot, B, L, T, match);
     return cuda_rc(cudaGetLastError());
 }
 

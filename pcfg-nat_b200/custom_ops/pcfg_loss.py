@@ -289,8 +289,8 @@ class _Kernel:
                 raise RuntimeError("targets must be [batch, tarlen]")
             targets = targets.to(device=dev, dtype=torch.int64).contiguous()
             T = targets.shape[1]
-        if (output_length is None) != (target_length is None):
-            raise RuntimeError("give both output_length and target_length (EOS masking) or neither")
+        if target_length is not None and output_length is None:
+            raise RuntimeError("target_length (EOS masking) needs output_length as well")
         ol = _lengths(output_length, "output_length", B, dev) if output_length is not None else None
         tl = _lengths(target_length, "target_length", B, dev) if target_length is not None else None
         l = _cabi.lib()

@@ -436,11 +436,15 @@ def test_fused_projection_against_torch(ops, syn, B, L, T, V, H, std):
     tl = torch.full((B,), T, device=DEV)
     ol[0] = L - 2
     tl[0] = max(T - 3, 2)
-    out2 = ops.proj_logsoftmax_gather(hidden, weight, targets, ol, tl)
+    out2 = ops.proj_logsoftmax_gather(hidden, weight, targets, ol, tl, want_max=True)
     want = syn.eos_mask_(match.clone(), ol.cpu(), tl.cpu())
+    real = (torch.arange(L, device=DEV)[None, :] < ol[:, None])  # with lengths only real nodes are projected
+    want[~real] = 0.0
     fin = torch.isfinite(want)
     assert torch.equal(fin, torch.isfinite(out2["match"]))
     torch.testing.assert_close(out2["match"][fin], want[fin], rtol=0, atol=2e-3)
+    assert float(out2["match"][~real].abs().sum()) == 0.0 and float(out2["max_lprob"][~real].abs().sum()) == 0.0
+    torch.testing.assert_close(out2["max_lprob"][real], mx[real], rtol=0, atol=2e-3)
     out3 = ops.proj_logsoftmax_gather(hidden, weight, want_max=True)
     assert torch.equal(out3["argmax"], out["argmax"]) and torch.equal(out3["max_lprob"], out["max_lprob"])
 
@@ -477,7 +481,7 @@ def test_loss_step_graph_replay_matches_eager(pkg, ops, syn):
         lk[:, :b.L, :, :b.L] = b.links
         tg = torch.ones(b.B, T, dtype=torch.long)
         tg[:, :b.T] = b.targets
-        return hid, lk, tg, b.output_length, b.target_length
+        return hid, lk, b.output_length, tg, b.target_length  # LossStep.load order
 
     weight = b1.weight.to(DEV)
     eager = runtime.LossStep(weight, w.batch, L, T, DEV, use_graph=False)
@@ -493,7 +497,7 @@ def test_loss_step_graph_replay_matches_eager(pkg, ops, syn):
         assert torch.equal(lg_, le) and torch.equal(sg, se)
         assert torch.equal(mgg, mge) and torch.equal(lgg, lge)
         # and against the torch reference of the projection feeding the oracle
-        hid, lk, tg, ol, tl = args
+        hid, lk, ol, tg, tl = args
         lp = torch.log_softmax(hid.float() @ b1.weight.float().t(), -1)  # the step object holds b1's projection matrix
         match = lp.gather(2, tg[:, None, :].expand(-1, L, -1)).contiguous()
         syn.eos_mask_(match, ol, tl)
@@ -501,3 +505,53 @@ def test_loss_step_graph_replay_matches_eager(pkg, ops, syn):
         np.testing.assert_allclose(le.cpu().numpy(), So[:, 0, 0], rtol=1e-4)
         want = -(torch.from_numpy(So[:, 0, 0]) / tl).sum()
         assert abs(float(-se[0]) - float(want)) < 1e-3 * abs(float(want)) and int(se[1]) == w.batch
+
+
+def test_decode_and_glance_steps_match_operator_chain(pkg, ops, syn):
+    """The graph-replayed decode / glancing steps give what the individual operators give."""
+    import importlib
+
+    runtime = importlib.import_module("pcfg_nat_b200.runtime")
+    w = syn.Workload("dec", batch=5, vocab=2000, hidden=64, src_min=6, src_max=24, kind="viterbi")
+    b = syn.make_batch(w, seed=4)
+    weight = b.weight.to(DEV)
+    dec = runtime.DecodeStep(weight, b.B, b.L, b.left_tree_mask, DEV, beta=1.0, pad_index=1)
+    dec.load(b.hidden.pin_memory(), b.links.pin_memory(), b.output_length.pin_memory())
+    for _ in range(2):  # capture, then replay
+        tokens, count, pred = [t.clone() for t in dec.run()]
+    torch.cuda.synchronize()
+    # reference chain on the CPU: fp32 projection -> log-softmax max -> oracle Viterbi -> oracle back-trace
+    lp = torch.log_softmax(b.hidden.float() @ b.weight.float().t(), -1)
+    ob, tok = lp.max(-1)
+    out = ops.proj_logsoftmax_gather(b.hidden.to(DEV), weight, None, b.output_length.to(DEV), None, want_max=True)
+    real = torch.arange(b.L)[None, :] < b.output_length[:, None]
+    torch.testing.assert_close(out["max_lprob"].cpu()[real], ob[real], rtol=0, atol=2e-3)
+    # Viterbi on the kernel's own emissions (bit-exact path), compared with the oracle on the same numbers
+    ob_k, tok_k = out["max_lprob"].cpu(), out["argmax"].cpu()
+    So, Ro, Lo, Mo = oracle.pcfg_viterbi(ob_k.numpy(), b.links.numpy(), b.output_length.numpy())
+    sc = torch.from_numpy(So[:, 1, :]) / torch.arange(b.L // 4).unsqueeze(0)
+    sc = torch.where(torch.isnan(sc), torch.full_like(sc, float("-inf")), sc)
+    want_pred = sc[:, 1:].max(-1)[1] + 1
+    assert torch.equal(pred.cpu(), want_pred)
+    want = oracle.viterbi_decoding_lists(want_pred.numpy(), b.output_length.numpy(), Lo, Ro, Mo, tok_k.numpy(),
+                                         b.left_tree_mask.long().numpy(), 1)
+    for i, row in enumerate(want):
+        assert tokens[i, :int(count[i])].cpu().tolist() == row
+        assert (tokens[i, int(count[i]):] == 1).all()
+
+    wg = syn.Workload("gl", batch=4, vocab=2000, hidden=64, src_min=6, src_max=20, kind="glance")
+    g = syn.make_batch(wg, seed=5)
+    gs = runtime.GlanceStep(g.weight.to(DEV), g.B, g.L, g.T, DEV)
+    gs.load(g.hidden.pin_memory(), g.links.pin_memory(), g.output_length.pin_memory(), g.targets.pin_memory(),
+            g.target_length.pin_memory())
+    for _ in range(2):
+        tree, ll, am = [t.clone() for t in gs.run()]
+    em = ops.proj_logsoftmax_gather(g.hidden.to(DEV), g.weight.to(DEV), g.targets.to(DEV), g.output_length.to(DEV),
+                                    g.target_length.to(DEV), want_max=True)
+    tree2, ll2 = ops.cuda_pcfg_best_tree(em["match"], g.links.to(DEV), g.output_length.to(DEV), g.target_length.to(DEV))
+    assert torch.equal(tree, tree2) and torch.equal(ll, ll2) and torch.equal(am, em["argmax"])
+    So, Co = oracle.pcfg_loss(em["match"].cpu().numpy(), g.links.numpy(), g.output_length.numpy(), g.target_length.numpy())
+    want_tree = oracle.pcfg_best_tree(So, Co, em["match"].cpu().numpy(), g.links.numpy(), g.output_length.numpy(),
+                                      g.target_length.numpy())
+    # same emissions; the tables differ from the oracle's only in the last ulp of expf/logf
+    assert (tree.cpu().numpy() == want_tree).mean() > 0.99
