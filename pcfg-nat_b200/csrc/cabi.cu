@@ -38,14 +38,12 @@ cudaError_t ensure_dynamic_smem_for(const void *kernel, size_t bytes) {
     return e;
 }
 
-bool force_row_kernels() {
-    const char *v = getenv("PCFGNAT_DP_ROWS");
-    return v && v[0] == '1';
-}
-
-bool force_balanced_inside() {
-    const char *v = getenv("PCFGNAT_DP_BALANCED_INSIDE");
-    return v && v[0] == '1' && !force_row_kernels();
+DpKernel dp_kernel_choice() {
+    const char *v = getenv("PCFGNAT_DP_KERNEL");
+    if (v && v[0] == 'r') return kDpRows;
+    if (v && v[0] == 'b') return kDpBalanced;
+    if (v && v[0] == 'c') return kDpCluster;
+    return kDpAuto;
 }
 
 }  // namespace pcfgnat

@@ -59,10 +59,21 @@ int launch_loss_fwd_balanced(const float *match_all, const float *links, const i
 int launch_outside_balanced(const float *grad_output, const float *S, const float *match_all, const float *links,
                             const int64_t *ol, const int64_t *tl, int B, int L, int T, float *G, int *status,
                             cudaStream_t st);
-// PCFGNAT_DP_ROWS=1 in the environment keeps the row-per-thread DP kernels for every shape (A/B runs, tests).
-bool force_row_kernels();
-// PCFGNAT_DP_BALANCED_INSIDE=1 selects the phase-balanced inside kernel where it fits (default: row-per-thread).
-bool force_balanced_inside();
+int launch_loss_fwd_cluster(const float *match_all, const float *links, const int64_t *ol, const int64_t *tl, int B,
+                            int L, int T, float *S, float *C, float *loss, int *status, cudaStream_t st);
+int launch_outside_cluster(const float *grad_output, const float *S, const float *match_all, const float *links,
+                           const int64_t *ol, const int64_t *tl, int B, int L, int T, float *G, int *status,
+                           cudaStream_t st);
+
+// Which family of DP kernels runs the inside / outside passes.  PCFGNAT_DP_KERNEL in the environment
+// selects one for A/B runs and tests: "cluster" (default: warp per node, cluster per sentence),
+// "balanced" (phase-balanced single CTA), "rows" (4 lanes per node, the only one without a size limit).
+// A family that cannot take a shape falls through to the next one in that order.
+// Unset (kDpAuto): clusters when cluster_kernels_pay(), else the measured-fastest single-CTA pair
+// (row-per-thread inside pass, phase-balanced outside pass).
+enum DpKernel { kDpCluster = 0, kDpBalanced = 1, kDpRows = 2, kDpAuto = 3 };
+DpKernel dp_kernel_choice();
+bool cluster_kernels_pay(int B, int L, int T);
 
 size_t proj_workspace_bytes(int B, int L, int T, int V);
 int launch_proj(const void *hidden, const void *weight, const int64_t *targets, const int64_t *ol, const int64_t *tl,

@@ -284,7 +284,10 @@ int launch_loss_bwd(const float *grad_output, const float *S, const float *match
     dim3 block(kLanes, rows), grid(B);
     cudaError_t e;
     int brc = PCFGNAT_ERR_UNSUPPORTED;
-    if (!force_row_kernels())  // sentences that fit shared memory: evenly spread phases (loss_balanced.cu)
+    const DpKernel choice = dp_kernel_choice();
+    if (choice == kDpCluster || (choice == kDpAuto && cluster_kernels_pay(B, L, T)))  // loss_cluster.cu
+        brc = launch_outside_cluster(grad_output, S, match_all, links, ol, tl, B, L, T, S_grad, status, st);
+    if (brc == PCFGNAT_ERR_UNSUPPORTED && choice != kDpRows)  // evenly spread phases in one CTA (loss_balanced.cu)
         brc = launch_outside_balanced(grad_output, S, match_all, links, ol, tl, B, L, T, S_grad, status, st);
     if (brc != PCFGNAT_ERR_UNSUPPORTED) {
         if (brc != PCFGNAT_OK) return brc;

@@ -1,0 +1,387 @@
+// Inside and outside passes of the PCFG loss, one WARP per tree node and one thread-block CLUSTER
+// per sentence (max_left == 1).  Same tables as loss_fwd.cu / loss_bwd.cu.
+//
+// Why: with 4 lanes per node (the reference's layout) the first node of a sentence walks M/4 right
+// children one after the other and sets the time of every dependent step; a single SM also caps the
+// step at ~16 us for a 256-node chain.  Here
+//   * a warp owns a node: lane l takes the children c = a + l + 32 i, so a step costs ceil(M/32)
+//     trips on its critical path instead of M/4;
+//   * the nodes of a sentence are dealt round-robin to the 1..16 CTAs of a cluster (one cluster per
+//     sentence, sized so that the batch fills the GPU).  Every CTA keeps the rolling S (or G)
+//     columns of the WHOLE chain in its shared memory; a warp that finishes a node stores the value
+//     into every CTA's copy through distributed shared memory and the cluster meets at a hardware
+//     barrier once per step.  Only the links rows of a CTA's own nodes are staged in its shared memory.
+//
+// Bit-exactness of the inside table (pcfg_loss.cu:149-213): the reference's lane x adds the
+// exponentials of children k = 0, 1, 2, ... (c = a + x + 4k), t0 before t1.  Lane l = x + 4h here
+// holds k = h + 8i, so after each trip i the eight lanes h = 0..7 of a virtual lane x are visited in
+// order with shuffles and every lane keeps the running sum of its virtual lane: the same additions
+// in the same order.  Lanes 0..3 are then combined (s0 + s2) + (s1 + s3).  max is order-free.
+#include <cooperative_groups.h>
+
+#include <cstdlib>
+
+#include "common.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace pcfgnat {
+
+namespace {
+
+constexpr int kCThreads = 1024;
+constexpr int kCWarps = kCThreads / 32;
+
+__device__ __forceinline__ float clean(float t) { return isnan(t) ? neg_inf() : t; }
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// ---------------------------------------------------------------------------------------
+// inside pass
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kCThreads, 1)
+    inside_cluster_kernel(const float *__restrict__ match_all, const float *__restrict__ links,
+                          const int64_t *__restrict__ ol, const int64_t *__restrict__ tl, int L, int T, float *S,
+                          float *C, float *loss, int *status, int Mc, int Lt, int cs, int rows_cap, int lk_stride) {
+    extern __shared__ float smem[];
+    cg::cluster_group cluster = cg::this_cluster();
+    const int NC = (int)cluster.num_blocks(), crank = (int)cluster.block_rank();
+    const int b = blockIdx.x / NC;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int ctid = crank * kCThreads + tid, cthreads = NC * kCThreads;  // thread index inside the cluster
+    const int W = T + 2;
+    const int m = (int)ol[b], n = (int)tl[b];
+    const bool ok = lengths_ok(m, n, L, T);
+    const float *mat = match_all + (size_t)b * L * T;
+    const float *lkb = links + (size_t)b * L * 2 * L;
+    float *Sb = S + (size_t)b * Mc * W;
+
+    for (int i = ctid; i < Mc * W; i += cthreads) Sb[i] = neg_inf();
+    if (C) {  // C[0][t][0] = 0 for t <= n; C[leaf slot][t][1] = match[leaf][t] for t < n (pcfg_loss.cu:288-297)
+        float *Cb = C + (size_t)b * Lt * W * 3;
+        for (int i = ctid; i < Lt * W * 3; i += cthreads) {
+            int g = i % 3, t = (i / 3) % W, a_id = i / (3 * W);
+            float v = neg_inf();
+            if (ok) {
+                if (a_id == 0) {
+                    if (g == 0 && t <= n) v = 0.f;
+                } else if (g == 1 && 2 * a_id < m && t < n) {
+                    v = __ldg(mat + (size_t)(2 * a_id) * T + t);
+                }
+            }
+            Cb[i] = v;
+        }
+    }
+    if (!ok) {  // uniform over the cluster: nobody reaches a cluster barrier
+        if (ctid == 0) {
+            flag(status, PCFGNAT_STATUS_BAD_LENGTH);
+            if (loss) loss[b] = neg_inf();
+        }
+        return;
+    }
+    const int Mb = main_nodes_below(m);
+    const int last = (m - 2) / 2;
+    const int my_rows = Mb > crank ? (Mb - crank + NC - 1) / NC : 0;  // nodes ai = crank + NC * r
+    float *col = smem;                 // [3][cs] rolling S columns of the whole chain (replicated per CTA)
+    float *lk0 = col + 3 * cs;         // [rows_cap][lk_stride] links[a][0][c] of this CTA's nodes, by child slot
+    float *lk1 = lk0 + (size_t)rows_cap * lk_stride;
+    // S entries of this CTA's nodes, flushed to global memory after the last step: a global store
+    // inside the step loop would make every cluster barrier (a release) wait for it to reach L2
+    float *own = lk1 + (size_t)rows_cap * lk_stride;  // [rows_cap][W]
+
+    for (int r = warp; r < my_rows; r += kCWarps) {
+        const int ai = crank + NC * r;
+        const float *row = lkb + (size_t)(2 * ai + 1) * 2 * L;
+        for (int ci = ai + lane; ci < Mb; ci += 32) {
+            lk0[r * lk_stride + ci] = __ldg(row + 2 * ci + 1);
+            lk1[r * lk_stride + ci] = __ldg(row + L + 2 * ci + 1);
+        }
+    }
+    for (int i = tid; i < 3 * cs; i += kCThreads) col[i] = neg_inf();
+    __syncthreads();
+    if (tid == 0) {
+        const float v = __ldg(mat + (size_t)(m - 1) * T + (n - 1));
+        col[((n - 1) % 3) * cs + last] = v;  // every CTA fills its own copy
+    }
+    // all copies initialised before anybody stores into a neighbour's; also orders the -inf fill of the
+    // global table (done by threads of any CTA of the cluster) before the cells written below
+    if (NC > 1) cluster.sync(); else __syncthreads();
+    if (ctid == 0) Sb[(size_t)last * W + (n - 1)] = __ldg(mat + (size_t)(m - 1) * T + (n - 1));
+
+    for (int start = n - 2; start >= 0; start--) {
+        const float *S1 = col + ((start + 1) % 3) * cs;
+        const float *S2 = col + ((start + 2) % 3) * cs;
+        float *S0 = col + (start % 3) * cs;
+        for (int r = warp; r < my_rows; r += kCWarps) {
+            const int ai = crank + NC * r, a = 2 * ai + 1;
+            const bool has_leaf = a >= 3;
+            const float ma0 = __ldg(mat + (size_t)a * T + start);
+            const float ma1 = has_leaf ? __ldg(mat + (size_t)a * T + start + 1) : 0.f;
+            const float ml = has_leaf ? __ldg(mat + (size_t)(a - 1) * T + start) : 0.f;
+            const float *r0 = lk0 + r * lk_stride, *r1 = lk1 + r * lk_stride;
+            const int trips = (Mb - ai + 31) / 32;
+            float mx = neg_inf();
+            for (int i = 0; i < trips; i++) {
+                const int ci = ai + lane + 32 * i;
+                if (ci < Mb) {
+                    const float t0 = clean((r0[ci] + S1[ci]) + ma0);
+                    if (t0 > mx) mx = t0;
+                    if (has_leaf) {
+                        const float t1 = clean(((r1[ci] + S2[ci]) + ml) + ma1);
+                        if (t1 > mx) mx = t1;
+                    }
+                }
+            }
+            mx = warp_max(mx);
+            float sum = 0.f;
+            if (!isinf(mx)) {
+                for (int i = 0; i < trips; i++) {
+                    const int ci = ai + lane + 32 * i;
+                    float e0 = 0.f, e1 = 0.f;  // exp(-inf) of the reference's absent / -inf terms
+                    if (ci < Mb) {
+                        e0 = expf(clean(((r0[ci] + S1[ci]) + ma0) - mx));
+                        if (has_leaf) e1 = expf(clean((((r1[ci] + S2[ci]) + ml) + ma1) - mx));
+                    }
+                    // children k = 8i .. 8i+7 of every virtual lane, in order
+#pragma unroll
+                    for (int h = 0; h < 8; h++) {
+                        const float v0 = __shfl_sync(0xffffffffu, e0, (lane & 3) + 4 * h);
+                        const float v1 = __shfl_sync(0xffffffffu, e1, (lane & 3) + 4 * h);
+                        sum += v0;
+                        sum += v1;
+                    }
+                }
+            }
+            sum += __shfl_down_sync(0xffffffffu, sum, 2, 4);  // lanes 0..3 hold the four virtual-lane sums
+            sum += __shfl_down_sync(0xffffffffu, sum, 1, 4);
+            sum = __shfl_sync(0xffffffffu, sum, 0);
+            const float res = isinf(mx) ? mx : logf(sum) + mx;
+            if (lane < NC) *cluster.map_shared_rank(S0 + ai, lane) = res;  // into every CTA's column
+            if (lane == 0) own[r * W + start] = res;
+        }
+        if (NC > 1) cluster.sync(); else __syncthreads();
+    }
+    for (int i = tid; i < my_rows * (n - 1); i += kCThreads) {  // computed cells: columns 0 .. n-2
+        const int r = i / (n - 1), t = i - r * (n - 1);
+        Sb[(size_t)(crank + NC * r) * W + t] = own[r * W + t];
+    }
+    if (loss && ctid == 0) loss[b] = (n >= 2) ? col[0] : Sb[0];
+}
+
+// ---------------------------------------------------------------------------------------
+// outside pass
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kCThreads, 1)
+    outside_cluster_kernel(const float *__restrict__ grad_output, const float *__restrict__ S,
+                           const float *__restrict__ match_all, const float *__restrict__ links,
+                           const int64_t *__restrict__ ol, const int64_t *__restrict__ tl, int L, int T, float *G,
+                           int *status, int Mc, int cs, int rows_cap, int lk_stride) {
+    extern __shared__ float smem[];
+    cg::cluster_group cluster = cg::this_cluster();
+    const int NC = (int)cluster.num_blocks(), crank = (int)cluster.block_rank();
+    const int b = blockIdx.x / NC;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int ctid = crank * kCThreads + tid, cthreads = NC * kCThreads;
+    const int W = T + 2;
+    const int m = (int)ol[b], n = (int)tl[b];
+    const float *mat = match_all + (size_t)b * L * T;
+    const float *lkb = links + (size_t)b * L * 2 * L;
+    const float *Sb = S + (size_t)b * Mc * W;
+    float *Gb = G + (size_t)b * Mc * W;
+    for (int i = ctid; i < Mc * W; i += cthreads) Gb[i] = 0.f;
+    if (!lengths_ok(m, n, L, T)) {
+        if (ctid == 0) flag(status, PCFGNAT_STATUS_BAD_LENGTH);
+        return;
+    }
+    const int Mb = main_nodes_below(m);
+    const int my_rows = Mb > crank ? (Mb - crank + NC - 1) / NC : 0;  // children ci = crank + NC * r
+    float *gcol = smem;            // [3][cs] rolling G columns of the whole chain (replicated per CTA)
+    float *ga = gcol + 3 * cs;     // [cs] G[a][s] where usable, else 0
+    float *q0 = ga + cs;           // [cs] match[a][s] - S[a][s]
+    float *q1 = q0 + cs;           // [cs] match[a-1][s] + match[a][s+1] - S[a][s]
+    float *lt0 = q1 + cs;          // [rows_cap][lk_stride] links[a][0][c] of this CTA's children, by parent slot
+    float *lt1 = lt0 + (size_t)rows_cap * lk_stride;
+    float *own = lt1 + (size_t)rows_cap * lk_stride;  // [rows_cap][W] G entries of this CTA's nodes, flushed at the end
+
+    for (int r = warp; r < my_rows; r += kCWarps) {
+        const int ci = crank + NC * r, c = 2 * ci + 1;
+        for (int ai = lane; ai < ci; ai += 32) {
+            const float *row = lkb + (size_t)(2 * ai + 1) * 2 * L + c;
+            lt0[r * lk_stride + ai] = __ldg(row);
+            lt1[r * lk_stride + ai] = __ldg(row + L);
+        }
+    }
+    for (int i = tid; i < 3 * cs; i += kCThreads) gcol[i] = 0.f;
+    __syncthreads();
+    if (tid == 0) {
+        const float go = grad_output ? grad_output[b] : 1.f;
+        gcol[0] = go;  // S_grad[0][0] = grad_output (pcfg_loss_backward.cu:78); every CTA fills its own copy
+    }
+    if (NC > 1) cluster.sync(); else __syncthreads();  // also orders the zero fill of G before the flush below
+
+    for (int s = 0; s + 1 < n; s++) {
+        const float *g0 = gcol + (s % 3) * cs;
+        float *g1 = gcol + ((s + 1) % 3) * cs;
+        float *g2 = gcol + ((s + 2) % 3) * cs;
+        // per-parent scalars of this step, for the whole chain (every CTA needs all of them)
+        for (int ai = tid; ai < Mb; ai += kCThreads) {
+            const int a = 2 * ai + 1;
+            const float sa = __ldg(Sb + (size_t)ai * W + s);
+            const float g = g0[ai];
+            const bool on = g != 0.f && !isinf(sa);
+            ga[ai] = on ? g : 0.f;
+            q0[ai] = on ? __ldg(mat + (size_t)a * T + s) - sa : 0.f;
+            float v1 = neg_inf();
+            if (on && a >= 3) v1 = (__ldg(mat + (size_t)(a - 1) * T + s) + __ldg(mat + (size_t)a * T + s + 1)) - sa;
+            q1[ai] = v1;
+        }
+        __syncthreads();
+        for (int r = warp; r < my_rows; r += kCWarps) {
+            const int ci = crank + NC * r;
+            const float sc1 = __ldg(Sb + (size_t)ci * W + s + 1);
+            const float sc2 = __ldg(Sb + (size_t)ci * W + s + 2);
+            const float *r0 = lt0 + r * lk_stride, *r1 = lt1 + r * lk_stride;
+            float acc0 = 0.f, acc1 = 0.f;
+            if (!isinf(sc1) || !isinf(sc2)) {
+                for (int ai = lane; ai < ci; ai += 32) {
+                    const float g = ga[ai];
+                    if (g != 0.f) {
+                        acc0 += g * expf((r0[ai] + sc1) + q0[ai]);
+                        acc1 += g * expf((r1[ai] + sc2) + q1[ai]);
+                    }
+                }
+            }
+            acc0 = warp_sum(acc0);
+            acc1 = warp_sum(acc1);
+            const float v = g1[ci] + acc0;  // column s+1 is final now (g1[ci] holds the j = 1 part from step s-1)
+            __syncwarp();                   // every lane has read g1[ci] before the local copy is overwritten
+            if (lane < NC) {
+                *cluster.map_shared_rank(g1 + ci, lane) = v;
+                *cluster.map_shared_rank(g2 + ci, lane) = acc1;  // first contribution to column s+2
+            }
+            if (lane == 0) own[r * W + s + 1] = v;
+        }
+        if (NC > 1) cluster.sync(); else __syncthreads();
+    }
+    for (int i = tid; i < my_rows * (n - 1); i += kCThreads) {  // columns 1 .. n-1 of this CTA's nodes
+        const int r = i / (n - 1), t = 1 + (i - r * (n - 1));
+        Gb[(size_t)(crank + NC * r) * W + t] = own[r * W + t];
+    }
+    if (ctid == 0) Gb[0] = grad_output ? grad_output[b] : 1.f;
+}
+
+struct ClusterGeometry {
+    int nc, cs, rows_cap, lk_stride;
+    size_t smem_in, smem_out;
+};
+
+// Cluster size: the largest power of two <= 16 that still lets all sentences run at once, raised if a
+// CTA's share of the links would not fit shared memory; nc = 0 when no size fits.
+ClusterGeometry cluster_geometry(int B, int Mc, int W) {
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    ClusterGeometry g;
+    g.cs = (Mc + 3) / 4 * 4;
+    g.lk_stride = (Mc + 31) / 32 * 32 + 1;
+    int nc = 1;
+    // measured on 8 sentences x 256 nodes: 8 CTAs per sentence 1.12 ms, 16 CTAs 1.85 ms (the barrier of a
+    // 16-CTA cluster costs more than the extra SMs give), 4 CTAs 1.65 ms: stop at 8
+    while (nc < 8 && (long long)B * nc * 2 <= sms && Mc > 8 * nc) nc *= 2;
+    if (const char *v = getenv("PCFGNAT_DP_CLUSTER_SIZE")) {  // experiments: 1, 2, 4, 8 or 16
+        const int want = atoi(v);
+        if (want == 1 || want == 2 || want == 4 || want == 8 || want == 16) nc = want;
+    }
+    for (;; nc *= 2) {
+        g.nc = nc;
+        g.rows_cap = (Mc + nc - 1) / nc;
+        const size_t lk = (size_t)2 * g.rows_cap * g.lk_stride * sizeof(float);
+        const size_t own = (size_t)g.rows_cap * W * sizeof(float);
+        g.smem_in = (size_t)3 * g.cs * sizeof(float) + lk + own;
+        g.smem_out = (size_t)6 * g.cs * sizeof(float) + lk + own;
+        if (g.smem_out <= (size_t)kSmemLimit - 1024) break;
+        if (nc >= 16) {
+            g.nc = 0;
+            break;
+        }
+    }
+    return g;
+}
+
+template <class Kernel, class... Args>
+int launch_cluster(Kernel kernel, int B, int nc, size_t smem, cudaStream_t st, Args... args) {
+    if (ensure_dynamic_smem(kernel, smem) != cudaSuccess) return PCFGNAT_ERR_CUDA;
+    if (nc > 8 && cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess)
+        return PCFGNAT_ERR_UNSUPPORTED;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(B * nc));
+    cfg.blockDim = dim3(kCThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)nc;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int max_clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&max_clusters, kernel, &cfg) != cudaSuccess || max_clusters < 1) {
+        cudaGetLastError();
+        return PCFGNAT_ERR_UNSUPPORTED;  // this cluster size cannot be scheduled on this GPU
+    }
+    return cuda_rc(cudaLaunchKernelEx(&cfg, kernel, args...));
+}
+
+}  // namespace
+
+// True when the batch is small enough that several CTAs per sentence are available (cluster size >= 2),
+// or the chain is too long for the single-CTA kernels to keep its links in shared memory.
+bool cluster_kernels_pay(int B, int L, int T) {
+    const int Mc = main_slots(L, 1);
+    const ClusterGeometry g = cluster_geometry(B, Mc, T + 2);
+    return g.nc >= 2 || Mc > 160;
+}
+
+// Both return PCFGNAT_ERR_UNSUPPORTED when the shape does not fit any cluster size (the caller then
+// uses the row-per-thread kernels that read links from global memory).
+int launch_loss_fwd_cluster(const float *match_all, const float *links, const int64_t *ol, const int64_t *tl, int B,
+                            int L, int T, float *S, float *C, float *loss, int *status, cudaStream_t st) {
+    const int Mc = main_slots(L, 1), Lt = L - Mc;
+    ClusterGeometry g = cluster_geometry(B, Mc, T + 2);
+    for (; g.nc >= 1; g.nc /= 2) {  // fall back to smaller clusters if the GPU cannot co-schedule this size
+        g.rows_cap = (Mc + g.nc - 1) / g.nc;
+        g.smem_in = ((size_t)3 * g.cs + (size_t)2 * g.rows_cap * g.lk_stride + (size_t)g.rows_cap * (T + 2)) * sizeof(float);
+        if (g.smem_in > (size_t)kSmemLimit - 1024) break;
+        int rc = launch_cluster(inside_cluster_kernel, B, g.nc, g.smem_in, st, match_all, links, ol, tl, L, T, S, C, loss,
+                                status, Mc, Lt, g.cs, g.rows_cap, g.lk_stride);
+        if (rc != PCFGNAT_ERR_UNSUPPORTED) return rc;
+    }
+    return PCFGNAT_ERR_UNSUPPORTED;
+}
+
+int launch_outside_cluster(const float *grad_output, const float *S, const float *match_all, const float *links,
+                           const int64_t *ol, const int64_t *tl, int B, int L, int T, float *G, int *status,
+                           cudaStream_t st) {
+    const int Mc = main_slots(L, 1);
+    ClusterGeometry g = cluster_geometry(B, Mc, T + 2);
+    for (; g.nc >= 1; g.nc /= 2) {
+        g.rows_cap = (Mc + g.nc - 1) / g.nc;
+        g.smem_out = ((size_t)6 * g.cs + (size_t)2 * g.rows_cap * g.lk_stride + (size_t)g.rows_cap * (T + 2)) * sizeof(float);
+        if (g.smem_out > (size_t)kSmemLimit - 1024) break;
+        int rc = launch_cluster(outside_cluster_kernel, B, g.nc, g.smem_out, st, grad_output, S, match_all, links, ol, tl,
+                                L, T, G, status, Mc, g.cs, g.rows_cap, g.lk_stride);
+        if (rc != PCFGNAT_ERR_UNSUPPORTED) return rc;
+    }
+    return PCFGNAT_ERR_UNSUPPORTED;
+}
+
+}  // namespace pcfgnat

@@ -210,10 +210,16 @@ __global__ void __launch_bounds__(kMaxRows *kLanes)
 int launch_loss_fwd(const float *match_all, const float *links, const int64_t *ol, const int64_t *tl, int B, int L,
                     int T, float *S, float *C, float *loss, int *status, cudaStream_t st) {
     if (B == 0) return PCFGNAT_OK;
-    // The phase-balanced inside kernel (loss_balanced.cu) is bit-identical but measured slower than the
-    // row-per-thread kernel below (248 vs 172 us on the training batch: it executes ~2.7x the instructions),
-    // so it is only used on request; the balanced OUTSIDE kernel is the default (74 vs 201 us).
-    if (force_balanced_inside()) {
+    // Kernel families, all producing bit-identical tables: warp-per-node clusters (loss_cluster.cu; chosen
+    // when few sentences leave several SMs per sentence, or the chain is long), phase-balanced single CTA
+    // (loss_balanced.cu, on request only: measured slower here) and the row-per-thread kernel below, which
+    // has no size limit because it can read links from global memory.
+    const DpKernel choice = dp_kernel_choice();
+    if (choice == kDpCluster || (choice == kDpAuto && cluster_kernels_pay(B, L, T))) {
+        const int rc = launch_loss_fwd_cluster(match_all, links, ol, tl, B, L, T, S, C, loss, status, st);
+        if (rc != PCFGNAT_ERR_UNSUPPORTED) return rc;
+    }
+    if (choice == kDpBalanced) {
         const int rc = launch_loss_fwd_balanced(match_all, links, ol, tl, B, L, T, S, C, loss, status, st);
         if (rc != PCFGNAT_ERR_UNSUPPORTED) return rc;
     }

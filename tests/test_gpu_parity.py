@@ -20,17 +20,15 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
 
-@pytest.fixture(params=["default", "rows", "balanced"])
+@pytest.fixture(params=["auto", "cluster", "balanced", "rows"])
 def dp_kernel(request, monkeypatch):
-    """Runs a test once per DP kernel selection: the default (row-per-thread inside pass, phase-balanced
-    outside pass where the sentence fits shared memory), row-per-thread only (PCFGNAT_DP_ROWS=1, what
-    longer graphs get) and phase-balanced for both passes (PCFGNAT_DP_BALANCED_INSIDE=1)."""
-    monkeypatch.delenv("PCFGNAT_DP_ROWS", raising=False)
-    monkeypatch.delenv("PCFGNAT_DP_BALANCED_INSIDE", raising=False)
-    if request.param == "rows":
-        monkeypatch.setenv("PCFGNAT_DP_ROWS", "1")
-    elif request.param == "balanced":
-        monkeypatch.setenv("PCFGNAT_DP_BALANCED_INSIDE", "1")
+    """Runs a test once per selection of inside/outside kernels (PCFGNAT_DP_KERNEL): the library's own
+    choice by shape, warp-per-node clusters, phase-balanced single CTA, and 4 lanes per node (the only
+    one without a size limit)."""
+    if request.param == "auto":
+        monkeypatch.delenv("PCFGNAT_DP_KERNEL", raising=False)
+    else:
+        monkeypatch.setenv("PCFGNAT_DP_KERNEL", request.param)
     return request.param
 
 
