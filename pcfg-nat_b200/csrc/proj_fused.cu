@@ -138,8 +138,9 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float *v) {
-    uint32_t r[32];
+// Issues the load of 32 accumulator columns of this thread's row; the registers are valid only after
+// tmem_ld_wait(r) on the same array.
+__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t *r) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
         "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -149,9 +150,18 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float *v) {
           "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
           "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 32; i++) v[i] = __uint_as_float(r[i]);
+}
+// Waits for the outstanding tcgen05.ld; the registers are listed as in/out operands so that the compiler
+// cannot move any use of them above the wait.
+__device__ __forceinline__ void tmem_ld_wait(uint32_t *r) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                   "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]),
+                   "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]),
+                   "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]),
+                   "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+                 :
+                 : "memory");
 }
 
 __device__ __forceinline__ float ex2(float x) {
@@ -373,6 +383,7 @@ __global__ void __launch_bounds__(PROJ_THREADS, 1)
                 }
                 p = lo;
             }
+            int next_tok = (my_tok && p < T) ? __ldg(my_tok + p) : INT_MAX;  // next target of this row's sentence
             float m = -CUDART_INF_F, s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
             float best = -CUDART_INF_F;
             int best_idx = 0;
@@ -384,12 +395,12 @@ __global__ void __launch_bounds__(PROJ_THREADS, 1)
                 }
                 tc_fence_after();
                 const int tile_col0 = (int)(u - (long long)rt * NT) * BN + half * HALF_COLS;
-#pragma unroll 1
-                for (int c = 0; c < HALF_COLS / 32; c++) {
+                const uint32_t tsrc = tmem_base + ((uint32_t)(sub * 32) << 16) + buf * BN + half * HALF_COLS;
+                // One 32-column chunk of this thread's row: online max / sum-exp, arg-max, target logits.
+                auto process = [&](const uint32_t *r, const int col0) {
                     float v[32];
-                    __syncwarp();  // the gather loop below may leave the lanes diverged; tcgen05.ld is warp-collective
-                    tmem_ld32(tmem_base + ((uint32_t)(sub * 32) << 16) + buf * BN + half * HALF_COLS + c * 32, v);
-                    const int col0 = tile_col0 + c * 32;
+#pragma unroll
+                    for (int i = 0; i < 32; i++) v[i] = __uint_as_float(r[i]);
                     if (col0 + 32 > V) {
 #pragma unroll
                         for (int i = 0; i < 32; i++)
@@ -425,21 +436,36 @@ __global__ void __launch_bounds__(PROJ_THREADS, 1)
                             s3 += ex2(fmaf(v[i + 3], kLog2e, nm));
                         }
                     }
-                    if (my_tok) {
-                        while (p < T) {  // targets are sorted; those below col0 belong to the other half
-                            const int tk = __ldg(my_tok + p);
-                            if (tk >= col0 + 32) break;
-                            const int idx = tk - col0;
-                            if (idx >= 0 && row_ok) {
-                                float val = v[0];
+                    while (next_tok < col0 + 32) {  // targets are sorted; those below col0 belong to the other half
+                        const int idx = next_tok - col0;
+                        if (idx >= 0 && row_ok) {
+                            float val = v[0];
 #pragma unroll
-                                for (int i = 1; i < 32; i++) val = (idx == i) ? v[i] : val;
-                                my_out[__ldg(my_slot + p)] = val;  // raw logit; the merge kernel subtracts lse
-                            }
-                            p++;
+                            for (int i = 1; i < 32; i++) val = (idx == i) ? v[i] : val;
+                            my_out[__ldg(my_slot + p)] = val;  // raw logit; the merge kernel subtracts lse
                         }
+                        p++;
+                        next_tok = p < T ? __ldg(my_tok + p) : INT_MAX;
                     }
-                }
+                };
+                // the load of chunk c+1 is in flight while chunk c is processed
+                uint32_t ra[32], rb[32];
+                __syncwarp();  // the target loop may leave the lanes diverged; tcgen05.ld is warp-collective
+                tmem_ld32_issue(tsrc, ra);
+                tmem_ld_wait(ra);
+                __syncwarp();
+                tmem_ld32_issue(tsrc + 32, rb);
+                process(ra, tile_col0);
+                tmem_ld_wait(rb);
+                __syncwarp();
+                tmem_ld32_issue(tsrc + 64, ra);
+                process(rb, tile_col0 + 32);
+                tmem_ld_wait(ra);
+                __syncwarp();
+                tmem_ld32_issue(tsrc + 96, rb);
+                process(ra, tile_col0 + 64);
+                tmem_ld_wait(rb);
+                process(rb, tile_col0 + 96);
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
