@@ -110,6 +110,13 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     return false;
 }
 
+// True in exactly one lane of a fully converged warp (the same lane on every call).
+__device__ __forceinline__ bool elect_one() {
+    uint32_t chosen;
+    asm volatile("{ .reg .pred p; elect.sync _|p, 0xffffffff; selp.b32 %0, 1, 0, p; }" : "=r"(chosen));
+    return chosen != 0;
+}
+
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int x, int y) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
@@ -278,61 +285,60 @@ __global__ void __launch_bounds__(PROJ_THREADS, 1)
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
 
+    // The two issuing warps run their loops with all 32 lanes (every lane waits on the barriers, the
+    // verdict is made warp-uniform) and elect one lane for the asynchronous instructions, so that loop
+    // state, descriptors and addresses stay warp-uniform values.
     if (warp == 0) {
         // ------------------------------ TMA producer: streams W, segment after segment ------------
-        if (lane == 0) {
-            uint32_t it = 0;
-            bool ok = true;
-            for (long long u = u_begin; u < u_end && ok; u++) {
-                const int t = (int)(u % NT);
-                for (int kc = 0; kc < KC; kc++, it++) {
-                    const uint32_t st = it % NSTAGE, ph = (it / NSTAGE) & 1;
-                    if (!mbar_wait(bar_empty + 8 * st, ph ^ 1, abort_flag)) {
-                        ok = false;
-                        break;
-                    }
+        uint32_t st = 0, ph = 0;
+        bool ok = true;
+        int t = (int)(u_begin % NT);
+        for (long long u = u_begin; u < u_end && ok; u++) {
+            for (int kc = 0; kc < KC; kc++) {
+                ok = __all_sync(0xffffffffu, mbar_wait(bar_empty + 8 * st, ph ^ 1, abort_flag));
+                if (!ok) break;
+                if (elect_one()) {
                     mbar_expect_tx(bar_full + 8 * st, B_STAGE_BYTES);
                     tma_load_2d(smem_b + st * B_STAGE_BYTES, &map_w, bar_full + 8 * st, kc * BK, t * BN);
                 }
+                if (++st == NSTAGE) st = 0, ph ^= 1;
             }
+            if (++t == NT) t = 0;
         }
     } else if (warp == 1) {
         // ------------------------------ MMA issuer ------------------------------
-        if (lane == 0) {
-            uint32_t it = 0, seg = 0, tile = 0;
-            bool ok = true;
-            long long u = u_begin;
-            while (u < u_end && ok) {
-                const int rt = (int)(u / NT);
-                const long long seg_end = min(u_end, (long long)(rt + 1) * NT);
-                if (!mbar_wait(bar_a, seg & 1, abort_flag)) break;
-                for (; u < seg_end && ok; u++, tile++) {
-                    const uint32_t buf = tile & 1, use = tile >> 1;
-                    if (!mbar_wait(bar_tempty + 8 * buf, (use & 1) ^ 1, abort_flag)) {
-                        ok = false;
-                        break;
-                    }
+        uint32_t st = 0, ph = 0, seg = 0, tile = 0;
+        bool ok = true;
+        long long u = u_begin;
+        while (u < u_end && ok) {
+            const int rt = (int)(u / NT);
+            const long long seg_end = min(u_end, (long long)(rt + 1) * NT);
+            ok = __all_sync(0xffffffffu, mbar_wait(bar_a, seg & 1, abort_flag));
+            if (!ok) break;
+            for (; u < seg_end && ok; u++, tile++) {
+                const uint32_t buf = tile & 1, use = tile >> 1;
+                ok = __all_sync(0xffffffffu, mbar_wait(bar_tempty + 8 * buf, (use & 1) ^ 1, abort_flag));
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t d = tmem_base + buf * BN;
+                for (int kc = 0; kc < KC; kc++) {
+                    ok = __all_sync(0xffffffffu, mbar_wait(bar_full + 8 * st, ph, abort_flag));
+                    if (!ok) break;
                     tc_fence_after();
-                    const uint32_t d = tmem_base + buf * BN;
-                    for (int kc = 0; kc < KC; kc++, it++) {
-                        const uint32_t st = it % NSTAGE, ph = (it / NSTAGE) & 1;
-                        if (!mbar_wait(bar_full + 8 * st, ph, abort_flag)) {
-                            ok = false;
-                            break;
-                        }
-                        tc_fence_after();
-                        const uint64_t da = umma_desc(smem_a + kc * A_CHUNK_BYTES);
-                        const uint64_t db = umma_desc(smem_b + st * B_STAGE_BYTES);
+                    const uint64_t da = umma_desc(smem_a + kc * A_CHUNK_BYTES);
+                    const uint64_t db = umma_desc(smem_b + st * B_STAGE_BYTES);
+                    if (elect_one()) {
 #pragma unroll
                         for (int k = 0; k < BK / UK; k++)  // +32 B along K inside the swizzle span = +2 in the address field
                             umma_f16(d, da + 2 * k, db + 2 * k, (kc | k) != 0);
                         umma_commit(bar_empty + 8 * st);  // frees the W stage when these MMAs have read it
                     }
-                    if (ok) umma_commit(bar_tfull + 8 * buf);
+                    if (++st == NSTAGE) st = 0, ph ^= 1;
                 }
-                if (ok) umma_commit(bar_a_free);
-                seg++;
+                if (ok && elect_one()) umma_commit(bar_tfull + 8 * buf);
             }
+            if (ok && elect_one()) umma_commit(bar_a_free);
+            seg++;
         }
     } else {
         // -------- state-tile loader + epilogue: one row and one 128-column half per thread --------
