@@ -180,43 +180,54 @@ __device__ __forceinline__ float ex2(float x) {
 // ---------------------------------------------------------------------------------------
 // preparation: compact row list, target lists sorted by token id
 // ---------------------------------------------------------------------------------------
-// row_src[compact row] = padded row b * L + l for every real node (l < m_b; every l when no
-// lengths are given), prefix[b] = compact index of sentence b's first row, *n_rows = their count.
-__global__ void compact_rows_kernel(const int64_t *__restrict__ ol, int B, int L, int *prefix, int *row_src,
-                                    int *n_rows, int *status) {
-    __shared__ int total;
-    if (threadIdx.x == 0) {
-        int acc = 0;
-        for (int b = 0; b < B; b++) {
-            prefix[b] = acc;
-            int m = ol ? (int)ol[b] : L;
-            if (m < 0 || m > L) {
-                flag(status, PCFGNAT_STATUS_BAD_LENGTH);
-                m = m < 0 ? 0 : L;
-            }
-            acc += m;
-        }
-        prefix[B] = acc;
-        *n_rows = acc;
-        total = acc;
+// One block per sentence b.
+//  * prefix[b] = compact index of its first row = sum of the lengths before it (every block reduces
+//    the lengths itself, so no block waits for another); row_src[prefix[b] + l] = padded row b * L + l
+//    for every real node (l < m_b; every l when no lengths are given); the last block also writes
+//    prefix[B] and *n_rows.
+//  * with targets: the sentence's target ids sorted ascending (stable rank sort) into stok, with
+//    their original positions in sslot; ids outside [0, V) sort last as INT_MAX and raise a status bit.
+__global__ void proj_prepare_kernel(const int64_t *__restrict__ ol, const int64_t *__restrict__ targets, int B, int L,
+                                    int T, int V, int *prefix, int *row_src, int *n_rows, int *stok, int *sslot,
+                                    int *status) {
+    __shared__ int warp_sum[32];
+    __shared__ int before_s;
+    const int b = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    auto length = [&](int i) {
+        int m = ol ? (int)ol[i] : L;
+        return m < 0 ? 0 : (m > L ? L : m);
+    };
+    int acc = 0;
+    for (int i = threadIdx.x; i < b; i += blockDim.x) acc += length(i);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) warp_sum[warp] = acc;
+    __syncthreads();
+    if (warp == 0) {
+        int v = lane < (int)(blockDim.x >> 5) ? warp_sum[lane] : 0;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        if (lane == 0) before_s = v;
     }
     __syncthreads();
-    for (int b = 0; b < B; b++) {
-        const int lo = prefix[b], len = prefix[b + 1] - lo;
-        for (int l = threadIdx.x; l < len; l += blockDim.x) row_src[lo + l] = b * L + l;
+    const int before = before_s, mine = length(b);
+    if (threadIdx.x == 0) {
+        if (ol && (ol[b] < 0 || ol[b] > L)) flag(status, PCFGNAT_STATUS_BAD_LENGTH);
+        prefix[b] = before;
+        if (b == B - 1) {
+            prefix[B] = before + mine;
+            *n_rows = before + mine;
+        }
     }
-    (void)total;
-}
-
-__global__ void sort_targets_kernel(const int64_t *__restrict__ targets, int T, int V, int *stok, int *sslot,
-                                    int *status) {
-    const int b = blockIdx.x;
+    for (int l = threadIdx.x; l < mine; l += blockDim.x) row_src[before + l] = b * L + l;
+    if (!targets) return;
     const int64_t *tg = targets + (size_t)b * T;
     for (int s = threadIdx.x; s < T; s += blockDim.x) {
-        int64_t mine = tg[s];
-        const bool bad = mine < 0 || mine >= V;
-        if (bad) flag(status, PCFGNAT_STATUS_BAD_INDEX);
-        const int64_t key = bad ? (int64_t)INT_MAX : mine;
+        int64_t key = tg[s];
+        if (key < 0 || key >= V) {
+            flag(status, PCFGNAT_STATUS_BAD_INDEX);
+            key = INT_MAX;
+        }
         int rank = 0;
         for (int j = 0; j < T; j++) {
             int64_t o = tg[j];
@@ -501,8 +512,9 @@ __global__ void __launch_bounds__(PROJ_THREADS, 1)
 // ---------------------------------------------------------------------------------------
 __global__ void proj_merge_kernel(const Partial *__restrict__ partials, const int *__restrict__ prefix,
                                   const int *__restrict__ n_rows_ptr, int ctas, int max_seg, int N, int V, int L, int T,
-                                  const int64_t *__restrict__ ol, const int64_t *__restrict__ tl, float *match,
-                                  float *max_lprob, int64_t *argmax, float *lse_out) {
+                                  const int64_t *__restrict__ ol, const int64_t *__restrict__ tl,
+                                  const int64_t *__restrict__ targets, float *match, float *max_lprob,
+                                  int64_t *argmax, float *lse_out) {
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (warp >= N) return;
     const int row = warp, b = row / L, l = row % L;
@@ -514,7 +526,10 @@ __global__ void proj_merge_kernel(const Partial *__restrict__ partials, const in
             if (argmax) argmax[row] = 0;
         }
         if (match)
-            for (int t = lane; t < T; t += 32) match[(size_t)row * T + t] = 0.f;
+            for (int t = lane; t < T; t += 32) {
+                const int64_t tok = targets[(size_t)b * T + t];
+                match[(size_t)row * T + t] = (tok < 0 || tok >= V) ? CUDART_NAN_F : 0.f;
+            }
         return;
     }
     const Plan plan = Plan::make(*n_rows_ptr, V, ctas, max_seg);
@@ -559,20 +574,12 @@ __global__ void proj_merge_kernel(const Partial *__restrict__ partials, const in
         }
         float *out = match + (size_t)row * T;
         for (int t = lane; t < T; t += 32) {
+            const int64_t tok = targets[(size_t)b * T + t];
             float v = out[t] - lse;
             if (t == eos_col && !keep_eos) v = -CUDART_INF_F;
+            if (tok < 0 || tok >= V) v = CUDART_NAN_F;  // never gathered
             out[t] = v;
         }
-    }
-}
-
-// rows whose target id is out of range get NaN (they were never gathered)
-__global__ void proj_poison_bad_targets_kernel(const int *__restrict__ stok, const int *__restrict__ sslot, int B,
-                                               int L, int T, float *match) {
-    const int b = blockIdx.x;
-    for (int p = T - 1; p >= 0 && stok[(size_t)b * T + p] == INT_MAX; p--) {
-        const int slot = sslot[(size_t)b * T + p];
-        for (int l = threadIdx.x; l < L; l += blockDim.x) match[((size_t)b * L + l) * T + slot] = CUDART_NAN_F;
     }
 }
 
@@ -673,8 +680,8 @@ int launch_proj(const void *hidden, const void *weight, const int64_t *targets, 
 
     CUtensorMap map_w;
     if (!make_map(&map_w, weight, (uint64_t)V, (uint64_t)H, BN)) return PCFGNAT_ERR_CUDA;
-    compact_rows_kernel<<<1, 1024, 0, st>>>(ol, B, L, w.prefix, w.row_src, w.n_rows, status);
-    if (gather) sort_targets_kernel<<<B, 128, 0, st>>>(targets, T, V, w.stok, w.sslot, status);
+    proj_prepare_kernel<<<B, 128, 0, st>>>(ol, gather ? targets : nullptr, B, L, T, V, w.prefix, w.row_src, w.n_rows,
+                                           w.stok, w.sslot, status);
     const size_t smem = (size_t)KC_MAX * A_CHUNK_BYTES + (size_t)NSTAGE * B_STAGE_BYTES + 1024;
     const bool want_arg = max_lprob != nullptr || argmax != nullptr;
     const __half *hid = static_cast<const __half *>(hidden);
@@ -694,9 +701,8 @@ int launch_proj(const void *hidden, const void *weight, const int64_t *targets, 
     if (cudaGetLastError() != cudaSuccess) return PCFGNAT_ERR_CUDA;
     const int warps_per_block = 8;
     proj_merge_kernel<<<(N + warps_per_block - 1) / warps_per_block, warps_per_block * 32, 0, st>>>(
-        w.partials, w.prefix, w.n_rows, geo.ctas, geo.max_seg, N, V, L, T, ol, tl, gather ? match : nullptr, max_lprob,
-        argmax, lse);
-    if (gather) proj_poison_bad_targets_kernel<<<B, 128, 0, st>>>(w.stok, w.sslot, B, L, T, match);
+        w.partials, w.prefix, w.n_rows, geo.ctas, geo.max_seg, N, V, L, T, ol, tl, targets, gather ? match : nullptr,
+        max_lprob, argmax, lse);
     return cuda_rc(cudaGetLastError());
 }
 

@@ -84,7 +84,7 @@ class LossStep(_GraphedStep):
     target_length [B].  ``run()`` returns (stats[3] f32 = [sum_b S_b/n_b, sentences, invalid],
     match_all_grad, links_grad, sentence_loss); static outputs, overwritten by the next ``run()``.
     """
-    kernels_per_step = 8  # compact_rows, sort_targets, proj, proj_merge, proj_poison, loss_fwd, outside, grad
+    kernels_per_step = 6  # proj_prepare, proj, proj_merge, loss_fwd, outside, grad
 
     def __init__(self, weight, B, L, T, device, use_graph=True):
         super().__init__(weight, B, L, device, use_graph)
@@ -107,7 +107,7 @@ class GlanceStep(LossStep):
     """projection (emissions + arg-max tokens) -> inside table -> best tree.
 
     ``run()`` returns (tree [B,L] i64, sentence log-likelihood [B], arg-max tokens [B,L] i64)."""
-    kernels_per_step = 7  # compact_rows, sort_targets, proj, proj_merge, proj_poison, loss_fwd, best_tree
+    kernels_per_step = 5  # proj_prepare, proj, proj_merge, loss_fwd, best_tree
 
     def _body(self):
         k = self.kernel
@@ -123,7 +123,7 @@ class DecodeStep(_GraphedStep):
 
     Inputs (``load`` order): hidden, links, output_length.  ``run()`` returns (tokens [B,L] i64 padded with
     ``pad_index``, count [B] i64, predicted length [B] i64)."""
-    kernels_per_step = 5  # compact_rows, proj, proj_merge, viterbi, backtrace
+    kernels_per_step = 5  # proj_prepare, proj, proj_merge, viterbi, backtrace
 
     def __init__(self, weight, B, L, left_tree_mask, device, beta=1.0, pad_index=1, use_graph=True):
         super().__init__(weight, B, L, device, use_graph)
