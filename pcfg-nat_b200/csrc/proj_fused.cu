@@ -45,6 +45,7 @@ constexpr int A_CHUNK_BYTES = BM * BK * 2;  // 16 KB
 constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KB
 constexpr int EPI_WARPS = 8;                // two per TMEM sub-partition
 constexpr int PROJ_THREADS = 32 * (2 + EPI_WARPS);
+constexpr int TMEM_BUF_COLS = 256;         // column pitch of the two accumulators (512 columns allocated)
 constexpr int HALF_COLS = BN / 2;           // columns of a tile owned by one epilogue thread
 constexpr uint32_t kSpinLimit = 1u << 22;
 constexpr float kLog2e = 1.4426950408889634f;
@@ -287,7 +288,7 @@ __global__ void __launch_bounds__(PROJ_THREADS, 1)
     }
     if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
-                     "r"(2 * BN)
+                     "r"(2 * TMEM_BUF_COLS)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -331,7 +332,7 @@ __global__ void __launch_bounds__(PROJ_THREADS, 1)
                 ok = __all_sync(0xffffffffu, mbar_wait(bar_tempty + 8 * buf, (use & 1) ^ 1, abort_flag));
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t d = tmem_base + buf * BN;
+                const uint32_t d = tmem_base + buf * TMEM_BUF_COLS;
                 for (int kc = 0; kc < KC; kc++) {
                     ok = __all_sync(0xffffffffu, mbar_wait(bar_full + 8 * st, ph, abort_flag));
                     if (!ok) break;
@@ -368,17 +369,33 @@ __global__ void __launch_bounds__(PROJ_THREADS, 1)
             {
                 const int chunks_per_row = KC * 8;  // 16-byte chunks
                 const int total = BM * chunks_per_row;
-                for (int q = et; q < total; q += EPI_WARPS * 32) {
-                    const int r = q / chunks_per_row, cc = q - r * chunks_per_row;
-                    const int kc = cc >> 3, c = cc & 7;
-                    const int cr = rt * BM + r;
-                    uint4 val = make_uint4(0u, 0u, 0u, 0u);
-                    if (cr < n_rows) {
-                        const int src = __ldg(row_src + cr);
-                        val = __ldg(reinterpret_cast<const uint4 *>(hidden + (size_t)src * (KC * BK)) + cc);
+                constexpr int STEP = EPI_WARPS * 32, DEPTH = 8;  // DEPTH independent loads in flight per thread
+                for (int q0 = et; q0 < total; q0 += STEP * DEPTH) {
+                    int src[DEPTH];
+                    uint4 val[DEPTH];
+#pragma unroll
+                    for (int j = 0; j < DEPTH; j++) {
+                        const int q = q0 + j * STEP, cr = rt * BM + q / chunks_per_row;
+                        src[j] = (q < total && cr < n_rows) ? __ldg(row_src + cr) : -1;
                     }
-                    uint8_t *dst = smem + kc * A_CHUNK_BYTES + (r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4);
-                    *reinterpret_cast<uint4 *>(dst) = val;
+#pragma unroll
+                    for (int j = 0; j < DEPTH; j++) {
+                        const int q = q0 + j * STEP, cc = q % chunks_per_row;
+                        val[j] = make_uint4(0u, 0u, 0u, 0u);
+                        if (src[j] >= 0)
+                            val[j] = __ldg(reinterpret_cast<const uint4 *>(hidden + (size_t)src[j] * (KC * BK)) + cc);
+                    }
+#pragma unroll
+                    for (int j = 0; j < DEPTH; j++) {
+                        const int q = q0 + j * STEP;
+                        if (q < total) {
+                            const int r = q / chunks_per_row, cc = q - r * chunks_per_row;
+                            const int kc = cc >> 3, c = cc & 7;
+                            uint8_t *dst =
+                                smem + kc * A_CHUNK_BYTES + (r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4);
+                            *reinterpret_cast<uint4 *>(dst) = val[j];
+                        }
+                    }
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> tensor-core reads
                 mbar_arrive(bar_a);
@@ -412,7 +429,7 @@ __global__ void __launch_bounds__(PROJ_THREADS, 1)
                 }
                 tc_fence_after();
                 const int tile_col0 = (int)(u - (long long)rt * NT) * BN + half * HALF_COLS;
-                const uint32_t tsrc = tmem_base + ((uint32_t)(sub * 32) << 16) + buf * BN + half * HALF_COLS;
+                const uint32_t tsrc = tmem_base + ((uint32_t)(sub * 32) << 16) + buf * TMEM_BUF_COLS + half * HALF_COLS;
                 // One 32-column chunk of this thread's row: online max / sum-exp, arg-max, target logits.
                 auto process = [&](const uint32_t *r, const int col0) {
                     float v[32];
@@ -466,23 +483,19 @@ __global__ void __launch_bounds__(PROJ_THREADS, 1)
                     }
                 };
                 // the load of chunk c+1 is in flight while chunk c is processed
-                uint32_t ra[32], rb[32];
+                uint32_t regs[2][32];
                 __syncwarp();  // the target loop may leave the lanes diverged; tcgen05.ld is warp-collective
-                tmem_ld32_issue(tsrc, ra);
-                tmem_ld_wait(ra);
-                __syncwarp();
-                tmem_ld32_issue(tsrc + 32, rb);
-                process(ra, tile_col0);
-                tmem_ld_wait(rb);
-                __syncwarp();
-                tmem_ld32_issue(tsrc + 64, ra);
-                process(rb, tile_col0 + 32);
-                tmem_ld_wait(ra);
-                __syncwarp();
-                tmem_ld32_issue(tsrc + 96, rb);
-                process(ra, tile_col0 + 64);
-                tmem_ld_wait(rb);
-                process(rb, tile_col0 + 96);
+                tmem_ld32_issue(tsrc, regs[0]);
+                tmem_ld_wait(regs[0]);
+#pragma unroll
+                for (int c = 0; c < HALF_COLS / 32; c++) {
+                    if (c + 1 < HALF_COLS / 32) {
+                        __syncwarp();
+                        tmem_ld32_issue(tsrc + (c + 1) * 32, regs[(c + 1) & 1]);
+                    }
+                    process(regs[c & 1], tile_col0 + c * 32);
+                    if (c + 1 < HALF_COLS / 32) tmem_ld_wait(regs[(c + 1) & 1]);
+                }
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
@@ -503,7 +516,7 @@ __global__ void __launch_bounds__(PROJ_THREADS, 1)
     __syncthreads();
     if (warp == 0) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * TMEM_BUF_COLS) : "memory");
     }
 }
 
