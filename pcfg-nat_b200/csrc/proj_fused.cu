@@ -521,77 +521,105 @@ __global__ void __launch_bounds__(PROJ_THREADS, 1)
 }
 
 // ---------------------------------------------------------------------------------------
-// merge of the per-segment partials; one warp per padded row
+// merge of the per-segment partials.  Blocks [0, 8 * row_tiles) take 16 rows of one tile of 128 compact
+// rows each (the schedule is looked up once per block, one warp per row); the B blocks after them fill
+// the padding rows of one sentence each.
 // ---------------------------------------------------------------------------------------
+constexpr int kMergeSplit = 8, kMergeThreads = 32 * (BM / kMergeSplit);
 __global__ void proj_merge_kernel(const Partial *__restrict__ partials, const int *__restrict__ prefix,
-                                  const int *__restrict__ n_rows_ptr, int ctas, int max_seg, int N, int V, int L, int T,
-                                  const int64_t *__restrict__ ol, const int64_t *__restrict__ tl,
-                                  const int64_t *__restrict__ targets, float *match, float *max_lprob,
-                                  int64_t *argmax, float *lse_out) {
-    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-    if (warp >= N) return;
-    const int row = warp, b = row / L, l = row % L;
-    const int len_b = prefix[b + 1] - prefix[b];
-    if (l >= len_b) {  // padding row: not projected
-        if (lane == 0) {
-            if (lse_out) lse_out[row] = 0.f;
-            if (max_lprob) max_lprob[row] = 0.f;
-            if (argmax) argmax[row] = 0;
-        }
-        if (match)
-            for (int t = lane; t < T; t += 32) {
-                const int64_t tok = targets[(size_t)b * T + t];
-                match[(size_t)row * T + t] = (tok < 0 || tok >= V) ? CUDART_NAN_F : 0.f;
+                                  const int *__restrict__ row_src, const int *__restrict__ n_rows_ptr, int ctas,
+                                  int max_seg, int row_tiles, int V, int L, int T, const int64_t *__restrict__ ol,
+                                  const int64_t *__restrict__ tl, const int64_t *__restrict__ targets, float *match,
+                                  float *max_lprob, int64_t *argmax, float *lse_out) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+    if ((int)blockIdx.x >= kMergeSplit * row_tiles) {  // padding rows of sentence b: not projected
+        const int b = blockIdx.x - kMergeSplit * row_tiles;
+        const int len_b = prefix[b + 1] - prefix[b];
+        for (int l = len_b + warp; l < L; l += n_warps) {
+            const int row = b * L + l;
+            if (lane == 0) {
+                if (lse_out) lse_out[row] = 0.f;
+                if (max_lprob) max_lprob[row] = 0.f;
+                if (argmax) argmax[row] = 0;
             }
+            if (match)
+                for (int t = lane; t < T; t += 32) {
+                    const int64_t tok = targets[(size_t)b * T + t];
+                    match[(size_t)row * T + t] = (tok < 0 || tok >= V) ? CUDART_NAN_F : 0.f;
+                }
+        }
         return;
     }
-    const Plan plan = Plan::make(*n_rows_ptr, V, ctas, max_seg);
-    const int cr = prefix[b] + l, rt = cr / BM, r_in = cr % BM;
-    const long long u0 = (long long)rt * plan.n_tiles, u1 = u0 + plan.n_tiles - 1;
-    const int g_lo = plan.cta_of(u0), g_hi = plan.cta_of(u1);
-    float m = -CUDART_INF_F, best = -CUDART_INF_F;
-    int best_idx = 0;
-    for (int g = g_lo; g <= g_hi; g++) {
-        const int seg = rt - (int)(plan.begin(g) / plan.n_tiles);
-        for (int h = 0; h < 2; h++) {
+    const int rt = blockIdx.x / kMergeSplit, part = blockIdx.x % kMergeSplit, n_rows = *n_rows_ptr;
+    if (rt * BM + part * (BM / kMergeSplit) >= n_rows) return;
+    __shared__ int s_glo, s_ghi, s_seg_lo;
+    if (threadIdx.x == 0) {
+        const Plan plan = Plan::make(n_rows, V, ctas, max_seg);
+        const long long u0 = (long long)rt * plan.n_tiles, u1 = u0 + plan.n_tiles - 1;
+        s_glo = plan.cta_of(u0);
+        s_ghi = plan.cta_of(u1);
+        // only the first CTA of the tile can have begun in an earlier row tile; the others start inside
+        // this one, where it is their segment 0
+        s_seg_lo = rt - (int)(plan.begin(s_glo) / plan.n_tiles);
+    }
+    __syncthreads();
+    const int g_lo = s_glo, seg_lo = s_seg_lo, n_part = (s_ghi - g_lo + 1) * 2;
+    for (int r_in = part * (BM / kMergeSplit) + warp; r_in < (part + 1) * (BM / kMergeSplit); r_in += n_warps) {
+        const int cr = rt * BM + r_in;
+        if (cr >= n_rows) break;
+        const int row = row_src[cr], b = row / L, l = row - b * L;
+        // lane i merges partials i, i + 32, ...; then the lanes are combined
+        float m = -CUDART_INF_F, s = 0.f, best = -CUDART_INF_F;
+        int best_idx = INT_MAX;
+        for (int i = lane; i < n_part; i += 32) {
+            const int g = g_lo + (i >> 1), h = i & 1, seg = (i >> 1) == 0 ? seg_lo : 0;
             const Partial p = partials[(((size_t)g * max_seg + seg) * 2 + h) * BM + r_in];
-            m = fmaxf(m, p.m);
-            // first maximum in column order: slots are not visited in column order (the two halves of a
-            // tile interleave), so equal values are resolved by the recorded column
+            if (p.s > 0.f) {  // then p.m is finite
+                const float nm = fmaxf(m, p.m);
+                s = (s > 0.f ? s * exp2f((m - nm) * kLog2e) : 0.f) + p.s * exp2f((p.m - nm) * kLog2e);
+                m = nm;
+            }
+            // first maximum in column order: equal values are resolved by the recorded column
             if (p.best > best || (p.best == best && p.best_idx < best_idx)) {
                 best = p.best;
                 best_idx = p.best_idx;
             }
         }
-    }
-    float s = 0.f;
-    for (int g = g_lo; g <= g_hi; g++) {
-        const int seg = rt - (int)(plan.begin(g) / plan.n_tiles);
-        for (int h = 0; h < 2; h++) {
-            const Partial p = partials[(((size_t)g * max_seg + seg) * 2 + h) * BM + r_in];
-            if (p.s > 0.f) s += p.s * exp2f((p.m - m) * kLog2e);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float om = __shfl_xor_sync(0xffffffffu, m, o), os = __shfl_xor_sync(0xffffffffu, s, o);
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, best_idx, o);
+            const float nm = fmaxf(m, om);
+            s = (s > 0.f ? s * exp2f((m - nm) * kLog2e) : 0.f) + (os > 0.f ? os * exp2f((om - nm) * kLog2e) : 0.f);
+            m = nm;
+            if (ob > best || (ob == best && oi < best_idx)) {
+                best = ob;
+                best_idx = oi;
+            }
         }
-    }
-    const float lse = m + log2f(s) * kLn2;
-    if (lane == 0) {
-        if (lse_out) lse_out[row] = lse;
-        if (max_lprob) max_lprob[row] = best - lse;
-        if (argmax) argmax[row] = best_idx;
-    }
-    if (match) {
-        int eos_col = -1;
-        bool keep_eos = true;
-        if (ol && tl) {  // criterion's EOS masking (criterions/nat_pcfg_loss.py:112-115)
-            eos_col = (int)tl[b] - 1;
-            keep_eos = l == (int)ol[b] - 1;
+        if (best_idx == INT_MAX) best_idx = 0;
+        const float lse = m + log2f(s) * kLn2;
+        if (lane == 0) {
+            if (lse_out) lse_out[row] = lse;
+            if (max_lprob) max_lprob[row] = best - lse;
+            if (argmax) argmax[row] = best_idx;
         }
-        float *out = match + (size_t)row * T;
-        for (int t = lane; t < T; t += 32) {
-            const int64_t tok = targets[(size_t)b * T + t];
-            float v = out[t] - lse;
-            if (t == eos_col && !keep_eos) v = -CUDART_INF_F;
-            if (tok < 0 || tok >= V) v = CUDART_NAN_F;  // never gathered
-            out[t] = v;
+        if (match) {
+            int eos_col = -1;
+            bool keep_eos = true;
+            if (ol && tl) {  // criterion's EOS masking (criterions/nat_pcfg_loss.py:112-115)
+                eos_col = (int)tl[b] - 1;
+                keep_eos = l == (int)ol[b] - 1;
+            }
+            float *out = match + (size_t)row * T;
+            for (int t = lane; t < T; t += 32) {
+                const int64_t tok = targets[(size_t)b * T + t];
+                float v = out[t] - lse;
+                if (t == eos_col && !keep_eos) v = -CUDART_INF_F;
+                if (tok < 0 || tok >= V) v = CUDART_NAN_F;  // never gathered
+                out[t] = v;
+            }
         }
     }
 }
@@ -712,10 +740,10 @@ int launch_proj(const void *hidden, const void *weight, const int64_t *targets, 
                                                 gather ? match : nullptr, w.partials, status);
     }
     if (cudaGetLastError() != cudaSuccess) return PCFGNAT_ERR_CUDA;
-    const int warps_per_block = 8;
-    proj_merge_kernel<<<(N + warps_per_block - 1) / warps_per_block, warps_per_block * 32, 0, st>>>(
-        w.partials, w.prefix, w.n_rows, geo.ctas, geo.max_seg, N, V, L, T, ol, tl, targets, gather ? match : nullptr,
-        max_lprob, argmax, lse);
+    const int row_tiles = (N + BM - 1) / BM;
+    proj_merge_kernel<<<kMergeSplit * row_tiles + B, kMergeThreads, 0, st>>>(w.partials, w.prefix, w.row_src, w.n_rows, geo.ctas, geo.max_seg,
+                                                     row_tiles, V, L, T, ol, tl, targets, gather ? match : nullptr,
+                                                     max_lprob, argmax, lse);
     return cuda_rc(cudaGetLastError());
 }
 
