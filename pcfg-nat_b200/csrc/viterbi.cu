@@ -7,41 +7,197 @@
 // lengths).  With max_left == 1 the two live expansions of node a at length len are
 //     t0 = ((links[a][0][c] + 0) + S[c][len-1]) + ob[a]                (j = 0, no left child)
 //     t1 = ((links[a][1][c] + ob[a-1]) + S[c][len-2]) + ob[a]          (j = 1, leaf a-1)
-// Thread (x, y) owns row id = y and scans c_id = id + x + 4k in increasing k, t0 before t1,
-// strict '>'; lanes are merged with shfl_down 2 then 1 under strict '>' — the reference's
-// order, so values and backpointers are bit-exact.  Tables are indexed by node id; R, Lt
-// hold node ids (Lt = 0 for "no left child"), Mt holds j.
+// The reference gives node id four threads x = 0..3; thread x scans c_id = id + x + 4k in increasing
+// k, t0 before t1, under strict '>', and the four are merged with shfl_down 2 then 1 under strict
+// '>'.  A maximum is order-free except for ties, so here a whole warp owns the node (lane l scans
+// c_id = id + l + 32 i, which is reference thread x = l & 3) and the reference's choice among equal
+// values is reproduced by an explicit tie key: thread priority 0 > 2 > 1 > 3, then the smaller c,
+// then j = 0 before j = 1.  Values and backpointers are bit-exact.  Tables are indexed by node id;
+// R, Lt hold node ids (Lt = 0 for "no left child"), Mt holds j.
+//
+// viterbi_cluster_kernel spreads the nodes of a sentence over the CTAs of a thread-block cluster
+// (one cluster per sentence, sized so that the batch fills the GPU): every CTA keeps the rolling
+// columns of the whole chain, a warp that finishes a node stores its value into every CTA's copy
+// through distributed shared memory, and the cluster meets at a hardware barrier once per length.
+// viterbi_global_kernel (one CTA per sentence, links read from global memory) takes the shapes
+// whose links do not fit the cluster's shared memory.
 //
 // backtrace_kernel replaces the host function viterbi_decoding
-// (fs_plugins/custom_ops/pcfg_loss.cpp:12-73): one thread per sentence does the in-order
-// walk with an explicit stack, skipping pad tokens and collapsing repeats.
+// (fs_plugins/custom_ops/pcfg_loss.cpp:12-73): one thread per sentence (a block each, so that the
+// walks run on different SMs) does the in-order walk with an explicit stack, skipping pad tokens and
+// collapsing repeats.  The three table entries of a node are fetched together when it is stacked.
+#include <cooperative_groups.h>
+
+#include <climits>
+#include <cstdlib>
+
 #include "common.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace pcfgnat {
 
 namespace {
 
-template <bool SMEM_LINKS>
-__global__ void __launch_bounds__(kMaxRows *kLanes)
-    viterbi_kernel(const float *__restrict__ ob_lprob, const float *__restrict__ links,
-                   const int64_t *__restrict__ ol, int L, float *S, int64_t *R, int64_t *Lt, int64_t *Mt, int *status,
-                   int Mc, int col_stride, int lk_stride) {
+constexpr int kVitThreads = 1024;
+constexpr int kVitWarps = kVitThreads / 32;
+
+// Monotone map float -> unsigned (no NaN reaches it); -0 is mapped like +0 so that, as under the
+// reference's '>', neither beats the other.
+__device__ __forceinline__ unsigned ordered_bits(float v) {
+    const unsigned u = __float_as_uint(v == 0.f ? 0.f : v);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+// Warp arg-max of (best, key) pairs: the largest value, among equal values the smallest key.
+// Every lane returns the winner's value and key (key INT_MAX: nothing finite was seen).
+__device__ __forceinline__ void warp_argmax(float &best, int &key, int lane) {
+    const unsigned ord = ordered_bits(best);
+    const unsigned top = __reduce_max_sync(0xffffffffu, ord);
+    const unsigned k = __reduce_min_sync(0xffffffffu, ord == top ? (unsigned)key : 0xffffffffu);
+    const unsigned holders = __ballot_sync(0xffffffffu, ord == top && (unsigned)key == k);
+    best = __shfl_sync(0xffffffffu, best, holders ? __ffs(holders) - 1 : lane);
+    key = (int)k;
+}
+
+// One step of node `id` for the lanes of a warp: children ci = id + lane + 32 i.
+//   t0 = ((links[a][0][c] + 0) + S[c][len-1]) + ob[a]      (k0[ci] holds links[a][0][c] + 0)
+//   t1 = ((links[a][1][c] + ob[a-1]) + S[c][len-2]) + ob[a] (k1[ci] holds links[a][1][c] + ob[a-1];
+//        -inf for the first node, which has no leaf, so that t1 never wins there)
+// A NaN term never wins a '>' either, which is what the reference's NaN -> -inf cleaning achieves.
+template <class K0, class K1>
+__device__ __forceinline__ void viterbi_node(int id, int Mb, int lane, int prio, float oa, const float *S1,
+                                             const float *S2, K0 k0, K1 k1, float &best, int &key) {
+    best = neg_inf();
+    key = INT_MAX;  // (prio << 24) | (c_slot << 1) | j of the current best; smaller wins ties
+    for (int ci = id + lane; ci < Mb; ci += 32) {
+        const int kk = (prio << 24) | (ci << 1);
+        const float t0 = (k0(ci) + S1[ci]) + oa;
+        if (t0 > best) {
+            best = t0;
+            key = kk;
+        }
+        const float t1 = (k1(ci) + S2[ci]) + oa;
+        if (t1 > best) {
+            best = t1;
+            key = kk | 1;
+        }
+    }
+    warp_argmax(best, key, lane);
+}
+
+__device__ __forceinline__ void viterbi_store(float best, int key, int a, int Q, int len, float *Sb, int64_t *Rb,
+                                              int64_t *Lb, int64_t *Mtb) {
+    if (isinf(best)) return;  // cell stays at its initial value (pcfg_viterbi.cu:113-121)
+    const int bj = key & 1, bc = 2 * ((key >> 1) & 0x7FFFFF) + 1;
+    const size_t o = (size_t)a * Q + len;
+    Sb[o] = best;
+    Lb[o] = bj ? a - 1 : 0;
+    Rb[o] = bc;
+    Mtb[o] = bj;
+}
+
+__global__ void __launch_bounds__(kVitThreads, 1)
+    viterbi_cluster_kernel(const float *__restrict__ ob_lprob, const float *__restrict__ links,
+                           const int64_t *__restrict__ ol, int L, float *S, int64_t *R, int64_t *Lt, int64_t *Mt,
+                           int *status, int Mc, int cs, int rows_cap, int lk_stride) {
     extern __shared__ float smem[];
-    const int b = blockIdx.x;
-    const int x = threadIdx.x, y = threadIdx.y;
-    const int rows = blockDim.y;
-    const int tid = y * kLanes + x, nthr = rows * kLanes;
+    cg::cluster_group cluster = cg::this_cluster();
+    const int NC = (int)cluster.num_blocks(), crank = (int)cluster.block_rank();
+    const int b = blockIdx.x / NC;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int ctid = crank * kVitThreads + tid, cthreads = NC * kVitThreads;  // thread index inside the cluster
     const int Q = L / 4;
     const int m = (int)ol[b];
     const float *ob = ob_lprob + (size_t)b * L;
     const float *lkb = links + (size_t)b * L * 2 * L;
     float *Sb = S + (size_t)b * L * Q;
-    int64_t *Rb = R + (size_t)b * L * Q, *Lb = Lt + (size_t)b * L * Q, *Mb_ = Mt + (size_t)b * L * Q;
+    int64_t *Rb = R + (size_t)b * L * Q, *Lb = Lt + (size_t)b * L * Q, *Mtb = Mt + (size_t)b * L * Q;
+    for (int i = ctid; i < L * Q; i += cthreads) {
+        Sb[i] = neg_inf();
+        Rb[i] = 0;
+        Lb[i] = 0;
+        Mtb[i] = 0;
+    }
+    if (m < 2 || m > L) {  // uniform over the cluster: nobody reaches a cluster barrier
+        if (ctid == 0) flag(status, PCFGNAT_STATUS_BAD_LENGTH);
+        return;
+    }
+    const int Mb = main_nodes_below(m);
+    const int my_rows = Mb > crank ? (Mb - crank + NC - 1) / NC : 0;  // nodes id = crank + NC * r
+    float *col = smem;                // [3][cs] rolling S columns of the whole chain (replicated per CTA)
+    float *lk0 = col + 3 * cs;        // [rows_cap][lk_stride] links[a][0][c] + 0 of this CTA's nodes, by child slot
+    float *lk1 = lk0 + (size_t)rows_cap * lk_stride;  // links[a][1][c] + ob[a-1]
+    // results of this CTA's nodes, flushed to global memory after the last length: a global store inside
+    // the loop would make every cluster barrier (a release) wait for it to reach L2
+    float *own_v = lk1 + (size_t)rows_cap * lk_stride;       // [rows_cap][Q]
+    int *own_k = reinterpret_cast<int *>(own_v + (size_t)rows_cap * Q);  // [rows_cap][Q]
+
+    for (int r = warp; r < my_rows; r += kVitWarps) {
+        const int id = crank + NC * r;
+        const float *row = lkb + (size_t)(2 * id + 1) * 2 * L;
+        const float olf = id >= 1 ? __ldg(ob + 2 * id) : neg_inf();  // C[a-1][1] = ob[a-1] (pcfg_viterbi.cu:203-205)
+        for (int ci = id + lane; ci < Mb; ci += 32) {
+            lk0[r * lk_stride + ci] = __ldg(row + 2 * ci + 1) + 0.f;
+            lk1[r * lk_stride + ci] = __ldg(row + L + 2 * ci + 1) + olf;
+        }
+    }
+    for (int i = tid; i < 3 * cs; i += kVitThreads) col[i] = neg_inf();  // lengths 0 and 1; slots >= Mb for good
+    __syncthreads();
+    // S[m-1][1] = ob[m-1] (pcfg_viterbi.cu:58); it feeds the recurrence only if m-1 is a main-chain node
+    if (tid == 0 && ((m - 1) & 1)) col[1 * cs + (m - 2) / 2] = __ldg(ob + (m - 1));  // every CTA fills its own copy
+    // all copies initialised before anybody stores into a neighbour's; also orders the initial fill of the
+    // global tables (done by threads of any CTA of the cluster) before the cells written below
+    if (NC > 1) cluster.sync(); else __syncthreads();
+    if (ctid == 0) Sb[(size_t)(m - 1) * Q + 1] = __ldg(ob + (m - 1));
+
+    const int x = lane & 3;
+    const int prio = ((x & 1) << 1) | (x >> 1);  // reference thread 0 wins ties, then 2, 1, 3
+    const int n_len = m / 4;
+    for (int len = 2; len < n_len; len++) {
+        const float *S1 = col + ((len - 1) % 3) * cs;
+        const float *S2 = col + ((len - 2) % 3) * cs;
+        float *S0 = col + (len % 3) * cs;
+        for (int r = warp; r < my_rows; r += kVitWarps) {
+            const int id = crank + NC * r;
+            const float *r0 = lk0 + r * lk_stride, *r1 = lk1 + r * lk_stride;
+            float best;
+            int key;
+            viterbi_node(id, Mb, lane, prio, __ldg(ob + 2 * id + 1), S1, S2, [&](int ci) { return r0[ci]; },
+                         [&](int ci) { return r1[ci]; }, best, key);
+            if (lane < NC) *cluster.map_shared_rank(S0 + id, lane) = best;  // into every CTA's column
+            if (lane == 0) {
+                own_v[r * Q + len] = best;
+                own_k[r * Q + len] = key;
+            }
+        }
+        if (NC > 1) cluster.sync(); else __syncthreads();
+    }
+    for (int i = tid; i < my_rows * (n_len - 2); i += kVitThreads) {  // computed cells: lengths 2 .. n_len-1
+        const int r = i / (n_len - 2), len = 2 + i - r * (n_len - 2);
+        viterbi_store(own_v[r * Q + len], own_k[r * Q + len], 2 * (crank + NC * r) + 1, Q, len, Sb, Rb, Lb, Mtb);
+    }
+}
+
+__global__ void __launch_bounds__(kVitThreads)
+    viterbi_global_kernel(const float *__restrict__ ob_lprob, const float *__restrict__ links,
+                          const int64_t *__restrict__ ol, int L, float *S, int64_t *R, int64_t *Lt, int64_t *Mt,
+                          int *status, int Mc, int cs) {
+    extern __shared__ float smem[];
+    const int b = blockIdx.x;
+    const int tid = threadIdx.x, nthr = blockDim.x;
+    const int warp = tid >> 5, lane = tid & 31, n_warps = nthr >> 5;
+    const int Q = L / 4;
+    const int m = (int)ol[b];
+    const float *ob = ob_lprob + (size_t)b * L;
+    const float *lkb = links + (size_t)b * L * 2 * L;
+    float *Sb = S + (size_t)b * L * Q;
+    int64_t *Rb = R + (size_t)b * L * Q, *Lb = Lt + (size_t)b * L * Q, *Mtb = Mt + (size_t)b * L * Q;
     for (int i = tid; i < L * Q; i += nthr) {
         Sb[i] = neg_inf();
         Rb[i] = 0;
         Lb[i] = 0;
-        Mb_[i] = 0;
+        Mtb[i] = 0;
     }
     if (m < 2 || m > L) {
         if (tid == 0) flag(status, PCFGNAT_STATUS_BAD_LENGTH);
@@ -49,97 +205,33 @@ __global__ void __launch_bounds__(kMaxRows *kLanes)
     }
     const int Mb = main_nodes_below(m);
     float *col = smem;  // 3 rolling columns of S over main-chain slots
-    float *obs = col + 3 * col_stride;  // ob of main node (slot) and of its leaf
-    float *obl = obs + col_stride;
-    float *lk0 = obl + col_stride;
-    float *lk1 = lk0 + (size_t)Mc * lk_stride;
-    if (SMEM_LINKS) {
-        for (int i = tid; i < Mb * 2 * L; i += nthr) {
-            int c = i % L, k = (i / L) & 1, ai = i / (2 * L);
-            int a = 2 * ai + 1;
-            if ((c & 1) && c >= a && c < m) (k ? lk1 : lk0)[ai * lk_stride + (c >> 1)] = __ldg(lkb + ((size_t)a * 2 + k) * L + c);
-        }
-    }
-    for (int i = tid; i < Mc; i += nthr) {
-        col[0 * col_stride + i] = neg_inf();  // length 0
-        col[1 * col_stride + i] = neg_inf();  // length 1
-        if (i < Mb) {
-            obs[i] = __ldg(ob + 2 * i + 1);
-            obl[i] = i >= 1 ? __ldg(ob + 2 * i) : neg_inf();  // C[a-1][1] = ob[a-1] (pcfg_viterbi.cu:203-205)
-        }
-    }
-    __syncthreads();
+    for (int i = tid; i < 3 * cs; i += nthr) col[i] = neg_inf();
+    __syncthreads();  // also orders the initial fill of the tables before the cells written below
     if (tid == 0) {
-        // S[m-1][1] = ob[m-1] (pcfg_viterbi.cu:58); it feeds the recurrence only if m-1 is a main-chain node
-        float v = __ldg(ob + (m - 1));
+        const float v = __ldg(ob + (m - 1));
         Sb[(size_t)(m - 1) * Q + 1] = v;
-        if ((m - 1) & 1) col[1 * col_stride + (m - 2) / 2] = v;
+        if ((m - 1) & 1) col[1 * cs + (m - 2) / 2] = v;
     }
     __syncthreads();
-    const int Mpad = (Mb + rows - 1) / rows * rows;
+    const int x = lane & 3;
+    const int prio = ((x & 1) << 1) | (x >> 1);
     for (int len = 2; len < m / 4; len++) {
-        const float *S1 = col + ((len - 1) % 3) * col_stride;
-        const float *S2 = col + ((len - 2) % 3) * col_stride;
-        float *S0 = col + (len % 3) * col_stride;
-        for (int id = y; id < Mpad; id += rows) {
-            const bool live = id < Mb;
+        const float *S1 = col + ((len - 1) % 3) * cs;
+        const float *S2 = col + ((len - 2) % 3) * cs;
+        float *S0 = col + (len % 3) * cs;
+        for (int id = warp; id < Mb; id += n_warps) {
             const int a = 2 * id + 1;
-            float best = neg_inf();
-            int bc = 0, bj = 0;  // max_c, max_j (max_b follows from j)
-            if (live) {
-                const float oa = obs[id];
-                const float olf = obl[id];
-                const bool has_leaf = a >= 3;
-                for (int ci = id + x; ci < Mb; ci += kLanes) {
-                    float l0, l1;
-                    if (SMEM_LINKS) {
-                        l0 = lk0[id * lk_stride + ci];
-                        l1 = lk1[id * lk_stride + ci];
-                    } else {
-                        l0 = __ldg(lkb + ((size_t)a * 2 + 0) * L + 2 * ci + 1);
-                        l1 = __ldg(lkb + ((size_t)a * 2 + 1) * L + 2 * ci + 1);
-                    }
-                    float t0 = ((l0 + 0.f) + S1[ci]) + oa;
-                    if (isnan(t0)) t0 = neg_inf();
-                    if (t0 > best) {
-                        best = t0;
-                        bc = 2 * ci + 1;
-                        bj = 0;
-                    }
-                    if (has_leaf) {
-                        float t1 = ((l1 + olf) + S2[ci]) + oa;
-                        if (isnan(t1)) t1 = neg_inf();
-                        if (t1 > best) {
-                            best = t1;
-                            bc = 2 * ci + 1;
-                            bj = 1;
-                        }
-                    }
-                }
-            }
-#pragma unroll
-            for (int o = 2; o > 0; o >>= 1) {
-                float ov = __shfl_down_sync(0xffffffffu, best, o, kLanes);
-                int oc = __shfl_down_sync(0xffffffffu, bc, o, kLanes);
-                int oj = __shfl_down_sync(0xffffffffu, bj, o, kLanes);
-                if (ov > best) {
-                    best = ov;
-                    bc = oc;
-                    bj = oj;
-                }
-            }
-            if (live && x == 0) {
+            const float *row = lkb + (size_t)a * 2 * L;
+            const float olf = id >= 1 ? __ldg(ob + 2 * id) : neg_inf();
+            float best;
+            int key;
+            viterbi_node(id, Mb, lane, prio, __ldg(ob + a), S1, S2, [&](int ci) { return __ldg(row + 2 * ci + 1) + 0.f; },
+                         [&](int ci) { return __ldg(row + L + 2 * ci + 1) + olf; }, best, key);
+            if (lane == 0) {
                 S0[id] = best;
-                if (!isinf(best)) {
-                    size_t o = (size_t)a * Q + len;
-                    Sb[o] = best;
-                    Lb[o] = bj ? a - 1 : 0;
-                    Rb[o] = bc;
-                    Mb_[o] = bj;
-                }
+                viterbi_store(best, key, a, Q, len, Sb, Rb, Lb, Mtb);
             }
         }
-        for (int i = Mb + tid; i < Mc; i += nthr) S0[i] = neg_inf();
         __syncthreads();
     }
 }
@@ -149,10 +241,10 @@ __global__ void backtrace_kernel(const int64_t *__restrict__ pred, const int64_t
                                  const int64_t *__restrict__ Mt, const int64_t *__restrict__ tokens,
                                  const int64_t *__restrict__ mask, int mask_dim, int64_t pad, int B, int L, int Q,
                                  int cap, int64_t *out, int64_t *cnt, int *status) {
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= B) return;
+    const int i = blockIdx.x;
+    if (i >= B || threadIdx.x != 0) return;
     constexpr int kStack = 32;  // the walk only stacks a node and its left spine: depth <= left_tree_layer + 2
-    int stk_node[kStack], stk_len[kStack];
+    int stk_node[kStack], stk_len[kStack], stk_right[kStack], stk_mt[kStack];
     int sp = 0, count = 0;
     int node = 1, len = (int)pred[i];
     const int max_h = (int)ol[i];
@@ -167,19 +259,22 @@ __global__ void backtrace_kernel(const int64_t *__restrict__ pred, const int64_t
                 bad = true;
                 break;
             }
+            const size_t at = base + (size_t)node * Q + len;
+            int left = (int)Lt[at];
+            const int mt = (int)Mt[at];
             stk_node[sp] = node;
             stk_len[sp] = len;
+            stk_right[sp] = (int)R[at];
+            stk_mt[sp] = mt;
             sp++;
-            int left = (int)Lt[base + (size_t)node * Q + len];
             if (left == node) left = 0;
             if (left < 0 || left >= mask_dim || node >= mask_dim) {
                 bad = true;
                 break;
             }
             if (mask[(size_t)node * mask_dim + left]) break;
-            int nl = (int)Mt[base + (size_t)node * Q + len];
             node = left;
-            len = nl;
+            len = mt;
         }
         if (bad) break;
         sp--;
@@ -191,10 +286,8 @@ __global__ void backtrace_kernel(const int64_t *__restrict__ pred, const int64_t
             if (count < cap) o[count] = tok;
             count++;
         }
-        const int right = (int)R[base + (size_t)node * Q + len];
-        const int nl = len - (int)Mt[base + (size_t)node * Q + len] - 1;
-        node = right;
-        len = nl;
+        len = len - stk_mt[sp] - 1;
+        node = stk_right[sp];
     }
     if (bad) flag(status, PCFGNAT_STATUS_BAD_TRACE);
     cnt[i] = count;
@@ -207,30 +300,56 @@ int launch_viterbi(const float *ob, const float *links, const int64_t *ol, int B
                    int64_t *Lt, int64_t *Mt, int *status, cudaStream_t st) {
     if (B == 0) return PCFGNAT_OK;
     if (L < 8) return PCFGNAT_ERR_INVALID_ARGUMENT;  // column 1 of an [L][L/4] table must exist
-    const int Mc = main_slots(L, 1);
-    int rows = (Mc + 7) / 8 * 8;
-    if (rows < 8) rows = 8;
-    if (rows > kMaxRows) rows = kMaxRows;
-    const int col_stride = (Mc + 3) / 4 * 4;
-    int lk_stride = Mc;
-    while (lk_stride % 8 != 3) lk_stride++;
-    const size_t smem_cols = (size_t)5 * col_stride * sizeof(float);
-    const size_t smem_links = (size_t)2 * Mc * lk_stride * sizeof(float);
-    dim3 block(kLanes, rows), grid(B);
-    cudaError_t e;
-    if (smem_cols + smem_links <= (size_t)kSmemLimit - 1024) {
-        auto k = viterbi_kernel<true>;
-        e = ensure_dynamic_smem(k, smem_cols + smem_links);
-        if (e != cudaSuccess) return PCFGNAT_ERR_CUDA;
-        k<<<grid, block, smem_cols + smem_links, st>>>(ob, links, ol, L, S, R, Lt, Mt, status, Mc, col_stride,
-                                                       lk_stride);
-    } else {
-        if (smem_cols > (size_t)kSmemLimit - 1024) return PCFGNAT_ERR_TOO_LARGE;
-        auto k = viterbi_kernel<false>;
-        e = ensure_dynamic_smem(k, smem_cols);
-        if (e != cudaSuccess) return PCFGNAT_ERR_CUDA;
-        k<<<grid, block, smem_cols, st>>>(ob, links, ol, L, S, R, Lt, Mt, status, Mc, col_stride, lk_stride);
+    const int Mc = main_slots(L, 1), Q = L / 4;
+    const int cs = (Mc + 3) / 4 * 4;
+    const int lk_stride = (Mc + 31) / 32 * 32 + 1;
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    // Cluster size: as many CTAs per sentence (up to 8) as still lets all sentences run at once; more when
+    // a CTA's share of the links would not fit shared memory.  PCFGNAT_DP_KERNEL=rows forces the
+    // single-CTA kernel (A/B runs and tests), PCFGNAT_DP_CLUSTER_SIZE a cluster size.
+    int nc = 1;
+    while (nc < 8 && (long long)B * nc * 2 <= sms && Mc > 8 * nc) nc *= 2;
+    if (const char *v = getenv("PCFGNAT_DP_CLUSTER_SIZE")) {
+        const int want = atoi(v);
+        if (want == 1 || want == 2 || want == 4 || want == 8 || want == 16) nc = want;
     }
+    if (dp_kernel_choice() == kDpRows) nc = 32;  // skips the loop below
+    for (; nc <= 16; nc *= 2) {
+        const int rows_cap = (Mc + nc - 1) / nc;
+        const size_t smem = ((size_t)3 * cs + (size_t)2 * rows_cap * lk_stride + (size_t)2 * rows_cap * Q) * sizeof(float);
+        if (smem > (size_t)kSmemLimit - 1024) continue;
+        if (ensure_dynamic_smem(viterbi_cluster_kernel, smem) != cudaSuccess) return PCFGNAT_ERR_CUDA;
+        if (nc > 8 && cudaFuncSetAttribute(viterbi_cluster_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) !=
+                          cudaSuccess) {
+            cudaGetLastError();
+            break;
+        }
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)(B * nc));
+        cfg.blockDim = dim3(kVitThreads);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = (unsigned)nc;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        int max_clusters = 0;
+        if (cudaOccupancyMaxActiveClusters(&max_clusters, viterbi_cluster_kernel, &cfg) != cudaSuccess || max_clusters < 1) {
+            cudaGetLastError();
+            continue;  // this cluster size cannot be scheduled here: try the next one
+        }
+        return cuda_rc(cudaLaunchKernelEx(&cfg, viterbi_cluster_kernel, ob, links, ol, L, S, R, Lt, Mt, status, Mc, cs,
+                                          rows_cap, lk_stride));
+    }
+    const size_t smem_cols = (size_t)3 * cs * sizeof(float);
+    if (smem_cols > (size_t)kSmemLimit - 1024) return PCFGNAT_ERR_TOO_LARGE;
+    if (ensure_dynamic_smem(viterbi_global_kernel, smem_cols) != cudaSuccess) return PCFGNAT_ERR_CUDA;
+    const int warps = Mc < 4 ? 4 : (Mc > kVitWarps ? kVitWarps : Mc);
+    viterbi_global_kernel<<<B, 32 * warps, smem_cols, st>>>(ob, links, ol, L, S, R, Lt, Mt, status, Mc, cs);
     return cuda_rc(cudaGetLastError());
 }
 
@@ -238,7 +357,7 @@ int launch_backtrace(const int64_t *pred, const int64_t *ol, const int64_t *Lt, 
                      const int64_t *tokens, const int64_t *mask, int mask_dim, int64_t pad, int B, int L, int Q,
                      int cap, int64_t *out, int64_t *cnt, int *status, cudaStream_t st) {
     if (B == 0) return PCFGNAT_OK;
-    backtrace_kernel<<<(B + 31) / 32, 32, 0, st>>>(pred, ol, Lt, R, Mt, tokens, mask, mask_dim, pad, B, L, Q, cap, out,
+    backtrace_kernel<<<B, 32, 0, st>>>(pred, ol, Lt, R, Mt, tokens, mask, mask_dim, pad, B, L, Q, cap, out,
                                                    cnt, status);
     return cuda_rc(cudaGetLastError());
 }

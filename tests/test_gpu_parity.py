@@ -32,6 +32,19 @@ def dp_kernel(request, monkeypatch):
     return request.param
 
 
+@pytest.fixture(params=["auto", "rows", "cluster1", "cluster4"])
+def vit_kernel(request, monkeypatch):
+    """Runs a Viterbi test once per kernel: the library's own choice of cluster size, the single-CTA kernel
+    that reads links from global memory, and fixed clusters of 1 and 4 CTAs per sentence."""
+    monkeypatch.delenv("PCFGNAT_DP_KERNEL", raising=False)
+    monkeypatch.delenv("PCFGNAT_DP_CLUSTER_SIZE", raising=False)
+    if request.param == "rows":
+        monkeypatch.setenv("PCFGNAT_DP_KERNEL", "rows")
+    elif request.param.startswith("cluster"):
+        monkeypatch.setenv("PCFGNAT_DP_CLUSTER_SIZE", request.param[len("cluster"):])
+    return request.param
+
+
 def _g(name):
     p = golden_path(name)
     if not os.path.isfile(p):
@@ -169,7 +182,7 @@ def _viterbi_inputs(syn, name, kw, seed):
 
 
 @pytest.mark.parametrize("name,kw,seed", VCASES)
-def test_viterbi_bit_exact_against_oracle(ops, syn, name, kw, seed):
+def test_viterbi_bit_exact_against_oracle(vit_kernel, ops, syn, name, kw, seed):
     b, ob, tok = _viterbi_inputs(syn, name, kw, seed)
     S, R, Lt, Mt = ops.get_pcfg_kernel().pcfg_viterbi(ob.to(DEV), b.links.to(DEV), b.output_length.to(DEV), 1)
     So, Ro, Lo, Mo = oracle.pcfg_viterbi(ob.numpy(), b.links.numpy(), b.output_length.numpy())
@@ -194,8 +207,26 @@ def test_viterbi_bit_exact_against_oracle(ops, syn, name, kw, seed):
     np.testing.assert_array_equal(got_cpu.numpy(), want)
 
 
+def test_viterbi_tie_breaking(vit_kernel, ops, syn):
+    # emissions and transitions from a handful of exactly representable values: many candidates of a
+    # node tie, so the backpointers are decided by the reference's scan and merge order alone
+    b = syn.make_batch(syn.Workload("v_ties", emissions="logits", kind="viterbi", batch=4, vocab=80, hidden=8,
+                                    src_min=10, src_max=45), seed=5)
+    g = torch.Generator().manual_seed(7)
+    ob = -torch.randint(1, 4, (b.B, b.L), generator=g).float() * 0.5
+    finite = torch.isfinite(b.links)
+    links = torch.where(finite, -torch.randint(1, 3, b.links.shape, generator=g).float() * 0.25, b.links)
+    S, R, Lt, Mt = ops.get_pcfg_kernel().pcfg_viterbi(ob.to(DEV), links.to(DEV), b.output_length.to(DEV), 1)
+    So, Ro, Lo, Mo = oracle.pcfg_viterbi(ob.numpy(), links.numpy(), b.output_length.numpy())
+    assert np.array_equal(_bits(S.cpu().numpy()), _bits(So))
+    np.testing.assert_array_equal(R.cpu().numpy(), Ro)
+    np.testing.assert_array_equal(Lt.cpu().numpy(), Lo)
+    np.testing.assert_array_equal(Mt.cpu().numpy(), Mo)
+    assert (np.isfinite(So).sum() > 100)
+
+
 @pytest.mark.parametrize("name", ["ref_viterbi_ragged.npz", "ref_viterbi_mid.npz"])
-def test_viterbi_against_reference_golden(ops, name):
+def test_viterbi_against_reference_golden(vit_kernel, ops, name):
     g = _g(name)
     S, R, Lt, Mt = ops.get_pcfg_kernel().pcfg_viterbi(_cu(g["ob_lprob"]), _cu(g["links"]), _cu(g["output_length"]), 1)
     assert np.array_equal(_bits(S.cpu().numpy()), _bits(g["S"]))
