@@ -197,8 +197,8 @@ def run_ours(a):
             flush.fill_(1)
             s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             s.record()
-            if e2e:
-                step.load(*host)
+            if e2e:  # over the copy stream, transitions last: they are still in flight while the projection runs
+                step.load(*host, overlap=True)
             out = step.run()
             if is_loss and world > 1:
                 dist.all_reduce(out[0])

@@ -12,9 +12,14 @@ Each step is what the reference's Python does around the custom operators for on
   back-trace on the device.
 
 A step launches a handful of small-to-medium kernels whose device time (~1 ms at training-batch size) is
-of the order of the host cost of enqueueing them through Python, so it is captured once into a CUDA graph
+of the order of the host cost of enqueueing them through Python, so it is captured once into CUDA graphs
 and replayed.  Inputs live in static device buffers; ``load`` copies a new batch into them (from pinned
-host memory or from device tensors) on the current stream.
+host memory or from device tensors).
+
+A step has two stages, each its own graph: the projection, which reads the decoder states, and the
+dynamic program, which reads the transition matrix (the larger input).  ``load(..., overlap=True)`` sends
+the inputs over a copy stream in that order and ``run`` lets each stage wait only for its own inputs, so
+that the transitions are still in flight from the host while the projection runs.
 """
 import torch
 
@@ -35,45 +40,97 @@ class _GraphedStep:
         self.links = torch.full((B, L, 2, L), float("-inf"), dtype=torch.float32, device=dev)
         self.output_length = torch.full((B,), 2, dtype=torch.int64, device=dev)
         self.use_graph = use_graph
-        self.graph = None
+        self.graphs = None
+        self.mid = None
         self.out = None
         self.kernel = ops.get_pcfg_kernel()
+        self.copy_stream = None
+        self._ev_stage1 = self._ev_stage2 = self._ev_done = None
+        self._pending = False
 
     def _inputs(self):
         return [self.hidden, self.links, self.output_length]
 
+    def _stage2_inputs(self):
+        """The inputs only the second stage reads (sent last by an overlapped load)."""
+        return [self.links]
+
     def input_bytes(self):
         return sum(t.numel() * t.element_size() for t in self._inputs())
 
-    def load(self, *tensors):
-        """Copies one batch into the static buffers (async on the current stream); same order as ``_inputs``."""
+    def load(self, *tensors, overlap=False):
+        """Copies one batch into the static buffers; same order as ``_inputs``.
+
+        overlap=False: asynchronous copies on the current stream.  overlap=True: on the step's copy stream,
+        first-stage inputs first; the next ``run`` orders each stage after the arrival of its own inputs and
+        the copies after the previous ``run`` (which still reads the buffers)."""
         bufs = self._inputs()
         if len(tensors) != len(bufs):
             raise RuntimeError(f"expected {len(bufs)} tensors")
-        for dst, src in zip(bufs, tensors):
-            dst.copy_(src, non_blocking=True)
+        if not overlap:
+            for dst, src in zip(bufs, tensors):
+                dst.copy_(src, non_blocking=True)
+            return
+        if self.copy_stream is None:
+            self.copy_stream = torch.cuda.Stream(self.device)
+            self._ev_stage1, self._ev_stage2, self._ev_done = (torch.cuda.Event() for _ in range(3))
+        cur = torch.cuda.current_stream(self.device)
+        self._ev_done.record(cur)  # everything queued so far, the previous run included
+        late = {id(t) for t in self._stage2_inputs()}
+        with torch.cuda.stream(self.copy_stream):
+            self.copy_stream.wait_event(self._ev_done)
+            for dst, src in zip(bufs, tensors):
+                if id(dst) not in late:
+                    dst.copy_(src, non_blocking=True)
+            self._ev_stage1.record(self.copy_stream)
+            for dst, src in zip(bufs, tensors):
+                if id(dst) in late:
+                    dst.copy_(src, non_blocking=True)
+            self._ev_stage2.record(self.copy_stream)
+        self._pending = True
 
-    def _body(self):
+    def _stage1(self):
         raise NotImplementedError
 
+    def _stage2(self, mid):
+        raise NotImplementedError
+
+    def _capture(self):
+        # warm up on a side stream (lazy module loading, allocator), then capture one graph per stage
+        s = torch.cuda.Stream(self.device)
+        s.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(s):
+            for _ in range(2):
+                self._stage2(self._stage1())
+        torch.cuda.current_stream(self.device).wait_stream(s)
+        torch.cuda.synchronize(self.device)
+        g1, g2 = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g1):
+            self.mid = self._stage1()
+        with torch.cuda.graph(g2, pool=g1.pool()):
+            self.out = self._stage2(self.mid)
+        self.graphs = (g1, g2)
+
     def run(self):
-        if not self.use_graph:
-            self.out = self._body()
-            return self.out
-        if self.graph is None:
-            # warm up on a side stream (lazy module loading, allocator), then capture
-            s = torch.cuda.Stream(self.device)
-            s.wait_stream(torch.cuda.current_stream(self.device))
-            with torch.cuda.stream(s):
-                for _ in range(2):
-                    self._body()
-            torch.cuda.current_stream(self.device).wait_stream(s)
-            torch.cuda.synchronize(self.device)
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
-                self.out = self._body()
-            self.graph = g
-        self.graph.replay()
+        cur = torch.cuda.current_stream(self.device)
+        pending, self._pending = self._pending, False
+        if self.use_graph and self.graphs is None:
+            if pending:  # capture must not race the copies
+                cur.wait_event(self._ev_stage2)
+                pending = False
+            self._capture()
+        if pending:
+            cur.wait_event(self._ev_stage1)
+        if self.use_graph:
+            self.graphs[0].replay()
+        else:
+            self.mid = self._stage1()
+        if pending:
+            cur.wait_event(self._ev_stage2)
+        if self.use_graph:
+            self.graphs[1].replay()
+        else:
+            self.out = self._stage2(self.mid)
         return self.out
 
 
@@ -95,10 +152,12 @@ class LossStep(_GraphedStep):
     def _inputs(self):
         return [self.hidden, self.links, self.output_length, self.targets, self.target_length]
 
-    def _body(self):
-        k = self.kernel
-        em = k.proj_logsoftmax_gather(self.hidden, self.weight, self.targets, self.output_length, self.target_length)
-        loss, mg, lg = k.pcfg_loss_fwd_bwd(em["match"], self.links, self.output_length, self.target_length)
+    def _stage1(self):
+        return self.kernel.proj_logsoftmax_gather(self.hidden, self.weight, self.targets, self.output_length,
+                                                  self.target_length)
+
+    def _stage2(self, em):
+        loss, mg, lg = self.kernel.pcfg_loss_fwd_bwd(em["match"], self.links, self.output_length, self.target_length)
         stats = sharding.local_loss_stats(loss, self.target_length)
         return stats, mg, lg, loss
 
@@ -109,10 +168,12 @@ class GlanceStep(LossStep):
     ``run()`` returns (tree [B,L] i64, sentence log-likelihood [B], arg-max tokens [B,L] i64)."""
     kernels_per_step = 5  # proj_prepare, proj, proj_merge, loss_fwd, best_tree
 
-    def _body(self):
+    def _stage1(self):
+        return self.kernel.proj_logsoftmax_gather(self.hidden, self.weight, self.targets, self.output_length,
+                                                  self.target_length, want_max=True)
+
+    def _stage2(self, em):
         k = self.kernel
-        em = k.proj_logsoftmax_gather(self.hidden, self.weight, self.targets, self.output_length, self.target_length,
-                                      want_max=True)
         S, _ = k.pcfg_loss(em["match"], self.links, self.output_length, self.target_length, 1, want_c=False)
         tree = k.pcfg_best_tree(S, None, em["match"], self.links, self.output_length, self.target_length, 1)
         return tree, S[:, 0, 0], em["argmax"]
@@ -132,9 +193,12 @@ class DecodeStep(_GraphedStep):
         # length penalty of the model: scores / arange(L // 4) ** beta (models/...pcfg.py:488-492)
         self.penalty = (torch.arange(L // 4, device=self.device) ** beta).to(torch.float32).unsqueeze(0)
 
-    def _body(self):
+    def _stage1(self):
+        return self.kernel.proj_logsoftmax_gather(self.hidden, self.weight, None, self.output_length, None,
+                                                  want_max=True)
+
+    def _stage2(self, em):
         k = self.kernel
-        em = k.proj_logsoftmax_gather(self.hidden, self.weight, None, self.output_length, None, want_max=True)
         S, R, Lt, Mt = k.pcfg_viterbi(em["max_lprob"], self.links, self.output_length, 1)
         scores = S[:, 1, :] / self.penalty
         scores = torch.where(torch.isnan(scores), torch.full_like(scores, float("-inf")), scores)

@@ -515,10 +515,12 @@ def test_loss_step_graph_replay_matches_eager(pkg, ops, syn):
     weight = b1.weight.to(DEV)
     eager = runtime.LossStep(weight, w.batch, L, T, DEV, use_graph=False)
     graphed = runtime.LossStep(weight, w.batch, L, T, DEV, use_graph=True)
-    for b in (b1, b2, b1):  # the graph is captured on the first batch and replayed on the others
+    # the graphs are captured on the first batch and replayed on the others; the last two loads go over the
+    # copy stream, transitions last, each stage waiting for its own inputs only
+    for b, overlap in ((b1, False), (b2, False), (b1, True), (b2, True)):
         args = padded(b)
         eager.load(*args)
-        graphed.load(*[t.pin_memory() for t in args])
+        graphed.load(*[t.pin_memory() for t in args], overlap=overlap)
         se, mge, lge, le = [t.clone() for t in eager.run()]
         sg, mgg, lgg, lg_ = graphed.run()
         torch.cuda.synchronize()
@@ -527,7 +529,7 @@ def test_loss_step_graph_replay_matches_eager(pkg, ops, syn):
         assert torch.equal(mgg, mge) and torch.equal(lgg, lge)
         # and against the torch reference of the projection feeding the oracle
         hid, lk, ol, tg, tl = args
-        lp = torch.log_softmax(hid.float() @ b1.weight.float().t(), -1)  # the step object holds b1's projection matrix
+        lp = torch.log_softmax(hid.float() @ b1.weight.float().t(), -1)  # the step objects hold b1's projection matrix
         match = lp.gather(2, tg[:, None, :].expand(-1, L, -1)).contiguous()
         syn.eos_mask_(match, ol, tl)
         So, _ = oracle.pcfg_loss(match.numpy(), lk.numpy(), ol.numpy(), tl.numpy())
