@@ -36,6 +36,9 @@ sys.path.insert(0, ROOT)
 import __graft_entry__ as entry  # noqa: E402
 
 UNIT = "sentences/s"
+# DRAM traffic of one proj_kernel launch as ncu measured it (bytes read + written), per workload captured.
+NCU_TRAFFIC_BYTES = {"train_batch": 52.3e6 + 0.6e6}
+
 METRICS = {"loss": "pcfg_loss_fwd_bwd_sentences_per_s", "glance": "pcfg_best_tree_sentences_per_s",
            "viterbi": "pcfg_viterbi_decode_sentences_per_s"}
 
@@ -281,10 +284,13 @@ def run_ours(a):
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": tot[1] / a.steps},
         "gpu_launches": step.kernels_per_step * a.steps,
-        "roofline": {"bound": "tensor", "kernel": "proj_kernel (timed with its helper launches: row compaction, "
+        "roofline": {"bound": "tensor", "kernel": "proj_kernel (timed with its helper launches: row compaction + "
                                                   "target sort, partial merge)",
                      "achieved": achieved, "peak": pk["tflops"], "unit": "TFLOP/s", "frac": achieved / pk["tflops"],
-                     "peak_source": pk["source"] + " (burst bf16 GEMM)", "traffic": None,
+                     "peak_source": pk["source"] + " (burst bf16 GEMM)", "traffic": NCU_TRAFFIC_BYTES.get(a.workload),
+                     "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of this "
+                                       "workload (profiles/proj_kernel_train_batch.md)"
+                     if a.workload in NCU_TRAFFIC_BYTES else None,
                      "ms_per_launch": proj_avg_s * 1e3, "flops_per_launch": alg["proj_flops"]},
         "dp": {"ms_per_step": rest_ms, "algorithmic_bytes": alg["dp_bytes"],
                "achieved_gbs": alg["dp_bytes"] / (rest_ms / 1e3) / 1e9, "hbm_peak_gbs": pk["gbs"],
