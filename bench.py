@@ -157,6 +157,9 @@ def make_step(runtime, batch, weight, dev, use_graph):
         cls = runtime.GlanceStep if kind == "glance" else runtime.LossStep
         step = cls(weight, batch.B, batch.L, batch.T, dev, use_graph=use_graph)
         host = (batch.hidden, batch.links, batch.output_length, batch.targets, batch.target_length)
+        if kind == "glance":  # decoder input of the first pass: <unk> on the graph nodes, padding after them
+            pos = torch.arange(batch.L)[None, :]
+            host += (torch.where(pos < batch.output_length[:, None], 3, 1),)
     return step, [t.contiguous().pin_memory() for t in host]
 
 

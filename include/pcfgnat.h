@@ -147,6 +147,32 @@ int pcfgnat_proj_logsoftmax_gather(const void *hidden, const void *weight, const
                                    int V, int H, float *match, float *max_lprob, int64_t *argmax, float *lse,
                                    void *workspace, size_t workspace_bytes, int *status, void *stream);
 
+/* The three numbers the criterion's scalar loss is formed from, in one launch
+ * (fs_plugins/criterions/nat_pcfg_loss.py:117-135: sentences whose loss is infinite or NaN are
+ * counted and left out, the others are divided by their target length):
+ *   stats[0] = sum_b loss[b] / max(target_length[b], 1) over valid sentences,
+ *   stats[1] = B,   stats[2] = number of invalid sentences.
+ * The caller sums stats over ranks and forms -stats[0] / stats[1]. */
+int pcfgnat_loss_stats(const float *sentence_loss, const int64_t *target_length, int B, float *stats, void *stream);
+
+/* Glancing sampler between the two decoder passes, strategy "number-random"
+ * (fs_plugins/criterions/nat_pcfg_loss.py:216-267), one launch instead of ~15 torch operators.
+ * path [B][L] int64: aligned target position of each graph node (the best tree), negative = none;
+ * pred_tokens [B][L], tgt_tokens [B][T], prev_output_tokens [B][L] int64; noise [B][L] f32: the
+ * caller's standard-normal draws (the reference's torch.randn).  Outputs:
+ *   matchmask [B][T][L] u8   1 where node l is aligned to target t
+ *   oracle    [B][L]   int64 target token of the node's alignment (position 0 when unaligned)
+ *   same_num  [B]      int64 aligned nodes whose predicted token already equals the oracle
+ *   glance_num[B]      int64 (long)((n_b - same_num) * context_p + 0.5) in float32
+ *   keep      [B][L]   u8    the glance_num nodes with the largest noise among the aligned ones
+ *                            (ties and glance_num beyond the aligned count as torch.sort + >= give)
+ *   glat_prev [B][L]   int64 prev_output_tokens with the oracle token at the kept nodes
+ * The reference's second draw (rand < keep_prob, keep_prob in {0,1}) selects the same mask. */
+int pcfgnat_glance_select(const int64_t *path, const int64_t *pred_tokens, const int64_t *tgt_tokens,
+                          const int64_t *prev_output_tokens, const int64_t *target_length, const float *noise,
+                          float context_p, int B, int L, int T, uint8_t *matchmask, int64_t *oracle,
+                          int64_t *same_num, int64_t *glance_num, uint8_t *keep, int64_t *glat_prev, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

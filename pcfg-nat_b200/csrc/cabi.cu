@@ -180,4 +180,22 @@ int pcfgnat_proj_logsoftmax_gather(const void *hidden, const void *weight, const
                        lse, workspace, workspace_bytes, status, static_cast<cudaStream_t>(stream));
 }
 
+int pcfgnat_loss_stats(const float *sentence_loss, const int64_t *target_length, int B, float *stats, void *stream) {
+    if (B < 0 || !stats || (B && (!sentence_loss || !target_length))) return PCFGNAT_ERR_INVALID_ARGUMENT;
+    return launch_loss_stats(sentence_loss, target_length, B, stats, static_cast<cudaStream_t>(stream));
+}
+
+int pcfgnat_glance_select(const int64_t *path, const int64_t *pred_tokens, const int64_t *tgt_tokens,
+                          const int64_t *prev_output_tokens, const int64_t *target_length, const float *noise,
+                          float context_p, int B, int L, int T, uint8_t *matchmask, int64_t *oracle,
+                          int64_t *same_num, int64_t *glance_num, uint8_t *keep, int64_t *glat_prev, void *stream) {
+    if (B < 0 || L < 1 || T < 1) return PCFGNAT_ERR_INVALID_ARGUMENT;
+    if (B && (!path || !pred_tokens || !tgt_tokens || !prev_output_tokens || !target_length || !noise || !matchmask ||
+              !oracle || !same_num || !glance_num || !keep || !glat_prev))
+        return PCFGNAT_ERR_INVALID_ARGUMENT;
+    return launch_glance_select(path, pred_tokens, tgt_tokens, prev_output_tokens, target_length, noise, context_p, B,
+                                L, T, matchmask, oracle, same_num, glance_num, keep, glat_prev,
+                                static_cast<cudaStream_t>(stream));
+}
+
 }  // extern "C"

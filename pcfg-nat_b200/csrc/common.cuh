@@ -75,6 +75,12 @@ enum DpKernel { kDpCluster = 0, kDpBalanced = 1, kDpRows = 2, kDpAuto = 3 };
 DpKernel dp_kernel_choice();
 bool cluster_kernels_pay(int B, int L, int T);
 
+int launch_loss_stats(const float *loss, const int64_t *tl, int B, float *stats, cudaStream_t st);
+int launch_glance_select(const int64_t *path, const int64_t *pred, const int64_t *tgt, const int64_t *prev,
+                         const int64_t *tl, const float *noise, float context_p, int B, int L, int T,
+                         uint8_t *matchmask, int64_t *oracle, int64_t *same_num, int64_t *glance_num, uint8_t *keep,
+                         int64_t *glat_prev, cudaStream_t st);
+
 size_t proj_workspace_bytes(int B, int L, int T, int V);
 int launch_proj(const void *hidden, const void *weight, const int64_t *targets, const int64_t *ol, const int64_t *tl,
                 int B, int L, int T, int V, int H, float *match, float *max_lprob, int64_t *argmax, float *lse,

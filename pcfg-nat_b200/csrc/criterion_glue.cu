@@ -1,0 +1,125 @@
+// The small reductions and selections the criterion does around the DP operators, one launch each
+// instead of a dozen element-wise torch kernels:
+//
+//  * loss_stats_kernel — the three numbers the scalar loss is formed from
+//    (fs_plugins/criterions/nat_pcfg_loss.py:117-135: invalid sentences zeroed, per-sentence loss divided by
+//    its target length, batch mean; the division by the sentence count is left to the caller so that the
+//    three numbers can be summed over ranks first);
+//  * glance_select_kernel — the glancing sampler between the two decoder passes
+//    (nat_pcfg_loss.py:216-267, strategy "number-random"): alignment -> match mask, oracle tokens, number of
+//    already-correct predictions, the glance_nums positions with the largest noise, and the decoder input
+//    with the oracle tokens revealed at those positions.
+#include "common.cuh"
+
+namespace pcfgnat {
+
+namespace {
+
+__device__ __forceinline__ float block_sum(float v, float *scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    __syncthreads();  // scratch may still be read from a previous call
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float t = 0.f;
+    for (int i = 0; i < n_warps; i++) t += scratch[i];  // same order in every thread: deterministic
+    return t;
+}
+
+// stats[0] = sum over valid sentences of loss_b / max(n_b, 1); stats[1] = B; stats[2] = invalid sentences
+// (loss_b infinite or NaN).
+__global__ void loss_stats_kernel(const float *__restrict__ loss, const int64_t *__restrict__ tl, int B, float *stats) {
+    __shared__ float scratch[32];
+    float s = 0.f, bad = 0.f;
+    for (int b = threadIdx.x; b < B; b += blockDim.x) {
+        const float v = loss[b];
+        if (isinf(v) || isnan(v)) {
+            bad += 1.f;
+        } else {
+            const int64_t n = tl[b];
+            s += v / (float)(n < 1 ? 1 : n);
+        }
+    }
+    s = block_sum(s, scratch);
+    bad = block_sum(bad, scratch);
+    if (threadIdx.x == 0) {
+        stats[0] = s;
+        stats[1] = (float)B;
+        stats[2] = bad;
+    }
+}
+
+// One block per sentence.  path[l] = aligned target position of graph node l, or < 0.
+//   aligned[l]   = path[l] >= 0                                   (taken before the range check below)
+//   p            = path[l] if 0 <= path[l] < T else -1
+//   matchmask[b][t][l] = (p == t)
+//   oracle[l]    = tgt[b][max(p, 0)]
+//   same         = #{l : pred[l] == oracle[l] and aligned[l]}
+//   k            = (long)((n_b - same) * context_p + 0.5)          (float32 arithmetic, as torch does it)
+//   keep[l]      = noise'[l] >= (k-th largest of noise')           noise' = noise, -100 where not aligned
+//                = fewer than k entries of noise' are strictly larger than noise'[l];   nothing if k == 0,
+//                  and k < 0 (never the case for a real alignment) acts as k = 1
+//   glat_prev[l] = keep[l] ? oracle[l] : prev[l]
+// The reference then draws rand < keep_prob with keep_prob in {0, 1}: the same mask, so no second draw.
+__global__ void glance_select_kernel(const int64_t *__restrict__ path, const int64_t *__restrict__ pred,
+                                     const int64_t *__restrict__ tgt, const int64_t *__restrict__ prev,
+                                     const int64_t *__restrict__ tl, const float *__restrict__ noise, float context_p,
+                                     int L, int T, uint8_t *matchmask, int64_t *oracle, int64_t *same_num,
+                                     int64_t *glance_num, uint8_t *keep, int64_t *glat_prev) {
+    extern __shared__ float sm_noise[];  // [L]
+    __shared__ float scratch[32];
+    const int b = blockIdx.x;
+    const int64_t *pb = path + (size_t)b * L;
+    float same = 0.f;
+    for (int l = threadIdx.x; l < L; l += blockDim.x) {
+        const int64_t raw = pb[l];
+        const bool aligned = raw >= 0;
+        const int p = (raw >= 0 && raw < T) ? (int)raw : -1;
+        const int64_t o = tgt[(size_t)b * T + (p < 0 ? 0 : p)];
+        oracle[(size_t)b * L + l] = o;
+        if (aligned && pred[(size_t)b * L + l] == o) same += 1.f;
+        sm_noise[l] = aligned ? noise[(size_t)b * L + l] : -100.f;
+    }
+    for (int i = threadIdx.x; i < T * L; i += blockDim.x) {
+        const int t = i / L, l = i - t * L;
+        matchmask[(size_t)b * T * L + i] = pb[l] == t;
+    }
+    same = block_sum(same, scratch);  // exact: a count below 2^24; its barriers also publish sm_noise
+    const int64_t n = tl[b];
+    const int64_t same_i = (int64_t)same;
+    const int64_t k = (int64_t)((float)(n - same_i) * context_p + 0.5f);
+    if (threadIdx.x == 0) {
+        same_num[b] = same_i;
+        glance_num[b] = k;
+    }
+    for (int l = threadIdx.x; l < L; l += blockDim.x) {
+        const float mine = sm_noise[l];
+        int larger = 0;
+        for (int j = 0; j < L; j++) larger += sm_noise[j] > mine;
+        const bool kp = k != 0 && larger < (k < 1 ? 1 : k);  // a negative k indexes the sorted list at 0, as torch's clip does
+        keep[(size_t)b * L + l] = kp;
+        glat_prev[(size_t)b * L + l] = kp ? oracle[(size_t)b * L + l] : prev[(size_t)b * L + l];
+    }
+}
+
+}  // namespace
+
+int launch_loss_stats(const float *loss, const int64_t *tl, int B, float *stats, cudaStream_t st) {
+    loss_stats_kernel<<<1, 256, 0, st>>>(loss, tl, B, stats);
+    return cuda_rc(cudaGetLastError());
+}
+
+int launch_glance_select(const int64_t *path, const int64_t *pred, const int64_t *tgt, const int64_t *prev,
+                         const int64_t *tl, const float *noise, float context_p, int B, int L, int T,
+                         uint8_t *matchmask, int64_t *oracle, int64_t *same_num, int64_t *glance_num, uint8_t *keep,
+                         int64_t *glat_prev, cudaStream_t st) {
+    if (B == 0) return PCFGNAT_OK;
+    const size_t smem = (size_t)L * sizeof(float);
+    if (smem > 48 * 1024 && ensure_dynamic_smem(glance_select_kernel, smem) != cudaSuccess) return PCFGNAT_ERR_TOO_LARGE;
+    glance_select_kernel<<<B, 256, smem, st>>>(path, pred, tgt, prev, tl, noise, context_p, L, T, matchmask, oracle,
+                                               same_num, glance_num, keep, glat_prev);
+    return cuda_rc(cudaGetLastError());
+}
+
+}  // namespace pcfgnat

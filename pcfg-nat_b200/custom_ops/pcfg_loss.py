@@ -352,6 +352,64 @@ class _Kernel:
         return out[:, :maxlen].to(dtype=torch.float32, device=pred_length.device)
 
 
+    @staticmethod
+    def loss_stats(sentence_loss, target_length):
+        """float32 [3] = [sum_b loss_b / n_b over valid sentences, sentences, invalid sentences]: what the
+        criterion's scalar is formed from (nat_pcfg_loss.py:117-135), in one launch."""
+        _require_cuda()
+        loss = _f32_cuda(sentence_loss, "sentence_loss", 1)
+        tl = _lengths(target_length, "target_length", loss.shape[0], loss.device)
+        with torch.cuda.device(loss.device):
+            stats = torch.empty((3,), dtype=torch.float32, device=loss.device)
+            rc = _cabi.lib().pcfgnat_loss_stats(loss.data_ptr(), tl.data_ptr(), loss.shape[0], stats.data_ptr(),
+                                                _stream(loss.device))
+        _cabi.check(rc, "pcfgnat_loss_stats")
+        return stats
+
+    @staticmethod
+    def glance_select(path, pred_tokens, tgt_tokens, prev_output_tokens, target_length, noise, context_p):
+        """The glancing sampler of the criterion (nat_pcfg_loss.py:216-267, strategy "number-random") in one
+        launch.  ``noise`` holds the caller's standard-normal draws.  Returns a dict with matchmask [B,T,L] bool,
+        oracle [B,L], same_num [B], glance_num [B], keep_word_mask [B,L] bool, glat_prev_output_tokens [B,L]."""
+        _require_cuda()
+        dev = path.device
+        if not path.is_cuda or path.dim() != 2:
+            raise RuntimeError("path must be a CUDA tensor [batch, prelen]")
+        B, L = path.shape
+
+        def i64(t, name, shape):
+            if t.device != dev or t.dtype != torch.int64 or tuple(t.shape) != shape:
+                raise RuntimeError(f"{name} must be an int64 tensor of shape {shape} on {dev}")
+            return t.contiguous()
+
+        if tgt_tokens.dim() != 2 or tgt_tokens.shape[0] != B:
+            raise RuntimeError("tgt_tokens must be [batch, tarlen]")
+        T = tgt_tokens.shape[1]
+        path = i64(path, "path", (B, L))
+        pred = i64(pred_tokens, "pred_tokens", (B, L))
+        tgt = i64(tgt_tokens, "tgt_tokens", (B, T))
+        prev = i64(prev_output_tokens, "prev_output_tokens", (B, L))
+        tl = _lengths(target_length, "target_length", B, dev)
+        if noise.device != dev or noise.dtype != torch.float32 or tuple(noise.shape) != (B, L):
+            raise RuntimeError(f"noise must be a float32 tensor of shape {(B, L)} on {dev}")
+        noise = noise.contiguous()
+        with torch.cuda.device(dev):
+            matchmask = torch.empty((B, T, L), dtype=torch.bool, device=dev)
+            keep = torch.empty((B, L), dtype=torch.bool, device=dev)
+            oracle = torch.empty((B, L), dtype=torch.int64, device=dev)
+            glat_prev = torch.empty((B, L), dtype=torch.int64, device=dev)
+            same_num = torch.empty((B,), dtype=torch.int64, device=dev)
+            glance_num = torch.empty((B,), dtype=torch.int64, device=dev)
+            rc = _cabi.lib().pcfgnat_glance_select(path.data_ptr(), pred.data_ptr(), tgt.data_ptr(), prev.data_ptr(),
+                                                   tl.data_ptr(), noise.data_ptr(), float(context_p), B, L, T,
+                                                   matchmask.data_ptr(), oracle.data_ptr(), same_num.data_ptr(),
+                                                   glance_num.data_ptr(), keep.data_ptr(), glat_prev.data_ptr(),
+                                                   _stream(dev))
+        _cabi.check(rc, "pcfgnat_glance_select")
+        return {"matchmask": matchmask, "oracle": oracle, "same_num": same_num, "glance_num": glance_num,
+                "keep_word_mask": keep, "glat_prev_output_tokens": glat_prev}
+
+
 def get_pcfg_kernel():
     """The extension object of the reference loader (pcfg_loss.py:18-47); nothing is JIT-compiled here."""
     global _kernel_shim

@@ -141,7 +141,7 @@ class LossStep(_GraphedStep):
     target_length [B].  ``run()`` returns (stats[3] f32 = [sum_b S_b/n_b, sentences, invalid],
     match_all_grad, links_grad, sentence_loss); static outputs, overwritten by the next ``run()``.
     """
-    kernels_per_step = 6  # proj_prepare, proj, proj_merge, loss_fwd, outside, grad
+    kernels_per_step = 7  # proj_prepare, proj, proj_merge, loss_fwd, outside, grad, loss_stats
 
     def __init__(self, weight, B, L, T, device, use_graph=True):
         super().__init__(weight, B, L, device, use_graph)
@@ -163,10 +163,22 @@ class LossStep(_GraphedStep):
 
 
 class GlanceStep(LossStep):
-    """projection (emissions + arg-max tokens) -> inside table -> best tree.
+    """projection (emissions + arg-max tokens) -> inside table -> best tree -> glancing sampler.
 
-    ``run()`` returns (tree [B,L] i64, sentence log-likelihood [B], arg-max tokens [B,L] i64)."""
-    kernels_per_step = 5  # proj_prepare, proj, proj_merge, loss_fwd, best_tree
+    Inputs (``load`` order): those of ``LossStep`` and prev_output_tokens [B,L] int64.  ``run()`` returns
+    (tree [B,L] i64, sentence log-likelihood [B], arg-max tokens [B,L] i64, sampler outputs: the dict of
+    ``glance_select`` — match mask, oracle tokens, kept positions, decoder input of the second pass).  The
+    sampler's normal draws are made inside the step into ``self.noise``."""
+    kernels_per_step = 6  # proj_prepare, proj, proj_merge, loss_fwd, best_tree, glance_select
+
+    def __init__(self, weight, B, L, T, device, use_graph=True, context_p=0.5):
+        super().__init__(weight, B, L, T, device, use_graph)
+        self.context_p = float(context_p)
+        self.prev_output_tokens = torch.ones((B, L), dtype=torch.int64, device=self.device)
+        self.noise = torch.zeros((B, L), dtype=torch.float32, device=self.device)
+
+    def _inputs(self):
+        return super()._inputs() + [self.prev_output_tokens]
 
     def _stage1(self):
         return self.kernel.proj_logsoftmax_gather(self.hidden, self.weight, self.targets, self.output_length,
@@ -176,7 +188,10 @@ class GlanceStep(LossStep):
         k = self.kernel
         S, _ = k.pcfg_loss(em["match"], self.links, self.output_length, self.target_length, 1, want_c=False)
         tree = k.pcfg_best_tree(S, None, em["match"], self.links, self.output_length, self.target_length, 1)
-        return tree, S[:, 0, 0], em["argmax"]
+        self.noise.normal_()
+        glance = k.glance_select(tree, em["argmax"], self.targets, self.prev_output_tokens, self.target_length,
+                                 self.noise, self.context_p)
+        return tree, S[:, 0, 0], em["argmax"], glance
 
 
 class DecodeStep(_GraphedStep):

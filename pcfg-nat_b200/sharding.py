@@ -38,6 +38,11 @@ def shard_sentences(costs: Sequence[float], world_size: int) -> List[List[int]]:
 def local_loss_stats(sentence_loss: torch.Tensor, target_length: torch.Tensor) -> torch.Tensor:
     """[sum_b S_b / n_b over valid sentences, sentences, invalid sentences] as a float32 vector
     on the loss's device."""
+    if sentence_loss.is_cuda:  # one launch of the library's kernel (it raises if the library is missing)
+        from .custom_ops import pcfg_loss as ops
+
+        return ops.get_pcfg_kernel().loss_stats(sentence_loss, target_length)
+    # host tensors: the multi-process logic of the CPU tests
     invalid = torch.isinf(sentence_loss) | torch.isnan(sentence_loss)
     s = torch.where(invalid, torch.zeros_like(sentence_loss), sentence_loss)
     tl = target_length.to(device=sentence_loss.device, dtype=sentence_loss.dtype).clamp(min=1)

@@ -73,3 +73,26 @@ def loss_bruteforce(match, links, m, n):
         return NEG
     mx = max(total)
     return mx + math.log(sum(math.exp(x - mx) for x in total))
+
+
+def glance_select(path, pred_tokens, tgt_tokens, prev_output_tokens, target_length, noise, context_p):
+    """Torch restatement of the glancing sampler, strategy "number-random"
+    (fs_plugins/criterions/nat_pcfg_loss.py:216-267), with the normal draws given."""
+    import torch
+
+    B, L = path.shape
+    T = tgt_tokens.shape[1]
+    path = path.clone()
+    aligned = path >= 0
+    path[(path + 1 >= T + 1) | (path + 1 < 0)] = -1
+    matchmask = torch.zeros(B, T + 1, L, dtype=torch.bool).scatter_(1, path.unsqueeze(1) + 1, True)[:, 1:]
+    oracle = tgt_tokens.gather(-1, path.clip(min=0))
+    same_num = ((pred_tokens == oracle) & aligned).sum(1)
+    prob = noise.clone().masked_fill_(~aligned, -100)
+    glance_nums = ((target_length - same_num) * context_p + 0.5).to(torch.long)
+    thresh = prob.sort(descending=True)[0].gather(-1, (glance_nums - 1).clip(min=0).unsqueeze(-1)).squeeze(-1)
+    thresh = thresh.masked_fill(glance_nums == 0, 100)
+    keep = prob >= thresh.unsqueeze(-1)
+    glat_prev = prev_output_tokens.masked_fill(keep, 0) + oracle.masked_fill(~keep, 0)
+    return {"matchmask": matchmask, "oracle": oracle, "same_num": same_num, "glance_num": glance_nums,
+            "keep_word_mask": keep, "glat_prev_output_tokens": glat_prev}

@@ -13,6 +13,7 @@ import pytest
 import torch
 
 import oracle
+import _pyref as pyref
 from conftest import golden_path
 
 pytestmark = pytest.mark.gpu
@@ -538,6 +539,37 @@ def test_loss_step_graph_replay_matches_eager(pkg, ops, syn):
         assert abs(float(-se[0]) - float(want)) < 1e-3 * abs(float(want)) and int(se[1]) == w.batch
 
 
+def test_loss_stats_and_glance_select(ops):
+    k = ops.get_pcfg_kernel()
+    g = torch.Generator().manual_seed(11)
+    loss = -torch.rand(37, generator=g) * 50
+    loss[3], loss[20], loss[21] = float("-inf"), float("nan"), float("inf")
+    tl = torch.randint(1, 40, (37,), generator=g)
+    tl[5] = 0  # clamped to 1
+    stats = k.loss_stats(loss.to(DEV), tl.to(DEV)).cpu()
+    ok = torch.isfinite(loss)
+    want = (loss[ok].double() / tl[ok].clamp(min=1).double()).sum()
+    assert abs(float(stats[0]) - float(want)) < 1e-5 * abs(float(want))
+    assert stats[1] == 37 and stats[2] == 3
+    assert k.loss_stats(loss[:0].to(DEV), tl[:0].to(DEV)).cpu().tolist() == [0.0, 0.0, 0.0]
+
+    for B, L, T, p, seed in ((5, 40, 12, 0.5, 0), (3, 300, 90, 0.3, 1), (2, 16, 5, 1.0, 2), (4, 24, 7, 0.0, 3)):
+        g = torch.Generator().manual_seed(seed)
+        tlen = torch.randint(2, T + 1, (B,), generator=g)
+        path = torch.randint(-1, T + 2, (B, L), generator=g)  # also positions past the target (dropped from the mask)
+        path[torch.rand(B, L, generator=g) < 0.4] = -1
+        tgt = torch.randint(4, 50, (B, T), generator=g)
+        pred = torch.randint(4, 50, (B, L), generator=g)
+        pred = torch.where(torch.rand(B, L, generator=g) < 0.5, tgt.gather(-1, path.clip(0, T - 1)), pred)
+        prev = torch.randint(1, 4, (B, L), generator=g)
+        noise = torch.randn(B, L, generator=g)
+        noise[0, : L // 2] = noise[0, 0]  # ties at the threshold
+        got = k.glance_select(path.to(DEV), pred.to(DEV), tgt.to(DEV), prev.to(DEV), tlen.to(DEV), noise.to(DEV), p)
+        want = pyref.glance_select(path, pred, tgt, prev, tlen, noise, p)
+        for key, val in want.items():
+            assert torch.equal(got[key].cpu(), val), (key, B, L, T)
+
+
 def test_decode_and_glance_steps_match_operator_chain(pkg, ops, syn):
     """The graph-replayed decode / glancing steps give what the individual operators give."""
     import importlib
@@ -572,11 +604,18 @@ def test_decode_and_glance_steps_match_operator_chain(pkg, ops, syn):
 
     wg = syn.Workload("gl", batch=4, vocab=2000, hidden=64, src_min=6, src_max=20, kind="glance")
     g = syn.make_batch(wg, seed=5)
-    gs = runtime.GlanceStep(g.weight.to(DEV), g.B, g.L, g.T, DEV)
+    gs = runtime.GlanceStep(g.weight.to(DEV), g.B, g.L, g.T, DEV, context_p=0.5)
+    prev = torch.where(torch.arange(g.L)[None, :] < g.output_length[:, None], 3, 1)
     gs.load(g.hidden.pin_memory(), g.links.pin_memory(), g.output_length.pin_memory(), g.targets.pin_memory(),
-            g.target_length.pin_memory())
+            g.target_length.pin_memory(), prev.pin_memory())
     for _ in range(2):
-        tree, ll, am = [t.clone() for t in gs.run()]
+        tree, ll, am, glance = gs.run()
+        tree, ll, am = tree.clone(), ll.clone(), am.clone()
+    noise = gs.noise.cpu()
+    assert noise.std() > 0.5  # drawn inside the replayed graph
+    want = pyref.glance_select(tree.cpu(), am.cpu(), g.targets, prev, g.target_length, noise, 0.5)
+    for key, val in want.items():
+        assert torch.equal(glance[key].cpu(), val), key
     em = ops.proj_logsoftmax_gather(g.hidden.to(DEV), g.weight.to(DEV), g.targets.to(DEV), g.output_length.to(DEV),
                                     g.target_length.to(DEV), want_max=True)
     tree2, ll2 = ops.cuda_pcfg_best_tree(em["match"], g.links.to(DEV), g.output_length.to(DEV), g.target_length.to(DEV))
