@@ -51,7 +51,8 @@ def parse():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="train_batch")
     ap.add_argument("--seed", type=int, default=0)
-    ap.add_argument("--cpu-sample", type=int, default=8, help="sentences in the CPU-baseline sample")
+    ap.add_argument("--cpu-sample", type=int, default=0,
+                    help="sentences per pass of the CPU baseline (0 = the whole batch of the workload)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true",
                     help="enqueue the step kernel by kernel instead of replaying a CUDA graph")
@@ -308,68 +309,100 @@ def run_ours(a):
         dist.destroy_process_group()
 
 
-def cpu_baseline(a, batch=None, steps=1):
-    """The same step on the host cores: the C oracle (a port of the reference kernels; the reference has
-    no CPU implementation of this path) with OpenMP over sentences, and torch's CPU GEMM for the
-    projection, on a bounded sample of the workload's sentences."""
+def cpu_pass(sub, kind, syn):
+    """One pass of the step over the sentences of ``sub`` on the host cores; returns (seconds, what ran)."""
     import numpy as np
 
+    import oracle
+
+    n = sub.B
+    t0 = time.perf_counter()
+    logits = sub.hidden.float().reshape(-1, sub.hidden.shape[-1]) @ sub.weight.float().t()
+    lp = torch.log_softmax(logits, -1).view(n, sub.L, -1)
+    l_np, ol = sub.links.numpy(), sub.output_length.numpy()
+    if kind == "viterbi":
+        ob, tok = lp.max(-1)
+        S, R, Lt, Mt = oracle.pcfg_viterbi(ob.numpy(), l_np, ol)
+        sc = torch.from_numpy(S[:, 1, :]) / torch.arange(sub.L // 4).unsqueeze(0)
+        sc = torch.where(torch.isnan(sc), torch.full_like(sc, float("-inf")), sc)
+        pred = sc[:, 1:].max(-1)[1] + 1
+        oracle.viterbi_decoding(pred.numpy(), ol, Lt, R, Mt, tok.numpy(), sub.left_tree_mask.long().numpy(), 1)
+        what = "torch CPU fp32 GEMM + log-softmax + max, C oracle Viterbi tables + back-trace"
+    else:
+        match = lp.gather(2, sub.targets[:, None, :].expand(-1, sub.L, -1)).contiguous()
+        syn.eos_mask_(match, sub.output_length, sub.target_length)
+        m_np, tl = match.numpy(), sub.target_length.numpy()
+        S, C = oracle.pcfg_loss(m_np, l_np, ol, tl)
+        if kind == "glance":
+            oracle.pcfg_best_tree(S, C, m_np, l_np, ol, tl)
+            what = "torch CPU fp32 GEMM + log-softmax + gather, C oracle inside pass + best tree"
+        else:
+            oracle.pcfg_loss_backward(np.ones(n, np.float32), S, C, m_np, l_np, ol, tl)
+            what = "torch CPU fp32 GEMM + log-softmax + gather, C oracle loss forward + backward"
+    return time.perf_counter() - t0, what
+
+
+def cpu_sample(a, batch):
     import oracle
 
     pkg = entry.load_package()
     syn = pkg.synthetic
     if batch is None:
         batch = syn.make_batch(a.workload, seed=a.seed)
-    kind = batch.workload.kind
-    n = min(a.cpu_sample, batch.B)
+    n = batch.B if a.cpu_sample <= 0 else min(a.cpu_sample, batch.B)
     sub = batch.select(list(range(n)))
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
     oracle.lib()
-    best = None
-    for _ in range(max(steps, 1)):
-        t0 = time.perf_counter()
-        logits = sub.hidden.float().reshape(-1, sub.hidden.shape[-1]) @ sub.weight.float().t()
-        lp = torch.log_softmax(logits, -1).view(n, sub.L, -1)
-        l_np, ol = sub.links.numpy(), sub.output_length.numpy()
-        if kind == "viterbi":
-            ob, tok = lp.max(-1)
-            S, R, Lt, Mt = oracle.pcfg_viterbi(ob.numpy(), l_np, ol)
-            sc = torch.from_numpy(S[:, 1, :]) / torch.arange(sub.L // 4).unsqueeze(0)
-            sc = torch.where(torch.isnan(sc), torch.full_like(sc, float("-inf")), sc)
-            pred = sc[:, 1:].max(-1)[1] + 1
-            oracle.viterbi_decoding(pred.numpy(), ol, Lt, R, Mt, tok.numpy(), sub.left_tree_mask.long().numpy(), 1)
-            what = "torch CPU fp32 GEMM + log-softmax + max, C oracle Viterbi tables + back-trace"
-        else:
-            match = lp.gather(2, sub.targets[:, None, :].expand(-1, sub.L, -1)).contiguous()
-            syn.eos_mask_(match, sub.output_length, sub.target_length)
-            m_np, tl = match.numpy(), sub.target_length.numpy()
-            S, C = oracle.pcfg_loss(m_np, l_np, ol, tl)
-            if kind == "glance":
-                oracle.pcfg_best_tree(S, C, m_np, l_np, ol, tl)
-                what = "torch CPU fp32 GEMM + log-softmax + gather, C oracle inside pass + best tree"
-            else:
-                oracle.pcfg_loss_backward(np.ones(n, np.float32), S, C, m_np, l_np, ol, tl)
-                what = "torch CPU fp32 GEMM + log-softmax + gather, C oracle loss forward + backward"
-        dt = time.perf_counter() - t0
-        best = dt if best is None else min(best, dt)
-    return {"value": n / best, "unit": UNIT, "cores": cores, "kind": "port",
-            "sample": f"first {n} of {batch.B} sentences of {a.workload} ({what}); best of {max(steps, 1)} passes, "
-                      f"{best:.3f} s per pass"}
+    return syn, batch, sub, n, cores
+
+
+def cpu_baseline(a, batch=None, budget_s=10.0):
+    """The same step on the host cores: the C oracle (a port of the reference kernels; the reference has
+    no CPU implementation of this path) with OpenMP over sentences, and torch's CPU GEMM for the
+    projection.  One warm-up pass, then passes over the sample until ``budget_s`` seconds are spent."""
+    syn, batch, sub, n, cores = cpu_sample(a, batch)
+    kind = batch.workload.kind
+    cpu_pass(sub, kind, syn)
+    times, what = [], ""
+    while len(times) < 2 or (sum(times) < budget_s and len(times) < 200):
+        dt, what = cpu_pass(sub, kind, syn)
+        times.append(dt)
+    med = sorted(times)[len(times) // 2]
+    return {"value": n / med, "unit": UNIT, "cores": cores, "kind": "port",
+            "sample": f"{n} of {batch.B} sentences of {a.workload} per pass ({what}); median of {len(times)} passes "
+                      f"after 1 warm-up pass, {med:.3f} s per pass, {sum(times):.1f} s in all"}
 
 
 def run_reference(a):
+    """The reference arm: the path's CPU implementation (the oracle port: the reference itself has none) on
+    all host cores, W warm-up passes and K timed passes over the workload's batch (a pass = a step; the number
+    of timed passes is cut so that the run stays within about two minutes)."""
     rank = int(os.environ.get("RANK", 0))
     if rank != 0:
         return
-    pkg = entry.load_package()
-    kind = pkg.synthetic.WORKLOADS[a.workload].kind
-    cb = cpu_baseline(a, None, steps=max(1, min(a.steps, 3)))
-    line = {"impl": "reference", "metric": METRICS[kind], "value": cb["value"], "unit": UNIT, "n_gpus": a.gpus,
-            "steps": a.steps, "warmup": a.warmup, "ms_per_step": None, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "f32 on the CPU", "data": "synthetic",
-            "config": {"workload": a.workload}, "cpu_baseline": cb,
-            "e2e": {"value": cb["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    syn, batch, sub, n, cores = cpu_sample(a, None)
+    kind = batch.workload.kind
+    for _ in range(max(1, min(a.warmup, 3))):
+        cpu_pass(sub, kind, syn)
+    times, what = [], ""
+    while len(times) < max(a.steps, 1) and (len(times) < 2 or sum(times) < 120.0):
+        dt, what = cpu_pass(sub, kind, syn)
+        times.append(dt)
+    mean = sum(times) / len(times)
+    value = n / mean
+    cb = {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
+          "sample": f"{n} of {batch.B} sentences of {a.workload} per step ({what}); {len(times)} timed steps of "
+                    f"{a.steps} asked, {mean:.3f} s per step"}
+    line = {"impl": "reference", "metric": METRICS[kind], "value": value, "unit": UNIT, "n_gpus": a.gpus,
+            "steps": len(times), "warmup": a.warmup, "ms_per_step": mean * 1e3, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32 on the CPU", "data": "synthetic",
+            "config": {"workload": a.workload, "sentences_per_gpu": batch.B, "graph_len_max": batch.L,
+                       "target_len_max": batch.T, "vocab": int(batch.weight.shape[0]),
+                       "hidden": int(batch.weight.shape[1]), "left_tree_layer": 1,
+                       "parallelism": "host cores of rank 0 only"},
+            "cpu_baseline": cb,
+            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
     print(json.dumps(line), flush=True)
 
