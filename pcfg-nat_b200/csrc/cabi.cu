@@ -38,6 +38,22 @@ cudaError_t ensure_dynamic_smem_for(const void *kernel, size_t bytes) {
     return e;
 }
 
+bool exact_order_forced() {
+    const char *v = getenv("PCFGNAT_EXACT_ORDER");
+    return v && v[0] && v[0] != '0';
+}
+
+// Inside pass of the fused forward + backward: the table stays inside the library, so the free-order kernel
+// may build it unless the caller asked for the reference's order or forced a kernel family.
+int launch_loss_fwd_internal(const float *match_all, const float *links, const int64_t *ol, const int64_t *tl, int B,
+                             int L, int T, float *S, float *loss, int *status, cudaStream_t st) {
+    if (!exact_order_forced() && dp_kernel_choice() == kDpAuto) {
+        const int rc = launch_loss_fwd_fast(match_all, links, ol, tl, B, L, T, S, loss, status, st);
+        if (rc != PCFGNAT_ERR_UNSUPPORTED) return rc;
+    }
+    return launch_loss_fwd(match_all, links, ol, tl, B, L, T, S, nullptr, loss, status, st);
+}
+
 DpKernel dp_kernel_choice() {
     const char *v = getenv("PCFGNAT_DP_KERNEL");
     if (v && v[0] == 'r') return kDpRows;
@@ -115,7 +131,7 @@ int pcfgnat_loss_fwd_bwd(const float *match_all, const float *links, const int64
     float *S = static_cast<float *>(workspace);
     float *G = reinterpret_cast<float *>(static_cast<char *>(workspace) + need / 2);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    int rc = launch_loss_fwd(match_all, links, output_length, target_length, B, L, T, S, nullptr, loss, status, st);
+    int rc = launch_loss_fwd_internal(match_all, links, output_length, target_length, B, L, T, S, loss, status, st);
     if (rc) return rc;
     return launch_loss_bwd(nullptr, S, match_all, links, output_length, target_length, B, L, T, G, match_all_grad,
                            links_grad, status, st);

@@ -61,6 +61,11 @@ int launch_outside_balanced(const float *grad_output, const float *S, const floa
                             cudaStream_t st);
 int launch_loss_fwd_cluster(const float *match_all, const float *links, const int64_t *ol, const int64_t *tl, int B,
                             int L, int T, float *S, float *C, float *loss, int *status, cudaStream_t st);
+int launch_loss_fwd_fast(const float *match_all, const float *links, const int64_t *ol, const int64_t *tl, int B, int L,
+                         int T, float *S, float *loss, int *status, cudaStream_t st);
+int launch_loss_fwd_internal(const float *match_all, const float *links, const int64_t *ol, const int64_t *tl, int B,
+                             int L, int T, float *S, float *loss, int *status, cudaStream_t st);
+bool exact_order_forced();  // PCFGNAT_EXACT_ORDER=1: the fused forward + backward also keeps the reference's order
 int launch_outside_cluster(const float *grad_output, const float *S, const float *match_all, const float *links,
                            const int64_t *ol, const int64_t *tl, int B, int L, int T, float *G, int *status,
                            cudaStream_t st);

@@ -17,6 +17,12 @@
 // holds k = h + 8i, so after each trip i the eight lanes h = 0..7 of a virtual lane x are visited in
 // order with shuffles and every lane keeps the running sum of its virtual lane: the same additions
 // in the same order.  Lanes 0..3 are then combined (s0 + s2) + (s1 + s3).  max is order-free.
+//
+// inside_cluster_kernel<TRIPS > 0> is the inside pass for callers that never see the table (the fused
+// forward + backward): same layout, but every lane keeps its own partial sum of exponentials and the warp
+// is reduced with a shuffle tree, exp and log are the hardware ex2 / lg2 approximations.  The table then
+// agrees with the reference's to a few ulp instead of bit for bit, and the pass costs about a quarter of
+// the instructions.
 #include <cooperative_groups.h>
 
 #include <cstdlib>
@@ -34,6 +40,17 @@ constexpr int kCWarps = kCThreads / 32;
 
 __device__ __forceinline__ float clean(float t) { return isnan(t) ? neg_inf() : t; }
 
+__device__ __forceinline__ float fast_ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float fast_lg2(float x) {
+    float y;
+    asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
@@ -48,6 +65,9 @@ __device__ __forceinline__ float warp_sum(float v) {
 // ---------------------------------------------------------------------------------------
 // inside pass
 // ---------------------------------------------------------------------------------------
+// TRIPS == 0: the reference's summation order (bit-exact table).  TRIPS > 0: free order, for chains of at
+// most 32 * TRIPS main nodes (a lane holds the terms of its TRIPS children in registers between the passes).
+template <int TRIPS>
 __global__ void __launch_bounds__(kCThreads, 1)
     inside_cluster_kernel(const float *__restrict__ match_all, const float *__restrict__ links,
                           const int64_t *__restrict__ ol, const int64_t *__restrict__ tl, int L, int T, float *S,
@@ -128,6 +148,34 @@ __global__ void __launch_bounds__(kCThreads, 1)
             const float ma1 = has_leaf ? __ldg(mat + (size_t)a * T + start + 1) : 0.f;
             const float ml = has_leaf ? __ldg(mat + (size_t)(a - 1) * T + start) : 0.f;
             const float *r0 = lk0 + r * lk_stride, *r1 = lk1 + r * lk_stride;
+            float res;
+            if constexpr (TRIPS > 0) {
+                constexpr float kLog2e = 1.4426950408889634f, kLn2 = 0.6931471805599453f;
+                float t0[TRIPS], t1[TRIPS];
+                float mx = neg_inf();
+#pragma unroll
+                for (int i = 0; i < TRIPS; i++) {
+                    const int ci = ai + lane + 32 * i;
+                    const bool in = ci < Mb;
+                    const int cc = in ? ci : ai;
+                    // fmaxf drops a NaN operand: the reference's NaN -> -inf cleaning
+                    const float a = fmaxf((r0[cc] + S1[cc]) + ma0, neg_inf());
+                    const float b = fmaxf(((r1[cc] + S2[cc]) + ml) + ma1, neg_inf());
+                    t0[i] = in ? a : neg_inf();
+                    t1[i] = (in && has_leaf) ? b : neg_inf();
+                    mx = fmaxf(mx, fmaxf(t0[i], t1[i]));
+                }
+                mx = warp_max(mx);
+                float sum = 0.f;
+                const float top = isinf(mx) ? 0.f : mx;
+#pragma unroll
+                for (int i = 0; i < TRIPS; i++) {  // the difference first: it is small, so its rounding error is too
+                    sum += fast_ex2((t0[i] - top) * kLog2e);  // ex2(-inf) = +0
+                    sum += fast_ex2((t1[i] - top) * kLog2e);
+                }
+                sum = warp_sum(sum);
+                res = isinf(mx) ? mx : fmaf(fast_lg2(sum), kLn2, mx);
+            } else {
             const int trips = (Mb - ai + 31) / 32;
             float mx = neg_inf();
             for (int i = 0; i < trips; i++) {
@@ -164,7 +212,8 @@ __global__ void __launch_bounds__(kCThreads, 1)
             sum += __shfl_down_sync(0xffffffffu, sum, 2, 4);  // lanes 0..3 hold the four virtual-lane sums
             sum += __shfl_down_sync(0xffffffffu, sum, 1, 4);
             sum = __shfl_sync(0xffffffffu, sum, 0);
-            const float res = isinf(mx) ? mx : logf(sum) + mx;
+            res = isinf(mx) ? mx : logf(sum) + mx;
+            }
             if (lane < NC) *cluster.map_shared_rank(S0 + ai, lane) = res;  // into every CTA's column
             if (lane == 0) own[r * W + start] = res;
         }
@@ -353,18 +402,36 @@ bool cluster_kernels_pay(int B, int L, int T) {
 
 // Both return PCFGNAT_ERR_UNSUPPORTED when the shape does not fit any cluster size (the caller then
 // uses the row-per-thread kernels that read links from global memory).
-int launch_loss_fwd_cluster(const float *match_all, const float *links, const int64_t *ol, const int64_t *tl, int B,
-                            int L, int T, float *S, float *C, float *loss, int *status, cudaStream_t st) {
+template <int TRIPS>
+int launch_inside(const float *match_all, const float *links, const int64_t *ol, const int64_t *tl, int B, int L, int T,
+                  float *S, float *C, float *loss, int *status, cudaStream_t st) {
     const int Mc = main_slots(L, 1), Lt = L - Mc;
     ClusterGeometry g = cluster_geometry(B, Mc, T + 2);
     for (; g.nc >= 1; g.nc /= 2) {  // fall back to smaller clusters if the GPU cannot co-schedule this size
         g.rows_cap = (Mc + g.nc - 1) / g.nc;
         g.smem_in = ((size_t)3 * g.cs + (size_t)2 * g.rows_cap * g.lk_stride + (size_t)g.rows_cap * (T + 2)) * sizeof(float);
         if (g.smem_in > (size_t)kSmemLimit - 1024) break;
-        int rc = launch_cluster(inside_cluster_kernel, B, g.nc, g.smem_in, st, match_all, links, ol, tl, L, T, S, C, loss,
-                                status, Mc, Lt, g.cs, g.rows_cap, g.lk_stride);
+        int rc = launch_cluster(inside_cluster_kernel<TRIPS>, B, g.nc, g.smem_in, st, match_all, links, ol, tl, L, T, S,
+                                C, loss, status, Mc, Lt, g.cs, g.rows_cap, g.lk_stride);
         if (rc != PCFGNAT_ERR_UNSUPPORTED) return rc;
     }
+    return PCFGNAT_ERR_UNSUPPORTED;
+}
+
+int launch_loss_fwd_cluster(const float *match_all, const float *links, const int64_t *ol, const int64_t *tl, int B,
+                            int L, int T, float *S, float *C, float *loss, int *status, cudaStream_t st) {
+    return launch_inside<0>(match_all, links, ol, tl, B, L, T, S, C, loss, status, st);
+}
+
+// Inside pass in free summation order (table equal to the reference's to a few ulp, not bit for bit): for
+// callers that use the table only to form the loss and the gradients.  PCFGNAT_ERR_UNSUPPORTED when the
+// shape does not fit (chains above 256 main nodes, or links beyond the cluster's shared memory).
+int launch_loss_fwd_fast(const float *match_all, const float *links, const int64_t *ol, const int64_t *tl, int B, int L,
+                         int T, float *S, float *loss, int *status, cudaStream_t st) {
+    const int Mc = main_slots(L, 1);
+    if (Mc <= 64) return launch_inside<2>(match_all, links, ol, tl, B, L, T, S, nullptr, loss, status, st);
+    if (Mc <= 128) return launch_inside<4>(match_all, links, ol, tl, B, L, T, S, nullptr, loss, status, st);
+    if (Mc <= 256) return launch_inside<8>(match_all, links, ol, tl, B, L, T, S, nullptr, loss, status, st);
     return PCFGNAT_ERR_UNSUPPORTED;
 }
 
