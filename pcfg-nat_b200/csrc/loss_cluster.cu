@@ -51,6 +51,13 @@ __device__ __forceinline__ float fast_lg2(float x) {
     return y;
 }
 
+// Warp maximum with the hardware integer reduction on an order-preserving image of the floats (no NaN).
+__device__ __forceinline__ float warp_max_redux(float v) {
+    unsigned u = __float_as_uint(v);
+    u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+    u = __reduce_max_sync(0xffffffffu, u);
+    return __uint_as_float((u & 0x80000000u) ? (u ^ 0x80000000u) : ~u);
+}
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
@@ -65,6 +72,38 @@ __device__ __forceinline__ float warp_sum(float v) {
 // ---------------------------------------------------------------------------------------
 // inside pass
 // ---------------------------------------------------------------------------------------
+// One node of the inside pass in free summation order; TR trips of 32 children cover the node's children.
+template <int TR>
+__device__ __forceinline__ float inside_node_free(const float *r0, const float *r1, const float *S1, const float *S2,
+                                                  int ai, int Mb, int lane, bool has_leaf, float ma0, float ma1,
+                                                  float ml) {
+    constexpr float kLog2e = 1.4426950408889634f, kLn2 = 0.6931471805599453f;
+    float t0[TR], t1[TR];
+    float mx = neg_inf();
+#pragma unroll
+    for (int i = 0; i < TR; i++) {
+        const int ci = ai + lane + 32 * i;
+        const bool in = ci < Mb;
+        const int cc = in ? ci : ai;
+        // fmaxf drops a NaN operand: the reference's NaN -> -inf cleaning
+        const float a = fmaxf((r0[cc] + S1[cc]) + ma0, neg_inf());
+        const float b = fmaxf(((r1[cc] + S2[cc]) + ml) + ma1, neg_inf());
+        t0[i] = in ? a : neg_inf();
+        t1[i] = (in && has_leaf) ? b : neg_inf();
+        mx = fmaxf(mx, fmaxf(t0[i], t1[i]));
+    }
+    mx = warp_max_redux(mx);
+    if (isinf(mx)) return mx;  // warp-uniform
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < TR; i++) {  // the difference first: it is small, so its rounding error is too
+        sum += fast_ex2((t0[i] - mx) * kLog2e);  // ex2(-inf) = +0
+        sum += fast_ex2((t1[i] - mx) * kLog2e);
+    }
+    sum = warp_sum(sum);
+    return fmaf(fast_lg2(sum), kLn2, mx);
+}
+
 // TRIPS == 0: the reference's summation order (bit-exact table).  TRIPS > 0: free order, for chains of at
 // most 32 * TRIPS main nodes (a lane holds the terms of its TRIPS children in registers between the passes).
 template <int TRIPS>
@@ -117,6 +156,16 @@ __global__ void __launch_bounds__(kCThreads, 1)
     // S entries of this CTA's nodes, flushed to global memory after the last step: a global store
     // inside the step loop would make every cluster barrier (a release) wait for it to reach L2
     float *own = lk1 + (size_t)rows_cap * lk_stride;  // [rows_cap][W]
+    // free-order variant: emissions of this CTA's nodes and of their leaves, so that a step reads them from
+    // shared memory instead of chasing three global addresses per node
+    float *em0 = own + (size_t)rows_cap * W, *eml = em0 + (size_t)rows_cap * W;  // [rows_cap][W] each
+    if constexpr (TRIPS > 0) {
+        for (int i = tid; i < my_rows * T; i += kCThreads) {
+            const int r = i / T, t = i - r * T, a = 2 * (crank + NC * r) + 1;
+            em0[r * W + t] = __ldg(mat + (size_t)a * T + t);
+            eml[r * W + t] = a >= 3 ? __ldg(mat + (size_t)(a - 1) * T + t) : 0.f;
+        }
+    }
 
     for (int r = warp; r < my_rows; r += kCWarps) {
         const int ai = crank + NC * r;
@@ -144,37 +193,29 @@ __global__ void __launch_bounds__(kCThreads, 1)
         for (int r = warp; r < my_rows; r += kCWarps) {
             const int ai = crank + NC * r, a = 2 * ai + 1;
             const bool has_leaf = a >= 3;
-            const float ma0 = __ldg(mat + (size_t)a * T + start);
-            const float ma1 = has_leaf ? __ldg(mat + (size_t)a * T + start + 1) : 0.f;
-            const float ml = has_leaf ? __ldg(mat + (size_t)(a - 1) * T + start) : 0.f;
+            float ma0, ma1, ml;
+            if constexpr (TRIPS > 0) {
+                ma0 = em0[r * W + start];
+                ma1 = has_leaf ? em0[r * W + start + 1] : 0.f;
+                ml = eml[r * W + start];  // 0 for the first node, which has no leaf
+            } else {
+                ma0 = __ldg(mat + (size_t)a * T + start);
+                ma1 = has_leaf ? __ldg(mat + (size_t)a * T + start + 1) : 0.f;
+                ml = has_leaf ? __ldg(mat + (size_t)(a - 1) * T + start) : 0.f;
+            }
             const float *r0 = lk0 + r * lk_stride, *r1 = lk1 + r * lk_stride;
             float res;
             if constexpr (TRIPS > 0) {
-                constexpr float kLog2e = 1.4426950408889634f, kLn2 = 0.6931471805599453f;
-                float t0[TRIPS], t1[TRIPS];
-                float mx = neg_inf();
-#pragma unroll
-                for (int i = 0; i < TRIPS; i++) {
-                    const int ci = ai + lane + 32 * i;
-                    const bool in = ci < Mb;
-                    const int cc = in ? ci : ai;
-                    // fmaxf drops a NaN operand: the reference's NaN -> -inf cleaning
-                    const float a = fmaxf((r0[cc] + S1[cc]) + ma0, neg_inf());
-                    const float b = fmaxf(((r1[cc] + S2[cc]) + ml) + ma1, neg_inf());
-                    t0[i] = in ? a : neg_inf();
-                    t1[i] = (in && has_leaf) ? b : neg_inf();
-                    mx = fmaxf(mx, fmaxf(t0[i], t1[i]));
+                // warp-uniform dispatch on the number of trips this node needs: each case is straight-line code
+                switch ((Mb - ai + 31) / 32) {
+                    case 1: res = inside_node_free<1>(r0, r1, S1, S2, ai, Mb, lane, has_leaf, ma0, ma1, ml); break;
+                    case 2: res = inside_node_free<2>(r0, r1, S1, S2, ai, Mb, lane, has_leaf, ma0, ma1, ml); break;
+                    case 3: res = inside_node_free<(TRIPS >= 4 ? 3 : TRIPS)>(r0, r1, S1, S2, ai, Mb, lane, has_leaf, ma0, ma1, ml); break;
+                    case 4: res = inside_node_free<(TRIPS >= 4 ? 4 : TRIPS)>(r0, r1, S1, S2, ai, Mb, lane, has_leaf, ma0, ma1, ml); break;
+                    case 5:
+                    case 6: res = inside_node_free<(TRIPS >= 8 ? 6 : TRIPS)>(r0, r1, S1, S2, ai, Mb, lane, has_leaf, ma0, ma1, ml); break;
+                    default: res = inside_node_free<TRIPS>(r0, r1, S1, S2, ai, Mb, lane, has_leaf, ma0, ma1, ml); break;
                 }
-                mx = warp_max(mx);
-                float sum = 0.f;
-                const float top = isinf(mx) ? 0.f : mx;
-#pragma unroll
-                for (int i = 0; i < TRIPS; i++) {  // the difference first: it is small, so its rounding error is too
-                    sum += fast_ex2((t0[i] - top) * kLog2e);  // ex2(-inf) = +0
-                    sum += fast_ex2((t1[i] - top) * kLog2e);
-                }
-                sum = warp_sum(sum);
-                res = isinf(mx) ? mx : fmaf(fast_lg2(sum), kLn2, mx);
             } else {
             const int trips = (Mb - ai + 31) / 32;
             float mx = neg_inf();
@@ -409,7 +450,8 @@ int launch_inside(const float *match_all, const float *links, const int64_t *ol,
     ClusterGeometry g = cluster_geometry(B, Mc, T + 2);
     for (; g.nc >= 1; g.nc /= 2) {  // fall back to smaller clusters if the GPU cannot co-schedule this size
         g.rows_cap = (Mc + g.nc - 1) / g.nc;
-        g.smem_in = ((size_t)3 * g.cs + (size_t)2 * g.rows_cap * g.lk_stride + (size_t)g.rows_cap * (T + 2)) * sizeof(float);
+        g.smem_in = ((size_t)3 * g.cs + (size_t)2 * g.rows_cap * g.lk_stride +
+                     (size_t)(TRIPS > 0 ? 3 : 1) * g.rows_cap * (T + 2)) * sizeof(float);
         if (g.smem_in > (size_t)kSmemLimit - 1024) break;
         int rc = launch_cluster(inside_cluster_kernel<TRIPS>, B, g.nc, g.smem_in, st, match_all, links, ol, tl, L, T, S,
                                 C, loss, status, Mc, Lt, g.cs, g.rows_cap, g.lk_stride);
