@@ -373,8 +373,8 @@ __global__ void __launch_bounds__(kBalThreads, 1)
             const float g = ga[ai];
             float w0 = 0.f, w1 = 0.f;
             if (g != 0.f) {
-                w0 = g * expf((lt0[p] + sc1[ci]) + q0[ai]);
-                w1 = g * expf((lt1[p] + sc2[ci]) + q1[ai]);
+                w0 = g * fast_exp((lt0[p] + sc1[ci]) + q0[ai]);
+                w1 = g * fast_exp((lt1[p] + sc2[ci]) + q1[ai]);
             }
             W0[p] = w0;
             W1[p] = w1;

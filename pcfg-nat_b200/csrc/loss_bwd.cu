@@ -116,8 +116,8 @@ __global__ void __launch_bounds__(kMaxRows *kLanes)
                                 l1 = __ldg(lkb + ((size_t)(2 * aa + 1) * 2 + 1) * L + c);
                             }
                             if (g != 0.f) {
-                                if (f1) p0[u] += g * expf((l0 + sc1) + q0[aa]);
-                                if (f2) p1[u] += g * expf((l1 + sc2) + q1[aa]);
+                                if (f1) p0[u] += g * fast_exp((l0 + sc1) + q0[aa]);
+                                if (f2) p1[u] += g * fast_exp((l1 + sc2) + q1[aa]);
                             }
                         }
                     }
@@ -206,8 +206,8 @@ __global__ void __launch_bounds__(kGradWarps * 32)
                         if (ci < Mb) {
                             float s2 = __ldg(Sb + (size_t)ci * W + s + 2);
                             if (on) {
-                                float w0 = isinf(s1[q]) ? 0.f : g * expf((l0[q] + s1[q]) + qq0);
-                                float w1 = isinf(s2) ? 0.f : g * expf((l1[q] + s2) + qq1);
+                                float w0 = isinf(s1[q]) ? 0.f : g * fast_exp((l0[q] + s1[q]) + qq0);
+                                float w1 = isinf(s2) ? 0.f : g * fast_exp((l1[q] + s2) + qq1);
                                 a0[q] += w0;
                                 a1[q] += w1;
                                 r0 += w0;

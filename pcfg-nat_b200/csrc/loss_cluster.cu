@@ -345,8 +345,8 @@ __global__ void __launch_bounds__(kCThreads, 1)
                 for (int ai = lane; ai < ci; ai += 32) {
                     const float g = ga[ai];
                     if (g != 0.f) {
-                        acc0 += g * expf((r0[ai] + sc1) + q0[ai]);
-                        acc1 += g * expf((r1[ai] + sc2) + q1[ai]);
+                        acc0 += g * fast_exp((r0[ai] + sc1) + q0[ai]);
+                        acc1 += g * fast_exp((r1[ai] + sc2) + q1[ai]);
                     }
                 }
             }
