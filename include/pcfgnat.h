@@ -173,6 +173,13 @@ int pcfgnat_glance_select(const int64_t *path, const int64_t *pred_tokens, const
                           float context_p, int B, int L, int T, uint8_t *matchmask, int64_t *oracle,
                           int64_t *same_num, int64_t *glance_num, uint8_t *keep, int64_t *glat_prev, void *stream);
 
+/* Copies the rows of a transition tensor that the kernels read — links[b][a][.][.] for main-chain nodes a
+ * (odd a at max_left == 1) — from src to dst, both [B][L][max_left+1][L] f32, either of them in host
+ * (preferably pinned) or device memory; asynchronous on `stream` (one strided cudaMemcpy2DAsync).  The other
+ * rows of dst are left as they are: a staging buffer filled with -inf once stays valid.  Host plumbing for
+ * callers that stage batches from host memory: it halves the bytes the largest input sends over PCIe. */
+int pcfgnat_copy_links_main_rows(void *dst, const void *src, int B, int L, int max_left, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -214,4 +214,22 @@ int pcfgnat_glance_select(const int64_t *path, const int64_t *pred_tokens, const
                                 static_cast<cudaStream_t>(stream));
 }
 
+int pcfgnat_copy_links_main_rows(void *dst, const void *src, int B, int L, int max_left, void *stream) {
+    if (max_left != 1) return PCFGNAT_ERR_UNSUPPORTED;
+    if (B < 0 || L < 1 || (B && (!dst || !src))) return PCFGNAT_ERR_INVALID_ARGUMENT;
+    if (B == 0) return PCFGNAT_OK;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const size_t row = (size_t)2 * L * sizeof(float);  // links[b][a]: (max_left + 1) x L
+    char *d = static_cast<char *>(dst);
+    const char *s = static_cast<const char *>(src);
+    if (L % 2 == 0)  // odd rows of the flat [B * L] row list are the odd nodes of every sentence
+        return cuda_rc(cudaMemcpy2DAsync(d + row, 2 * row, s + row, 2 * row, row, (size_t)B * L / 2, cudaMemcpyDefault, st));
+    for (int b = 0; b < B; b++) {
+        const size_t off = (size_t)b * L * row + row;
+        cudaError_t e = cudaMemcpy2DAsync(d + off, 2 * row, s + off, 2 * row, row, (size_t)L / 2, cudaMemcpyDefault, st);
+        if (e != cudaSuccess) return PCFGNAT_ERR_CUDA;
+    }
+    return PCFGNAT_OK;
+}
+
 }  // extern "C"

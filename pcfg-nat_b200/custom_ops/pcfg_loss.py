@@ -353,6 +353,23 @@ class _Kernel:
 
 
     @staticmethod
+    def copy_links_main_rows(dst, src):
+        """Copies the rows of the transition tensor the kernels read (main-chain nodes: odd a) from ``src``
+        (pinned host or device, [B, L, 2, L] f32 contiguous) into the CUDA tensor ``dst`` of the same shape,
+        asynchronously on the current stream; the other rows of ``dst`` keep their contents."""
+        _require_cuda()
+        if not dst.is_cuda or dst.dtype != torch.float32 or dst.dim() != 4 or dst.shape[2] != 2:
+            raise RuntimeError("dst must be a float32 CUDA tensor [batch, prelen, 2, prelen]")
+        if src.dtype != torch.float32 or tuple(src.shape) != tuple(dst.shape):
+            raise RuntimeError("src must be a float32 tensor of dst's shape")
+        if not dst.is_contiguous() or not src.is_contiguous():
+            raise RuntimeError("dst and src must be contiguous")
+        B, L = dst.shape[0], dst.shape[1]
+        with torch.cuda.device(dst.device):
+            rc = _cabi.lib().pcfgnat_copy_links_main_rows(dst.data_ptr(), src.data_ptr(), B, L, 1, _stream(dst.device))
+        _cabi.check(rc, "pcfgnat_copy_links_main_rows")
+
+    @staticmethod
     def loss_stats(sentence_loss, target_length):
         """float32 [3] = [sum_b loss_b / n_b over valid sentences, sentences, invalid sentences]: what the
         criterion's scalar is formed from (nat_pcfg_loss.py:117-135), in one launch."""

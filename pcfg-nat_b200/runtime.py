@@ -56,7 +56,16 @@ class _GraphedStep:
         return [self.links]
 
     def input_bytes(self):
-        return sum(t.numel() * t.element_size() for t in self._inputs())
+        """Bytes one ``load`` moves: every input whole, except the transitions, of which only the rows of
+        main-chain nodes (every other row) are read by the kernels and therefore copied."""
+        return sum(t.numel() * t.element_size() // (2 if t is self.links else 1) for t in self._inputs())
+
+    def _copy_in(self, dst, src):
+        if dst is self.links and src.dtype == torch.float32 and src.is_contiguous() and dst.shape[1] % 2 == 0 \
+                and tuple(src.shape) == tuple(dst.shape):
+            self.kernel.copy_links_main_rows(dst, src)  # the other rows stay -inf, as the constructor left them
+        else:
+            dst.copy_(src, non_blocking=True)
 
     def load(self, *tensors, overlap=False):
         """Copies one batch into the static buffers; same order as ``_inputs``.
@@ -69,7 +78,7 @@ class _GraphedStep:
             raise RuntimeError(f"expected {len(bufs)} tensors")
         if not overlap:
             for dst, src in zip(bufs, tensors):
-                dst.copy_(src, non_blocking=True)
+                self._copy_in(dst, src)
             return
         if self.copy_stream is None:
             self.copy_stream = torch.cuda.Stream(self.device)
@@ -81,11 +90,11 @@ class _GraphedStep:
             self.copy_stream.wait_event(self._ev_done)
             for dst, src in zip(bufs, tensors):
                 if id(dst) not in late:
-                    dst.copy_(src, non_blocking=True)
+                    self._copy_in(dst, src)
             self._ev_stage1.record(self.copy_stream)
             for dst, src in zip(bufs, tensors):
                 if id(dst) in late:
-                    dst.copy_(src, non_blocking=True)
+                    self._copy_in(dst, src)
             self._ev_stage2.record(self.copy_stream)
         self._pending = True
 

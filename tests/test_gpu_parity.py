@@ -548,6 +548,19 @@ def test_loss_step_graph_replay_matches_eager(pkg, ops, syn):
         assert abs(float(-se[0]) - float(want)) < 1e-3 * abs(float(want)) and int(se[1]) == w.batch
 
 
+@pytest.mark.parametrize("L", [12, 9])
+def test_copy_links_main_rows(ops, L):
+    k = ops.get_pcfg_kernel()
+    g = torch.Generator().manual_seed(L)
+    src = torch.randn(3, L, 2, L, generator=g)
+    for s_ in (src.pin_memory(), src.to(DEV)):
+        dst = torch.full((3, L, 2, L), -7.0, device=DEV)
+        k.copy_links_main_rows(dst, s_)
+        torch.cuda.synchronize()
+        assert torch.equal(dst[:, 1::2].cpu(), src[:, 1::2])  # main-chain nodes
+        assert (dst[:, 0::2] == -7.0).all()  # rows no kernel reads keep their contents
+
+
 def test_loss_stats_and_glance_select(ops):
     k = ops.get_pcfg_kernel()
     g = torch.Generator().manual_seed(11)
