@@ -51,6 +51,8 @@ def parse():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="train_batch")
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--copy-chunks", type=int, default=2,
+                    help="sentence groups the end-to-end leg sends (and projects) the decoder states in")
     ap.add_argument("--cpu-sample", type=int, default=0,
                     help="sentences per pass of the CPU baseline (0 = the whole batch of the workload)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -147,16 +149,16 @@ def algorithmic(batch):
             "proj_flops_padded": 2.0 * batch.B * batch.L * H * V, "dp_bytes": dp}
 
 
-def make_step(runtime, batch, weight, dev, use_graph):
+def make_step(runtime, batch, weight, dev, use_graph, copy_chunks=2):
     """The public step object of the workload's kind and the host tensors it loads, in load() order."""
     kind = batch.workload.kind
     if kind == "viterbi":
         step = runtime.DecodeStep(weight, batch.B, batch.L, batch.left_tree_mask, dev, beta=1.0, pad_index=1,
-                                  use_graph=use_graph)
+                                  use_graph=use_graph, copy_chunks=copy_chunks)
         host = (batch.hidden, batch.links, batch.output_length)
     else:
         cls = runtime.GlanceStep if kind == "glance" else runtime.LossStep
-        step = cls(weight, batch.B, batch.L, batch.T, dev, use_graph=use_graph)
+        step = cls(weight, batch.B, batch.L, batch.T, dev, use_graph=use_graph, copy_chunks=copy_chunks)
         host = (batch.hidden, batch.links, batch.output_length, batch.targets, batch.target_length)
         if kind == "glance":  # decoder input of the first pass: <unk> on the graph nodes, padding after them
             pos = torch.arange(batch.L)[None, :]
@@ -189,7 +191,7 @@ def run_ours(a):
     kind = batch.workload.kind
     alg = algorithmic(batch)
     weight = batch.weight.to(dev)
-    step, host = make_step(runtime, batch, weight, dev, not a.no_graph)  # host: pinned copies for the end-to-end leg
+    step, host = make_step(runtime, batch, weight, dev, not a.no_graph, a.copy_chunks)  # host: pinned copies for the end-to-end leg
     step.load(*host)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)  # > 126 MB L2
     h2d = step.input_bytes()

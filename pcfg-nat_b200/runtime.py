@@ -19,7 +19,9 @@ host memory or from device tensors).
 A step has two stages, each its own graph: the projection, which reads the decoder states, and the
 dynamic program, which reads the transition matrix (the larger input).  ``load(..., overlap=True)`` sends
 the inputs over a copy stream in that order and ``run`` lets each stage wait only for its own inputs, so
-that the transitions are still in flight from the host while the projection runs.
+that the transitions are still in flight from the host while the projection runs.  The decoder states
+themselves are sent in ``copy_chunks`` groups of sentences, each projected (by a graph of its own) as soon
+as it has landed, so that only the first group's copy is not hidden behind the tensor cores.
 """
 import torch
 
@@ -28,7 +30,7 @@ from .custom_ops import pcfg_loss as ops
 
 
 class _GraphedStep:
-    def __init__(self, weight, B, L, device, use_graph=True):
+    def __init__(self, weight, B, L, device, use_graph=True, copy_chunks=2):
         if weight.dtype != torch.float16 or not weight.is_cuda:
             raise RuntimeError("weight must be a float16 CUDA tensor [V, H]")
         self.device = torch.device(device)
@@ -47,6 +49,11 @@ class _GraphedStep:
         self.copy_stream = None
         self._ev_stage1 = self._ev_stage2 = self._ev_done = None
         self._pending = False
+        # sentence groups [b0, b1) of an overlapped load; chunking needs the graphs (it is a replay trick)
+        n = max(1, min(int(copy_chunks), B)) if use_graph else 1
+        self.chunks = [(B * i // n, B * (i + 1) // n) for i in range(n)]
+        self.chunk_graphs = None
+        self._ev_chunk = None
 
     def _inputs(self):
         return [self.hidden, self.links, self.output_length]
@@ -83,14 +90,19 @@ class _GraphedStep:
         if self.copy_stream is None:
             self.copy_stream = torch.cuda.Stream(self.device)
             self._ev_stage1, self._ev_stage2, self._ev_done = (torch.cuda.Event() for _ in range(3))
+            self._ev_chunk = [torch.cuda.Event() for _ in self.chunks]
         cur = torch.cuda.current_stream(self.device)
         self._ev_done.record(cur)  # everything queued so far, the previous run included
         late = {id(t) for t in self._stage2_inputs()}
         with torch.cuda.stream(self.copy_stream):
             self.copy_stream.wait_event(self._ev_done)
-            for dst, src in zip(bufs, tensors):
-                if id(dst) not in late:
+            for dst, src in zip(bufs, tensors):  # the small inputs first, then the states group by group
+                if id(dst) not in late and dst is not self.hidden:
                     self._copy_in(dst, src)
+            src_hidden = tensors[[id(t) for t in bufs].index(id(self.hidden))]
+            for (b0, b1), ev in zip(self.chunks, self._ev_chunk):
+                self.hidden[b0:b1].copy_(src_hidden[b0:b1], non_blocking=True)
+                ev.record(self.copy_stream)
             self._ev_stage1.record(self.copy_stream)
             for dst, src in zip(bufs, tensors):
                 if id(dst) in late:
@@ -98,7 +110,8 @@ class _GraphedStep:
             self._ev_stage2.record(self.copy_stream)
         self._pending = True
 
-    def _stage1(self):
+    def _stage1(self, b0=0, b1=None):
+        """The projection of sentences [b0, b1) (all of them by default): a dict of [b1 - b0, ...] tensors."""
         raise NotImplementedError
 
     def _stage2(self, mid):
@@ -119,6 +132,18 @@ class _GraphedStep:
         with torch.cuda.graph(g2, pool=g1.pool()):
             self.out = self._stage2(self.mid)
         self.graphs = (g1, g2)
+        self.chunk_graphs = []
+        if len(self.chunks) > 1:  # the first stage once more, group by group, writing into the same tensors
+            for b0, b1 in self.chunks:
+                with torch.cuda.stream(s):
+                    self._stage1(b0, b1)
+                torch.cuda.synchronize(self.device)
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, pool=g1.pool()):
+                    part = self._stage1(b0, b1)
+                    for key, val in part.items():
+                        self.mid[key][b0:b1].copy_(val)
+                self.chunk_graphs.append(g)
 
     def run(self):
         cur = torch.cuda.current_stream(self.device)
@@ -128,12 +153,17 @@ class _GraphedStep:
                 cur.wait_event(self._ev_stage2)
                 pending = False
             self._capture()
-        if pending:
-            cur.wait_event(self._ev_stage1)
-        if self.use_graph:
-            self.graphs[0].replay()
+        if pending and self.chunk_graphs:
+            for ev, g in zip(self._ev_chunk, self.chunk_graphs):
+                cur.wait_event(ev)
+                g.replay()
         else:
-            self.mid = self._stage1()
+            if pending:
+                cur.wait_event(self._ev_stage1)
+            if self.use_graph:
+                self.graphs[0].replay()
+            else:
+                self.mid = self._stage1()
         if pending:
             cur.wait_event(self._ev_stage2)
         if self.use_graph:
@@ -152,8 +182,8 @@ class LossStep(_GraphedStep):
     """
     kernels_per_step = 7  # proj_prepare, proj, proj_merge, loss_fwd, outside, grad, loss_stats
 
-    def __init__(self, weight, B, L, T, device, use_graph=True):
-        super().__init__(weight, B, L, device, use_graph)
+    def __init__(self, weight, B, L, T, device, use_graph=True, copy_chunks=2):
+        super().__init__(weight, B, L, device, use_graph, copy_chunks)
         self.T = T
         self.targets = torch.zeros((B, T), dtype=torch.int64, device=self.device)
         self.target_length = torch.ones((B,), dtype=torch.int64, device=self.device)
@@ -161,9 +191,9 @@ class LossStep(_GraphedStep):
     def _inputs(self):
         return [self.hidden, self.links, self.output_length, self.targets, self.target_length]
 
-    def _stage1(self):
-        return self.kernel.proj_logsoftmax_gather(self.hidden, self.weight, self.targets, self.output_length,
-                                                  self.target_length)
+    def _stage1(self, b0=0, b1=None):
+        return self.kernel.proj_logsoftmax_gather(self.hidden[b0:b1], self.weight, self.targets[b0:b1],
+                                                  self.output_length[b0:b1], self.target_length[b0:b1])
 
     def _stage2(self, em):
         loss, mg, lg = self.kernel.pcfg_loss_fwd_bwd(em["match"], self.links, self.output_length, self.target_length)
@@ -180,8 +210,8 @@ class GlanceStep(LossStep):
     sampler's normal draws are made inside the step into ``self.noise``."""
     kernels_per_step = 6  # proj_prepare, proj, proj_merge, loss_fwd, best_tree, glance_select
 
-    def __init__(self, weight, B, L, T, device, use_graph=True, context_p=0.5):
-        super().__init__(weight, B, L, T, device, use_graph)
+    def __init__(self, weight, B, L, T, device, use_graph=True, context_p=0.5, copy_chunks=2):
+        super().__init__(weight, B, L, T, device, use_graph, copy_chunks)
         self.context_p = float(context_p)
         self.prev_output_tokens = torch.ones((B, L), dtype=torch.int64, device=self.device)
         self.noise = torch.zeros((B, L), dtype=torch.float32, device=self.device)
@@ -189,9 +219,9 @@ class GlanceStep(LossStep):
     def _inputs(self):
         return super()._inputs() + [self.prev_output_tokens]
 
-    def _stage1(self):
-        return self.kernel.proj_logsoftmax_gather(self.hidden, self.weight, self.targets, self.output_length,
-                                                  self.target_length, want_max=True)
+    def _stage1(self, b0=0, b1=None):
+        return self.kernel.proj_logsoftmax_gather(self.hidden[b0:b1], self.weight, self.targets[b0:b1],
+                                                  self.output_length[b0:b1], self.target_length[b0:b1], want_max=True)
 
     def _stage2(self, em):
         k = self.kernel
@@ -210,15 +240,15 @@ class DecodeStep(_GraphedStep):
     ``pad_index``, count [B] i64, predicted length [B] i64)."""
     kernels_per_step = 5  # proj_prepare, proj, proj_merge, viterbi, backtrace
 
-    def __init__(self, weight, B, L, left_tree_mask, device, beta=1.0, pad_index=1, use_graph=True):
-        super().__init__(weight, B, L, device, use_graph)
+    def __init__(self, weight, B, L, left_tree_mask, device, beta=1.0, pad_index=1, use_graph=True, copy_chunks=2):
+        super().__init__(weight, B, L, device, use_graph, copy_chunks)
         self.mask = left_tree_mask.to(device=self.device, dtype=torch.int64).contiguous()
         self.pad_index = int(pad_index)
         # length penalty of the model: scores / arange(L // 4) ** beta (models/...pcfg.py:488-492)
         self.penalty = (torch.arange(L // 4, device=self.device) ** beta).to(torch.float32).unsqueeze(0)
 
-    def _stage1(self):
-        return self.kernel.proj_logsoftmax_gather(self.hidden, self.weight, None, self.output_length, None,
+    def _stage1(self, b0=0, b1=None):
+        return self.kernel.proj_logsoftmax_gather(self.hidden[b0:b1], self.weight, None, self.output_length[b0:b1], None,
                                                   want_max=True)
 
     def _stage2(self, em):
