@@ -113,6 +113,16 @@ int pcfgnat_viterbi_backtrace(const int64_t *pred_length, const int64_t *output_
                               const int64_t *left_tree_mask, int mask_dim, int64_t pad_index, int B, int L, int Q,
                               int cap, int64_t *out_tokens, int64_t *out_count, int *status, void *stream);
 
+/* Choice of the output length and back-trace in one launch: what the model does between the Viterbi
+ * tables and the token list (fs_plugins/models/glat_decomposed_with_link_two_hands_tri_pcfg.py:488-502):
+ *   scores = S[b][1][len] / penalty[len]  (penalty [Q] f32, the caller's arange(Q) ** beta), NaN -> -inf,
+ *   pred_length[b] = first maximum over len = 1 .. Q-1,
+ * then the walk of pcfgnat_viterbi_backtrace from that length.  S [B][L][Q] f32 from pcfgnat_viterbi. */
+int pcfgnat_viterbi_decode(const float *S, const float *penalty, const int64_t *output_length, const int64_t *Lt,
+                           const int64_t *R, const int64_t *Mt, const int64_t *tokens, const int64_t *left_tree_mask,
+                           int mask_dim, int64_t pad_index, int B, int L, int Q, int cap, int64_t *pred_length,
+                           int64_t *out_tokens, int64_t *out_count, int *status, void *stream);
+
 /* log-softmax over the vocabulary + gather of selected columns, optional in-place
  * softmax for the backward.  Replaces logsoftmax_gather()
  * (fs_plugins/custom_ops/logsoftmax_gather.cu:295-359, kernel :240-292).

@@ -21,6 +21,7 @@ SIGNATURES = {
     "pcfgnat_best_tree": (c_int, [c_void] * 5 + [c_int] * 4 + [c_void] * 3),
     "pcfgnat_viterbi": (c_int, [c_void] * 3 + [c_int] * 3 + [c_void] * 6),
     "pcfgnat_viterbi_backtrace": (c_int, [c_void] * 7 + [c_int, c_i64] + [c_int] * 4 + [c_void] * 4),
+    "pcfgnat_viterbi_decode": (c_int, [c_void] * 8 + [c_int, c_i64] + [c_int] * 4 + [c_void] * 5),
     "pcfgnat_logsoftmax_gather": (c_int, [c_void, c_int, c_void] + [c_i64] * 5 + [c_int] * 3 + [c_void] * 3),
     "pcfgnat_proj_workspace_bytes": (c_size, [c_int] * 4),
     "pcfgnat_proj_logsoftmax_gather": (c_int, [c_void] * 5 + [c_int] * 5 + [c_void] * 5 + [c_size] + [c_void] * 2),

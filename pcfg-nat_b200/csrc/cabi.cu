@@ -169,6 +169,18 @@ int pcfgnat_viterbi_backtrace(const int64_t *pred_length, const int64_t *output_
                             Q, cap, out_tokens, out_count, status, static_cast<cudaStream_t>(stream));
 }
 
+int pcfgnat_viterbi_decode(const float *S, const float *penalty, const int64_t *output_length, const int64_t *Lt,
+                           const int64_t *R, const int64_t *Mt, const int64_t *tokens, const int64_t *left_tree_mask,
+                           int mask_dim, int64_t pad_index, int B, int L, int Q, int cap, int64_t *pred_length,
+                           int64_t *out_tokens, int64_t *out_count, int *status, void *stream) {
+    if (B < 0 || L < 2 || Q < 2 || cap < 0 || mask_dim < 1) return PCFGNAT_ERR_INVALID_ARGUMENT;
+    if (B && (!S || !penalty || !output_length || !Lt || !R || !Mt || !tokens || !left_tree_mask || !pred_length ||
+              !out_count || (cap && !out_tokens)))
+        return PCFGNAT_ERR_INVALID_ARGUMENT;
+    return launch_viterbi_decode(S, penalty, output_length, Lt, R, Mt, tokens, left_tree_mask, mask_dim, pad_index, B, L,
+                                 Q, cap, pred_length, out_tokens, out_count, status, static_cast<cudaStream_t>(stream));
+}
+
 int pcfgnat_logsoftmax_gather(void *logits, int dtype, const int64_t *select_idx, int64_t stride_b, int64_t stride_l,
                               int64_t stride_s, int64_t rows, int64_t rows_per_batch, int V, int slen,
                               int require_gradient, float *selected, int *status, void *stream) {

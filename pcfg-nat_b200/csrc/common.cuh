@@ -58,6 +58,10 @@ int launch_viterbi(const float *ob, const float *links, const int64_t *ol, int B
 int launch_backtrace(const int64_t *pred, const int64_t *ol, const int64_t *Lt, const int64_t *R, const int64_t *Mt,
                      const int64_t *tokens, const int64_t *mask, int mask_dim, int64_t pad, int B, int L, int Q,
                      int cap, int64_t *out, int64_t *cnt, int *status, cudaStream_t st);
+int launch_viterbi_decode(const float *S, const float *penalty, const int64_t *ol, const int64_t *Lt, const int64_t *R,
+                          const int64_t *Mt, const int64_t *tokens, const int64_t *mask, int mask_dim, int64_t pad, int B,
+                          int L, int Q, int cap, int64_t *pred_out, int64_t *out, int64_t *cnt, int *status,
+                          cudaStream_t st);
 int launch_logsoftmax_gather(void *logits, int dtype, const int64_t *sel, int64_t sb, int64_t sl, int64_t ss,
                              int64_t rows, int64_t rpb, int V, int slen, int req_grad, float *selected, int *status,
                              cudaStream_t st);

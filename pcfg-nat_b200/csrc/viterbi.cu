@@ -236,17 +236,40 @@ __global__ void __launch_bounds__(kVitThreads)
     }
 }
 
-__global__ void backtrace_kernel(const int64_t *__restrict__ pred, const int64_t *__restrict__ ol,
+// With S and penalty given, the output length is chosen here first, as the model does it
+// (fs_plugins/models/glat_decomposed_with_link_two_hands_tri_pcfg.py:488-492): scores = S[b][1][len] /
+// penalty[len] with NaN -> -inf, first maximum over len = 1 .. Q-1; it is written to pred_out.
+__global__ void backtrace_kernel(const float *__restrict__ S, const float *__restrict__ penalty, int64_t *pred_out,
+                                 const int64_t *__restrict__ pred, const int64_t *__restrict__ ol,
                                  const int64_t *__restrict__ Lt, const int64_t *__restrict__ R,
                                  const int64_t *__restrict__ Mt, const int64_t *__restrict__ tokens,
                                  const int64_t *__restrict__ mask, int mask_dim, int64_t pad, int B, int L, int Q,
                                  int cap, int64_t *out, int64_t *cnt, int *status) {
     const int i = blockIdx.x;
-    if (i >= B || threadIdx.x != 0) return;
+    if (i >= B) return;
+    int chosen = 0;
+    if (S) {
+        const int lane = threadIdx.x;
+        const float *row = S + ((size_t)i * L + 1) * Q;
+        float best = neg_inf();
+        int key = INT_MAX;
+        for (int len = 1 + lane; len < Q; len += 32) {
+            float v = row[len] / penalty[len];
+            if (isnan(v)) v = neg_inf();
+            if (v > best || key == INT_MAX) {  // the first entry counts even at -inf: an all -inf row picks len = 1
+                best = v;
+                key = len;
+            }
+        }
+        warp_argmax(best, key, lane);
+        chosen = key == INT_MAX ? 1 : key;
+        if (lane == 0) pred_out[i] = chosen;
+    }
+    if (threadIdx.x != 0) return;
     constexpr int kStack = 32;  // the walk only stacks a node and its left spine: depth <= left_tree_layer + 2
     int stk_node[kStack], stk_len[kStack], stk_right[kStack], stk_mt[kStack];
     int sp = 0, count = 0;
-    int node = 1, len = (int)pred[i];
+    int node = 1, len = S ? chosen : (int)pred[i];
     const int max_h = (int)ol[i];
     int64_t last = -1;
     bool bad = false;
@@ -357,8 +380,18 @@ int launch_backtrace(const int64_t *pred, const int64_t *ol, const int64_t *Lt, 
                      const int64_t *tokens, const int64_t *mask, int mask_dim, int64_t pad, int B, int L, int Q,
                      int cap, int64_t *out, int64_t *cnt, int *status, cudaStream_t st) {
     if (B == 0) return PCFGNAT_OK;
-    backtrace_kernel<<<B, 32, 0, st>>>(pred, ol, Lt, R, Mt, tokens, mask, mask_dim, pad, B, L, Q, cap, out,
-                                                   cnt, status);
+    backtrace_kernel<<<B, 32, 0, st>>>(nullptr, nullptr, nullptr, pred, ol, Lt, R, Mt, tokens, mask, mask_dim, pad, B, L, Q,
+                                       cap, out, cnt, status);
+    return cuda_rc(cudaGetLastError());
+}
+
+int launch_viterbi_decode(const float *S, const float *penalty, const int64_t *ol, const int64_t *Lt, const int64_t *R,
+                          const int64_t *Mt, const int64_t *tokens, const int64_t *mask, int mask_dim, int64_t pad, int B,
+                          int L, int Q, int cap, int64_t *pred_out, int64_t *out, int64_t *cnt, int *status,
+                          cudaStream_t st) {
+    if (B == 0) return PCFGNAT_OK;
+    backtrace_kernel<<<B, 32, 0, st>>>(S, penalty, pred_out, nullptr, ol, Lt, R, Mt, tokens, mask, mask_dim, pad, B, L, Q,
+                                       cap, out, cnt, status);
     return cuda_rc(cudaGetLastError());
 }
 

@@ -342,6 +342,37 @@ class _Kernel:
         return out, cnt
 
     @staticmethod
+    def viterbi_decode_device(S, penalty, output_length, L_trace, R_trace, M_trace, unreduced_tokens, left_tree_mask,
+                              pad_index):
+        """Length choice + back-trace in one launch (models/...pcfg.py:488-502): scores = S[:, 1, :] / penalty,
+        NaN -> -inf, first maximum over lengths 1 .. Q-1, then the walk.  Returns (tokens [B, L] int64 padded
+        with pad_index, count [B] int64, pred_length [B] int64), no host sync."""
+        _require_cuda()
+        S = _f32_cuda(S, "S", 3)
+        dev = S.device
+        B, L, Q = S.shape
+        i64 = lambda t: t.to(device=dev, dtype=torch.int64).contiguous()
+        Lt, R, Mt = i64(L_trace), i64(R_trace), i64(M_trace)
+        if tuple(Lt.shape) != (B, L, Q) or R.shape != Lt.shape or Mt.shape != Lt.shape:
+            raise RuntimeError("L_trace, R_trace, M_trace must have S's shape [batch, prelen, prelen//4]")
+        pen = penalty.to(device=dev, dtype=torch.float32).reshape(-1).contiguous()
+        if pen.numel() != Q:
+            raise RuntimeError(f"penalty must hold {Q} values")
+        ol, tk, mk = i64(output_length), i64(unreduced_tokens), i64(left_tree_mask)
+        if ol.shape != (B,) or tk.shape != (B, L) or mk.dim() != 2 or mk.shape[0] != mk.shape[1]:
+            raise RuntimeError("output_length [batch], unreduced_tokens [batch, prelen], square left_tree_mask expected")
+        with torch.cuda.device(dev):
+            out = torch.empty((B, L), dtype=torch.int64, device=dev)
+            cnt = torch.empty((B,), dtype=torch.int64, device=dev)
+            pred = torch.empty((B,), dtype=torch.int64, device=dev)
+            rc = _cabi.lib().pcfgnat_viterbi_decode(S.data_ptr(), pen.data_ptr(), ol.data_ptr(), Lt.data_ptr(), R.data_ptr(),
+                                                    Mt.data_ptr(), tk.data_ptr(), mk.data_ptr(), mk.shape[0],
+                                                    int(pad_index), B, L, Q, L, pred.data_ptr(), out.data_ptr(),
+                                                    cnt.data_ptr(), _status_ptr(dev), _stream(dev))
+        _cabi.check(rc, "pcfgnat_viterbi_decode")
+        return out, cnt, pred
+
+    @staticmethod
     def viterbi_decoding(pred_length, output_length, L_trace, R_trace, M_trace, unreduced_tokens, left_tree_mask,
                          pad_index):
         """float32 [B, maxlen] padded with pad_index on the device of ``pred_length``;

@@ -254,9 +254,6 @@ class DecodeStep(_GraphedStep):
     def _stage2(self, em):
         k = self.kernel
         S, R, Lt, Mt = k.pcfg_viterbi(em["max_lprob"], self.links, self.output_length, 1)
-        scores = S[:, 1, :] / self.penalty
-        scores = torch.where(torch.isnan(scores), torch.full_like(scores, float("-inf")), scores)
-        pred = scores[:, 1:].max(-1)[1] + 1
-        tokens, count = k.viterbi_decoding_device(pred, self.output_length, Lt, R, Mt, em["argmax"], self.mask,
-                                                  self.pad_index)
+        tokens, count, pred = k.viterbi_decode_device(S, self.penalty, self.output_length, Lt, R, Mt, em["argmax"],
+                                                      self.mask, self.pad_index)
         return tokens, count, pred

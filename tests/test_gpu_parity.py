@@ -206,6 +206,14 @@ def test_viterbi_bit_exact_against_oracle(vit_kernel, ops, syn, name, kw, seed):
     mask = b.left_tree_mask.long()
     want = oracle.viterbi_decoding(pred.cpu().numpy(), b.output_length.numpy(), Lo, Ro, Mo, tok.numpy(), mask.numpy(), 1)
     got = ops.viterbi_decoding(pred, b.output_length.to(DEV), L2, R2, M2, tok.to(DEV), mask.to(DEV), 1)
+    # the same in one launch: length choice fused into the back-trace
+    pen = torch.arange(b.L // 4, device=DEV).float()
+    f_tok, f_cnt, f_pred = ops.get_pcfg_kernel().viterbi_decode_device(S, pen, b.output_length.to(DEV), L2, R2, M2,
+                                                                       tok.to(DEV), mask.to(DEV), 1)
+    assert torch.equal(f_pred, pred)
+    width = want.shape[1]
+    np.testing.assert_array_equal(f_tok[:, :width].cpu().numpy(), want.astype(np.int64))
+    assert (f_tok[:, width:] == 1).all() and int(f_cnt.max()) == width
     assert got.dtype == torch.float32 and got.is_cuda
     np.testing.assert_array_equal(got.cpu().numpy(), want)
     # the reference call pattern: traces moved to the host first
