@@ -556,6 +556,43 @@ def test_loss_step_graph_replay_matches_eager(pkg, ops, syn):
         assert abs(float(-se[0]) - float(want)) < 1e-3 * abs(float(want)) and int(se[1]) == w.batch
 
 
+def test_empty_and_minimal_inputs(ops, syn):
+    k = ops.get_pcfg_kernel()
+    L, T = 8, 3
+    ma = torch.zeros(0, L, T, device=DEV)
+    lk = torch.zeros(0, L, 2, L, device=DEV)
+    n0 = torch.zeros(0, dtype=torch.long, device=DEV)
+    # no sentences at all: every operator returns empty outputs without launching anything harmful
+    S, C = k.pcfg_loss(ma, lk, n0, n0, 1)
+    assert S.shape[0] == 0 and C.shape[0] == 0
+    loss, mg, lg = k.pcfg_loss_fwd_bwd(ma, lk, n0, n0)
+    assert loss.numel() == 0 and mg.shape == ma.shape and lg.shape == lk.shape
+    assert k.pcfg_best_tree(S, None, ma, lk, n0, n0, 1).shape == (0, L)
+    Sv, R, Lt, Mt = k.pcfg_viterbi(torch.zeros(0, L, device=DEV), lk, n0, 1)
+    assert Sv.shape == (0, L, L // 4)
+    tok, cnt = k.viterbi_decoding_device(n0, n0, Lt, R, Mt, torch.zeros(0, L, dtype=torch.long, device=DEV),
+                                         torch.zeros(L, L, dtype=torch.long, device=DEV), 1)
+    assert tok.shape == (0, L) and cnt.numel() == 0
+    em = k.proj_logsoftmax_gather(torch.zeros(0, L, 64, dtype=torch.float16, device=DEV),
+                                  torch.zeros(100, 64, dtype=torch.float16, device=DEV),
+                                  torch.zeros(0, T, dtype=torch.long, device=DEV), n0, n0, want_max=True)
+    assert em["match"].shape == (0, L, T) and em["argmax"].shape == (0, L)
+    assert k.loss_stats(loss, n0).cpu().tolist() == [0.0, 0.0, 0.0]
+    torch.cuda.synchronize()
+    # the smallest sentence the grammar admits: two graph nodes... and the smallest table the decoder admits
+    b = syn.make_batch(syn.Workload("min", batch=3, vocab=30, hidden=8, src_min=1, src_max=2, emissions="logits"),
+                       seed=3)
+    ma2 = syn.reference_match_all(b)
+    S2, C2 = k.pcfg_loss(ma2.to(DEV), b.links.to(DEV), b.output_length.to(DEV), b.target_length.to(DEV), 1)
+    So, Co = oracle.pcfg_loss(ma2.numpy(), b.links.numpy(), b.output_length.numpy(), b.target_length.numpy())
+    _rel_close(S2.cpu().numpy(), So, 1e-5, 1e-5)
+    tree = k.pcfg_best_tree(S2, None, ma2.to(DEV), b.links.to(DEV), b.output_length.to(DEV), b.target_length.to(DEV), 1)
+    want = oracle.pcfg_best_tree(S2.cpu().numpy(), Co, ma2.numpy(), b.links.numpy(), b.output_length.numpy(),
+                                 b.target_length.numpy())
+    np.testing.assert_array_equal(tree.cpu().numpy(), want)
+    assert ops.read_status(DEV) == 0
+
+
 @pytest.mark.parametrize("L", [12, 9])
 def test_copy_links_main_rows(ops, L):
     k = ops.get_pcfg_kernel()
