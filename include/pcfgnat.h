@@ -157,6 +157,19 @@ int pcfgnat_proj_logsoftmax_gather(const void *hidden, const void *weight, const
                                    int V, int H, float *match, float *max_lprob, int64_t *argmax, float *lse,
                                    void *workspace, size_t workspace_bytes, int *status, void *stream);
 
+/* Backward of pcfgnat_proj_logsoftmax_gather with respect to the logits, without the [rows][V] log-probabilities
+ * ever having been stored: the logits tiles are recomputed on the tensor cores and turned into
+ *   dlogits[row][v] = sum_t grad_match[row][t] * ([targets[t] == v] - exp(logit[row][v] - lse[row]))
+ * written as bf16 [B*L][V] (16-byte aligned; rows of padding nodes, l >= m_b, are zero).  It stands in for the
+ * in-place softmax buffer of logsoftmax_gather (fs_plugins/custom_ops/logsoftmax_gather.cu:278-289) and the
+ * backward of DagLogsoftmaxGatherFunc (fs_plugins/custom_ops/pcfg_loss.py:168-180); the caller finishes with two
+ * plain GEMMs: d hidden = dlogits . weight, d weight = dlogits^T . hidden.  lse [B*L] f32 is the forward's
+ * output; grad_match [B*L][T] f32; entries the forward masked as EOS (both lengths given) get no gradient.
+ * workspace: pcfgnat_proj_workspace_bytes(B, L, T, V) bytes. */
+int pcfgnat_proj_dlogits(const void *hidden, const void *weight, const int64_t *targets, const int64_t *output_length,
+                         const int64_t *target_length, const float *lse, const float *grad_match, int B, int L, int T, int V,
+                         int H, void *dlogits, void *workspace, size_t workspace_bytes, int *status, void *stream);
+
 /* The three numbers the criterion's scalar loss is formed from, in one launch
  * (fs_plugins/criterions/nat_pcfg_loss.py:117-135: sentences whose loss is infinite or NaN are
  * counted and left out, the others are divided by their target length):

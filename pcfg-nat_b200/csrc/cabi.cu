@@ -244,4 +244,16 @@ int pcfgnat_copy_links_main_rows(void *dst, const void *src, int B, int L, int m
     return PCFGNAT_OK;
 }
 
+int pcfgnat_proj_dlogits(const void *hidden, const void *weight, const int64_t *targets, const int64_t *output_length,
+                         const int64_t *target_length, const float *lse, const float *grad_match, int B, int L, int T, int V,
+                         int H, void *dlogits, void *workspace, size_t workspace_bytes, int *status, void *stream) {
+    if (B < 0 || L < 1 || T < 1 || V < 1 || H < 1) return PCFGNAT_ERR_INVALID_ARGUMENT;
+    if ((long long)B * L > (1ll << 30)) return PCFGNAT_ERR_TOO_LARGE;
+    if (B && (!hidden || !weight || !targets || !lse || !grad_match || !dlogits || !workspace))
+        return PCFGNAT_ERR_INVALID_ARGUMENT;
+    if (target_length != nullptr && output_length == nullptr) return PCFGNAT_ERR_INVALID_ARGUMENT;
+    return launch_proj_dlogits(hidden, weight, targets, output_length, target_length, lse, grad_match, B, L, T, V, H,
+                               dlogits, workspace, workspace_bytes, status, static_cast<cudaStream_t>(stream));
+}
+
 }  // extern "C"

@@ -103,4 +103,8 @@ int launch_proj(const void *hidden, const void *weight, const int64_t *targets, 
                 int B, int L, int T, int V, int H, float *match, float *max_lprob, int64_t *argmax, float *lse,
                 void *workspace, size_t ws_bytes, int *status, cudaStream_t st);
 
+int launch_proj_dlogits(const void *hidden, const void *weight, const int64_t *targets, const int64_t *ol,
+                        const int64_t *tl, const float *lse, const float *grad_match, int B, int L, int T, int V, int H,
+                        void *dlogits, void *workspace, size_t ws_bytes, int *status, cudaStream_t st);
+
 }  // namespace pcfgnat

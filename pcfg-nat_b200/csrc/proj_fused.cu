@@ -27,6 +27,7 @@
 // Every wait on an mbarrier is bounded; on expiry the CTA records PCFGNAT_STATUS_TIMEOUT, stops
 // issuing work, and still frees its tensor memory.
 #include <cuda.h>
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
 #include "common.cuh"
@@ -253,12 +254,26 @@ __global__ void proj_prepare_kernel(const int64_t *__restrict__ ol, const int64_
 // ---------------------------------------------------------------------------------------
 // main kernel
 // ---------------------------------------------------------------------------------------
-template <bool WANT_ARGMAX>
+// MODE: kForward / kForwardArgmax as described above; kGradLogits recomputes the logits tile the same way and,
+// instead of reducing it, writes d loss / d logits = scatter_t(g[row][t] at target t) - softmax(row) * sum_t g[row][t]
+// for every projected row as bf16 into dlogits [B*L][V] (rows in padded order), from the row's saved
+// log-sum-exp and the gradient g of the emissions (entries the forward masked as EOS carry no gradient).
+enum ProjMode { kForward = 0, kForwardArgmax = 1, kGradLogits = 2 };
+
+struct GradArgs {  // kGradLogits only
+    const float *lse;        // [B*L] from the forward
+    const float *gmatch;     // [B*L][T] gradient of the emissions
+    const int64_t *ol, *tl;  // lengths (EOS masking), or null
+    __nv_bfloat16 *dlogits;  // [B*L][V]
+};
+
+template <int MODE>
 __global__ void __launch_bounds__(PROJ_THREADS, 1)
     proj_kernel(const __grid_constant__ CUtensorMap map_w, const __half *__restrict__ hidden,
                 const int *__restrict__ row_src, const int *__restrict__ n_rows_ptr, int max_seg, int V, int KC, int L,
                 int T, const int *__restrict__ stok, const int *__restrict__ sslot, float *match, Partial *partials,
-                int *status) {
+                GradArgs ga, int *status) {
+    constexpr bool WANT_ARGMAX = MODE == kForwardArgmax;
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t bars[2 * NSTAGE + 2 + 4];
     __shared__ uint32_t tmem_base_slot;
@@ -433,6 +448,21 @@ __global__ void __launch_bounds__(PROJ_THREADS, 1)
             float m = -CUDART_INF_F, s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
             float best = -CUDART_INF_F;
             int best_idx = 0;
+            // kGradLogits: this row's log-sum-exp, the sum of its emission gradients, and which target slot the
+            // forward masked (the EOS column of every node but the last, criterions/nat_pcfg_loss.py:112-115)
+            float row_nlse = 0.f, row_gsum = 0.f;
+            int masked_slot = -1;
+            const float *my_g = nullptr;
+            if (MODE == kGradLogits && row_ok) {
+                row_nlse = -ga.lse[row] * kLog2e;
+                my_g = ga.gmatch + (size_t)row * T;
+                if (ga.ol && ga.tl && row - sent * L != (int)ga.ol[sent] - 1) masked_slot = (int)ga.tl[sent] - 1;
+                for (int q = 0; q < T; q++) {
+                    if (__ldg(my_tok + q) == INT_MAX) break;  // ids out of range sort last: never gathered, no gradient
+                    const int slot = __ldg(my_slot + q);
+                    if (slot != masked_slot) row_gsum += my_g[slot];
+                }
+            }
             for (; u < seg_end && ok; u++, tile++) {
                 const uint32_t buf = tile & 1, use = tile >> 1;
                 if (!mbar_wait(bar_tfull + 8 * buf, use & 1, abort_flag)) {
@@ -451,6 +481,40 @@ __global__ void __launch_bounds__(PROJ_THREADS, 1)
 #pragma unroll
                         for (int i = 0; i < 32; i++)
                             if (col0 + i >= V) v[i] = -CUDART_INF_F;
+                    }
+                    if (MODE == kGradLogits) {
+#pragma unroll
+                        for (int i = 0; i < 32; i++) v[i] = -row_gsum * ex2(fmaf(v[i], kLog2e, row_nlse));
+                        while (next_tok < col0 + 32) {
+                            const int idx = next_tok - col0;
+                            if (idx >= 0 && row_ok) {
+                                const int slot = __ldg(my_slot + p);
+                                const float g = slot == masked_slot ? 0.f : my_g[slot];
+#pragma unroll
+                                for (int i = 0; i < 32; i++) v[i] += (idx == i) ? g : 0.f;
+                            }
+                            p++;
+                            next_tok = p < T ? __ldg(my_tok + p) : INT_MAX;
+                        }
+                        if (row_ok) {
+                            __nv_bfloat16 *dst = ga.dlogits + (size_t)row * V + col0;
+                            if (col0 + 32 <= V && (V & 7) == 0) {
+                                uint32_t pk[16];
+#pragma unroll
+                                for (int i = 0; i < 16; i++) {
+                                    const __nv_bfloat162 two = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+                                    pk[i] = *reinterpret_cast<const uint32_t *>(&two);
+                                }
+#pragma unroll
+                                for (int i = 0; i < 4; i++)
+                                    reinterpret_cast<uint4 *>(dst)[i] = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
+                            } else {
+#pragma unroll
+                                for (int i = 0; i < 32; i++)
+                                    if (col0 + i < V) dst[i] = __float2bfloat16_rn(v[i]);
+                            }
+                        }
+                        return;
                     }
                     float w16[16];  // tree max
 #pragma unroll
@@ -512,7 +576,7 @@ __global__ void __launch_bounds__(PROJ_THREADS, 1)
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
             }
-            if (ok) {
+            if (ok && MODE != kGradLogits) {
                 Partial pr;
                 pr.m = m;
                 pr.s = (s0 + s1) + (s2 + s3);
@@ -739,24 +803,65 @@ int launch_proj(const void *hidden, const void *weight, const int64_t *targets, 
     const size_t smem = (size_t)KC_MAX * A_CHUNK_BYTES + (size_t)NSTAGE * B_STAGE_BYTES + 1024;
     const bool want_arg = max_lprob != nullptr || argmax != nullptr;
     const __half *hid = static_cast<const __half *>(hidden);
+    const GradArgs none = {nullptr, nullptr, nullptr, nullptr, nullptr};
     if (want_arg) {
-        auto k = proj_kernel<true>;
+        auto k = proj_kernel<kForwardArgmax>;
         if (ensure_dynamic_smem(k, smem) != cudaSuccess) return PCFGNAT_ERR_CUDA;
         k<<<geo.ctas, PROJ_THREADS, smem, st>>>(map_w, hid, w.row_src, w.n_rows, geo.max_seg, V, H / BK, L, T,
                                                 gather ? w.stok : nullptr, gather ? w.sslot : nullptr,
-                                                gather ? match : nullptr, w.partials, status);
+                                                gather ? match : nullptr, w.partials, none, status);
     } else {
-        auto k = proj_kernel<false>;
+        auto k = proj_kernel<kForward>;
         if (ensure_dynamic_smem(k, smem) != cudaSuccess) return PCFGNAT_ERR_CUDA;
         k<<<geo.ctas, PROJ_THREADS, smem, st>>>(map_w, hid, w.row_src, w.n_rows, geo.max_seg, V, H / BK, L, T,
                                                 gather ? w.stok : nullptr, gather ? w.sslot : nullptr,
-                                                gather ? match : nullptr, w.partials, status);
+                                                gather ? match : nullptr, w.partials, none, status);
     }
     if (cudaGetLastError() != cudaSuccess) return PCFGNAT_ERR_CUDA;
     const int row_tiles = (N + BM - 1) / BM;
     proj_merge_kernel<<<kMergeSplit * row_tiles + B, kMergeThreads, 0, st>>>(w.partials, w.prefix, w.row_src, w.n_rows, geo.ctas, geo.max_seg,
                                                      row_tiles, V, L, T, ol, tl, targets, gather ? match : nullptr,
                                                      max_lprob, argmax, lse);
+    return cuda_rc(cudaGetLastError());
+}
+
+// Rows of padding (l >= m_b) are not projected: their gradient rows are zero.
+__global__ void proj_zero_padding_rows_kernel(const int *__restrict__ prefix, int L, int V, __nv_bfloat16 *dlogits) {
+    const int b = blockIdx.x;
+    const int len_b = prefix[b + 1] - prefix[b];
+    for (int l = len_b + blockIdx.y; l < L; l += gridDim.y) {
+        __nv_bfloat16 *row = dlogits + ((size_t)b * L + l) * V;
+        if ((V & 7) == 0) {
+            for (int i = threadIdx.x; i < V / 8; i += blockDim.x) reinterpret_cast<uint4 *>(row)[i] = make_uint4(0u, 0u, 0u, 0u);
+        } else {
+            for (int i = threadIdx.x; i < V; i += blockDim.x) row[i] = __float2bfloat16_rn(0.f);
+        }
+    }
+}
+
+int launch_proj_dlogits(const void *hidden, const void *weight, const int64_t *targets, const int64_t *ol,
+                        const int64_t *tl, const float *lse, const float *grad_match, int B, int L, int T, int V, int H,
+                        void *dlogits, void *workspace, size_t ws_bytes, int *status, cudaStream_t st) {
+    const int N = B * L;
+    if (N == 0) return PCFGNAT_OK;
+    if (H % BK != 0 || H > KC_MAX * BK) return PCFGNAT_ERR_UNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(hidden) | reinterpret_cast<uintptr_t>(weight) | reinterpret_cast<uintptr_t>(dlogits)) % 16)
+        return PCFGNAT_ERR_INVALID_ARGUMENT;
+    if (ws_bytes < proj_workspace_bytes(B, L, T, V) || reinterpret_cast<uintptr_t>(workspace) % 16)
+        return PCFGNAT_ERR_WORKSPACE;
+    const Geometry geo = make_geometry(N, V);
+    const Workspace w = carve(workspace, B, L, T, V);
+    CUtensorMap map_w;
+    if (!make_map(&map_w, weight, (uint64_t)V, (uint64_t)H, BN)) return PCFGNAT_ERR_CUDA;
+    proj_prepare_kernel<<<B, 128, 0, st>>>(ol, targets, B, L, T, V, w.prefix, w.row_src, w.n_rows, w.stok, w.sslot, status);
+    __nv_bfloat16 *dl = static_cast<__nv_bfloat16 *>(dlogits);
+    if (ol) proj_zero_padding_rows_kernel<<<dim3(B, 8), 256, 0, st>>>(w.prefix, L, V, dl);
+    const size_t smem = (size_t)KC_MAX * A_CHUNK_BYTES + (size_t)NSTAGE * B_STAGE_BYTES + 1024;
+    auto k = proj_kernel<kGradLogits>;
+    if (ensure_dynamic_smem(k, smem) != cudaSuccess) return PCFGNAT_ERR_CUDA;
+    const GradArgs ga = {lse, grad_match, ol, tl, dl};
+    k<<<geo.ctas, PROJ_THREADS, smem, st>>>(map_w, static_cast<const __half *>(hidden), w.row_src, w.n_rows, geo.max_seg, V,
+                                            H / BK, L, T, w.stok, w.sslot, nullptr, w.partials, ga, status);
     return cuda_rc(cudaGetLastError());
 }
 

@@ -316,6 +316,40 @@ class _Kernel:
         return out
 
     @staticmethod
+    def proj_dlogits(hidden, weight, targets, output_length, target_length, lse, grad_match):
+        """d loss / d logits of ``proj_logsoftmax_gather`` as bf16 [B * L, V], the logits recomputed on the
+        tensor cores tile by tile (nothing of size [B, L, V] was kept from the forward).  ``lse`` [B, L] is the
+        forward's ``want_lse`` output, ``grad_match`` [B, L, T] the gradient of its ``match``."""
+        _require_cuda()
+        if hidden.dtype != torch.float16 or weight.dtype != torch.float16 or not (hidden.is_cuda and weight.is_cuda):
+            raise RuntimeError("hidden and weight must be float16 CUDA tensors")
+        B, L, H = hidden.shape
+        V = weight.shape[0]
+        dev = hidden.device
+        hidden, weight = hidden.contiguous(), weight.contiguous()
+        targets = targets.to(device=dev, dtype=torch.int64).contiguous()
+        T = targets.shape[1]
+        lse = _f32_cuda(lse, "lse", 2)
+        g = _f32_cuda(grad_match, "grad_match", 3)
+        if tuple(lse.shape) != (B, L) or tuple(g.shape) != (B, L, T):
+            raise RuntimeError("lse must be [batch, prelen] and grad_match [batch, prelen, tarlen]")
+        if target_length is not None and output_length is None:
+            raise RuntimeError("target_length (EOS masking) needs output_length as well")
+        ol = _lengths(output_length, "output_length", B, dev) if output_length is not None else None
+        tl = _lengths(target_length, "target_length", B, dev) if target_length is not None else None
+        l = _cabi.lib()
+        nbytes = l.pcfgnat_proj_workspace_bytes(B, L, T, V)
+        ptr = lambda t: t.data_ptr() if t is not None else None
+        with torch.cuda.device(dev):
+            ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=dev)
+            dl = torch.empty((B * L, V), dtype=torch.bfloat16, device=dev)
+            rc = l.pcfgnat_proj_dlogits(hidden.data_ptr(), weight.data_ptr(), targets.data_ptr(), ptr(ol), ptr(tl),
+                                        lse.data_ptr(), g.data_ptr(), B, L, T, V, H, dl.data_ptr(), ws.data_ptr(), nbytes,
+                                        _status_ptr(dev), _stream(dev))
+        _cabi.check(rc, "pcfgnat_proj_dlogits")
+        return dl
+
+    @staticmethod
     def viterbi_decoding_device(pred_length, output_length, L_trace, R_trace, M_trace, unreduced_tokens,
                                 left_tree_mask, pad_index):
         """Device back-trace: (tokens [B, L] int64 padded with pad_index, count [B] int64), no host sync."""
@@ -569,9 +603,42 @@ class DagLogsoftmaxGatherFunc(Function):
 dag_logsoftmax_gather_inplace = DagLogsoftmaxGatherFunc.apply
 
 
+class ProjLogsoftmaxGatherFunc(Function):
+    """match = log_softmax(hidden @ weight.T)[targets] with a backward that never holds a [B, L, V] tensor of
+    the forward: the forward keeps only the per-row log-sum-exp; the backward recomputes the logits on the
+    tensor cores into d loss / d logits (bf16, the only [B * L, V] buffer, alive during the backward only) and
+    finishes with two library GEMMs.  Stands in for output_projection + DagLogsoftmaxGatherFunc
+    (models/...pcfg.py:237, custom_ops/pcfg_loss.py:160-180), whose forward overwrites the float32 logits with
+    the softmax to keep them for the backward."""
+
+    @staticmethod
+    def forward(ctx, hidden, weight, targets, output_length, target_length):
+        out = get_pcfg_kernel().proj_logsoftmax_gather(hidden, weight, targets, output_length, target_length,
+                                                       want_lse=True)
+        ctx.save_for_backward(hidden, weight, targets, output_length, target_length, out["lse"])
+        return out["match"]
+
+    @staticmethod
+    def backward(ctx, grad_match):
+        hidden, weight, targets, ol, tl, lse = ctx.saved_tensors
+        B, L, H = hidden.shape
+        dl = get_pcfg_kernel().proj_dlogits(hidden, weight, targets, ol, tl, lse, grad_match.contiguous())
+        d_hidden = d_weight = None
+        if ctx.needs_input_grad[0]:
+            d_hidden = (dl @ weight.to(torch.bfloat16)).view(B, L, H).to(hidden.dtype)
+        if ctx.needs_input_grad[1]:
+            d_weight = (dl.t() @ hidden.reshape(B * L, H).to(torch.bfloat16)).to(weight.dtype)
+        return d_hidden, d_weight, None, None, None
+
+
+def proj_logsoftmax_gather_with_grad(hidden, weight, targets, output_length=None, target_length=None):
+    """``match`` [B, L, T] of ``proj_logsoftmax_gather``, differentiable with respect to hidden and weight."""
+    return ProjLogsoftmaxGatherFunc.apply(hidden, weight, targets, output_length, target_length)
+
+
 def proj_logsoftmax_gather(hidden, weight, targets=None, output_length=None, target_length=None, want_max=False,
                            want_lse=False):
-    """See ``_Kernel.proj_logsoftmax_gather`` (no gradient is defined for this operator yet)."""
+    """See ``_Kernel.proj_logsoftmax_gather`` (not differentiable; ``proj_logsoftmax_gather_with_grad`` is)."""
     return get_pcfg_kernel().proj_logsoftmax_gather(hidden, weight, targets, output_length, target_length, want_max,
                                                     want_lse)
 

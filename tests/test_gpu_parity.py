@@ -496,6 +496,40 @@ def test_fused_projection_against_torch(ops, syn, B, L, T, V, H, std):
     assert torch.equal(out3["argmax"], out["argmax"]) and torch.equal(out3["max_lprob"], out["max_lprob"])
 
 
+@pytest.mark.parametrize("V,H,std", [(1000, 64, 1.0), (4104, 128, 0.3), (997, 64, 1.0)])
+def test_fused_projection_backward_against_torch(ops, syn, V, H, std):
+    """Gradients of the fused projection (logits recomputed on the tensor cores, bf16 d-logits, two GEMMs)
+    against float32 autograd of the same expression."""
+    w = syn.Workload("pb", batch=5, vocab=V, hidden=H, src_min=8, src_max=40, hidden_std=std)
+    b = syn.make_batch(w, seed=V)
+    g = torch.Generator().manual_seed(1)
+    gm = torch.randn(b.B, b.L, b.T, generator=g)
+    gm[torch.rand(b.B, b.L, b.T, generator=g) < 0.5] = 0
+    hid = b.hidden.to(DEV).requires_grad_(True)
+    wt = b.weight.to(DEV).requires_grad_(True)
+    ol, tl = b.output_length.to(DEV), b.target_length.to(DEV)
+    match = ops.proj_logsoftmax_gather_with_grad(hid, wt, b.targets.to(DEV), ol, tl)
+    fin = torch.isfinite(match)
+    (match[fin] * gm.to(DEV)[fin]).sum().backward()
+    # float32 reference of the same expression
+    h32 = b.hidden.float().to(DEV).requires_grad_(True)
+    w32 = b.weight.float().to(DEV).requires_grad_(True)
+    lp = torch.log_softmax(h32 @ w32.t(), -1)
+    ref = lp.gather(2, b.targets.to(DEV)[:, None, :].expand(-1, b.L, -1))
+    rows = torch.arange(b.L, device=DEV)[None, :] < ol[:, None]
+    syn.eos_mask_(ref, ol, tl)
+    ref = torch.where(rows[:, :, None], ref, torch.zeros_like(ref))  # padding nodes are not projected: zeros
+    assert torch.equal(torch.isfinite(ref), fin)
+    torch.testing.assert_close(match[fin], ref[fin].detach(), rtol=2e-3, atol=2e-3)
+    (ref[fin] * gm.to(DEV)[fin]).sum().backward()
+    for got, want in ((hid.grad.float(), h32.grad), (wt.grad.float(), w32.grad)):
+        err = (got - want).norm() / want.norm()
+        assert float(err) < 1.5e-2, float(err)
+        assert float((got - want).abs().max()) < 3e-2 * float(want.abs().max()) + 1e-3
+    assert float(hid.grad[~rows].abs().sum()) == 0.0
+    assert ops.read_status(DEV) == 0
+
+
 def test_fused_projection_flags_bad_targets(ops):
     g = torch.Generator().manual_seed(0)
     hidden = torch.randn(1, 16, 64, generator=g).half().to(DEV)
