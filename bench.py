@@ -51,6 +51,8 @@ def parse():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="train_batch")
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--no-proj-backward", action="store_true",
+                    help="skip the extra measurement of the step with the projection backward")
     ap.add_argument("--copy-chunks", type=int, default=2,
                     help="sentence groups the end-to-end leg sends (and projects) the decoder states in")
     ap.add_argument("--cpu-sample", type=int, default=0,
@@ -263,6 +265,22 @@ def run_ours(a):
     timed_projection(3)
     proj_ms = timed_projection(a.steps)
     sync_all()
+    # the same step carried back through the projection as well (a wider step than the metric's: reported aside)
+    full_ms = None
+    if is_loss and kind != "glance" and world == 1 and not a.no_proj_backward:
+        full = runtime.LossStep(weight, batch.B, batch.L, batch.T, dev, use_graph=not a.no_graph, proj_backward=True)
+        full.load(*[t.to(dev) for t in host])
+        times = []
+        for i in range(3 + a.steps):
+            flush.fill_(1)
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            full.run()
+            e.record()
+            times.append((s, e))
+        torch.cuda.synchronize()
+        full_ms = sum(s.elapsed_time(e) for s, e in times[3:]) / a.steps
+        del full
     status = ops.read_status(dev)
     d2h = sum(h.numel() * h.element_size() for h in result_host)
 
@@ -303,6 +321,11 @@ def run_ours(a):
                "note": "DP kernels: step time minus the separately timed projection call; latency-bound"},
         "clocks": clocks, "device_status": status,
     }
+    if full_ms is not None:
+        line["with_projection_backward"] = {
+            "ms_per_step": full_ms, "value": sentences / (full_ms / 1e3), "unit": UNIT,
+            "what": "the step plus d hidden and d weight of the projection: logits recomputed into bf16 d-logits "
+                    "by proj_kernel's gradient mode, then two library bf16 GEMMs over the padded rows"}
     if rank == 0:
         if world == 1 and not a.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(a, batch)

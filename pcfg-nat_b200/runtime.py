@@ -182,23 +182,36 @@ class LossStep(_GraphedStep):
     """
     kernels_per_step = 7  # proj_prepare, proj, proj_merge, loss_fwd, outside, grad, loss_stats
 
-    def __init__(self, weight, B, L, T, device, use_graph=True, copy_chunks=2):
+    def __init__(self, weight, B, L, T, device, use_graph=True, copy_chunks=2, proj_backward=False):
         super().__init__(weight, B, L, device, use_graph, copy_chunks)
         self.T = T
         self.targets = torch.zeros((B, T), dtype=torch.int64, device=self.device)
         self.target_length = torch.ones((B,), dtype=torch.int64, device=self.device)
+        # with proj_backward the step also carries the emission gradients back through the projection:
+        # run() then returns d hidden [B,L,H] f16 and d weight [V,H] f16 as two more outputs
+        self.proj_backward = bool(proj_backward)
+        if self.proj_backward:
+            self.kernels_per_step = LossStep.kernels_per_step + 3  # proj_prepare, zero padding rows, proj (grad mode)
+            self.weight_bf16 = self.weight.to(torch.bfloat16)
 
     def _inputs(self):
         return [self.hidden, self.links, self.output_length, self.targets, self.target_length]
 
     def _stage1(self, b0=0, b1=None):
         return self.kernel.proj_logsoftmax_gather(self.hidden[b0:b1], self.weight, self.targets[b0:b1],
-                                                  self.output_length[b0:b1], self.target_length[b0:b1])
+                                                  self.output_length[b0:b1], self.target_length[b0:b1],
+                                                  want_lse=self.proj_backward)
 
     def _stage2(self, em):
         loss, mg, lg = self.kernel.pcfg_loss_fwd_bwd(em["match"], self.links, self.output_length, self.target_length)
         stats = sharding.local_loss_stats(loss, self.target_length)
-        return stats, mg, lg, loss
+        if not self.proj_backward:
+            return stats, mg, lg, loss
+        dl = self.kernel.proj_dlogits(self.hidden, self.weight, self.targets, self.output_length, self.target_length,
+                                      em["lse"], mg)
+        d_hidden = (dl @ self.weight_bf16).view(self.B, self.L, self.H).to(torch.float16)
+        d_weight = (dl.t() @ self.hidden.view(self.B * self.L, self.H).to(torch.bfloat16)).to(torch.float16)
+        return stats, mg, lg, loss, d_hidden, d_weight
 
 
 class GlanceStep(LossStep):
