@@ -27,6 +27,8 @@
 // Every wait on an mbarrier is bounded; on expiry the CTA records PCFGNAT_STATUS_TIMEOUT, stops
 // issuing work, and still frees its tensor memory.
 #include <cuda.h>
+
+#include <cstdlib>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -42,10 +44,12 @@ constexpr int BK = 64;         // K elements per smem tile row: 64 fp16 = 128 B 
 constexpr int UK = 16;         // K per tcgen05.mma for 16-bit inputs
 constexpr int WK = 64;         // K extent of one W ring stage: 64 (128-byte swizzle) or 32 (64-byte swizzle; six
                                // 16 KB stages were measured slower, 0.40 vs 0.33 ms: the issuing warp's per-stage cost)
-constexpr int NSTAGE = 3;      // W ring depth
+constexpr int NSTAGE = 3;      // W ring depth (one CTA per tile)
+constexpr int NSTAGE_PAIR = 6; // W ring depth when two CTAs share each W tile: every CTA holds half of it per stage
 constexpr int KC_MAX = 8;      // H <= 512
 constexpr int A_CHUNK_BYTES = BM * BK * 2;  // 16 KB
 constexpr int B_STAGE_BYTES = BN * WK * 2;  // 32 KB at WK = 64
+constexpr int B_STAGE_BYTES_PAIR = B_STAGE_BYTES / 2;
 constexpr int EPI_WARPS = 8;                // two per TMEM sub-partition
 constexpr int PROJ_THREADS = 32 * (2 + EPI_WARPS);
 constexpr int TMEM_BUF_COLS = 256;         // column pitch of the two accumulators (512 columns allocated)
@@ -57,6 +61,8 @@ constexpr float kLn2 = 0.6931471805599453f;
 // tcgen05 instruction descriptor, kind::f16: D = F32 (bits 4-5 = 1), A = B = F16 (0), both K-major (0),
 // N >> 3 at bits 17-22, M >> 4 at bits 24-28.
 constexpr uint32_t kIdesc = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+// the same for a CTA pair (cta_group::2): M = 256, 128 rows in each CTA's tensor memory
+constexpr uint32_t kIdescPair = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
 
 struct Partial {  // per (CTA, segment, column half, row)
     float m, s, best;
@@ -68,12 +74,14 @@ struct Partial {  // per (CTA, segment, column half, row)
 struct Plan {
     int n_tiles, ctas, max_seg;
     long long units, q, rem;  // the first `rem` CTAs own q + 1 units, the others q
-    __host__ __device__ static Plan make(int rows, int V, int ctas, int max_seg) {
+    // pair: two CTAs share every unit, each with its own row tile, so a unit covers two row tiles
+    __host__ __device__ static Plan make(int rows, int V, int ctas, int max_seg, bool pair = false) {
         Plan p;
         p.n_tiles = (V + BN - 1) / BN;
         p.ctas = ctas;
         p.max_seg = max_seg;
-        p.units = (long long)((rows + BM - 1) / BM) * p.n_tiles;
+        const int row_tiles = (rows + BM - 1) / BM;
+        p.units = (long long)(pair ? (row_tiles + 1) / 2 : row_tiles) * p.n_tiles;
         p.q = p.units / ctas;
         p.rem = p.units % ctas;
         return p;
@@ -114,6 +122,48 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     return false;
 }
 
+// ---- CTA pair (cluster of 2) variants: barriers that live in the pair's first CTA, loads that signal them ----
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Address of the same shared-memory location in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// Bounded wait on a barrier that CTAs of the cluster arrive on.
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+    for (uint32_t it = 0; it < kSpinLimit; ++it) {
+        uint32_t ok;
+        asm volatile(
+            "{ .reg .pred p; mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2; selp.b32 %0, 1, 0, p; }"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (ok) return true;
+        if (it > 32) __nanosleep(128);
+        if ((it & 255u) == 255u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    return false;
+}
+// TMA load into this CTA's shared memory that reports its bytes to a barrier of the pair's first CTA.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap *map, uint32_t cluster_bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(cluster_bar), "r"(x), "r"(y)
+        : "memory");
+}
+
 // True in exactly one lane of a fully converged warp (the same lane on every call).
 __device__ __forceinline__ bool elect_one() {
     uint32_t chosen;
@@ -150,6 +200,21 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t da, uint64_t 
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
         "l"(da), "l"(db), "r"(kIdesc), "r"(accumulate)
         : "memory");
+}
+// The pair's MMA: 256 x BN x 16, rows 0-127 from this CTA's state tile into its tensor memory, rows 128-255 from
+// the second CTA's into that CTA's; each CTA supplies BN / 2 rows of the W tile at the same shared-memory offset.
+__device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "l"(da), "l"(db), "r"(kIdescPair), "r"(accumulate)
+        : "memory");
+}
+// Arrives on the barrier at this shared-memory offset in both CTAs of the pair when the MMAs issued so far are done.
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+                 "h"((uint16_t)3)
+                 : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
@@ -267,7 +332,10 @@ struct GradArgs {  // kGradLogits only
     __nv_bfloat16 *dlogits;  // [B*L][V]
 };
 
-template <int MODE>
+// PAIR: launched as clusters of two CTAs that share every W tile (tcgen05 cta_group::2).  A unit is then two
+// row tiles (one per CTA) x one vocabulary tile; each CTA loads half of the W tile per stage, which halves the
+// traffic per SM and lets the same shared memory hold a ring twice as deep; the first CTA issues the MMAs for both.
+template <int MODE, bool PAIR>
 __global__ void __launch_bounds__(PROJ_THREADS, 1)
     proj_kernel(const __grid_constant__ CUtensorMap map_w, const __half *__restrict__ hidden,
                 const int *__restrict__ row_src, const int *__restrict__ n_rows_ptr, int max_seg, int V, int KC, int L,
@@ -275,50 +343,64 @@ __global__ void __launch_bounds__(PROJ_THREADS, 1)
                 GradArgs ga, int *status) {
     constexpr bool WANT_ARGMAX = MODE == kForwardArgmax;
     extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t bars[2 * NSTAGE + 2 + 4];
+    constexpr int NST = PAIR ? NSTAGE_PAIR : NSTAGE;
+    constexpr int STAGE_BYTES = PAIR ? B_STAGE_BYTES_PAIR : B_STAGE_BYTES;
+    __shared__ __align__(8) uint64_t bars[2 * NST + 2 + 4];
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag_s;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int g = blockIdx.x;
+    const int g = blockIdx.x;  // owner of a partial slot
+    const uint32_t rank = PAIR ? cluster_ctarank() : 0;  // 0: the CTA that owns the pair's barriers and issues its MMAs
+    const int sched = PAIR ? blockIdx.x / 2 : blockIdx.x;
     const int n_rows = *n_rows_ptr;
-    const Plan plan = Plan::make(n_rows, V, gridDim.x, max_seg);
-    const long long u_begin = plan.begin(g), u_end = plan.begin(g + 1);
+    const Plan plan = Plan::make(n_rows, V, PAIR ? gridDim.x / 2 : gridDim.x, max_seg, PAIR);
+    const long long u_begin = plan.begin(sched), u_end = plan.begin(sched + 1);
     const int NT = plan.n_tiles;
 
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const uint32_t smem_a = smem_u32(smem);
     const uint32_t smem_b = smem_a + KC_MAX * A_CHUNK_BYTES;
-    const uint32_t bar_full = smem_u32(&bars[0]);                 // [NSTAGE] W stage landed
-    const uint32_t bar_empty = smem_u32(&bars[NSTAGE]);           // [NSTAGE] W stage consumed
-    const uint32_t bar_a = smem_u32(&bars[2 * NSTAGE]);           // state tile written (one arrival per loader thread)
-    const uint32_t bar_a_free = smem_u32(&bars[2 * NSTAGE + 1]);  // all MMAs of the segment have read it
-    const uint32_t bar_tfull = smem_u32(&bars[2 * NSTAGE + 2]);   // [2] accumulator ready
-    const uint32_t bar_tempty = smem_u32(&bars[2 * NSTAGE + 4]);  // [2] accumulator drained
+    // In a pair, `full`, `a` and `tempty` are used in the first CTA only (both CTAs report to them); `empty`,
+    // `a_free` and `tfull` exist in both and are signalled in both by the first CTA's commits.
+    const uint32_t bar_full = smem_u32(&bars[0]);              // [NST] W stage landed
+    const uint32_t bar_empty = smem_u32(&bars[NST]);           // [NST] W stage consumed
+    const uint32_t bar_a = smem_u32(&bars[2 * NST]);           // state tile(s) written (one arrival per CTA)
+    const uint32_t bar_a_free = smem_u32(&bars[2 * NST + 1]);  // all MMAs of the segment have read it
+    const uint32_t bar_tfull = smem_u32(&bars[2 * NST + 2]);   // [2] accumulator ready
+    const uint32_t bar_tempty = smem_u32(&bars[2 * NST + 4]);  // [2] accumulator drained
     volatile int *abort_flag = &abort_flag_s;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < NSTAGE; i++) {
+        for (int i = 0; i < NST; i++) {
             mbar_init(bar_full + 8 * i, 1);
             mbar_init(bar_empty + 8 * i, 1);
         }
-        mbar_init(bar_a, EPI_WARPS * 32);  // every loader thread arrives after fencing its own writes
+        mbar_init(bar_a, PAIR ? 2 : 1);  // one arrival per CTA, after its loader threads have met
         mbar_init(bar_a_free, 1);
         for (int i = 0; i < 2; i++) {
             mbar_init(bar_tfull + 8 * i, 1);
-            mbar_init(bar_tempty + 8 * i, EPI_WARPS);  // one arrival per epilogue warp
+            mbar_init(bar_tempty + 8 * i, (PAIR ? 2 : 1) * EPI_WARPS);  // one arrival per epilogue warp
         }
         abort_flag_s = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
-                     "r"(2 * TMEM_BUF_COLS)
-                     : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if (PAIR) {
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
+                         "r"(2 * TMEM_BUF_COLS)
+                         : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
+                         "r"(2 * TMEM_BUF_COLS)
+                         : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     tc_fence_before();
-    __syncthreads();
+    if (PAIR) cluster_sync_all();  // both CTAs' barriers are initialised before either reports to the other's
+    else __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
 
@@ -335,48 +417,66 @@ __global__ void __launch_bounds__(PROJ_THREADS, 1)
                 ok = __all_sync(0xffffffffu, mbar_wait(bar_empty + 8 * st, ph ^ 1, abort_flag));
                 if (!ok) break;
                 if (elect_one()) {
-                    mbar_expect_tx(bar_full + 8 * st, B_STAGE_BYTES);
-                    tma_load_2d(smem_b + st * B_STAGE_BYTES, &map_w, bar_full + 8 * st, kw * WK, t * BN);
+                    if (PAIR) {  // this CTA's half of the tile; the bytes of both halves are counted in the first CTA
+                        if (rank == 0) mbar_expect_tx(bar_full + 8 * st, 2 * STAGE_BYTES);
+                        tma_load_2d_pair(smem_b + st * STAGE_BYTES, &map_w, map_to_cta(bar_full + 8 * st, 0), kw * WK,
+                                         t * BN + (int)rank * (BN / 2));
+                    } else {
+                        mbar_expect_tx(bar_full + 8 * st, STAGE_BYTES);
+                        tma_load_2d(smem_b + st * STAGE_BYTES, &map_w, bar_full + 8 * st, kw * WK, t * BN);
+                    }
                 }
-                if (++st == NSTAGE) st = 0, ph ^= 1;
+                if (++st == NST) st = 0, ph ^= 1;
             }
             if (++t == NT) t = 0;
         }
     } else if (warp == 1) {
-        // ------------------------------ MMA issuer ------------------------------
+        // ------------------------------ MMA issuer (of the pair: in its first CTA only) ------------------------
         uint32_t st = 0, ph = 0, seg = 0, tile = 0;
         bool ok = true;
-        long long u = u_begin;
+        long long u = rank == 0 ? u_begin : u_end;
         while (u < u_end && ok) {
             const int rt = (int)(u / NT);
             const long long seg_end = min(u_end, (long long)(rt + 1) * NT);
-            ok = __all_sync(0xffffffffu, mbar_wait(bar_a, seg & 1, abort_flag));
+            ok = __all_sync(0xffffffffu, PAIR ? mbar_wait_cluster(bar_a, seg & 1, abort_flag) : mbar_wait(bar_a, seg & 1, abort_flag));
             if (!ok) break;
             for (; u < seg_end && ok; u++, tile++) {
                 const uint32_t buf = tile & 1, use = tile >> 1;
-                ok = __all_sync(0xffffffffu, mbar_wait(bar_tempty + 8 * buf, (use & 1) ^ 1, abort_flag));
+                ok = __all_sync(0xffffffffu, PAIR ? mbar_wait_cluster(bar_tempty + 8 * buf, (use & 1) ^ 1, abort_flag)
+                                                  : mbar_wait(bar_tempty + 8 * buf, (use & 1) ^ 1, abort_flag));
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t d = tmem_base + buf * TMEM_BUF_COLS;
                 for (int kw = 0; kw < KC * (BK / WK); kw++) {
-                    ok = __all_sync(0xffffffffu, mbar_wait(bar_full + 8 * st, ph, abort_flag));
+                    ok = __all_sync(0xffffffffu, PAIR ? mbar_wait_cluster(bar_full + 8 * st, ph, abort_flag)
+                                                      : mbar_wait(bar_full + 8 * st, ph, abort_flag));
                     if (!ok) break;
                     tc_fence_after();
                     // the state tile is in 64-wide chunks; this stage covers WK of them starting at kw * WK
                     const int kc = kw / (BK / WK), sub = kw % (BK / WK);
                     const uint64_t da = umma_desc(smem_a + kc * A_CHUNK_BYTES) + 2 * sub * (WK / UK);
-                    const uint64_t db = umma_desc_w(smem_b + st * B_STAGE_BYTES);
+                    const uint64_t db = umma_desc_w(smem_b + st * STAGE_BYTES);
                     if (elect_one()) {
 #pragma unroll
-                        for (int k = 0; k < WK / UK; k++)  // +32 B along K inside the swizzle span = +2 in the address field
-                            umma_f16(d, da + 2 * k, db + 2 * k, (kw | k) != 0);
-                        umma_commit(bar_empty + 8 * st);  // frees the W stage when these MMAs have read it
+                        for (int k = 0; k < WK / UK; k++) {  // +32 B along K inside the swizzle span = +2 in the address field
+                            if (PAIR) umma_f16_pair(d, da + 2 * k, db + 2 * k, (kw | k) != 0);
+                            else umma_f16(d, da + 2 * k, db + 2 * k, (kw | k) != 0);
+                        }
+                        // frees the W stage (in both CTAs of a pair) when these MMAs have read it
+                        if (PAIR) umma_commit_pair(bar_empty + 8 * st);
+                        else umma_commit(bar_empty + 8 * st);
                     }
-                    if (++st == NSTAGE) st = 0, ph ^= 1;
+                    if (++st == NST) st = 0, ph ^= 1;
                 }
-                if (ok && elect_one()) umma_commit(bar_tfull + 8 * buf);
+                if (ok && elect_one()) {
+                    if (PAIR) umma_commit_pair(bar_tfull + 8 * buf);
+                    else umma_commit(bar_tfull + 8 * buf);
+                }
             }
-            if (ok && elect_one()) umma_commit(bar_a_free);
+            if (ok && elect_one()) {
+                if (PAIR) umma_commit_pair(bar_a_free);
+                else umma_commit(bar_a_free);
+            }
             seg++;
         }
     } else {
@@ -389,8 +489,9 @@ __global__ void __launch_bounds__(PROJ_THREADS, 1)
         bool ok = true;
         long long u = u_begin;
         while (u < u_end && ok) {
-            const int rt = (int)(u / NT);
-            const long long seg_end = min(u_end, (long long)(rt + 1) * NT);
+            const int ut = (int)(u / NT);  // row tile (or pair of row tiles) of this segment
+            const int rt = PAIR ? 2 * ut + (int)rank : ut;
+            const long long seg_end = min(u_end, (long long)(ut + 1) * NT);
             // ---- gather the 128 x H state tile into the swizzled layout tcgen05.mma reads ----
             if (seg > 0 && !mbar_wait(bar_a_free, (seg - 1) & 1, abort_flag)) break;
             {
@@ -425,7 +526,11 @@ __global__ void __launch_bounds__(PROJ_THREADS, 1)
                     }
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> tensor-core reads
-                mbar_arrive(bar_a);
+                asm volatile("bar.sync 1, %0;" ::"n"(EPI_WARPS * 32) : "memory");  // the loader threads of this CTA
+                if (et == 0) {
+                    if (PAIR) mbar_arrive_cluster(map_to_cta(bar_a, 0));
+                    else mbar_arrive(bar_a);
+                }
             }
             const int cr = rt * BM + sub * 32 + lane;
             const bool row_ok = cr < n_rows;
@@ -436,7 +541,7 @@ __global__ void __launch_bounds__(PROJ_THREADS, 1)
             float *my_out = match ? match + (size_t)row * T : nullptr;
             int p = 0;
             if (my_tok) {  // first target at or after this segment's first column
-                const int c_first = (int)(u - (long long)rt * NT) * BN;
+                const int c_first = (int)(u - (long long)ut * NT) * BN;
                 int lo = 0, hi = T;
                 while (lo < hi) {
                     int mid = (lo + hi) >> 1;
@@ -470,7 +575,7 @@ __global__ void __launch_bounds__(PROJ_THREADS, 1)
                     break;
                 }
                 tc_fence_after();
-                const int tile_col0 = (int)(u - (long long)rt * NT) * BN + half * HALF_COLS;
+                const int tile_col0 = (int)(u - (long long)ut * NT) * BN + half * HALF_COLS;
                 const uint32_t tsrc = tmem_base + ((uint32_t)(sub * 32) << 16) + buf * TMEM_BUF_COLS + half * HALF_COLS;
                 // One 32-column chunk of this thread's row: online max / sum-exp, arg-max, target logits.
                 auto process = [&](const uint32_t *r, const int col0) {
@@ -574,7 +679,10 @@ __global__ void __launch_bounds__(PROJ_THREADS, 1)
                 }
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
+                if (lane == 0) {
+                    if (PAIR) mbar_arrive_cluster(map_to_cta(bar_tempty + 8 * buf, 0));
+                    else mbar_arrive(bar_tempty + 8 * buf);
+                }
             }
             if (ok && MODE != kGradLogits) {
                 Partial pr;
@@ -589,10 +697,14 @@ __global__ void __launch_bounds__(PROJ_THREADS, 1)
     }
     if (*abort_flag && threadIdx.x == 0) flag(status, PCFGNAT_STATUS_TIMEOUT);
     tc_fence_before();
-    __syncthreads();
+    if (PAIR) cluster_sync_all();  // neither CTA frees tensor memory the pair's MMAs may still write
+    else __syncthreads();
     if (warp == 0) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * TMEM_BUF_COLS) : "memory");
+        if (PAIR)
+            asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * TMEM_BUF_COLS) : "memory");
+        else
+            asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * TMEM_BUF_COLS) : "memory");
     }
 }
 
@@ -604,7 +716,7 @@ __global__ void __launch_bounds__(PROJ_THREADS, 1)
 constexpr int kMergeSplit = 8, kMergeThreads = 32 * (BM / kMergeSplit);
 __global__ void proj_merge_kernel(const Partial *__restrict__ partials, const int *__restrict__ prefix,
                                   const int *__restrict__ row_src, const int *__restrict__ n_rows_ptr, int ctas,
-                                  int max_seg, int row_tiles, int V, int L, int T, const int64_t *__restrict__ ol,
+                                  int max_seg, int row_tiles, int pair, int V, int L, int T, const int64_t *__restrict__ ol,
                                   const int64_t *__restrict__ tl, const int64_t *__restrict__ targets, float *match,
                                   float *max_lprob, int64_t *argmax, float *lse_out) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
@@ -630,13 +742,16 @@ __global__ void proj_merge_kernel(const Partial *__restrict__ partials, const in
     if (rt * BM + part * (BM / kMergeSplit) >= n_rows) return;
     __shared__ int s_glo, s_ghi, s_seg_lo;
     if (threadIdx.x == 0) {
-        const Plan plan = Plan::make(n_rows, V, ctas, max_seg);
-        const long long u0 = (long long)rt * plan.n_tiles, u1 = u0 + plan.n_tiles - 1;
+        // `ctas` counts schedule owners: CTAs, or CTA pairs (then a unit is two row tiles and the partials of
+        // row tile rt are in CTA 2 * owner + (rt & 1))
+        const Plan plan = Plan::make(n_rows, V, ctas, max_seg, pair != 0);
+        const int ut = pair ? rt >> 1 : rt;
+        const long long u0 = (long long)ut * plan.n_tiles, u1 = u0 + plan.n_tiles - 1;
         s_glo = plan.cta_of(u0);
         s_ghi = plan.cta_of(u1);
-        // only the first CTA of the tile can have begun in an earlier row tile; the others start inside
+        // only the first owner of the tile can have begun in an earlier row tile; the others start inside
         // this one, where it is their segment 0
-        s_seg_lo = rt - (int)(plan.begin(s_glo) / plan.n_tiles);
+        s_seg_lo = ut - (int)(plan.begin(s_glo) / plan.n_tiles);
     }
     __syncthreads();
     const int g_lo = s_glo, seg_lo = s_seg_lo, n_part = (s_ghi - g_lo + 1) * 2;
@@ -648,7 +763,8 @@ __global__ void proj_merge_kernel(const Partial *__restrict__ partials, const in
         float m = -CUDART_INF_F, s = 0.f, best = -CUDART_INF_F;
         int best_idx = INT_MAX;
         for (int i = lane; i < n_part; i += 32) {
-            const int g = g_lo + (i >> 1), h = i & 1, seg = (i >> 1) == 0 ? seg_lo : 0;
+            const int owner = g_lo + (i >> 1), h = i & 1, seg = (i >> 1) == 0 ? seg_lo : 0;
+            const int g = pair ? 2 * owner + (rt & 1) : owner;
             const Partial p = partials[(((size_t)g * max_seg + seg) * 2 + h) * BM + r_in];
             if (p.s > 0.f) {  // then p.m is finite
                 const float nm = fmaxf(m, p.m);
@@ -735,19 +851,64 @@ bool make_map(CUtensorMap *map, const void *base, uint64_t rows, uint64_t K, uin
 // device knows): number of CTAs and the most segments a CTA's range can touch.
 struct Geometry {
     int ctas, max_seg;
+    bool pair;   // CTA pairs (clusters of 2) share every W tile
+    int owners;  // schedule owners: ctas, or ctas / 2 pairs
 };
+
+// PCFGNAT_PROJ_PAIR=1 selects CTA pairs (A/B runs and tests).  Measured on 10 804 rows x 40 000 x 512: 0.347 ms
+// per call with pairs against 0.325 ms with single CTAs, so single CTAs are the default: the deeper ring and
+// the halved L2 traffic of a pair do not pay for its cross-CTA barrier hops.
+bool want_pairs(int row_tiles) {
+    (void)row_tiles;
+    if (const char *v = getenv("PCFGNAT_PROJ_PAIR")) return v[0] == '1';
+    return false;
+}
 
 Geometry make_geometry(int N, int V) {
     int dev = 0, sms = 148;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (sms < 1) sms = 148;
     const int n_tiles = (V + BN - 1) / BN;
-    const long long units = (long long)((N + BM - 1) / BM) * n_tiles;
+    const int row_tiles = (N + BM - 1) / BM;
     Geometry g;
-    g.ctas = (int)(units < sms ? units : sms);
-    const long long per_cta = (units + g.ctas - 1) / g.ctas;
-    g.max_seg = (int)((per_cta + n_tiles - 1) / n_tiles) + 1;
+    g.pair = want_pairs(row_tiles) && sms >= 2;
+    const long long units = (long long)(g.pair ? (row_tiles + 1) / 2 : row_tiles) * n_tiles;
+    const int slots = g.pair ? sms / 2 : sms;
+    g.owners = (int)(units < slots ? units : slots);
+    g.ctas = g.pair ? 2 * g.owners : g.owners;
+    const long long per_owner = (units + g.owners - 1) / g.owners;
+    g.max_seg = (int)((per_owner + n_tiles - 1) / n_tiles) + 1;
     return g;
+}
+
+// Launches proj_kernel<MODE, PAIR>: plain launch, or clusters of two CTAs.
+template <int MODE>
+int launch_proj_kernel(const Geometry &geo, size_t smem, cudaStream_t st, const CUtensorMap &map_w, const __half *hidden,
+                       const int *row_src, const int *n_rows, int V, int KC, int L, int T, const int *stok,
+                       const int *sslot, float *match, Partial *partials, GradArgs ga, int *status) {
+    if (!geo.pair) {
+        auto k = proj_kernel<MODE, false>;
+        if (ensure_dynamic_smem(k, smem) != cudaSuccess) return PCFGNAT_ERR_CUDA;
+        k<<<geo.ctas, PROJ_THREADS, smem, st>>>(map_w, hidden, row_src, n_rows, geo.max_seg, V, KC, L, T, stok, sslot, match,
+                                                partials, ga, status);
+        return cuda_rc(cudaGetLastError());
+    }
+    auto k = proj_kernel<MODE, true>;
+    if (ensure_dynamic_smem(k, smem) != cudaSuccess) return PCFGNAT_ERR_CUDA;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)geo.ctas);
+    cfg.blockDim = dim3(PROJ_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cuda_rc(cudaLaunchKernelEx(&cfg, k, map_w, hidden, row_src, n_rows, geo.max_seg, V, KC, L, T, stok, sslot, match,
+                                      partials, ga, status));
 }
 
 struct Workspace {
@@ -797,30 +958,23 @@ int launch_proj(const void *hidden, const void *weight, const int64_t *targets, 
     const Workspace w = carve(workspace, B, L, T, V);
 
     CUtensorMap map_w;
-    if (!make_map(&map_w, weight, (uint64_t)V, (uint64_t)H, BN)) return PCFGNAT_ERR_CUDA;
+    if (!make_map(&map_w, weight, (uint64_t)V, (uint64_t)H, geo.pair ? BN / 2 : BN)) return PCFGNAT_ERR_CUDA;
     proj_prepare_kernel<<<B, 128, 0, st>>>(ol, gather ? targets : nullptr, B, L, T, V, w.prefix, w.row_src, w.n_rows,
                                            w.stok, w.sslot, status);
     const size_t smem = (size_t)KC_MAX * A_CHUNK_BYTES + (size_t)NSTAGE * B_STAGE_BYTES + 1024;
     const bool want_arg = max_lprob != nullptr || argmax != nullptr;
     const __half *hid = static_cast<const __half *>(hidden);
     const GradArgs none = {nullptr, nullptr, nullptr, nullptr, nullptr};
-    if (want_arg) {
-        auto k = proj_kernel<kForwardArgmax>;
-        if (ensure_dynamic_smem(k, smem) != cudaSuccess) return PCFGNAT_ERR_CUDA;
-        k<<<geo.ctas, PROJ_THREADS, smem, st>>>(map_w, hid, w.row_src, w.n_rows, geo.max_seg, V, H / BK, L, T,
-                                                gather ? w.stok : nullptr, gather ? w.sslot : nullptr,
-                                                gather ? match : nullptr, w.partials, none, status);
-    } else {
-        auto k = proj_kernel<kForward>;
-        if (ensure_dynamic_smem(k, smem) != cudaSuccess) return PCFGNAT_ERR_CUDA;
-        k<<<geo.ctas, PROJ_THREADS, smem, st>>>(map_w, hid, w.row_src, w.n_rows, geo.max_seg, V, H / BK, L, T,
-                                                gather ? w.stok : nullptr, gather ? w.sslot : nullptr,
-                                                gather ? match : nullptr, w.partials, none, status);
-    }
-    if (cudaGetLastError() != cudaSuccess) return PCFGNAT_ERR_CUDA;
+    const int rc = want_arg ? launch_proj_kernel<kForwardArgmax>(geo, smem, st, map_w, hid, w.row_src, w.n_rows, V, H / BK, L, T,
+                                                                 gather ? w.stok : nullptr, gather ? w.sslot : nullptr,
+                                                                 gather ? match : nullptr, w.partials, none, status)
+                            : launch_proj_kernel<kForward>(geo, smem, st, map_w, hid, w.row_src, w.n_rows, V, H / BK, L, T,
+                                                           gather ? w.stok : nullptr, gather ? w.sslot : nullptr,
+                                                           gather ? match : nullptr, w.partials, none, status);
+    if (rc != PCFGNAT_OK) return rc;
     const int row_tiles = (N + BM - 1) / BM;
-    proj_merge_kernel<<<kMergeSplit * row_tiles + B, kMergeThreads, 0, st>>>(w.partials, w.prefix, w.row_src, w.n_rows, geo.ctas, geo.max_seg,
-                                                     row_tiles, V, L, T, ol, tl, targets, gather ? match : nullptr,
+    proj_merge_kernel<<<kMergeSplit * row_tiles + B, kMergeThreads, 0, st>>>(w.partials, w.prefix, w.row_src, w.n_rows, geo.owners, geo.max_seg,
+                                                     row_tiles, geo.pair ? 1 : 0, V, L, T, ol, tl, targets, gather ? match : nullptr,
                                                      max_lprob, argmax, lse);
     return cuda_rc(cudaGetLastError());
 }
@@ -852,17 +1006,14 @@ int launch_proj_dlogits(const void *hidden, const void *weight, const int64_t *t
     const Geometry geo = make_geometry(N, V);
     const Workspace w = carve(workspace, B, L, T, V);
     CUtensorMap map_w;
-    if (!make_map(&map_w, weight, (uint64_t)V, (uint64_t)H, BN)) return PCFGNAT_ERR_CUDA;
+    if (!make_map(&map_w, weight, (uint64_t)V, (uint64_t)H, geo.pair ? BN / 2 : BN)) return PCFGNAT_ERR_CUDA;
     proj_prepare_kernel<<<B, 128, 0, st>>>(ol, targets, B, L, T, V, w.prefix, w.row_src, w.n_rows, w.stok, w.sslot, status);
     __nv_bfloat16 *dl = static_cast<__nv_bfloat16 *>(dlogits);
     if (ol) proj_zero_padding_rows_kernel<<<dim3(B, 8), 256, 0, st>>>(w.prefix, L, V, dl);
     const size_t smem = (size_t)KC_MAX * A_CHUNK_BYTES + (size_t)NSTAGE * B_STAGE_BYTES + 1024;
-    auto k = proj_kernel<kGradLogits>;
-    if (ensure_dynamic_smem(k, smem) != cudaSuccess) return PCFGNAT_ERR_CUDA;
     const GradArgs ga = {lse, grad_match, ol, tl, dl};
-    k<<<geo.ctas, PROJ_THREADS, smem, st>>>(map_w, static_cast<const __half *>(hidden), w.row_src, w.n_rows, geo.max_seg, V,
-                                            H / BK, L, T, w.stok, w.sslot, nullptr, w.partials, ga, status);
-    return cuda_rc(cudaGetLastError());
+    return launch_proj_kernel<kGradLogits>(geo, smem, st, map_w, static_cast<const __half *>(hidden), w.row_src, w.n_rows, V,
+                                           H / BK, L, T, w.stok, w.sslot, nullptr, w.partials, ga, status);
 }
 
 }  // namespace pcfgnat

@@ -257,6 +257,13 @@ def test_backtrace_against_reference_host_golden(ops):
     np.testing.assert_array_equal(got.cpu().numpy().astype(np.int64), g["decoded"])
 
 
+@pytest.fixture(params=["single", "pair"])
+def proj_pair(request, monkeypatch):
+    """Runs a projection test with one CTA per tile and with CTA pairs sharing every W tile (cta_group::2)."""
+    monkeypatch.setenv("PCFGNAT_PROJ_PAIR", "1" if request.param == "pair" else "0")
+    return request.param
+
+
 @pytest.mark.parametrize("dtype,atol", [(torch.float32, 2e-5), (torch.float16, 2e-5)])
 @pytest.mark.parametrize("V", [1000, 40000, 997])
 def test_logsoftmax_gather_against_oracle(ops, dtype, atol, V):
@@ -459,7 +466,7 @@ PROJ_CASES = [
 
 
 @pytest.mark.parametrize("B,L,T,V,H,std", PROJ_CASES)
-def test_fused_projection_against_torch(ops, syn, B, L, T, V, H, std):
+def test_fused_projection_against_torch(proj_pair, ops, syn, B, L, T, V, H, std):
     g = torch.Generator().manual_seed(B * 1000 + L)
     hidden = (torch.randn(B, L, H, generator=g) * std).half().to(DEV)
     weight = (torch.randn(V, H, generator=g) * 0.02).half().to(DEV)
@@ -497,7 +504,7 @@ def test_fused_projection_against_torch(ops, syn, B, L, T, V, H, std):
 
 
 @pytest.mark.parametrize("V,H,std", [(1000, 64, 1.0), (4104, 128, 0.3), (997, 64, 1.0)])
-def test_fused_projection_backward_against_torch(ops, syn, V, H, std):
+def test_fused_projection_backward_against_torch(proj_pair, ops, syn, V, H, std):
     """Gradients of the fused projection (logits recomputed on the tensor cores, bf16 d-logits, two GEMMs)
     against float32 autograd of the same expression."""
     w = syn.Workload("pb", batch=5, vocab=V, hidden=H, src_min=8, src_max=40, hidden_std=std)
