@@ -156,15 +156,13 @@ __global__ void __launch_bounds__(kCThreads, 1)
     // S entries of this CTA's nodes, flushed to global memory after the last step: a global store
     // inside the step loop would make every cluster barrier (a release) wait for it to reach L2
     float *own = lk1 + (size_t)rows_cap * lk_stride;  // [rows_cap][W]
-    // free-order variant: emissions of this CTA's nodes and of their leaves, so that a step reads them from
-    // shared memory instead of chasing three global addresses per node
+    // emissions of this CTA's nodes and of their leaves, so that a step reads them from shared memory
+    // instead of chasing three global addresses per node
     float *em0 = own + (size_t)rows_cap * W, *eml = em0 + (size_t)rows_cap * W;  // [rows_cap][W] each
-    if constexpr (TRIPS > 0) {
-        for (int i = tid; i < my_rows * T; i += kCThreads) {
-            const int r = i / T, t = i - r * T, a = 2 * (crank + NC * r) + 1;
-            em0[r * W + t] = __ldg(mat + (size_t)a * T + t);
-            eml[r * W + t] = a >= 3 ? __ldg(mat + (size_t)(a - 1) * T + t) : 0.f;
-        }
+    for (int i = tid; i < my_rows * T; i += kCThreads) {
+        const int r = i / T, t = i - r * T, a = 2 * (crank + NC * r) + 1;
+        em0[r * W + t] = __ldg(mat + (size_t)a * T + t);
+        eml[r * W + t] = a >= 3 ? __ldg(mat + (size_t)(a - 1) * T + t) : 0.f;
     }
 
     for (int r = warp; r < my_rows; r += kCWarps) {
@@ -193,16 +191,9 @@ __global__ void __launch_bounds__(kCThreads, 1)
         for (int r = warp; r < my_rows; r += kCWarps) {
             const int ai = crank + NC * r, a = 2 * ai + 1;
             const bool has_leaf = a >= 3;
-            float ma0, ma1, ml;
-            if constexpr (TRIPS > 0) {
-                ma0 = em0[r * W + start];
-                ma1 = has_leaf ? em0[r * W + start + 1] : 0.f;
-                ml = eml[r * W + start];  // 0 for the first node, which has no leaf
-            } else {
-                ma0 = __ldg(mat + (size_t)a * T + start);
-                ma1 = has_leaf ? __ldg(mat + (size_t)a * T + start + 1) : 0.f;
-                ml = has_leaf ? __ldg(mat + (size_t)(a - 1) * T + start) : 0.f;
-            }
+            const float ma0 = em0[r * W + start];
+            const float ma1 = has_leaf ? em0[r * W + start + 1] : 0.f;
+            const float ml = eml[r * W + start];  // 0 for the first node, which has no leaf
             const float *r0 = lk0 + r * lk_stride, *r1 = lk1 + r * lk_stride;
             float res;
             if constexpr (TRIPS > 0) {
@@ -295,12 +286,24 @@ __global__ void __launch_bounds__(kCThreads, 1)
     const int Mb = main_nodes_below(m);
     const int my_rows = Mb > crank ? (Mb - crank + NC - 1) / NC : 0;  // children ci = crank + NC * r
     float *gcol = smem;            // [3][cs] rolling G columns of the whole chain (replicated per CTA)
-    float *ga = gcol + 3 * cs;     // [cs] G[a][s] where usable, else 0
-    float *q0 = ga + cs;           // [cs] match[a][s] - S[a][s]
-    float *q1 = q0 + cs;           // [cs] match[a-1][s] + match[a][s+1] - S[a][s]
-    float *lt0 = q1 + cs;          // [rows_cap][lk_stride] links[a][0][c] of this CTA's children, by parent slot
+    // per-parent scalars of a step, for the whole chain (every CTA needs all of them), double-buffered: those of
+    // step s+1 are fetched from global memory while step s is computed
+    float *q0 = gcol + 3 * cs;     // [2][cs] match[a][s] - S[a][s]; -inf where S[a][s] is
+    float *q1 = q0 + 2 * cs;       // [2][cs] match[a-1][s] + match[a][s+1] - S[a][s]; -inf without a leaf
+    float *lt0 = q1 + 2 * cs;      // [rows_cap][lk_stride] links[a][0][c] of this CTA's children, by parent slot
     float *lt1 = lt0 + (size_t)rows_cap * lk_stride;
     float *own = lt1 + (size_t)rows_cap * lk_stride;  // [rows_cap][W] G entries of this CTA's nodes, flushed at the end
+    float *sown = own + (size_t)rows_cap * W;         // [rows_cap][W] inside values of this CTA's nodes
+    // the scalars of parent ai at step s (thread ai computes them; chains of more than kCThreads nodes are not
+    // launched with this kernel)
+    auto parent_scalars = [&](int ai, int s, float &v0, float &v1) {
+        const int a = 2 * ai + 1;
+        const float sa = __ldg(Sb + (size_t)ai * W + s);
+        const float m0 = __ldg(mat + (size_t)a * T + s);
+        v0 = isinf(sa) ? neg_inf() : m0 - sa;
+        v1 = neg_inf();
+        if (!isinf(sa) && a >= 3) v1 = (__ldg(mat + (size_t)(a - 1) * T + s) + __ldg(mat + (size_t)a * T + s + 1)) - sa;
+    };
 
     for (int r = warp; r < my_rows; r += kCWarps) {
         const int ci = crank + NC * r, c = 2 * ci + 1;
@@ -310,6 +313,11 @@ __global__ void __launch_bounds__(kCThreads, 1)
             lt1[r * lk_stride + ai] = __ldg(row + L);
         }
     }
+    for (int i = tid; i < my_rows * W; i += kCThreads) {
+        const int r = i / W, t = i - r * W;
+        sown[i] = __ldg(Sb + (size_t)(crank + NC * r) * W + t);
+    }
+    if (tid < Mb && n >= 2) parent_scalars(tid, 0, q0[tid], q1[tid]);
     for (int i = tid; i < 3 * cs; i += kCThreads) gcol[i] = 0.f;
     __syncthreads();
     if (tid == 0) {
@@ -322,31 +330,23 @@ __global__ void __launch_bounds__(kCThreads, 1)
         const float *g0 = gcol + (s % 3) * cs;
         float *g1 = gcol + ((s + 1) % 3) * cs;
         float *g2 = gcol + ((s + 2) % 3) * cs;
-        // per-parent scalars of this step, for the whole chain (every CTA needs all of them)
-        for (int ai = tid; ai < Mb; ai += kCThreads) {
-            const int a = 2 * ai + 1;
-            const float sa = __ldg(Sb + (size_t)ai * W + s);
-            const float g = g0[ai];
-            const bool on = g != 0.f && !isinf(sa);
-            ga[ai] = on ? g : 0.f;
-            q0[ai] = on ? __ldg(mat + (size_t)a * T + s) - sa : 0.f;
-            float v1 = neg_inf();
-            if (on && a >= 3) v1 = (__ldg(mat + (size_t)(a - 1) * T + s) + __ldg(mat + (size_t)a * T + s + 1)) - sa;
-            q1[ai] = v1;
-        }
-        __syncthreads();
+        const float *c0 = q0 + (s & 1) * cs, *c1 = q1 + (s & 1) * cs;
+        // the next step's scalars: the loads are in flight while this step's nodes are computed
+        float n0 = 0.f, n1 = 0.f;
+        const bool fetch = tid < Mb && s + 2 < n;
+        if (fetch) parent_scalars(tid, s + 1, n0, n1);
         for (int r = warp; r < my_rows; r += kCWarps) {
             const int ci = crank + NC * r;
-            const float sc1 = __ldg(Sb + (size_t)ci * W + s + 1);
-            const float sc2 = __ldg(Sb + (size_t)ci * W + s + 2);
+            const float sc1 = sown[r * W + s + 1];
+            const float sc2 = sown[r * W + s + 2];
             const float *r0 = lt0 + r * lk_stride, *r1 = lt1 + r * lk_stride;
             float acc0 = 0.f, acc1 = 0.f;
             if (!isinf(sc1) || !isinf(sc2)) {
                 for (int ai = lane; ai < ci; ai += 32) {
-                    const float g = ga[ai];
-                    if (g != 0.f) {
-                        acc0 += g * fast_exp((r0[ai] + sc1) + q0[ai]);
-                        acc1 += g * fast_exp((r1[ai] + sc2) + q1[ai]);
+                    const float g = g0[ai];
+                    if (g != 0.f) {  // exp(-inf) = 0 where the parent's inside value is -inf
+                        acc0 += g * fast_exp((r0[ai] + sc1) + c0[ai]);
+                        acc1 += g * fast_exp((r1[ai] + sc2) + c1[ai]);
                     }
                 }
             }
@@ -359,6 +359,10 @@ __global__ void __launch_bounds__(kCThreads, 1)
                 *cluster.map_shared_rank(g2 + ci, lane) = acc1;  // first contribution to column s+2
             }
             if (lane == 0) own[r * W + s + 1] = v;
+        }
+        if (fetch) {
+            q0[((s + 1) & 1) * cs + tid] = n0;
+            q1[((s + 1) & 1) * cs + tid] = n1;
         }
         if (NC > 1) cluster.sync(); else __syncthreads();
     }
@@ -395,8 +399,8 @@ ClusterGeometry cluster_geometry(int B, int Mc, int W) {
         g.rows_cap = (Mc + nc - 1) / nc;
         const size_t lk = (size_t)2 * g.rows_cap * g.lk_stride * sizeof(float);
         const size_t own = (size_t)g.rows_cap * W * sizeof(float);
-        g.smem_in = (size_t)3 * g.cs * sizeof(float) + lk + own;
-        g.smem_out = (size_t)6 * g.cs * sizeof(float) + lk + own;
+        g.smem_in = (size_t)3 * g.cs * sizeof(float) + lk + 3 * own;
+        g.smem_out = (size_t)7 * g.cs * sizeof(float) + lk + 2 * own;
         if (g.smem_out <= (size_t)kSmemLimit - 1024) break;
         if (nc >= 16) {
             g.nc = 0;
@@ -450,8 +454,7 @@ int launch_inside(const float *match_all, const float *links, const int64_t *ol,
     ClusterGeometry g = cluster_geometry(B, Mc, T + 2);
     for (; g.nc >= 1; g.nc /= 2) {  // fall back to smaller clusters if the GPU cannot co-schedule this size
         g.rows_cap = (Mc + g.nc - 1) / g.nc;
-        g.smem_in = ((size_t)3 * g.cs + (size_t)2 * g.rows_cap * g.lk_stride +
-                     (size_t)(TRIPS > 0 ? 3 : 1) * g.rows_cap * (T + 2)) * sizeof(float);
+        g.smem_in = ((size_t)3 * g.cs + (size_t)2 * g.rows_cap * g.lk_stride + (size_t)3 * g.rows_cap * (T + 2)) * sizeof(float);
         if (g.smem_in > (size_t)kSmemLimit - 1024) break;
         int rc = launch_cluster(inside_cluster_kernel<TRIPS>, B, g.nc, g.smem_in, st, match_all, links, ol, tl, L, T, S,
                                 C, loss, status, Mc, Lt, g.cs, g.rows_cap, g.lk_stride);
@@ -481,10 +484,11 @@ int launch_outside_cluster(const float *grad_output, const float *S, const float
                            const int64_t *ol, const int64_t *tl, int B, int L, int T, float *G, int *status,
                            cudaStream_t st) {
     const int Mc = main_slots(L, 1);
+    if (Mc > kCThreads) return PCFGNAT_ERR_UNSUPPORTED;  // one thread per parent fetches the step's scalars
     ClusterGeometry g = cluster_geometry(B, Mc, T + 2);
     for (; g.nc >= 1; g.nc /= 2) {
         g.rows_cap = (Mc + g.nc - 1) / g.nc;
-        g.smem_out = ((size_t)6 * g.cs + (size_t)2 * g.rows_cap * g.lk_stride + (size_t)g.rows_cap * (T + 2)) * sizeof(float);
+        g.smem_out = ((size_t)7 * g.cs + (size_t)2 * g.rows_cap * g.lk_stride + (size_t)2 * g.rows_cap * (T + 2)) * sizeof(float);
         if (g.smem_out > (size_t)kSmemLimit - 1024) break;
         int rc = launch_cluster(outside_cluster_kernel, B, g.nc, g.smem_out, st, grad_output, S, match_all, links, ol, tl,
                                 L, T, G, status, Mc, g.cs, g.rows_cap, g.lk_stride);
