@@ -72,6 +72,49 @@ __device__ __forceinline__ float warp_sum(float v) {
 // ---------------------------------------------------------------------------------------
 // inside pass
 // ---------------------------------------------------------------------------------------
+// One node of the inside pass in the reference's summation order (see the head of this file), for a node
+// whose children fit TR trips of 32.  The terms of the first pass (NaN -> -inf already applied; -inf for
+// absent children, whose exponential is the reference's +0) stay in registers for the second.
+template <int TR>
+__device__ __forceinline__ float inside_node_exact(const float *r0, const float *r1, const float *S1, const float *S2,
+                                                   int ai, int Mb, int lane, bool has_leaf, float ma0, float ma1,
+                                                   float ml) {
+    float t0[TR], t1[TR];
+    float mx = neg_inf();
+#pragma unroll
+    for (int i = 0; i < TR; i++) {
+        const int ci = ai + lane + 32 * i;
+        t0[i] = t1[i] = neg_inf();
+        if (ci < Mb) {
+            t0[i] = clean((r0[ci] + S1[ci]) + ma0);
+            if (t0[i] > mx) mx = t0[i];
+            if (has_leaf) {
+                t1[i] = clean(((r1[ci] + S2[ci]) + ml) + ma1);
+                if (t1[i] > mx) mx = t1[i];
+            }
+        }
+    }
+    mx = warp_max(mx);
+    if (isinf(mx)) return mx;  // warp-uniform
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < TR; i++) {
+        const float e0 = expf(t0[i] - mx), e1 = expf(t1[i] - mx);
+        // children k = 8i .. 8i+7 of every virtual lane, in order
+#pragma unroll
+        for (int h = 0; h < 8; h++) {
+            const float v0 = __shfl_sync(0xffffffffu, e0, (lane & 3) + 4 * h);
+            const float v1 = __shfl_sync(0xffffffffu, e1, (lane & 3) + 4 * h);
+            sum += v0;
+            sum += v1;
+        }
+    }
+    sum += __shfl_down_sync(0xffffffffu, sum, 2, 4);  // lanes 0..3 hold the four virtual-lane sums
+    sum += __shfl_down_sync(0xffffffffu, sum, 1, 4);
+    sum = __shfl_sync(0xffffffffu, sum, 0);
+    return logf(sum) + mx;
+}
+
 // One node of the inside pass in free summation order; TR trips of 32 children cover the node's children.
 template <int TR>
 __device__ __forceinline__ float inside_node_free(const float *r0, const float *r1, const float *S1, const float *S2,
@@ -209,6 +252,17 @@ __global__ void __launch_bounds__(kCThreads, 1)
                 }
             } else {
             const int trips = (Mb - ai + 31) / 32;
+            if (trips <= 8) {  // straight-line code per trip count, terms kept in registers between the passes
+                switch (trips) {
+                    case 1: res = inside_node_exact<1>(r0, r1, S1, S2, ai, Mb, lane, has_leaf, ma0, ma1, ml); break;
+                    case 2: res = inside_node_exact<2>(r0, r1, S1, S2, ai, Mb, lane, has_leaf, ma0, ma1, ml); break;
+                    case 3: res = inside_node_exact<3>(r0, r1, S1, S2, ai, Mb, lane, has_leaf, ma0, ma1, ml); break;
+                    case 4: res = inside_node_exact<4>(r0, r1, S1, S2, ai, Mb, lane, has_leaf, ma0, ma1, ml); break;
+                    case 5:
+                    case 6: res = inside_node_exact<6>(r0, r1, S1, S2, ai, Mb, lane, has_leaf, ma0, ma1, ml); break;
+                    default: res = inside_node_exact<8>(r0, r1, S1, S2, ai, Mb, lane, has_leaf, ma0, ma1, ml); break;
+                }
+            } else {
             float mx = neg_inf();
             for (int i = 0; i < trips; i++) {
                 const int ci = ai + lane + 32 * i;
@@ -245,6 +299,7 @@ __global__ void __launch_bounds__(kCThreads, 1)
             sum += __shfl_down_sync(0xffffffffu, sum, 1, 4);
             sum = __shfl_sync(0xffffffffu, sum, 0);
             res = isinf(mx) ? mx : logf(sum) + mx;
+            }
             }
             if (lane < NC) *cluster.map_shared_rank(S0 + ai, lane) = res;  // into every CTA's column
             if (lane == 0) own[r * W + start] = res;
