@@ -144,8 +144,10 @@ __global__ void __launch_bounds__(kMaxRows *kLanes)
 // 2. gradients
 // ---------------------------------------------------------------------------------------
 constexpr int kGradWarps = 8;
-constexpr int kMaxCPerLane = 8;  // right children per lane: supports Mc <= 32 * 8 = 256 per pass
+// kMaxCPerLane right children per lane and pass over the children: instantiated for 2, 3, 4 and 8, the
+// smallest that covers the chain in one pass is launched (longer chains take several passes of 8)
 
+template <int kMaxCPerLane>
 __global__ void __launch_bounds__(kGradWarps * 32)
     grad_kernel(const float *__restrict__ S, const float *__restrict__ G, const float *__restrict__ match_all,
                 const float *__restrict__ links, const int64_t *__restrict__ ol, const int64_t *__restrict__ tl, int L,
@@ -309,11 +311,16 @@ int launch_loss_bwd(const float *grad_output, const float *S, const float *match
     const int npairs = (L + 1) / 2;
     const size_t gsm = (size_t)kGradWarps * 2 * T * sizeof(float);
     if (gsm > (size_t)kSmemLimit - 1024) return PCFGNAT_ERR_TOO_LARGE;
-    e = ensure_dynamic_smem(grad_kernel, gsm);
-    if (e != cudaSuccess) return PCFGNAT_ERR_CUDA;
     dim3 ggrid((npairs + kGradWarps - 1) / kGradWarps, B);
-    grad_kernel<<<ggrid, kGradWarps * 32, gsm, st>>>(S, S_grad, match_all, links, ol, tl, L, T, mg, lg, Mc);
-    return cuda_rc(cudaGetLastError());
+    auto launch = [&](auto kernel) {
+        if (ensure_dynamic_smem(kernel, gsm) != cudaSuccess) return PCFGNAT_ERR_CUDA;
+        kernel<<<ggrid, kGradWarps * 32, gsm, st>>>(S, S_grad, match_all, links, ol, tl, L, T, mg, lg, Mc);
+        return cuda_rc(cudaGetLastError());
+    };
+    if (Mc <= 64) return launch(grad_kernel<2>);
+    if (Mc <= 96) return launch(grad_kernel<3>);
+    if (Mc <= 128) return launch(grad_kernel<4>);
+    return launch(grad_kernel<8>);
 }
 
 }  // namespace pcfgnat
