@@ -53,6 +53,8 @@ def parse():
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-proj-backward", action="store_true",
                     help="skip the extra measurement of the step with the projection backward")
+    ap.add_argument("--nccl-reduce", action="store_true",
+                    help="N > 1: sum the loss statistics with an NCCL all-reduce instead of the in-kernel exchange")
     ap.add_argument("--copy-chunks", type=int, default=2,
                     help="sentence groups the end-to-end leg sends (and projects) the decoder states in")
     ap.add_argument("--cpu-sample", type=int, default=0,
@@ -151,7 +153,7 @@ def algorithmic(batch):
             "proj_flops_padded": 2.0 * batch.B * batch.L * H * V, "dp_bytes": dp}
 
 
-def make_step(runtime, batch, weight, dev, use_graph, copy_chunks=2):
+def make_step(runtime, batch, weight, dev, use_graph, copy_chunks=2, exchange=None):
     """The public step object of the workload's kind and the host tensors it loads, in load() order."""
     kind = batch.workload.kind
     if kind == "viterbi":
@@ -159,8 +161,11 @@ def make_step(runtime, batch, weight, dev, use_graph, copy_chunks=2):
                                   use_graph=use_graph, copy_chunks=copy_chunks)
         host = (batch.hidden, batch.links, batch.output_length)
     else:
-        cls = runtime.GlanceStep if kind == "glance" else runtime.LossStep
-        step = cls(weight, batch.B, batch.L, batch.T, dev, use_graph=use_graph, copy_chunks=copy_chunks)
+        if kind == "glance":
+            step = runtime.GlanceStep(weight, batch.B, batch.L, batch.T, dev, use_graph=use_graph, copy_chunks=copy_chunks)
+        else:
+            step = runtime.LossStep(weight, batch.B, batch.L, batch.T, dev, use_graph=use_graph, copy_chunks=copy_chunks,
+                                    exchange=exchange)
         host = (batch.hidden, batch.links, batch.output_length, batch.targets, batch.target_length)
         if kind == "glance":  # decoder input of the first pass: <unk> on the graph nodes, padding after them
             pos = torch.arange(batch.L)[None, :]
@@ -193,7 +198,12 @@ def run_ours(a):
     kind = batch.workload.kind
     alg = algorithmic(batch)
     weight = batch.weight.to(dev)
-    step, host = make_step(runtime, batch, weight, dev, not a.no_graph, a.copy_chunks)  # host: pinned copies for the end-to-end leg
+    # N > 1: the loss statistics are summed over the ranks inside the statistics kernel (peer stores over
+    # NVLink); --nccl-reduce uses a 12-byte NCCL all-reduce after the step instead
+    exchange = None
+    if world > 1 and kind == "loss" and not a.nccl_reduce:
+        exchange = importlib.import_module("pcfg_nat_b200.sharding").LossExchange(dev)
+    step, host = make_step(runtime, batch, weight, dev, not a.no_graph, a.copy_chunks, exchange)  # host: pinned copies
     step.load(*host)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)  # > 126 MB L2
     h2d = step.input_bytes()
@@ -211,7 +221,7 @@ def run_ours(a):
             if e2e:  # over the copy stream, transitions last: they are still in flight while the projection runs
                 step.load(*host, overlap=True)
             out = step.run()
-            if is_loss and world > 1:
+            if is_loss and world > 1 and exchange is None:
                 dist.all_reduce(out[0])
             if e2e:  # the step's result goes back to the host: loss statistics / token ids + counts / alignment
                 res = (out[0],) if is_loss else ((out[0], out[1]) if kind == "viterbi" else (out[0],))

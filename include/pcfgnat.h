@@ -178,6 +178,21 @@ int pcfgnat_proj_dlogits(const void *hidden, const void *weight, const int64_t *
  * The caller sums stats over ranks and forms -stats[0] / stats[1]. */
 int pcfgnat_loss_stats(const float *sentence_loss, const int64_t *target_length, int B, float *stats, void *stream);
 
+/* pcfgnat_loss_stats summed over the `world` GPUs of a sentence-sharded job in the same launch: each rank
+ * stores its three numbers into every peer's exchange buffer (plain peer stores over NVLink) and adds, in rank
+ * order, what the peers stored into its own; stats [3] is then the same on every rank.  It stands in for the
+ * all-reduce of the criterion's logging outputs that fairseq's trainer issues after every update.
+ * peer_buffers: device array of `world` device pointers, entry r = rank r's exchange buffer as mapped in THIS
+ * process (peer-accessible memory, e.g. torch symmetric memory), each PCFGNAT_EXCHANGE_BYTES(world) bytes,
+ * zero-filled before the first call and used for nothing else.  Every rank must make the same sequence of
+ * calls.  A peer that does not arrive within the bounded wait contributes zeros and sets
+ * PCFGNAT_STATUS_TIMEOUT in `status`. */
+#define PCFGNAT_EXCHANGE_MAX_WORLD 32
+#define PCFGNAT_EXCHANGE_BYTES(world) (64u + 64u * (unsigned)(world))
+int pcfgnat_loss_stats_exchange(const float *sentence_loss, const int64_t *target_length, int B,
+                                const uint64_t *peer_buffers, int rank, int world, float *stats, int *status,
+                                void *stream);
+
 /* Glancing sampler between the two decoder passes, strategy "number-random"
  * (fs_plugins/criterions/nat_pcfg_loss.py:216-267), one launch instead of ~15 torch operators.
  * path [B][L] int64: aligned target position of each graph node (the best tree), negative = none;

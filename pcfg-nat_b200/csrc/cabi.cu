@@ -213,6 +213,16 @@ int pcfgnat_loss_stats(const float *sentence_loss, const int64_t *target_length,
     return launch_loss_stats(sentence_loss, target_length, B, stats, static_cast<cudaStream_t>(stream));
 }
 
+int pcfgnat_loss_stats_exchange(const float *sentence_loss, const int64_t *target_length, int B,
+                                const uint64_t *peer_buffers, int rank, int world, float *stats, int *status,
+                                void *stream) {
+    if (B < 0 || !stats || !peer_buffers || world < 1 || world > PCFGNAT_EXCHANGE_MAX_WORLD || rank < 0 || rank >= world ||
+        (B && (!sentence_loss || !target_length)))
+        return PCFGNAT_ERR_INVALID_ARGUMENT;
+    return launch_loss_stats_exchange(sentence_loss, target_length, B, peer_buffers, rank, world, stats, status,
+                                      static_cast<cudaStream_t>(stream));
+}
+
 int pcfgnat_glance_select(const int64_t *path, const int64_t *pred_tokens, const int64_t *tgt_tokens,
                           const int64_t *prev_output_tokens, const int64_t *target_length, const float *noise,
                           float context_p, int B, int L, int T, uint8_t *matchmask, int64_t *oracle,

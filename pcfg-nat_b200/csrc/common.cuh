@@ -93,6 +93,8 @@ DpKernel dp_kernel_choice();
 bool cluster_kernels_pay(int B, int L, int T);
 
 int launch_loss_stats(const float *loss, const int64_t *tl, int B, float *stats, cudaStream_t st);
+int launch_loss_stats_exchange(const float *loss, const int64_t *tl, int B, const uint64_t *peer_bufs, int rank, int world,
+                               float *stats, int *status, cudaStream_t st);
 int launch_glance_select(const int64_t *path, const int64_t *pred, const int64_t *tgt, const int64_t *prev,
                          const int64_t *tl, const float *noise, float context_p, int B, int L, int T,
                          uint8_t *matchmask, int64_t *oracle, int64_t *same_num, int64_t *glance_num, uint8_t *keep,

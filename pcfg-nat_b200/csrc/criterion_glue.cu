@@ -5,6 +5,10 @@
 //    (fs_plugins/criterions/nat_pcfg_loss.py:117-135: invalid sentences zeroed, per-sentence loss divided by
 //    its target length, batch mean; the division by the sentence count is left to the caller so that the
 //    three numbers can be summed over ranks first);
+//  * loss_stats_exchange_kernel — the same three numbers summed over the GPUs of a sentence-sharded job, in the
+//    same launch: every rank stores its partial into every peer's exchange buffer over NVLink (plain peer
+//    stores, no multimem) and adds up what the peers stored into its own.  It replaces the 12-byte NCCL
+//    all-reduce that otherwise follows the kernel, whose launch latency is several percent of a step;
 //  * glance_select_kernel — the glancing sampler between the two decoder passes
 //    (nat_pcfg_loss.py:216-267, strategy "number-random"): alignment -> match mask, oracle tokens, number of
 //    already-correct predictions, the glance_nums positions with the largest noise, and the decoder input
@@ -47,6 +51,71 @@ __global__ void loss_stats_kernel(const float *__restrict__ loss, const int64_t 
         stats[0] = s;
         stats[1] = (float)B;
         stats[2] = bad;
+    }
+}
+
+// Exchange buffer of a rank (PCFGNAT_EXCHANGE_BYTES(world) bytes, zeroed once, mapped into every peer):
+//   [0]            uint32 epoch: calls made so far (only this rank's kernel touches it)
+//   [64 + 32 * (parity * world + src)]  slot written by rank src: float data[3], uint32 flag = epoch of the call
+// Two parities: a rank can be at most one call ahead of a peer (it needs the peer's slot of the current call to
+// finish it), so the slots of call e are not overwritten before call e + 2, when every rank has read them.
+__global__ void loss_stats_exchange_kernel(const float *__restrict__ loss, const int64_t *__restrict__ tl, int B,
+                                           const uint64_t *__restrict__ peer_bufs, int rank, int world, float *stats,
+                                           int *status) {
+    __shared__ float scratch[32];
+    __shared__ float part[PCFGNAT_EXCHANGE_MAX_WORLD][3];
+    __shared__ unsigned epoch_s;
+    float s = 0.f, bad = 0.f;
+    for (int b = threadIdx.x; b < B; b += blockDim.x) {
+        const float v = loss[b];
+        if (isinf(v) || isnan(v)) {
+            bad += 1.f;
+        } else {
+            const int64_t n = tl[b];
+            s += v / (float)(n < 1 ? 1 : n);
+        }
+    }
+    s = block_sum(s, scratch);
+    bad = block_sum(bad, scratch);
+    char *mine = reinterpret_cast<char *>(peer_bufs[rank]);
+    if (threadIdx.x == 0) epoch_s = ++*reinterpret_cast<unsigned *>(mine);
+    __syncthreads();
+    const unsigned epoch = epoch_s;
+    const size_t slot0 = 64 + (size_t)32 * ((epoch & 1u) * world);
+    if ((int)threadIdx.x < world) {
+        // this rank's partial into peer threadIdx.x's buffer (its own included), data before flag
+        char *dst = reinterpret_cast<char *>(peer_bufs[threadIdx.x]) + slot0 + (size_t)32 * rank;
+        volatile float *d = reinterpret_cast<volatile float *>(dst);
+        d[0] = s;
+        d[1] = (float)B;
+        d[2] = bad;
+        __threadfence_system();
+        *reinterpret_cast<volatile unsigned *>(dst + 16) = epoch;
+        // the partial peer threadIdx.x stored here; bounded wait (a peer that never arrives leaves zeros and a flag)
+        const char *src = mine + slot0 + (size_t)32 * threadIdx.x;
+        bool there = false;
+        for (unsigned it = 0; it < (1u << 21) && !there; ++it) {
+            there = *reinterpret_cast<const volatile unsigned *>(src + 16) == epoch;
+            if (!there) __nanosleep(200);
+        }
+        __threadfence_system();
+        const volatile float *q = reinterpret_cast<const volatile float *>(src);
+        part[threadIdx.x][0] = there ? q[0] : 0.f;
+        part[threadIdx.x][1] = there ? q[1] : 0.f;
+        part[threadIdx.x][2] = there ? q[2] : 0.f;
+        if (!there) flag(status, PCFGNAT_STATUS_TIMEOUT);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t0 = 0.f, t1 = 0.f, t2 = 0.f;
+        for (int r = 0; r < world; r++) {  // rank order on every rank: the same sum everywhere
+            t0 += part[r][0];
+            t1 += part[r][1];
+            t2 += part[r][2];
+        }
+        stats[0] = t0;
+        stats[1] = t1;
+        stats[2] = t2;
     }
 }
 
@@ -107,6 +176,12 @@ __global__ void glance_select_kernel(const int64_t *__restrict__ path, const int
 
 int launch_loss_stats(const float *loss, const int64_t *tl, int B, float *stats, cudaStream_t st) {
     loss_stats_kernel<<<1, 256, 0, st>>>(loss, tl, B, stats);
+    return cuda_rc(cudaGetLastError());
+}
+
+int launch_loss_stats_exchange(const float *loss, const int64_t *tl, int B, const uint64_t *peer_bufs, int rank, int world,
+                               float *stats, int *status, cudaStream_t st) {
+    loss_stats_exchange_kernel<<<1, 256, 0, st>>>(loss, tl, B, peer_bufs, rank, world, stats, status);
     return cuda_rc(cudaGetLastError());
 }
 

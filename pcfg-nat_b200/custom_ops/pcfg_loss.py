@@ -449,6 +449,24 @@ class _Kernel:
         return stats
 
     @staticmethod
+    def loss_stats_exchange(sentence_loss, target_length, peer_buffers, rank, world):
+        """``loss_stats`` summed over the GPUs of the job in the same launch (peer stores over NVLink instead of
+        a 12-byte all-reduce).  ``peer_buffers``: int64 CUDA tensor [world] of device pointers to every rank's
+        exchange buffer as mapped in this process (see ``sharding.LossExchange``)."""
+        _require_cuda()
+        loss = _f32_cuda(sentence_loss, "sentence_loss", 1)
+        tl = _lengths(target_length, "target_length", loss.shape[0], loss.device)
+        if peer_buffers.dtype != torch.int64 or peer_buffers.device != loss.device or peer_buffers.numel() != world:
+            raise RuntimeError("peer_buffers must be an int64 tensor of `world` device pointers on the loss's device")
+        with torch.cuda.device(loss.device):
+            stats = torch.empty((3,), dtype=torch.float32, device=loss.device)
+            rc = _cabi.lib().pcfgnat_loss_stats_exchange(loss.data_ptr(), tl.data_ptr(), loss.shape[0],
+                                                         peer_buffers.data_ptr(), int(rank), int(world), stats.data_ptr(),
+                                                         _status_ptr(loss.device), _stream(loss.device))
+        _cabi.check(rc, "pcfgnat_loss_stats_exchange")
+        return stats
+
+    @staticmethod
     def glance_select(path, pred_tokens, tgt_tokens, prev_output_tokens, target_length, noise, context_p):
         """The glancing sampler of the criterion (nat_pcfg_loss.py:216-267, strategy "number-random") in one
         launch.  ``noise`` holds the caller's standard-normal draws.  Returns a dict with matchmask [B,T,L] bool,

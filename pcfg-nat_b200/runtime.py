@@ -182,9 +182,11 @@ class LossStep(_GraphedStep):
     """
     kernels_per_step = 7  # proj_prepare, proj, proj_merge, loss_fwd, outside, grad, loss_stats
 
-    def __init__(self, weight, B, L, T, device, use_graph=True, copy_chunks=2, proj_backward=False):
+    def __init__(self, weight, B, L, T, device, use_graph=True, copy_chunks=2, proj_backward=False, exchange=None):
         super().__init__(weight, B, L, device, use_graph, copy_chunks)
         self.T = T
+        # a sharding.LossExchange: the statistics come back summed over the ranks of the job (same launch)
+        self.exchange = exchange
         self.targets = torch.zeros((B, T), dtype=torch.int64, device=self.device)
         self.target_length = torch.ones((B,), dtype=torch.int64, device=self.device)
         # with proj_backward the step also carries the emission gradients back through the projection:
@@ -204,7 +206,8 @@ class LossStep(_GraphedStep):
 
     def _stage2(self, em):
         loss, mg, lg = self.kernel.pcfg_loss_fwd_bwd(em["match"], self.links, self.output_length, self.target_length)
-        stats = sharding.local_loss_stats(loss, self.target_length)
+        stats = (self.exchange.stats(loss, self.target_length) if self.exchange is not None
+                 else sharding.local_loss_stats(loss, self.target_length))
         if not self.proj_backward:
             return stats, mg, lg, loss
         dl = self.kernel.proj_dlogits(self.hidden, self.weight, self.targets, self.output_length, self.target_length,

@@ -58,3 +58,37 @@ def reduce_loss(sentence_loss: torch.Tensor, target_length: torch.Tensor, group=
         dist.all_reduce(stats, op=dist.ReduceOp.SUM, group=group)
     loss = -stats[0] / stats[1].clamp(min=1)
     return loss, stats[1], stats[2]
+
+
+class LossExchange:
+    """Sums the loss statistics over the ranks of a process group inside the statistics kernel itself: every
+    rank's kernel stores its three numbers into every peer's buffer over NVLink and adds up what it received
+    (``pcfgnat_loss_stats_exchange``), instead of a separate 12-byte NCCL all-reduce whose launch latency is
+    several percent of a training step.  The buffers are torch symmetric memory; every rank must call
+    ``stats`` the same number of times.  One GPU: the plain local kernel."""
+
+    def __init__(self, device, group=None):
+        from .custom_ops import pcfg_loss as ops
+
+        self.kernel = ops.get_pcfg_kernel()
+        self.device = torch.device(device)
+        self.world = dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if self.world > 1 else 0
+        self.peers = None
+        if self.world > 1:
+            import torch.distributed._symmetric_memory as symm
+
+            nbytes = 64 + 64 * self.world  # PCFGNAT_EXCHANGE_BYTES(world)
+            self.buffer = symm.empty((nbytes + 3) // 4, dtype=torch.float32, device=self.device)
+            self.buffer.zero_()
+            torch.cuda.synchronize(self.device)
+            pg = group if group is not None else dist.group.WORLD
+            self.handle = symm.rendezvous(self.buffer, pg.group_name)
+            self.peers = torch.tensor([int(p) for p in self.handle.buffer_ptrs], dtype=torch.int64, device=self.device)
+            dist.barrier(group)  # every buffer is zeroed and mapped before any rank's first call
+
+    def stats(self, sentence_loss, target_length):
+        """[sum_b S_b / n_b, sentences, invalid] over all ranks (float32 [3], the same on every rank)."""
+        if self.world == 1:
+            return self.kernel.loss_stats(sentence_loss, target_length)
+        return self.kernel.loss_stats_exchange(sentence_loss, target_length, self.peers, self.rank, self.world)

@@ -678,6 +678,24 @@ def test_loss_stats_and_glance_select(ops):
             assert torch.equal(got[key].cpu(), val), (key, B, L, T)
 
 
+def test_loss_stats_exchange_bounded_wait(ops):
+    """The in-kernel exchange of the loss statistics with a peer that never arrives: the wait runs out, the
+    status word says so, the statistics hold this rank's part only, and the context stays usable."""
+    k = ops.get_pcfg_kernel()
+    bufs = [torch.zeros(64, dtype=torch.float32, device=DEV) for _ in range(2)]  # >= PCFGNAT_EXCHANGE_BYTES(2)
+    peers = torch.tensor([b.data_ptr() for b in bufs], dtype=torch.int64, device=DEV)
+    loss = torch.tensor([-4.0, -9.0, float("-inf")], device=DEV)
+    tl = torch.tensor([2, 3, 5], device=DEV)
+    ops.read_status(DEV)
+    stats = k.loss_stats_exchange(loss, tl, peers, 0, 2).cpu()
+    assert stats.tolist() == [-5.0, 3.0, 1.0]
+    assert ops.read_status(DEV) & 8  # PCFGNAT_STATUS_TIMEOUT
+    # a world of one rank needs nobody else
+    one = torch.zeros(64, dtype=torch.float32, device=DEV)
+    stats = k.loss_stats_exchange(loss, tl, torch.tensor([one.data_ptr()], dtype=torch.int64, device=DEV), 0, 1).cpu()
+    assert stats.tolist() == [-5.0, 3.0, 1.0] and ops.read_status(DEV) == 0
+
+
 def test_decode_and_glance_steps_match_operator_chain(pkg, ops, syn):
     """The graph-replayed decode / glancing steps give what the individual operators give."""
     import importlib
