@@ -202,7 +202,14 @@ def run_ours(a):
     # NVLink); --nccl-reduce uses a 12-byte NCCL all-reduce after the step instead
     exchange = None
     if world > 1 and kind == "loss" and not a.nccl_reduce:
-        exchange = importlib.import_module("pcfg_nat_b200.sharding").LossExchange(dev)
+        try:
+            exchange = importlib.import_module("pcfg_nat_b200.sharding").LossExchange(dev)
+        except Exception as err:  # no peer-mapped memory on this box: every rank then falls back together
+            print(f"[bench] rank {rank}: in-kernel exchange unavailable ({err}); using the NCCL all-reduce", file=sys.stderr)
+        agreed = torch.tensor([1 if exchange is not None else 0], device=dev)
+        dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
+        if int(agreed) == 0:
+            exchange = None
     step, host = make_step(runtime, batch, weight, dev, not a.no_graph, a.copy_chunks, exchange)  # host: pinned copies
     step.load(*host)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)  # > 126 MB L2
@@ -314,7 +321,9 @@ def run_ours(a):
                    "left_tree_layer": 1, "graph_nodes_per_gpu": alg["rows"],
                    "target_tokens_per_gpu": int(batch.target_length.sum()),
                    "l2": "flushed between timed steps (256 MB write)", "cuda_graph": not a.no_graph,
-                   "parallelism": f"sentence-sharded x{world}"},
+                   "parallelism": f"sentence-sharded x{world}",
+                   "loss_reduce": "none (one GPU)" if world == 1 or not is_loss else
+                   ("in the statistics kernel, peer stores over NVLink" if exchange is not None else "NCCL all-reduce")},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": tot[1] / a.steps},
         "gpu_launches": step.kernels_per_step * a.steps,
