@@ -435,6 +435,46 @@ class _Kernel:
         _cabi.check(rc, "pcfgnat_copy_links_main_rows")
 
     @staticmethod
+    def extract_links(query, key_left, key_right, gate_logits, prev_output_tokens, pad_index, left_tree_mask,
+                      right_tree_mask, main_chain):
+        """links [B, L, 2, L] f32 as the model's extract_links() forms them from the projected link features
+        (models/...pcfg.py:140-201, max_left == 1): ``query``, ``key_left``, ``key_right`` [B, L, heads, head_dim]
+        (outputs of the three link projections, reshaped), ``gate_logits`` [B, L, heads].  Two library batched
+        GEMMs give the per-head score matrices; one launch does masking, gather, joint log-softmax, head mixture
+        and the -inf rows.  No gradient (decoding / inference)."""
+        _require_cuda()
+        if query.dim() != 4 or key_left.shape != query.shape or key_right.shape != query.shape:
+            raise RuntimeError("query, key_left, key_right must be [batch, prelen, heads, head_dim] and agree")
+        if not query.is_cuda:
+            raise RuntimeError("query must be a CUDA tensor")
+        B, L, H, D = query.shape
+        dev = query.device
+        q = query.to(torch.float32).contiguous()
+        kl = key_left.to(device=dev, dtype=torch.float32).contiguous()
+        kr = key_right.to(device=dev, dtype=torch.float32)
+        gates = gate_logits.to(device=dev, dtype=torch.float32).contiguous()
+        if tuple(gates.shape) != (B, L, H):
+            raise RuntimeError("gate_logits must be [batch, prelen, heads]")
+        if tuple(prev_output_tokens.shape) != (B, L):
+            raise RuntimeError("prev_output_tokens must be [batch, prelen]")
+        u8 = lambda t, n: t.to(device=dev)[:L, :L].ne(0).to(torch.uint8).contiguous() if n == 2 else \
+            t.to(device=dev)[:L].ne(0).to(torch.uint8).contiguous()
+        lm, rm, mc = u8(left_tree_mask, 2), u8(right_tree_mask, 2), u8(main_chain, 1)
+        if tuple(lm.shape) != (L, L) or tuple(rm.shape) != (L, L) or tuple(mc.shape) != (L,):
+            raise RuntimeError("tree masks must cover prelen nodes")
+        nonpad = prev_output_tokens.to(dev).ne(pad_index).to(torch.uint8).contiguous()
+        with torch.cuda.device(dev):
+            krt = kr.permute(0, 2, 3, 1)  # [B, heads, head_dim, L]
+            ac = torch.matmul(q.permute(0, 2, 1, 3), krt).contiguous()   # [B, heads, L, L]
+            bc = torch.matmul(kl.permute(0, 2, 1, 3), krt).contiguous()
+            links = torch.empty((B, L, 2, L), dtype=torch.float32, device=dev)
+            rc = _cabi.lib().pcfgnat_links_from_scores(ac.data_ptr(), bc.data_ptr(), q.data_ptr(), kl.data_ptr(),
+                                                       gates.data_ptr(), nonpad.data_ptr(), lm.data_ptr(), rm.data_ptr(),
+                                                       mc.data_ptr(), B, L, H, D, 1, links.data_ptr(), _stream(dev))
+        _cabi.check(rc, "pcfgnat_links_from_scores")
+        return links
+
+    @staticmethod
     def loss_stats(sentence_loss, target_length):
         """float32 [3] = [sum_b loss_b / n_b over valid sentences, sentences, invalid sentences]: what the
         criterion's scalar is formed from (nat_pcfg_loss.py:117-135), in one launch."""

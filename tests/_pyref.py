@@ -96,3 +96,32 @@ def glance_select(path, pred_tokens, tgt_tokens, prev_output_tokens, target_leng
     glat_prev = prev_output_tokens.masked_fill(keep, 0) + oracle.masked_fill(~keep, 0)
     return {"matchmask": matchmask, "oracle": oracle, "same_num": same_num, "glance_num": glance_nums,
             "keep_word_mask": keep, "glat_prev_output_tokens": glat_prev}
+
+
+def extract_links(q, kl, kr, gate_logits, prev_output_tokens, pad, left_mask, right_mask, main_chain):
+    """Torch restatement (max_left == 1) of what the model's extract_links computes
+    (fs_plugins/models/glat_decomposed_with_link_two_hands_tri_pcfg.py:140-201), from the projected link features
+    q, kl, kr [B, L, heads, D] and gate logits [B, L, heads]:
+    links[b, a, k, c] = logsumexp_h( log_softmax_{(k, c)}( (ab + bc) + ac ) + log_softmax_h(gates) )."""
+    import torch
+
+    B, L, H, D = q.shape
+    q, kl, kr = q.float(), kl.float(), kr.float()
+    scale = D ** 0.5
+    nonpad = prev_output_tokens.ne(pad)
+    left_ok = nonpad[:, None, :] & ~left_mask.bool()[None, :L, :L]                      # [B, a, j]
+    right_ok = nonpad[:, None, :] & ~right_mask.bool()[None, :L, :L] & main_chain.bool()[None, None, :L]
+    use = left_ok.any(-1) & right_ok.any(-1)                                             # [B, a]
+    left_idx = torch.stack([torch.zeros(L, dtype=torch.long), (torch.arange(L) - 1).clamp(min=0)], -1)  # [a, k]
+    kl_opt = kl[:, left_idx]                                                             # [B, a, k, H, D]
+    ab = torch.einsum("bahd,bakhd->bakh", q, kl_opt) / scale
+    ab_ok = torch.gather(left_ok, 2, left_idx[None].expand(B, -1, -1))                   # [B, a, k]
+    ab = ab.masked_fill(~ab_ok[..., None] & use[:, :, None, None], float("-inf"))
+    bc = torch.einsum("bakhd,bchd->bakch", kl_opt, kr) / scale
+    ac = torch.einsum("bahd,bchd->bach", q, kr) / scale
+    ac = ac.masked_fill(~right_ok[..., None] & use[:, :, None, None], float("-inf"))
+    abc = (ab[:, :, :, None, :] + bc) + ac[:, :, None, :, :]                             # [B, a, k, c, H]
+    lp = torch.log_softmax(abc.reshape(B, L, 2 * L, H), 2)
+    lg = torch.log_softmax(gate_logits.float(), -1)
+    links = torch.logsumexp(lp + lg[:, :, None, :], -1).view(B, L, 2, L)
+    return links.masked_fill(~use[:, :, None, None], float("-inf"))

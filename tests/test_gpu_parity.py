@@ -678,6 +678,32 @@ def test_loss_stats_and_glance_select(ops):
             assert torch.equal(got[key].cpu(), val), (key, B, L, T)
 
 
+@pytest.mark.parametrize("case", ["small", "mid"])
+def test_extract_links_against_reference_model(ops, case):
+    """links from the projected link features against the reference model's own extract_links (run on the CPU
+    by tests/golden/make_golden_links.py)."""
+    g = np.load(golden_path("host_extract_links.npz"))
+    heads = int(g[f"{case}_heads"])
+    q, kl, kr = (torch.from_numpy(g[f"{case}_{n}"]) for n in ("q", "kl", "kr"))
+    B, L, E = q.shape
+    shape = (B, L, heads, E // heads)
+    links = ops.get_pcfg_kernel().extract_links(
+        q.view(shape).to(DEV), kl.view(shape).to(DEV), kr.view(shape).to(DEV), torch.from_numpy(g[f"{case}_gates"]).to(DEV),
+        torch.from_numpy(g[f"{case}_prev"]).to(DEV), 1, torch.from_numpy(g[f"{case}_left_mask"]),
+        torch.from_numpy(g[f"{case}_right_mask"]), torch.from_numpy(g[f"{case}_main_chain"]))
+    want = g[f"{case}_links"]
+    got = links.cpu().numpy()
+    assert got.shape == want.shape
+    assert np.array_equal(np.isfinite(got), np.isfinite(want))
+    fin = np.isfinite(want)
+    assert fin.sum() > 20
+    np.testing.assert_allclose(got[fin], want[fin], rtol=1e-4, atol=1e-5)
+    # the rows of a node are a distribution over (left option, right child)
+    rows = np.isfinite(want).any(axis=(2, 3))
+    mass = np.exp(got[rows].reshape(rows.sum(), -1).astype(np.float64)).sum(-1)
+    np.testing.assert_allclose(mass, 1.0, atol=1e-4)
+
+
 def test_loss_stats_exchange_bounded_wait(ops):
     """The in-kernel exchange of the loss statistics with a peer that never arrives: the wait runs out, the
     status word says so, the statistics hold this rank's part only, and the context stays usable."""

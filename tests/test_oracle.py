@@ -201,3 +201,23 @@ def test_oracle_logsoftmax_gather_against_reference_kernel():
     sel16, probs16 = oracle.logsoftmax_gather(half, sel_idx, True)
     np.testing.assert_allclose(sel16, g["selected_f16_0"], atol=1e-4)
     np.testing.assert_allclose(probs16, g["probs_f16"], atol=1e-3)
+
+
+@pytest.mark.parametrize("case", ["small", "mid"])
+def test_links_restatement_against_reference_model(case):
+    """The torch restatement of extract_links (tests/_pyref.py) against the reference model's own function, whose
+    output tests/golden/make_golden_links.py recorded."""
+    import _pyref
+
+    g = np.load(golden_path("host_extract_links.npz"))
+    heads = int(g[f"{case}_heads"])
+    q, kl, kr = (torch.from_numpy(g[f"{case}_{n}"]) for n in ("q", "kl", "kr"))
+    B, L, E = q.shape
+    shape = (B, L, heads, E // heads)
+    got = _pyref.extract_links(q.view(shape), kl.view(shape), kr.view(shape), torch.from_numpy(g[f"{case}_gates"]),
+                               torch.from_numpy(g[f"{case}_prev"]), 1, torch.from_numpy(g[f"{case}_left_mask"]),
+                               torch.from_numpy(g[f"{case}_right_mask"]), torch.from_numpy(g[f"{case}_main_chain"])).numpy()
+    want = g[f"{case}_links"]
+    assert np.array_equal(np.isfinite(got), np.isfinite(want))
+    fin = np.isfinite(want)
+    np.testing.assert_allclose(got[fin], want[fin], rtol=1e-5, atol=1e-6)
