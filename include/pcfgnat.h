@@ -215,15 +215,18 @@ int pcfgnat_glance_select(const int64_t *path, const int64_t *pred_tokens, const
  * extract_links() (fs_plugins/models/glat_decomposed_with_link_two_hands_tri_pcfg.py:163-199) in one launch —
  * masking of inadmissible children, the gather of the two left options (none, node a-1), the joint log-softmax
  * over (left option, right child) per head, the log-sum-exp mixture of the heads with log-softmax(gate logits),
- * and -inf rows for nodes without an admissible left or right child.  The caller supplies the two score
- * matrices from library batched GEMMs, unscaled: ac [B][heads][L][L] = q . kr^T and bc [B][heads][L][L] = kl . kr^T,
+ * and -inf rows for nodes without an admissible left or right child.  The caller supplies the score matrices from
+ * library batched GEMMs, unscaled and compact (only main-chain nodes have or are right children): with M
+ * main-chain nodes and slot_of [L] int32 = index of a node among them or -1,
+ *   ac [B][heads][M][M]     ac[..][slot(a)][slot(c)] = q[a] . kr[c]
+ *   bc [B][heads][M+1][M]   row 0 = kl[0] . kr[c], row 1 + slot(a) = kl[a-1] . kr[c]
  * and q, kl [B][L][heads][head_dim] f32 (the q . kl products are only needed for two left options per node and
  * are formed here); scores are scaled by 1/sqrt(head_dim) as in the reference.  nonpad [B][L] u8 (token != pad),
  * left_tree_mask, right_tree_mask [L][L] u8 (1 = not allowed), main_chain [L] u8 as lemon_tree.get_mask gives them. */
 int pcfgnat_links_from_scores(const float *ac, const float *bc, const float *q, const float *kl, const float *gate_logits,
                               const uint8_t *nonpad, const uint8_t *left_tree_mask, const uint8_t *right_tree_mask,
-                              const uint8_t *main_chain, int B, int L, int heads, int head_dim, int max_left, float *links,
-                              void *stream);
+                              const uint8_t *main_chain, const int *slot_of, int M, int B, int L, int heads, int head_dim,
+                              int max_left, float *links, void *stream);
 
 /* Copies the rows of a transition tensor that the kernels read — links[b][a][.][.] for main-chain nodes a
  * (odd a at max_left == 1) — from src to dst, both [B][L][max_left+1][L] f32, either of them in host

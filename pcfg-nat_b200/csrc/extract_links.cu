@@ -32,14 +32,23 @@ __device__ __forceinline__ float warp_max_f(float v) {
     return v;
 }
 
-// ac, bc: [B][H][L][L] f32 (ac[b][h][a][c] = q.kr, bc[b][h][j][c] = kl.kr, unscaled); q, kl: [B][L][H][D] f32;
-// gates [B][L][H] f32 (logits); nonpad [B][L] u8; left_mask, right_mask [L][L] u8 (1 = not allowed), main_chain [L] u8.
+// Only main-chain nodes have right children and only main-chain nodes are right children, so the score matrices
+// are compact: with M main-chain nodes and slot_of[node] = index among them (or -1),
+//   ac [B][H][M][M]      ac[b][h][slot(a)][slot(c)] = q[a] . kr[c]
+//   bc [B][H][M + 1][M]  row 0 = kl[0] . kr[c] (no left child), row 1 + slot(a) = kl[a - 1] . kr[c]
+// both unscaled.  q, kl: [B][L][H][D] f32; gates [B][L][H] f32 (logits); nonpad [B][L] u8; left_mask, right_mask
+// [L][L] u8 (1 = not allowed), main_chain [L] u8.  A node that is not on the main chain gets a -inf row.
+// HT: number of heads known at compile time (terms of a cell stay in registers between the two reductions over
+// the heads), or 0 for any number up to kMaxHeads.
+template <int HT>
 __global__ void __launch_bounds__(kLinkThreads)
     links_from_scores_kernel(const float *__restrict__ ac, const float *__restrict__ bc, const float *__restrict__ q,
                              const float *__restrict__ kl, const float *__restrict__ gates,
                              const uint8_t *__restrict__ nonpad, const uint8_t *__restrict__ left_mask,
-                             const uint8_t *__restrict__ right_mask, const uint8_t *__restrict__ main_chain, int L, int H,
-                             int D, float scale, float *__restrict__ links) {
+                             const uint8_t *__restrict__ right_mask, const uint8_t *__restrict__ main_chain,
+                             const int *__restrict__ slot_of, int M, int L, int H, int D, float scale,
+                             float *__restrict__ links) {
+    extern __shared__ uint8_t s_right_ok[];  // [L] right child c admissible for this node
     __shared__ float s_ab[2][kMaxHeads], s_lse[kMaxHeads], s_lg[kMaxHeads];
     const int a = blockIdx.x, b = blockIdx.y;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, n_warps = kLinkThreads / 32;
@@ -50,11 +59,14 @@ __global__ void __launch_bounds__(kLinkThreads)
     for (int j = tid; j < L; j += kLinkThreads) {
         const bool there = np[j] != 0;
         any_left |= there && !left_mask[(size_t)a * L + j];
-        any_right |= there && !right_mask[(size_t)a * L + j] && main_chain[j];
+        const bool r_ok = there && !right_mask[(size_t)a * L + j] && main_chain[j];
+        s_right_ok[j] = r_ok;
+        any_right |= r_ok;
     }
     any_left = __syncthreads_or(any_left);
     any_right = __syncthreads_or(any_right);
-    if (!any_left || !any_right) {
+    const int sa = slot_of[a];
+    if (!any_left || !any_right || sa < 0) {
         for (int i = tid; i < 2 * L; i += kLinkThreads) out[i] = neg_inf();
         return;
     }
@@ -92,15 +104,17 @@ __global__ void __launch_bounds__(kLinkThreads)
     // logit of (k, c) for head h: (ab + bc) + ac, -inf where the right child is not admissible
     auto logit = [&](int h, int k, int c, bool right_ok) {
         if (!right_ok) return neg_inf();
-        const float vac = ac[(((size_t)b * H + h) * L + a) * L + c] * scale;
-        const float vbc = bc[(((size_t)b * H + h) * L + (k ? left1 : 0)) * L + c] * scale;
+        const int sc = slot_of[c];  // >= 0: an admissible right child is a main-chain node
+        const float vac = ac[(((size_t)b * H + h) * M + sa) * M + sc] * scale;
+        const float vbc = bc[(((size_t)b * H + h) * (M + 1) + (k ? 1 + sa : 0)) * M + sc] * scale;
         return (s_ab[k][h] + vbc) + vac;
     };
     // pass 1: log-sum-exp over (k, c) per head
     for (int h = warp; h < H; h += n_warps) {
         float mx = neg_inf(), sum = 0.f;
         for (int c = lane; c < L; c += 32) {
-            const bool right_ok = np[c] && !right_mask[(size_t)a * L + c] && main_chain[c];
+            const bool right_ok = s_right_ok[c];
+            if (!right_ok) continue;
 #pragma unroll
             for (int k = 0; k < 2; k++) {
                 const float v = logit(h, k, c, right_ok);
@@ -121,17 +135,35 @@ __global__ void __launch_bounds__(kLinkThreads)
     // pass 2: mix the heads
     for (int i = tid; i < 2 * L; i += kLinkThreads) {
         const int k = i / L, c = i - k * L;
-        const bool right_ok = np[c] && !right_mask[(size_t)a * L + c] && main_chain[c];
-        float mx = neg_inf();
-        for (int h = 0; h < H; h++) mx = fmaxf(mx, (logit(h, k, c, right_ok) - s_lse[h]) + s_lg[h]);  // fmaxf drops NaN
         float res = neg_inf();
-        if (!isinf(mx)) {
-            float sum = 0.f;
-            for (int h = 0; h < H; h++) {
-                const float t = (logit(h, k, c, right_ok) - s_lse[h]) + s_lg[h];
-                if (t > neg_inf()) sum += expf(t - mx);
+        if (s_right_ok[c]) {
+            if (HT > 0) {
+                float term[HT > 0 ? HT : 1];
+                float mx = neg_inf();
+#pragma unroll
+                for (int h = 0; h < HT; h++) {
+                    term[h] = (logit(h, k, c, true) - s_lse[h]) + s_lg[h];
+                    mx = fmaxf(mx, term[h]);  // fmaxf drops NaN
+                }
+                if (!isinf(mx)) {
+                    float sum = 0.f;
+#pragma unroll
+                    for (int h = 0; h < HT; h++)
+                        if (term[h] > neg_inf()) sum += expf(term[h] - mx);
+                    res = mx + logf(sum);
+                }
+            } else {
+                float mx = neg_inf();
+                for (int h = 0; h < H; h++) mx = fmaxf(mx, (logit(h, k, c, true) - s_lse[h]) + s_lg[h]);
+                if (!isinf(mx)) {
+                    float sum = 0.f;
+                    for (int h = 0; h < H; h++) {
+                        const float t = (logit(h, k, c, true) - s_lse[h]) + s_lg[h];
+                        if (t > neg_inf()) sum += expf(t - mx);
+                    }
+                    res = mx + logf(sum);
+                }
             }
-            res = mx + logf(sum);
         }
         out[i] = res;
     }
@@ -141,12 +173,19 @@ __global__ void __launch_bounds__(kLinkThreads)
 
 int launch_links_from_scores(const float *ac, const float *bc, const float *q, const float *kl, const float *gates,
                              const uint8_t *nonpad, const uint8_t *left_mask, const uint8_t *right_mask,
-                             const uint8_t *main_chain, int B, int L, int H, int D, float *links, cudaStream_t st) {
+                             const uint8_t *main_chain, const int *slot_of, int M, int B, int L, int H, int D,
+                             float *links, cudaStream_t st) {
     if (B == 0) return PCFGNAT_OK;
     if (H > kMaxHeads) return PCFGNAT_ERR_TOO_LARGE;
     const float scale = 1.f / sqrtf((float)D);
-    links_from_scores_kernel<<<dim3(L, B), kLinkThreads, 0, st>>>(ac, bc, q, kl, gates, nonpad, left_mask, right_mask, main_chain,
-                                                                 L, H, D, scale, links);
+    const size_t smem = (size_t)(L + 15) / 16 * 16;
+    if (smem > 40 * 1024) return PCFGNAT_ERR_TOO_LARGE;
+    if (H == 8)
+        links_from_scores_kernel<8><<<dim3(L, B), kLinkThreads, smem, st>>>(ac, bc, q, kl, gates, nonpad, left_mask, right_mask,
+                                                                          main_chain, slot_of, M, L, H, D, scale, links);
+    else
+        links_from_scores_kernel<0><<<dim3(L, B), kLinkThreads, smem, st>>>(ac, bc, q, kl, gates, nonpad, left_mask, right_mask,
+                                                                          main_chain, slot_of, M, L, H, D, scale, links);
     return cuda_rc(cudaGetLastError());
 }
 

@@ -112,6 +112,9 @@ def table_shapes(B, L, T, max_left):
     return (B, Mc, T + 2), (B, L - Mc, T + 2, max_left + 2)
 
 
+_main_chain_cache = {}  # (address of the main-chain mask, prelen) -> node list, slots, left rows
+
+
 class _Kernel:
     """Extension-level API: the functions of the reference's pybind module (pcfg_loss.cpp:75-82)."""
 
@@ -457,20 +460,39 @@ class _Kernel:
             raise RuntimeError("gate_logits must be [batch, prelen, heads]")
         if tuple(prev_output_tokens.shape) != (B, L):
             raise RuntimeError("prev_output_tokens must be [batch, prelen]")
-        u8 = lambda t, n: t.to(device=dev)[:L, :L].ne(0).to(torch.uint8).contiguous() if n == 2 else \
-            t.to(device=dev)[:L].ne(0).to(torch.uint8).contiguous()
-        lm, rm, mc = u8(left_tree_mask, 2), u8(right_tree_mask, 2), u8(main_chain, 1)
+        def u8(t, shape):  # masks prepared once (uint8, on the device, exact size) are used as they are
+            if t.dtype == torch.uint8 and t.device == dev and tuple(t.shape) == shape and t.is_contiguous():
+                return t
+            t = t.to(device=dev)
+            t = t[:L, :L] if len(shape) == 2 else t[:L]
+            return t.ne(0).to(torch.uint8).contiguous()
+
+        lm, rm, mc = u8(left_tree_mask, (L, L)), u8(right_tree_mask, (L, L)), u8(main_chain, (L,))
         if tuple(lm.shape) != (L, L) or tuple(rm.shape) != (L, L) or tuple(mc.shape) != (L,):
             raise RuntimeError("tree masks must cover prelen nodes")
         nonpad = prev_output_tokens.to(dev).ne(pad_index).to(torch.uint8).contiguous()
+        # main-chain nodes: the only ones that have, or are, right children -> compact score matrices
+        key = (mc.data_ptr(), L)
+        cached = _main_chain_cache.get(key)
+        if cached is None:
+            nodes = mc.nonzero().flatten()                                   # [M] main-chain node ids
+            slot_of = torch.full((L,), -1, dtype=torch.int32, device=dev)
+            slot_of[nodes] = torch.arange(nodes.numel(), dtype=torch.int32, device=dev)
+            left_rows = torch.cat([nodes.new_zeros(1), (nodes - 1).clamp(min=0)])  # node 0, then a - 1 per node
+            cached = (mc, nodes, slot_of, left_rows)  # keeps mc alive: its address is the key
+            _main_chain_cache.clear()
+            _main_chain_cache[key] = cached
+        _, nodes, slot_of, left_rows = cached
+        M = nodes.numel()
         with torch.cuda.device(dev):
-            krt = kr.permute(0, 2, 3, 1)  # [B, heads, head_dim, L]
-            ac = torch.matmul(q.permute(0, 2, 1, 3), krt).contiguous()   # [B, heads, L, L]
-            bc = torch.matmul(kl.permute(0, 2, 1, 3), krt).contiguous()
+            krt = kr.index_select(1, nodes).permute(0, 2, 3, 1)                          # [B, heads, head_dim, M]
+            ac = torch.matmul(q.index_select(1, nodes).permute(0, 2, 1, 3), krt).contiguous()   # [B, heads, M, M]
+            bc = torch.matmul(kl.index_select(1, left_rows).permute(0, 2, 1, 3), krt).contiguous()  # [B, heads, M+1, M]
             links = torch.empty((B, L, 2, L), dtype=torch.float32, device=dev)
             rc = _cabi.lib().pcfgnat_links_from_scores(ac.data_ptr(), bc.data_ptr(), q.data_ptr(), kl.data_ptr(),
                                                        gates.data_ptr(), nonpad.data_ptr(), lm.data_ptr(), rm.data_ptr(),
-                                                       mc.data_ptr(), B, L, H, D, 1, links.data_ptr(), _stream(dev))
+                                                       mc.data_ptr(), slot_of.data_ptr(), M, B, L, H, D, 1,
+                                                       links.data_ptr(), _stream(dev))
         _cabi.check(rc, "pcfgnat_links_from_scores")
         return links
 

@@ -256,12 +256,39 @@ class DecodeStep(_GraphedStep):
     ``pad_index``, count [B] i64, predicted length [B] i64)."""
     kernels_per_step = 5  # proj_prepare, proj, proj_merge, viterbi, backtrace
 
-    def __init__(self, weight, B, L, left_tree_mask, device, beta=1.0, pad_index=1, use_graph=True, copy_chunks=2):
+    def __init__(self, weight, B, L, left_tree_mask, device, beta=1.0, pad_index=1, use_graph=True, copy_chunks=2,
+                 link_features=None, right_tree_mask=None, main_chain=None):
+        """link_features=(heads, head_dim): the step takes the projected link features instead of the transition
+        matrix and forms the latter itself (the model's extract_links, models/...pcfg.py:140-201).  Inputs
+        (``load`` order) are then hidden, query, key_left, key_right [B,L,heads,head_dim] f16, gate_logits
+        [B,L,heads] f32, prev_output_tokens [B,L] i64 and output_length; right_tree_mask and main_chain are needed."""
         super().__init__(weight, B, L, device, use_graph, copy_chunks)
         self.mask = left_tree_mask.to(device=self.device, dtype=torch.int64).contiguous()
         self.pad_index = int(pad_index)
         # length penalty of the model: scores / arange(L // 4) ** beta (models/...pcfg.py:488-492)
         self.penalty = (torch.arange(L // 4, device=self.device) ** beta).to(torch.float32).unsqueeze(0)
+        self.link_features = link_features
+        if link_features is not None:
+            heads, dim = link_features
+            dev = self.device
+            self.query, self.key_left, self.key_right = (torch.zeros((B, L, heads, dim), dtype=torch.float16, device=dev)
+                                                         for _ in range(3))
+            self.gate_logits = torch.zeros((B, L, heads), dtype=torch.float32, device=dev)
+            self.prev_output_tokens = torch.full((B, L), self.pad_index, dtype=torch.int64, device=dev)
+            u8 = lambda t: t.to(dev).ne(0).to(torch.uint8).contiguous()
+            self.left_u8, self.right_u8 = u8(left_tree_mask[:L, :L]), u8(right_tree_mask[:L, :L])
+            self.main_u8 = u8(main_chain[:L])
+
+    def _inputs(self):
+        if self.link_features is None:
+            return super()._inputs()
+        return [self.hidden, self.query, self.key_left, self.key_right, self.gate_logits, self.prev_output_tokens,
+                self.output_length]
+
+    def _stage2_inputs(self):
+        if self.link_features is None:
+            return super()._stage2_inputs()
+        return [self.query, self.key_left, self.key_right, self.gate_logits, self.prev_output_tokens]
 
     def _stage1(self, b0=0, b1=None):
         return self.kernel.proj_logsoftmax_gather(self.hidden[b0:b1], self.weight, None, self.output_length[b0:b1], None,
@@ -269,7 +296,11 @@ class DecodeStep(_GraphedStep):
 
     def _stage2(self, em):
         k = self.kernel
-        S, R, Lt, Mt = k.pcfg_viterbi(em["max_lprob"], self.links, self.output_length, 1)
+        links = self.links
+        if self.link_features is not None:
+            links = k.extract_links(self.query, self.key_left, self.key_right, self.gate_logits, self.prev_output_tokens,
+                                    self.pad_index, self.left_u8, self.right_u8, self.main_u8)
+        S, R, Lt, Mt = k.pcfg_viterbi(em["max_lprob"], links, self.output_length, 1)
         tokens, count, pred = k.viterbi_decode_device(S, self.penalty, self.output_length, Lt, R, Mt, em["argmax"],
                                                       self.mask, self.pad_index)
         return tokens, count, pred

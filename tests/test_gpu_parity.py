@@ -704,6 +704,39 @@ def test_extract_links_against_reference_model(ops, case):
     np.testing.assert_allclose(mass, 1.0, atol=1e-4)
 
 
+def test_decode_step_from_link_features(pkg, ops, syn):
+    """DecodeStep fed with the projected link features gives what extract_links + the transition-fed step give."""
+    import importlib
+
+    runtime = importlib.import_module("pcfg_nat_b200.runtime")
+    support_tree = importlib.import_module("pcfg_nat_b200.support_tree")
+    w = syn.Workload("decf", batch=4, vocab=500, hidden=64, src_min=4, src_max=12, kind="viterbi")
+    b = syn.make_batch(w, seed=8)
+    heads, dim = 8, 16
+    g = torch.Generator().manual_seed(3)
+    q, kl, kr = (torch.randn(b.B, b.L, heads, dim, generator=g).half() for _ in range(3))
+    gates = torch.randn(b.B, b.L, heads, generator=g)
+    prev = torch.where(torch.arange(b.L)[None, :] < b.output_length[:, None], 3, 1)
+    lm, rm, mc = support_tree.get_mask(b.L, 1)
+    k = ops.get_pcfg_kernel()
+    links = k.extract_links(q.to(DEV), kl.to(DEV), kr.to(DEV), gates.to(DEV), prev.to(DEV), 1, lm, rm, mc)
+    want = pyref.extract_links(q, kl, kr, gates, prev, 1, lm, rm, mc)
+    assert torch.equal(torch.isfinite(links).cpu(), torch.isfinite(want))
+    fin = torch.isfinite(want)
+    torch.testing.assert_close(links.cpu()[fin], want[fin], rtol=1e-4, atol=1e-5)
+    weight = b.weight.to(DEV)
+    plain = runtime.DecodeStep(weight, b.B, b.L, lm, DEV)
+    plain.load(b.hidden.pin_memory(), links, b.output_length.pin_memory())
+    feat = runtime.DecodeStep(weight, b.B, b.L, lm, DEV, link_features=(heads, dim), right_tree_mask=rm, main_chain=mc)
+    feat.load(b.hidden.pin_memory(), q.pin_memory(), kl.pin_memory(), kr.pin_memory(), gates.pin_memory(),
+              prev.pin_memory(), b.output_length.pin_memory(), overlap=True)
+    for _ in range(2):
+        t1, c1, p1 = [t.clone() for t in plain.run()]
+        t2, c2, p2 = [t.clone() for t in feat.run()]
+    assert torch.equal(t1, t2) and torch.equal(c1, c2) and torch.equal(p1, p2)
+    assert int(c1.min()) >= 1
+
+
 def test_loss_stats_exchange_bounded_wait(ops):
     """The in-kernel exchange of the loss statistics with a peer that never arrives: the wait runs out, the
     status word says so, the statistics hold this rank's part only, and the context stays usable."""
