@@ -211,22 +211,27 @@ int pcfgnat_glance_select(const int64_t *path, const int64_t *pred_tokens, const
                           float context_p, int B, int L, int T, uint8_t *matchmask, int64_t *oracle,
                           int64_t *same_num, int64_t *glance_num, uint8_t *keep, int64_t *glat_prev, void *stream);
 
-/* The transition log-probabilities links [B][L][2][L] f32 from per-head attention scores: the tail of
- * extract_links() (fs_plugins/models/glat_decomposed_with_link_two_hands_tri_pcfg.py:163-199) in one launch —
- * masking of inadmissible children, the gather of the two left options (none, node a-1), the joint log-softmax
- * over (left option, right child) per head, the log-sum-exp mixture of the heads with log-softmax(gate logits),
- * and -inf rows for nodes without an admissible left or right child.  The caller supplies the score matrices from
- * library batched GEMMs, unscaled and compact (only main-chain nodes have or are right children): with M
- * main-chain nodes and slot_of [L] int32 = index of a node among them or -1,
- *   ac [B][heads][M][M]     ac[..][slot(a)][slot(c)] = q[a] . kr[c]
- *   bc [B][heads][M+1][M]   row 0 = kl[0] . kr[c], row 1 + slot(a) = kl[a-1] . kr[c]
- * and q, kl [B][L][heads][head_dim] f32 (the q . kl products are only needed for two left options per node and
- * are formed here); scores are scaled by 1/sqrt(head_dim) as in the reference.  nonpad [B][L] u8 (token != pad),
- * left_tree_mask, right_tree_mask [L][L] u8 (1 = not allowed), main_chain [L] u8 as lemon_tree.get_mask gives them. */
-int pcfgnat_links_from_scores(const float *ac, const float *bc, const float *q, const float *kl, const float *gate_logits,
-                              const uint8_t *nonpad, const uint8_t *left_tree_mask, const uint8_t *right_tree_mask,
-                              const uint8_t *main_chain, const int *slot_of, int M, int B, int L, int heads, int head_dim,
-                              int max_left, float *links, void *stream);
+/* The transition log-probabilities links [B][L][2][L] f32 from the projected link features: extract_links()
+ * after its link projections (fs_plugins/models/glat_decomposed_with_link_two_hands_tri_pcfg.py:163-199) as two
+ * launches around two library batched GEMMs.  Only main-chain nodes have, or are, right children, so everything is
+ * compact over the M main-chain nodes: nodes [M] int32 = their ids (ascending), slot_of [L] int32 = index of a
+ * node among them or -1.
+ *  1. pcfgnat_links_gather_features: q, kl, kr [B][L][heads][head_dim] (dtype PCFGNAT_DTYPE_F16 or PCFGNAT_DTYPE_F32) ->
+ *     float32 GEMM operands qm = q[nodes], krm = kr[nodes] ([B][heads][M][head_dim]) and klm
+ *     ([B][heads][M+1][head_dim]: row 0 = kl[0], "no left child"; row 1 + s = kl[nodes[s] - 1]);
+ *  2. (caller, library GEMMs) ac [B][heads][M][M] = qm krm^T, bc [B][heads][M+1][M] = klm krm^T, unscaled;
+ *  3. pcfgnat_links_from_scores: masking of inadmissible children, the two left options (none, node a-1), the
+ *     joint log-softmax over (left option, right child) per head with scores scaled by 1/sqrt(head_dim), the
+ *     log-sum-exp mixture of the heads with log-softmax(gate_logits [B][L][heads]), -inf rows for nodes without an
+ *     admissible left or right child.  nonpad [B][L] u8 (token != pad); left_tree_mask, right_tree_mask [L][L] u8
+ *     (1 = not allowed) and main_chain [L] u8 as lemon_tree.get_mask gives them. */
+int pcfgnat_links_gather_features(const void *q, const void *kl, const void *kr, int dtype, const int *nodes, int M,
+                                  int B, int L, int heads, int head_dim, float *qm, float *klm, float *krm, void *stream);
+int pcfgnat_links_from_scores(const float *ac, const float *bc, const float *qm, const float *klm,
+                              const float *gate_logits, const uint8_t *nonpad, const uint8_t *left_tree_mask,
+                              const uint8_t *right_tree_mask, const uint8_t *main_chain, const int *slot_of,
+                              const int *nodes, int M, int B, int L, int heads, int head_dim, int max_left, float *links,
+                              void *stream);
 
 /* Copies the rows of a transition tensor that the kernels read — links[b][a][.][.] for main-chain nodes a
  * (odd a at max_left == 1) — from src to dst, both [B][L][max_left+1][L] f32, either of them in host

@@ -266,17 +266,27 @@ int pcfgnat_proj_dlogits(const void *hidden, const void *weight, const int64_t *
                                dlogits, workspace, workspace_bytes, status, static_cast<cudaStream_t>(stream));
 }
 
-int pcfgnat_links_from_scores(const float *ac, const float *bc, const float *q, const float *kl, const float *gate_logits,
-                              const uint8_t *nonpad, const uint8_t *left_tree_mask, const uint8_t *right_tree_mask,
-                              const uint8_t *main_chain, const int *slot_of, int M, int B, int L, int heads, int head_dim,
-                              int max_left, float *links, void *stream) {
+int pcfgnat_links_gather_features(const void *q, const void *kl, const void *kr, int dtype, const int *nodes, int M,
+                                  int B, int L, int heads, int head_dim, float *qm, float *klm, float *krm, void *stream) {
+    if (dtype != PCFGNAT_DTYPE_F32 && dtype != PCFGNAT_DTYPE_F16) return PCFGNAT_ERR_UNSUPPORTED;
+    if (B < 0 || L < 1 || M < 0 || M > L || heads < 1 || head_dim < 1) return PCFGNAT_ERR_INVALID_ARGUMENT;
+    if (B && (!q || !kl || !kr || !nodes || !qm || !klm || !krm)) return PCFGNAT_ERR_INVALID_ARGUMENT;
+    return launch_links_gather(q, kl, kr, dtype == PCFGNAT_DTYPE_F16, nodes, M, B, L, heads, head_dim, qm, klm, krm,
+                               static_cast<cudaStream_t>(stream));
+}
+
+int pcfgnat_links_from_scores(const float *ac, const float *bc, const float *qm, const float *klm,
+                              const float *gate_logits, const uint8_t *nonpad, const uint8_t *left_tree_mask,
+                              const uint8_t *right_tree_mask, const uint8_t *main_chain, const int *slot_of,
+                              const int *nodes, int M, int B, int L, int heads, int head_dim, int max_left, float *links,
+                              void *stream) {
     if (max_left != 1) return PCFGNAT_ERR_UNSUPPORTED;
     if (B < 0 || L < 1 || M < 0 || M > L || heads < 1 || head_dim < 1) return PCFGNAT_ERR_INVALID_ARGUMENT;
-    if (B && (!ac || !bc || !q || !kl || !gate_logits || !nonpad || !left_tree_mask || !right_tree_mask || !main_chain ||
-              !slot_of || !links))
+    if (B && (!ac || !bc || !qm || !klm || !gate_logits || !nonpad || !left_tree_mask || !right_tree_mask || !main_chain ||
+              !slot_of || !nodes || !links))
         return PCFGNAT_ERR_INVALID_ARGUMENT;
-    return launch_links_from_scores(ac, bc, q, kl, gate_logits, nonpad, left_tree_mask, right_tree_mask, main_chain, slot_of,
-                                    M, B, L, heads, head_dim, links, static_cast<cudaStream_t>(stream));
+    return launch_links_from_scores(ac, bc, qm, klm, gate_logits, nonpad, left_tree_mask, right_tree_mask, main_chain,
+                                    slot_of, nodes, M, B, L, heads, head_dim, links, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

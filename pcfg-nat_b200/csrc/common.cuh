@@ -105,10 +105,12 @@ int launch_proj(const void *hidden, const void *weight, const int64_t *targets, 
                 int B, int L, int T, int V, int H, float *match, float *max_lprob, int64_t *argmax, float *lse,
                 void *workspace, size_t ws_bytes, int *status, cudaStream_t st);
 
-int launch_links_from_scores(const float *ac, const float *bc, const float *q, const float *kl, const float *gates,
+int launch_links_gather(const void *q, const void *kl, const void *kr, int is_half, const int *nodes, int M, int B, int L,
+                        int H, int D, float *qm, float *klm, float *krm, cudaStream_t st);
+int launch_links_from_scores(const float *ac, const float *bc, const float *qm, const float *klm, const float *gates,
                              const uint8_t *nonpad, const uint8_t *left_mask, const uint8_t *right_mask,
-                             const uint8_t *main_chain, const int *slot_of, int M, int B, int L, int H, int D,
-                             float *links, cudaStream_t st);
+                             const uint8_t *main_chain, const int *slot_of, const int *nodes, int M, int B, int L, int H,
+                             int D, float *links, cudaStream_t st);
 int launch_proj_dlogits(const void *hidden, const void *weight, const int64_t *targets, const int64_t *ol,
                         const int64_t *tl, const float *lse, const float *grad_match, int B, int L, int T, int V, int H,
                         void *dlogits, void *workspace, size_t ws_bytes, int *status, cudaStream_t st);

@@ -452,14 +452,16 @@ class _Kernel:
             raise RuntimeError("query must be a CUDA tensor")
         B, L, H, D = query.shape
         dev = query.device
-        q = query.to(torch.float32).contiguous()
-        kl = key_left.to(device=dev, dtype=torch.float32).contiguous()
-        kr = key_right.to(device=dev, dtype=torch.float32)
+        dt = query.dtype if query.dtype in (torch.float16, torch.float32) else torch.float32
+        q = query.to(dt).contiguous()
+        kl = key_left.to(device=dev, dtype=dt).contiguous()
+        kr = key_right.to(device=dev, dtype=dt).contiguous()
         gates = gate_logits.to(device=dev, dtype=torch.float32).contiguous()
         if tuple(gates.shape) != (B, L, H):
             raise RuntimeError("gate_logits must be [batch, prelen, heads]")
         if tuple(prev_output_tokens.shape) != (B, L):
             raise RuntimeError("prev_output_tokens must be [batch, prelen]")
+
         def u8(t, shape):  # masks prepared once (uint8, on the device, exact size) are used as they are
             if t.dtype == torch.uint8 and t.device == dev and tuple(t.shape) == shape and t.is_contiguous():
                 return t
@@ -475,24 +477,31 @@ class _Kernel:
         key = (mc.data_ptr(), L)
         cached = _main_chain_cache.get(key)
         if cached is None:
-            nodes = mc.nonzero().flatten()                                   # [M] main-chain node ids
+            nodes = mc.nonzero().flatten().to(torch.int32)                   # [M] main-chain node ids
             slot_of = torch.full((L,), -1, dtype=torch.int32, device=dev)
-            slot_of[nodes] = torch.arange(nodes.numel(), dtype=torch.int32, device=dev)
-            left_rows = torch.cat([nodes.new_zeros(1), (nodes - 1).clamp(min=0)])  # node 0, then a - 1 per node
-            cached = (mc, nodes, slot_of, left_rows)  # keeps mc alive: its address is the key
+            slot_of[nodes.long()] = torch.arange(nodes.numel(), dtype=torch.int32, device=dev)
+            cached = (mc, nodes, slot_of)  # keeps mc alive: its address is the key
             _main_chain_cache.clear()
             _main_chain_cache[key] = cached
-        _, nodes, slot_of, left_rows = cached
+        _, nodes, slot_of = cached
         M = nodes.numel()
+        lib = _cabi.lib()
         with torch.cuda.device(dev):
-            krt = kr.index_select(1, nodes).permute(0, 2, 3, 1)                          # [B, heads, head_dim, M]
-            ac = torch.matmul(q.index_select(1, nodes).permute(0, 2, 1, 3), krt).contiguous()   # [B, heads, M, M]
-            bc = torch.matmul(kl.index_select(1, left_rows).permute(0, 2, 1, 3), krt).contiguous()  # [B, heads, M+1, M]
+            qm = torch.empty((B, H, M, D), dtype=torch.float32, device=dev)
+            krm = torch.empty((B, H, M, D), dtype=torch.float32, device=dev)
+            klm = torch.empty((B, H, M + 1, D), dtype=torch.float32, device=dev)
+            rc = lib.pcfgnat_links_gather_features(q.data_ptr(), kl.data_ptr(), kr.data_ptr(),
+                                                   1 if dt == torch.float16 else 0, nodes.data_ptr(), M, B,  # PCFGNAT_DTYPE_*
+                                                   L, H, D, qm.data_ptr(), klm.data_ptr(), krm.data_ptr(), _stream(dev))
+            _cabi.check(rc, "pcfgnat_links_gather_features")
+            krt = krm.transpose(-1, -2)
+            ac = torch.matmul(qm, krt)    # [B, heads, M, M]
+            bc = torch.matmul(klm, krt)   # [B, heads, M+1, M]
             links = torch.empty((B, L, 2, L), dtype=torch.float32, device=dev)
-            rc = _cabi.lib().pcfgnat_links_from_scores(ac.data_ptr(), bc.data_ptr(), q.data_ptr(), kl.data_ptr(),
-                                                       gates.data_ptr(), nonpad.data_ptr(), lm.data_ptr(), rm.data_ptr(),
-                                                       mc.data_ptr(), slot_of.data_ptr(), M, B, L, H, D, 1,
-                                                       links.data_ptr(), _stream(dev))
+            rc = lib.pcfgnat_links_from_scores(ac.data_ptr(), bc.data_ptr(), qm.data_ptr(), klm.data_ptr(),
+                                               gates.data_ptr(), nonpad.data_ptr(), lm.data_ptr(), rm.data_ptr(),
+                                               mc.data_ptr(), slot_of.data_ptr(), nodes.data_ptr(), M, B, L, H, D, 1,
+                                               links.data_ptr(), _stream(dev))
         _cabi.check(rc, "pcfgnat_links_from_scores")
         return links
 
