@@ -153,12 +153,39 @@ template <int TRIPS>
 __global__ void __launch_bounds__(kCThreads, 1)
     inside_cluster_kernel(const float *__restrict__ match_all, const float *__restrict__ links,
                           const int64_t *__restrict__ ol, const int64_t *__restrict__ tl, int L, int T, float *S,
-                          float *C, float *loss, int *status, int Mc, int Lt, int cs, int rows_cap, int lk_stride) {
+                          float *C, float *loss, int *status, int Mc, int Lt, int cs, int rows_cap, int lk_stride,
+                          int B, int wide) {
     extern __shared__ float smem[];
     cg::cluster_group cluster = cg::this_cluster();
-    const int NC = (int)cluster.num_blocks(), crank = (int)cluster.block_rank();
-    const int b = blockIdx.x / NC;
+    const int crank = (int)cluster.block_rank();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    // wide < 0: every sentence gets the whole cluster.  wide >= 0 (batches with more sentences than half the
+    // SMs): the clusters take the sentences in order of decreasing cost m * n, the `wide` costliest get the whole
+    // cluster and for the others only the first CTA works (the second leaves at once and frees its SM), so that
+    // the long sentences, which set the kernel's time, run on two SMs while every sentence still starts at once.
+    int NC = (int)cluster.num_blocks();
+    int b = blockIdx.x / NC;
+    if (wide >= 0) {
+        __shared__ int s_b;
+        const int want = b;  // this cluster takes the sentence of this cost rank
+        for (int i = tid; i < B; i += kCThreads) {
+            const long long mi = ol[i], ni = tl[i];
+            const long long ci = lengths_ok((int)mi, (int)ni, L, T) ? mi * ni : 0;
+            int before = 0;
+            for (int j = 0; j < B; j++) {
+                const long long mj = ol[j], nj = tl[j];
+                const long long cj = lengths_ok((int)mj, (int)nj, L, T) ? mj * nj : 0;
+                before += cj > ci || (cj == ci && j < i);
+            }
+            if (before == want) s_b = i;
+        }
+        __syncthreads();
+        b = s_b;
+        if (want >= wide) {
+            if (crank > 0) return;  // before any cluster barrier; nothing of this CTA is touched by the first one
+            NC = 1;
+        }
+    }
     const int ctid = crank * kCThreads + tid, cthreads = NC * kCThreads;  // thread index inside the cluster
     const int W = T + 2;
     const int m = (int)ol[b], n = (int)tl[b];
@@ -511,8 +538,20 @@ int launch_inside(const float *match_all, const float *links, const int64_t *ol,
         g.rows_cap = (Mc + g.nc - 1) / g.nc;
         g.smem_in = ((size_t)3 * g.cs + (size_t)2 * g.rows_cap * g.lk_stride + (size_t)3 * g.rows_cap * (T + 2)) * sizeof(float);
         if (g.smem_in > (size_t)kSmemLimit - 1024) break;
+        if (TRIPS > 0 && g.nc == 1) {
+            // more sentences than half the SMs: clusters of two, of which only the costliest sentences use both
+            // CTAs (see the kernel); every CTA can hold a whole chain, so the shared memory is that of one CTA
+            int dev = 0, sms = 148;
+            if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+            const int wide = sms - B;
+            if (wide > 0 && B <= 256 && Mc > 16 && !getenv("PCFGNAT_DP_CLUSTER_SIZE")) {
+                int rc = launch_cluster(inside_cluster_kernel<TRIPS>, B, 2, g.smem_in, st, match_all, links, ol, tl, L, T,
+                                        S, C, loss, status, Mc, Lt, g.cs, g.rows_cap, g.lk_stride, B, wide);
+                if (rc != PCFGNAT_ERR_UNSUPPORTED) return rc;
+            }
+        }
         int rc = launch_cluster(inside_cluster_kernel<TRIPS>, B, g.nc, g.smem_in, st, match_all, links, ol, tl, L, T, S,
-                                C, loss, status, Mc, Lt, g.cs, g.rows_cap, g.lk_stride);
+                                C, loss, status, Mc, Lt, g.cs, g.rows_cap, g.lk_stride, B, -1);
         if (rc != PCFGNAT_ERR_UNSUPPORTED) return rc;
     }
     return PCFGNAT_ERR_UNSUPPORTED;
