@@ -305,6 +305,32 @@ def test_logsoftmax_gather_reference_golden_and_autograd(ops):
     np.testing.assert_allclose(xb.grad.cpu().numpy(), xa.grad.cpu().numpy(), atol=1e-5)
 
 
+def test_fused_loss_many_sentences_mixed_cluster_widths(ops, syn, monkeypatch):
+    """More sentences than half the SMs: the fused forward + backward runs its inside pass as cost-ordered clusters
+    of two in which only the costliest sentences use both CTAs.  Loss and gradients against the oracle, with an
+    invalid sentence and wildly different lengths in the batch."""
+    monkeypatch.delenv("PCFGNAT_DP_KERNEL", raising=False)
+    monkeypatch.delenv("PCFGNAT_DP_CLUSTER_SIZE", raising=False)
+    monkeypatch.delenv("PCFGNAT_EXACT_ORDER", raising=False)
+    b, ma = _loss_inputs(syn, syn.Workload("many", batch=97, vocab=40, hidden=8, src_min=2, src_max=24,
+                                           emissions="logits"), 21)
+    ol, tl = b.output_length.clone(), b.target_length.clone()
+    tl[5] = 0  # invalid: skipped, -inf loss, zero gradients
+    So, Co = oracle.pcfg_loss(ma.numpy(), b.links.numpy(), ol.numpy(), tl.numpy())
+    go = np.ones(b.B, np.float32)
+    mgo, lgo = oracle.pcfg_loss_backward(go, So, Co, ma.numpy(), b.links.numpy(), ol.numpy(), tl.numpy())
+    ops.read_status(DEV)
+    loss, mg, lg = ops.get_pcfg_kernel().pcfg_loss_fwd_bwd(ma.to(DEV), b.links.to(DEV), ol.to(DEV), tl.to(DEV))
+    want = So[:, 0, 0].copy()
+    want[5] = -np.inf
+    _rel_close(loss.cpu().numpy(), want, 1e-4)
+    ok = np.isfinite(want)
+    np.testing.assert_allclose(mg.cpu().numpy()[ok], mgo[ok], rtol=1e-3, atol=2e-6)
+    np.testing.assert_allclose(lg.cpu().numpy()[ok], lgo[ok], rtol=1e-3, atol=2e-6)
+    assert float(mg[5].abs().sum()) == 0.0 and float(lg[5].abs().sum()) == 0.0
+    assert ops.read_status(DEV) & 1  # PCFGNAT_STATUS_BAD_LENGTH
+
+
 def test_invalid_sentences_are_skipped_not_faulted(dp_kernel, ops, syn):
     b, ma = _loss_inputs(syn, syn.Workload("bad", batch=4, vocab=50, hidden=8, src_min=4, src_max=6,
                                            emissions="logits"), 9)
