@@ -97,6 +97,36 @@ __device__ __forceinline__ void viterbi_store(float best, int key, int a, int Q,
     Mtb[o] = bj;
 }
 
+// ---- column exchange without a cluster barrier: a finished node is sent to every CTA of the cluster with
+// st.async, which also counts its bytes on a barrier in the receiving CTA; a CTA starts the next length when its
+// own barrier has seen the whole column.  Two barriers alternate by length (a CTA can be at most one length
+// ahead of a peer: it needs the peer's part of the current column), and the columns roll over four buffers, so
+// that the buffer written at length l + 1 is not one that a CTA still at length l reads.
+__device__ __forceinline__ uint32_t vit_smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ uint32_t vit_map_to_cta(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void vit_store_async(uint32_t cluster_addr, float v, uint32_t cluster_bar) {
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];" ::"r"(cluster_addr),
+                 "r"(__float_as_uint(v)), "r"(cluster_bar)
+                 : "memory");
+}
+// Bounded wait for the column of a length; false when the limit ran out (a peer that never arrives).
+__device__ __forceinline__ bool vit_wait_column(uint32_t bar, uint32_t parity) {
+    for (uint32_t it = 0; it < (1u << 22); ++it) {
+        uint32_t ok;
+        asm volatile(
+            "{ .reg .pred p; mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2; selp.b32 %0, 1, 0, p; }"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+
 __global__ void __launch_bounds__(kVitThreads, 1)
     viterbi_cluster_kernel(const float *__restrict__ ob_lprob, const float *__restrict__ links,
                            const int64_t *__restrict__ ol, int L, float *S, int64_t *R, int64_t *Lt, int64_t *Mt,
@@ -125,8 +155,8 @@ __global__ void __launch_bounds__(kVitThreads, 1)
     }
     const int Mb = main_nodes_below(m);
     const int my_rows = Mb > crank ? (Mb - crank + NC - 1) / NC : 0;  // nodes id = crank + NC * r
-    float *col = smem;                // [3][cs] rolling S columns of the whole chain (replicated per CTA)
-    float *lk0 = col + 3 * cs;        // [rows_cap][lk_stride] links[a][0][c] + 0 of this CTA's nodes, by child slot
+    float *col = smem;                // [4][cs] rolling S columns of the whole chain (replicated per CTA)
+    float *lk0 = col + 4 * cs;        // [rows_cap][lk_stride] links[a][0][c] + 0 of this CTA's nodes, by child slot
     float *lk1 = lk0 + (size_t)rows_cap * lk_stride;  // links[a][1][c] + ob[a-1]
     // results of this CTA's nodes, flushed to global memory after the last length: a global store inside
     // the loop would make every cluster barrier (a release) wait for it to reach L2
@@ -142,7 +172,13 @@ __global__ void __launch_bounds__(kVitThreads, 1)
             lk1[r * lk_stride + ci] = __ldg(row + L + 2 * ci + 1) + olf;
         }
     }
-    for (int i = tid; i < 3 * cs; i += kVitThreads) col[i] = neg_inf();  // lengths 0 and 1; slots >= Mb for good
+    __shared__ __align__(8) uint64_t col_bar[2];
+    for (int i = tid; i < 4 * cs; i += kVitThreads) col[i] = neg_inf();  // lengths 0 and 1; slots >= Mb for good
+    if (tid == 0) {
+        for (int i = 0; i < 2; i++)
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(vit_smem_u32(&col_bar[i])) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
     __syncthreads();
     // S[m-1][1] = ob[m-1] (pcfg_viterbi.cu:58); it feeds the recurrence only if m-1 is a main-chain node
     if (tid == 0 && ((m - 1) & 1)) col[1 * cs + (m - 2) / 2] = __ldg(ob + (m - 1));  // every CTA fills its own copy
@@ -154,10 +190,15 @@ __global__ void __launch_bounds__(kVitThreads, 1)
     const int x = lane & 3;
     const int prio = ((x & 1) << 1) | (x >> 1);  // reference thread 0 wins ties, then 2, 1, 3
     const int n_len = m / 4;
+    bool arrived = true;
     for (int len = 2; len < n_len; len++) {
-        const float *S1 = col + ((len - 1) % 3) * cs;
-        const float *S2 = col + ((len - 2) % 3) * cs;
-        float *S0 = col + (len % 3) * cs;
+        const float *S1 = col + ((len - 1) & 3) * cs;
+        const float *S2 = col + ((len - 2) & 3) * cs;
+        float *S0 = col + (len & 3) * cs;
+        const uint32_t bar = vit_smem_u32(&col_bar[len & 1]);
+        if (NC > 1 && tid == 0)  // this CTA expects the whole column of this length: one value per node of the chain
+            asm volatile("{ .reg .b64 st; mbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1; }" ::"r"(bar), "r"(4 * Mb)
+                         : "memory");
         for (int r = warp; r < my_rows; r += kVitWarps) {
             const int id = crank + NC * r;
             const float *r0 = lk0 + r * lk_stride, *r1 = lk1 + r * lk_stride;
@@ -165,14 +206,23 @@ __global__ void __launch_bounds__(kVitThreads, 1)
             int key;
             viterbi_node(id, Mb, lane, prio, __ldg(ob + 2 * id + 1), S1, S2, [&](int ci) { return r0[ci]; },
                          [&](int ci) { return r1[ci]; }, best, key);
-            if (lane < NC) *cluster.map_shared_rank(S0 + id, lane) = best;  // into every CTA's column
+            if (NC > 1) {  // into every CTA's column, counted on that CTA's barrier of this length
+                if (lane < NC) vit_store_async(vit_map_to_cta(vit_smem_u32(S0 + id), lane), best, vit_map_to_cta(bar, lane));
+            } else if (lane == 0) {
+                S0[id] = best;
+            }
             if (lane == 0) {
                 own_v[r * Q + len] = best;
                 own_k[r * Q + len] = key;
             }
         }
-        if (NC > 1) cluster.sync(); else __syncthreads();
+        if (NC > 1) arrived = vit_wait_column(bar, ((len - 2) >> 1) & 1) && arrived;
+        else __syncthreads();
     }
+    if (!arrived) flag(status, PCFGNAT_STATUS_TIMEOUT);
+    // no CTA leaves (its shared memory with it) while a peer may still send to it: the last column has arrived
+    // everywhere once every CTA has passed its last wait
+    if (NC > 1) cluster.sync();
     for (int i = tid; i < my_rows * (n_len - 2); i += kVitThreads) {  // computed cells: lengths 2 .. n_len-1
         const int r = i / (n_len - 2), len = 2 + i - r * (n_len - 2);
         viterbi_store(own_v[r * Q + len], own_k[r * Q + len], 2 * (crank + NC * r) + 1, Q, len, Sb, Rb, Lb, Mtb);
@@ -340,7 +390,7 @@ int launch_viterbi(const float *ob, const float *links, const int64_t *ol, int B
     if (dp_kernel_choice() == kDpRows) nc = 32;  // skips the loop below
     for (; nc <= 16; nc *= 2) {
         const int rows_cap = (Mc + nc - 1) / nc;
-        const size_t smem = ((size_t)3 * cs + (size_t)2 * rows_cap * lk_stride + (size_t)2 * rows_cap * Q) * sizeof(float);
+        const size_t smem = ((size_t)4 * cs + (size_t)2 * rows_cap * lk_stride + (size_t)2 * rows_cap * Q) * sizeof(float);
         if (smem > (size_t)kSmemLimit - 1024) continue;
         if (ensure_dynamic_smem(viterbi_cluster_kernel, smem) != cudaSuccess) return PCFGNAT_ERR_CUDA;
         if (nc > 8 && cudaFuncSetAttribute(viterbi_cluster_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) !=
