@@ -34,6 +34,37 @@ __device__ __forceinline__ float fast_exp(float x) {
     return y;
 }
 
+// ---- column exchange without a cluster barrier: a finished node is sent to every CTA of the cluster with
+// st.async, which also counts its bytes on a barrier in the receiving CTA; a CTA starts the next step when its
+// own barrier has seen the whole column.  Two barriers alternate by step (a CTA can be at most one step
+// ahead of a peer: it needs the peer's part of the current column), and the columns roll over four buffers, so
+// that the buffer written at step t + 1 is not one that a CTA still at step t reads.  Used by the cluster DP
+// kernels (Viterbi, inside pass).
+__device__ __forceinline__ uint32_t dsm_smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ uint32_t dsm_map_to_cta(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void dsm_store_async(uint32_t cluster_addr, float v, uint32_t cluster_bar) {
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];" ::"r"(cluster_addr),
+                 "r"(__float_as_uint(v)), "r"(cluster_bar)
+                 : "memory");
+}
+// Bounded wait for the column of a step; false when the limit ran out (a peer that never arrives).
+__device__ __forceinline__ bool dsm_wait_column(uint32_t bar, uint32_t parity) {
+    for (uint32_t it = 0; it < (1u << 22); ++it) {
+        uint32_t ok;
+        asm volatile(
+            "{ .reg .pred p; mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2; selp.b32 %0, 1, 0, p; }"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+
 inline int cuda_rc(cudaError_t e) { return e == cudaSuccess ? PCFGNAT_OK : PCFGNAT_ERR_CUDA; }
 
 // Raises a kernel's dynamic shared-memory limit, remembering per device the largest value already

@@ -220,8 +220,8 @@ __global__ void __launch_bounds__(kCThreads, 1)
     const int Mb = main_nodes_below(m);
     const int last = (m - 2) / 2;
     const int my_rows = Mb > crank ? (Mb - crank + NC - 1) / NC : 0;  // nodes ai = crank + NC * r
-    float *col = smem;                 // [3][cs] rolling S columns of the whole chain (replicated per CTA)
-    float *lk0 = col + 3 * cs;         // [rows_cap][lk_stride] links[a][0][c] of this CTA's nodes, by child slot
+    float *col = smem;                 // [4][cs] rolling S columns of the whole chain (replicated per CTA)
+    float *lk0 = col + 4 * cs;         // [rows_cap][lk_stride] links[a][0][c] of this CTA's nodes, by child slot
     float *lk1 = lk0 + (size_t)rows_cap * lk_stride;
     // S entries of this CTA's nodes, flushed to global memory after the last step: a global store
     // inside the step loop would make every cluster barrier (a release) wait for it to reach L2
@@ -243,21 +243,33 @@ __global__ void __launch_bounds__(kCThreads, 1)
             lk1[r * lk_stride + ci] = __ldg(row + L + 2 * ci + 1);
         }
     }
-    for (int i = tid; i < 3 * cs; i += kCThreads) col[i] = neg_inf();
+    // columns are exchanged with st.async counted on two alternating barriers (common.cuh), not a cluster barrier
+    __shared__ __align__(8) uint64_t col_bar[2];
+    for (int i = tid; i < 4 * cs; i += kCThreads) col[i] = neg_inf();
+    if (tid == 0) {
+        for (int i = 0; i < 2; i++)
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(dsm_smem_u32(&col_bar[i])) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
     __syncthreads();
     if (tid == 0) {
         const float v = __ldg(mat + (size_t)(m - 1) * T + (n - 1));
-        col[((n - 1) % 3) * cs + last] = v;  // every CTA fills its own copy
+        col[((n - 1) & 3) * cs + last] = v;  // every CTA fills its own copy
     }
     // all copies initialised before anybody stores into a neighbour's; also orders the -inf fill of the
     // global table (done by threads of any CTA of the cluster) before the cells written below
     if (NC > 1) cluster.sync(); else __syncthreads();
     if (ctid == 0) Sb[(size_t)last * W + (n - 1)] = __ldg(mat + (size_t)(m - 1) * T + (n - 1));
 
+    bool arrived = true;
     for (int start = n - 2; start >= 0; start--) {
-        const float *S1 = col + ((start + 1) % 3) * cs;
-        const float *S2 = col + ((start + 2) % 3) * cs;
-        float *S0 = col + (start % 3) * cs;
+        const float *S1 = col + ((start + 1) & 3) * cs;
+        const float *S2 = col + ((start + 2) & 3) * cs;
+        float *S0 = col + (start & 3) * cs;
+        const uint32_t bar = dsm_smem_u32(&col_bar[start & 1]);
+        if (NC > 1 && tid == 0)  // this CTA expects the whole column of this step: one value per node of the chain
+            asm volatile("{ .reg .b64 st; mbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1; }" ::"r"(bar), "r"(4 * Mb)
+                         : "memory");
         for (int r = warp; r < my_rows; r += kCWarps) {
             const int ai = crank + NC * r, a = 2 * ai + 1;
             const bool has_leaf = a >= 3;
@@ -328,11 +340,17 @@ __global__ void __launch_bounds__(kCThreads, 1)
             res = isinf(mx) ? mx : logf(sum) + mx;
             }
             }
-            if (lane < NC) *cluster.map_shared_rank(S0 + ai, lane) = res;  // into every CTA's column
+            if (NC > 1) {  // into every CTA's column, counted on that CTA's barrier of this step
+                if (lane < NC) dsm_store_async(dsm_map_to_cta(dsm_smem_u32(S0 + ai), lane), res, dsm_map_to_cta(bar, lane));
+            } else if (lane == 0) {
+                S0[ai] = res;
+            }
             if (lane == 0) own[r * W + start] = res;
         }
-        if (NC > 1) cluster.sync(); else __syncthreads();
+        if (NC > 1) arrived = dsm_wait_column(bar, (((n - 2) - start) >> 1) & 1) && arrived;
+        else __syncthreads();
     }
+    if (!arrived) flag(status, PCFGNAT_STATUS_TIMEOUT);
     for (int i = tid; i < my_rows * (n - 1); i += kCThreads) {  // computed cells: columns 0 .. n-2
         const int r = i / (n - 1), t = i - r * (n - 1);
         Sb[(size_t)(crank + NC * r) * W + t] = own[r * W + t];
@@ -481,7 +499,7 @@ ClusterGeometry cluster_geometry(int B, int Mc, int W) {
         g.rows_cap = (Mc + nc - 1) / nc;
         const size_t lk = (size_t)2 * g.rows_cap * g.lk_stride * sizeof(float);
         const size_t own = (size_t)g.rows_cap * W * sizeof(float);
-        g.smem_in = (size_t)3 * g.cs * sizeof(float) + lk + 3 * own;
+        g.smem_in = (size_t)4 * g.cs * sizeof(float) + lk + 3 * own;
         g.smem_out = (size_t)7 * g.cs * sizeof(float) + lk + 2 * own;
         if (g.smem_out <= (size_t)kSmemLimit - 1024) break;
         if (nc >= 16) {
@@ -536,7 +554,7 @@ int launch_inside(const float *match_all, const float *links, const int64_t *ol,
     ClusterGeometry g = cluster_geometry(B, Mc, T + 2);
     for (; g.nc >= 1; g.nc /= 2) {  // fall back to smaller clusters if the GPU cannot co-schedule this size
         g.rows_cap = (Mc + g.nc - 1) / g.nc;
-        g.smem_in = ((size_t)3 * g.cs + (size_t)2 * g.rows_cap * g.lk_stride + (size_t)3 * g.rows_cap * (T + 2)) * sizeof(float);
+        g.smem_in = ((size_t)4 * g.cs + (size_t)2 * g.rows_cap * g.lk_stride + (size_t)3 * g.rows_cap * (T + 2)) * sizeof(float);
         if (g.smem_in > (size_t)kSmemLimit - 1024) break;
         if (TRIPS > 0 && g.nc == 1) {
             // more sentences than half the SMs: clusters of two, of which only the costliest sentences use both

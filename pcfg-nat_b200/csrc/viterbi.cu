@@ -97,36 +97,6 @@ __device__ __forceinline__ void viterbi_store(float best, int key, int a, int Q,
     Mtb[o] = bj;
 }
 
-// ---- column exchange without a cluster barrier: a finished node is sent to every CTA of the cluster with
-// st.async, which also counts its bytes on a barrier in the receiving CTA; a CTA starts the next length when its
-// own barrier has seen the whole column.  Two barriers alternate by length (a CTA can be at most one length
-// ahead of a peer: it needs the peer's part of the current column), and the columns roll over four buffers, so
-// that the buffer written at length l + 1 is not one that a CTA still at length l reads.
-__device__ __forceinline__ uint32_t vit_smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ uint32_t vit_map_to_cta(uint32_t addr, uint32_t rank) {
-    uint32_t r;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
-    return r;
-}
-__device__ __forceinline__ void vit_store_async(uint32_t cluster_addr, float v, uint32_t cluster_bar) {
-    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];" ::"r"(cluster_addr),
-                 "r"(__float_as_uint(v)), "r"(cluster_bar)
-                 : "memory");
-}
-// Bounded wait for the column of a length; false when the limit ran out (a peer that never arrives).
-__device__ __forceinline__ bool vit_wait_column(uint32_t bar, uint32_t parity) {
-    for (uint32_t it = 0; it < (1u << 22); ++it) {
-        uint32_t ok;
-        asm volatile(
-            "{ .reg .pred p; mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2; selp.b32 %0, 1, 0, p; }"
-            : "=r"(ok)
-            : "r"(bar), "r"(parity)
-            : "memory");
-        if (ok) return true;
-    }
-    return false;
-}
-
 __global__ void __launch_bounds__(kVitThreads, 1)
     viterbi_cluster_kernel(const float *__restrict__ ob_lprob, const float *__restrict__ links,
                            const int64_t *__restrict__ ol, int L, float *S, int64_t *R, int64_t *Lt, int64_t *Mt,
@@ -176,7 +146,7 @@ __global__ void __launch_bounds__(kVitThreads, 1)
     for (int i = tid; i < 4 * cs; i += kVitThreads) col[i] = neg_inf();  // lengths 0 and 1; slots >= Mb for good
     if (tid == 0) {
         for (int i = 0; i < 2; i++)
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(vit_smem_u32(&col_bar[i])) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(dsm_smem_u32(&col_bar[i])) : "memory");
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
@@ -195,7 +165,7 @@ __global__ void __launch_bounds__(kVitThreads, 1)
         const float *S1 = col + ((len - 1) & 3) * cs;
         const float *S2 = col + ((len - 2) & 3) * cs;
         float *S0 = col + (len & 3) * cs;
-        const uint32_t bar = vit_smem_u32(&col_bar[len & 1]);
+        const uint32_t bar = dsm_smem_u32(&col_bar[len & 1]);
         if (NC > 1 && tid == 0)  // this CTA expects the whole column of this length: one value per node of the chain
             asm volatile("{ .reg .b64 st; mbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1; }" ::"r"(bar), "r"(4 * Mb)
                          : "memory");
@@ -207,7 +177,7 @@ __global__ void __launch_bounds__(kVitThreads, 1)
             viterbi_node(id, Mb, lane, prio, __ldg(ob + 2 * id + 1), S1, S2, [&](int ci) { return r0[ci]; },
                          [&](int ci) { return r1[ci]; }, best, key);
             if (NC > 1) {  // into every CTA's column, counted on that CTA's barrier of this length
-                if (lane < NC) vit_store_async(vit_map_to_cta(vit_smem_u32(S0 + id), lane), best, vit_map_to_cta(bar, lane));
+                if (lane < NC) dsm_store_async(dsm_map_to_cta(dsm_smem_u32(S0 + id), lane), best, dsm_map_to_cta(bar, lane));
             } else if (lane == 0) {
                 S0[id] = best;
             }
@@ -216,7 +186,7 @@ __global__ void __launch_bounds__(kVitThreads, 1)
                 own_k[r * Q + len] = key;
             }
         }
-        if (NC > 1) arrived = vit_wait_column(bar, ((len - 2) >> 1) & 1) && arrived;
+        if (NC > 1) arrived = dsm_wait_column(bar, ((len - 2) >> 1) & 1) && arrived;
         else __syncthreads();
     }
     if (!arrived) flag(status, PCFGNAT_STATUS_TIMEOUT);
