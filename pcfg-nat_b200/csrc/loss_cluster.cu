@@ -385,10 +385,10 @@ __global__ void __launch_bounds__(kCThreads, 1)
     }
     const int Mb = main_nodes_below(m);
     const int my_rows = Mb > crank ? (Mb - crank + NC - 1) / NC : 0;  // children ci = crank + NC * r
-    float *gcol = smem;            // [3][cs] rolling G columns of the whole chain (replicated per CTA)
+    float *gcol = smem;            // [4][cs] rolling G columns of the whole chain (replicated per CTA)
     // per-parent scalars of a step, for the whole chain (every CTA needs all of them), double-buffered: those of
     // step s+1 are fetched from global memory while step s is computed
-    float *q0 = gcol + 3 * cs;     // [2][cs] match[a][s] - S[a][s]; -inf where S[a][s] is
+    float *q0 = gcol + 4 * cs;     // [2][cs] match[a][s] - S[a][s]; -inf where S[a][s] is
     float *q1 = q0 + 2 * cs;       // [2][cs] match[a-1][s] + match[a][s+1] - S[a][s]; -inf without a leaf
     float *lt0 = q1 + 2 * cs;      // [rows_cap][lk_stride] links[a][0][c] of this CTA's children, by parent slot
     float *lt1 = lt0 + (size_t)rows_cap * lk_stride;
@@ -418,7 +418,14 @@ __global__ void __launch_bounds__(kCThreads, 1)
         sown[i] = __ldg(Sb + (size_t)(crank + NC * r) * W + t);
     }
     if (tid < Mb && n >= 2) parent_scalars(tid, 0, q0[tid], q1[tid]);
-    for (int i = tid; i < 3 * cs; i += kCThreads) gcol[i] = 0.f;
+    // columns are exchanged with st.async counted on two alternating barriers (common.cuh), not a cluster barrier
+    __shared__ __align__(8) uint64_t col_bar[2];
+    for (int i = tid; i < 4 * cs; i += kCThreads) gcol[i] = 0.f;
+    if (tid == 0) {
+        for (int i = 0; i < 2; i++)
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(dsm_smem_u32(&col_bar[i])) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
     __syncthreads();
     if (tid == 0) {
         const float go = grad_output ? grad_output[b] : 1.f;
@@ -426,10 +433,17 @@ __global__ void __launch_bounds__(kCThreads, 1)
     }
     if (NC > 1) cluster.sync(); else __syncthreads();  // also orders the zero fill of G before the flush below
 
+    bool arrived = true;
     for (int s = 0; s + 1 < n; s++) {
-        const float *g0 = gcol + (s % 3) * cs;
-        float *g1 = gcol + ((s + 1) % 3) * cs;
-        float *g2 = gcol + ((s + 2) % 3) * cs;
+        // four rolling columns: the one that receives the first contributions to column s + 3 at step s + 1 is
+        // not the one (column s) that a CTA still at step s reads
+        const float *g0 = gcol + (s & 3) * cs;
+        float *g1 = gcol + ((s + 1) & 3) * cs;
+        float *g2 = gcol + ((s + 2) & 3) * cs;
+        const uint32_t bar = dsm_smem_u32(&col_bar[s & 1]);
+        if (NC > 1 && tid == 0)  // this CTA expects two values per node of the chain (columns s + 1 and s + 2)
+            asm volatile("{ .reg .b64 st; mbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1; }" ::"r"(bar), "r"(8 * Mb)
+                         : "memory");
         const float *c0 = q0 + (s & 1) * cs, *c1 = q1 + (s & 1) * cs;
         // the next step's scalars: the loads are in flight while this step's nodes are computed
         float n0 = 0.f, n1 = 0.f;
@@ -454,9 +468,15 @@ __global__ void __launch_bounds__(kCThreads, 1)
             acc1 = warp_sum(acc1);
             const float v = g1[ci] + acc0;  // column s+1 is final now (g1[ci] holds the j = 1 part from step s-1)
             __syncwarp();                   // every lane has read g1[ci] before the local copy is overwritten
-            if (lane < NC) {
-                *cluster.map_shared_rank(g1 + ci, lane) = v;
-                *cluster.map_shared_rank(g2 + ci, lane) = acc1;  // first contribution to column s+2
+            if (NC > 1) {
+                if (lane < NC) {
+                    const uint32_t peer_bar = dsm_map_to_cta(bar, lane);
+                    dsm_store_async(dsm_map_to_cta(dsm_smem_u32(g1 + ci), lane), v, peer_bar);
+                    dsm_store_async(dsm_map_to_cta(dsm_smem_u32(g2 + ci), lane), acc1, peer_bar);  // first part of column s+2
+                }
+            } else if (lane == 0) {
+                g1[ci] = v;
+                g2[ci] = acc1;
             }
             if (lane == 0) own[r * W + s + 1] = v;
         }
@@ -464,8 +484,10 @@ __global__ void __launch_bounds__(kCThreads, 1)
             q0[((s + 1) & 1) * cs + tid] = n0;
             q1[((s + 1) & 1) * cs + tid] = n1;
         }
-        if (NC > 1) cluster.sync(); else __syncthreads();
+        __syncthreads();  // the next step's scalars are written before any thread of this CTA reads them
+        if (NC > 1) arrived = dsm_wait_column(bar, (s >> 1) & 1) && arrived;
     }
+    if (!arrived) flag(status, PCFGNAT_STATUS_TIMEOUT);
     for (int i = tid; i < my_rows * (n - 1); i += kCThreads) {  // columns 1 .. n-1 of this CTA's nodes
         const int r = i / (n - 1), t = 1 + (i - r * (n - 1));
         Gb[(size_t)(crank + NC * r) * W + t] = own[r * W + t];
@@ -500,7 +522,7 @@ ClusterGeometry cluster_geometry(int B, int Mc, int W) {
         const size_t lk = (size_t)2 * g.rows_cap * g.lk_stride * sizeof(float);
         const size_t own = (size_t)g.rows_cap * W * sizeof(float);
         g.smem_in = (size_t)4 * g.cs * sizeof(float) + lk + 3 * own;
-        g.smem_out = (size_t)7 * g.cs * sizeof(float) + lk + 2 * own;
+        g.smem_out = (size_t)8 * g.cs * sizeof(float) + lk + 2 * own;
         if (g.smem_out <= (size_t)kSmemLimit - 1024) break;
         if (nc >= 16) {
             g.nc = 0;
@@ -600,7 +622,7 @@ int launch_outside_cluster(const float *grad_output, const float *S, const float
     ClusterGeometry g = cluster_geometry(B, Mc, T + 2);
     for (; g.nc >= 1; g.nc /= 2) {
         g.rows_cap = (Mc + g.nc - 1) / g.nc;
-        g.smem_out = ((size_t)7 * g.cs + (size_t)2 * g.rows_cap * g.lk_stride + (size_t)2 * g.rows_cap * (T + 2)) * sizeof(float);
+        g.smem_out = ((size_t)8 * g.cs + (size_t)2 * g.rows_cap * g.lk_stride + (size_t)2 * g.rows_cap * (T + 2)) * sizeof(float);
         if (g.smem_out > (size_t)kSmemLimit - 1024) break;
         int rc = launch_cluster(outside_cluster_kernel, B, g.nc, g.smem_out, st, grad_output, S, match_all, links, ol, tl,
                                 L, T, G, status, Mc, g.cs, g.rows_cap, g.lk_stride);
