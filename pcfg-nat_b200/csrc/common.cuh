@@ -122,6 +122,7 @@ int launch_outside_cluster(const float *grad_output, const float *S, const float
 enum DpKernel { kDpCluster = 0, kDpBalanced = 1, kDpRows = 2, kDpAuto = 3 };
 DpKernel dp_kernel_choice();
 bool cluster_kernels_pay(int B, int L, int T);
+bool inside_mixed_widths_pay(int B, int L, int T);
 
 int launch_loss_stats(const float *loss, const int64_t *tl, int B, float *stats, cudaStream_t st);
 int launch_loss_stats_exchange(const float *loss, const int64_t *tl, int B, const uint64_t *peer_bufs, int rank, int world,

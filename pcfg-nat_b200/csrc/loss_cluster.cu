@@ -559,6 +559,24 @@ int launch_cluster(Kernel kernel, int B, int nc, size_t smem, cudaStream_t st, A
 
 }  // namespace
 
+// Number of sentences that get both CTAs of a cluster of two when the batch has more sentences than half the
+// SMs (so that one cluster size for all would leave SMs idle or sentences waiting), or 0 when that mode does not
+// apply: the SMs left over once every sentence has one.
+int mixed_width_count(int B, int Mc) {
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (B * 2 <= sms || B >= sms || B > 256 || Mc <= 16 || getenv("PCFGNAT_DP_CLUSTER_SIZE")) return 0;
+    return sms - B;
+}
+
+// True when the inside pass should run on the cluster kernel although cluster_kernels_pay() is false: batches
+// between half the SMs and all of them, where the costliest sentences get a second CTA (mixed widths).
+bool inside_mixed_widths_pay(int B, int L, int T) {
+    const int Mc = main_slots(L, 1);
+    const ClusterGeometry g = cluster_geometry(B, Mc, T + 2);
+    return g.nc == 1 && mixed_width_count(B, Mc) > 0 && g.smem_in <= (size_t)kSmemLimit - 1024;
+}
+
 // True when the batch is small enough that several CTAs per sentence are available (cluster size >= 2),
 // or the chain is too long for the single-CTA kernels to keep its links in shared memory.
 bool cluster_kernels_pay(int B, int L, int T) {
@@ -578,13 +596,11 @@ int launch_inside(const float *match_all, const float *links, const int64_t *ol,
         g.rows_cap = (Mc + g.nc - 1) / g.nc;
         g.smem_in = ((size_t)4 * g.cs + (size_t)2 * g.rows_cap * g.lk_stride + (size_t)3 * g.rows_cap * (T + 2)) * sizeof(float);
         if (g.smem_in > (size_t)kSmemLimit - 1024) break;
-        if (TRIPS > 0 && g.nc == 1) {
+        if (g.nc == 1) {
             // more sentences than half the SMs: clusters of two, of which only the costliest sentences use both
             // CTAs (see the kernel); every CTA can hold a whole chain, so the shared memory is that of one CTA
-            int dev = 0, sms = 148;
-            if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-            const int wide = sms - B;
-            if (wide > 0 && B <= 256 && Mc > 16 && !getenv("PCFGNAT_DP_CLUSTER_SIZE")) {
+            const int wide = mixed_width_count(B, Mc);
+            if (wide > 0) {
                 int rc = launch_cluster(inside_cluster_kernel<TRIPS>, B, 2, g.smem_in, st, match_all, links, ol, tl, L, T,
                                         S, C, loss, status, Mc, Lt, g.cs, g.rows_cap, g.lk_stride, B, wide);
                 if (rc != PCFGNAT_ERR_UNSUPPORTED) return rc;

@@ -215,7 +215,7 @@ int launch_loss_fwd(const float *match_all, const float *links, const int64_t *o
     // (loss_balanced.cu, on request only: measured slower here) and the row-per-thread kernel below, which
     // has no size limit because it can read links from global memory.
     const DpKernel choice = dp_kernel_choice();
-    if (choice == kDpCluster || (choice == kDpAuto && cluster_kernels_pay(B, L, T))) {
+    if (choice == kDpCluster || (choice == kDpAuto && (cluster_kernels_pay(B, L, T) || inside_mixed_widths_pay(B, L, T)))) {
         const int rc = launch_loss_fwd_cluster(match_all, links, ol, tl, B, L, T, S, C, loss, status, st);
         if (rc != PCFGNAT_ERR_UNSUPPORTED) return rc;
     }

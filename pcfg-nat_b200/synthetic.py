@@ -60,6 +60,9 @@ WORKLOADS: Dict[str, Workload] = {
     "viterbi_b64": Workload("viterbi_b64", batch=64, vocab=40000, hidden=512, src_min=10, src_max=60,
                             kind="viterbi"),
     "glance": Workload("glance", batch=64, vocab=40000, hidden=512, fixed_graph=256, fixed_target=64, kind="glance"),
+    # the glancing pass over the training batch itself (what a GLAT training step runs before the loss pass)
+    "glance_train": Workload("glance_train", batch=90, vocab=40000, hidden=512, src_min=20, src_max=40,
+                             hidden_std=0.02, kind="glance"),
 }
 
 

@@ -329,6 +329,14 @@ def test_fused_loss_many_sentences_mixed_cluster_widths(ops, syn, monkeypatch):
     np.testing.assert_allclose(lg.cpu().numpy()[ok], lgo[ok], rtol=1e-3, atol=2e-6)
     assert float(mg[5].abs().sum()) == 0.0 and float(lg[5].abs().sum()) == 0.0
     assert ops.read_status(DEV) & 1  # PCFGNAT_STATUS_BAD_LENGTH
+    # the table-returning operator takes the same mixed widths with the reference's summation order: bit for bit
+    # the table of the 4-lanes-per-node kernel (itself pinned against the reference kernels elsewhere)
+    k = ops.get_pcfg_kernel()
+    S_mixed, _ = k.pcfg_loss(ma.to(DEV), b.links.to(DEV), ol.to(DEV), tl.to(DEV), 1)
+    monkeypatch.setenv("PCFGNAT_DP_KERNEL", "rows")
+    S_rows, _ = k.pcfg_loss(ma.to(DEV), b.links.to(DEV), ol.to(DEV), tl.to(DEV), 1)
+    assert np.array_equal(_bits(S_mixed.cpu().numpy()), _bits(S_rows.cpu().numpy()))
+    ops.read_status(DEV)
 
 
 def test_invalid_sentences_are_skipped_not_faulted(dp_kernel, ops, syn):
