@@ -100,12 +100,35 @@ __device__ __forceinline__ void viterbi_store(float best, int key, int a, int Q,
 __global__ void __launch_bounds__(kVitThreads, 1)
     viterbi_cluster_kernel(const float *__restrict__ ob_lprob, const float *__restrict__ links,
                            const int64_t *__restrict__ ol, int L, float *S, int64_t *R, int64_t *Lt, int64_t *Mt,
-                           int *status, int Mc, int cs, int rows_cap, int lk_stride) {
+                           int *status, int Mc, int cs, int rows_cap, int lk_stride, int B, int wide) {
     extern __shared__ float smem[];
     cg::cluster_group cluster = cg::this_cluster();
-    const int NC = (int)cluster.num_blocks(), crank = (int)cluster.block_rank();
-    const int b = blockIdx.x / NC;
+    const int crank = (int)cluster.block_rank();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    // wide < 0: every sentence gets the whole cluster.  wide >= 0 (more sentences than half the SMs): the clusters
+    // take the sentences in order of decreasing graph length, the `wide` longest get both CTAs of a cluster of
+    // two and for the others only the first CTA works (the second leaves at once and frees its SM).
+    int NC = (int)cluster.num_blocks();
+    int b = blockIdx.x / NC;
+    if (wide >= 0) {
+        __shared__ int s_b;
+        const int want = b;  // this cluster takes the sentence of this length rank
+        for (int i = tid; i < B; i += kVitThreads) {
+            const long long mi = ol[i], ci = (mi >= 2 && mi <= L) ? mi : 0;
+            int before = 0;
+            for (int j = 0; j < B; j++) {
+                const long long mj = ol[j], cj = (mj >= 2 && mj <= L) ? mj : 0;
+                before += cj > ci || (cj == ci && j < i);
+            }
+            if (before == want) s_b = i;
+        }
+        __syncthreads();
+        b = s_b;
+        if (want >= wide) {
+            if (crank > 0) return;  // before any cluster barrier; nothing of this CTA is touched by the first one
+            NC = 1;
+        }
+    }
     const int ctid = crank * kVitThreads + tid, cthreads = NC * kVitThreads;  // thread index inside the cluster
     const int Q = L / 4;
     const int m = (int)ol[b];
@@ -357,9 +380,13 @@ int launch_viterbi(const float *ob, const float *links, const int64_t *ol, int B
         const int want = atoi(v);
         if (want == 1 || want == 2 || want == 4 || want == 8 || want == 16) nc = want;
     }
+    // more sentences than half the SMs but fewer than SMs: clusters of two of which only the longest sentences
+    // use both CTAs (see the kernel); `wide` = the SMs left over once every sentence has one
+    int wide = -1;
+    if (nc == 1 && B * 2 > sms && B < sms && B <= 256 && Mc > 16 && !getenv("PCFGNAT_DP_CLUSTER_SIZE")) wide = sms - B;
     if (dp_kernel_choice() == kDpRows) nc = 32;  // skips the loop below
     for (; nc <= 16; nc *= 2) {
-        const int rows_cap = (Mc + nc - 1) / nc;
+        const int rows_cap = (Mc + nc - 1) / nc;  // also right for mixed widths: nc is 1 there, every CTA may hold a chain
         const size_t smem = ((size_t)4 * cs + (size_t)2 * rows_cap * lk_stride + (size_t)2 * rows_cap * Q) * sizeof(float);
         if (smem > (size_t)kSmemLimit - 1024) continue;
         if (ensure_dynamic_smem(viterbi_cluster_kernel, smem) != cudaSuccess) return PCFGNAT_ERR_CUDA;
@@ -369,13 +396,14 @@ int launch_viterbi(const float *ob, const float *links, const int64_t *ol, int B
             break;
         }
         cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3((unsigned)(B * nc));
+        const int launch_nc = wide >= 0 ? 2 : nc;
+        cfg.gridDim = dim3((unsigned)(B * launch_nc));
         cfg.blockDim = dim3(kVitThreads);
         cfg.dynamicSmemBytes = smem;
         cfg.stream = st;
         cudaLaunchAttribute attr[1];
         attr[0].id = cudaLaunchAttributeClusterDimension;
-        attr[0].val.clusterDim.x = (unsigned)nc;
+        attr[0].val.clusterDim.x = (unsigned)launch_nc;
         attr[0].val.clusterDim.y = 1;
         attr[0].val.clusterDim.z = 1;
         cfg.attrs = attr;
@@ -386,7 +414,7 @@ int launch_viterbi(const float *ob, const float *links, const int64_t *ol, int B
             continue;  // this cluster size cannot be scheduled here: try the next one
         }
         return cuda_rc(cudaLaunchKernelEx(&cfg, viterbi_cluster_kernel, ob, links, ol, L, S, R, Lt, Mt, status, Mc, cs,
-                                          rows_cap, lk_stride));
+                                          rows_cap, lk_stride, B, wide));
     }
     const size_t smem_cols = (size_t)3 * cs * sizeof(float);
     if (smem_cols > (size_t)kSmemLimit - 1024) return PCFGNAT_ERR_TOO_LARGE;

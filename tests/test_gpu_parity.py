@@ -179,6 +179,7 @@ VCASES = [
     ("v_ragged", dict(batch=6, vocab=80, hidden=8, src_min=2, src_max=20), 0),
     ("v_mid", dict(batch=3, vocab=80, hidden=8, src_min=40, src_max=60), 1),
     ("v_global_links", dict(batch=2, vocab=80, hidden=8, fixed_graph=400), 2),
+    ("v_many", dict(batch=93, vocab=40, hidden=8, src_min=2, src_max=30), 3),  # mixed cluster widths by default
 ]
 
 
