@@ -71,6 +71,10 @@ int pcfgnat_loss_bwd(const float *grad_output, const float *S, const float *matc
  * (pcfgnat_loss_workspace_bytes); loss [B] f32 receives S[b][0][0]; gradients are for
  * grad_output == 1. */
 size_t pcfgnat_loss_workspace_bytes(int B, int L, int T, int max_left);
+/* Number of kernels pcfgnat_loss_fwd_bwd / _static launch for this shape on the current device and with the
+ * current environment switches: 2 when the outside pass also sums up both gradients (batches that run one CTA per
+ * sentence), else 3 (inside, outside, gradients).  For launch accounting; 0 for unsupported arguments. */
+int pcfgnat_loss_fwd_bwd_kernels(int B, int L, int T, int max_left);
 int pcfgnat_loss_fwd_bwd(const float *match_all, const float *links, const int64_t *output_length,
                          const int64_t *target_length, int B, int L, int T, int max_left, void *workspace,
                          size_t workspace_bytes, float *loss, float *match_all_grad, float *links_grad, int *status,

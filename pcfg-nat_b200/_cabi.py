@@ -16,6 +16,7 @@ SIGNATURES = {
     "pcfgnat_loss_fwd": (c_int, [c_void] * 4 + [c_int] * 4 + [c_void] * 4),
     "pcfgnat_loss_bwd": (c_int, [c_void] * 6 + [c_int] * 4 + [c_void] * 5),
     "pcfgnat_loss_workspace_bytes": (c_size, [c_int] * 4),
+    "pcfgnat_loss_fwd_bwd_kernels": (c_int, [c_int] * 4),
     "pcfgnat_loss_fwd_bwd": (c_int, [c_void] * 4 + [c_int] * 4 + [c_void, c_size] + [c_void] * 5),
     "pcfgnat_loss_fwd_bwd_static": (c_int, [c_void] * 4 + [c_int] * 4 + [c_void] * 5),
     "pcfgnat_best_tree": (c_int, [c_void] * 5 + [c_int] * 4 + [c_void] * 3),

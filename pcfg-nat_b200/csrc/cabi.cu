@@ -46,9 +46,13 @@ bool exact_order_forced() {
 // Inside pass of the fused forward + backward: the table stays inside the library, so the free-order kernel
 // may build it unless the caller asked for the reference's order or forced a kernel family.
 int launch_loss_fwd_internal(const float *match_all, const float *links, const int64_t *ol, const int64_t *tl, int B,
-                             int L, int T, float *S, float *loss, int *status, cudaStream_t st) {
+                             int L, int T, float *S, float *loss, int *status, cudaStream_t st, float *mg,
+                             bool *shares_in_mg) {
+    *shares_in_mg = false;
     if (!exact_order_forced() && dp_kernel_choice() == kDpAuto) {
-        const int rc = launch_loss_fwd_fast(match_all, links, ol, tl, B, L, T, S, loss, status, st);
+        float *shares = (mg && fused_grad_applies(B, L, T)) ? mg : nullptr;
+        const int rc = launch_loss_fwd_fast(match_all, links, ol, tl, B, L, T, S, loss, status, st, shares);
+        if (rc == PCFGNAT_OK) *shares_in_mg = shares != nullptr;
         if (rc != PCFGNAT_ERR_UNSUPPORTED) return rc;
     }
     return launch_loss_fwd(match_all, links, ol, tl, B, L, T, S, nullptr, loss, status, st);
@@ -116,6 +120,13 @@ size_t pcfgnat_loss_workspace_bytes(int B, int L, int T, int max_left) {
     return 2 * table;  // S and S_grad
 }
 
+int pcfgnat_loss_fwd_bwd_kernels(int B, int L, int T, int max_left) {
+    if (max_left != 1 || bad_dims(B, L, T)) return 0;
+    // the shares the fused backward needs come from the free-order inside pass only
+    const bool free_order = !exact_order_forced() && dp_kernel_choice() == kDpAuto && main_slots(L, 1) <= 256;
+    return free_order && fused_grad_applies(B, L, T) ? 2 : 3;
+}
+
 int pcfgnat_loss_fwd_bwd(const float *match_all, const float *links, const int64_t *output_length,
                          const int64_t *target_length, int B, int L, int T, int max_left, void *workspace,
                          size_t workspace_bytes, float *loss, float *match_all_grad, float *links_grad, int *status,
@@ -131,10 +142,12 @@ int pcfgnat_loss_fwd_bwd(const float *match_all, const float *links, const int64
     float *S = static_cast<float *>(workspace);
     float *G = reinterpret_cast<float *>(static_cast<char *>(workspace) + need / 2);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    int rc = launch_loss_fwd_internal(match_all, links, output_length, target_length, B, L, T, S, loss, status, st);
+    bool shares_in_mg = false;
+    int rc = launch_loss_fwd_internal(match_all, links, output_length, target_length, B, L, T, S, loss, status, st,
+                                      match_all_grad, &shares_in_mg);
     if (rc) return rc;
     return launch_loss_bwd(nullptr, S, match_all, links, output_length, target_length, B, L, T, G, match_all_grad,
-                           links_grad, status, st);
+                           links_grad, status, st, shares_in_mg);
 }
 
 int pcfgnat_best_tree(const float *S, const float *match_all, const float *links, const int64_t *output_length,

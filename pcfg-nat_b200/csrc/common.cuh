@@ -81,7 +81,7 @@ int launch_loss_fwd(const float *match_all, const float *links, const int64_t *o
                     int T, float *S, float *C, float *loss, int *status, cudaStream_t st);
 int launch_loss_bwd(const float *grad_output, const float *S, const float *match_all, const float *links,
                     const int64_t *ol, const int64_t *tl, int B, int L, int T, float *S_grad, float *mg, float *lg,
-                    int *status, cudaStream_t st);
+                    int *status, cudaStream_t st, bool shares_in_mg = false);
 int launch_best_tree(const float *S, const float *match_all, const float *links, const int64_t *ol, const int64_t *tl,
                      int B, int L, int T, int64_t *tree, int *status, cudaStream_t st);
 int launch_viterbi(const float *ob, const float *links, const int64_t *ol, int B, int L, float *S, int64_t *R,
@@ -100,14 +100,21 @@ int launch_logsoftmax_gather(void *logits, int dtype, const int64_t *sel, int64_
 int launch_loss_fwd_balanced(const float *match_all, const float *links, const int64_t *ol, const int64_t *tl, int B,
                              int L, int T, float *S, float *C, float *loss, int *status, cudaStream_t st);
 int launch_outside_balanced(const float *grad_output, const float *S, const float *match_all, const float *links,
-                            const int64_t *ol, const int64_t *tl, int B, int L, int T, float *G, int *status,
-                            cudaStream_t st);
+                            const int64_t *ol, const int64_t *tl, int B, int L, int T, float *G, float *mg, float *lg,
+                            int *status, cudaStream_t st);
 int launch_loss_fwd_cluster(const float *match_all, const float *links, const int64_t *ol, const int64_t *tl, int B,
                             int L, int T, float *S, float *C, float *loss, int *status, cudaStream_t st);
 int launch_loss_fwd_fast(const float *match_all, const float *links, const int64_t *ol, const int64_t *tl, int B, int L,
-                         int T, float *S, float *loss, int *status, cudaStream_t st);
+                         int T, float *S, float *loss, int *status, cudaStream_t st, float *shares = nullptr);
+// Whether the backward pass of this shape runs as the one kernel that takes the emission shares the free-order
+// inside pass leaves in match_all_grad (loss_bwd.cu); the inside pass asks before it writes them.
+bool fused_grad_applies(int B, int L, int T);
+bool outside_balanced_fits_grad(int L);
+// mg: the match_all_grad buffer of the backward pass that follows; *shares_in_mg tells whether the emission
+// shares were left in it (pass that on to launch_loss_bwd).
 int launch_loss_fwd_internal(const float *match_all, const float *links, const int64_t *ol, const int64_t *tl, int B,
-                             int L, int T, float *S, float *loss, int *status, cudaStream_t st);
+                             int L, int T, float *S, float *loss, int *status, cudaStream_t st, float *mg,
+                             bool *shares_in_mg);
 bool exact_order_forced();  // PCFGNAT_EXACT_ORDER=1: the fused forward + backward also keeps the reference's order
 int launch_outside_cluster(const float *grad_output, const float *S, const float *match_all, const float *links,
                            const int64_t *ol, const int64_t *tl, int B, int L, int T, float *G, int *status,

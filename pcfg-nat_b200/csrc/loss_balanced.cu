@@ -257,12 +257,20 @@ __global__ void __launch_bounds__(kBalThreads, 1)
 // ---------------------------------------------------------------------------------------
 // outside pass
 // ---------------------------------------------------------------------------------------
-template <int NIT>
+// GRAD: the weights of a step are also the terms of both gradients (pcfg_loss_backward.cu:223-276, 339-382,
+// 547-602), so the kernel sums them up as it goes instead of leaving that to a second kernel that would compute
+// every weight again.  A pair's weights over the steps give links_grad[a][j][c] (same values, same order as
+// grad_kernel: bit-identical).  The emission gradients need the weights of a parent summed over its children,
+// per j: that is G[a][s] times the share of j in the parent's inside value, which the free-order inside kernel
+// has left in the cells of match_all_grad where the two gradients go (share of j = 0 at [a][s], of j = 1 at
+// [a-1][s]); thread 512 + row turns them into gradients step by step.  All other cells of the dense gradients
+// are zero-filled first.
+template <int NIT, bool GRAD>
 __global__ void __launch_bounds__(kBalThreads, 1)
     outside_balanced_kernel(const float *__restrict__ grad_output, const float *__restrict__ S,
                             const float *__restrict__ match_all, const float *__restrict__ links,
                             const int64_t *__restrict__ ol, const int64_t *__restrict__ tl, int L, int T, float *G,
-                            int *status, int Mc, int cs, int P) {
+                            float *mg, float *lg, int *status, int Mc, int cs, int P) {
     extern __shared__ float smem[];
     const int b = blockIdx.x;
     const int tid = threadIdx.x, nthr = blockDim.x;
@@ -272,7 +280,34 @@ __global__ void __launch_bounds__(kBalThreads, 1)
     const float *lkb = links + (size_t)b * L * 2 * L;
     const float *Sb = S + (size_t)b * Mc * W;
     float *Gb = G + (size_t)b * Mc * W;
+    float *mgb = GRAD ? mg + (size_t)b * L * T : nullptr;
+    float *lgb = GRAD ? lg + (size_t)b * L * 2 * L : nullptr;
     for (int i = tid; i < Mc * W; i += nthr) Gb[i] = 0.f;
+    // GRAD: links_grad is zero-filled in units of 16 bytes where its size and address allow, else of 4
+    const bool lg_vec = GRAD && (((size_t)L * 2 * L) & 3) == 0 && (reinterpret_cast<uintptr_t>(lgb) & 15) == 0;
+    const int lg_units = GRAD ? (int)((size_t)L * 2 * L / (lg_vec ? 4 : 1)) : 0;
+    auto zero_lg = [&](int lo, int hi, int first, int stride) {
+        if (lg_vec)
+            for (int i = lo + first; i < hi; i += stride) reinterpret_cast<float4 *>(lgb)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        else
+            for (int i = lo + first; i < hi; i += stride) lgb[i] = 0.f;
+    };
+    if (GRAD) {
+        // (slicing this fill over the steps, for the threads that idle in a step's second phase, was slower)
+        const bool usable = lengths_ok(m, n, L, T);
+        zero_lg(0, lg_units, tid, nthr);
+        // emission gradients: every cell that does not hold a share (for an unusable sentence: every cell)
+        const int live_rows = usable ? 2 * main_nodes_below(m) : 0;
+        for (int row = tid / T, t = tid - row * T; row < L; ) {
+            const bool share = row >= 1 && row < live_rows && t < n - 1;
+            if (!share) mgb[(size_t)row * T + t] = 0.f;
+            t += nthr;
+            while (t >= T) {
+                t -= T;
+                row++;
+            }
+        }
+    }
     if (!lengths_ok(m, n, L, T)) {
         if (tid == 0) flag(status, PCFGNAT_STATUS_BAD_LENGTH);
         return;
@@ -288,6 +323,8 @@ __global__ void __launch_bounds__(kBalThreads, 1)
     float *lt1 = lt0 + P;
     float *W0 = lt1 + P;
     float *W1 = W0 + P;
+    float *D0 = W1 + P;           // GRAD only: the pair's weights summed over the steps
+    float *D1 = D0 + P;
 
     // strict triangle: column c = 1..Mb-1 has c parents; fold column r+1 with column Mb-1-r
     const int tri = Mb - 1;
@@ -306,6 +343,9 @@ __global__ void __launch_bounds__(kBalThreads, 1)
     };
     auto colstart = [&](int ci) { return (ci * (ci - 1)) / 2; };
 
+    // GRAD: a pair's weights summed over the steps, in registers when the pairs per thread are few
+    constexpr int kRegAcc = 4;
+    float d0[kRegAcc] = {0.f, 0.f, 0.f, 0.f}, d1[kRegAcc] = {0.f, 0.f, 0.f, 0.f};
     int pk[NIT];  // this thread's (parent, child) pairs, the same at every step: a-slot | c-slot << 8, or -1
     {
         FoldIter f(tid, nthr, fold_len);
@@ -319,6 +359,10 @@ __global__ void __launch_bounds__(kBalThreads, 1)
                 const float *row = lkb + (size_t)(2 * ai + 1) * 2 * L + (2 * ci + 1);
                 lt0[p] = __ldg(row);
                 lt1[p] = __ldg(row + L);
+                if (GRAD) {
+                    D0[p] = 0.f;
+                    D1[p] = 0.f;
+                }
             }
         }
     }
@@ -329,6 +373,15 @@ __global__ void __launch_bounds__(kBalThreads, 1)
     const bool p2_warp = tid < ((4 * Mb + 31) / 32) * 32;
     const bool row_live = my_row < Mb;
     const bool owner = row_live && x == 0;
+    // GRAD: thread 512 + a finishes the emission gradients of parent a
+    const int h_row = tid - kBalThreads / 2;
+    const bool h_live = h_row >= 0 && h_row < Mb;
+    const int h_a = 2 * h_row + 1;
+    float sh0 = 0.f, sh1 = 0.f;  // shares of the j = 0 and of the j = 1 terms in S[h_row][s]
+    if (GRAD && h_live && n >= 2) {
+        sh0 = mgb[(size_t)h_a * T];
+        if (h_a >= 3) sh1 = mgb[(size_t)(h_a - 1) * T];
+    }
     const int a_node = 2 * my_row + 1;
     const float *Srow = Sb + (size_t)my_row * W;
     const float *Mrow = mat + (size_t)a_node * T;
@@ -336,6 +389,7 @@ __global__ void __launch_bounds__(kBalThreads, 1)
     // owner state for step s: s_cur = S[row][s], s_n1 = S[row][s+1], s_n2 = S[row][s+2], m_n1 = match[a][s+1]
     float s_cur = 0.f, s_n1 = 0.f, s_n2 = 0.f, m_n1 = 0.f;
     float pf_s = 0.f, pf_m = 0.f, pf_l = 0.f;  // prefetched: S[row][s+3], match[a][s+2], match[a-1][s+1]
+    float carry = 0.f, g_col = 0.f;            // GRAD: row h_row's j = 1 weight of the step before; G[my_row][s]
     __syncthreads();
     if (owner) {
         const float go = grad_output ? grad_output[b] : 1.f;
@@ -353,6 +407,7 @@ __global__ void __launch_bounds__(kBalThreads, 1)
         if (my_row == 0) {
             gcol[0] = go;  // S_grad[0][0] = grad_output (pcfg_loss_backward.cu:78)
             Gb[0] = go;
+            g_col = go;
         }
         pf_s = 3 < W ? __ldg(Srow + 3) : neg_inf();
         pf_m = 2 < n ? __ldg(Mrow + 2) : 0.f;
@@ -373,11 +428,22 @@ __global__ void __launch_bounds__(kBalThreads, 1)
             const float g = ga[ai];
             float w0 = 0.f, w1 = 0.f;
             if (g != 0.f) {
-                w0 = g * fast_exp((lt0[p] + sc1[ci]) + q0[ai]);
-                w1 = g * fast_exp((lt1[p] + sc2[ci]) + q1[ai]);
+                const float e0 = fast_exp((lt0[p] + sc1[ci]) + q0[ai]);
+                const float e1 = fast_exp((lt1[p] + sc2[ci]) + q1[ai]);
+                w0 = g * e0;
+                w1 = g * e1;
             }
             W0[p] = w0;
             W1[p] = w1;
+            if (GRAD) {
+                if (NIT <= kRegAcc) {
+                    d0[it < kRegAcc ? it : 0] += w0;
+                    d1[it < kRegAcc ? it : 0] += w1;
+                } else if (g != 0.f) {  // slot p is this thread's alone
+                    D0[p] += w0;
+                    D1[p] += w1;
+                }
+            }
         }
         __syncthreads();
         // ---- P2: column sums, G columns, scalars of the next step -----------------------------
@@ -409,6 +475,7 @@ __global__ void __launch_bounds__(kBalThreads, 1)
                 const float v = g1[my_row] + acc0;  // column s+1 is final now
                 g1[my_row] = v;
                 Gb[(size_t)my_row * W + s + 1] = v;
+                if (GRAD) g_col = v;
                 g2[my_row] = acc1;  // first contribution to column s+2
                 // this row as parent and as child at step s+1
                 const float sa = s_n1;  // S[row][s+1]
@@ -427,19 +494,52 @@ __global__ void __launch_bounds__(kBalThreads, 1)
                 pf_l = (a_node >= 3 && s + 2 < n) ? __ldg(Lrow + s + 2) : 0.f;
             }
         }
+        if (GRAD && h_live) {
+            // G[h_row][s] is still in its rolling column; a share next to a zero G may be anything
+            const float g = gcol[(s % 3) * cs + h_row];
+            const float r0 = g != 0.f ? g * sh0 : 0.f, r1 = g != 0.f ? g * sh1 : 0.f;
+            // j = 0 weights are match[a][s]'s; j = 1 weights are match[a][s+1]'s and match[a-1][s]'s
+            // (pcfg_loss_backward.cu:339-382)
+            mgb[(size_t)h_a * T + s] = r0 + carry;
+            if (h_a >= 3) mgb[(size_t)(h_a - 1) * T + s] = r1;
+            carry = r1;
+            if (s + 2 < n) {  // shares of the next step
+                sh0 = mgb[(size_t)h_a * T + s + 1];
+                if (h_a >= 3) sh1 = mgb[(size_t)(h_a - 1) * T + s + 1];
+            }
+        }
         __syncthreads();
+    }
+    if (GRAD) {
+        if (h_live) mgb[(size_t)h_a * T + n - 1] = carry;
+        __syncthreads();  // the terminal cell below is added to a cell written above
+        if (owner) {
+            // terminal cell: match_all_grad[m-1][n-1] += S_grad[slot of m-1][n-1] (pcfg_loss_backward.cu:379-382)
+            // (the slot's own row holds no j = 1 weight there: the last node has no children)
+            if (my_row == (m - 2) / 2) mgb[(size_t)(m - 1) * T + n - 1] = g_col;
+        }
+#pragma unroll
+        for (int it = 0; it < NIT; it++) {
+            const int q = pk[it];
+            if (q < 0) continue;
+            const int ai = q & 0xff, ci = (q >> 8) & 0xff;
+            const int p = colstart(ci) + ai;
+            float *cell = lgb + (size_t)(2 * ai + 1) * 2 * L + (2 * ci + 1);
+            cell[0] = NIT <= kRegAcc ? d0[it < kRegAcc ? it : 0] : D0[p];
+            cell[L] = NIT <= kRegAcc ? d1[it < kRegAcc ? it : 0] : D1[p];
+        }
     }
 }
 
 // trips of 1024 threads over a folded triangle of `rows` combined rows of `len` positions (batch maximum)
 int fold_trips(int len, int rows) { return (len * rows + kBalThreads - 1) / kBalThreads; }
 
-size_t balanced_smem_bytes(int Mc, int *cs_out, int *P_out) {
+size_t balanced_smem_bytes(int Mc, int *cs_out, int *P_out, bool with_grad = false) {
     const int cs = (Mc + 3) / 4 * 4;
     const int P = Mc * (Mc + 1) / 2;
     *cs_out = cs;
     *P_out = P;
-    return ((size_t)8 * cs + (size_t)4 * P) * sizeof(float);
+    return ((size_t)8 * cs + (size_t)(with_grad ? 6 : 4) * P) * sizeof(float);
 }
 
 }  // namespace
@@ -467,24 +567,41 @@ int launch_loss_fwd_balanced(const float *match_all, const float *links, const i
     return cuda_rc(cudaGetLastError());
 }
 
-int launch_outside_balanced(const float *grad_output, const float *S, const float *match_all, const float *links,
-                            const int64_t *ol, const int64_t *tl, int B, int L, int T, float *G, int *status,
-                            cudaStream_t st) {
+bool outside_balanced_fits_grad(int L) {
     const int Mc = main_slots(L, 1);
     int cs, P;
-    const size_t bytes = balanced_smem_bytes(Mc, &cs, &P);
+    const size_t bytes = balanced_smem_bytes(Mc, &cs, &P, true);
+    return bytes <= (size_t)kSmemLimit - 1024 && 8 * Mc <= kBalThreads && fold_trips(Mc, Mc / 2) <= 9;
+}
+
+// mg, lg both given: the kernel also writes both gradients from the emission shares the inside pass left in mg
+// (only for shapes outside_balanced_fits_grad accepts).
+int launch_outside_balanced(const float *grad_output, const float *S, const float *match_all, const float *links,
+                            const int64_t *ol, const int64_t *tl, int B, int L, int T, float *G, float *mg, float *lg,
+                            int *status, cudaStream_t st) {
+    const int Mc = main_slots(L, 1);
+    const bool with_grad = mg != nullptr && lg != nullptr;
+    int cs, P;
+    const size_t bytes = balanced_smem_bytes(Mc, &cs, &P, with_grad);
     if (bytes > (size_t)kSmemLimit - 1024 || 4 * Mc > kBalThreads) return PCFGNAT_ERR_UNSUPPORTED;
+    if (with_grad && 8 * Mc > kBalThreads) return PCFGNAT_ERR_UNSUPPORTED;  // second set of (x, row) threads
     const int trips = fold_trips(Mc, Mc / 2);
-#define PCFGNAT_LAUNCH_OUTSIDE(NIT)                                                                                   \
+#define PCFGNAT_LAUNCH_OUTSIDE(NIT, GRAD)                                                                             \
     do {                                                                                                              \
-        if (ensure_dynamic_smem(outside_balanced_kernel<NIT>, bytes) != cudaSuccess) return PCFGNAT_ERR_CUDA;         \
-        outside_balanced_kernel<NIT><<<B, kBalThreads, bytes, st>>>(grad_output, S, match_all, links, ol, tl, L, T, G, \
-                                                                    status, Mc, cs, P);                               \
+        if (ensure_dynamic_smem(outside_balanced_kernel<NIT, GRAD>, bytes) != cudaSuccess) return PCFGNAT_ERR_CUDA;   \
+        outside_balanced_kernel<NIT, GRAD><<<B, kBalThreads, bytes, st>>>(grad_output, S, match_all, links, ol, tl, L, \
+                                                                          T, G, mg, lg, status, Mc, cs, P);           \
     } while (0)
-    if (trips <= 4) PCFGNAT_LAUNCH_OUTSIDE(4);
-    else if (trips <= 9) PCFGNAT_LAUNCH_OUTSIDE(9);
-    else if (trips <= 13) PCFGNAT_LAUNCH_OUTSIDE(13);
-    else return PCFGNAT_ERR_UNSUPPORTED;
+    if (with_grad) {
+        if (trips <= 4) PCFGNAT_LAUNCH_OUTSIDE(4, true);
+        else if (trips <= 9) PCFGNAT_LAUNCH_OUTSIDE(9, true);
+        else return PCFGNAT_ERR_UNSUPPORTED;
+    } else {
+        if (trips <= 4) PCFGNAT_LAUNCH_OUTSIDE(4, false);
+        else if (trips <= 9) PCFGNAT_LAUNCH_OUTSIDE(9, false);
+        else if (trips <= 13) PCFGNAT_LAUNCH_OUTSIDE(13, false);
+        else return PCFGNAT_ERR_UNSUPPORTED;
+    }
 #undef PCFGNAT_LAUNCH_OUTSIDE
     return cuda_rc(cudaGetLastError());
 }

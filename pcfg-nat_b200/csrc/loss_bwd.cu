@@ -16,6 +16,8 @@
 //     does not pre-zero them.
 //
 // Gradients are compared by tolerance (1e-3 relative), so the summation order here is free.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace pcfgnat {
@@ -270,9 +272,18 @@ __global__ void __launch_bounds__(kGradWarps * 32)
 
 }  // namespace
 
+bool fused_grad_applies(int B, int L, int T) {
+    const char *fused = std::getenv("PCFGNAT_FUSED_GRAD");  // 0: outside pass, then the gradient kernel
+    if (fused && fused[0] == '0') return false;
+    const DpKernel choice = dp_kernel_choice();
+    if (choice == kDpRows || choice == kDpCluster) return false;
+    if (choice == kDpAuto && cluster_kernels_pay(B, L, T)) return false;
+    return outside_balanced_fits_grad(L);
+}
+
 int launch_loss_bwd(const float *grad_output, const float *S, const float *match_all, const float *links,
                     const int64_t *ol, const int64_t *tl, int B, int L, int T, float *S_grad, float *mg, float *lg,
-                    int *status, cudaStream_t st) {
+                    int *status, cudaStream_t st, bool shares_in_mg) {
     if (B == 0) return PCFGNAT_OK;
     const int Mc = main_slots(L, 1);
     int rows = (Mc + 7) / 8 * 8;
@@ -289,8 +300,12 @@ int launch_loss_bwd(const float *grad_output, const float *S, const float *match
     const DpKernel choice = dp_kernel_choice();
     if (choice == kDpCluster || (choice == kDpAuto && cluster_kernels_pay(B, L, T)))  // loss_cluster.cu
         brc = launch_outside_cluster(grad_output, S, match_all, links, ol, tl, B, L, T, S_grad, status, st);
-    if (brc == PCFGNAT_ERR_UNSUPPORTED && choice != kDpRows)  // evenly spread phases in one CTA (loss_balanced.cu)
-        brc = launch_outside_balanced(grad_output, S, match_all, links, ol, tl, B, L, T, S_grad, status, st);
+    if (brc == PCFGNAT_ERR_UNSUPPORTED && choice != kDpRows) {  // evenly spread phases in one CTA (loss_balanced.cu)
+        // with the emission shares of the inside pass at hand the same kernel sums up both gradients
+        if (shares_in_mg && fused_grad_applies(B, L, T))
+            return launch_outside_balanced(grad_output, S, match_all, links, ol, tl, B, L, T, S_grad, mg, lg, status, st);
+        brc = launch_outside_balanced(grad_output, S, match_all, links, ol, tl, B, L, T, S_grad, nullptr, nullptr, status, st);
+    }
     if (brc != PCFGNAT_ERR_UNSUPPORTED) {
         if (brc != PCFGNAT_OK) return brc;
     } else if (smem_cols + smem_links <= (size_t)kSmemLimit - 1024) {

@@ -116,10 +116,12 @@ __device__ __forceinline__ float inside_node_exact(const float *r0, const float 
 }
 
 // One node of the inside pass in free summation order; TR trips of 32 children cover the node's children.
-template <int TR>
+// SH: also the shares of the j = 0 terms (returned in lane 0) and of the j = 1 terms (in lane 16) in the
+// node's value, which the backward pass turns into emission gradients.
+template <int TR, bool SH>
 __device__ __forceinline__ float inside_node_free(const float *r0, const float *r1, const float *S1, const float *S2,
                                                   int ai, int Mb, int lane, bool has_leaf, float ma0, float ma1,
-                                                  float ml) {
+                                                  float ml, float &share) {
     constexpr float kLog2e = 1.4426950408889634f, kLn2 = 0.6931471805599453f;
     float t0[TR], t1[TR];
     float mx = neg_inf();
@@ -136,7 +138,26 @@ __device__ __forceinline__ float inside_node_free(const float *r0, const float *
         mx = fmaxf(mx, fmaxf(t0[i], t1[i]));
     }
     mx = warp_max_redux(mx);
+    if (SH) share = 0.f;
     if (isinf(mx)) return mx;  // warp-uniform
+    if (SH) {
+        float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+        for (int i = 0; i < TR; i++) {
+            sum0 += fast_ex2((t0[i] - mx) * kLog2e);
+            sum1 += fast_ex2((t1[i] - mx) * kLog2e);
+        }
+        const float sum = warp_sum(sum0 + sum1);
+        // both partial sums in one tree: after the first round the lower half-warp carries the j = 0 sums and
+        // the upper one the j = 1 sums
+        const bool upper = lane & 16;
+        float v = upper ? sum1 : sum0;
+        v += __shfl_xor_sync(0xffffffffu, upper ? sum0 : sum1, 16);
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        share = __fdividef(v, sum);
+        return fmaf(fast_lg2(sum), kLn2, mx);
+    }
     float sum = 0.f;
 #pragma unroll
     for (int i = 0; i < TR; i++) {  // the difference first: it is small, so its rounding error is too
@@ -149,12 +170,15 @@ __device__ __forceinline__ float inside_node_free(const float *r0, const float *
 
 // TRIPS == 0: the reference's summation order (bit-exact table).  TRIPS > 0: free order, for chains of at
 // most 32 * TRIPS main nodes (a lane holds the terms of its TRIPS children in registers between the passes).
-template <int TRIPS>
+// SHARES (free order only): `shares` is a [B][L][T] buffer; the share of the j = 0 terms in S[a][t] goes to
+// [a][t] and that of the j = 1 terms to [a-1][t] (the cells of match_all_grad those terms contribute to).  The
+// shared memory then holds two more [rows_cap][W] arrays.
+template <int TRIPS, bool SHARES = false>
 __global__ void __launch_bounds__(kCThreads, 1)
     inside_cluster_kernel(const float *__restrict__ match_all, const float *__restrict__ links,
                           const int64_t *__restrict__ ol, const int64_t *__restrict__ tl, int L, int T, float *S,
                           float *C, float *loss, int *status, int Mc, int Lt, int cs, int rows_cap, int lk_stride,
-                          int B, int wide) {
+                          int B, int wide, float *shares) {
     extern __shared__ float smem[];
     cg::cluster_group cluster = cg::this_cluster();
     const int crank = (int)cluster.block_rank();
@@ -229,6 +253,7 @@ __global__ void __launch_bounds__(kCThreads, 1)
     // emissions of this CTA's nodes and of their leaves, so that a step reads them from shared memory
     // instead of chasing three global addresses per node
     float *em0 = own + (size_t)rows_cap * W, *eml = em0 + (size_t)rows_cap * W;  // [rows_cap][W] each
+    float *own0 = eml + (size_t)rows_cap * W, *own1 = own0 + (size_t)rows_cap * W;  // SHARES only: [rows_cap][W] each
     for (int i = tid; i < my_rows * T; i += kCThreads) {
         const int r = i / T, t = i - r * T, a = 2 * (crank + NC * r) + 1;
         em0[r * W + t] = __ldg(mat + (size_t)a * T + t);
@@ -280,15 +305,19 @@ __global__ void __launch_bounds__(kCThreads, 1)
             float res;
             if constexpr (TRIPS > 0) {
                 // warp-uniform dispatch on the number of trips this node needs: each case is straight-line code
+                float share = 0.f;
                 switch ((Mb - ai + 31) / 32) {
-                    case 1: res = inside_node_free<1>(r0, r1, S1, S2, ai, Mb, lane, has_leaf, ma0, ma1, ml); break;
-                    case 2: res = inside_node_free<2>(r0, r1, S1, S2, ai, Mb, lane, has_leaf, ma0, ma1, ml); break;
-                    case 3: res = inside_node_free<(TRIPS >= 4 ? 3 : TRIPS)>(r0, r1, S1, S2, ai, Mb, lane, has_leaf, ma0, ma1, ml); break;
-                    case 4: res = inside_node_free<(TRIPS >= 4 ? 4 : TRIPS)>(r0, r1, S1, S2, ai, Mb, lane, has_leaf, ma0, ma1, ml); break;
+#define PCFGNAT_NODE(TR) res = inside_node_free<(TR), SHARES>(r0, r1, S1, S2, ai, Mb, lane, has_leaf, ma0, ma1, ml, share)
+                    case 1: PCFGNAT_NODE(1); break;
+                    case 2: PCFGNAT_NODE(2); break;
+                    case 3: PCFGNAT_NODE(TRIPS >= 4 ? 3 : TRIPS); break;
+                    case 4: PCFGNAT_NODE(TRIPS >= 4 ? 4 : TRIPS); break;
                     case 5:
-                    case 6: res = inside_node_free<(TRIPS >= 8 ? 6 : TRIPS)>(r0, r1, S1, S2, ai, Mb, lane, has_leaf, ma0, ma1, ml); break;
-                    default: res = inside_node_free<TRIPS>(r0, r1, S1, S2, ai, Mb, lane, has_leaf, ma0, ma1, ml); break;
+                    case 6: PCFGNAT_NODE(TRIPS >= 8 ? 6 : TRIPS); break;
+                    default: PCFGNAT_NODE(TRIPS); break;
+#undef PCFGNAT_NODE
                 }
+                if (SHARES && (lane & 15) == 0) (lane ? own1 : own0)[r * W + start] = share;
             } else {
             const int trips = (Mb - ai + 31) / 32;
             if (trips <= 8) {  // straight-line code per trip count, terms kept in registers between the passes
@@ -354,6 +383,14 @@ __global__ void __launch_bounds__(kCThreads, 1)
     for (int i = tid; i < my_rows * (n - 1); i += kCThreads) {  // computed cells: columns 0 .. n-2
         const int r = i / (n - 1), t = i - r * (n - 1);
         Sb[(size_t)(crank + NC * r) * W + t] = own[r * W + t];
+    }
+    if (SHARES) {
+        float *sb = shares + (size_t)b * L * T;
+        for (int i = tid; i < my_rows * (n - 1); i += kCThreads) {
+            const int r = i / (n - 1), t = i - r * (n - 1), a = 2 * (crank + NC * r) + 1;
+            sb[(size_t)a * T + t] = own0[r * W + t];
+            if (a >= 3) sb[(size_t)(a - 1) * T + t] = own1[r * W + t];
+        }
     }
     if (loss && ctid == 0) loss[b] = (n >= 2) ? col[0] : Sb[0];
 }
@@ -587,27 +624,28 @@ bool cluster_kernels_pay(int B, int L, int T) {
 
 // Both return PCFGNAT_ERR_UNSUPPORTED when the shape does not fit any cluster size (the caller then
 // uses the row-per-thread kernels that read links from global memory).
-template <int TRIPS>
+template <int TRIPS, bool SHARES = false>
 int launch_inside(const float *match_all, const float *links, const int64_t *ol, const int64_t *tl, int B, int L, int T,
-                  float *S, float *C, float *loss, int *status, cudaStream_t st) {
+                  float *S, float *C, float *loss, int *status, cudaStream_t st, float *shares = nullptr) {
     const int Mc = main_slots(L, 1), Lt = L - Mc;
     ClusterGeometry g = cluster_geometry(B, Mc, T + 2);
     for (; g.nc >= 1; g.nc /= 2) {  // fall back to smaller clusters if the GPU cannot co-schedule this size
         g.rows_cap = (Mc + g.nc - 1) / g.nc;
-        g.smem_in = ((size_t)4 * g.cs + (size_t)2 * g.rows_cap * g.lk_stride + (size_t)3 * g.rows_cap * (T + 2)) * sizeof(float);
+        g.smem_in = ((size_t)4 * g.cs + (size_t)2 * g.rows_cap * g.lk_stride + (size_t)(SHARES ? 5 : 3) * g.rows_cap * (T + 2)) *
+                    sizeof(float);
         if (g.smem_in > (size_t)kSmemLimit - 1024) break;
         if (g.nc == 1) {
             // more sentences than half the SMs: clusters of two, of which only the costliest sentences use both
             // CTAs (see the kernel); every CTA can hold a whole chain, so the shared memory is that of one CTA
             const int wide = mixed_width_count(B, Mc);
             if (wide > 0) {
-                int rc = launch_cluster(inside_cluster_kernel<TRIPS>, B, 2, g.smem_in, st, match_all, links, ol, tl, L, T,
-                                        S, C, loss, status, Mc, Lt, g.cs, g.rows_cap, g.lk_stride, B, wide);
+                int rc = launch_cluster(inside_cluster_kernel<TRIPS, SHARES>, B, 2, g.smem_in, st, match_all, links, ol, tl,
+                                        L, T, S, C, loss, status, Mc, Lt, g.cs, g.rows_cap, g.lk_stride, B, wide, shares);
                 if (rc != PCFGNAT_ERR_UNSUPPORTED) return rc;
             }
         }
-        int rc = launch_cluster(inside_cluster_kernel<TRIPS>, B, g.nc, g.smem_in, st, match_all, links, ol, tl, L, T, S,
-                                C, loss, status, Mc, Lt, g.cs, g.rows_cap, g.lk_stride, B, -1);
+        int rc = launch_cluster(inside_cluster_kernel<TRIPS, SHARES>, B, g.nc, g.smem_in, st, match_all, links, ol, tl, L,
+                                T, S, C, loss, status, Mc, Lt, g.cs, g.rows_cap, g.lk_stride, B, -1, shares);
         if (rc != PCFGNAT_ERR_UNSUPPORTED) return rc;
     }
     return PCFGNAT_ERR_UNSUPPORTED;
@@ -622,8 +660,14 @@ int launch_loss_fwd_cluster(const float *match_all, const float *links, const in
 // callers that use the table only to form the loss and the gradients.  PCFGNAT_ERR_UNSUPPORTED when the
 // shape does not fit (chains above 256 main nodes, or links beyond the cluster's shared memory).
 int launch_loss_fwd_fast(const float *match_all, const float *links, const int64_t *ol, const int64_t *tl, int B, int L,
-                         int T, float *S, float *loss, int *status, cudaStream_t st) {
+                         int T, float *S, float *loss, int *status, cudaStream_t st, float *shares) {
     const int Mc = main_slots(L, 1);
+    if (shares) {  // [B][L][T]: the shares of the two kinds of terms in every value, for the backward pass
+        if (Mc <= 64) return launch_inside<2, true>(match_all, links, ol, tl, B, L, T, S, nullptr, loss, status, st, shares);
+        if (Mc <= 128) return launch_inside<4, true>(match_all, links, ol, tl, B, L, T, S, nullptr, loss, status, st, shares);
+        if (Mc <= 256) return launch_inside<8, true>(match_all, links, ol, tl, B, L, T, S, nullptr, loss, status, st, shares);
+        return PCFGNAT_ERR_UNSUPPORTED;
+    }
     if (Mc <= 64) return launch_inside<2>(match_all, links, ol, tl, B, L, T, S, nullptr, loss, status, st);
     if (Mc <= 128) return launch_inside<4>(match_all, links, ol, tl, B, L, T, S, nullptr, loss, status, st);
     if (Mc <= 256) return launch_inside<8>(match_all, links, ol, tl, B, L, T, S, nullptr, loss, status, st);

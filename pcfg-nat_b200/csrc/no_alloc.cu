@@ -72,8 +72,10 @@ extern "C" int pcfgnat_loss_fwd_bwd_static(const float *match_all, const float *
     float *S = static_cast<float *>(base);
     float *G = reinterpret_cast<float *>(static_cast<unsigned char *>(base) + table);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    rc = launch_loss_fwd_internal(match_all, links, output_length, target_length, B, L, T, S, loss, status, st);
+    bool shares_in_mg = false;
+    rc = launch_loss_fwd_internal(match_all, links, output_length, target_length, B, L, T, S, loss, status, st,
+                                  match_all_grad, &shares_in_mg);
     if (rc) return rc;
     return launch_loss_bwd(nullptr, S, match_all, links, output_length, target_length, B, L, T, G, match_all_grad,
-                           links_grad, status, st);
+                           links_grad, status, st, shares_in_mg);
 }

@@ -180,7 +180,7 @@ class LossStep(_GraphedStep):
     target_length [B].  ``run()`` returns (stats[3] f32 = [sum_b S_b/n_b, sentences, invalid],
     match_all_grad, links_grad, sentence_loss); static outputs, overwritten by the next ``run()``.
     """
-    kernels_per_step = 7  # proj_prepare, proj, proj_merge, loss_fwd, outside, grad, loss_stats
+    kernels_per_step = 7  # proj_prepare, proj, proj_merge, loss_fwd, outside, grad, loss_stats (set per shape below)
 
     def __init__(self, weight, B, L, T, device, use_graph=True, copy_chunks=2, proj_backward=False, exchange=None):
         super().__init__(weight, B, L, device, use_graph, copy_chunks)
@@ -192,8 +192,15 @@ class LossStep(_GraphedStep):
         # with proj_backward the step also carries the emission gradients back through the projection:
         # run() then returns d hidden [B,L,H] f16 and d weight [V,H] f16 as two more outputs
         self.proj_backward = bool(proj_backward)
+        if type(self) is LossStep:
+            # the library says whether the outside pass of this shape also sums up the gradients (2 DP kernels) or
+            # a gradient kernel follows it (3); around them: proj_prepare, proj, proj_merge and loss_stats
+            from . import _cabi
+            with torch.cuda.device(self.device):
+                dp = _cabi.lib().pcfgnat_loss_fwd_bwd_kernels(B, L, T, 1)
+            self.kernels_per_step = 4 + (dp if dp > 0 else 3)
         if self.proj_backward:
-            self.kernels_per_step = LossStep.kernels_per_step + 3  # proj_prepare, zero padding rows, proj (grad mode)
+            self.kernels_per_step += 3  # proj_prepare, zero padding rows, proj (grad mode)
             self.weight_bf16 = self.weight.to(torch.bfloat16)
 
     def _inputs(self):

@@ -37,7 +37,8 @@ class Workload:
     left_tree_layer: int = 1
     src_min: int = 8
     src_max: int = 8
-    upsample: int = 4  # graph length = upsample * source length
+    upsample: int = 4  # graph length = upsample * source length + graph_offset
+    graph_offset: int = 0
     fixed_graph: Optional[int] = None  # all sentences use this graph length
     fixed_target: Optional[int] = None
     target_jitter: float = 0.2  # target length = source length * U[1-j, 1+j]
@@ -54,6 +55,10 @@ WORKLOADS: Dict[str, Workload] = {
     # one training batch: ~90 sentences, ~2730 target tokens (--max-tokens 2730)
     "train_batch": Workload("train_batch", batch=90, vocab=40000, hidden=512, src_min=20, src_max=40,
                             hidden_std=0.02),
+    # the same sentences with the graph size the reference model really builds, 8 * source + 2 nodes
+    # (models/glat_decomposed_with_link_two_hands_tri_pcfg.py:322: source * upsample scale * 2^left_tree_layer + 2)
+    "train_batch_model_graph": Workload("train_batch_model_graph", batch=90, vocab=40000, hidden=512, src_min=20,
+                                        src_max=40, upsample=8, graph_offset=2, hidden_std=0.02),
     # long sequences: 8 sentences, graph 512, target 128
     "long_seq": Workload("long_seq", batch=8, vocab=40000, hidden=512, fixed_graph=512, fixed_target=128),
     "viterbi_b1": Workload("viterbi_b1", batch=1, vocab=40000, hidden=512, src_min=10, src_max=60, kind="viterbi"),
@@ -141,7 +146,7 @@ def make_batch(name_or_workload, seed=0, batch=None) -> Batch:
         src = out_len // scale
     else:
         src = torch.randint(w.src_min, w.src_max + 1, (B,), generator=g)
-        out_len = src * scale
+        out_len = src * scale + w.graph_offset
     if w.fixed_target is not None:
         tgt_len = torch.full((B,), w.fixed_target, dtype=torch.long)
     else:

@@ -340,6 +340,86 @@ def test_fused_loss_many_sentences_mixed_cluster_widths(ops, syn, monkeypatch):
     ops.read_status(DEV)
 
 
+def test_fused_loss_model_graph_size(ops, syn, monkeypatch):
+    """Graphs of 8 * source + 2 nodes, the size the reference model builds at left_tree_layer 1
+    (models/glat_decomposed_with_link_two_hands_tri_pcfg.py:322), on the sentence lengths of the training batch:
+    up to 161 main-chain nodes per sentence.  Loss and gradients against the oracle, Viterbi tables bit for bit."""
+    monkeypatch.delenv("PCFGNAT_DP_KERNEL", raising=False)
+    monkeypatch.delenv("PCFGNAT_DP_CLUSTER_SIZE", raising=False)
+    monkeypatch.delenv("PCFGNAT_EXACT_ORDER", raising=False)
+    w = syn.WORKLOADS["train_batch_model_graph"]
+    b, ma = _loss_inputs(syn, syn.Workload("model_graph", batch=24, vocab=40, hidden=8, src_min=w.src_min,
+                                           src_max=w.src_max, upsample=w.upsample, graph_offset=w.graph_offset,
+                                           emissions="logits"), 33)
+    assert int(b.output_length.max()) > 256 and (b.output_length % 8 == 2).all()
+    ol, tl = b.output_length, b.target_length
+    So, Co = oracle.pcfg_loss(ma.numpy(), b.links.numpy(), ol.numpy(), tl.numpy())
+    go = np.ones(b.B, np.float32)
+    mgo, lgo = oracle.pcfg_loss_backward(go, So, Co, ma.numpy(), b.links.numpy(), ol.numpy(), tl.numpy())
+    ops.read_status(DEV)
+    k = ops.get_pcfg_kernel()
+    loss, mg, lg = k.pcfg_loss_fwd_bwd(ma.to(DEV), b.links.to(DEV), ol.to(DEV), tl.to(DEV))
+    _rel_close(loss.cpu().numpy(), So[:, 0, 0], 1e-4)
+    np.testing.assert_allclose(mg.cpu().numpy(), mgo, rtol=1e-3, atol=2e-6)
+    np.testing.assert_allclose(lg.cpu().numpy(), lgo, rtol=1e-3, atol=2e-6)
+    g = torch.Generator().manual_seed(5)
+    ob = torch.log_softmax(torch.randn(b.B, b.L, 50, generator=g), -1).max(-1).values.contiguous()
+    So2, Ro, Lo, Mo = oracle.pcfg_viterbi(ob.numpy(), b.links.numpy(), ol.numpy())
+    S2, R2, L2, M2 = k.pcfg_viterbi(ob.to(DEV), b.links.to(DEV), ol.to(DEV), 1)
+    assert np.array_equal(_bits(S2.cpu().numpy()), _bits(So2))
+    np.testing.assert_array_equal(R2.cpu().numpy(), Ro)
+    np.testing.assert_array_equal(L2.cpu().numpy(), Lo)
+    np.testing.assert_array_equal(M2.cpu().numpy(), Mo)
+    assert ops.read_status(DEV) == 0
+
+
+@pytest.mark.parametrize("L_even", [True, False])
+def test_outside_pass_with_fused_gradients_matches_the_gradient_kernel(ops, syn, monkeypatch, L_even):
+    """Fused forward + backward on a batch that runs one CTA per sentence: the outside kernel that also sums up
+    both gradients (emission gradients from the shares the inside pass leaves in match_all_grad) against the
+    outside kernel followed by the gradient kernel (PCFGNAT_FUSED_GRAD=0): both gradients to rounding, and both
+    against the oracle.  The batch has odd graph lengths, a
+    one-token target, an invalid sentence, and the outputs are handed over filled with garbage."""
+    monkeypatch.delenv("PCFGNAT_DP_KERNEL", raising=False)
+    monkeypatch.delenv("PCFGNAT_DP_CLUSTER_SIZE", raising=False)
+    monkeypatch.delenv("PCFGNAT_EXACT_ORDER", raising=False)
+    b, ma = _loss_inputs(syn, syn.Workload("fg", batch=97, vocab=40, hidden=8, src_min=3, src_max=20,
+                                           emissions="logits"), 77)
+    links = b.links
+    if not L_even:  # an odd padded width: the zero fill cannot use 16-byte stores
+        ma = torch.nn.functional.pad(ma, (0, 0, 0, 1), value=0.0).contiguous()
+        links = torch.nn.functional.pad(links, (0, 1, 0, 0, 0, 1), value=float("-inf")).contiguous()
+    ol, tl = b.output_length.clone(), b.target_length.clone()
+    ol[1] -= 1  # odd number of nodes: the last token is emitted by an even node
+    tl[2] = 1   # one target token
+    tl[3] = 0   # invalid
+    k = ops.get_pcfg_kernel()
+    ops.read_status(DEV)
+    outs = {}
+    for mode in ("1", "0"):
+        monkeypatch.setenv("PCFGNAT_FUSED_GRAD", mode)
+        # whatever the allocator hands out next is dirty
+        torch.empty(64 << 20, dtype=torch.uint8, device=DEV).fill_(0x7f)
+        loss, mg, lg = k.pcfg_loss_fwd_bwd(ma.to(DEV), links.to(DEV), ol.to(DEV), tl.to(DEV))
+        outs[mode] = (mg.cpu().numpy(), lg.cpu().numpy(), loss.cpu().numpy())
+    assert ops.read_status(DEV) & 1  # PCFGNAT_STATUS_BAD_LENGTH for sentence 3
+    # the inside pass that also emits the shares adds its two kinds of terms up separately: last-bit differences
+    _rel_close(outs["1"][2], outs["0"][2], 1e-6)
+    np.testing.assert_allclose(outs["1"][1], outs["0"][1], rtol=1e-4, atol=1e-7)
+    np.testing.assert_allclose(outs["1"][0], outs["0"][0], rtol=1e-4, atol=1e-9)  # no absolute slack
+    assert not np.array_equal(outs["1"][0], outs["0"][0])  # the switch chose another kernel
+    So, Co = oracle.pcfg_loss(ma.numpy(), links.numpy(), ol.numpy(), tl.numpy())
+    go = np.ones(b.B, np.float32)
+    mgo, lgo = oracle.pcfg_loss_backward(go, So, Co, ma.numpy(), links.numpy(), ol.numpy(), tl.numpy())
+    finite = np.isfinite(So[:, 0, 0])
+    finite[3] = False
+    np.testing.assert_allclose(outs["1"][0][finite], mgo[finite], rtol=1e-3, atol=2e-6)
+    np.testing.assert_allclose(outs["1"][1][finite], lgo[finite], rtol=1e-3, atol=2e-6)
+    assert not outs["1"][0][3].any() and not outs["1"][1][3].any()
+    infeasible = ~np.isfinite(outs["1"][2])
+    assert not outs["1"][0][infeasible].any() and not outs["1"][1][infeasible].any()
+
+
 def test_invalid_sentences_are_skipped_not_faulted(dp_kernel, ops, syn):
     b, ma = _loss_inputs(syn, syn.Workload("bad", batch=4, vocab=50, hidden=8, src_min=4, src_max=6,
                                            emissions="logits"), 9)
