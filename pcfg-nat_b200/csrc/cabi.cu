@@ -51,8 +51,10 @@ int launch_loss_fwd_internal(const float *match_all, const float *links, const i
     *shares_in_mg = false;
     if (!exact_order_forced() && dp_kernel_choice() == kDpAuto) {
         float *shares = (mg && fused_grad_applies(B, L, T)) ? mg : nullptr;
-        const int rc = launch_loss_fwd_fast(match_all, links, ol, tl, B, L, T, S, loss, status, st, shares);
+        int rc = launch_loss_fwd_fast(match_all, links, ol, tl, B, L, T, S, loss, status, st, shares);
         if (rc == PCFGNAT_OK) *shares_in_mg = shares != nullptr;
+        if (rc == PCFGNAT_ERR_UNSUPPORTED && shares)  // the two more arrays did not fit: without the shares
+            rc = launch_loss_fwd_fast(match_all, links, ol, tl, B, L, T, S, loss, status, st, nullptr);
         if (rc != PCFGNAT_ERR_UNSUPPORTED) return rc;
     }
     return launch_loss_fwd(match_all, links, ol, tl, B, L, T, S, nullptr, loss, status, st);

@@ -117,8 +117,9 @@ int launch_loss_fwd_internal(const float *match_all, const float *links, const i
                              bool *shares_in_mg);
 bool exact_order_forced();  // PCFGNAT_EXACT_ORDER=1: the fused forward + backward also keeps the reference's order
 int launch_outside_cluster(const float *grad_output, const float *S, const float *match_all, const float *links,
-                           const int64_t *ol, const int64_t *tl, int B, int L, int T, float *G, int *status,
-                           cudaStream_t st);
+                           const int64_t *ol, const int64_t *tl, int B, int L, int T, float *G, float *mg, float *lg,
+                           int *status, cudaStream_t st);
+bool outside_cluster_fits_grad(int B, int L, int T);
 
 // Which family of DP kernels runs the inside / outside passes.  PCFGNAT_DP_KERNEL in the environment
 // selects one for A/B runs and tests: "cluster" (default: warp per node, cluster per sentence),

@@ -277,7 +277,7 @@ bool fused_grad_applies(int B, int L, int T) {
     if (fused && fused[0] == '0') return false;
     const DpKernel choice = dp_kernel_choice();
     if (choice == kDpRows || choice == kDpCluster) return false;
-    if (choice == kDpAuto && cluster_kernels_pay(B, L, T)) return false;
+    if (choice == kDpAuto && cluster_kernels_pay(B, L, T)) return outside_cluster_fits_grad(B, L, T);
     return outside_balanced_fits_grad(L);
 }
 
@@ -298,12 +298,20 @@ int launch_loss_bwd(const float *grad_output, const float *S, const float *match
     cudaError_t e;
     int brc = PCFGNAT_ERR_UNSUPPORTED;
     const DpKernel choice = dp_kernel_choice();
-    if (choice == kDpCluster || (choice == kDpAuto && cluster_kernels_pay(B, L, T)))  // loss_cluster.cu
-        brc = launch_outside_cluster(grad_output, S, match_all, links, ol, tl, B, L, T, S_grad, status, st);
+    if (choice == kDpCluster || (choice == kDpAuto && cluster_kernels_pay(B, L, T))) {  // loss_cluster.cu
+        // with the emission shares of the inside pass at hand the same kernel sums up both gradients
+        if (shares_in_mg && fused_grad_applies(B, L, T)) {
+            const int rc = launch_outside_cluster(grad_output, S, match_all, links, ol, tl, B, L, T, S_grad, mg, lg, status, st);
+            if (rc != PCFGNAT_ERR_UNSUPPORTED) return rc;  // else: two kernels; the second overwrites the shares
+        }
+        brc = launch_outside_cluster(grad_output, S, match_all, links, ol, tl, B, L, T, S_grad, nullptr, nullptr, status, st);
+    }
     if (brc == PCFGNAT_ERR_UNSUPPORTED && choice != kDpRows) {  // evenly spread phases in one CTA (loss_balanced.cu)
         // with the emission shares of the inside pass at hand the same kernel sums up both gradients
-        if (shares_in_mg && fused_grad_applies(B, L, T))
-            return launch_outside_balanced(grad_output, S, match_all, links, ol, tl, B, L, T, S_grad, mg, lg, status, st);
+        if (shares_in_mg && fused_grad_applies(B, L, T) && outside_balanced_fits_grad(L)) {
+            const int rc = launch_outside_balanced(grad_output, S, match_all, links, ol, tl, B, L, T, S_grad, mg, lg, status, st);
+            if (rc != PCFGNAT_ERR_UNSUPPORTED) return rc;  // else: two kernels; the second overwrites the shares
+        }
         brc = launch_outside_balanced(grad_output, S, match_all, links, ol, tl, B, L, T, S_grad, nullptr, nullptr, status, st);
     }
     if (brc != PCFGNAT_ERR_UNSUPPORTED) {

@@ -398,11 +398,16 @@ __global__ void __launch_bounds__(kCThreads, 1)
 // ---------------------------------------------------------------------------------------
 // outside pass
 // ---------------------------------------------------------------------------------------
+// GRAD: the kernel also sums up both gradients (the weights of a step are their terms): a (parent, child) pair's
+// weights over the steps, in shared memory, give links_grad (same values and order as grad_kernel); the emission
+// gradients are G[a][s] times the shares of the j = 0 / j = 1 terms in S[a][s] that the free-order inside kernel
+// left in the cells [a][s] / [a-1][s] of match_all_grad.  The dense gradients are zero-filled first.
+template <bool GRAD>
 __global__ void __launch_bounds__(kCThreads, 1)
     outside_cluster_kernel(const float *__restrict__ grad_output, const float *__restrict__ S,
                            const float *__restrict__ match_all, const float *__restrict__ links,
                            const int64_t *__restrict__ ol, const int64_t *__restrict__ tl, int L, int T, float *G,
-                           int *status, int Mc, int cs, int rows_cap, int lk_stride) {
+                           float *mg, float *lg, int *status, int Mc, int cs, int rows_cap, int lk_stride) {
     extern __shared__ float smem[];
     cg::cluster_group cluster = cg::this_cluster();
     const int NC = (int)cluster.num_blocks(), crank = (int)cluster.block_rank();
@@ -416,6 +421,27 @@ __global__ void __launch_bounds__(kCThreads, 1)
     const float *Sb = S + (size_t)b * Mc * W;
     float *Gb = G + (size_t)b * Mc * W;
     for (int i = ctid; i < Mc * W; i += cthreads) Gb[i] = 0.f;
+    float *mgb = GRAD ? mg + (size_t)b * L * T : nullptr;
+    float *lgb = GRAD ? lg + (size_t)b * L * 2 * L : nullptr;
+    if (GRAD) {
+        const size_t n_lg = (size_t)L * 2 * L;
+        if ((n_lg & 3) == 0 && (reinterpret_cast<uintptr_t>(lgb) & 15) == 0) {
+            for (size_t i = ctid; i < n_lg / 4; i += cthreads) reinterpret_cast<float4 *>(lgb)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        } else {
+            for (size_t i = ctid; i < n_lg; i += cthreads) lgb[i] = 0.f;
+        }
+        // emission gradients: every cell that does not hold a share (for an unusable sentence: every cell)
+        const int live_rows = lengths_ok(m, n, L, T) ? 2 * main_nodes_below(m) : 0;
+        for (int row = ctid / T, t = ctid - row * T; row < L;) {
+            const bool share = row >= 1 && row < live_rows && t < n - 1;
+            if (!share) mgb[(size_t)row * T + t] = 0.f;
+            t += cthreads;
+            while (t >= T) {
+                t -= T;
+                row++;
+            }
+        }
+    }
     if (!lengths_ok(m, n, L, T)) {
         if (ctid == 0) flag(status, PCFGNAT_STATUS_BAD_LENGTH);
         return;
@@ -431,6 +457,8 @@ __global__ void __launch_bounds__(kCThreads, 1)
     float *lt1 = lt0 + (size_t)rows_cap * lk_stride;
     float *own = lt1 + (size_t)rows_cap * lk_stride;  // [rows_cap][W] G entries of this CTA's nodes, flushed at the end
     float *sown = own + (size_t)rows_cap * W;         // [rows_cap][W] inside values of this CTA's nodes
+    float *D0 = sown + (size_t)rows_cap * W;          // GRAD only: [rows_cap][lk_stride] weights summed over the steps
+    float *D1 = D0 + (size_t)rows_cap * lk_stride;
     // the scalars of parent ai at step s (thread ai computes them; chains of more than kCThreads nodes are not
     // launched with this kernel)
     auto parent_scalars = [&](int ai, int s, float &v0, float &v1) {
@@ -448,11 +476,24 @@ __global__ void __launch_bounds__(kCThreads, 1)
             const float *row = lkb + (size_t)(2 * ai + 1) * 2 * L + c;
             lt0[r * lk_stride + ai] = __ldg(row);
             lt1[r * lk_stride + ai] = __ldg(row + L);
+            if (GRAD) {
+                D0[r * lk_stride + ai] = 0.f;
+                D1[r * lk_stride + ai] = 0.f;
+            }
         }
     }
     for (int i = tid; i < my_rows * W; i += kCThreads) {
         const int r = i / W, t = i - r * W;
         sown[i] = __ldg(Sb + (size_t)(crank + NC * r) * W + t);
+    }
+    // GRAD: thread kCThreads - 1 - r finishes the emission gradients of this CTA's node r
+    const int h_r = kCThreads - 1 - tid;
+    const bool h_live = GRAD && h_r < my_rows;
+    const int h_ai = crank + NC * h_r, h_a = 2 * h_ai + 1;
+    float sh0 = 0.f, sh1 = 0.f, carry = 0.f;  // shares of the j = 0 / j = 1 terms in S[h_ai][s]; last step's j = 1 weight
+    if (h_live && n >= 2) {
+        sh0 = mgb[(size_t)h_a * T];
+        if (h_a >= 3) sh1 = mgb[(size_t)(h_a - 1) * T];
     }
     if (tid < Mb && n >= 2) parent_scalars(tid, 0, q0[tid], q1[tid]);
     // columns are exchanged with st.async counted on two alternating barriers (common.cuh), not a cluster barrier
@@ -496,8 +537,14 @@ __global__ void __launch_bounds__(kCThreads, 1)
                 for (int ai = lane; ai < ci; ai += 32) {
                     const float g = g0[ai];
                     if (g != 0.f) {  // exp(-inf) = 0 where the parent's inside value is -inf
-                        acc0 += g * fast_exp((r0[ai] + sc1) + c0[ai]);
-                        acc1 += g * fast_exp((r1[ai] + sc2) + c1[ai]);
+                        const float w0 = g * fast_exp((r0[ai] + sc1) + c0[ai]);
+                        const float w1 = g * fast_exp((r1[ai] + sc2) + c1[ai]);
+                        acc0 += w0;
+                        acc1 += w1;
+                        if (GRAD) {  // the slot is this lane's alone
+                            D0[r * lk_stride + ai] += w0;
+                            D1[r * lk_stride + ai] += w1;
+                        }
                     }
                 }
             }
@@ -521,6 +568,19 @@ __global__ void __launch_bounds__(kCThreads, 1)
             q0[((s + 1) & 1) * cs + tid] = n0;
             q1[((s + 1) & 1) * cs + tid] = n1;
         }
+        if (h_live) {
+            // j = 0 weights are match[a][s]'s; j = 1 weights are match[a][s+1]'s and match[a-1][s]'s
+            // (pcfg_loss_backward.cu:339-382); a share next to a zero G may be anything
+            const float g = g0[h_ai];
+            const float w0 = g != 0.f ? g * sh0 : 0.f, w1 = g != 0.f ? g * sh1 : 0.f;
+            mgb[(size_t)h_a * T + s] = w0 + carry;
+            if (h_a >= 3) mgb[(size_t)(h_a - 1) * T + s] = w1;
+            carry = w1;
+            if (s + 2 < n) {  // shares of the next step
+                sh0 = mgb[(size_t)h_a * T + s + 1];
+                if (h_a >= 3) sh1 = mgb[(size_t)(h_a - 1) * T + s + 1];
+            }
+        }
         __syncthreads();  // the next step's scalars are written before any thread of this CTA reads them
         if (NC > 1) arrived = dsm_wait_column(bar, (s >> 1) & 1) && arrived;
     }
@@ -530,6 +590,28 @@ __global__ void __launch_bounds__(kCThreads, 1)
         Gb[(size_t)(crank + NC * r) * W + t] = own[r * W + t];
     }
     if (ctid == 0) Gb[0] = grad_output ? grad_output[b] : 1.f;
+    if (GRAD) {
+        if (h_live) {
+            // terminal cell: match_all_grad[m-1][n-1] += S_grad[slot of m-1][n-1] (pcfg_loss_backward.cu:379-382);
+            // the slot's own row holds no j = 1 weight there (the last node has no children)
+            float v = carry;
+            if (h_ai == (m - 2) / 2) {
+                const float go = grad_output ? grad_output[b] : 1.f;
+                const float term = n >= 2 ? own[h_r * W + n - 1] : (h_ai == 0 ? go : 0.f);
+                if (h_a == m - 1) v += term;
+                else mgb[(size_t)(m - 1) * T + n - 1] = term;  // odd m: an even node
+            }
+            mgb[(size_t)h_a * T + n - 1] = v;
+        }
+        for (int r = warp; r < my_rows; r += kCWarps) {
+            const int ci = crank + NC * r;
+            for (int ai = lane; ai < ci; ai += 32) {
+                float *cell = lgb + (size_t)(2 * ai + 1) * 2 * L + (2 * ci + 1);
+                cell[0] = D0[r * lk_stride + ai];
+                cell[L] = D1[r * lk_stride + ai];
+            }
+        }
+    }
 }
 
 struct ClusterGeometry {
@@ -674,18 +756,37 @@ int launch_loss_fwd_fast(const float *match_all, const float *links, const int64
     return PCFGNAT_ERR_UNSUPPORTED;
 }
 
+// Shared memory of the outside kernel at the cluster size the geometry picks first, with the gradient sums.
+static size_t outside_grad_smem(const ClusterGeometry &g, int T) {
+    return ((size_t)8 * g.cs + (size_t)4 * g.rows_cap * g.lk_stride + (size_t)2 * g.rows_cap * (T + 2)) * sizeof(float);
+}
+
+bool outside_cluster_fits_grad(int B, int L, int T) {
+    const int Mc = main_slots(L, 1);
+    if (Mc > kCThreads / 2) return false;  // parents' scalars from the low threads, emission gradients from the high ones
+    const ClusterGeometry g = cluster_geometry(B, Mc, T + 2);
+    return g.nc >= 2 && outside_grad_smem(g, T) <= (size_t)kSmemLimit - 1024;
+}
+
+// mg, lg both given: the kernel also writes both gradients from the emission shares the inside pass left in mg;
+// only at the first cluster size (PCFGNAT_ERR_UNSUPPORTED otherwise: the caller then runs the two kernels).
 int launch_outside_cluster(const float *grad_output, const float *S, const float *match_all, const float *links,
-                           const int64_t *ol, const int64_t *tl, int B, int L, int T, float *G, int *status,
-                           cudaStream_t st) {
+                           const int64_t *ol, const int64_t *tl, int B, int L, int T, float *G, float *mg, float *lg,
+                           int *status, cudaStream_t st) {
     const int Mc = main_slots(L, 1);
     if (Mc > kCThreads) return PCFGNAT_ERR_UNSUPPORTED;  // one thread per parent fetches the step's scalars
     ClusterGeometry g = cluster_geometry(B, Mc, T + 2);
+    if (mg && lg) {
+        if (!outside_cluster_fits_grad(B, L, T)) return PCFGNAT_ERR_UNSUPPORTED;
+        return launch_cluster(outside_cluster_kernel<true>, B, g.nc, outside_grad_smem(g, T), st, grad_output, S, match_all,
+                              links, ol, tl, L, T, G, mg, lg, status, Mc, g.cs, g.rows_cap, g.lk_stride);
+    }
     for (; g.nc >= 1; g.nc /= 2) {
         g.rows_cap = (Mc + g.nc - 1) / g.nc;
         g.smem_out = ((size_t)8 * g.cs + (size_t)2 * g.rows_cap * g.lk_stride + (size_t)2 * g.rows_cap * (T + 2)) * sizeof(float);
         if (g.smem_out > (size_t)kSmemLimit - 1024) break;
-        int rc = launch_cluster(outside_cluster_kernel, B, g.nc, g.smem_out, st, grad_output, S, match_all, links, ol, tl,
-                                L, T, G, status, Mc, g.cs, g.rows_cap, g.lk_stride);
+        int rc = launch_cluster(outside_cluster_kernel<false>, B, g.nc, g.smem_out, st, grad_output, S, match_all, links, ol,
+                                tl, L, T, G, nullptr, nullptr, status, Mc, g.cs, g.rows_cap, g.lk_stride);
         if (rc != PCFGNAT_ERR_UNSUPPORTED) return rc;
     }
     return PCFGNAT_ERR_UNSUPPORTED;

@@ -373,9 +373,10 @@ def test_fused_loss_model_graph_size(ops, syn, monkeypatch):
     assert ops.read_status(DEV) == 0
 
 
+@pytest.mark.parametrize("batch", [97, 6])  # one CTA per sentence; a cluster of CTAs per sentence
 @pytest.mark.parametrize("L_even", [True, False])
-def test_outside_pass_with_fused_gradients_matches_the_gradient_kernel(ops, syn, monkeypatch, L_even):
-    """Fused forward + backward on a batch that runs one CTA per sentence: the outside kernel that also sums up
+def test_outside_pass_with_fused_gradients_matches_the_gradient_kernel(ops, syn, monkeypatch, L_even, batch):
+    """Fused forward + backward: the outside kernel (single-CTA or cluster family, by batch size) that also sums up
     both gradients (emission gradients from the shares the inside pass leaves in match_all_grad) against the
     outside kernel followed by the gradient kernel (PCFGNAT_FUSED_GRAD=0): both gradients to rounding, and both
     against the oracle.  The batch has odd graph lengths, a
@@ -383,7 +384,7 @@ def test_outside_pass_with_fused_gradients_matches_the_gradient_kernel(ops, syn,
     monkeypatch.delenv("PCFGNAT_DP_KERNEL", raising=False)
     monkeypatch.delenv("PCFGNAT_DP_CLUSTER_SIZE", raising=False)
     monkeypatch.delenv("PCFGNAT_EXACT_ORDER", raising=False)
-    b, ma = _loss_inputs(syn, syn.Workload("fg", batch=97, vocab=40, hidden=8, src_min=3, src_max=20,
+    b, ma = _loss_inputs(syn, syn.Workload("fg", batch=batch, vocab=40, hidden=8, src_min=3, src_max=20 if batch > 6 else 60,
                                            emissions="logits"), 77)
     links = b.links
     if not L_even:  # an odd padded width: the zero fill cannot use 16-byte stores
