@@ -1,10 +1,17 @@
 /*
  * libpcfgnat — C ABI of the B200 (sm_100a) kernels for PCFG-NAT's structured loss and
  * decoding path.  Plain pointers and sizes only; every pointer is a DEVICE pointer unless
- * marked "host".  The caller owns all memory (inputs, outputs, scratch); the library
- * keeps no state between calls, launches on the stream it is given and never
- * synchronises or calls exit().  Each entry point replaces the reference interface cited
- * beside it (paths relative to the reference project root).
+ * marked "host".  The caller owns the memory of inputs, outputs and scratch; the library
+ * launches on the stream it is given and never synchronises or calls exit().  It keeps no
+ * state between calls, with these exceptions:
+ *   - pcfgnat_loss_fwd_bwd_static uses a fixed PCFGNAT_STATIC_SCRATCH_BYTES array inside the
+ *     library's device image, shared by all calls on a device (they must not overlap), and
+ *     caches that array's address per device (stale after cudaDeviceReset);
+ *   - the largest dynamic shared-memory size requested per kernel and device is remembered
+ *     (an attribute of the loaded function, also lost by cudaDeviceReset);
+ *   - the exchange buffers of pcfgnat_loss_stats_exchange carry an epoch counter from call to call.
+ * Each entry point replaces the reference interface cited beside it (paths relative to the
+ * reference project root).
  *
  * Conventions shared by all entry points
  *   B            sentences in the batch
@@ -189,31 +196,55 @@ int pcfgnat_loss_stats(const float *sentence_loss, const int64_t *target_length,
  * peer_buffers: device array of `world` device pointers, entry r = rank r's exchange buffer as mapped in THIS
  * process (peer-accessible memory, e.g. torch symmetric memory), each PCFGNAT_EXCHANGE_BYTES(world) bytes,
  * zero-filled before the first call and used for nothing else.  Every rank must make the same sequence of
- * calls.  A peer that does not arrive within the bounded wait contributes zeros and sets
- * PCFGNAT_STATUS_TIMEOUT in `status`. */
+ * calls.  The wait for a peer is bounded (2^21 polls 200 ns apart: about half a second).  When a peer has not
+ * arrived by then the call does NOT return a short sum: all three numbers of `stats` are NaN on the rank that
+ * gave up and PCFGNAT_STATUS_TIMEOUT is set in `status`; the context stays usable.  A caller whose ranks may
+ * drift further apart than that (a checkpoint written by one rank, validation on rank 0) must either line the
+ * ranks up before the step or sum pcfgnat_loss_stats with an all-reduce, which simply waits. */
 #define PCFGNAT_EXCHANGE_MAX_WORLD 32
 #define PCFGNAT_EXCHANGE_BYTES(world) (64u + 64u * (unsigned)(world))
 int pcfgnat_loss_stats_exchange(const float *sentence_loss, const int64_t *target_length, int B,
                                 const uint64_t *peer_buffers, int rank, int world, float *stats, int *status,
                                 void *stream);
 
-/* Glancing sampler between the two decoder passes, strategy "number-random"
- * (fs_plugins/criterions/nat_pcfg_loss.py:216-267), one launch instead of ~15 torch operators.
+/* Glancing sampler between the two decoder passes (fs_plugins/criterions/nat_pcfg_loss.py:216-267), one launch
+ * instead of ~15 torch operators.
  * path [B][L] int64: aligned target position of each graph node (the best tree), negative = none;
- * pred_tokens [B][L], tgt_tokens [B][T], prev_output_tokens [B][L] int64; noise [B][L] f32: the
- * caller's standard-normal draws (the reference's torch.randn).  Outputs:
+ * pred_tokens [B][L], tgt_tokens [B][T], prev_output_tokens [B][L] int64.  The random draws are the caller's
+ * (torch's generator stays the source of randomness): noise [B][L] f32 standard-normal (the reference's
+ * torch.randn; strategies NUMBER_RANDOM and CMLM), uniform f32 in [0, 1) (the reference's torch.rand): [B] for
+ * CMLM, [B][L] for FRACTION, unused (may be NULL) for NUMBER_RANDOM.  strategy = the criterion's
+ * --glance-strategy: "number-random", "cmlm", or none (FRACTION).  Outputs:
  *   matchmask [B][T][L] u8   1 where node l is aligned to target t
  *   oracle    [B][L]   int64 target token of the node's alignment (position 0 when unaligned)
  *   same_num  [B]      int64 aligned nodes whose predicted token already equals the oracle
- *   glance_num[B]      int64 (long)((n_b - same_num) * context_p + 0.5) in float32
- *   keep      [B][L]   u8    the glance_num nodes with the largest noise among the aligned ones
- *                            (ties and glance_num beyond the aligned count as torch.sort + >= give)
+ *   glance_num[B]      int64 NUMBER_RANDOM: (long)((n_b - same_num) * context_p + 0.5) in float32;
+ *                            CMLM: (long)(n_b * uniform[b] + 0.5); FRACTION: the number of kept nodes
+ *   keep      [B][L]   u8    NUMBER_RANDOM / CMLM: the glance_num nodes with the largest noise among the aligned
+ *                            ones (ties and glance_num beyond the aligned count as torch.sort + >= give);
+ *                            FRACTION: aligned and uniform[b][l] < (n_b - same_num) / n_b * context_p
  *   glat_prev [B][L]   int64 prev_output_tokens with the oracle token at the kept nodes
- * The reference's second draw (rand < keep_prob, keep_prob in {0,1}) selects the same mask. */
+ * For the two counting strategies the reference's second draw (rand < keep_prob, keep_prob in {0,1}) selects the
+ * same mask. */
+#define PCFGNAT_GLANCE_NUMBER_RANDOM 0
+#define PCFGNAT_GLANCE_CMLM 1
+#define PCFGNAT_GLANCE_FRACTION 2
 int pcfgnat_glance_select(const int64_t *path, const int64_t *pred_tokens, const int64_t *tgt_tokens,
                           const int64_t *prev_output_tokens, const int64_t *target_length, const float *noise,
-                          float context_p, int B, int L, int T, uint8_t *matchmask, int64_t *oracle,
-                          int64_t *same_num, int64_t *glance_num, uint8_t *keep, int64_t *glat_prev, void *stream);
+                          const float *uniform, int strategy, float context_p, int B, int L, int T, uint8_t *matchmask,
+                          int64_t *oracle, int64_t *same_num, int64_t *glance_num, uint8_t *keep, int64_t *glat_prev,
+                          void *stream);
+
+/* Force-emit mask of the training pass (fs_plugins/criterions/nat_pcfg_loss.py:116-121, active unless
+ * --no-force-emit): a node whose token the glancing sampler revealed (keep [B][L] u8) may only emit the target
+ * position it is aligned to (matchmask [B][T][L] u8, as pcfgnat_glance_select writes it):
+ *   out[b][l][t] = keep[b][l] && !matchmask[b][t][l] ? -inf : match[b][l][t]
+ * and, as the reference detaches that part, carries no gradient:
+ *   out[b][l][t] = keep[b][l] ? 0 : grad[b][l][t]            (pcfgnat_force_emit_grad)
+ * match, grad, out [B][L][T] f32; out may be the input itself. */
+int pcfgnat_force_emit(const float *match, const uint8_t *matchmask, const uint8_t *keep, int B, int L, int T,
+                       float *out, void *stream);
+int pcfgnat_force_emit_grad(const float *grad, const uint8_t *keep, int B, int L, int T, float *out, void *stream);
 
 /* The transition log-probabilities links [B][L][2][L] f32 from the projected link features: extract_links()
  * after its link projections (fs_plugins/models/glat_decomposed_with_link_two_hands_tri_pcfg.py:163-199) as two

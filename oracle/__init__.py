@@ -24,21 +24,44 @@ _f32p = ctypes.POINTER(ctypes.c_float)
 _i64p = ctypes.POINTER(ctypes.c_int64)
 
 
-def build(force=False):
-    """Compile pcfg_oracle.c with gcc (no fast-math, no FMA contraction, OpenMP over sentences)."""
-    if not force and os.path.isfile(_LIB) and os.path.getmtime(_LIB) >= os.path.getmtime(_SRC):
-        return _LIB
-    cmd = ["gcc", "-O2", "-std=c11", "-fno-fast-math", "-ffp-contract=off", "-fopenmp", "-shared", "-fPIC",
-           _SRC, "-o", _LIB, "-lm"]
+# Two builds of the same source: "faithful" (no FMA contraction, -O2: the checker, bit-comparable with the
+# reference kernels' arithmetic) and "native" (-O3 -march=native: only ever timed, as a second CPU figure).
+_FLAGS = {"faithful": ["-O2", "-std=c11", "-fno-fast-math", "-ffp-contract=off", "-fopenmp"],
+          "native": ["-O3", "-march=native", "-std=c11", "-fno-fast-math", "-fopenmp"]}
+_LIBS = {"faithful": _LIB, "native": os.path.join(_HERE, "liboracle_native.so")}
+_loaded = {}
+_active = "faithful"
+
+
+def build(force=False, which="faithful"):
+    """Compile pcfg_oracle.c with gcc (no fast-math, OpenMP over sentences; see ``_FLAGS``)."""
+    out = _LIBS[which]
+    if not force and os.path.isfile(out) and os.path.getmtime(out) >= os.path.getmtime(_SRC):
+        return out
+    cmd = ["gcc", *_FLAGS[which], "-shared", "-fPIC", _SRC, "-o", out, "-lm"]
     subprocess.run(cmd, check=True)
-    return _LIB
+    return out
+
+
+def use_build(which):
+    """Selects the build the wrappers below call ("faithful" is the checker; "native" is for timing only)."""
+    global _active, _lib
+    if which not in _FLAGS:
+        raise ValueError(which)
+    _active = which
+    _lib = None
+
+
+def build_flags():
+    return " ".join(_FLAGS[_active])
 
 
 def lib():
     global _lib
     if _lib is None:
-        build()
-        _lib = ctypes.CDLL(_LIB)
+        if _active not in _loaded:
+            _loaded[_active] = ctypes.CDLL(build(which=_active))
+        _lib = _loaded[_active]
     return _lib
 
 

@@ -10,12 +10,17 @@ the output directory is git-ignored and only holds build products.
 The resulting module is the checker the golden fixtures are generated from
 (tests/golden/make_golden_ref.py) and is never imported by the product package.
 
-Usage:  python oracle/build_ref.py [--reference /path/to/PCFG-NAT]
+Beside the extension it stages a byte-for-byte copy of the reference's Python wrapper
+(fs_plugins/custom_ops/pcfg_loss.py) into the same git-ignored directory, so that a test can run the
+UNMODIFIED wrapper on top of this package's extension object where the reference checkout is not mounted.
+
+Usage:  python oracle/build_ref.py --reference /path/to/PCFG-NAT      (or PCFGNAT_REFERENCE=/path/to/PCFG-NAT)
 """
 import argparse
 import importlib.machinery
 import importlib.util
 import os
+import shutil
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
@@ -31,8 +36,39 @@ SOURCES = [
 ]
 
 
+WRAPPER_COPY = "reference_pcfg_loss_wrapper.py"
+
+
 def ref_so_path():
     return os.path.join(REF_DIR, MODULE_NAME + ".so")
+
+
+def ref_wrapper_path():
+    return os.path.join(REF_DIR, WRAPPER_COPY)
+
+
+def find_reference():
+    """The reference checkout: $PCFGNAT_REFERENCE, else a directory ``reference`` beside this repository.
+    None when neither holds fs_plugins/custom_ops."""
+    cands = [os.environ.get("PCFGNAT_REFERENCE"), os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")]
+    for c in cands:
+        if c and os.path.isdir(os.path.join(c, "fs_plugins", "custom_ops")):
+            return c
+    return None
+
+
+def stage_wrapper(reference_root):
+    """Copies the reference's own Python wrapper, unchanged, beside the built extension."""
+    os.makedirs(REF_DIR, exist_ok=True)
+    shutil.copyfile(os.path.join(reference_root, "fs_plugins", "custom_ops", "pcfg_loss.py"), ref_wrapper_path())
+    return ref_wrapper_path()
+
+
+def build_if_stale(reference_root):
+    if not os.path.isfile(ref_so_path()):
+        build(reference_root)
+    if not os.path.isfile(ref_wrapper_path()):
+        stage_wrapper(reference_root)
 
 
 def build(reference_root, verbose=False):
@@ -77,8 +113,11 @@ def load_ref():
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default=os.environ.get("PCFGNAT_REFERENCE", "/root/reference"))
+    ap.add_argument("--reference", default=find_reference(), help="root of the PCFG-NAT checkout")
     ap.add_argument("-v", "--verbose", action="store_true")
     a = ap.parse_args()
+    if not a.reference:
+        ap.error("no reference checkout found: pass --reference or set PCFGNAT_REFERENCE")
     p = build(a.reference, a.verbose)
+    stage_wrapper(a.reference)
     print("built", p, file=sys.stderr)

@@ -32,7 +32,9 @@ SIGNATURES = {
     "pcfgnat_copy_links_main_rows": (c_int, [c_void] * 2 + [c_int] * 3 + [c_void]),
     "pcfgnat_loss_stats": (c_int, [c_void] * 2 + [c_int] + [c_void] * 2),
     "pcfgnat_loss_stats_exchange": (c_int, [c_void] * 2 + [c_int] + [c_void] + [c_int] * 2 + [c_void] * 3),
-    "pcfgnat_glance_select": (c_int, [c_void] * 6 + [ctypes.c_float] + [c_int] * 3 + [c_void] * 7),
+    "pcfgnat_glance_select": (c_int, [c_void] * 7 + [c_int, ctypes.c_float] + [c_int] * 3 + [c_void] * 7),
+    "pcfgnat_force_emit": (c_int, [c_void] * 3 + [c_int] * 3 + [c_void] * 2),
+    "pcfgnat_force_emit_grad": (c_int, [c_void] * 2 + [c_int] * 3 + [c_void] * 2),
 }
 
 

@@ -240,15 +240,33 @@ int pcfgnat_loss_stats_exchange(const float *sentence_loss, const int64_t *targe
 
 int pcfgnat_glance_select(const int64_t *path, const int64_t *pred_tokens, const int64_t *tgt_tokens,
                           const int64_t *prev_output_tokens, const int64_t *target_length, const float *noise,
-                          float context_p, int B, int L, int T, uint8_t *matchmask, int64_t *oracle,
-                          int64_t *same_num, int64_t *glance_num, uint8_t *keep, int64_t *glat_prev, void *stream) {
+                          const float *uniform, int strategy, float context_p, int B, int L, int T, uint8_t *matchmask,
+                          int64_t *oracle, int64_t *same_num, int64_t *glance_num, uint8_t *keep, int64_t *glat_prev,
+                          void *stream) {
     if (B < 0 || L < 1 || T < 1) return PCFGNAT_ERR_INVALID_ARGUMENT;
-    if (B && (!path || !pred_tokens || !tgt_tokens || !prev_output_tokens || !target_length || !noise || !matchmask ||
-              !oracle || !same_num || !glance_num || !keep || !glat_prev))
+    if (strategy != PCFGNAT_GLANCE_NUMBER_RANDOM && strategy != PCFGNAT_GLANCE_CMLM && strategy != PCFGNAT_GLANCE_FRACTION)
+        return PCFGNAT_ERR_UNSUPPORTED;
+    if (B && (!path || !pred_tokens || !tgt_tokens || !prev_output_tokens || !target_length || !matchmask || !oracle ||
+              !same_num || !glance_num || !keep || !glat_prev))
         return PCFGNAT_ERR_INVALID_ARGUMENT;
-    return launch_glance_select(path, pred_tokens, tgt_tokens, prev_output_tokens, target_length, noise, context_p, B,
-                                L, T, matchmask, oracle, same_num, glance_num, keep, glat_prev,
+    if (B && strategy != PCFGNAT_GLANCE_FRACTION && !noise) return PCFGNAT_ERR_INVALID_ARGUMENT;
+    if (B && strategy != PCFGNAT_GLANCE_NUMBER_RANDOM && !uniform) return PCFGNAT_ERR_INVALID_ARGUMENT;
+    return launch_glance_select(path, pred_tokens, tgt_tokens, prev_output_tokens, target_length, noise, uniform,
+                                strategy, context_p, B, L, T, matchmask, oracle, same_num, glance_num, keep, glat_prev,
                                 static_cast<cudaStream_t>(stream));
+}
+
+int pcfgnat_force_emit(const float *match, const uint8_t *matchmask, const uint8_t *keep, int B, int L, int T,
+                       float *out, void *stream) {
+    if (B < 0 || L < 1 || T < 1) return PCFGNAT_ERR_INVALID_ARGUMENT;
+    if (B && (!match || !matchmask || !keep || !out)) return PCFGNAT_ERR_INVALID_ARGUMENT;
+    return launch_force_emit(match, matchmask, keep, B, L, T, out, static_cast<cudaStream_t>(stream));
+}
+
+int pcfgnat_force_emit_grad(const float *grad, const uint8_t *keep, int B, int L, int T, float *out, void *stream) {
+    if (B < 0 || L < 1 || T < 1) return PCFGNAT_ERR_INVALID_ARGUMENT;
+    if (B && (!grad || !keep || !out)) return PCFGNAT_ERR_INVALID_ARGUMENT;
+    return launch_force_emit_grad(grad, keep, B, L, T, out, static_cast<cudaStream_t>(stream));
 }
 
 int pcfgnat_copy_links_main_rows(void *dst, const void *src, int B, int L, int max_left, void *stream) {

@@ -136,9 +136,12 @@ int launch_loss_stats(const float *loss, const int64_t *tl, int B, float *stats,
 int launch_loss_stats_exchange(const float *loss, const int64_t *tl, int B, const uint64_t *peer_bufs, int rank, int world,
                                float *stats, int *status, cudaStream_t st);
 int launch_glance_select(const int64_t *path, const int64_t *pred, const int64_t *tgt, const int64_t *prev,
-                         const int64_t *tl, const float *noise, float context_p, int B, int L, int T,
-                         uint8_t *matchmask, int64_t *oracle, int64_t *same_num, int64_t *glance_num, uint8_t *keep,
-                         int64_t *glat_prev, cudaStream_t st);
+                         const int64_t *tl, const float *noise, const float *uniform, int strategy, float context_p,
+                         int B, int L, int T, uint8_t *matchmask, int64_t *oracle, int64_t *same_num,
+                         int64_t *glance_num, uint8_t *keep, int64_t *glat_prev, cudaStream_t st);
+int launch_force_emit(const float *match, const uint8_t *matchmask, const uint8_t *keep, int B, int L, int T, float *out,
+                      cudaStream_t st);
+int launch_force_emit_grad(const float *grad, const uint8_t *keep, int B, int L, int T, float *out, cudaStream_t st);
 
 size_t proj_workspace_bytes(int B, int L, int T, int V);
 int launch_proj(const void *hidden, const void *weight, const int64_t *targets, const int64_t *ol, const int64_t *tl,

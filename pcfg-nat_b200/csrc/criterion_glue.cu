@@ -10,9 +10,12 @@
 //    stores, no multimem) and adds up what the peers stored into its own.  It replaces the 12-byte NCCL
 //    all-reduce that otherwise follows the kernel, whose launch latency is several percent of a step;
 //  * glance_select_kernel — the glancing sampler between the two decoder passes
-//    (nat_pcfg_loss.py:216-267, strategy "number-random"): alignment -> match mask, oracle tokens, number of
-//    already-correct predictions, the glance_nums positions with the largest noise, and the decoder input
-//    with the oracle tokens revealed at those positions.
+//    (nat_pcfg_loss.py:216-267, all three strategies): alignment -> match mask, oracle tokens, number of
+//    already-correct predictions, the kept positions (the glance_nums ones with the largest noise, or an
+//    independent draw per node), and the decoder input with the oracle tokens revealed at those positions;
+//  * force_emit_kernel / force_emit_grad_kernel — the force-emit mask of the training pass
+//    (nat_pcfg_loss.py:116-121): a node whose token was revealed may only emit the target position it is
+//    aligned to, and carries no gradient.
 #include "common.cuh"
 
 namespace pcfgnat {
@@ -66,6 +69,7 @@ __global__ void loss_stats_exchange_kernel(const float *__restrict__ loss, const
     __shared__ float part[PCFGNAT_EXCHANGE_MAX_WORLD][3];
     __shared__ unsigned epoch_s;
     float s = 0.f, bad = 0.f;
+    bool arrived = true;
     for (int b = threadIdx.x; b < B; b += blockDim.x) {
         const float v = loss[b];
         if (isinf(v) || isnan(v)) {
@@ -91,7 +95,7 @@ __global__ void loss_stats_exchange_kernel(const float *__restrict__ loss, const
         d[2] = bad;
         __threadfence_system();
         *reinterpret_cast<volatile unsigned *>(dst + 16) = epoch;
-        // the partial peer threadIdx.x stored here; bounded wait (a peer that never arrives leaves zeros and a flag)
+        // the partial peer threadIdx.x stored here; bounded wait: 2^21 polls 200 ns apart, about half a second
         const char *src = mine + slot0 + (size_t)32 * threadIdx.x;
         bool there = false;
         for (unsigned it = 0; it < (1u << 21) && !there; ++it) {
@@ -103,9 +107,10 @@ __global__ void loss_stats_exchange_kernel(const float *__restrict__ loss, const
         part[threadIdx.x][0] = there ? q[0] : 0.f;
         part[threadIdx.x][1] = there ? q[1] : 0.f;
         part[threadIdx.x][2] = there ? q[2] : 0.f;
+        arrived = there;
         if (!there) flag(status, PCFGNAT_STATUS_TIMEOUT);
     }
-    __syncthreads();
+    const int missing = __syncthreads_count((int)threadIdx.x < world && !arrived);
     if (threadIdx.x == 0) {
         float t0 = 0.f, t1 = 0.f, t2 = 0.f;
         for (int r = 0; r < world; r++) {  // rank order on every rank: the same sum everywhere
@@ -113,9 +118,12 @@ __global__ void loss_stats_exchange_kernel(const float *__restrict__ loss, const
             t1 += part[r][1];
             t2 += part[r][2];
         }
-        stats[0] = t0;
-        stats[1] = t1;
-        stats[2] = t2;
+        // a short sum must not pass for a loss: with a peer missing all three numbers are NaN, so that the
+        // host sees it in the value it reads anyway (the status word carries PCFGNAT_STATUS_TIMEOUT as well)
+        const float poison = missing ? CUDART_NAN_F : 0.f;
+        stats[0] = t0 + poison;
+        stats[1] = t1 + poison;
+        stats[2] = t2 + poison;
     }
 }
 
@@ -125,17 +133,24 @@ __global__ void loss_stats_exchange_kernel(const float *__restrict__ loss, const
 //   matchmask[b][t][l] = (p == t)
 //   oracle[l]    = tgt[b][max(p, 0)]
 //   same         = #{l : pred[l] == oracle[l] and aligned[l]}
+// strategy PCFGNAT_GLANCE_NUMBER_RANDOM (nat_pcfg_loss.py:232-238):
 //   k            = (long)((n_b - same) * context_p + 0.5)          (float32 arithmetic, as torch does it)
 //   keep[l]      = noise'[l] >= (k-th largest of noise')           noise' = noise, -100 where not aligned
 //                = fewer than k entries of noise' are strictly larger than noise'[l];   nothing if k == 0,
 //                  and k < 0 (never the case for a real alignment) acts as k = 1
+// strategy PCFGNAT_GLANCE_CMLM (:240-246): the same with k = (long)(n_b * uniform[b] + 0.5), uniform [B]
+// strategy PCFGNAT_GLANCE_FRACTION (glance_strategy None, :229-230):
+//   keep[l]      = aligned[l] and uniform[b][l] < ((n_b - same) / n_b) * context_p,  uniform [B][L];
+//   glance_num   = number of kept nodes
 //   glat_prev[l] = keep[l] ? oracle[l] : prev[l]
-// The reference then draws rand < keep_prob with keep_prob in {0, 1}: the same mask, so no second draw.
+// For the two counting strategies the reference then draws rand < keep_prob with keep_prob in {0, 1}: the same
+// mask, so no second draw.
 __global__ void glance_select_kernel(const int64_t *__restrict__ path, const int64_t *__restrict__ pred,
                                      const int64_t *__restrict__ tgt, const int64_t *__restrict__ prev,
-                                     const int64_t *__restrict__ tl, const float *__restrict__ noise, float context_p,
-                                     int L, int T, uint8_t *matchmask, int64_t *oracle, int64_t *same_num,
-                                     int64_t *glance_num, uint8_t *keep, int64_t *glat_prev) {
+                                     const int64_t *__restrict__ tl, const float *__restrict__ noise,
+                                     const float *__restrict__ uniform, int strategy, float context_p, int L, int T,
+                                     uint8_t *matchmask, int64_t *oracle, int64_t *same_num, int64_t *glance_num,
+                                     uint8_t *keep, int64_t *glat_prev) {
     extern __shared__ float sm_noise[];  // [L]
     __shared__ float scratch[32];
     const int b = blockIdx.x;
@@ -148,7 +163,8 @@ __global__ void glance_select_kernel(const int64_t *__restrict__ path, const int
         const int64_t o = tgt[(size_t)b * T + (p < 0 ? 0 : p)];
         oracle[(size_t)b * L + l] = o;
         if (aligned && pred[(size_t)b * L + l] == o) same += 1.f;
-        sm_noise[l] = aligned ? noise[(size_t)b * L + l] : -100.f;
+        if (strategy == PCFGNAT_GLANCE_FRACTION) sm_noise[l] = aligned ? 1.f : 0.f;
+        else sm_noise[l] = aligned ? noise[(size_t)b * L + l] : -100.f;
     }
     for (int i = threadIdx.x; i < T * L; i += blockDim.x) {
         const int t = i / L, l = i - t * L;
@@ -157,7 +173,24 @@ __global__ void glance_select_kernel(const int64_t *__restrict__ path, const int
     same = block_sum(same, scratch);  // exact: a count below 2^24; its barriers also publish sm_noise
     const int64_t n = tl[b];
     const int64_t same_i = (int64_t)same;
-    const int64_t k = (int64_t)((float)(n - same_i) * context_p + 0.5f);
+    if (strategy == PCFGNAT_GLANCE_FRACTION) {
+        const float kp = ((float)(n - same_i) / (float)n) * context_p;
+        float kept = 0.f;
+        for (int l = threadIdx.x; l < L; l += blockDim.x) {
+            const bool k_l = uniform[(size_t)b * L + l] < kp * sm_noise[l];
+            keep[(size_t)b * L + l] = k_l;
+            glat_prev[(size_t)b * L + l] = k_l ? oracle[(size_t)b * L + l] : prev[(size_t)b * L + l];
+            kept += k_l ? 1.f : 0.f;
+        }
+        kept = block_sum(kept, scratch);
+        if (threadIdx.x == 0) {
+            same_num[b] = same_i;
+            glance_num[b] = (int64_t)kept;
+        }
+        return;
+    }
+    const int64_t k = strategy == PCFGNAT_GLANCE_CMLM ? (int64_t)((float)n * uniform[b] + 0.5f)
+                                                      : (int64_t)((float)(n - same_i) * context_p + 0.5f);
     if (threadIdx.x == 0) {
         same_num[b] = same_i;
         glance_num[b] = k;
@@ -170,6 +203,27 @@ __global__ void glance_select_kernel(const int64_t *__restrict__ path, const int
         keep[(size_t)b * L + l] = kp;
         glat_prev[(size_t)b * L + l] = kp ? oracle[(size_t)b * L + l] : prev[(size_t)b * L + l];
     }
+}
+
+// out[b][l][t] = keep[b][l] && !matchmask[b][t][l] ? -inf : match[b][l][t]   (out may be match itself)
+__global__ void force_emit_kernel(const float *match, const uint8_t *__restrict__ matchmask,
+                                  const uint8_t *__restrict__ keep, int L, int T, size_t total, float *out) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t row = i / T;  // b * L + l
+        const int t = (int)(i - row * T);
+        const size_t b = row / L;
+        const int l = (int)(row - b * L);
+        float v = match[i];
+        if (keep[row] && !matchmask[(b * T + t) * L + l]) v = neg_inf();
+        out[i] = v;
+    }
+}
+
+// out[b][l][t] = keep[b][l] ? 0 : grad[b][l][t]   (out may be grad itself)
+__global__ void force_emit_grad_kernel(const float *grad, const uint8_t *__restrict__ keep, int T, size_t total,
+                                       float *out) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
+        out[i] = keep[i / T] ? 0.f : grad[i];
 }
 
 }  // namespace
@@ -186,14 +240,31 @@ int launch_loss_stats_exchange(const float *loss, const int64_t *tl, int B, cons
 }
 
 int launch_glance_select(const int64_t *path, const int64_t *pred, const int64_t *tgt, const int64_t *prev,
-                         const int64_t *tl, const float *noise, float context_p, int B, int L, int T,
-                         uint8_t *matchmask, int64_t *oracle, int64_t *same_num, int64_t *glance_num, uint8_t *keep,
-                         int64_t *glat_prev, cudaStream_t st) {
+                         const int64_t *tl, const float *noise, const float *uniform, int strategy, float context_p,
+                         int B, int L, int T, uint8_t *matchmask, int64_t *oracle, int64_t *same_num,
+                         int64_t *glance_num, uint8_t *keep, int64_t *glat_prev, cudaStream_t st) {
     if (B == 0) return PCFGNAT_OK;
     const size_t smem = (size_t)L * sizeof(float);
     if (smem > 48 * 1024 && ensure_dynamic_smem(glance_select_kernel, smem) != cudaSuccess) return PCFGNAT_ERR_TOO_LARGE;
-    glance_select_kernel<<<B, 256, smem, st>>>(path, pred, tgt, prev, tl, noise, context_p, L, T, matchmask, oracle,
-                                               same_num, glance_num, keep, glat_prev);
+    glance_select_kernel<<<B, 256, smem, st>>>(path, pred, tgt, prev, tl, noise, uniform, strategy, context_p, L, T,
+                                               matchmask, oracle, same_num, glance_num, keep, glat_prev);
+    return cuda_rc(cudaGetLastError());
+}
+
+int launch_force_emit(const float *match, const uint8_t *matchmask, const uint8_t *keep, int B, int L, int T, float *out,
+                      cudaStream_t st) {
+    const size_t total = (size_t)B * L * T;
+    if (total == 0) return PCFGNAT_OK;
+    const int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
+    force_emit_kernel<<<blocks, 256, 0, st>>>(match, matchmask, keep, L, T, total, out);
+    return cuda_rc(cudaGetLastError());
+}
+
+int launch_force_emit_grad(const float *grad, const uint8_t *keep, int B, int L, int T, float *out, cudaStream_t st) {
+    const size_t total = (size_t)B * L * T;
+    if (total == 0) return PCFGNAT_OK;
+    const int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
+    force_emit_grad_kernel<<<blocks, 256, 0, st>>>(grad, keep, T, total, out);
     return cuda_rc(cudaGetLastError());
 }
 

@@ -380,6 +380,9 @@ __global__ void __launch_bounds__(kCThreads, 1)
         else __syncthreads();
     }
     if (!arrived) flag(status, PCFGNAT_STATUS_TIMEOUT);
+    // no CTA leaves (its shared memory with it) while a peer may still send to it; every wait above is bounded,
+    // so every CTA gets here
+    if (NC > 1) cluster.sync();
     for (int i = tid; i < my_rows * (n - 1); i += kCThreads) {  // computed cells: columns 0 .. n-2
         const int r = i / (n - 1), t = i - r * (n - 1);
         Sb[(size_t)(crank + NC * r) * W + t] = own[r * W + t];
@@ -585,6 +588,7 @@ __global__ void __launch_bounds__(kCThreads, 1)
         if (NC > 1) arrived = dsm_wait_column(bar, (s >> 1) & 1) && arrived;
     }
     if (!arrived) flag(status, PCFGNAT_STATUS_TIMEOUT);
+    if (NC > 1) cluster.sync();  // as in the inside pass: nobody exits while a peer may still send to it
     for (int i = tid; i < my_rows * (n - 1); i += kCThreads) {  // columns 1 .. n-1 of this CTA's nodes
         const int r = i / (n - 1), t = 1 + (i - r * (n - 1));
         Gb[(size_t)(crank + NC * r) * W + t] = own[r * W + t];

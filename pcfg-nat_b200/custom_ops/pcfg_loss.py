@@ -538,19 +538,30 @@ class _Kernel:
         return stats
 
     @staticmethod
-    def glance_select(path, pred_tokens, tgt_tokens, prev_output_tokens, target_length, noise, context_p):
-        """The glancing sampler of the criterion (nat_pcfg_loss.py:216-267, strategy "number-random") in one
-        launch.  ``noise`` holds the caller's standard-normal draws.  Returns a dict with matchmask [B,T,L] bool,
-        oracle [B,L], same_num [B], glance_num [B], keep_word_mask [B,L] bool, glat_prev_output_tokens [B,L]."""
+    def glance_select(path, pred_tokens, tgt_tokens, prev_output_tokens, target_length, noise, context_p,
+                      strategy="number-random", uniform=None):
+        """The glancing sampler of the criterion (nat_pcfg_loss.py:216-267) in one launch.  ``strategy`` is the
+        criterion's ``--glance-strategy``: "number-random", "cmlm" or None.  The random draws are the caller's:
+        ``noise`` [B, L] standard-normal (the two counting strategies), ``uniform`` in [0, 1): [B] for "cmlm",
+        [B, L] for None.  Returns a dict with matchmask [B,T,L] bool, oracle [B,L], same_num [B], glance_num [B],
+        keep_word_mask [B,L] bool, glat_prev_output_tokens [B,L]."""
         _require_cuda()
         dev = path.device
         if not path.is_cuda or path.dim() != 2:
             raise RuntimeError("path must be a CUDA tensor [batch, prelen]")
         B, L = path.shape
+        if strategy not in GLANCE_STRATEGIES:
+            raise RuntimeError(f"unknown glance strategy {strategy!r}")
+        code = GLANCE_STRATEGIES[strategy]
 
         def i64(t, name, shape):
             if t.device != dev or t.dtype != torch.int64 or tuple(t.shape) != shape:
                 raise RuntimeError(f"{name} must be an int64 tensor of shape {shape} on {dev}")
+            return t.contiguous()
+
+        def f32(t, name, shape):
+            if t is None or t.device != dev or t.dtype != torch.float32 or tuple(t.shape) != shape:
+                raise RuntimeError(f"{name} must be a float32 tensor of shape {shape} on {dev}")
             return t.contiguous()
 
         if tgt_tokens.dim() != 2 or tgt_tokens.shape[0] != B:
@@ -561,9 +572,14 @@ class _Kernel:
         tgt = i64(tgt_tokens, "tgt_tokens", (B, T))
         prev = i64(prev_output_tokens, "prev_output_tokens", (B, L))
         tl = _lengths(target_length, "target_length", B, dev)
-        if noise.device != dev or noise.dtype != torch.float32 or tuple(noise.shape) != (B, L):
-            raise RuntimeError(f"noise must be a float32 tensor of shape {(B, L)} on {dev}")
-        noise = noise.contiguous()
+        noise = f32(noise, "noise", (B, L)) if code != 2 else None
+        if code == 1:
+            uniform = f32(uniform, "uniform", (B,))
+        elif code == 2:
+            uniform = f32(uniform, "uniform", (B, L))
+        else:
+            uniform = None
+        ptr = lambda t: t.data_ptr() if t is not None else None
         with torch.cuda.device(dev):
             matchmask = torch.empty((B, T, L), dtype=torch.bool, device=dev)
             keep = torch.empty((B, L), dtype=torch.bool, device=dev)
@@ -572,13 +588,56 @@ class _Kernel:
             same_num = torch.empty((B,), dtype=torch.int64, device=dev)
             glance_num = torch.empty((B,), dtype=torch.int64, device=dev)
             rc = _cabi.lib().pcfgnat_glance_select(path.data_ptr(), pred.data_ptr(), tgt.data_ptr(), prev.data_ptr(),
-                                                   tl.data_ptr(), noise.data_ptr(), float(context_p), B, L, T,
-                                                   matchmask.data_ptr(), oracle.data_ptr(), same_num.data_ptr(),
-                                                   glance_num.data_ptr(), keep.data_ptr(), glat_prev.data_ptr(),
-                                                   _stream(dev))
+                                                   tl.data_ptr(), ptr(noise), ptr(uniform), code, float(context_p),
+                                                   B, L, T, matchmask.data_ptr(), oracle.data_ptr(),
+                                                   same_num.data_ptr(), glance_num.data_ptr(), keep.data_ptr(),
+                                                   glat_prev.data_ptr(), _stream(dev))
         _cabi.check(rc, "pcfgnat_glance_select")
         return {"matchmask": matchmask, "oracle": oracle, "same_num": same_num, "glance_num": glance_num,
                 "keep_word_mask": keep, "glat_prev_output_tokens": glat_prev}
+
+    @staticmethod
+    def _force_emit_args(x, keep, name):
+        x = _f32_cuda(x, name, 3)
+        B, L, T = x.shape
+        if keep.device != x.device or keep.dtype not in (torch.bool, torch.uint8) or tuple(keep.shape) != (B, L):
+            raise RuntimeError(f"keep_word_mask must be a bool tensor of shape {(B, L)} on {x.device}")
+        return x, keep.contiguous(), B, L, T
+
+    @staticmethod
+    def force_emit(match_all, matchmask, keep_word_mask, out=None):
+        """The force-emit mask of the training pass (nat_pcfg_loss.py:116-121): entries [b, l, t] of a node whose
+        token was revealed (``keep_word_mask`` [B, L]) become -inf unless ``matchmask`` [B, T, L] aligns it to t.
+        ``out`` may be ``match_all`` itself."""
+        _require_cuda()
+        ma, keep, B, L, T = _Kernel._force_emit_args(match_all, keep_word_mask, "match_all")
+        if matchmask.device != ma.device or matchmask.dtype not in (torch.bool, torch.uint8) or \
+                tuple(matchmask.shape) != (B, T, L):
+            raise RuntimeError(f"matchmask must be a bool tensor of shape {(B, T, L)} on {ma.device}")
+        mm = matchmask.contiguous()
+        with torch.cuda.device(ma.device):
+            if out is None:
+                out = torch.empty_like(ma)
+            rc = _cabi.lib().pcfgnat_force_emit(ma.data_ptr(), mm.data_ptr(), keep.data_ptr(), B, L, T, out.data_ptr(),
+                                                _stream(ma.device))
+        _cabi.check(rc, "pcfgnat_force_emit")
+        return out
+
+    @staticmethod
+    def force_emit_grad(grad, keep_word_mask, out=None):
+        """Gradient side of ``force_emit``: rows of revealed nodes are zero (the reference detaches them)."""
+        _require_cuda()
+        g, keep, B, L, T = _Kernel._force_emit_args(grad, keep_word_mask, "grad")
+        with torch.cuda.device(g.device):
+            if out is None:
+                out = torch.empty_like(g)
+            rc = _cabi.lib().pcfgnat_force_emit_grad(g.data_ptr(), keep.data_ptr(), B, L, T, out.data_ptr(),
+                                                     _stream(g.device))
+        _cabi.check(rc, "pcfgnat_force_emit_grad")
+        return out
+
+
+GLANCE_STRATEGIES = {"number-random": 0, "cmlm": 1, None: 2}  # PCFGNAT_GLANCE_*
 
 
 def get_pcfg_kernel():
@@ -718,6 +777,27 @@ class ProjLogsoftmaxGatherFunc(Function):
         if ctx.needs_input_grad[1]:
             d_weight = (dl.t() @ hidden.reshape(B * L, H).to(torch.bfloat16)).to(weight.dtype)
         return d_hidden, d_weight, None, None, None
+
+
+class ForceEmitFunc(Function):
+    """match_all with the force-emit mask applied; no gradient reaches the rows of revealed nodes
+    (criterions/nat_pcfg_loss.py:116-121)."""
+
+    @staticmethod
+    def forward(ctx, match_all, matchmask, keep_word_mask):
+        ctx.save_for_backward(keep_word_mask)
+        return get_pcfg_kernel().force_emit(match_all, matchmask, keep_word_mask)
+
+    @staticmethod
+    def backward(ctx, grad):
+        (keep,) = ctx.saved_tensors
+        return get_pcfg_kernel().force_emit_grad(grad.contiguous(), keep), None, None
+
+
+def force_emit_mask(match_all_eos_masked, matchmask, keep_word_mask):
+    """What the criterion does to the emissions when the glancing sampler revealed tokens and ``--no-force-emit``
+    is not set: ``matchmask`` [B, T, L] and ``keep_word_mask`` [B, L] as ``glance_select`` returns them."""
+    return ForceEmitFunc.apply(match_all_eos_masked, matchmask, keep_word_mask)
 
 
 def proj_logsoftmax_gather_with_grad(hidden, weight, targets, output_length=None, target_length=None):

@@ -182,9 +182,17 @@ class LossStep(_GraphedStep):
     """
     kernels_per_step = 7  # proj_prepare, proj, proj_merge, loss_fwd, outside, grad, loss_stats (set per shape below)
 
-    def __init__(self, weight, B, L, T, device, use_graph=True, copy_chunks=2, proj_backward=False, exchange=None):
+    def __init__(self, weight, B, L, T, device, use_graph=True, copy_chunks=2, proj_backward=False, exchange=None,
+                 force_emit=False):
         super().__init__(weight, B, L, device, use_graph, copy_chunks)
         self.T = T
+        # force_emit: the training pass after a glancing pass (criterions/nat_pcfg_loss.py:116-121): two more
+        # inputs, matchmask [B,T,L] and keep_word_mask [B,L] (bool, as GlanceStep returns them); a revealed node
+        # may only emit its aligned target position and gets no gradient
+        self.force_emit = bool(force_emit)
+        if self.force_emit:
+            self.matchmask = torch.zeros((B, T, L), dtype=torch.bool, device=self.device)
+            self.keep_word_mask = torch.zeros((B, L), dtype=torch.bool, device=self.device)
         # a sharding.LossExchange: the statistics come back summed over the ranks of the job (same launch)
         self.exchange = exchange
         self.targets = torch.zeros((B, T), dtype=torch.int64, device=self.device)
@@ -198,13 +206,18 @@ class LossStep(_GraphedStep):
             from . import _cabi
             with torch.cuda.device(self.device):
                 dp = _cabi.lib().pcfgnat_loss_fwd_bwd_kernels(B, L, T, 1)
-            self.kernels_per_step = 4 + (dp if dp > 0 else 3)
+            self.kernels_per_step = 4 + (dp if dp > 0 else 3) + (2 if self.force_emit else 0)
+        self.proj_backward_note = None
         if self.proj_backward:
             self.kernels_per_step += 3  # proj_prepare, zero padding rows, proj (grad mode)
             self.weight_bf16 = self.weight.to(torch.bfloat16)
+            self.proj_backward_note = ("the step plus d hidden and d weight of the projection: logits recomputed into "
+                                       "bf16 d-logits by proj_kernel's gradient mode, then two library bf16 GEMMs over "
+                                       "the padded rows")
 
     def _inputs(self):
-        return [self.hidden, self.links, self.output_length, self.targets, self.target_length]
+        base = [self.hidden, self.links, self.output_length, self.targets, self.target_length]
+        return base + ([self.matchmask, self.keep_word_mask] if self.force_emit else [])
 
     def _stage1(self, b0=0, b1=None):
         return self.kernel.proj_logsoftmax_gather(self.hidden[b0:b1], self.weight, self.targets[b0:b1],
@@ -212,7 +225,11 @@ class LossStep(_GraphedStep):
                                                   want_lse=self.proj_backward)
 
     def _stage2(self, em):
+        if self.force_emit:
+            self.kernel.force_emit(em["match"], self.matchmask, self.keep_word_mask, out=em["match"])
         loss, mg, lg = self.kernel.pcfg_loss_fwd_bwd(em["match"], self.links, self.output_length, self.target_length)
+        if self.force_emit:
+            self.kernel.force_emit_grad(mg, self.keep_word_mask, out=mg)
         stats = (self.exchange.stats(loss, self.target_length) if self.exchange is not None
                  else sharding.local_loss_stats(loss, self.target_length))
         if not self.proj_backward:
@@ -233,11 +250,18 @@ class GlanceStep(LossStep):
     sampler's normal draws are made inside the step into ``self.noise``."""
     kernels_per_step = 6  # proj_prepare, proj, proj_merge, loss_fwd, best_tree, glance_select
 
-    def __init__(self, weight, B, L, T, device, use_graph=True, context_p=0.5, copy_chunks=2):
+    def __init__(self, weight, B, L, T, device, use_graph=True, context_p=0.5, copy_chunks=2,
+                 strategy="number-random"):
         super().__init__(weight, B, L, T, device, use_graph, copy_chunks)
         self.context_p = float(context_p)
+        self.strategy = strategy  # the criterion's --glance-strategy: "number-random", "cmlm" or None
         self.prev_output_tokens = torch.ones((B, L), dtype=torch.int64, device=self.device)
         self.noise = torch.zeros((B, L), dtype=torch.float32, device=self.device)
+        self.uniform = None
+        if strategy == "cmlm":
+            self.uniform = torch.zeros((B,), dtype=torch.float32, device=self.device)
+        elif strategy is None:
+            self.uniform = torch.zeros((B, L), dtype=torch.float32, device=self.device)
 
     def _inputs(self):
         return super()._inputs() + [self.prev_output_tokens]
@@ -250,9 +274,12 @@ class GlanceStep(LossStep):
         k = self.kernel
         S, _ = k.pcfg_loss(em["match"], self.links, self.output_length, self.target_length, 1, want_c=False)
         tree = k.pcfg_best_tree(S, None, em["match"], self.links, self.output_length, self.target_length, 1)
-        self.noise.normal_()
+        if self.strategy is not None:
+            self.noise.normal_()
+        if self.uniform is not None:
+            self.uniform.uniform_()
         glance = k.glance_select(tree, em["argmax"], self.targets, self.prev_output_tokens, self.target_length,
-                                 self.noise, self.context_p)
+                                 self.noise, self.context_p, self.strategy, self.uniform)
         return tree, S[:, 0, 0], em["argmax"], glance
 
 

@@ -60,12 +60,26 @@ def reduce_loss(sentence_loss: torch.Tensor, target_length: torch.Tensor, group=
     return loss, stats[1], stats[2]
 
 
+def check_exchanged_stats(stats_host: torch.Tensor):
+    """Raises when the statistics a ``LossExchange`` returned are the NaN triple its kernel writes after a peer
+    did not arrive within the bounded wait (about half a second).  Call it where the step's result is read on
+    the host anyway; an NCCL all-reduce in the same place would simply have waited for the late rank."""
+    if bool(torch.isnan(torch.as_tensor(stats_host)).any()):
+        raise RuntimeError("loss statistics exchange: a peer rank did not arrive within the bounded device-side wait "
+                           "(PCFGNAT_STATUS_TIMEOUT); line the ranks up before the step or use sharding.reduce_loss")
+
+
 class LossExchange:
     """Sums the loss statistics over the ranks of a process group inside the statistics kernel itself: every
     rank's kernel stores its three numbers into every peer's buffer over NVLink and adds up what it received
     (``pcfgnat_loss_stats_exchange``), instead of a separate 12-byte NCCL all-reduce whose launch latency is
     several percent of a training step.  The buffers are torch symmetric memory; every rank must call
-    ``stats`` the same number of times.  One GPU: the plain local kernel."""
+    ``stats`` the same number of times.  One GPU: the plain local kernel.
+
+    The device-side wait for a peer is bounded (about half a second).  A rank that gives up returns NaN in all
+    three numbers, never a short sum; ``check_exchanged_stats`` turns that into an exception where the host reads
+    the result.  Ranks that may drift apart by more than the bound (a checkpoint written by one rank, validation on
+    rank 0) should use ``reduce_loss`` (an all-reduce waits) or synchronise before the step."""
 
     def __init__(self, device, group=None):
         from .custom_ops import pcfg_loss as ops

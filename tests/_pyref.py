@@ -75,9 +75,11 @@ def loss_bruteforce(match, links, m, n):
     return mx + math.log(sum(math.exp(x - mx) for x in total))
 
 
-def glance_select(path, pred_tokens, tgt_tokens, prev_output_tokens, target_length, noise, context_p):
-    """Torch restatement of the glancing sampler, strategy "number-random"
-    (fs_plugins/criterions/nat_pcfg_loss.py:216-267), with the normal draws given."""
+def glance_select(path, pred_tokens, tgt_tokens, prev_output_tokens, target_length, noise, context_p,
+                  strategy="number-random", uniform=None):
+    """Torch restatement of the glancing sampler (fs_plugins/criterions/nat_pcfg_loss.py:216-267) with the random
+    draws given: ``noise`` = the reference's torch.randn, ``uniform`` = its torch.rand ([B] for "cmlm", [B, L] for
+    strategy None).  Pinned against the reference's own function by tests/golden/host_criterion.npz."""
     import torch
 
     B, L = path.shape
@@ -88,14 +90,46 @@ def glance_select(path, pred_tokens, tgt_tokens, prev_output_tokens, target_leng
     matchmask = torch.zeros(B, T + 1, L, dtype=torch.bool).scatter_(1, path.unsqueeze(1) + 1, True)[:, 1:]
     oracle = tgt_tokens.gather(-1, path.clip(min=0))
     same_num = ((pred_tokens == oracle) & aligned).sum(1)
-    prob = noise.clone().masked_fill_(~aligned, -100)
-    glance_nums = ((target_length - same_num) * context_p + 0.5).to(torch.long)
-    thresh = prob.sort(descending=True)[0].gather(-1, (glance_nums - 1).clip(min=0).unsqueeze(-1)).squeeze(-1)
-    thresh = thresh.masked_fill(glance_nums == 0, 100)
-    keep = prob >= thresh.unsqueeze(-1)
+    if strategy is None:
+        keep_prob = ((target_length - same_num) / target_length * context_p).unsqueeze(-1) * aligned.float()
+        keep = uniform < keep_prob
+        glance_nums = keep.sum(1)
+    else:
+        prob = noise.clone().masked_fill_(~aligned, -100)
+        if strategy == "cmlm":
+            glance_nums = (target_length * uniform + 0.5).to(torch.long)
+        else:
+            glance_nums = ((target_length - same_num) * context_p + 0.5).to(torch.long)
+        thresh = prob.sort(descending=True)[0].gather(-1, (glance_nums - 1).clip(min=0).unsqueeze(-1)).squeeze(-1)
+        thresh = thresh.masked_fill(glance_nums == 0, 100)
+        keep = prob >= thresh.unsqueeze(-1)
     glat_prev = prev_output_tokens.masked_fill(keep, 0) + oracle.masked_fill(~keep, 0)
     return {"matchmask": matchmask, "oracle": oracle, "same_num": same_num, "glance_num": glance_nums,
             "keep_word_mask": keep, "glat_prev_output_tokens": glat_prev}
+
+
+def criterion_draws(strategy, seed, B, L):
+    """The draws torch's seeded global generator gives the reference's glat_function, in its order
+    (nat_pcfg_loss.py:233, :241-243, :248): (noise [B, L] or None, uniform or None)."""
+    import torch
+
+    torch.manual_seed(seed)
+    if strategy is None:
+        return None, torch.rand(B, L)
+    noise = torch.randn(B, L, dtype=torch.float)
+    uniform = torch.rand(B, dtype=torch.float) if strategy == "cmlm" else None
+    return noise, uniform
+
+
+def force_emit(match_eos_masked, matchmask, keep_word_mask):
+    """(masked emissions, gradient mask) of the force-emit step (nat_pcfg_loss.py:116-121): a revealed node keeps
+    only the entry of its aligned target position and passes no gradient."""
+    import torch
+
+    keep = keep_word_mask.unsqueeze(-1)
+    mm = matchmask.transpose(1, 2)
+    out = torch.where(keep & ~mm, torch.full_like(match_eos_masked, NEG), match_eos_masked)
+    return out, (~keep).expand_as(match_eos_masked)
 
 
 def extract_links(q, kl, kr, gate_logits, prev_output_tokens, pad, left_mask, right_mask, main_chain):

@@ -9,7 +9,7 @@ reference launch has a single row segment per sentence, so none of its inter-blo
 spin-waits (pcfg_loss.cu:131-136, pcfg_viterbi.cu:69) depends on another block being
 resident, and its ticket overshoot (pcfg_loss.cu:121-127) only reaches empty segments.
 
-Usage (on a GPU box):  python tests/golden/make_golden_ref.py --out gpurun_out/golden
+Usage (on a GPU box):  python tests/golden/make_golden_ref.py --out <directory>
 """
 import argparse
 import os
@@ -44,7 +44,7 @@ VITERBI_CASES = {
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--out", default=os.path.join(ROOT, "gpurun_out", "golden"))
+    ap.add_argument("--out", required=True, help="directory the .npz fixtures are written to")
     a = ap.parse_args()
     os.makedirs(a.out, exist_ok=True)
     ref = load_ref()

@@ -855,7 +855,8 @@ def test_decode_step_from_link_features(pkg, ops, syn):
 
 def test_loss_stats_exchange_bounded_wait(ops):
     """The in-kernel exchange of the loss statistics with a peer that never arrives: the wait runs out, the
-    status word says so, the statistics hold this rank's part only, and the context stays usable."""
+    status word says so, the statistics are NaN (never a short sum that could pass for a loss), the host-side
+    check raises, and the context stays usable."""
     k = ops.get_pcfg_kernel()
     bufs = [torch.zeros(64, dtype=torch.float32, device=DEV) for _ in range(2)]  # >= PCFGNAT_EXCHANGE_BYTES(2)
     peers = torch.tensor([b.data_ptr() for b in bufs], dtype=torch.int64, device=DEV)
@@ -863,8 +864,14 @@ def test_loss_stats_exchange_bounded_wait(ops):
     tl = torch.tensor([2, 3, 5], device=DEV)
     ops.read_status(DEV)
     stats = k.loss_stats_exchange(loss, tl, peers, 0, 2).cpu()
-    assert stats.tolist() == [-5.0, 3.0, 1.0]
+    assert torch.isnan(stats).all()
     assert ops.read_status(DEV) & 8  # PCFGNAT_STATUS_TIMEOUT
+    import importlib
+
+    sharding = importlib.import_module("pcfg_nat_b200.sharding")
+    with pytest.raises(RuntimeError, match="did not arrive"):
+        sharding.check_exchanged_stats(stats)
+    assert sharding.check_exchanged_stats(torch.tensor([-5.0, 3.0, 1.0])) is None
     # a world of one rank needs nobody else
     one = torch.zeros(64, dtype=torch.float32, device=DEV)
     stats = k.loss_stats_exchange(loss, tl, torch.tensor([one.data_ptr()], dtype=torch.int64, device=DEV), 0, 1).cpu()
@@ -926,3 +933,86 @@ def test_decode_and_glance_steps_match_operator_chain(pkg, ops, syn):
                                       g.target_length.numpy())
     # same emissions; the tables differ from the oracle's only in the last ulp of expf/logf
     assert (tree.cpu().numpy() == want_tree).mean() > 0.99
+
+
+# ---- criterion glue against the reference criterion's own code (tests/golden/host_criterion.npz) -----------------
+
+@pytest.mark.parametrize("tag,strategy", [("none", None), ("number_random", "number-random"), ("cmlm", "cmlm")])
+def test_glance_select_against_reference_criterion(ops, tag, strategy):
+    g = _g("host_criterion.npz")
+    t = lambda key: torch.from_numpy(g[key]).to(DEV)
+    B, L = g["path"].shape
+    noise, uniform = pyref.criterion_draws(strategy, int(g[f"{tag}_seed"]), B, L)
+    k = ops.get_pcfg_kernel()
+    pred = t("logits").argmax(-1)
+    got = k.glance_select(t("path"), pred, t("tgt"), t("prev"), t("tgt_len"),
+                          None if noise is None else noise.to(DEV), 0.5, strategy,
+                          None if uniform is None else uniform.to(DEV))
+    assert torch.equal(got["matchmask"], t(f"{tag}_matchmask"))
+    assert torch.equal(got["keep_word_mask"], t(f"{tag}_keep"))
+    assert torch.equal(got["glat_prev_output_tokens"], t(f"{tag}_glat_prev"))
+    accu = float(got["same_num"].sum() / t("tgt_len").sum())
+    assert abs(accu - float(g[f"{tag}_glat_accu"])) < 1e-6
+    want = pyref.glance_select(t("path").cpu(), pred.cpu(), t("tgt").cpu(), t("prev").cpu(), t("tgt_len").cpu(), noise,
+                               0.5, strategy, uniform)
+    for key, val in want.items():
+        assert torch.equal(got[key].cpu(), val), key
+
+
+def test_force_emit_against_reference_criterion(pkg, ops, syn):
+    g = _g("host_criterion.npz")
+    t = lambda key: torch.from_numpy(g[key]).to(DEV)
+    eos = syn.eos_mask_(t("match_plain").clone(), t("out_len"), t("tgt_len"))
+    assert torch.equal(eos, t("plain_loss_match"))
+    ma = eos.clone().requires_grad_(True)
+    out = ops.force_emit_mask(ma, t("number_random_matchmask"), t("number_random_keep"))
+    assert torch.equal(out.detach(), t("force_loss_match"))
+    # the same recording loss as the fixture's: linear with weights loss_w on the finite entries
+    n = t("tgt_len").float()
+    fin = torch.isfinite(out)
+    sent = (torch.where(fin, out, torch.zeros_like(out)) * t("loss_w")).sum((1, 2))
+    valid = torch.tensor([True, True, False, True, True], device=DEV)
+    (-(torch.where(valid, sent, torch.zeros_like(sent)) / n).mean()).backward()
+    torch.testing.assert_close(ma.grad, t("force_match_grad"), rtol=1e-6, atol=0)
+    # in place, as the step object uses it
+    k = ops.get_pcfg_kernel()
+    buf = eos.clone()
+    k.force_emit(buf, t("number_random_matchmask"), t("number_random_keep"), out=buf)
+    assert torch.equal(buf, t("force_loss_match"))
+
+
+def test_loss_step_with_force_emit_matches_operator_chain(pkg, ops, syn):
+    """GlanceStep -> LossStep(force_emit=True), as a GLAT training step chains them, against the operators one by
+    one with autograd and against the oracle fed the masked emissions."""
+    import importlib
+
+    runtime = importlib.import_module("pcfg_nat_b200.runtime")
+    w = syn.Workload("fe", batch=5, vocab=2000, hidden=64, src_min=6, src_max=20, kind="glance")
+    b = syn.make_batch(w, seed=6)
+    weight = b.weight.to(DEV)
+    prev = torch.where(torch.arange(b.L)[None, :] < b.output_length[:, None], 3, 1)
+    gs = runtime.GlanceStep(weight, b.B, b.L, b.T, DEV, context_p=0.5)
+    gs.load(b.hidden, b.links, b.output_length, b.targets, b.target_length, prev)
+    tree, ll, am, glance = gs.run()
+    assert glance["keep_word_mask"].any()
+    ls = runtime.LossStep(weight, b.B, b.L, b.T, DEV, force_emit=True)
+    ls.load(b.hidden, b.links, b.output_length, b.targets, b.target_length, glance["matchmask"], glance["keep_word_mask"])
+    for _ in range(2):  # capture, replay
+        stats, mg, lg, loss = [x.clone() for x in ls.run()]
+    em = ops.proj_logsoftmax_gather(b.hidden.to(DEV), weight, b.targets.to(DEV), b.output_length.to(DEV),
+                                    b.target_length.to(DEV))["match"].requires_grad_(True)
+    lk = b.links.to(DEV).requires_grad_(True)
+    masked = ops.force_emit_mask(em, glance["matchmask"], glance["keep_word_mask"])
+    loss2 = ops.cuda_pcfg_loss(masked, lk, b.output_length.to(DEV), b.target_length.to(DEV))
+    loss2.sum().backward()
+    assert torch.isfinite(loss2).all()
+    assert torch.equal(loss, loss2.detach()) and torch.equal(mg, em.grad) and torch.equal(lg, lk.grad)
+    assert (mg[glance["keep_word_mask"]] == 0).all()
+    m_np = masked.detach().cpu().numpy()
+    So, Co = oracle.pcfg_loss(m_np, b.links.numpy(), b.output_length.numpy(), b.target_length.numpy())
+    np.testing.assert_allclose(loss.cpu().numpy(), So[:, 0, 0], rtol=1e-4)
+    mgo, lgo = oracle.pcfg_loss_backward(np.ones(b.B, np.float32), So, Co, m_np, b.links.numpy(),
+                                         b.output_length.numpy(), b.target_length.numpy())
+    mgo[glance["keep_word_mask"].cpu().numpy()] = 0
+    np.testing.assert_allclose(mg.cpu().numpy(), mgo, rtol=1e-3, atol=2e-6)
+    np.testing.assert_allclose(lg.cpu().numpy(), lgo, rtol=1e-3, atol=2e-6)

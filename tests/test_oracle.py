@@ -221,3 +221,65 @@ def test_links_restatement_against_reference_model(case):
     assert np.array_equal(np.isfinite(got), np.isfinite(want))
     fin = np.isfinite(want)
     np.testing.assert_allclose(got[fin], want[fin], rtol=1e-5, atol=1e-6)
+
+
+# ---- criterion glue: the restatements in _pyref.py against the reference criterion's own code --------------------
+
+@pytest.mark.parametrize("tag,strategy", [("none", None), ("number_random", "number-random"), ("cmlm", "cmlm")])
+def test_glance_select_restatement_against_reference_criterion(tag, strategy):
+    """tests/golden/make_golden_criterion.py ran the reference's glat_function (nat_pcfg_loss.py:193-269) with a
+    seeded alignment; the restatement must give the same masks and tokens from the same draws."""
+    import _pyref as pyref
+
+    g = np.load(golden_path("host_criterion.npz"))
+    t = lambda k: torch.from_numpy(g[k])
+    B, L = g["path"].shape
+    noise, uniform = pyref.criterion_draws(strategy, int(g[f"{tag}_seed"]), B, L)
+    pred = t("logits").argmax(-1)
+    got = pyref.glance_select(t("path"), pred, t("tgt"), t("prev"), t("tgt_len"), noise, 0.5, strategy, uniform)
+    assert torch.equal(got["matchmask"], t(f"{tag}_matchmask"))
+    assert torch.equal(got["keep_word_mask"], t(f"{tag}_keep"))
+    assert torch.equal(got["glat_prev_output_tokens"], t(f"{tag}_glat_prev"))
+    accu = float(got["same_num"].sum() / t("tgt_len").sum())
+    assert abs(accu - float(g[f"{tag}_glat_accu"])) < 1e-6
+    assert got["keep_word_mask"].any()
+    # the emissions the best-tree operator was handed: EOS column masked except at the last graph node
+    lp = torch.log_softmax(t("logits"), -1).gather(-1, t("tgt").unsqueeze(1).expand(-1, L, -1))
+    import __graft_entry__ as entry
+
+    syn = entry.load_package().synthetic
+    assert torch.equal(syn.eos_mask_(lp.clone(), t("out_len"), t("tgt_len")), t("glance_match"))
+
+
+def test_force_emit_and_loss_scalar_against_reference_criterion():
+    """The reference's _compute_pfcg_loss (nat_pcfg_loss.py:98-145) with a recording loss operator: emissions it
+    hands to the loss (EOS + force-emit masks), which entries carry a gradient, the scalar and the invalid count."""
+    import _pyref as pyref
+    import __graft_entry__ as entry
+
+    pkg = entry.load_package()
+    syn = pkg.synthetic
+    g = np.load(golden_path("host_criterion.npz"))
+    t = lambda k: torch.from_numpy(g[k])
+    eos = syn.eos_mask_(t("match_plain").clone(), t("out_len"), t("tgt_len"))
+    assert torch.equal(eos, t("plain_loss_match"))
+    out, live = pyref.force_emit(eos, t("number_random_matchmask"), t("number_random_keep"))
+    assert torch.equal(out, t("force_loss_match"))
+    # gradient of -mean_b(loss_b / n_b) over valid sentences w.r.t. the gathered emissions; loss_b is linear with
+    # weights loss_w on finite entries
+    n = t("tgt_len").float()
+    valid = torch.tensor([True, True, False, True, True])
+    for tag, masked, alive in (("plain", eos, torch.ones_like(live)), ("force", out, live)):
+        want = -(t("loss_w") / n[:, None, None]) / len(n)
+        want = want * torch.isfinite(masked) * alive * valid[:, None, None]
+        torch.testing.assert_close(t(f"{tag}_match_grad"), want, rtol=1e-6, atol=0)
+        # the scalar: invalid sentences zeroed and counted, the others divided by their length, batch mean
+        fin = torch.isfinite(masked)
+        sent = (torch.where(fin, masked, torch.zeros_like(masked)) * t("loss_w")).sum((1, 2))
+        sent[2] = float("-inf")
+        import importlib
+
+        sharding = importlib.import_module("pcfg_nat_b200.sharding")
+        stats = sharding.local_loss_stats(sent, t("tgt_len"))
+        assert abs(float(-stats[0] / stats[1]) - float(g[f"{tag}_loss"])) < 1e-5 * abs(float(g[f"{tag}_loss"]))
+        assert int(stats[2]) == int(g[f"{tag}_invalid"]) == 1
