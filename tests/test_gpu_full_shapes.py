@@ -94,7 +94,7 @@ def test_loss_step_full_shape_against_oracle(pkg, ops, syn, wname):
     # replay after the overlapped load against the capture run: the overlapped load projects the sentences in two
     # groups, whose tile schedule merges the softmax partials of a row in another order (last-ulp differences)
     for a, b in zip(first, (stats, mg, lg, loss)):
-        torch.testing.assert_close(b, a, rtol=1e-4, atol=1e-6)
+        torch.testing.assert_close(b, a, rtol=1e-3, atol=2e-5)
     torch.testing.assert_close(loss, first[3], rtol=1e-6, atol=0)
     assert ops.read_status(DEV) == 0
     ol, tl = batch.output_length.numpy(), batch.target_length.numpy()
