@@ -74,13 +74,18 @@ int pcfgnat_loss_bwd(const float *grad_output, const float *S, const float *matc
                      float *S_grad, float *match_all_grad, float *links_grad, int *status, void *stream);
 
 /* Forward and backward in one call, as CUDAPCFGLossFunc.forward always runs them
- * (fs_plugins/custom_ops/pcfg_loss.py:63-74).  workspace holds S and S_grad
- * (pcfgnat_loss_workspace_bytes); loss [B] f32 receives S[b][0][0]; gradients are for
- * grad_output == 1. */
+ * (fs_plugins/custom_ops/pcfg_loss.py:63-74).  workspace holds the two DP tables and a small
+ * per-sentence record (pcfgnat_loss_workspace_bytes); loss [B] f32 receives S[b][0][0]; gradients
+ * are for grad_output == 1.  The tables stay inside the call, so they are built in linear space
+ * (probabilities scaled per column: one multiply-add per term instead of one exponential; loss equal
+ * to the reference's to ~1e-6 relative, gradients to 1e-3); a sentence whose numbers leave the range
+ * of that representation, or whose lengths are unusual, is recomputed in log space within the same
+ * call.  PCFGNAT_EXACT_ORDER=1 in the environment keeps everything in the reference's order. */
 size_t pcfgnat_loss_workspace_bytes(int B, int L, int T, int max_left);
 /* Number of kernels pcfgnat_loss_fwd_bwd / _static launch for this shape on the current device and with the
- * current environment switches: 2 when the outside pass also sums up both gradients (batches that run one CTA per
- * sentence), else 3 (inside, outside, gradients).  For launch accounting; 0 for unsupported arguments. */
+ * current environment switches: 5 on the linear-space path (inside, outside + gradients, and the three log-space
+ * kernels that recompute marked sentences and otherwise return at once); on the log-space path 2 when the outside
+ * pass also sums up both gradients, else 3.  For launch accounting; 0 for unsupported arguments. */
 int pcfgnat_loss_fwd_bwd_kernels(int B, int L, int T, int max_left);
 int pcfgnat_loss_fwd_bwd(const float *match_all, const float *links, const int64_t *output_length,
                          const int64_t *target_length, int B, int L, int T, int max_left, void *workspace,
@@ -91,8 +96,8 @@ int pcfgnat_loss_fwd_bwd(const float *match_all, const float *links, const int64
  * holds device pointers owned by another framework, or a process whose device memory all belongs
  * to its own arena so that no library may call cudaMalloc).  It has no counterpart in the
  * reference.  The two DP tables live in a fixed PCFGNAT_STATIC_SCRATCH_BYTES array inside the
- * library's device image (held on every GPU that loads the library, until exit); shapes with
- * 2 * roundup256(B * Mc * (T+2) * 4) above that are refused with PCFGNAT_ERR_TOO_LARGE.  The call
+ * library's device image (held on every GPU that loads the library, until exit); shapes whose
+ * pcfgnat_loss_workspace_bytes() exceeds it are refused with PCFGNAT_ERR_TOO_LARGE.  The call
  * allocates nothing.  All calls on a device share the array: calls that may overlap on the GPU
  * race and must be serialised by the caller.  The first call on each device looks up the array's
  * address and should come before any stream capture on that device. */

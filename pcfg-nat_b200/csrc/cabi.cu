@@ -70,6 +70,32 @@ DpKernel dp_kernel_choice() {
 
 }  // namespace pcfgnat
 
+namespace pcfgnat {
+
+// Forward + backward with the tables in [tables, tables + 2 * table_bytes) and the frames behind them.
+int loss_fwd_bwd_in(const float *match_all, const float *links, const int64_t *ol, const int64_t *tl, int B, int L, int T,
+                    void *tables, size_t table_bytes, float *loss, float *mg, float *lg, int *status, cudaStream_t st) {
+    float *S = static_cast<float *>(tables);
+    float *G = reinterpret_cast<float *>(static_cast<char *>(tables) + table_bytes);
+    float *frames = reinterpret_cast<float *>(static_cast<char *>(tables) + 2 * table_bytes);
+    if (!exact_order_forced() && dp_kernel_choice() == kDpAuto && linear_dp_applies(B, L, T)) {
+        // linear space first; the log-space kernels then recompute the sentences it left marked (normally none)
+        int rc = launch_loss_linear(match_all, links, ol, tl, B, L, T, S, G, frames, loss, mg, lg, status, st);
+        if (rc == PCFGNAT_OK) {
+            rc = launch_loss_fwd_rows(match_all, links, ol, tl, B, L, T, S, nullptr, loss, status, st, frames);
+            if (rc) return rc;
+            return launch_loss_bwd_rows(nullptr, S, match_all, links, ol, tl, B, L, T, G, mg, lg, status, st, frames);
+        }
+        if (rc != PCFGNAT_ERR_UNSUPPORTED) return rc;
+    }
+    bool shares_in_mg = false;
+    int rc = launch_loss_fwd_internal(match_all, links, ol, tl, B, L, T, S, loss, status, st, mg, &shares_in_mg);
+    if (rc) return rc;
+    return launch_loss_bwd(nullptr, S, match_all, links, ol, tl, B, L, T, G, mg, lg, status, st, shares_in_mg);
+}
+
+}  // namespace pcfgnat
+
 namespace {
 
 inline bool bad_dims(int B, int L, int T) { return B < 0 || L < 2 || T < 1; }
@@ -119,11 +145,14 @@ int pcfgnat_loss_bwd(const float *grad_output, const float *S, const float *matc
 size_t pcfgnat_loss_workspace_bytes(int B, int L, int T, int max_left) {
     if (max_left != 1 || bad_dims(B, L, T)) return 0;
     const size_t table = align256((size_t)B * main_slots(L, 1) * (T + 2) * sizeof(float));
-    return 2 * table;  // S and S_grad
+    return 2 * table + linear_frames_bytes(B, T);  // two DP tables and the per-sentence frames of the linear-space pass
 }
+
 
 int pcfgnat_loss_fwd_bwd_kernels(int B, int L, int T, int max_left) {
     if (max_left != 1 || bad_dims(B, L, T)) return 0;
+    // linear-space inside and outside kernels, then the three log-space kernels that pick up marked sentences
+    if (!exact_order_forced() && dp_kernel_choice() == kDpAuto && linear_dp_applies(B, L, T)) return 5;
     // the shares the fused backward needs come from the free-order inside pass only
     const bool free_order = !exact_order_forced() && dp_kernel_choice() == kDpAuto && main_slots(L, 1) <= 256;
     return free_order && fused_grad_applies(B, L, T) ? 2 : 3;
@@ -141,15 +170,9 @@ int pcfgnat_loss_fwd_bwd(const float *match_all, const float *links, const int64
     const size_t need = pcfgnat_loss_workspace_bytes(B, L, T, max_left);
     if (workspace_bytes < need) return PCFGNAT_ERR_WORKSPACE;
     if (reinterpret_cast<uintptr_t>(workspace) % 16) return PCFGNAT_ERR_INVALID_ARGUMENT;
-    float *S = static_cast<float *>(workspace);
-    float *G = reinterpret_cast<float *>(static_cast<char *>(workspace) + need / 2);
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
-    bool shares_in_mg = false;
-    int rc = launch_loss_fwd_internal(match_all, links, output_length, target_length, B, L, T, S, loss, status, st,
-                                      match_all_grad, &shares_in_mg);
-    if (rc) return rc;
-    return launch_loss_bwd(nullptr, S, match_all, links, output_length, target_length, B, L, T, G, match_all_grad,
-                           links_grad, status, st, shares_in_mg);
+    const size_t table = align256((size_t)B * main_slots(L, 1) * (T + 2) * sizeof(float));
+    return loss_fwd_bwd_in(match_all, links, output_length, target_length, B, L, T, workspace, table, loss, match_all_grad,
+                           links_grad, status, static_cast<cudaStream_t>(stream));
 }
 
 int pcfgnat_best_tree(const float *S, const float *match_all, const float *links, const int64_t *output_length,

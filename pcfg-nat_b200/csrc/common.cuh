@@ -26,6 +26,16 @@ __device__ __forceinline__ void flag(int *status, int bit) {
     if (status) atomicOr(status, bit);
 }
 
+// Per-sentence record the linear-space loss kernels (loss_linear.cu) leave in the workspace: kLinearFrameHead
+// floats ([0] u_0[root], [1] log Z, [2] total of the sentence's emission gradients, [3] != 0: marked by the inside
+// pass) followed by T + 2 column scales.  A sentence is recomputed by the log-space kernels when it was marked,
+// when Z is zero or not finite, or when the emission gradients do not total the n target tokens to 1e-4.
+constexpr int kLinearFrameHead = 4;
+__device__ __forceinline__ bool linear_needs_redo(const float *fr, int n) {
+    return fr[3] != 0.f || !(fr[0] > 0.f) || !(fabsf(fr[1]) < CUDART_INF_F) ||
+           !(fabsf(fr[2] - (float)n) <= 1e-4f * (float)n);
+}
+
 // exp() through the hardware ex2 approximation (relative error ~1e-6 for the arguments met here): for the
 // gradient kernels, whose results are held to 1e-3, never for the tables that must match bit for bit.
 __device__ __forceinline__ float fast_exp(float x) {
@@ -97,6 +107,22 @@ int launch_logsoftmax_gather(void *logits, int dtype, const int64_t *sel, int64_
                              int64_t rows, int64_t rpb, int V, int slen, int req_grad, float *selected, int *status,
                              cudaStream_t st);
 
+// row-per-thread family on its own; redo != nullptr: only the sentences the linear-space kernels left marked
+int launch_loss_fwd_rows(const float *match_all, const float *links, const int64_t *ol, const int64_t *tl, int B, int L,
+                         int T, float *S, float *C, float *loss, int *status, cudaStream_t st, const float *redo);
+int launch_loss_bwd_rows(const float *grad_output, const float *S, const float *match_all, const float *links,
+                         const int64_t *ol, const int64_t *tl, int B, int L, int T, float *S_grad, float *mg, float *lg,
+                         int *status, cudaStream_t st, const float *redo);
+int launch_grad_rows(const float *S, const float *S_grad, const float *match_all, const float *links, const int64_t *ol,
+                     const int64_t *tl, int B, int L, int T, float *mg, float *lg, cudaStream_t st, const float *redo);
+// linear-space inside + outside + gradients (loss_linear.cu)
+bool linear_dp_applies(int B, int L, int T);
+size_t linear_frames_bytes(int B, int T);
+int launch_loss_linear(const float *match_all, const float *links, const int64_t *ol, const int64_t *tl, int B, int L,
+                       int T, float *Y, float *O, float *frames, float *loss, float *mg, float *lg, int *status,
+                       cudaStream_t st);
+int mixed_width_count(int B, int Mc);
+
 int launch_loss_fwd_balanced(const float *match_all, const float *links, const int64_t *ol, const int64_t *tl, int B,
                              int L, int T, float *S, float *C, float *loss, int *status, cudaStream_t st);
 int launch_outside_balanced(const float *grad_output, const float *S, const float *match_all, const float *links,
@@ -115,6 +141,8 @@ bool outside_balanced_fits_grad(int L);
 int launch_loss_fwd_internal(const float *match_all, const float *links, const int64_t *ol, const int64_t *tl, int B,
                              int L, int T, float *S, float *loss, int *status, cudaStream_t st, float *mg,
                              bool *shares_in_mg);
+int loss_fwd_bwd_in(const float *match_all, const float *links, const int64_t *ol, const int64_t *tl, int B, int L, int T,
+                    void *tables, size_t table_bytes, float *loss, float *mg, float *lg, int *status, cudaStream_t st);
 bool exact_order_forced();  // PCFGNAT_EXACT_ORDER=1: the fused forward + backward also keeps the reference's order
 int launch_outside_cluster(const float *grad_output, const float *S, const float *match_all, const float *links,
                            const int64_t *ol, const int64_t *tl, int B, int L, int T, float *G, float *mg, float *lg,

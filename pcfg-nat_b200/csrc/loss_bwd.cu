@@ -32,9 +32,11 @@ __global__ void __launch_bounds__(kMaxRows *kLanes)
     outside_kernel(const float *__restrict__ grad_output, const float *__restrict__ S,
                    const float *__restrict__ match_all, const float *__restrict__ links,
                    const int64_t *__restrict__ ol, const int64_t *__restrict__ tl, int L, int T, float *G, int *status,
-                   int Mc, int col_stride, int lk_stride) {
+                   int Mc, int col_stride, int lk_stride, const float *redo) {
     extern __shared__ float smem[];
     const int b = blockIdx.x;
+    // redo: only the sentences the linear-space kernels left marked (loss_linear.cu)
+    if (redo && !linear_needs_redo(redo + (size_t)b * (kLinearFrameHead + T + 2), (int)tl[b])) return;
     const int x = threadIdx.x, y = threadIdx.y;
     const int rows = blockDim.y;
     const int tid = y * kLanes + x, nthr = rows * kLanes;
@@ -153,9 +155,10 @@ template <int kMaxCPerLane>
 __global__ void __launch_bounds__(kGradWarps * 32)
     grad_kernel(const float *__restrict__ S, const float *__restrict__ G, const float *__restrict__ match_all,
                 const float *__restrict__ links, const int64_t *__restrict__ ol, const int64_t *__restrict__ tl, int L,
-                int T, float *mg, float *lg, int Mc) {
+                int T, float *mg, float *lg, int Mc, const float *redo) {
     extern __shared__ float smem[];  // per warp: 2 rows of T floats (emission gradients of a and a-1)
     const int b = blockIdx.y;
+    if (redo && !linear_needs_redo(redo + (size_t)b * (kLinearFrameHead + T + 2), (int)tl[b])) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int p = blockIdx.x * kGradWarps + warp;  // node pair (2p, 2p+1)
     const int npairs = (L + 1) / 2;
@@ -285,17 +288,6 @@ int launch_loss_bwd(const float *grad_output, const float *S, const float *match
                     const int64_t *ol, const int64_t *tl, int B, int L, int T, float *S_grad, float *mg, float *lg,
                     int *status, cudaStream_t st, bool shares_in_mg) {
     if (B == 0) return PCFGNAT_OK;
-    const int Mc = main_slots(L, 1);
-    int rows = (Mc + 7) / 8 * 8;
-    if (rows < 8) rows = 8;
-    if (rows > kMaxRows) rows = kMaxRows;
-    const int col_stride = (Mc + 3) / 4 * 4;
-    int lk_stride = Mc;
-    while (lk_stride % 8 != 4) lk_stride++;  // transposed tile: 8 rows x 4 lanes of a warp in distinct banks
-    const size_t smem_cols = (size_t)6 * col_stride * sizeof(float);
-    const size_t smem_links = (size_t)2 * Mc * lk_stride * sizeof(float);
-    dim3 block(kLanes, rows), grid(B);
-    cudaError_t e;
     int brc = PCFGNAT_ERR_UNSUPPORTED;
     const DpKernel choice = dp_kernel_choice();
     if (choice == kDpCluster || (choice == kDpAuto && cluster_kernels_pay(B, L, T))) {  // loss_cluster.cu
@@ -316,34 +308,63 @@ int launch_loss_bwd(const float *grad_output, const float *S, const float *match
     }
     if (brc != PCFGNAT_ERR_UNSUPPORTED) {
         if (brc != PCFGNAT_OK) return brc;
-    } else if (smem_cols + smem_links <= (size_t)kSmemLimit - 1024) {
-        auto k = outside_kernel<true>;
-        e = ensure_dynamic_smem(k, smem_cols + smem_links);
-        if (e != cudaSuccess) return PCFGNAT_ERR_CUDA;
-        k<<<grid, block, smem_cols + smem_links, st>>>(grad_output, S, match_all, links, ol, tl, L, T, S_grad, status,
-                                                       Mc, col_stride, lk_stride);
-    } else {
-        if (smem_cols > (size_t)kSmemLimit - 1024) return PCFGNAT_ERR_TOO_LARGE;
-        auto k = outside_kernel<false>;
-        e = ensure_dynamic_smem(k, smem_cols);
-        if (e != cudaSuccess) return PCFGNAT_ERR_CUDA;
-        k<<<grid, block, smem_cols, st>>>(grad_output, S, match_all, links, ol, tl, L, T, S_grad, status, Mc,
-                                          col_stride, lk_stride);
+        return launch_grad_rows(S, S_grad, match_all, links, ol, tl, B, L, T, mg, lg, st, nullptr);
     }
-    if (cudaGetLastError() != cudaSuccess) return PCFGNAT_ERR_CUDA;
+    return launch_loss_bwd_rows(grad_output, S, match_all, links, ol, tl, B, L, T, S_grad, mg, lg, status, st, nullptr);
+}
+
+// Gradient kernel over (S, G).  redo: see launch_loss_bwd_rows.
+int launch_grad_rows(const float *S, const float *S_grad, const float *match_all, const float *links, const int64_t *ol,
+                     const int64_t *tl, int B, int L, int T, float *mg, float *lg, cudaStream_t st, const float *redo) {
+    const int Mc = main_slots(L, 1);
     const int npairs = (L + 1) / 2;
     const size_t gsm = (size_t)kGradWarps * 2 * T * sizeof(float);
     if (gsm > (size_t)kSmemLimit - 1024) return PCFGNAT_ERR_TOO_LARGE;
     dim3 ggrid((npairs + kGradWarps - 1) / kGradWarps, B);
     auto launch = [&](auto kernel) {
         if (ensure_dynamic_smem(kernel, gsm) != cudaSuccess) return PCFGNAT_ERR_CUDA;
-        kernel<<<ggrid, kGradWarps * 32, gsm, st>>>(S, S_grad, match_all, links, ol, tl, L, T, mg, lg, Mc);
+        kernel<<<ggrid, kGradWarps * 32, gsm, st>>>(S, S_grad, match_all, links, ol, tl, L, T, mg, lg, Mc, redo);
         return cuda_rc(cudaGetLastError());
     };
     if (Mc <= 64) return launch(grad_kernel<2>);
     if (Mc <= 96) return launch(grad_kernel<3>);
     if (Mc <= 128) return launch(grad_kernel<4>);
     return launch(grad_kernel<8>);
+}
+
+// Outside pass of the row-per-thread family (no size limit) + the gradient kernel.  redo != nullptr: only the
+// sentences marked in the frames of the linear-space kernels are computed, the others are left untouched.
+int launch_loss_bwd_rows(const float *grad_output, const float *S, const float *match_all, const float *links,
+                         const int64_t *ol, const int64_t *tl, int B, int L, int T, float *S_grad, float *mg, float *lg,
+                         int *status, cudaStream_t st, const float *redo) {
+    if (B == 0) return PCFGNAT_OK;
+    const int Mc = main_slots(L, 1);
+    int rows = (Mc + 7) / 8 * 8;
+    if (rows < 8) rows = 8;
+    if (rows > kMaxRows) rows = kMaxRows;
+    const int col_stride = (Mc + 3) / 4 * 4;
+    int lk_stride = Mc;
+    while (lk_stride % 8 != 4) lk_stride++;  // transposed tile: 8 rows x 4 lanes of a warp in distinct banks
+    const size_t smem_cols = (size_t)6 * col_stride * sizeof(float);
+    const size_t smem_links = (size_t)2 * Mc * lk_stride * sizeof(float);
+    dim3 block(kLanes, rows), grid(B);
+    cudaError_t e;
+    if (smem_cols + smem_links <= (size_t)kSmemLimit - 1024) {
+        auto k = outside_kernel<true>;
+        e = ensure_dynamic_smem(k, smem_cols + smem_links);
+        if (e != cudaSuccess) return PCFGNAT_ERR_CUDA;
+        k<<<grid, block, smem_cols + smem_links, st>>>(grad_output, S, match_all, links, ol, tl, L, T, S_grad, status,
+                                                       Mc, col_stride, lk_stride, redo);
+    } else {
+        if (smem_cols > (size_t)kSmemLimit - 1024) return PCFGNAT_ERR_TOO_LARGE;
+        auto k = outside_kernel<false>;
+        e = ensure_dynamic_smem(k, smem_cols);
+        if (e != cudaSuccess) return PCFGNAT_ERR_CUDA;
+        k<<<grid, block, smem_cols, st>>>(grad_output, S, match_all, links, ol, tl, L, T, S_grad, status, Mc,
+                                          col_stride, lk_stride, redo);
+    }
+    if (cudaGetLastError() != cudaSuccess) return PCFGNAT_ERR_CUDA;
+    return launch_grad_rows(S, S_grad, match_all, links, ol, tl, B, L, T, mg, lg, st, redo);
 }
 
 }  // namespace pcfgnat

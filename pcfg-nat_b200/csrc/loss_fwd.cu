@@ -104,9 +104,11 @@ template <bool SMEM_LINKS>
 __global__ void __launch_bounds__(kMaxRows *kLanes)
     loss_fwd_kernel(const float *__restrict__ match_all, const float *__restrict__ links,
                     const int64_t *__restrict__ ol, const int64_t *__restrict__ tl, int L, int T, float *S, float *C,
-                    float *loss, int *status, int Mc, int Lt, int col_stride, int lk_stride) {
+                    float *loss, int *status, int Mc, int Lt, int col_stride, int lk_stride, const float *redo) {
     extern __shared__ float smem[];
     const int b = blockIdx.x;
+    // redo: only the sentences the linear-space kernels left marked (loss_linear.cu)
+    if (redo && !linear_needs_redo(redo + (size_t)b * (kLinearFrameHead + T + 2), (int)tl[b])) return;
     const int x = threadIdx.x, y = threadIdx.y;
     const int rows = blockDim.y;
     const int tid = y * kLanes + x, nthr = rows * kLanes;
@@ -223,6 +225,14 @@ int launch_loss_fwd(const float *match_all, const float *links, const int64_t *o
         const int rc = launch_loss_fwd_balanced(match_all, links, ol, tl, B, L, T, S, C, loss, status, st);
         if (rc != PCFGNAT_ERR_UNSUPPORTED) return rc;
     }
+    return launch_loss_fwd_rows(match_all, links, ol, tl, B, L, T, S, C, loss, status, st, nullptr);
+}
+
+// The row-per-thread kernel (no size limit).  redo != nullptr: only the sentences marked in the frames of the
+// linear-space kernels are computed, the others are left untouched.
+int launch_loss_fwd_rows(const float *match_all, const float *links, const int64_t *ol, const int64_t *tl, int B, int L,
+                         int T, float *S, float *C, float *loss, int *status, cudaStream_t st, const float *redo) {
+    if (B == 0) return PCFGNAT_OK;
     const int Mc = main_slots(L, 1), Lt = L - Mc;
     int rows = (Mc + 7) / 8 * 8;
     if (rows < 8) rows = 8;
@@ -239,14 +249,14 @@ int launch_loss_fwd(const float *match_all, const float *links, const int64_t *o
         e = ensure_dynamic_smem(k, smem_cols + smem_links);
         if (e != cudaSuccess) return PCFGNAT_ERR_CUDA;
         k<<<grid, block, smem_cols + smem_links, st>>>(match_all, links, ol, tl, L, T, S, C, loss, status, Mc, Lt,
-                                                       col_stride, lk_stride);
+                                                       col_stride, lk_stride, redo);
     } else {
         if (smem_cols > (size_t)kSmemLimit - 1024) return PCFGNAT_ERR_TOO_LARGE;
         auto k = loss_fwd_kernel<false>;
         e = ensure_dynamic_smem(k, smem_cols);
         if (e != cudaSuccess) return PCFGNAT_ERR_CUDA;
         k<<<grid, block, smem_cols, st>>>(match_all, links, ol, tl, L, T, S, C, loss, status, Mc, Lt, col_stride,
-                                          lk_stride);
+                                          lk_stride, redo);
     }
     return cuda_rc(cudaGetLastError());
 }

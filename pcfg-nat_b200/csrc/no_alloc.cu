@@ -62,20 +62,13 @@ extern "C" int pcfgnat_loss_fwd_bwd_static(const float *match_all, const float *
     if (B < 0 || L < 2 || T < 1) return PCFGNAT_ERR_INVALID_ARGUMENT;
     if (B && (!match_all || !links || !output_length || !target_length || !loss || !match_all_grad || !links_grad))
         return PCFGNAT_ERR_INVALID_ARGUMENT;
-    // two tables of B x Mc x (T+2) floats, each rounded up to 256 bytes
+    // two tables of B x Mc x (T+2) floats, each rounded up to 256 bytes, and the frames of the linear-space pass
     const size_t table = ((size_t)B * main_slots(L, 1) * (size_t)(T + 2) * sizeof(float) + 255) / 256 * 256;
-    if (2 * table > kScratchBytes) return PCFGNAT_ERR_TOO_LARGE;
+    if (2 * table + linear_frames_bytes(B, T) > kScratchBytes) return PCFGNAT_ERR_TOO_LARGE;
     if (B == 0) return PCFGNAT_OK;
     void *base = nullptr;
     int rc = scratch_for_current_device(&base);
     if (rc) return rc;
-    float *S = static_cast<float *>(base);
-    float *G = reinterpret_cast<float *>(static_cast<unsigned char *>(base) + table);
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
-    bool shares_in_mg = false;
-    rc = launch_loss_fwd_internal(match_all, links, output_length, target_length, B, L, T, S, loss, status, st,
-                                  match_all_grad, &shares_in_mg);
-    if (rc) return rc;
-    return launch_loss_bwd(nullptr, S, match_all, links, output_length, target_length, B, L, T, G, match_all_grad,
-                           links_grad, status, st, shares_in_mg);
+    return loss_fwd_bwd_in(match_all, links, output_length, target_length, B, L, T, base, table, loss, match_all_grad,
+                           links_grad, status, static_cast<cudaStream_t>(stream));
 }

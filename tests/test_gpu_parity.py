@@ -384,6 +384,7 @@ def test_outside_pass_with_fused_gradients_matches_the_gradient_kernel(ops, syn,
     monkeypatch.delenv("PCFGNAT_DP_KERNEL", raising=False)
     monkeypatch.delenv("PCFGNAT_DP_CLUSTER_SIZE", raising=False)
     monkeypatch.delenv("PCFGNAT_EXACT_ORDER", raising=False)
+    monkeypatch.setenv("PCFGNAT_LINEAR_DP", "0")  # this test is about the log-space kernels behind the fused entry
     b, ma = _loss_inputs(syn, syn.Workload("fg", batch=batch, vocab=40, hidden=8, src_min=3, src_max=20 if batch > 6 else 60,
                                            emissions="logits"), 77)
     links = b.links
@@ -1016,3 +1017,76 @@ def test_loss_step_with_force_emit_matches_operator_chain(pkg, ops, syn):
     mgo[glance["keep_word_mask"].cpu().numpy()] = 0
     np.testing.assert_allclose(mg.cpu().numpy(), mgo, rtol=1e-3, atol=2e-6)
     np.testing.assert_allclose(lg.cpu().numpy(), lgo, rtol=1e-3, atol=2e-6)
+
+
+# ---- linear-space loss forward + backward (the default of the fused entry point) ---------------------------------
+
+def _fused(ops, ma, lk, ol, tl):
+    k = ops.get_pcfg_kernel()
+    loss, mg, lg = k.pcfg_loss_fwd_bwd(ma, lk, ol, tl)
+    torch.cuda.synchronize()
+    return loss, mg, lg
+
+
+@pytest.mark.parametrize("peak", [1.0, 8.0, 25.0])
+@pytest.mark.parametrize("shape", [dict(batch=5, src_min=4, src_max=30), dict(batch=3, fixed_graph=384, fixed_target=90),
+                                   dict(batch=70, src_min=6, src_max=20)])
+def test_linear_space_loss_against_oracle_peaked_inputs(ops, syn, monkeypatch, peak, shape):
+    """Emissions and transitions sharpened by `peak` (a trained model is far from the near-uniform synthetic
+    inputs): columns then span many e-folds, which is what the per-column scaling has to absorb; whatever it
+    cannot is recomputed in log space.  Either way the results hold the parity tolerances."""
+    monkeypatch.delenv("PCFGNAT_DP_KERNEL", raising=False)
+    w = syn.Workload("lin", vocab=50, hidden=8, emissions="logits", **shape)
+    b = syn.make_batch(w, seed=31)
+    b.logits.mul_(peak)
+    ma = syn.reference_match_all(b)
+    lk = torch.log_softmax((b.links * peak).view(b.B, b.L, -1), -1).view_as(b.links)
+    lk = torch.where(torch.isfinite(b.links), lk, b.links).contiguous()
+    lk = torch.where(torch.isnan(lk), torch.full_like(lk, float("-inf")), lk)
+    ol, tl = b.output_length.numpy(), b.target_length.numpy()
+    So, Co = oracle.pcfg_loss(ma.numpy(), lk.numpy(), ol, tl)
+    mgo, lgo = oracle.pcfg_loss_backward(np.ones(b.B, np.float32), So, Co, ma.numpy(), lk.numpy(), ol, tl)
+    loss, mg, lg = _fused(ops, ma.to(DEV), lk.to(DEV), b.output_length.to(DEV), b.target_length.to(DEV))
+    assert np.isfinite(So[:, 0, 0]).all()
+    np.testing.assert_allclose(loss.cpu().numpy(), So[:, 0, 0], rtol=1e-4)
+    np.testing.assert_allclose(mg.cpu().numpy(), mgo, rtol=1e-3, atol=2e-6)
+    np.testing.assert_allclose(lg.cpu().numpy(), lgo, rtol=1e-3, atol=2e-6)
+    # and against the log-space kernels of the same library
+    monkeypatch.setenv("PCFGNAT_LINEAR_DP", "0")
+    loss2, mg2, lg2 = _fused(ops, ma.to(DEV), lk.to(DEV), b.output_length.to(DEV), b.target_length.to(DEV))
+    torch.testing.assert_close(loss, loss2, rtol=1e-5, atol=0)
+    torch.testing.assert_close(mg, mg2, rtol=1e-3, atol=2e-6)
+    torch.testing.assert_close(lg, lg2, rtol=1e-3, atol=2e-6)
+
+
+def test_linear_space_loss_hands_unusual_sentences_to_the_log_space_kernels(ops, syn, monkeypatch):
+    """One batch with everything the linear-space kernels do not take themselves: an emission far above the range of
+    exp(), an out-of-range length, an odd graph length, a single target token, an infeasible sentence (more tokens
+    than the graph can emit), next to ordinary sentences.  Every sentence must come out as the log-space kernels
+    alone give it, and output buffers that were dirty must be fully overwritten."""
+    monkeypatch.delenv("PCFGNAT_DP_KERNEL", raising=False)
+    w = syn.Workload("lin2", batch=8, vocab=50, hidden=8, src_min=5, src_max=12, emissions="logits")
+    b = syn.make_batch(w, seed=32)
+    ma = syn.reference_match_all(b)
+    ol, tl = b.output_length.clone(), b.target_length.clone()
+    ma[0, 1, 0] = 200.0           # exp() overflows
+    ol[1] = b.L + 4               # out of range
+    ol[2] = ol[2] - 1             # odd graph length
+    tl[3] = 1                     # one target token
+    tl[4] = min(int(ol[4]) - 1, b.T)  # infeasible: n > m - 2
+    k = ops.get_pcfg_kernel()
+    args = (ma.to(DEV), b.links.to(DEV), ol.to(DEV), tl.to(DEV))
+    ops.read_status(DEV)
+    loss, mg, lg = _fused(ops, *args)
+    assert ops.read_status(DEV) & 1
+    monkeypatch.setenv("PCFGNAT_DP_KERNEL", "rows")  # the kernels that pick up the marked sentences, on their own
+    loss2, mg2, lg2 = _fused(ops, *args)
+    ops.read_status(DEV)
+    assert torch.equal(torch.isfinite(loss), torch.isfinite(loss2))
+    fin = torch.isfinite(loss2)
+    assert fin[5:].all() and not fin[1] and not fin[4]
+    torch.testing.assert_close(loss[fin], loss2[fin], rtol=1e-5, atol=0)
+    torch.testing.assert_close(mg, mg2, rtol=1e-3, atol=2e-6, equal_nan=True)
+    torch.testing.assert_close(lg, lg2, rtol=1e-3, atol=2e-6, equal_nan=True)
+    for i in (0, 1, 2, 3, 4):  # handed over: bit for bit what the log-space kernels give
+        assert torch.equal(mg[i].nan_to_num(7.0), mg2[i].nan_to_num(7.0)) and torch.equal(lg[i].nan_to_num(7.0), lg2[i].nan_to_num(7.0))
