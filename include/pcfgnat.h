@@ -49,6 +49,8 @@ extern "C" {
 #define PCFGNAT_STATUS_BAD_TRACE 2  /* a back-trace left the tables and was cut short */
 #define PCFGNAT_STATUS_BAD_INDEX 4  /* a gather index outside [0, V) produced NaN */
 #define PCFGNAT_STATUS_TIMEOUT 8    /* a bounded device-side wait ran out */
+#define PCFGNAT_STATUS_RECOMPUTED 16 /* pcfgnat_loss_fwd_bwd: a sentence was recomputed in log space (information,
+                                        not an error: unusual lengths, or numbers beyond the linear-space range) */
 
 #define PCFGNAT_DTYPE_F32 0
 #define PCFGNAT_DTYPE_F16 1

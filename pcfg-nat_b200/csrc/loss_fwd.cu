@@ -108,7 +108,10 @@ __global__ void __launch_bounds__(kMaxRows *kLanes)
     extern __shared__ float smem[];
     const int b = blockIdx.x;
     // redo: only the sentences the linear-space kernels left marked (loss_linear.cu)
-    if (redo && !linear_needs_redo(redo + (size_t)b * (kLinearFrameHead + T + 2), (int)tl[b])) return;
+    if (redo) {
+        if (!linear_needs_redo(redo + (size_t)b * (kLinearFrameHead + T + 2), (int)tl[b])) return;
+        if (threadIdx.x == 0 && threadIdx.y == 0) flag(status, PCFGNAT_STATUS_RECOMPUTED);
+    }
     const int x = threadIdx.x, y = threadIdx.y;
     const int rows = blockDim.y;
     const int tid = y * kLanes + x, nthr = rows * kLanes;

@@ -10,26 +10,27 @@
 //     s_t[a] = E0[a][t] * sum_c P0[a][c] s_{t+1}[c]  +  E1[a][t] * sum_c P1[a][c] s_{t+2}[c]
 // i.e. one fused multiply-add per term and O(M) transcendentals per step instead of O(M^2).
 //
-// Scaling.  s_t spans hundreds of e-folds over a sentence, so every column is kept relative to the maximum of
-// the column computed before it: the kernel stores u_t[a] = s_t[a] / Phi_{t+1}, Phi_t = N_t Phi_{t+1},
-// N_t = max_a u_t[a], and the recurrence becomes
-//     u_t[a] = E0 inv_{t+1} sum_c P0 u_{t+1}[c] + E1 inv_{t+1} inv_{t+2} sum_c P1 u_{t+2}[c],   inv_t = 1 / N_t.
-// Every warp reads the whole column for its dot products anyway, so it takes the column maximum from the same
-// registers (one integer warp reduction): no extra exchange, and all warps of all CTAs get the identical N_t.
-// log Z = log u_0[root] + sum_t log N_t.
+// Scaling.  s_t spans hundreds of e-folds over a sentence, so every column is stored with a scale of its own:
+// the kernel keeps u_t[a] = s_t[a] / G_t, G_t = G_{t+1} / rho_t, and the recurrence becomes
+//     u_t[a] = rho_t ( E0 sum_c P0 u_{t+1}[c] + rho_{t+1} E1 sum_c P1 u_{t+2}[c] ).
+// Any positive rho_t that all warps agree on is exact; it only has to keep the numbers in range.  rho_t is
+// taken from the maximum of column t + 2 (column_scale), which every warp reads off the finished column one
+// step ahead of need, after its own nodes of the step are on their way: finding it costs the chain of dependent
+// steps nothing, and all warps of all CTAs get the identical value.  log Z = log u_0[root] - sum_t log rho_t.
+// (In the code inv_{t+1} names rho_t.)
 //
-// The outside pass needs no inside values in linear space.  With o_t[a] = out_t[a] Phi_{t+1} / Z the posterior
+// The outside pass needs no inside values in linear space.  With o_t[a] = out_t[a] G_t / Z the posterior
 // of a cell is simply o_t[a] u_t[a], and
-//     o_{t+1}[c] = inv_{t+1} ( sum_a x0_t[a] P0[a][c] + inv_t sum_a x1_{t-1}[a] P1[a][c] ),
+//     o_{t+1}[c] = rho_t ( sum_a x0_t[a] P0[a][c] + rho_{t-1} sum_a x1_{t-1}[a] P1[a][c] ),
 //     x0_t[a] = o_t[a] E0[a][t],  x1_t[a] = o_t[a] E1[a][t],  o_0[root] = 1 / u_0[root]:
 // two transposed matrix-vector products per step with the frames the inside pass recorded.  The gradients are
 // then sums of products over the steps, which need no dependent chain and run after the loop on all threads:
-//     links_grad[a][0][c] = P0[a][c] sum_t x0_t[a] y_{t+1}[c],   y_t[c] = u_t[c] inv_t
-//     links_grad[a][1][c] = P1[a][c] sum_t x1_t[a] inv_{t+1} y_{t+2}[c]
+//     links_grad[a][0][c] = P0[a][c] sum_t x0_t[a] y_{t+1}[c],   y_t[c] = u_t[c] rho_{t-1}
+//     links_grad[a][1][c] = P1[a][c] sum_t x1_t[a] rho_t y_{t+2}[c]
 //     match_grad[a][t]    = o_t[a] p0_t[a] + o_{t-1}[a] p1_{t-1}[a]      (p0, p1: the two halves of u_t[a])
 //     match_grad[a-1][t]  = o_t[a] p1_t[a]
 //
-// Cells more than ~87 e-folds below their column's maximum flush to zero.  They carry no measurable posterior
+// Cells some 60 e-folds below their column's maximum flush to zero.  They carry no measurable posterior
 // mass in a normal sentence, but the kernels do not rely on that: the outside kernel adds up the emission
 // gradients of the sentence, which must total the number of target tokens; when they do not (to 1e-4), when Z
 // is zero or not finite, when an input overflowed exp(), or when the lengths are unusual (odd graph length, one
@@ -47,12 +48,33 @@
 
 namespace cg = cooperative_groups;
 
+// Development aid, compiled out of the library: with -DPCFGNAT_TIMING the first thread of every sentence's first
+// CTA records clock64() stamps of the kernel's phases.
+#ifdef PCFGNAT_TIMING
+__device__ long long g_linear_timing[2][256][16];
+#define PCFGNAT_STAMP(k, i) \
+    if (tid == 0 && crank == 0 && b < 256) g_linear_timing[k][b][i] = clock64();
+#define PCFGNAT_ACC(k, i, v) \
+    if (tid == 0 && crank == 0 && b < 256) g_linear_timing[k][b][i] += (v);
+extern "C" int pcfgnat_debug_linear_timing(long long *host_out) {
+    return (int)cudaMemcpyFromSymbol(host_out, g_linear_timing, sizeof(g_linear_timing));
+}
+extern "C" int pcfgnat_debug_linear_timing_reset() {
+    static long long zeros[2 * 256 * 16];
+    return (int)cudaMemcpyToSymbol(g_linear_timing, zeros, sizeof(zeros));
+}
+#else
+#define PCFGNAT_STAMP(k, i)
+#define PCFGNAT_ACC(k, i, v)
+#endif
+
 namespace pcfgnat {
 
 namespace {
 
-constexpr int kLThreads = 1024;
+constexpr int kLThreads = 512;
 constexpr int kLWarps = kLThreads / 32;
+constexpr int kMaxMixedBatch = 256;                // mixed cluster widths only up to this many sentences (mixed_width_count)
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
@@ -66,6 +88,12 @@ __device__ __forceinline__ float lg2f(float x) {
     asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+// Scale applied to column t, from the maximum m of column t + 2 (known a whole step earlier, so that finding it
+// is not on the chain of dependent steps): m^(-3/4).  With x_t = log max of column t the columns then follow
+// x_t = e_t + x_{t+1} - 0.75 x_{t+2} (e_t: log of a typical emission x transition), a damped recurrence: the maxima
+// settle around exp(4/3 e) instead of drifting, with fluctuations of the order of those of e_t.  A column below
+// 1e-36 counts as empty (Z then comes out zero and the sentence is recomputed in log space).
+__device__ __forceinline__ float column_scale(float m) { return m > 1e-36f ? ex2f(-0.75f * lg2f(m)) : 0.f; }
 // exp of a log-probability; NaN counts as -inf (the reference's cleaning of NaN terms, pcfg_loss.cu:162)
 __device__ __forceinline__ float exp_clean(float x) { return ex2f(fmaxf(x, neg_inf()) * kLog2e); }
 
@@ -82,6 +110,9 @@ __device__ __forceinline__ float dot4(const float4 &a, const float4 &b) {
     return fmaf(a.x, b.x, fmaf(a.y, b.y, fmaf(a.z, b.z, a.w * b.w)));
 }
 
+// Floats the outside kernel keeps in front of its step-loop memory (E0, E1 and the column scales), a multiple of 4.
+__host__ __device__ inline int linear_outside_head(int rows_cap, int W) { return (2 * rows_cap * W + W + 3) & ~3; }
+
 // The sentence of this cluster and the number of its CTAs that work on it (the mixed-width rule of
 // loss_cluster.cu: with `wide` >= 0 the clusters take the sentences by decreasing cost and only the `wide`
 // costliest use every CTA).  False: this CTA has nothing to do and must return at once.
@@ -91,14 +122,18 @@ __device__ __forceinline__ bool pick_sentence(const int64_t *ol, const int64_t *
     b = blockIdx.x / cluster_blocks;
     if (wide < 0) return true;
     __shared__ int s_b;
+    __shared__ int s_cost[kMaxMixedBatch];  // m n of every sentence (0: lengths out of range)
     const int want = b;
     for (int i = threadIdx.x; i < B; i += kLThreads) {
         const long long mi = ol[i], ni = tl[i];
-        const long long ci = lengths_ok((int)mi, (int)ni, L, T) ? mi * ni : 0;
+        s_cost[i] = lengths_ok((int)mi, (int)ni, L, T) ? (int)(mi * ni) : 0;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < B; i += kLThreads) {
+        const int ci = s_cost[i];
         int before = 0;
         for (int j = 0; j < B; j++) {
-            const long long mj = ol[j], nj = tl[j];
-            const long long cj = lengths_ok((int)mj, (int)nj, L, T) ? mj * nj : 0;
+            const int cj = s_cost[j];
             before += cj > ci || (cj == ci && j < i);
         }
         if (before == want) s_b = i;
@@ -110,6 +145,43 @@ __device__ __forceinline__ bool pick_sentence(const int64_t *ol, const int64_t *
         NC = 1;
     }
     return true;
+}
+
+// lmx[t] = max over the main-chain nodes in use of match[a][t] (0 when the token has no finite emission): the
+// emissions of token t are taken relative to it, which only changes the units of s_t (posteriors do not notice,
+// log Z gets the sum back) but keeps the columns of both passes centred in the range of the floats however
+// peaked the emissions are.  Both kernels compute it the same way, so nothing has to be handed over.
+__device__ __forceinline__ void token_maxima(const float *__restrict__ mat, int m, int n, int T, int W, float *lmx) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int *enc = reinterpret_cast<int *>(lmx);  // order-preserving integer image of the floats while the maxima are taken
+    for (int t = threadIdx.x; t < W; t += kLThreads) enc[t] = (int)0x80000000;
+    __syncthreads();
+    // lanes over tokens (coalesced rows), warps over nodes; the warps meet in shared-memory integer maxima
+    for (int t0 = 0; t0 < n; t0 += 128) {
+        float v[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) v[j] = neg_inf();
+        for (int a = 2 * warp + 1; a < m; a += 2 * kLWarps) {
+            const float *row = mat + (size_t)a * T + t0 + lane;
+#pragma unroll
+            for (int j = 0; j < 4; j++)
+                if (t0 + lane + 32 * j < n) v[j] = fmaxf(v[j], __ldg(row + 32 * j));
+        }
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int t = t0 + lane + 32 * j;
+            if (t < n) {
+                const int i = __float_as_int(v[j]);
+                atomicMax(enc + t, i >= 0 ? i : i ^ 0x7fffffff);
+            }
+        }
+    }
+    __syncthreads();
+    for (int t = threadIdx.x; t < W; t += kLThreads) {
+        const int i = enc[t];
+        const float v = __int_as_float(i >= 0 ? i : i ^ 0x7fffffff);
+        lmx[t] = (t < n && v > neg_inf() && v < CUDART_INF_F) ? v : 0.f;
+    }
 }
 
 __device__ __forceinline__ void bar_init(uint64_t *bars, int count) {
@@ -128,7 +200,7 @@ __device__ __forceinline__ void bar_expect(uint32_t bar, int bytes) {
 // frames [B][F], F = kLinearFrameHead + W:  [0] u_0[root]  [1] log Z  [2] emission-gradient mass (outside pass)
 //                     [3] != 0: an input overflowed  [4 + t] inv_t
 // shares [B][L][T]    (the match_all_grad buffer) p0_t[a] in cell [a][t], p1_t[a] in cell [a-1][t], t <= n-2
-template <int TR>
+template <int G, int TRIPS>
 __global__ void __launch_bounds__(kLThreads, 1)
     inside_linear_kernel(const float *__restrict__ match_all, const float *__restrict__ links,
                          const int64_t *__restrict__ ol, const int64_t *__restrict__ tl, int L, int T, float *Y,
@@ -139,8 +211,14 @@ __global__ void __launch_bounds__(kLThreads, 1)
     cg::cluster_group cluster = cg::this_cluster();
     const int crank = (int)cluster.block_rank();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+#ifdef PCFGNAT_TIMING
+    const long long t_start = clock64();
+#endif
     int b, NC;
     if (!pick_sentence(ol, tl, B, L, T, wide, (int)cluster.num_blocks(), crank, b, NC)) return;
+#ifdef PCFGNAT_TIMING
+    if (tid == 0 && crank == 0 && b < 256) g_linear_timing[0][b][0] = t_start;
+#endif
     const int ctid = crank * kLThreads + tid;
     const int W = T + 2, F = kLinearFrameHead + W;
     const int m = (int)ol[b], n = (int)tl[b];
@@ -155,6 +233,7 @@ __global__ void __launch_bounds__(kLThreads, 1)
         }
         return;
     }
+    PCFGNAT_STAMP(0, 1)
     const float *mat = match_all + (size_t)b * L * T;
     const float *lkb = links + (size_t)b * L * 2 * L;
     const int Mb = m / 2, last = (m - 2) / 2;
@@ -169,20 +248,27 @@ __global__ void __launch_bounds__(kLThreads, 1)
     float *e1 = e0 + (size_t)rows_cap * W;
     float *invs = e1 + (size_t)rows_cap * W;    // [W]
     __shared__ __align__(8) uint64_t col_bar[2];
-    __shared__ int s_overflow;
-    if (tid == 0) s_overflow = 0;
+    __shared__ int s_overflow, s_timeout;
+    __shared__ float s_rho[4], s_sumlog;  // scales of the steps in flight (slot t & 3); - sum of their log2
+    __shared__ float s_lmx_sum, s_lmx_last;
+    if (tid == 0) {
+        s_overflow = 0;
+        s_lmx_sum = 0.f;
+    }
     __syncthreads();
 
+    token_maxima(mat, m, n, T, W, invs);  // borrowed until the scales are written: invs[t] = lmx[t]
+    __syncthreads();
     bool big = false;
     for (int i = tid; i < my_rows * W; i += kLThreads) {
         const int r = i / W, t = i - r * W, a = 2 * (crank + NC * r) + 1;
         float v0 = 0.f, v1 = 0.f;
         if (t < n) {
             const float ma = __ldg(mat + (size_t)a * T + t);
-            v0 = exp_clean(ma);
+            v0 = exp_clean(ma - invs[t]);
             if (a >= 3 && t + 1 < n)
-                v1 = exp_clean(fmaxf(__ldg(mat + (size_t)(a - 1) * T + t), neg_inf()) +
-                               fmaxf(__ldg(mat + (size_t)a * T + t + 1), neg_inf()));
+                v1 = exp_clean((fmaxf(__ldg(mat + (size_t)(a - 1) * T + t), neg_inf()) - invs[t]) +
+                               (fmaxf(__ldg(mat + (size_t)a * T + t + 1), neg_inf()) - invs[t + 1]));
         }
         big |= !(v0 < 1e30f) || !(v1 < 1e30f);
         e0[i] = v0;
@@ -205,6 +291,15 @@ __global__ void __launch_bounds__(kLThreads, 1)
     }
     if (big) s_overflow = 1;
     for (int i = tid; i < 4 * cs; i += kLThreads) col[i] = 0.f;
+    __syncthreads();  // E0 and E1 are formed: the per-token maxima make room for the scales
+    float lmx_part = 0.f;  // this thread's part of sum_t lmx[t]
+    for (int i = tid; i < W; i += kLThreads) {
+        lmx_part += i < n ? invs[i] : 0.f;
+        if (i == n - 1) s_lmx_last = invs[i];
+    }
+    lmx_part = warp_sum(lmx_part);
+    if (lane == 0 && lmx_part != 0.f) atomicAdd(&s_lmx_sum, lmx_part);
+    __syncthreads();
     for (int i = tid; i < W; i += kLThreads) invs[i] = 0.f;
     if (tid == 0) bar_init(col_bar, 2);
     if (ctid == 0) {
@@ -212,78 +307,158 @@ __global__ void __launch_bounds__(kLThreads, 1)
         fr[3] = 0.f;
     }
     __syncthreads();
-    const float base = exp_clean(__ldg(mat + (size_t)(m - 1) * T + (n - 1)));
+    const float base = exp_clean(__ldg(mat + (size_t)(m - 1) * T + (n - 1)) - s_lmx_last);
     if (tid == 0) {
         col[((n - 1) & 3) * cs + last] = base;  // every CTA fills its own copy
         if (last % NC == crank) ownu[(size_t)(last / NC) * W + (n - 1)] = base;
     }
+    PCFGNAT_STAMP(0, 2)
     if (NC > 1) cluster.sync(); else __syncthreads();
+    PCFGNAT_STAMP(0, 3)
     if (s_overflow && tid == 0) fr[3] = 1.f;  // after the reset above (ordered by the barrier)
 
-    bool arrived = true;
-    float inv_prev = 0.f, sumlog = 0.f;
+    // Step loop.  G lanes share a node (lane q of them covers the groups of four children q, q + G, ...), so a warp
+    // does 32 / G nodes at once, always the same ones: their rows of P0 and P1 stay in REGISTERS for the whole loop
+    // (TRIPS float4 each per lane), and a step reads only the two columns from shared memory.  Nodes beyond what
+    // the warps can hold that way (long chains on few CTAs) take their rows from shared memory every step.
+    // The last warp does not compute nodes unless the chain is that long: it derives the scale two steps ahead
+    // from the finished column, keeps the books of the scales, and waits for the column of the step on the
+    // byte-counting barrier; the block barrier then releases the others, so nobody else spins.
+    constexpr int R = 32 / G;  // nodes per warp
+    const int cs4 = cs >> 2;
+    const int groups = (my_rows + R - 1) / R;
+    const int q = lane % G, sub = lane / G;
+    const float4 *P0v = reinterpret_cast<const float4 *>(P0), *P1v = reinterpret_cast<const float4 *>(P1);
+    const int r_own = warp * R + sub;
+    const bool live_own = r_own < my_rows;
+    float4 rp0[TRIPS], rp1[TRIPS];
+#pragma unroll
+    for (int i = 0; i < TRIPS; i++) {
+        const int c4 = q + G * i;
+        rp0[i] = rp1[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (live_own && c4 < cs4) {
+            rp0[i] = P0v[r_own * cs4 + c4];
+            rp1[i] = P1v[r_own * cs4 + c4];
+        }
+    }
+    uint32_t rcol = 0, rbar0 = 0, rbar1 = 0;  // lane q < NC: this CTA's columns and barriers as CTA q maps them
+    if (NC > 1 && q < NC) {
+        rcol = dsm_map_to_cta(dsm_smem_u32(col), q);
+        rbar0 = dsm_map_to_cta(dsm_smem_u32(&col_bar[0]), q);
+        rbar1 = dsm_map_to_cta(dsm_smem_u32(&col_bar[1]), q);
+    }
+    if (tid == 0) {
+        s_timeout = 0;
+        s_rho[(n - 2) & 3] = column_scale(base);  // the first step's scale comes from the terminal cell
+        s_rho[(n - 1) & 3] = 0.f;
+    }
+    __syncthreads();
+    float sumlog = 0.f;  // lane 0 of the last warp: - sum of log2 rho_t
+#ifdef PCFGNAT_TIMING
+    long long tA = 0, tB = 0, tC = 0, tD = 0, tq = clock64();
+#define PCFGNAT_LAP(acc) { const long long now_ = clock64(); acc += now_ - tq; tq = now_; }
+#else
+#define PCFGNAT_LAP(acc)
+#endif
     for (int t = n - 2; t >= 0; t--) {
-        const float *S1 = col + ((t + 1) & 3) * cs;
-        const float *S2 = col + ((t + 2) & 3) * cs;
+        const float4 *S1v = reinterpret_cast<const float4 *>(col + ((t + 1) & 3) * cs);
+        const float4 *S2v = reinterpret_cast<const float4 *>(col + ((t + 2) & 3) * cs);
         float *S0 = col + (t & 3) * cs;
         const uint32_t bar = dsm_smem_u32(&col_bar[t & 1]);
         if (NC > 1 && tid == 0) bar_expect(bar, 4 * Mb);
-        float4 s1[TR], s2[TR];
-        float mx = 0.f;
+        if (warp < groups) {
+            const float rho = s_rho[t & 3], rho_prev = s_rho[(t + 1) & 3];
+            const uint32_t rS0 = rcol + 4u * ((t & 3) * cs), rbar = (t & 1) ? rbar1 : rbar0;
+            PCFGNAT_LAP(tA)
+            for (int g = warp; g < groups; g += kLWarps) {
+                const int r = g * R + sub;
+                const bool live = r < my_rows;
+                const int rr = live ? r : 0;
+                float acc0 = 0.f, acc1 = 0.f;
+                if (g == warp) {  // this warp's resident nodes
+                    float a[TRIPS], c[TRIPS];
 #pragma unroll
-        for (int i = 0; i < TR; i++) {
-            const int c4 = 4 * lane + 128 * i;
-            s1[i] = s2[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (c4 < cs) {
-                s1[i] = *reinterpret_cast<const float4 *>(S1 + c4);
-                s2[i] = *reinterpret_cast<const float4 *>(S2 + c4);
-            }
-            mx = fmaxf(fmaxf(mx, fmaxf(s1[i].x, s1[i].y)), fmaxf(s1[i].z, s1[i].w));
-        }
-        const float N1 = warp_max_nonneg(mx);  // N_{t+1}: the same value in every warp of every CTA
-        // inv_{t+1}; a column below 1e-36 counts as empty (its reciprocal would leave the range; Z then comes
-        // out zero and the sentence is recomputed in log space)
-        const float inv1 = N1 > 1e-36f ? __frcp_rn(N1) : 0.f;
-        for (int r = warp; r < my_rows; r += kLWarps) {
-            const int ai = crank + NC * r;
-            const float *p0 = P0 + (size_t)r * cs, *p1 = P1 + (size_t)r * cs;
-            float acc0 = 0.f, acc1 = 0.f;
+                    for (int i = 0; i < TRIPS; i++) {
+                        const int c4 = q + G * i;
+                        a[i] = c[i] = 0.f;
+                        if (c4 < cs4) {
+                            a[i] = dot4(rp0[i], S1v[c4]);
+                            c[i] = dot4(rp1[i], S2v[c4]);
+                        }
+                    }
 #pragma unroll
-            for (int i = 0; i < TR; i++) {
-                const int c4 = 4 * lane + 128 * i;
-                if (c4 < cs) {
-                    acc0 += dot4(*reinterpret_cast<const float4 *>(p0 + c4), s1[i]);
-                    acc1 += dot4(*reinterpret_cast<const float4 *>(p1 + c4), s2[i]);
+                    for (int i = 0; i < TRIPS; i++) {
+                        acc0 += a[i];
+                        acc1 += c[i];
+                    }
+                } else {  // further nodes of a long chain: rows from shared memory, children ci > ai only
+                    const float4 *p0 = P0v + rr * cs4, *p1 = P1v + rr * cs4;
+                    for (int c4 = q + ((crank + NC * rr + 1) >> 2) / G * G; c4 < cs4; c4 += G) {
+                        acc0 += dot4(p0[c4], S1v[c4]);
+                        acc1 += dot4(p1[c4], S2v[c4]);
+                    }
+                }
+                PCFGNAT_LAP(tB)
+                // one scale at a time: the product of two scales can leave the range although the result does not
+                float v0 = e0[rr * W + t] * (acc0 * rho);
+                float v1 = e1[rr * W + t] * ((acc1 * rho_prev) * rho);
+#pragma unroll
+                for (int o = G / 2; o > 0; o >>= 1) {
+                    v0 += __shfl_xor_sync(0xffffffffu, v0, o);
+                    v1 += __shfl_xor_sync(0xffffffffu, v1, o);
+                }
+                const float u = v0 + v1;
+                if (live) {
+                    const int ai = crank + NC * r;
+                    if (NC > 1) {  // lane q of the node sends to CTA q: into its column, counted on its barrier of this step
+                        if (q < NC) dsm_store_async(rS0 + 4u * ai, u, rbar);
+                    } else if (q == 0) {
+                        S0[ai] = u;
+                    }
+                    if (q == 0) {
+                        ownu[r * W + t] = u;
+                        own0[r * W + t] = v0;
+                        own1[r * W + t] = v1;
+                    }
                 }
             }
-            acc0 = warp_sum(acc0);
-            acc1 = warp_sum(acc1);
-            // one scale at a time: the product of two reciprocals can leave the range although the result does not
-            const float v0 = e0[(size_t)r * W + t] * (acc0 * inv1);
-            const float v1 = e1[(size_t)r * W + t] * ((acc1 * inv_prev) * inv1);
-            const float u = v0 + v1;
-            if (NC > 1) {  // into every CTA's column, counted on that CTA's barrier of this step
-                if (lane < NC) dsm_store_async(dsm_map_to_cta(dsm_smem_u32(S0 + ai), lane), u, dsm_map_to_cta(bar, lane));
-            } else if (lane == 0) {
-                S0[ai] = u;
+        }
+        PCFGNAT_LAP(tC)
+        if (warp == kLWarps - 1) {
+            // The scale of step t - 1, from the column that has been complete since the previous barrier (t + 1).
+            // Every CTA's last warp reads the same column and gets the same value.
+            float mx = 0.f;
+            for (int c4 = lane; c4 < cs4; c4 += 32) {
+                const float4 v = S1v[c4];
+                mx = fmaxf(fmaxf(mx, fmaxf(v.x, v.y)), fmaxf(v.z, v.w));
             }
+            mx = warp_max_nonneg(mx);
             if (lane == 0) {
-                ownu[(size_t)r * W + t] = u;
-                own0[(size_t)r * W + t] = v0;
-                own1[(size_t)r * W + t] = v1;
+                const float rho = s_rho[t & 3];
+                s_rho[(t + 3) & 3] = column_scale(mx);  // slot of step t - 1
+                invs[t + 1] = rho;
+                sumlog -= lg2f(rho);
             }
+            if (NC > 1 && !dsm_wait_column(bar, (((n - 2) - t) >> 1) & 1)) s_timeout = 1;
         }
-        if (tid == 0) {
-            invs[t + 1] = inv1;
-            sumlog += lg2f(N1);
-        }
-        inv_prev = inv1;
-        if (NC > 1) arrived = dsm_wait_column(bar, (((n - 2) - t) >> 1) & 1) && arrived;
-        else __syncthreads();
+        __syncthreads();
+        PCFGNAT_LAP(tD)
     }
-    if (!arrived) flag(status, PCFGNAT_STATUS_TIMEOUT);
+    if (warp == kLWarps - 1 && lane == 0) s_sumlog = sumlog;
+#ifdef PCFGNAT_TIMING
+    if (tid == 0 && crank == 0 && b < 256) {
+        g_linear_timing[0][b][8] = tD;
+        g_linear_timing[0][b][11] = tA;
+        g_linear_timing[0][b][12] = tB;
+        g_linear_timing[0][b][13] = tC;
+    }
+#endif
+    PCFGNAT_STAMP(0, 4)
+    const bool arrived = s_timeout == 0;
+    if (!arrived && tid == 0) flag(status, PCFGNAT_STATUS_TIMEOUT);
     // no CTA leaves (its shared memory with it) while a peer may still send to it; every wait above is bounded
     if (NC > 1) cluster.sync(); else __syncthreads();
+    PCFGNAT_STAMP(0, 5)
 
     float *Yb = Y + (size_t)b * W * Mc;
     for (int i = tid; i < my_rows * (n - 1); i += kLThreads) {  // columns 1 .. n-1 of this CTA's nodes, normalised
@@ -300,32 +475,40 @@ __global__ void __launch_bounds__(kLThreads, 1)
         for (int t = tid; t < W; t += kLThreads) fr[kLinearFrameHead + t] = invs[t];
         if (tid == 0) {
             const float u00 = ownu[0];  // row 0 of rank 0 is the root, column 0
-            const float lz = u00 > 0.f ? (lg2f(u00) + sumlog) * kLn2 : neg_inf();
+            const float lz = u00 > 0.f ? (lg2f(u00) + s_sumlog) * kLn2 + s_lmx_sum : neg_inf();
             fr[0] = arrived ? u00 : 0.f;
             fr[1] = lz;
             if (loss) loss[b] = lz;
         }
     }
+    PCFGNAT_STAMP(0, 6)
+    PCFGNAT_ACC(0, 9, NC)
 }
 
 // ---------------------------------------------------------------------------------------
 // outside pass + gradients
 // ---------------------------------------------------------------------------------------
 // J = children per lane in the links-gradient sums (32 J >= main-chain nodes).
-template <int TR>
+template <int G, int TRIPS>
 __global__ void __launch_bounds__(kLThreads, 1)
     outside_linear_kernel(const float *__restrict__ match_all, const float *__restrict__ links,
                           const int64_t *__restrict__ ol, const int64_t *__restrict__ tl, int L, int T,
                           const float *__restrict__ Y, float *O, float *frames, float *mg, float *lg, int *status, int Mc,
                           int cs, int rows_cap, int B, int wide) {
-    constexpr int J = 4 * TR;
+    constexpr int kGradChunk = 2;
     extern __shared__ float4 smem4[];
     float *smem = reinterpret_cast<float *>(smem4);
     cg::cluster_group cluster = cg::this_cluster();
     const int crank = (int)cluster.block_rank();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+#ifdef PCFGNAT_TIMING
+    const long long t_start = clock64();
+#endif
     int b, NC;
     if (!pick_sentence(ol, tl, B, L, T, wide, (int)cluster.num_blocks(), crank, b, NC)) return;
+#ifdef PCFGNAT_TIMING
+    if (tid == 0 && crank == 0 && b < 256) g_linear_timing[1][b][0] = t_start;
+#endif
     const int ctid = crank * kLThreads + tid, cthreads = NC * kLThreads;
     const int W = T + 2, F = kLinearFrameHead + W;
     const int m = (int)ol[b], n = (int)tl[b];
@@ -333,34 +516,42 @@ __global__ void __launch_bounds__(kLThreads, 1)
     // what the inside pass marked, or could not finish, is left to the log-space kernels (uniform over the cluster)
     const float u00 = fr[0];
     if (fr[3] != 0.f || !(u00 > 0.f) || !(fabsf(fr[1]) < CUDART_INF_F)) return;
+    PCFGNAT_STAMP(1, 1)
     const float *mat = match_all + (size_t)b * L * T;
     const float *lkb = links + (size_t)b * L * 2 * L;
     const int Mb = m / 2, last = (m - 2) / 2;
     const int my_rows = Mb > crank ? (Mb - crank + NC - 1) / NC : 0;  // nodes ci = crank + NC * r
-    float *xc0 = smem;                           // [4][cs] rolling columns x0_s of the whole chain
+    float *e0 = smem;                            // [rows_cap][W] E0, E1; after the loop x0_t and x1_t inv_{t+1}
+    float *e1 = e0 + (size_t)rows_cap * W;
+    float *invs = e1 + (size_t)rows_cap * W;     // [W]
+    float *loop_mem = smem + linear_outside_head(rows_cap, W);  // what follows is only needed by the step loop
+    float *xc0 = loop_mem;                       // [4][cs] rolling columns x0_s of the whole chain
     float *xc1 = xc0 + 4 * cs;                   // [4][cs] x1_s
     float *PT0 = xc1 + 4 * cs;                   // [rows_cap][cs] exp(links[a][0][c]) of this CTA's CHILDREN c, by parent
     float *PT1 = PT0 + (size_t)rows_cap * cs;
     float *owno = PT1 + (size_t)rows_cap * cs;   // [rows_cap][W] o_t of this CTA's nodes
-    float *e0 = owno + (size_t)rows_cap * W;     // [rows_cap][W] E0, E1; after the loop x0_t and x1_t inv_{t+1}
-    float *e1 = e0 + (size_t)rows_cap * W;
-    float *invs = e1 + (size_t)rows_cap * W;     // [W]
     __shared__ __align__(8) uint64_t col_bar[2];
     __shared__ float red[kLWarps];
+    __shared__ int s_timeout, s_range;
 
+    token_maxima(mat, m, n, T, W, invs);  // borrowed until the scales are loaded: invs[t] = lmx[t]
+    __syncthreads();
     for (int i = tid; i < my_rows * W; i += kLThreads) {
         const int r = i / W, t = i - r * W, a = 2 * (crank + NC * r) + 1;
         float v0 = 0.f, v1 = 0.f;
         if (t < n) {
-            v0 = exp_clean(__ldg(mat + (size_t)a * T + t));
+            v0 = exp_clean(__ldg(mat + (size_t)a * T + t) - invs[t]);
             if (a >= 3 && t + 1 < n)
-                v1 = exp_clean(fmaxf(__ldg(mat + (size_t)(a - 1) * T + t), neg_inf()) +
-                               fmaxf(__ldg(mat + (size_t)a * T + t + 1), neg_inf()));
+                v1 = exp_clean((fmaxf(__ldg(mat + (size_t)(a - 1) * T + t), neg_inf()) - invs[t]) +
+                               (fmaxf(__ldg(mat + (size_t)a * T + t + 1), neg_inf()) - invs[t + 1]));
         }
         e0[i] = v0;
         e1[i] = v1;
         owno[i] = 0.f;
     }
+    const float e_root = exp_clean(__ldg(mat + (size_t)1 * T + 0) - invs[0]);       // E0 of the root at token 0
+    const float e_term = exp_clean(__ldg(mat + (size_t)(m - 1) * T + (n - 1)) - invs[n - 1]);  // u of the terminal cell
+    __syncthreads();  // the maxima are used up: invs takes the scales below
     for (int r = warp; r < my_rows; r += kLWarps) {
         const int ci = crank + NC * r;
         for (int ai = lane; ai < cs; ai += 32) {
@@ -380,64 +571,117 @@ __global__ void __launch_bounds__(kLThreads, 1)
     __syncthreads();
     const float o_root = __frcp_rn(u00);
     if (tid == 0) {
-        xc0[0] = o_root * exp_clean(__ldg(mat + (size_t)1 * T + 0));  // x0_0[root]; the root has no left child: x1 = 0
+        xc0[0] = o_root * e_root;  // x0_0[root]; the root has no left child: x1 = 0
         if (crank == 0) owno[0] = o_root;
     }
+    PCFGNAT_STAMP(1, 2)
     if (NC > 1) cluster.sync(); else __syncthreads();
+    PCFGNAT_STAMP(1, 3)
 
-    bool arrived = true;
+    // Step loop, laid out as in the inside pass: G lanes per node, the node's rows of the transposed matrices in
+    // registers, the last warp waits for the columns of the step.
+    constexpr int R = 32 / G;
+    const int cs4 = cs >> 2;
+    const int groups = (my_rows + R - 1) / R;
+    const int q = lane % G, sub = lane / G;
+    const float4 *PT0v = reinterpret_cast<const float4 *>(PT0), *PT1v = reinterpret_cast<const float4 *>(PT1);
+    const int r_own = warp * R + sub;
+    const bool live_own = r_own < my_rows;
+    float4 rp0[TRIPS], rp1[TRIPS];
+#pragma unroll
+    for (int i = 0; i < TRIPS; i++) {
+        const int c4 = q + G * i;
+        rp0[i] = rp1[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (live_own && c4 < cs4) {
+            rp0[i] = PT0v[r_own * cs4 + c4];
+            rp1[i] = PT1v[r_own * cs4 + c4];
+        }
+    }
+    uint32_t rx0 = 0, rx1 = 0, rbar0 = 0, rbar1 = 0;  // lane q < NC: this CTA's columns and barriers as CTA q maps them
+    if (NC > 1 && q < NC) {
+        rx0 = dsm_map_to_cta(dsm_smem_u32(xc0), q);
+        rx1 = dsm_map_to_cta(dsm_smem_u32(xc1), q);
+        rbar0 = dsm_map_to_cta(dsm_smem_u32(&col_bar[0]), q);
+        rbar1 = dsm_map_to_cta(dsm_smem_u32(&col_bar[1]), q);
+    }
+    if (tid == 0) s_timeout = s_range = 0;
+    __syncthreads();
     for (int s = 0; s <= n - 2; s++) {  // step s forms column s + 1
-        const float *X0 = xc0 + (s & 3) * cs;
-        const float *X1 = xc1 + ((s + 3) & 3) * cs;  // column s - 1 (all zero at s = 0)
+        const float4 *X0v = reinterpret_cast<const float4 *>(xc0 + (s & 3) * cs);
+        const float4 *X1v = reinterpret_cast<const float4 *>(xc1 + ((s + 3) & 3) * cs);  // column s - 1 (all zero at s = 0)
         float *D0 = xc0 + ((s + 1) & 3) * cs, *D1 = xc1 + ((s + 1) & 3) * cs;
         const uint32_t bar = dsm_smem_u32(&col_bar[s & 1]);
         if (NC > 1 && tid == 0) bar_expect(bar, 8 * Mb);
-        float4 x0[TR], x1[TR];
+        if (warp < groups) {
+            const float k0 = invs[s + 1], k1 = invs[s];
+            const uint32_t off = 4u * (((s + 1) & 3) * cs);
+            const uint32_t rD0 = rx0 + off, rD1 = rx1 + off, rbar = (s & 1) ? rbar1 : rbar0;
+            for (int g = warp; g < groups; g += kLWarps) {
+                const int r = g * R + sub;
+                const bool live = r < my_rows;
+                const int rr = live ? r : 0;
+                float acc0 = 0.f, acc1 = 0.f;
+                if (g == warp) {
+                    float a[TRIPS], c[TRIPS];
 #pragma unroll
-        for (int i = 0; i < TR; i++) {
-            const int c4 = 4 * lane + 128 * i;
-            x0[i] = x1[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (c4 < cs) {
-                x0[i] = *reinterpret_cast<const float4 *>(X0 + c4);
-                x1[i] = *reinterpret_cast<const float4 *>(X1 + c4);
-            }
-        }
-        const float k0 = invs[s + 1], k1 = invs[s];
-        for (int r = warp; r < my_rows; r += kLWarps) {
-            const int ci = crank + NC * r;
-            const float *p0 = PT0 + (size_t)r * cs, *p1 = PT1 + (size_t)r * cs;
-            float acc0 = 0.f, acc1 = 0.f;
+                    for (int i = 0; i < TRIPS; i++) {
+                        const int c4 = q + G * i;
+                        a[i] = c[i] = 0.f;
+                        if (c4 < cs4) {
+                            a[i] = dot4(rp0[i], X0v[c4]);
+                            c[i] = dot4(rp1[i], X1v[c4]);
+                        }
+                    }
 #pragma unroll
-            for (int i = 0; i < TR; i++) {
-                const int c4 = 4 * lane + 128 * i;
-                if (c4 < cs) {
-                    acc0 += dot4(*reinterpret_cast<const float4 *>(p0 + c4), x0[i]);
-                    acc1 += dot4(*reinterpret_cast<const float4 *>(p1 + c4), x1[i]);
+                    for (int i = 0; i < TRIPS; i++) {
+                        acc0 += a[i];
+                        acc1 += c[i];
+                    }
+                } else {  // further nodes of a long chain: rows from shared memory, parents ai < ci only
+                    const float4 *p0 = PT0v + rr * cs4, *p1 = PT1v + rr * cs4;
+                    const int end4 = min(cs4, (crank + NC * rr + 3) >> 2);
+                    for (int c4 = q; c4 < end4; c4 += G) {
+                        acc0 += dot4(p0[c4], X0v[c4]);
+                        acc1 += dot4(p1[c4], X1v[c4]);
+                    }
+                }
+                float o = fmaf(k1, acc1, acc0);
+#pragma unroll
+                for (int w = G / 2; w > 0; w >>= 1) o += __shfl_xor_sync(0xffffffffu, o, w);
+                // o_{s+1}[c] = rho_s (acc0 + rho_{s-1} acc1).  o u is a posterior (<= 1): as long as o stays inside the
+                // floats, what the inside pass flushed to zero or kept as a denormal costs less than 1e-7 of posterior
+                // per cell.  An o at the edge of the range (or NaN) means the cell's inside value was below ~1e-37
+                // while it still carries mass: the sentence goes to the log-space kernels.  Clamped so that the
+                // products below stay finite until then.
+                o *= k0;
+                if (!(o < 1e37f)) {
+                    o = 1e37f;
+                    if (live) s_range = 1;
+                }
+                if (live) {
+                    const int ci = crank + NC * r;
+                    const float n0 = o * e0[r * W + s + 1], n1 = o * e1[r * W + s + 1];
+                    if (NC > 1) {
+                        if (q < NC) {
+                            dsm_store_async(rD0 + 4u * ci, n0, rbar);
+                            dsm_store_async(rD1 + 4u * ci, n1, rbar);
+                        }
+                    } else if (q == 0) {
+                        D0[ci] = n0;
+                        D1[ci] = n1;
+                    }
+                    if (q == 0) owno[r * W + s + 1] = o;
                 }
             }
-            // o_{s+1}[c] = inv_{s+1} (acc0 + inv_s acc1).  o u is a posterior (<= 1), so o only grows beyond 1e30 on
-            // cells whose inside value is below 1e-30 of its column: clamped (also NaN), so that no infinity enters
-            // the products below; the mass check at the end notices if that ever cost anything
-            float o = warp_sum(fmaf(k1, acc1, acc0)) * k0;
-            o = o < 1e30f ? o : 1e30f;
-            const float n0 = o * e0[(size_t)r * W + s + 1], n1 = o * e1[(size_t)r * W + s + 1];
-            if (NC > 1) {
-                if (lane < NC) {
-                    const uint32_t rb = dsm_map_to_cta(bar, lane);
-                    dsm_store_async(dsm_map_to_cta(dsm_smem_u32(D0 + ci), lane), n0, rb);
-                    dsm_store_async(dsm_map_to_cta(dsm_smem_u32(D1 + ci), lane), n1, rb);
-                }
-            } else if (lane == 0) {
-                D0[ci] = n0;
-                D1[ci] = n1;
-            }
-            if (lane == 0) owno[(size_t)r * W + s + 1] = o;
         }
-        if (NC > 1) arrived = dsm_wait_column(bar, (s >> 1) & 1) && arrived;
-        else __syncthreads();
+        if (NC > 1 && warp == kLWarps - 1 && !dsm_wait_column(bar, (s >> 1) & 1)) s_timeout = 1;
+        __syncthreads();
     }
-    if (!arrived) flag(status, PCFGNAT_STATUS_TIMEOUT);
+    PCFGNAT_STAMP(1, 4)
+    if (s_timeout && tid == 0) flag(status, PCFGNAT_STATUS_TIMEOUT);
+    if ((s_range || s_timeout) && tid == 0) fr[3] = 1.f;  // marked: the log-space kernels recompute the sentence
     if (NC > 1) cluster.sync(); else __syncthreads();  // nobody exits while a peer may still send to it
+    PCFGNAT_STAMP(1, 5)
 
     // ---- o table to global memory (the emission gradients of a node need it from whichever CTA sweeps the cell)
     float *Ob = O + (size_t)b * Mc * W;
@@ -454,52 +698,60 @@ __global__ void __launch_bounds__(kLThreads, 1)
     }
     __syncthreads();
 
-    // ---- links_grad rows of this CTA's nodes: sums over the steps, J children per lane
+    // ---- links_grad rows of this CTA's nodes: sums over the steps.  The y table of the whole chain is staged in
+    // the shared memory the matrices and columns no longer need (the launcher sizes the kernel for it).
     const float *Yb = Y + (size_t)b * W * Mc;
+    float *ys = loop_mem;  // [n - 1][cs]: y_t[c] in row t - 1, over the columns and matrices of the step loop
     float *lgb = lg + (size_t)b * L * 2 * L;
+    for (int i = tid; i < (n - 1) * cs; i += kLThreads) {
+        const int tc = 1 + i / cs, c = i - (tc - 1) * cs;
+        ys[i] = c < Mb ? __ldg(Yb + (size_t)tc * Mc + c) : 0.f;
+    }
+    __syncthreads();
     for (int r = warp; r < my_rows; r += kLWarps) {
         const int ai = crank + NC * r, a = 2 * ai + 1;
-        float acc0[J], acc1[J], y1[J];
-        bool live[J];
-#pragma unroll
-        for (int j = 0; j < J; j++) {
-            const int ci = lane + 32 * j;
-            live[j] = ci > ai && ci < Mb;
-            acc0[j] = acc1[j] = 0.f;
-            y1[j] = live[j] ? __ldg(Yb + (size_t)1 * Mc + ci) : 0.f;
-        }
-        const float *x0r = e0 + (size_t)r * W, *x1r = e1 + (size_t)r * W;
-        for (int t = 0; t <= n - 2; t++) {
-            const float x0 = x0r[t], x1 = x1r[t];
-#pragma unroll
-            for (int j = 0; j < J; j++) {
-                const int ci = lane + 32 * j;
-                const float y2 = (live[j] && t + 2 <= n - 1) ? __ldg(Yb + (size_t)(t + 2) * Mc + ci) : 0.f;
-                acc0[j] = fmaf(x0, y1[j], acc0[j]);
-                acc1[j] = fmaf(x1, y2, acc1[j]);
-                y1[j] = y2;
-            }
-        }
+        const float *x0r = e0 + r * W, *x1r = e1 + r * W;
         float *row = lgb + (size_t)a * 2 * L;
         const float *lrow = lkb + (size_t)a * 2 * L;
+        for (int j0 = 0; j0 * 32 < cs; j0 += kGradChunk) {  // kGradChunk x 32 children per pass over the steps
+            float acc0[kGradChunk], acc1[kGradChunk], l0[kGradChunk], l1[kGradChunk];
 #pragma unroll
-        for (int j = 0; j < J; j++) {
-            const int ci = lane + 32 * j;
-            if (2 * ci < L) {
-                row[2 * ci] = 0.f;
-                row[L + 2 * ci] = 0.f;
-            }
-            if (2 * ci + 1 < L) {
-                float g0 = 0.f, g1 = 0.f;
-                if (live[j]) {
-                    g0 = exp_clean(__ldg(lrow + 2 * ci + 1)) * acc0[j];
-                    if (ai >= 1) g1 = exp_clean(__ldg(lrow + L + 2 * ci + 1)) * acc1[j];
+            for (int j = 0; j < kGradChunk; j++) {  // the links of these pairs, on their way while the sums run
+                const int ci = lane + 32 * (j0 + j);
+                acc0[j] = acc1[j] = 0.f;
+                l0[j] = l1[j] = neg_inf();
+                if (ci > ai && ci < Mb) {
+                    l0[j] = __ldg(lrow + 2 * ci + 1);
+                    if (ai >= 1) l1[j] = __ldg(lrow + L + 2 * ci + 1);
                 }
-                row[2 * ci + 1] = g0;
-                row[L + 2 * ci + 1] = g1;
+            }
+            if ((j0 + kGradChunk) * 32 > ai + 1) {  // else: all of these children are at or below the node itself
+                // column tc of y meets x0 of step tc - 1 and x1 of step tc - 2: one load per column and child
+                for (int tc = 1; tc <= n - 1; tc++) {
+                    const float xa = x0r[tc - 1], xb = tc >= 2 ? x1r[tc - 2] : 0.f;
+                    const float *ycol = ys + (tc - 1) * cs + 32 * j0 + lane;
+#pragma unroll
+                    for (int j = 0; j < kGradChunk; j++) {
+                        const float y = 32 * (j0 + j) + lane < cs ? ycol[32 * j] : 0.f;
+                        acc0[j] = fmaf(xa, y, acc0[j]);
+                        acc1[j] = fmaf(xb, y, acc1[j]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < kGradChunk; j++) {
+                const int ci = lane + 32 * (j0 + j);
+                if (2 * ci < L) {
+                    row[2 * ci] = 0.f;
+                    row[L + 2 * ci] = 0.f;
+                }
+                if (2 * ci + 1 < L) {
+                    row[2 * ci + 1] = exp_clean(l0[j]) * acc0[j];  // exp(-inf) = 0 where there is no pair
+                    row[L + 2 * ci + 1] = exp_clean(l1[j]) * acc1[j];
+                }
             }
         }
-        for (int c = 64 * J + lane; c < L; c += 32) {  // columns beyond the main chain's reach (never with L <= 64 J)
+        for (int c = 2 * ((cs + 31) / 32 * 32) + lane; c < L; c += 32) {  // an odd last column beyond the chain
             row[c] = 0.f;
             row[L + c] = 0.f;
         }
@@ -512,7 +764,9 @@ __global__ void __launch_bounds__(kLThreads, 1)
     }
 
     // ---- emission gradients, pass 1: every cell times the o of its main-chain node (cells without a share: 0)
+    PCFGNAT_STAMP(1, 6)
     if (NC > 1) cluster.sync(); else __syncthreads();  // the o table is complete
+    PCFGNAT_STAMP(1, 7)
     float *mgb = mg + (size_t)b * L * T;
     for (int i = ctid; i < L * T; i += cthreads) {
         const int node = i / T, t = i - node * T;
@@ -532,7 +786,7 @@ __global__ void __launch_bounds__(kLThreads, 1)
         if (node >= m || t >= n) continue;
         float v = mgb[i];
         if ((node & 1) && node >= 3 && t >= 1) v += mgb[(size_t)(node - 1) * T + t - 1];
-        if (node == m - 1 && t == n - 1) v += Ob[(size_t)last * W + n - 1] * (invs[n - 1] > 0.f ? __frcp_rn(invs[n - 1]) : 0.f);
+        if (node == m - 1 && t == n - 1) v += Ob[(size_t)last * W + n - 1] * e_term;  // o u of the terminal cell
         if ((node & 1) && t >= 1) mgb[i] = v;
         mass += v;
     }
@@ -544,6 +798,8 @@ __global__ void __launch_bounds__(kLThreads, 1)
         for (int i = 0; i < kLWarps; i++) tot += red[i];
         atomicAdd(fr + 2, tot);
     }
+    PCFGNAT_STAMP(1, 10)
+    PCFGNAT_ACC(1, 9, NC)
 }
 
 struct LinearGeometry {
@@ -570,7 +826,9 @@ LinearGeometry linear_geometry(int B, int Mc, int W) {
         g.rows_cap = (Mc + nc - 1) / nc;
         const size_t mat = (size_t)2 * g.rows_cap * g.cs, own = (size_t)g.rows_cap * W;
         g.smem_in = ((size_t)4 * g.cs + mat + 5 * own + W) * sizeof(float);
-        g.smem_out = ((size_t)8 * g.cs + mat + 3 * own + W) * sizeof(float);
+        // the step loop's columns, matrices and o table, later overlaid by the y table of the gradient sums
+        const size_t loop_mem = (size_t)8 * g.cs + mat + own, y_table = (size_t)W * g.cs;
+        g.smem_out = ((size_t)linear_outside_head(g.rows_cap, W) + (loop_mem > y_table ? loop_mem : y_table)) * sizeof(float);
         if (g.smem_in <= (size_t)kSmemLimit - 1024 && g.smem_out <= (size_t)kSmemLimit - 1024) break;
         if (nc >= 16) {
             g.nc = 0;
@@ -609,17 +867,16 @@ int launch_linear_cluster(Kernel kernel, int B, int nc, size_t smem, cudaStream_
     return cuda_rc(cudaLaunchKernelEx(&cfg, kernel, args...));
 }
 
-template <int TR>
-int launch_linear(const float *match_all, const float *links, const int64_t *ol, const int64_t *tl, int B, int L, int T,
-                  float *Y, float *O, float *frames, float *loss, float *mg, float *lg, int *status, cudaStream_t st) {
+template <int G, int TRIPS>
+int launch_linear(const LinearGeometry &g, const float *match_all, const float *links, const int64_t *ol, const int64_t *tl,
+                  int B, int L, int T, float *Y, float *O, float *frames, float *loss, float *mg, float *lg, int *status,
+                  cudaStream_t st) {
     const int Mc = main_slots(L, 1);
-    const LinearGeometry g = linear_geometry(B, Mc, T + 2);
-    if (g.nc == 0) return PCFGNAT_ERR_UNSUPPORTED;
     const int nc = g.wide >= 0 ? 2 : g.nc;  // mixed widths: clusters of two of which only the costliest use both CTAs
-    int rc = launch_linear_cluster(inside_linear_kernel<TR>, B, nc, g.smem_in, st, match_all, links, ol, tl, L, T, Y, frames,
-                                   loss, mg, status, Mc, g.cs, g.rows_cap, B, g.wide);
+    int rc = launch_linear_cluster(inside_linear_kernel<G, TRIPS>, B, nc, g.smem_in, st, match_all, links, ol, tl, L, T, Y,
+                                   frames, loss, mg, status, Mc, g.cs, g.rows_cap, B, g.wide);
     if (rc) return rc;
-    return launch_linear_cluster(outside_linear_kernel<TR>, B, nc, g.smem_out, st, match_all, links, ol, tl, L, T,
+    return launch_linear_cluster(outside_linear_kernel<G, TRIPS>, B, nc, g.smem_out, st, match_all, links, ol, tl, L, T,
                                  (const float *)Y, O, frames, mg, lg, status, Mc, g.cs, g.rows_cap, B, g.wide);
 }
 
@@ -645,9 +902,20 @@ int launch_loss_linear(const float *match_all, const float *links, const int64_t
                        int T, float *Y, float *O, float *frames, float *loss, float *mg, float *lg, int *status,
                        cudaStream_t st) {
     const int Mc = main_slots(L, 1);
-    if (Mc <= 128) return launch_linear<1>(match_all, links, ol, tl, B, L, T, Y, O, frames, loss, mg, lg, status, st);
-    if (Mc <= 256) return launch_linear<2>(match_all, links, ol, tl, B, L, T, Y, O, frames, loss, mg, lg, status, st);
-    return PCFGNAT_ERR_UNSUPPORTED;
+    if (Mc > 256) return PCFGNAT_ERR_UNSUPPORTED;
+    const LinearGeometry g = linear_geometry(B, Mc, T + 2);
+    if (g.nc == 0) return PCFGNAT_ERR_UNSUPPORTED;
+    // lanes per node and float4 per lane so that a node's row of g.cs / 4 groups of four children fits the lanes' registers
+    const int cs4 = g.cs / 4;
+#define PCFGNAT_LINEAR_CASE(G_, TRIPS_) \
+    return launch_linear<G_, TRIPS_>(g, match_all, links, ol, tl, B, L, T, Y, O, frames, loss, mg, lg, status, st)
+    if (cs4 <= 8) PCFGNAT_LINEAR_CASE(8, 1);
+    if (cs4 <= 16) PCFGNAT_LINEAR_CASE(8, 2);
+    if (cs4 <= 24) PCFGNAT_LINEAR_CASE(8, 3);
+    if (cs4 <= 32) PCFGNAT_LINEAR_CASE(8, 4);
+    if (cs4 <= 48) PCFGNAT_LINEAR_CASE(16, 3);
+    PCFGNAT_LINEAR_CASE(16, 4);
+#undef PCFGNAT_LINEAR_CASE
 }
 
 }  // namespace pcfgnat

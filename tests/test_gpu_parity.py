@@ -1046,7 +1046,10 @@ def test_linear_space_loss_against_oracle_peaked_inputs(ops, syn, monkeypatch, p
     ol, tl = b.output_length.numpy(), b.target_length.numpy()
     So, Co = oracle.pcfg_loss(ma.numpy(), lk.numpy(), ol, tl)
     mgo, lgo = oracle.pcfg_loss_backward(np.ones(b.B, np.float32), So, Co, ma.numpy(), lk.numpy(), ol, tl)
+    ops.read_status(DEV)
     loss, mg, lg = _fused(ops, ma.to(DEV), lk.to(DEV), b.output_length.to(DEV), b.target_length.to(DEV))
+    recomputed = bool(ops.read_status(DEV) & 16)  # PCFGNAT_STATUS_RECOMPUTED
+    assert peak > 1.0 or not recomputed  # ordinary inputs stay in linear space
     assert np.isfinite(So[:, 0, 0]).all()
     np.testing.assert_allclose(loss.cpu().numpy(), So[:, 0, 0], rtol=1e-4)
     np.testing.assert_allclose(mg.cpu().numpy(), mgo, rtol=1e-3, atol=2e-6)
@@ -1060,8 +1063,8 @@ def test_linear_space_loss_against_oracle_peaked_inputs(ops, syn, monkeypatch, p
 
 
 def test_linear_space_loss_hands_unusual_sentences_to_the_log_space_kernels(ops, syn, monkeypatch):
-    """One batch with everything the linear-space kernels do not take themselves: an emission far above the range of
-    exp(), an out-of-range length, an odd graph length, a single target token, an infeasible sentence (more tokens
+    """One batch with everything the linear-space kernels do not take themselves: an emission far beyond the range of
+    exp() relative to its token's maximum, an out-of-range length, an odd graph length, a single target token, an infeasible sentence (more tokens
     than the graph can emit), next to ordinary sentences.  Every sentence must come out as the log-space kernels
     alone give it, and output buffers that were dirty must be fully overwritten."""
     monkeypatch.delenv("PCFGNAT_DP_KERNEL", raising=False)
@@ -1069,7 +1072,7 @@ def test_linear_space_loss_hands_unusual_sentences_to_the_log_space_kernels(ops,
     b = syn.make_batch(w, seed=32)
     ma = syn.reference_match_all(b)
     ol, tl = b.output_length.clone(), b.target_length.clone()
-    ma[0, 1, 0] = 200.0           # exp() overflows
+    ma[0, 2, 0] = 200.0           # a leaf emission far above the main chain's: exp() overflows
     ol[1] = b.L + 4               # out of range
     ol[2] = ol[2] - 1             # odd graph length
     tl[3] = 1                     # one target token
@@ -1078,7 +1081,8 @@ def test_linear_space_loss_hands_unusual_sentences_to_the_log_space_kernels(ops,
     args = (ma.to(DEV), b.links.to(DEV), ol.to(DEV), tl.to(DEV))
     ops.read_status(DEV)
     loss, mg, lg = _fused(ops, *args)
-    assert ops.read_status(DEV) & 1
+    st = ops.read_status(DEV)
+    assert st & 1 and st & 16  # a bad length was seen; sentences were recomputed in log space
     monkeypatch.setenv("PCFGNAT_DP_KERNEL", "rows")  # the kernels that pick up the marked sentences, on their own
     loss2, mg2, lg2 = _fused(ops, *args)
     ops.read_status(DEV)
