@@ -48,6 +48,7 @@ class _GraphedStep:
         self.kernel = ops.get_pcfg_kernel()
         self.copy_stream = None
         self._ev_stage1 = self._ev_stage2 = self._ev_done = None
+        self._ev_ran = None  # end of this object's last run(): the point after which its input buffers are free
         self._pending = False
         # sentence groups [b0, b1) of an overlapped load; chunking needs the graphs (it is a replay trick)
         n = max(1, min(int(copy_chunks), B)) if use_graph else 1
@@ -79,7 +80,7 @@ class _GraphedStep:
 
         overlap=False: asynchronous copies on the current stream.  overlap=True: on the step's copy stream,
         first-stage inputs first; the next ``run`` orders each stage after the arrival of its own inputs and
-        the copies after the previous ``run`` (which still reads the buffers)."""
+        the copies after this object's previous ``run`` (which still reads the buffers)."""
         bufs = self._inputs()
         if len(tensors) != len(bufs):
             raise RuntimeError(f"expected {len(bufs)} tensors")
@@ -91,11 +92,15 @@ class _GraphedStep:
             self.copy_stream = torch.cuda.Stream(self.device)
             self._ev_stage1, self._ev_stage2, self._ev_done = (torch.cuda.Event() for _ in range(3))
             self._ev_chunk = [torch.cuda.Event() for _ in self.chunks]
-        cur = torch.cuda.current_stream(self.device)
-        self._ev_done.record(cur)  # everything queued so far, the previous run included
         late = {id(t) for t in self._stage2_inputs()}
         with torch.cuda.stream(self.copy_stream):
-            self.copy_stream.wait_event(self._ev_done)
+            # the buffers are free once this object's own last run has read them; work queued since then on the
+            # current stream (another step object's run, say) does not hold the copies back
+            if self._ev_ran is not None:
+                self.copy_stream.wait_event(self._ev_ran)
+            else:  # never run yet: after whatever initialised the buffers on the current stream
+                self._ev_done.record(torch.cuda.current_stream(self.device))
+                self.copy_stream.wait_event(self._ev_done)
             for dst, src in zip(bufs, tensors):  # the small inputs first, then the states group by group
                 if id(dst) not in late and dst is not self.hidden:
                     self._copy_in(dst, src)
@@ -170,7 +175,36 @@ class _GraphedStep:
             self.graphs[1].replay()
         else:
             self.out = self._stage2(self.mid)
+        if self._ev_ran is None:
+            self._ev_ran = torch.cuda.Event()
+        self._ev_ran.record(cur)
         return self.out
+
+
+class PipelinedStep:
+    """Two step objects of the same shape used in turn, so that the host-to-device copies of batch i + 1 run while
+    batch i is computed (each object has its own static buffers and graphs): ``load`` always goes over the copy
+    stream of the object whose turn it is and waits only for that object's previous run, two batches back.
+    ``run`` returns that object's static outputs, which stay valid until the run after next."""
+
+    def __init__(self, make_step):
+        self.steps = [make_step(), make_step()]
+        self.turn = 0
+
+    def load(self, *tensors):
+        self.steps[self.turn].load(*tensors, overlap=True)
+
+    def run(self):
+        out = self.steps[self.turn].run()
+        self.turn ^= 1
+        return out
+
+    def input_bytes(self):
+        return self.steps[0].input_bytes()
+
+    @property
+    def kernels_per_step(self):
+        return self.steps[0].kernels_per_step
 
 
 class LossStep(_GraphedStep):

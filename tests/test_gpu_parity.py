@@ -1094,3 +1094,33 @@ def test_linear_space_loss_hands_unusual_sentences_to_the_log_space_kernels(ops,
     torch.testing.assert_close(lg, lg2, rtol=1e-3, atol=2e-6, equal_nan=True)
     for i in (0, 1, 2, 3, 4):  # handed over: bit for bit what the log-space kernels give
         assert torch.equal(mg[i].nan_to_num(7.0), mg2[i].nan_to_num(7.0)) and torch.equal(lg[i].nan_to_num(7.0), lg2[i].nan_to_num(7.0))
+
+
+def test_pipelined_steps_overlap_copies_without_mixing_batches(pkg, ops, syn):
+    """Two step objects in turn (copies of the next batch while the current one is computed): different batches
+    through the pipeline come out exactly as through a single step object, in order."""
+    import importlib
+
+    runtime = importlib.import_module("pcfg_nat_b200.runtime")
+    w = syn.Workload("pipe", batch=6, vocab=3000, hidden=128, fixed_graph=40, fixed_target=9, hidden_std=1.0)
+    batches = [syn.make_batch(w, seed=40 + i) for i in range(5)]
+    weight = batches[0].weight.to(DEV)
+    B, L, T = batches[0].B, batches[0].L, batches[0].T
+    host = [[t.contiguous().pin_memory() for t in (b.hidden, b.links, b.output_length, b.targets, b.target_length)]
+            for b in batches]
+    single = runtime.LossStep(weight, B, L, T, DEV)
+    want = []
+    for h in host:
+        single.load(*h)
+        want.append([t.clone() for t in single.run()])
+    pipe = runtime.PipelinedStep(lambda: runtime.LossStep(weight, B, L, T, DEV))
+    got = []
+    for h in host:
+        pipe.load(*h)
+        out = pipe.run()
+        got.append([t.clone() for t in out])  # cloned on the run's stream, before the run after next reuses the buffers
+    torch.cuda.synchronize()
+    for a, b in zip(got, want):
+        for x, y in zip(a, b):
+            assert torch.equal(x, y)
+    assert not torch.equal(want[0][3], want[1][3])
