@@ -141,6 +141,22 @@ int pcfgnat_viterbi_decode(const float *S, const float *penalty, const int64_t *
                            int mask_dim, int64_t pad_index, int B, int L, int Q, int cap, int64_t *pred_length,
                            int64_t *out_tokens, int64_t *out_count, int *status, void *stream);
 
+/* Lookahead / greedy decoding on the device, one launch.  Replaces the decode strategies "lookahead" and "greedy"
+ * of the model (fs_plugins/models/glat_decomposed_with_link_two_hands_tri_pcfg.py:419-482): the arg-max over
+ * (left option, right child) per node of
+ *     lookahead != 0:  (links[a][k][c] + ob_lprob[c] * beta) + ob_lprob[left(a, k)] * beta
+ *     lookahead == 0:   links[a][k][c]                                  (ob_lprob may be NULL)
+ * (first maximum in the order k * L + c), then the reference's in-order walk from node 1 — which it does on the host
+ * over links_idx.cpu().tolist() — emitting every visited node's token unless it is pad_index.
+ * links [B][L][2][L] f32, ob_lprob [B][L] f32 (max log-prob per node), tokens [B][L] int64, left_tree_mask as for
+ * pcfgnat_viterbi_backtrace.  Writes out_tokens [B][cap] int64 (pad_index beyond the sentence) and out_count [B].
+ * The reference takes the left-child lookahead term of every sentence from sentence 0 when B > 1
+ * (models/...pcfg.py:425); here every sentence uses its own (equal for B == 1, the setting it is published with). */
+int pcfgnat_lookahead_decode(const float *links, const float *ob_lprob, const int64_t *tokens,
+                             const int64_t *output_length, const int64_t *left_tree_mask, int mask_dim, float beta,
+                             int lookahead, int64_t pad_index, int B, int L, int max_left, int cap, int64_t *out_tokens,
+                             int64_t *out_count, int *status, void *stream);
+
 /* log-softmax over the vocabulary + gather of selected columns, optional in-place
  * softmax for the backward.  Replaces logsoftmax_gather()
  * (fs_plugins/custom_ops/logsoftmax_gather.cu:295-359, kernel :240-292).
@@ -254,14 +270,15 @@ int pcfgnat_force_emit(const float *match, const uint8_t *matchmask, const uint8
 int pcfgnat_force_emit_grad(const float *grad, const uint8_t *keep, int B, int L, int T, float *out, void *stream);
 
 /* The transition log-probabilities links [B][L][2][L] f32 from the projected link features: extract_links()
- * after its link projections (fs_plugins/models/glat_decomposed_with_link_two_hands_tri_pcfg.py:163-199) as two
- * launches around two library batched GEMMs.  Only main-chain nodes have, or are, right children, so everything is
+ * after its link projections (fs_plugins/models/glat_decomposed_with_link_two_hands_tri_pcfg.py:163-199) as
+ * three launches.  Only main-chain nodes have, or are, right children, so everything is
  * compact over the M main-chain nodes: nodes [M] int32 = their ids (ascending), slot_of [L] int32 = index of a
  * node among them or -1.
  *  1. pcfgnat_links_gather_features: q, kl, kr [B][L][heads][head_dim] (dtype PCFGNAT_DTYPE_F16 or PCFGNAT_DTYPE_F32) ->
  *     float32 GEMM operands qm = q[nodes], krm = kr[nodes] ([B][heads][M][head_dim]) and klm
  *     ([B][heads][M+1][head_dim]: row 0 = kl[0], "no left child"; row 1 + s = kl[nodes[s] - 1]);
- *  2. (caller, library GEMMs) ac [B][heads][M][M] = qm krm^T, bc [B][heads][M+1][M] = klm krm^T, unscaled;
+ *  2. pcfgnat_links_scores: ac [B][heads][M][M] = qm krm^T, bc [B][heads][M+1][M] = klm krm^T, unscaled (small
+ *     batched float32 products);
  *  3. pcfgnat_links_from_scores: masking of inadmissible children, the two left options (none, node a-1), the
  *     joint log-softmax over (left option, right child) per head with scores scaled by 1/sqrt(head_dim), the
  *     log-sum-exp mixture of the heads with log-softmax(gate_logits [B][L][heads]), -inf rows for nodes without an
@@ -269,6 +286,20 @@ int pcfgnat_force_emit_grad(const float *grad, const uint8_t *keep, int B, int L
  *     (1 = not allowed) and main_chain [L] u8 as lemon_tree.get_mask gives them. */
 int pcfgnat_links_gather_features(const void *q, const void *kl, const void *kr, int dtype, const int *nodes, int M,
                                   int B, int L, int heads, int head_dim, float *qm, float *klm, float *krm, void *stream);
+int pcfgnat_links_scores(const float *qm, const float *klm, const float *krm, int M, int B, int heads, int head_dim,
+                         float *ac, float *bc, void *stream);
+/* Gradient of those links with respect to the link features and the gate logits (training; the reference gets it
+ * from autograd through the ~30 operators of extract_links).  links_grad [B][L][2][L] f32; ac, bc, qm, klm, krm and
+ * the masks as in the forward.  Scratch: X0, X1 [B][heads][M][M] and dab [B][heads][M][2] f32 (fully overwritten at
+ * the rows of main-chain nodes; the caller zero-fills them once for the others).  Outputs, all f32: dq, dkl, dkr
+ * [B][L][heads][head_dim] (zero-filled by the caller: only main-chain nodes and their left options are written)
+ * and dgates [B][L][heads] (every cell written). */
+int pcfgnat_links_backward(const float *links_grad, const float *ac, const float *bc, const float *qm, const float *klm,
+                           const float *krm, const float *gate_logits, const uint8_t *nonpad,
+                           const uint8_t *left_tree_mask, const uint8_t *right_tree_mask, const uint8_t *main_chain,
+                           const int *slot_of, const int *nodes, int M, int B, int L, int heads, int head_dim, int max_left,
+                           float *X0, float *X1, float *dab, float *dq, float *dkl, float *dkr, float *dgates,
+                           void *stream);
 int pcfgnat_links_from_scores(const float *ac, const float *bc, const float *qm, const float *klm,
                               const float *gate_logits, const uint8_t *nonpad, const uint8_t *left_tree_mask,
                               const uint8_t *right_tree_mask, const uint8_t *main_chain, const int *slot_of,

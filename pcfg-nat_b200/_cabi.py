@@ -23,11 +23,14 @@ SIGNATURES = {
     "pcfgnat_viterbi": (c_int, [c_void] * 3 + [c_int] * 3 + [c_void] * 6),
     "pcfgnat_viterbi_backtrace": (c_int, [c_void] * 7 + [c_int, c_i64] + [c_int] * 4 + [c_void] * 4),
     "pcfgnat_viterbi_decode": (c_int, [c_void] * 8 + [c_int, c_i64] + [c_int] * 4 + [c_void] * 5),
+    "pcfgnat_lookahead_decode": (c_int, [c_void] * 5 + [c_int, ctypes.c_float, c_int, c_i64] + [c_int] * 4 + [c_void] * 4),
     "pcfgnat_logsoftmax_gather": (c_int, [c_void, c_int, c_void] + [c_i64] * 5 + [c_int] * 3 + [c_void] * 3),
     "pcfgnat_proj_workspace_bytes": (c_size, [c_int] * 4),
     "pcfgnat_proj_logsoftmax_gather": (c_int, [c_void] * 5 + [c_int] * 5 + [c_void] * 5 + [c_size] + [c_void] * 2),
     "pcfgnat_proj_dlogits": (c_int, [c_void] * 7 + [c_int] * 5 + [c_void] * 2 + [c_size] + [c_void] * 2),
     "pcfgnat_links_gather_features": (c_int, [c_void] * 3 + [c_int] + [c_void] + [c_int] * 5 + [c_void] * 4),
+    "pcfgnat_links_scores": (c_int, [c_void] * 3 + [c_int] * 4 + [c_void] * 3),
+    "pcfgnat_links_backward": (c_int, [c_void] * 13 + [c_int] * 6 + [c_void] * 8),
     "pcfgnat_links_from_scores": (c_int, [c_void] * 11 + [c_int] * 6 + [c_void] * 2),
     "pcfgnat_copy_links_main_rows": (c_int, [c_void] * 2 + [c_int] * 3 + [c_void]),
     "pcfgnat_loss_stats": (c_int, [c_void] * 2 + [c_int] + [c_void] * 2),

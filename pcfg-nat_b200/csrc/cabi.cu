@@ -219,6 +219,19 @@ int pcfgnat_viterbi_decode(const float *S, const float *penalty, const int64_t *
                                  Q, cap, pred_length, out_tokens, out_count, status, static_cast<cudaStream_t>(stream));
 }
 
+int pcfgnat_lookahead_decode(const float *links, const float *ob_lprob, const int64_t *tokens,
+                             const int64_t *output_length, const int64_t *left_tree_mask, int mask_dim, float beta,
+                             int lookahead, int64_t pad_index, int B, int L, int max_left, int cap, int64_t *out_tokens,
+                             int64_t *out_count, int *status, void *stream) {
+    if (max_left != 1) return PCFGNAT_ERR_UNSUPPORTED;
+    if (B < 0 || L < 2 || cap < 0 || mask_dim < 1) return PCFGNAT_ERR_INVALID_ARGUMENT;
+    if (B && (!links || !tokens || !output_length || !left_tree_mask || !out_count || (cap && !out_tokens) ||
+              (lookahead && !ob_lprob)))
+        return PCFGNAT_ERR_INVALID_ARGUMENT;
+    return launch_lookahead_decode(links, ob_lprob, tokens, output_length, left_tree_mask, mask_dim, beta, lookahead != 0,
+                                   pad_index, B, L, cap, out_tokens, out_count, status, static_cast<cudaStream_t>(stream));
+}
+
 int pcfgnat_logsoftmax_gather(void *logits, int dtype, const int64_t *select_idx, int64_t stride_b, int64_t stride_l,
                               int64_t stride_s, int64_t rows, int64_t rows_per_batch, int V, int slen,
                               int require_gradient, float *selected, int *status, void *stream) {
@@ -329,6 +342,29 @@ int pcfgnat_links_gather_features(const void *q, const void *kl, const void *kr,
     if (B && (!q || !kl || !kr || !nodes || !qm || !klm || !krm)) return PCFGNAT_ERR_INVALID_ARGUMENT;
     return launch_links_gather(q, kl, kr, dtype == PCFGNAT_DTYPE_F16, nodes, M, B, L, heads, head_dim, qm, klm, krm,
                                static_cast<cudaStream_t>(stream));
+}
+
+int pcfgnat_links_scores(const float *qm, const float *klm, const float *krm, int M, int B, int heads, int head_dim,
+                         float *ac, float *bc, void *stream) {
+    if (B < 0 || M < 0 || heads < 1 || head_dim < 1) return PCFGNAT_ERR_INVALID_ARGUMENT;
+    if (B && M && (!qm || !klm || !krm || !ac || !bc)) return PCFGNAT_ERR_INVALID_ARGUMENT;
+    return launch_links_scores(qm, klm, krm, M, B, heads, head_dim, ac, bc, static_cast<cudaStream_t>(stream));
+}
+
+int pcfgnat_links_backward(const float *links_grad, const float *ac, const float *bc, const float *qm, const float *klm,
+                           const float *krm, const float *gate_logits, const uint8_t *nonpad,
+                           const uint8_t *left_tree_mask, const uint8_t *right_tree_mask, const uint8_t *main_chain,
+                           const int *slot_of, const int *nodes, int M, int B, int L, int heads, int head_dim, int max_left,
+                           float *X0, float *X1, float *dab, float *dq, float *dkl, float *dkr, float *dgates,
+                           void *stream) {
+    if (max_left != 1) return PCFGNAT_ERR_UNSUPPORTED;
+    if (B < 0 || L < 1 || M < 0 || M > L || heads < 1 || head_dim < 1) return PCFGNAT_ERR_INVALID_ARGUMENT;
+    if (B && (!links_grad || !ac || !bc || !qm || !klm || !krm || !gate_logits || !nonpad || !left_tree_mask ||
+              !right_tree_mask || !main_chain || !slot_of || !nodes || !X0 || !X1 || !dab || !dq || !dkl || !dkr || !dgates))
+        return PCFGNAT_ERR_INVALID_ARGUMENT;
+    return launch_links_backward(links_grad, ac, bc, qm, klm, krm, gate_logits, nonpad, left_tree_mask, right_tree_mask,
+                                 main_chain, slot_of, nodes, M, B, L, heads, head_dim, X0, X1, dab, dq, dkl, dkr, dgates,
+                                 static_cast<cudaStream_t>(stream));
 }
 
 int pcfgnat_links_from_scores(const float *ac, const float *bc, const float *qm, const float *klm,

@@ -103,6 +103,9 @@ int launch_viterbi_decode(const float *S, const float *penalty, const int64_t *o
                           const int64_t *Mt, const int64_t *tokens, const int64_t *mask, int mask_dim, int64_t pad, int B,
                           int L, int Q, int cap, int64_t *pred_out, int64_t *out, int64_t *cnt, int *status,
                           cudaStream_t st);
+int launch_lookahead_decode(const float *links, const float *ob, const int64_t *tokens, const int64_t *ol,
+                            const int64_t *mask, int mask_dim, float beta, int lookahead, int64_t pad, int B, int L,
+                            int cap, int64_t *out, int64_t *cnt, int *status, cudaStream_t st);
 int launch_logsoftmax_gather(void *logits, int dtype, const int64_t *sel, int64_t sb, int64_t sl, int64_t ss,
                              int64_t rows, int64_t rpb, int V, int slen, int req_grad, float *selected, int *status,
                              cudaStream_t st);
@@ -178,6 +181,13 @@ int launch_proj(const void *hidden, const void *weight, const int64_t *targets, 
 
 int launch_links_gather(const void *q, const void *kl, const void *kr, int is_half, const int *nodes, int M, int B, int L,
                         int H, int D, float *qm, float *klm, float *krm, cudaStream_t st);
+int launch_links_scores(const float *qm, const float *klm, const float *krm, int M, int B, int H, int D, float *ac,
+                        float *bc, cudaStream_t st);
+int launch_links_backward(const float *links_grad, const float *ac, const float *bc, const float *qm, const float *klm,
+                          const float *krm, const float *gates, const uint8_t *nonpad, const uint8_t *left_mask,
+                          const uint8_t *right_mask, const uint8_t *main_chain, const int *slot_of, const int *nodes, int M,
+                          int B, int L, int H, int D, float *X0, float *X1, float *dab, float *dq, float *dkl, float *dkr,
+                          float *dgates, cudaStream_t st);
 int launch_links_from_scores(const float *ac, const float *bc, const float *qm, const float *klm, const float *gates,
                              const uint8_t *nonpad, const uint8_t *left_mask, const uint8_t *right_mask,
                              const uint8_t *main_chain, const int *slot_of, const int *nodes, int M, int B, int L, int H,

@@ -410,6 +410,39 @@ class _Kernel:
         return out, cnt, pred
 
     @staticmethod
+    def lookahead_decode_device(links, ob_lprob, unreduced_tokens, output_length, left_tree_mask, pad_index,
+                                decode_beta=1.0, strategy="lookahead"):
+        """The model's "lookahead" / "greedy" decoding (models/...pcfg.py:419-482) in one launch: per-node arg-max of
+        the (lookahead-adjusted) transitions and the in-order walk from node 1.  Returns (tokens [B, L] int64 padded
+        with pad_index, count [B] int64), no host sync.  Every sentence uses its own log-probabilities for the
+        left-child term (the reference uses sentence 0's for all when B > 1, :425)."""
+        _require_cuda()
+        if strategy not in ("lookahead", "greedy"):
+            raise RuntimeError(f"unknown decode strategy {strategy!r}")
+        lk = _f32_cuda(links, "links", 4)
+        B, L = lk.shape[0], lk.shape[1]
+        if lk.shape[2] != 2 or lk.shape[3] != L:
+            raise RuntimeError("links must be [batch, prelen, 2, prelen] (max_left == 1)")
+        dev = lk.device
+        i64 = lambda t: t.to(device=dev, dtype=torch.int64).contiguous()
+        ob = _f32_cuda(ob_lprob, "ob_lprob", 2) if strategy == "lookahead" else None
+        if ob is not None and (tuple(ob.shape) != (B, L) or ob.device != dev):
+            raise RuntimeError("ob_lprob must be [batch, prelen] on the device of links")
+        tk, ol, mk = i64(unreduced_tokens), i64(output_length), i64(left_tree_mask)
+        if tuple(tk.shape) != (B, L) or tuple(ol.shape) != (B,) or mk.dim() != 2 or mk.shape[0] != mk.shape[1]:
+            raise RuntimeError("unreduced_tokens [batch, prelen], output_length [batch], square left_tree_mask expected")
+        with torch.cuda.device(dev):
+            out = torch.empty((B, L), dtype=torch.int64, device=dev)
+            cnt = torch.empty((B,), dtype=torch.int64, device=dev)
+            rc = _cabi.lib().pcfgnat_lookahead_decode(lk.data_ptr(), ob.data_ptr() if ob is not None else None,
+                                                      tk.data_ptr(), ol.data_ptr(), mk.data_ptr(), mk.shape[0],
+                                                      float(decode_beta), 1 if strategy == "lookahead" else 0,
+                                                      int(pad_index), B, L, 1, L, out.data_ptr(), cnt.data_ptr(),
+                                                      _status_ptr(dev), _stream(dev))
+        _cabi.check(rc, "pcfgnat_lookahead_decode")
+        return out, cnt
+
+    @staticmethod
     def viterbi_decoding(pred_length, output_length, L_trace, R_trace, M_trace, unreduced_tokens, left_tree_mask,
                          pad_index):
         """float32 [B, maxlen] padded with pad_index on the device of ``pred_length``;
@@ -438,13 +471,9 @@ class _Kernel:
         _cabi.check(rc, "pcfgnat_copy_links_main_rows")
 
     @staticmethod
-    def extract_links(query, key_left, key_right, gate_logits, prev_output_tokens, pad_index, left_tree_mask,
-                      right_tree_mask, main_chain):
-        """links [B, L, 2, L] f32 as the model's extract_links() forms them from the projected link features
-        (models/...pcfg.py:140-201, max_left == 1): ``query``, ``key_left``, ``key_right`` [B, L, heads, head_dim]
-        (outputs of the three link projections, reshaped), ``gate_logits`` [B, L, heads].  Two library batched
-        GEMMs give the per-head score matrices; one launch does masking, gather, joint log-softmax, head mixture
-        and the -inf rows.  No gradient (decoding / inference)."""
+    def _links_forward(query, key_left, key_right, gate_logits, prev_output_tokens, pad_index, left_tree_mask,
+                       right_tree_mask, main_chain):
+        """Forward of ``extract_links``; returns (links, everything the backward needs)."""
         _require_cuda()
         if query.dim() != 4 or key_left.shape != query.shape or key_right.shape != query.shape:
             raise RuntimeError("query, key_left, key_right must be [batch, prelen, heads, head_dim] and agree")
@@ -453,10 +482,10 @@ class _Kernel:
         B, L, H, D = query.shape
         dev = query.device
         dt = query.dtype if query.dtype in (torch.float16, torch.float32) else torch.float32
-        q = query.to(dt).contiguous()
-        kl = key_left.to(device=dev, dtype=dt).contiguous()
-        kr = key_right.to(device=dev, dtype=dt).contiguous()
-        gates = gate_logits.to(device=dev, dtype=torch.float32).contiguous()
+        q = query.detach().to(dt).contiguous()
+        kl = key_left.detach().to(device=dev, dtype=dt).contiguous()
+        kr = key_right.detach().to(device=dev, dtype=dt).contiguous()
+        gates = gate_logits.detach().to(device=dev, dtype=torch.float32).contiguous()
         if tuple(gates.shape) != (B, L, H):
             raise RuntimeError("gate_logits must be [batch, prelen, heads]")
         if tuple(prev_output_tokens.shape) != (B, L):
@@ -494,16 +523,59 @@ class _Kernel:
                                                    1 if dt == torch.float16 else 0, nodes.data_ptr(), M, B,  # PCFGNAT_DTYPE_*
                                                    L, H, D, qm.data_ptr(), klm.data_ptr(), krm.data_ptr(), _stream(dev))
             _cabi.check(rc, "pcfgnat_links_gather_features")
-            krt = krm.transpose(-1, -2)
-            ac = torch.matmul(qm, krt)    # [B, heads, M, M]
-            bc = torch.matmul(klm, krt)   # [B, heads, M+1, M]
+            ac = torch.empty((B, H, M, M), dtype=torch.float32, device=dev)
+            bc = torch.empty((B, H, M + 1, M), dtype=torch.float32, device=dev)
+            rc = lib.pcfgnat_links_scores(qm.data_ptr(), klm.data_ptr(), krm.data_ptr(), M, B, H, D, ac.data_ptr(),
+                                          bc.data_ptr(), _stream(dev))
+            _cabi.check(rc, "pcfgnat_links_scores")
             links = torch.empty((B, L, 2, L), dtype=torch.float32, device=dev)
             rc = lib.pcfgnat_links_from_scores(ac.data_ptr(), bc.data_ptr(), qm.data_ptr(), klm.data_ptr(),
                                                gates.data_ptr(), nonpad.data_ptr(), lm.data_ptr(), rm.data_ptr(),
                                                mc.data_ptr(), slot_of.data_ptr(), nodes.data_ptr(), M, B, L, H, D, 1,
                                                links.data_ptr(), _stream(dev))
         _cabi.check(rc, "pcfgnat_links_from_scores")
-        return links
+        saved = dict(ac=ac, bc=bc, qm=qm, klm=klm, krm=krm, gates=gates, nonpad=nonpad, lm=lm, rm=rm, mc=mc, slot_of=slot_of,
+                     nodes=nodes, dims=(B, L, H, D, M))
+        return links, saved
+
+    @staticmethod
+    def _links_backward(links_grad, saved):
+        """(d query, d key_left, d key_right [B, L, heads, head_dim] f32, d gate_logits [B, L, heads] f32)."""
+        B, L, H, D, M = saved["dims"]
+        g = _f32_cuda(links_grad, "links_grad", 4)
+        if tuple(g.shape) != (B, L, 2, L):
+            raise RuntimeError("links_grad must have the shape of links")
+        dev = g.device
+        p = lambda name: saved[name].data_ptr()
+        with torch.cuda.device(dev):
+            X0 = torch.zeros((B, H, M, M), dtype=torch.float32, device=dev)
+            X1 = torch.zeros((B, H, M, M), dtype=torch.float32, device=dev)
+            dab = torch.zeros((B, H, M, 2), dtype=torch.float32, device=dev)
+            dq = torch.zeros((B, L, H, D), dtype=torch.float32, device=dev)
+            dkl = torch.zeros_like(dq)
+            dkr = torch.zeros_like(dq)
+            dgates = torch.empty((B, L, H), dtype=torch.float32, device=dev)
+            rc = _cabi.lib().pcfgnat_links_backward(g.data_ptr(), p("ac"), p("bc"), p("qm"), p("klm"), p("krm"), p("gates"),
+                                                    p("nonpad"), p("lm"), p("rm"), p("mc"), p("slot_of"), p("nodes"), M,
+                                                    B, L, H, D, 1, X0.data_ptr(), X1.data_ptr(), dab.data_ptr(),
+                                                    dq.data_ptr(), dkl.data_ptr(), dkr.data_ptr(), dgates.data_ptr(),
+                                                    _stream(dev))
+        _cabi.check(rc, "pcfgnat_links_backward")
+        return dq, dkl, dkr, dgates
+
+    @staticmethod
+    def extract_links(query, key_left, key_right, gate_logits, prev_output_tokens, pad_index, left_tree_mask,
+                      right_tree_mask, main_chain):
+        """links [B, L, 2, L] f32 as the model's extract_links() forms them from the projected link features
+        (models/...pcfg.py:140-201, max_left == 1): ``query``, ``key_left``, ``key_right`` [B, L, heads, head_dim]
+        (outputs of the three link projections, reshaped), ``gate_logits`` [B, L, heads].  Three launches: feature
+        gather, the per-head score products, and masking + joint log-softmax + head mixture + -inf rows.
+        Differentiable with respect to the four feature tensors (``ExtractLinksFunc``)."""
+        if torch.is_grad_enabled() and any(t.requires_grad for t in (query, key_left, key_right, gate_logits)):
+            return ExtractLinksFunc.apply(query, key_left, key_right, gate_logits, prev_output_tokens, pad_index,
+                                          left_tree_mask, right_tree_mask, main_chain)
+        return _Kernel._links_forward(query, key_left, key_right, gate_logits, prev_output_tokens, pad_index, left_tree_mask,
+                                      right_tree_mask, main_chain)[0]
 
     @staticmethod
     def loss_stats(sentence_loss, target_length):
@@ -777,6 +849,29 @@ class ProjLogsoftmaxGatherFunc(Function):
         if ctx.needs_input_grad[1]:
             d_weight = (dl.t() @ hidden.reshape(B * L, H).to(torch.bfloat16)).to(weight.dtype)
         return d_hidden, d_weight, None, None, None
+
+
+class ExtractLinksFunc(Function):
+    """links = extract_links(link features) with a hand-written backward: the reference gets its gradient from autograd
+    through the ~30 operators of the model's extract_links (models/...pcfg.py:163-199), which keeps several
+    [B, L, 2, L, heads] tensors alive; here the backward recomputes a row's quantities from the compact per-head score
+    matrices the forward kept."""
+
+    @staticmethod
+    def forward(ctx, query, key_left, key_right, gate_logits, prev_output_tokens, pad_index, left_tree_mask, right_tree_mask,
+                main_chain):
+        links, saved = _Kernel._links_forward(query, key_left, key_right, gate_logits, prev_output_tokens, pad_index,
+                                              left_tree_mask, right_tree_mask, main_chain)
+        ctx.saved = saved
+        ctx.dtypes = (query.dtype, key_left.dtype, key_right.dtype, gate_logits.dtype)
+        return links
+
+    @staticmethod
+    def backward(ctx, links_grad):
+        dq, dkl, dkr, dgates = _Kernel._links_backward(links_grad.contiguous(), ctx.saved)
+        out = [g.to(dt) if need else None
+               for g, dt, need in zip((dq, dkl, dkr, dgates), ctx.dtypes, ctx.needs_input_grad[:4])]
+        return (*out, None, None, None, None, None)
 
 
 class ForceEmitFunc(Function):

@@ -325,12 +325,20 @@ class DecodeStep(_GraphedStep):
     kernels_per_step = 5  # proj_prepare, proj, proj_merge, viterbi, backtrace
 
     def __init__(self, weight, B, L, left_tree_mask, device, beta=1.0, pad_index=1, use_graph=True, copy_chunks=2,
-                 link_features=None, right_tree_mask=None, main_chain=None):
+                 link_features=None, right_tree_mask=None, main_chain=None, strategy="viterbi", decode_beta=1.0):
         """link_features=(heads, head_dim): the step takes the projected link features instead of the transition
         matrix and forms the latter itself (the model's extract_links, models/...pcfg.py:140-201).  Inputs
         (``load`` order) are then hidden, query, key_left, key_right [B,L,heads,head_dim] f16, gate_logits
         [B,L,heads] f32, prev_output_tokens [B,L] i64 and output_length; right_tree_mask and main_chain are needed."""
         super().__init__(weight, B, L, device, use_graph, copy_chunks)
+        if strategy not in ("viterbi", "lookahead", "greedy"):
+            raise RuntimeError(f"unknown decode strategy {strategy!r}")
+        # the model's decode_strategy (models/...pcfg.py:419-502); "lookahead" weighs the children's best token
+        # log-probabilities with decode_beta, "greedy" follows the transitions alone.  With these two ``run()``
+        # returns (tokens, count) and no predicted length.
+        self.strategy, self.decode_beta = strategy, float(decode_beta)
+        if strategy != "viterbi":
+            self.kernels_per_step = 4  # proj_prepare, proj, proj_merge, lookahead_decode
         self.mask = left_tree_mask.to(device=self.device, dtype=torch.int64).contiguous()
         self.pad_index = int(pad_index)
         # length penalty of the model: scores / arange(L // 4) ** beta (models/...pcfg.py:488-492)
@@ -368,6 +376,9 @@ class DecodeStep(_GraphedStep):
         if self.link_features is not None:
             links = k.extract_links(self.query, self.key_left, self.key_right, self.gate_logits, self.prev_output_tokens,
                                     self.pad_index, self.left_u8, self.right_u8, self.main_u8)
+        if self.strategy != "viterbi":
+            return k.lookahead_decode_device(links, em["max_lprob"], em["argmax"], self.output_length, self.mask,
+                                             self.pad_index, self.decode_beta, self.strategy)
         S, R, Lt, Mt = k.pcfg_viterbi(em["max_lprob"], links, self.output_length, 1)
         tokens, count, pred = k.viterbi_decode_device(S, self.penalty, self.output_length, Lt, R, Mt, em["argmax"],
                                                       self.mask, self.pad_index)

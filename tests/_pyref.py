@@ -159,3 +159,38 @@ def extract_links(q, kl, kr, gate_logits, prev_output_tokens, pad, left_mask, ri
     lg = torch.log_softmax(gate_logits.float(), -1)
     links = torch.logsumexp(lp + lg[:, :, None, :], -1).view(B, L, 2, L)
     return links.masked_fill(~use[:, :, None, None], float("-inf"))
+
+
+def lookahead_decode(links, ob_lprob, tokens, output_length, left_tree_mask, pad, beta=1.0, lookahead=True):
+    """Restatement of the model's "lookahead" / "greedy" decoding
+    (fs_plugins/models/glat_decomposed_with_link_two_hands_tri_pcfg.py:419-482), every sentence with its own
+    log-probabilities.  Returns the per-sentence token lists.  Pinned against the reference's own block by
+    tests/golden/host_lookahead.npz."""
+    import torch
+
+    B, L = links.shape[0], links.shape[1]
+    if lookahead:
+        left = torch.stack([torch.zeros(L, dtype=torch.long), (torch.arange(L) - 1).clamp(min=0)], -1)  # [a, k]
+        look = (links + ob_lprob[:, None, None, :] * beta) + (ob_lprob[:, left] * beta)[..., None]
+    else:
+        look = links
+    idx = look.reshape(B, L, 2 * L).max(-1)[1].tolist()
+    rows = []
+    for i in range(B):
+        length = int(output_length[i])
+        now, stack, res = 1, [], []
+        while (now < length and now != 0) or stack:
+            while now < length and now != 0:
+                stack.append(now)
+                k = idx[i][now] // L
+                lft = 0 if k == 0 else now - k
+                if left_tree_mask[now][lft]:
+                    break
+                now = lft
+            now = stack.pop()
+            t = int(tokens[i][now])
+            if t != pad:
+                res.append(t)
+            now = idx[i][now] % L
+        rows.append(res)
+    return rows

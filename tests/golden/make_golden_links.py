@@ -2,7 +2,9 @@
 (fs_plugins/models/glat_decomposed_with_link_two_hands_tri_pcfg.py:140-201) and ``buffered_tree_mask`` (:205-226),
 run on the CPU.  The model class cannot be imported without fairseq, so the two method definitions (and the
 module's ``logsumexp`` helper) are compiled from the file's text and called with a stand-in ``self`` that carries
-the attributes they read; the link projections are passed as callables that return the seeded tensors.
+the attributes they read; the link projections are passed as callables that return the seeded tensors.  The seeded
+tensors are autograd leaves: the gradient of sum(links * G) over the finite entries, for a seeded G, is recorded as
+well (the reference's own backward through its ~30 operators), which pins the hand-written backward.
 
 Usage:  python tests/golden/make_golden_links.py --reference /path/to/PCFG-NAT
 """
@@ -45,8 +47,8 @@ def main():
     cases = [("small", 3, 18, 4, 8, 0), ("mid", 2, 42, 8, 16, 1)]
     for name, B, L, heads, dim, seed in cases:
         g = torch.Generator().manual_seed(seed)
-        q, kl, kr = (torch.randn(B, L, heads * dim, generator=g) for _ in range(3))
-        gates = torch.randn(B, L, heads, generator=g)
+        q, kl, kr = (torch.randn(B, L, heads * dim, generator=g).requires_grad_(True) for _ in range(3))
+        gates = torch.randn(B, L, heads, generator=g).requires_grad_(True)
         lengths = torch.tensor([L, L - 8, max(2, L - 16)][:B])
         lengths = lengths - (lengths % 2)  # graph lengths are even at left_tree_layer 1
         pad = 1
@@ -63,6 +65,12 @@ def main():
         features = torch.zeros(B, L, 1)
         links = ns["extract_links"](me, features, prev, None, lambda x: q, lambda x: kl, lambda x: kr, lambda x: gates,
                                     left_mask, right_mask, main_chain)
+        G = torch.randn(links.shape, generator=g)
+        fin = torch.isfinite(links)
+        (torch.where(fin, links, torch.zeros_like(links)) * G).sum().backward()
+        out.update({f"{name}_G": G.numpy(), f"{name}_dq": q.grad.numpy(), f"{name}_dkl": kl.grad.numpy(),
+                    f"{name}_dkr": kr.grad.numpy(), f"{name}_dgates": gates.grad.numpy()})
+        q, kl, kr, gates, links = q.detach(), kl.detach(), kr.detach(), gates.detach(), links.detach()
         out.update({f"{name}_q": q.numpy(), f"{name}_kl": kl.numpy(), f"{name}_kr": kr.numpy(), f"{name}_gates": gates.numpy(),
                     f"{name}_prev": prev.numpy(), f"{name}_heads": np.int64(heads),
                     f"{name}_left_mask": left_mask.numpy(), f"{name}_right_mask": right_mask.numpy(),

@@ -821,6 +821,46 @@ def test_extract_links_against_reference_model(ops, case):
     np.testing.assert_allclose(mass, 1.0, atol=1e-4)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+@pytest.mark.parametrize("case", ["small", "mid"])
+def test_extract_links_backward_against_reference_autograd(ops, case, dtype):
+    """The hand-written backward of extract_links against the reference model's own function differentiated by
+    autograd (tests/golden/make_golden_links.py): gradient of sum(links * G) over the finite entries with respect to
+    the three link feature tensors and the gate logits."""
+    g = np.load(golden_path("host_extract_links.npz"))
+    heads = int(g[f"{case}_heads"])
+    t = lambda n: torch.from_numpy(g[f"{case}_{n}"])
+    B, L, E = t("q").shape
+    shape = (B, L, heads, E // heads)
+    leaves = [t(n).view(shape).to(DEV, dtype).requires_grad_(True) for n in ("q", "kl", "kr")]
+    gates = t("gates").to(DEV).requires_grad_(True)
+    links = ops.get_pcfg_kernel().extract_links(*leaves, gates, t("prev").to(DEV), 1, t("left_mask"), t("right_mask"),
+                                                t("main_chain"))
+    assert links.requires_grad
+    fin = torch.isfinite(links)
+    (torch.where(fin, links, torch.zeros_like(links)) * t("G").to(DEV)).sum().backward()
+    tol = dict(rtol=1e-3, atol=1e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)  # f16 inputs are rounded
+    for leaf, name in zip(leaves, ("dq", "dkl", "dkr")):
+        assert leaf.grad.dtype == dtype
+        np.testing.assert_allclose(leaf.grad.float().cpu().numpy().reshape(B, L, E), g[f"{case}_{name}"], **tol)
+    np.testing.assert_allclose(gates.grad.cpu().numpy(), g[f"{case}_dgates"], **tol)
+    if dtype == torch.float32:  # and through the loss: d loss / d link features, against float64 torch autograd
+        import importlib
+
+        match = torch.randn(B, L, 5, device=DEV).log_softmax(0)
+        ol = t("prev").ne(1).sum(1).to(DEV)
+        tl = torch.full((B,), 5, device=DEV)
+        for x in leaves + [gates]:
+            x.grad = None
+        links = ops.get_pcfg_kernel().extract_links(*leaves, gates, t("prev").to(DEV), 1, t("left_mask"), t("right_mask"),
+                                                    t("main_chain"))
+        loss = ops.cuda_pcfg_loss(match, links, ol, tl)
+        ok = torch.isfinite(loss)
+        assert ok.any()
+        loss[ok].sum().backward()
+        assert all(torch.isfinite(x.grad).all() for x in leaves + [gates]) and leaves[0].grad.abs().sum() > 0
+
+
 def test_decode_step_from_link_features(pkg, ops, syn):
     """DecodeStep fed with the projected link features gives what extract_links + the transition-fed step give."""
     import importlib
@@ -1124,3 +1164,43 @@ def test_pipelined_steps_overlap_copies_without_mixing_batches(pkg, ops, syn):
         for x, y in zip(a, b):
             assert torch.equal(x, y)
     assert not torch.equal(want[0][3], want[1][3])
+
+
+# ---- lookahead / greedy decoding ---------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("name", ["look_b1_a", "look_b1_b", "greedy_b4", "greedy_b1"])
+def test_lookahead_decode_against_reference_model(ops, name):
+    g = _g("host_lookahead.npz")
+    t = lambda key: torch.from_numpy(g[f"{name}_{key}"]).to(DEV)
+    strategy = "lookahead" if int(g[f"{name}_lookahead"]) else "greedy"
+    k = ops.get_pcfg_kernel()
+    ops.read_status(DEV)
+    out, cnt = k.lookahead_decode_device(t("links"), t("ob"), t("tok"), t("out_len"), t("mask"), 1,
+                                         float(g[f"{name}_beta"]), strategy)
+    want = g[f"{name}_result"]
+    assert int(cnt.max()) == want.shape[1]
+    assert np.array_equal(out[:, :want.shape[1]].cpu().numpy(), want)
+    assert (out[:, want.shape[1]:] == 1).all() and ops.read_status(DEV) == 0
+
+
+@pytest.mark.parametrize("strategy", ["lookahead", "greedy"])
+def test_lookahead_decode_step_against_restatement(pkg, ops, syn, strategy):
+    """DecodeStep with the two host-loop strategies of the model, on a ragged batch, against the restatement fed the
+    kernel's own emissions (arg-max decoding on identical numbers: exact)."""
+    import importlib
+
+    runtime = importlib.import_module("pcfg_nat_b200.runtime")
+    w = syn.Workload("la", batch=9, vocab=2000, hidden=64, src_min=4, src_max=40, kind="viterbi")
+    b = syn.make_batch(w, seed=8)
+    weight = b.weight.to(DEV)
+    step = runtime.DecodeStep(weight, b.B, b.L, b.left_tree_mask, DEV, strategy=strategy, decode_beta=0.7)
+    step.load(b.hidden, b.links, b.output_length)
+    for _ in range(2):
+        tokens, count = [x.clone() for x in step.run()]
+    em = ops.proj_logsoftmax_gather(b.hidden.to(DEV), weight, None, b.output_length.to(DEV), None, want_max=True)
+    rows = pyref.lookahead_decode(b.links, em["max_lprob"].cpu(), em["argmax"].cpu(), b.output_length,
+                                  b.left_tree_mask.bool(), 1, 0.7, strategy == "lookahead")
+    assert min(len(r) for r in rows) >= 2
+    for i, r in enumerate(rows):
+        assert int(count[i]) == len(r) and tokens[i, :len(r)].cpu().tolist() == r
+        assert (tokens[i, len(r):] == 1).all()

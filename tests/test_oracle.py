@@ -283,3 +283,19 @@ def test_force_emit_and_loss_scalar_against_reference_criterion():
         stats = sharding.local_loss_stats(sent, t("tgt_len"))
         assert abs(float(-stats[0] / stats[1]) - float(g[f"{tag}_loss"])) < 1e-5 * abs(float(g[f"{tag}_loss"]))
         assert int(stats[2]) == int(g[f"{tag}_invalid"]) == 1
+
+
+@pytest.mark.parametrize("name", ["look_b1_a", "look_b1_b", "greedy_b4", "greedy_b1"])
+def test_lookahead_restatement_against_reference_model(name):
+    """tests/golden/make_golden_lookahead.py executed the reference's own decoding block
+    (models/glat_decomposed_with_link_two_hands_tri_pcfg.py:419-482); the restatement must give the same tokens."""
+    import _pyref as pyref
+
+    g = np.load(golden_path("host_lookahead.npz"))
+    t = lambda k: torch.from_numpy(g[f"{name}_{k}"])
+    rows = pyref.lookahead_decode(t("links"), t("ob"), t("tok"), t("out_len"), t("mask").bool(), 1,
+                                  float(g[f"{name}_beta"]), bool(g[f"{name}_lookahead"]))
+    want = t("result")
+    assert max(len(r) for r in rows) == want.shape[1]
+    for r, w in zip(rows, want.tolist()):
+        assert r + [1] * (len(w) - len(r)) == w
