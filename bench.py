@@ -733,6 +733,36 @@ def run_ours(a):
             "ms_per_step": full_ms, "value": batch.B / (full_ms / 1e3), "unit": UNIT,
             "gpu_launches_per_step": full.kernels_per_step, "what": full.proj_backward_note}
         del full
+    # the same step fed with the projected link features instead of the transition matrix: the transitions are formed
+    # inside the step (the model's extract_links) and the loss gradient is carried back to the features
+    if is_loss and world == 1 and not a.no_proj_backward:
+        support = importlib.import_module("pcfg_nat_b200.support_tree")
+        heads, dim = 8, 64  # decoder_attention_heads and embed_dim / heads of the published configuration (512 / 8)
+        lm, rm, mc = support.get_mask(batch.L, 1)
+        g = torch.Generator().manual_seed(a.seed)
+        feats = [torch.randn(batch.B, batch.L, heads, dim, generator=g).half().to(dev) for _ in range(3)]
+        gates = torch.randn(batch.B, batch.L, heads, generator=g).to(dev)
+        prev = torch.where(torch.arange(batch.L)[None, :] < batch.output_length[:, None], 3, 1).to(dev)
+        lf = runtime.LossStep(ctx.weight(batch), batch.B, batch.L, batch.T, dev, use_graph=not a.no_graph,
+                              link_features=(heads, dim), left_tree_mask=lm, right_tree_mask=rm, main_chain=mc)
+        lf.load(host[0].to(dev), *feats, gates, prev, *[t.to(dev) for t in host[2:5]])
+        times = []
+        for i in range(3 + a.steps):
+            ctx.flush.fill_(1)
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            lf.run()
+            e.record()
+            times.append((s, e))
+        torch.cuda.synchronize()
+        lf_ms = sum(s.elapsed_time(e) for s, e in times[3:]) / a.steps
+        line["with_link_features"] = {
+            "ms_per_step": lf_ms, "value": batch.B / (lf_ms / 1e3), "unit": UNIT, "gpu_launches_per_step": lf.kernels_per_step,
+            "h2d_bytes_per_step_if_loaded": lf.input_bytes(),
+            "what": f"the step with the transitions formed from {heads} x {dim} link features per node inside it "
+                    "(feature gather, per-head score products, masking + joint log-softmax + head mixture) and the "
+                    "loss gradient carried back to the features (two more kernels); random features"}
+        del lf
     del step
     torch.cuda.empty_cache()
 

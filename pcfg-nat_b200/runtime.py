@@ -213,13 +213,33 @@ class LossStep(_GraphedStep):
     Inputs (``load`` order): hidden [B,L,H] f16, links [B,L,2,L] f32, output_length [B], targets [B,T],
     target_length [B].  ``run()`` returns (stats[3] f32 = [sum_b S_b/n_b, sentences, invalid],
     match_all_grad, links_grad, sentence_loss); static outputs, overwritten by the next ``run()``.
+    With ``link_features`` the transitions are formed from the projected link features inside the step and the
+    third output is the tuple of their gradients (see the constructor).
     """
     kernels_per_step = 7  # proj_prepare, proj, proj_merge, loss_fwd, outside, grad, loss_stats (set per shape below)
 
     def __init__(self, weight, B, L, T, device, use_graph=True, copy_chunks=2, proj_backward=False, exchange=None,
-                 force_emit=False):
+                 force_emit=False, link_features=None, left_tree_mask=None, right_tree_mask=None, main_chain=None,
+                 pad_index=1):
         super().__init__(weight, B, L, device, use_graph, copy_chunks)
         self.T = T
+        # link_features=(heads, head_dim): the step takes the projected link features instead of the transition
+        # matrix (inputs query, key_left, key_right [B,L,heads,head_dim] f16, gate_logits [B,L,heads] f32,
+        # prev_output_tokens [B,L] in place of links), forms the transitions itself (the model's extract_links,
+        # models/...pcfg.py:140-201) and carries the loss gradient back to the features: run() then returns d query,
+        # d key_left, d key_right, d gate_logits in place of links_grad.  The three tree masks are needed.
+        self.link_features = link_features
+        if link_features is not None:
+            heads, dim = link_features
+            dev = self.device
+            self.pad_index = int(pad_index)
+            self.query, self.key_left, self.key_right = (torch.zeros((B, L, heads, dim), dtype=torch.float16, device=dev)
+                                                         for _ in range(3))
+            self.gate_logits = torch.zeros((B, L, heads), dtype=torch.float32, device=dev)
+            self.prev_output_tokens = torch.full((B, L), self.pad_index, dtype=torch.int64, device=dev)
+            u8 = lambda t: t.to(dev).ne(0).to(torch.uint8).contiguous()
+            self.left_u8, self.right_u8 = u8(left_tree_mask[:L, :L]), u8(right_tree_mask[:L, :L])
+            self.main_u8 = u8(main_chain[:L])
         # force_emit: the training pass after a glancing pass (criterions/nat_pcfg_loss.py:116-121): two more
         # inputs, matchmask [B,T,L] and keep_word_mask [B,L] (bool, as GlanceStep returns them); a revealed node
         # may only emit its aligned target position and gets no gradient
@@ -240,7 +260,8 @@ class LossStep(_GraphedStep):
             from . import _cabi
             with torch.cuda.device(self.device):
                 dp = _cabi.lib().pcfgnat_loss_fwd_bwd_kernels(B, L, T, 1)
-            self.kernels_per_step = 4 + (dp if dp > 0 else 3) + (2 if self.force_emit else 0)
+            # with link features: feature gather, score products, links, and the two backward kernels
+            self.kernels_per_step = 4 + (dp if dp > 0 else 3) + (2 if self.force_emit else 0) + (5 if link_features else 0)
         self.proj_backward_note = None
         if self.proj_backward:
             self.kernels_per_step += 3  # proj_prepare, zero padding rows, proj (grad mode)
@@ -250,8 +271,17 @@ class LossStep(_GraphedStep):
                                        "the padded rows")
 
     def _inputs(self):
-        base = [self.hidden, self.links, self.output_length, self.targets, self.target_length]
+        if self.link_features is not None:
+            base = [self.hidden, self.query, self.key_left, self.key_right, self.gate_logits, self.prev_output_tokens,
+                    self.output_length, self.targets, self.target_length]
+        else:
+            base = [self.hidden, self.links, self.output_length, self.targets, self.target_length]
         return base + ([self.matchmask, self.keep_word_mask] if self.force_emit else [])
+
+    def _stage2_inputs(self):
+        if self.link_features is None:
+            return super()._stage2_inputs()
+        return [self.query, self.key_left, self.key_right, self.gate_logits, self.prev_output_tokens]
 
     def _stage1(self, b0=0, b1=None):
         return self.kernel.proj_logsoftmax_gather(self.hidden[b0:b1], self.weight, self.targets[b0:b1],
@@ -261,9 +291,16 @@ class LossStep(_GraphedStep):
     def _stage2(self, em):
         if self.force_emit:
             self.kernel.force_emit(em["match"], self.matchmask, self.keep_word_mask, out=em["match"])
-        loss, mg, lg = self.kernel.pcfg_loss_fwd_bwd(em["match"], self.links, self.output_length, self.target_length)
+        links, saved = self.links, None
+        if self.link_features is not None:
+            links, saved = self.kernel._links_forward(self.query, self.key_left, self.key_right, self.gate_logits,
+                                                      self.prev_output_tokens, self.pad_index, self.left_u8, self.right_u8,
+                                                      self.main_u8)
+        loss, mg, lg = self.kernel.pcfg_loss_fwd_bwd(em["match"], links, self.output_length, self.target_length)
         if self.force_emit:
             self.kernel.force_emit_grad(mg, self.keep_word_mask, out=mg)
+        if saved is not None:
+            lg = self.kernel._links_backward(lg, saved)  # (d query, d key_left, d key_right, d gate_logits), float32
         stats = (self.exchange.stats(loss, self.target_length) if self.exchange is not None
                  else sharding.local_loss_stats(loss, self.target_length))
         if not self.proj_backward:

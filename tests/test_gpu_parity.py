@@ -1204,3 +1204,40 @@ def test_lookahead_decode_step_against_restatement(pkg, ops, syn, strategy):
     for i, r in enumerate(rows):
         assert int(count[i]) == len(r) and tokens[i, :len(r)].cpu().tolist() == r
         assert (tokens[i, len(r):] == 1).all()
+
+
+def test_loss_step_from_link_features_matches_autograd_chain(pkg, ops, syn):
+    """LossStep fed with the projected link features (transitions formed and differentiated inside the step) against
+    the operators chained by autograd: extract_links -> cuda_pcfg_loss -> backward."""
+    import importlib
+
+    runtime = importlib.import_module("pcfg_nat_b200.runtime")
+    support = importlib.import_module("pcfg_nat_b200.support_tree")
+    w = syn.Workload("lf", batch=5, vocab=2000, hidden=64, src_min=5, src_max=14)
+    b = syn.make_batch(w, seed=9)
+    heads, dim = 4, 16
+    g = torch.Generator().manual_seed(3)
+    q, kl, kr = (torch.randn(b.B, b.L, heads, dim, generator=g).half() for _ in range(3))
+    gates = torch.randn(b.B, b.L, heads, generator=g)
+    prev = torch.where(torch.arange(b.L)[None, :] < b.output_length[:, None], 3, 1)
+    lm, rm, mc = support.get_mask(b.L, 1)
+    weight = b.weight.to(DEV)
+    step = runtime.LossStep(weight, b.B, b.L, b.T, DEV, link_features=(heads, dim), left_tree_mask=lm, right_tree_mask=rm,
+                            main_chain=mc)
+    step.load(b.hidden, q, kl, kr, gates, prev, b.output_length, b.targets, b.target_length)
+    for _ in range(2):  # capture, replay
+        stats, mg, (dq, dkl, dkr, dgates), loss = step.run()
+    torch.cuda.synchronize()
+    leaves = [x.to(DEV).requires_grad_(True) for x in (q, kl, kr)]
+    gt = gates.to(DEV).requires_grad_(True)
+    links = ops.get_pcfg_kernel().extract_links(*leaves, gt, prev.to(DEV), 1, lm, rm, mc)
+    em = ops.proj_logsoftmax_gather(b.hidden.to(DEV), weight, b.targets.to(DEV), b.output_length.to(DEV),
+                                    b.target_length.to(DEV))["match"]
+    loss2 = ops.cuda_pcfg_loss(em, links, b.output_length.to(DEV), b.target_length.to(DEV))
+    assert torch.isfinite(loss2).all()
+    loss2.sum().backward()
+    assert torch.equal(loss, loss2.detach())
+    for got, leaf in zip((dq, dkl, dkr), leaves):
+        torch.testing.assert_close(got, leaf.grad.float(), rtol=1e-3, atol=1e-3)  # the chain rounds its gradients to f16
+    torch.testing.assert_close(dgates, gt.grad, rtol=1e-5, atol=1e-6)
+    assert dq.abs().sum() > 0 and dkr.abs().sum() > 0
