@@ -78,6 +78,8 @@ def parse():
                     help="N > 1: sum the loss statistics with an NCCL all-reduce instead of the in-kernel exchange")
     ap.add_argument("--copy-chunks", type=int, default=2,
                     help="sentence groups the end-to-end leg sends (and projects) the decoder states in")
+    ap.add_argument("--fetch", default="auto", choices=["auto", "none", "links", "all"],
+                    help="what the end-to-end leg fetches from the host buffers by kernel instead of by copy engine")
     ap.add_argument("--cpu-sample", type=int, default=0,
                     help="sentences per pass of the CPU baseline (0 = the whole batch of the workload)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -355,8 +357,12 @@ def measure(ctx, name, batch, global_sentences, steps, warm, blocks=None, exchan
     block(3, True)
     serial_ms = [block(steps, True) for _ in range(min(nb, 5))]  # load -> run -> read-back, one batch at a time
     # the end-to-end figure: two step objects in turn, so that batch i + 1 is copied while batch i is computed
+    # several GPUs pull from one host: the bus is the bottleneck, so the transitions are fetched by the kernel that
+    # moves only the entries the kernels read; on one GPU the copy engines alone overlap better
+    fetch = a.fetch if a.fetch != "auto" else ("links" if ctx.world > 1 else "none")
     pipe = ctx.runtime.PipelinedStep(lambda: make_step(ctx.runtime, batch, weight, dev, not a.no_graph, a.copy_chunks,
-                                                       exchange, **shape)[0]) if not a.no_graph else None
+                                                       exchange, **shape)[0],
+                                     fetch_from_host=None if fetch == "none" else fetch) if not a.no_graph else None
     if pipe is not None:
         step_single = step
         step = pipe
@@ -388,10 +394,13 @@ def measure(ctx, name, batch, global_sentences, steps, warm, blocks=None, exchan
 
         block_piped(3)
         e2e_ms = [block_piped(steps) for _ in range(nb)]
+        h2d = pipe.input_bytes()
         step = step_single
         del pipe
+        pipe_used = True
     else:
         e2e_ms = serial_ms
+        pipe_used = False
     projection_block(3)
     proj_ms = [projection_block(steps) for _ in range(min(nb, 5))]
     copy_block(2)
@@ -421,6 +430,7 @@ def measure(ctx, name, batch, global_sentences, steps, warm, blocks=None, exchan
                 "copy_ms": copy_max, "h2d_gbs": h2d / (copy_max / 1e3) / 1e9,
                 "how": "every step copies its inputs from pinned host memory and reads its result back; two step "
                        "objects in turn, so that the copies of batch i + 1 run while batch i is computed",
+                "fetch_by_kernel": fetch if pipe_used else "none",
                 "one_batch_at_a_time": {"value": per_s(statistics.median(serial_ms)),
                                         "ms_per_step": statistics.median(serial_ms) / steps},
                 "bound": "host-to-device copies (PCIe)" if copy_max > e2e_med / steps * 0.95 else "device time"},

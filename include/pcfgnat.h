@@ -313,6 +313,18 @@ int pcfgnat_links_from_scores(const float *ac, const float *bc, const float *qm,
  * callers that stage batches from host memory: it halves the bytes the largest input sends over PCIe. */
 int pcfgnat_copy_links_main_rows(void *dst, const void *src, int B, int L, int max_left, void *stream);
 
+/* Fetches a batch's large inputs from HOST memory with one kernel that reads the host buffers itself (mapped pinned
+ * memory, e.g. cudaHostAlloc / torch pin_memory; device memory works too), and only what the kernels of this library
+ * read: the decoder states of the real graph nodes, hidden[b][l][.] for l < m_b (row_bytes per node, a multiple of
+ * 16), and the transitions links[b][a][k][c] for main-chain a < m_b and a < c < m_b; the other cells of the
+ * main-chain rows of links_dst are set to -inf, rows of other nodes are left as they are (fill the buffer with -inf
+ * once).  Either pair of pointers may be NULL.  output_length [B] int64 is a DEVICE array and must be there when the
+ * kernel runs.  Host plumbing with no counterpart in the reference, whose inputs are made on the device: for a
+ * training batch it moves about 14 MB over PCIe where the padded tensors have 33 MB.  The host buffers must not
+ * change until the kernel has run. */
+int pcfgnat_stage_inputs(const void *hidden_src, void *hidden_dst, int row_bytes, const float *links_src,
+                         float *links_dst, const int64_t *output_length, int B, int L, int max_left, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -323,6 +323,29 @@ int pcfgnat_copy_links_main_rows(void *dst, const void *src, int B, int L, int m
     return PCFGNAT_OK;
 }
 
+int pcfgnat_stage_inputs(const void *hidden_src, void *hidden_dst, int row_bytes, const float *links_src,
+                         float *links_dst, const int64_t *output_length, int B, int L, int max_left, void *stream) {
+    if (max_left != 1) return PCFGNAT_ERR_UNSUPPORTED;
+    if (B < 0 || L < 2 || row_bytes < 0 || row_bytes % 16) return PCFGNAT_ERR_INVALID_ARGUMENT;
+    if (B && (!output_length || (hidden_src && !hidden_dst) || (links_src && !links_dst))) return PCFGNAT_ERR_INVALID_ARGUMENT;
+    // the sources are read by the kernel itself: they must be memory the device can address (mapped pinned host
+    // memory, or device memory); what the device sees may differ from the host's pointer
+    const void *src[2] = {hidden_src, links_src};
+    for (int i = 0; i < 2; i++) {
+        if (!src[i]) continue;
+        cudaPointerAttributes at;
+        if (cudaPointerGetAttributes(&at, src[i]) != cudaSuccess) {
+            cudaGetLastError();
+            return PCFGNAT_ERR_INVALID_ARGUMENT;
+        }
+        if (at.type == cudaMemoryTypeUnregistered || !at.devicePointer) return PCFGNAT_ERR_INVALID_ARGUMENT;
+        src[i] = at.devicePointer;
+    }
+    if ((reinterpret_cast<uintptr_t>(src[0]) | reinterpret_cast<uintptr_t>(hidden_dst)) % 16) return PCFGNAT_ERR_INVALID_ARGUMENT;
+    return launch_stage_inputs(src[0], hidden_dst, row_bytes, static_cast<const float *>(src[1]), links_dst, output_length, B,
+                               L, static_cast<cudaStream_t>(stream));
+}
+
 int pcfgnat_proj_dlogits(const void *hidden, const void *weight, const int64_t *targets, const int64_t *output_length,
                          const int64_t *target_length, const float *lse, const float *grad_match, int B, int L, int T, int V,
                          int H, void *dlogits, void *workspace, size_t workspace_bytes, int *status, void *stream) {

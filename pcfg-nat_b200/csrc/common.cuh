@@ -103,6 +103,8 @@ int launch_viterbi_decode(const float *S, const float *penalty, const int64_t *o
                           const int64_t *Mt, const int64_t *tokens, const int64_t *mask, int mask_dim, int64_t pad, int B,
                           int L, int Q, int cap, int64_t *pred_out, int64_t *out, int64_t *cnt, int *status,
                           cudaStream_t st);
+int launch_stage_inputs(const void *hidden_src, void *hidden_dst, int row_bytes, const float *links_src, float *links_dst,
+                        const int64_t *ol, int B, int L, cudaStream_t st);
 int launch_lookahead_decode(const float *links, const float *ob, const int64_t *tokens, const int64_t *ol,
                             const int64_t *mask, int mask_dim, float beta, int lookahead, int64_t pad, int B, int L,
                             int cap, int64_t *out, int64_t *cnt, int *status, cudaStream_t st);

@@ -471,6 +471,48 @@ class _Kernel:
         _cabi.check(rc, "pcfgnat_copy_links_main_rows")
 
     @staticmethod
+    def stage_inputs(output_length, hidden_dst=None, hidden_src=None, links_dst=None, links_src=None):
+        """Fetches a batch's large inputs from pinned host memory with one kernel that reads the host buffers itself,
+        and only what the kernels read: the decoder states of the real graph nodes (``hidden`` [B, L, H]) and the
+        transitions of main-chain nodes to later nodes inside the sentence (``links`` [B, L, 2, L]; the rest of those
+        rows becomes -inf, other rows are left alone).  ``output_length`` is the DEVICE tensor of the lengths.
+        Asynchronous on the current stream; the host buffers must stay unchanged until it has run."""
+        _require_cuda()
+        dev = output_length.device
+        if not output_length.is_cuda or output_length.dtype != torch.int64 or output_length.dim() != 1:
+            raise RuntimeError("output_length must be an int64 CUDA tensor [batch]")
+        B = output_length.shape[0]
+        L = None
+        row_bytes = 0
+        for dst, src, nd, name in ((hidden_dst, hidden_src, 3, "hidden"), (links_dst, links_src, 4, "links")):
+            if (dst is None) != (src is None):
+                raise RuntimeError(f"{name}: give both the destination and the source")
+            if dst is None:
+                continue
+            if not dst.is_cuda or dst.device != dev or dst.dim() != nd or dst.shape[0] != B or not dst.is_contiguous():
+                raise RuntimeError(f"{name}_dst must be a contiguous CUDA tensor with the batch in front")
+            if tuple(src.shape) != tuple(dst.shape) or src.dtype != dst.dtype or not src.is_contiguous():
+                raise RuntimeError(f"{name}_src must have the shape and type of {name}_dst")
+            if not (src.is_cuda or src.is_pinned()):
+                raise RuntimeError(f"{name}_src must be pinned host memory (or device memory): the kernel reads it itself")
+            if L is not None and dst.shape[1] != L:
+                raise RuntimeError("hidden and links disagree on prelen")
+            L = dst.shape[1]
+        if L is None:
+            return
+        if hidden_dst is not None:
+            row_bytes = hidden_dst.shape[2] * hidden_dst.element_size()
+            if row_bytes % 16:
+                raise RuntimeError("a row of hidden must be a multiple of 16 bytes")
+        if links_dst is not None and (links_dst.dtype != torch.float32 or links_dst.shape[2] != 2 or links_dst.shape[3] != L):
+            raise RuntimeError("links must be float32 [batch, prelen, 2, prelen]")
+        ptr = lambda t: t.data_ptr() if t is not None else None
+        with torch.cuda.device(dev):
+            rc = _cabi.lib().pcfgnat_stage_inputs(ptr(hidden_src), ptr(hidden_dst), row_bytes, ptr(links_src), ptr(links_dst),
+                                                  output_length.data_ptr(), B, L, 1, _stream(dev))
+        _cabi.check(rc, "pcfgnat_stage_inputs")
+
+    @staticmethod
     def _links_forward(query, key_left, key_right, gate_logits, prev_output_tokens, pad_index, left_tree_mask,
                        right_tree_mask, main_chain):
         """Forward of ``extract_links``; returns (links, everything the backward needs)."""

@@ -50,6 +50,15 @@ class _GraphedStep:
         self._ev_stage1 = self._ev_stage2 = self._ev_done = None
         self._ev_ran = None  # end of this object's last run(): the point after which its input buffers are free
         self._pending = False
+        self._pending_chunked = False
+        self.last_load_bytes = None
+        # How an overlapped load takes the large inputs from pinned host memory.  None: copy engines only (the padded
+        # states and the main-chain rows of the transitions; copies overlap the kernels of the previous batch
+        # completely).  "links": the transitions by a kernel that reads the host buffer itself and fetches only the
+        # entries the tree masks leave finite (a quarter of the bytes of the main-chain rows); "all": the states of
+        # the real graph nodes that way too.  A fetching kernel needs SMs, which the persistent compute kernels do not
+        # share, so it pays where the bus is the bottleneck (several GPUs pulling from one host), not on one GPU.
+        self.fetch_from_host = None
         # sentence groups [b0, b1) of an overlapped load; chunking needs the graphs (it is a replay trick)
         n = max(1, min(int(copy_chunks), B)) if use_graph else 1
         self.chunks = [(B * i // n, B * (i + 1) // n) for i in range(n)]
@@ -64,9 +73,31 @@ class _GraphedStep:
         return [self.links]
 
     def input_bytes(self):
-        """Bytes one ``load`` moves: every input whole, except the transitions, of which only the rows of
-        main-chain nodes (every other row) are read by the kernels and therefore copied."""
+        """Bytes one ``load`` moves.  After an overlapped load from pinned host memory: what that load fetched (the
+        decoder states of the real nodes and the transitions the kernels read, see ``load``).  Otherwise every input
+        whole, except the transitions, of which only the rows of main-chain nodes (every other row) are copied."""
+        if self.last_load_bytes is not None:
+            return self.last_load_bytes
         return sum(t.numel() * t.element_size() // (2 if t is self.links else 1) for t in self._inputs())
+
+    def _fetched_bytes(self, tensors, lengths, fetch_hidden, fetch_links):
+        """Bytes an overlapped load moves for sentences of ``lengths`` graph nodes when a kernel fetches the states
+        and / or the transitions from the host buffers."""
+        bufs = self._inputs()
+        m = lengths.clamp(max=self.L).double()
+        total = 0.0
+        for dst, src in zip(bufs, tensors):
+            if dst is self.hidden and fetch_hidden:
+                total += float(m.sum()) * self.H * 2
+            elif dst is self.links and fetch_links:
+                # main-chain nodes a = 1, 3, .. < m, both left options, columns a + 1 .. m - 1
+                k = torch.floor(m / 2)  # their number; sum over them of (m - 1 - a) = k (m - 1) - k^2
+                total += float((2 * 4 * (k * (m - 1) - k * k)).clamp(min=0).sum())
+            elif dst is self.links:
+                total += src.numel() * src.element_size() // 2  # the strided copy of the main-chain rows
+            else:
+                total += src.numel() * src.element_size()
+        return int(total)
 
     def _copy_in(self, dst, src):
         if dst is self.links and src.dtype == torch.float32 and src.is_contiguous() and dst.shape[1] % 2 == 0 \
@@ -80,7 +111,10 @@ class _GraphedStep:
 
         overlap=False: asynchronous copies on the current stream.  overlap=True: on the step's copy stream,
         first-stage inputs first; the next ``run`` orders each stage after the arrival of its own inputs and
-        the copies after this object's previous ``run`` (which still reads the buffers)."""
+        the copies after this object's previous ``run`` (which still reads the buffers).  From pinned host tensors
+        an overlapped load moves only what the kernels read (``fetch_from_host``): the decoder states of the real
+        graph nodes, and of the transitions the entries links[a][k][c] with a on the main chain and a < c < m_b —
+        everything the model's tree masks leave finite; the rest of those rows is -inf in the step's buffer."""
         bufs = self._inputs()
         if len(tensors) != len(bufs):
             raise RuntimeError(f"expected {len(bufs)} tensors")
@@ -104,16 +138,35 @@ class _GraphedStep:
             for dst, src in zip(bufs, tensors):  # the small inputs first, then the states group by group
                 if id(dst) not in late and dst is not self.hidden:
                     self._copy_in(dst, src)
-            src_hidden = tensors[[id(t) for t in bufs].index(id(self.hidden))]
-            for (b0, b1), ev in zip(self.chunks, self._ev_chunk):
-                self.hidden[b0:b1].copy_(src_hidden[b0:b1], non_blocking=True)
-                ev.record(self.copy_stream)
+            src_of = {id(dst): src for dst, src in zip(bufs, tensors)}
+            src_hidden = src_of[id(self.hidden)]
+            src_links = src_of.get(id(self.links))
+            pinned = lambda t, buf: t is not None and not t.is_cuda and t.is_pinned() and t.dtype == buf.dtype and \
+                tuple(t.shape) == tuple(buf.shape)
+            fetch = self.fetch_from_host == "all" and pinned(src_hidden, self.hidden)
+            if fetch:  # one kernel reads the real nodes' states from the host buffer
+                self.kernel.stage_inputs(self.output_length, hidden_dst=self.hidden, hidden_src=src_hidden)
+                for ev in self._ev_chunk:
+                    ev.record(self.copy_stream)
+            else:
+                for (b0, b1), ev in zip(self.chunks, self._ev_chunk):
+                    self.hidden[b0:b1].copy_(src_hidden[b0:b1], non_blocking=True)
+                    ev.record(self.copy_stream)
             self._ev_stage1.record(self.copy_stream)
+            fetch_links = self.fetch_from_host in ("links", "all") and id(self.links) in late and pinned(src_links, self.links)
             for dst, src in zip(bufs, tensors):
                 if id(dst) in late:
-                    self._copy_in(dst, src)
+                    if dst is self.links and fetch_links:  # the transitions the tree masks leave finite, nothing else
+                        self.kernel.stage_inputs(self.output_length, links_dst=self.links, links_src=src)
+                    else:
+                        self._copy_in(dst, src)
             self._ev_stage2.record(self.copy_stream)
+            self.last_load_bytes = None
+            if fetch or fetch_links:
+                lengths = src_of[id(self.output_length)].cpu()
+                self.last_load_bytes = self._fetched_bytes(tensors, lengths, fetch, fetch_links)
         self._pending = True
+        self._pending_chunked = not fetch
 
     def _stage1(self, b0=0, b1=None):
         """The projection of sentences [b0, b1) (all of them by default): a dict of [b1 - b0, ...] tensors."""
@@ -158,7 +211,7 @@ class _GraphedStep:
                 cur.wait_event(self._ev_stage2)
                 pending = False
             self._capture()
-        if pending and self.chunk_graphs:
+        if pending and self.chunk_graphs and self._pending_chunked:
             for ev, g in zip(self._ev_chunk, self.chunk_graphs):
                 cur.wait_event(ev)
                 g.replay()
@@ -187,8 +240,10 @@ class PipelinedStep:
     stream of the object whose turn it is and waits only for that object's previous run, two batches back.
     ``run`` returns that object's static outputs, which stay valid until the run after next."""
 
-    def __init__(self, make_step):
+    def __init__(self, make_step, fetch_from_host=None):
         self.steps = [make_step(), make_step()]
+        for st in self.steps:
+            st.fetch_from_host = fetch_from_host
         self.turn = 0
 
     def load(self, *tensors):
@@ -200,7 +255,7 @@ class PipelinedStep:
         return out
 
     def input_bytes(self):
-        return self.steps[0].input_bytes()
+        return self.steps[self.turn ^ 1].input_bytes()  # of the batch loaded last
 
     @property
     def kernels_per_step(self):

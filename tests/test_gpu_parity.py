@@ -1241,3 +1241,42 @@ def test_loss_step_from_link_features_matches_autograd_chain(pkg, ops, syn):
         torch.testing.assert_close(got, leaf.grad.float(), rtol=1e-3, atol=1e-3)  # the chain rounds its gradients to f16
     torch.testing.assert_close(dgates, gt.grad, rtol=1e-5, atol=1e-6)
     assert dq.abs().sum() > 0 and dkr.abs().sum() > 0
+
+
+@pytest.mark.parametrize("mode", ["links", "all"])
+def test_overlapped_load_fetching_from_host_buffers(pkg, ops, syn, mode):
+    """An overlapped load whose large inputs are fetched by the kernel that reads the pinned host buffers itself
+    (only the real nodes' states / only the transitions the tree masks leave finite) gives the step exactly what the
+    plain copies give it, batch after batch (shorter sentences after longer ones: nothing stale is read)."""
+    import importlib
+
+    runtime = importlib.import_module("pcfg_nat_b200.runtime")
+    w = syn.Workload("fh", batch=6, vocab=3000, hidden=128, src_min=3, src_max=12, hidden_std=1.0)
+    batches = [syn.make_batch(w, seed=50 + i) for i in range(4)]
+    L, T = max(b.L for b in batches), max(b.T for b in batches)
+
+    def padded(b):
+        hid = torch.randn(b.B, L, w.hidden).half()  # garbage beyond the real nodes: it must not matter
+        hid[:, :b.L] = b.hidden
+        lk = torch.full((b.B, L, 2, L), float("-inf"))
+        lk[:, :b.L, :, :b.L] = b.links
+        tg = torch.ones(b.B, T, dtype=torch.long)
+        tg[:, :b.T] = b.targets
+        return [t.contiguous().pin_memory() for t in (hid, lk, b.output_length, tg, b.target_length)]
+
+    weight = batches[0].weight.to(DEV)
+    plain = runtime.LossStep(weight, w.batch, L, T, DEV)
+    fetched = runtime.LossStep(weight, w.batch, L, T, DEV)
+    fetched.fetch_from_host = mode
+    for b in batches:
+        args = padded(b)
+        plain.load(*args)
+        want = [t.clone() for t in plain.run()]
+        fetched.load(*args, overlap=True)
+        got = fetched.run()
+        torch.cuda.synchronize()
+        for x, y in zip(got, want):
+            assert torch.equal(x, y)
+        assert fetched.input_bytes() < plain.input_bytes()
+        kernel_links = fetched.links.cpu()
+        assert torch.equal(kernel_links, args[1])  # the model's masks leave nothing finite outside what was fetched
