@@ -72,6 +72,9 @@ def parse():
                     help="timed blocks of --steps steps (0 = as many as make 0.25 s of device time, 5..50)")
     ap.add_argument("--no-subs", action="store_true",
                     help="only the headline workload: no workloads / strong / gpu_reference / drop_in records")
+    ap.add_argument("--drop-in-only", action="store_true",
+                    help="N = 1: only the drop_in record of --workload (the reference-named operators on materialised "
+                         "logits, with the log-softmax + gather kernel timed alone), printed as one JSON line")
     ap.add_argument("--no-proj-backward", action="store_true",
                     help="skip the extra measurement of the step with the projection backward")
     ap.add_argument("--nccl-reduce", action="store_true",
@@ -694,6 +697,12 @@ def run_ours(a):
         raise RuntimeError(f"workload {a.workload} has no decoder states; the benchmark runs the projection path")
     kind = batch.workload.kind
     is_loss = kind == "loss"
+    if a.drop_in_only:
+        if world > 1:
+            raise RuntimeError("--drop-in-only is a single-GPU measurement")
+        print(json.dumps({"drop_in": {a.workload: drop_in(ctx, a.workload, batch, a.steps)},
+                          "device_status": ops.read_status(dev)}), flush=True)
+        return
     # N > 1: the loss statistics are summed over the ranks inside the statistics kernel (peer stores over
     # NVLink); --nccl-reduce uses a 12-byte NCCL all-reduce after the step instead
     exchange = None

@@ -285,6 +285,53 @@ def test_logsoftmax_gather_against_oracle(ops, dtype, atol, V):
                                rtol=1e-4 if dtype == torch.float32 else 2e-3)
 
 
+@pytest.mark.parametrize("stream", ["1", "0"])
+@pytest.mark.parametrize("dtype,V", [(torch.float16, 40000), (torch.float32, 8000), (torch.float32, 40000), (torch.float16, 1000)])
+def test_logsoftmax_gather_several_rows_per_cta(ops, monkeypatch, stream, dtype, V):
+    """More rows than CTAs: the streaming kernel refills a row's chunks with the next row's bytes while it still works
+    on the row (both phases of every chunk barrier come into use); rows of one full chunk and a part, of several
+    chunks, and of less than a chunk; PCFGNAT_LSG_STREAM=0 runs the single-buffer kernel instead."""
+    monkeypatch.setenv("PCFGNAT_LSG_STREAM", stream)
+    g = torch.Generator().manual_seed(V + 1)
+    B, L, slen = 3, 250, 7
+    x = (torch.randn(B, L, V, generator=g) * 3).to(dtype)
+    tgt = torch.randint(0, V, (B, slen), generator=g)
+    sel_idx = tgt[:, None, :].expand(-1, L, -1)
+    want, probs = oracle.logsoftmax_gather(x.float().numpy(), sel_idx.numpy(), True)
+    k = ops.get_pcfg_kernel()
+    xc = x.to(DEV).clone()
+    got = k.logsoftmax_gather(xc, sel_idx.to(DEV), False)
+    np.testing.assert_allclose(got.cpu().numpy(), want, atol=1.2e-4)
+    assert torch.equal(xc.cpu(), x)
+    got2 = k.logsoftmax_gather(xc, sel_idx.to(DEV), True)
+    np.testing.assert_allclose(got2.cpu().numpy(), want, atol=1.2e-4)
+    np.testing.assert_allclose(xc.float().cpu().numpy(), probs, atol=1e-6 if dtype == torch.float32 else 1e-3,
+                               rtol=1e-4 if dtype == torch.float32 else 2e-3)
+    assert ops.read_status(DEV) == 0
+
+
+def test_logsoftmax_gather_more_selected_columns_than_threads(ops):
+    """More gathered columns per row than the streaming kernel has threads: its late gather loop, with and without
+    the softmax kept; an index out of range gives NaN and the status bit in both."""
+    g = torch.Generator().manual_seed(5)
+    B, L, V, slen = 2, 200, 2000, 700
+    x = (torch.randn(B, L, V, generator=g) * 2).half()
+    tgt = torch.randint(0, V, (B, slen), generator=g)
+    sel_idx = tgt[:, None, :].expand(-1, L, -1)
+    want, _ = oracle.logsoftmax_gather(x.float().numpy(), sel_idx.numpy(), True)
+    k = ops.get_pcfg_kernel()
+    for keep in (False, True):
+        got = k.logsoftmax_gather(x.to(DEV).clone(), sel_idx.to(DEV), keep)
+        np.testing.assert_allclose(got.cpu().numpy(), want, atol=1.2e-4)
+    assert ops.read_status(DEV) == 0
+    for n_sel in (700, 9):  # the late and the early gather
+        bad = tgt[:, :n_sel].clone()
+        bad[1, 3] = V
+        got = k.logsoftmax_gather(x.to(DEV).clone(), bad[:, None, :].expand(-1, L, -1).to(DEV), False)
+        assert torch.isnan(got[1, :, 3]).all() and torch.isfinite(got[0]).all()
+        assert ops.read_status(DEV) & 4  # PCFGNAT_STATUS_BAD_INDEX
+
+
 def test_logsoftmax_gather_reference_golden_and_autograd(ops):
     g = _g("ref_logsoftmax_gather.npz")
     k = ops.get_pcfg_kernel()
