@@ -360,9 +360,10 @@ def measure(ctx, name, batch, global_sentences, steps, warm, blocks=None, exchan
     block(3, True)
     serial_ms = [block(steps, True) for _ in range(min(nb, 5))]  # load -> run -> read-back, one batch at a time
     # the end-to-end figure: two step objects in turn, so that batch i + 1 is copied while batch i is computed
-    # several GPUs pull from one host: the bus is the bottleneck, so the transitions are fetched by the kernel that
-    # moves only the entries the kernels read; on one GPU the copy engines alone overlap better
-    fetch = a.fetch if a.fetch != "auto" else ("links" if ctx.world > 1 else "none")
+    # eight GPUs pulling from one host: the bus is the bottleneck (24 GB/s per rank against 44 alone), so the
+    # transitions are fetched by the kernel that moves only the entries the kernels read (measured at N = 8: 984k
+    # sentences/s against 761k with copies alone); up to four GPUs the copy engines alone are as fast or faster
+    fetch = a.fetch if a.fetch != "auto" else ("links" if ctx.world > 4 else "none")
     pipe = ctx.runtime.PipelinedStep(lambda: make_step(ctx.runtime, batch, weight, dev, not a.no_graph, a.copy_chunks,
                                                        exchange, **shape)[0],
                                      fetch_from_host=None if fetch == "none" else fetch) if not a.no_graph else None

@@ -204,6 +204,18 @@ int pcfgnat_proj_dlogits(const void *hidden, const void *weight, const int64_t *
                          const int64_t *target_length, const float *lse, const float *grad_match, int B, int L, int T, int V,
                          int H, void *dlogits, void *workspace, size_t workspace_bytes, int *status, void *stream);
 
+/* pcfgnat_proj_dlogits for the real graph nodes only: row i of dlogits [capacity][V] belongs to the i-th real node of
+ * the batch (sentence after sentence, nodes l < m_b), so that the caller's two GEMMs run over sum_b m_b rows
+ * instead of B*L.  row_index [capacity] i64 receives the padded position b * L + l of every compact row (0 beyond
+ * the last one) for the gather of the states and the scatter of their gradient, n_rows (device, may be null) their
+ * number.  capacity is normally sum_b m_b as the host knows it (at most B*L); a batch with more real nodes than
+ * capacity sets PCFGNAT_STATUS_BAD_LENGTH and writes only the first capacity rows. */
+int pcfgnat_proj_dlogits_compact(const void *hidden, const void *weight, const int64_t *targets,
+                                 const int64_t *output_length, const int64_t *target_length, const float *lse,
+                                 const float *grad_match, int B, int L, int T, int V, int H, int capacity, void *dlogits,
+                                 int64_t *row_index, int *n_rows, void *workspace, size_t workspace_bytes, int *status,
+                                 void *stream);
+
 /* The three numbers the criterion's scalar loss is formed from, in one launch
  * (fs_plugins/criterions/nat_pcfg_loss.py:117-135: sentences whose loss is infinite or NaN are
  * counted and left out, the others are divided by their target length):
@@ -312,6 +324,17 @@ int pcfgnat_links_from_scores(const float *ac, const float *bc, const float *qm,
  * rows of dst are left as they are: a staging buffer filled with -inf once stays valid.  Host plumbing for
  * callers that stage batches from host memory: it halves the bytes the largest input sends over PCIe. */
 int pcfgnat_copy_links_main_rows(void *dst, const void *src, int B, int L, int max_left, void *stream);
+
+/* Copies the rows of the real graph nodes of sentences [b0, b1) from src to dst, both [B][L][row_bytes]:
+ * rows l < m_b with m_b = host_lengths[b] clamped to [0, L]; one cudaMemcpyAsync per run of adjacent rows on
+ * `stream`, through the copy engine, no kernel.  A copy costs the host several microseconds, so with max_copies > 0
+ * at most that many are issued: runs are joined across the smallest gaps of padding rows, which are then sent along
+ * (0 = one copy per sentence, or per group of sentences that fill their L rows).  rows_sent (host, may be NULL)
+ * receives the number of rows copied.  host_lengths [B] int64 is a HOST array, read before the call returns.  Padding rows of dst that are not sent keep what they held (no kernel of
+ * this library reads them).  Host plumbing with no counterpart in the reference, whose inputs are made on the
+ * device: for a training batch it sends 11 to 13 MB of decoder states where the padded tensor has 15 MB. */
+int pcfgnat_copy_real_rows(void *dst, const void *src, const int64_t *host_lengths, int b0, int b1, int L,
+                           size_t row_bytes, int max_copies, int64_t *rows_sent, void *stream);
 
 /* Fetches a batch's large inputs from HOST memory with one kernel that reads the host buffers itself (mapped pinned
  * memory, e.g. cudaHostAlloc / torch pin_memory; device memory works too), and only what the kernels of this library

@@ -28,11 +28,13 @@ SIGNATURES = {
     "pcfgnat_proj_workspace_bytes": (c_size, [c_int] * 4),
     "pcfgnat_proj_logsoftmax_gather": (c_int, [c_void] * 5 + [c_int] * 5 + [c_void] * 5 + [c_size] + [c_void] * 2),
     "pcfgnat_proj_dlogits": (c_int, [c_void] * 7 + [c_int] * 5 + [c_void] * 2 + [c_size] + [c_void] * 2),
+    "pcfgnat_proj_dlogits_compact": (c_int, [c_void] * 7 + [c_int] * 6 + [c_void] * 4 + [c_size] + [c_void] * 2),
     "pcfgnat_links_gather_features": (c_int, [c_void] * 3 + [c_int] + [c_void] + [c_int] * 5 + [c_void] * 4),
     "pcfgnat_links_scores": (c_int, [c_void] * 3 + [c_int] * 4 + [c_void] * 3),
     "pcfgnat_links_backward": (c_int, [c_void] * 13 + [c_int] * 6 + [c_void] * 8),
     "pcfgnat_links_from_scores": (c_int, [c_void] * 11 + [c_int] * 6 + [c_void] * 2),
     "pcfgnat_copy_links_main_rows": (c_int, [c_void] * 2 + [c_int] * 3 + [c_void]),
+    "pcfgnat_copy_real_rows": (c_int, [c_void] * 3 + [c_int] * 3 + [c_size] + [c_int] + [c_void] * 2),
     "pcfgnat_stage_inputs": (c_int, [c_void] * 2 + [c_int] + [c_void] * 3 + [c_int] * 3 + [c_void]),
     "pcfgnat_loss_stats": (c_int, [c_void] * 2 + [c_int] + [c_void] * 2),
     "pcfgnat_loss_stats_exchange": (c_int, [c_void] * 2 + [c_int] + [c_void] + [c_int] * 2 + [c_void] * 3),

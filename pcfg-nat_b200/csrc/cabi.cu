@@ -1,4 +1,8 @@
 // extern "C" entry points declared in include/pcfgnat.h: argument checks, then launch.
+#include <algorithm>
+#include <utility>
+#include <vector>
+
 #include "common.cuh"
 
 #include <cstdlib>
@@ -323,6 +327,57 @@ int pcfgnat_copy_links_main_rows(void *dst, const void *src, int B, int L, int m
     return PCFGNAT_OK;
 }
 
+int pcfgnat_copy_real_rows(void *dst, const void *src, const int64_t *host_lengths, int b0, int b1, int L,
+                           size_t row_bytes, int max_copies, int64_t *rows_sent, void *stream) {
+    if (rows_sent) *rows_sent = 0;
+    if (b0 < 0 || b1 < b0 || L < 1 || row_bytes == 0 || max_copies < 0) return PCFGNAT_ERR_INVALID_ARGUMENT;
+    if (b1 > b0 && (!dst || !src || !host_lengths)) return PCFGNAT_ERR_INVALID_ARGUMENT;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    unsigned char *d = static_cast<unsigned char *>(dst);
+    const unsigned char *s = static_cast<const unsigned char *>(src);
+    // runs of rows to send: one per non-empty sentence, as (first row, rows), in rows of the [B * L] view
+    std::vector<std::pair<int64_t, int64_t>> runs;
+    runs.reserve((size_t)(b1 - b0));
+    for (int b = b0; b < b1; b++) {
+        int64_t m = host_lengths[b];
+        m = m < 0 ? 0 : (m > L ? L : m);
+        if (m == 0) continue;
+        const int64_t start = (int64_t)b * L;
+        if (!runs.empty() && runs.back().first + runs.back().second == start) runs.back().second += m;
+        else runs.emplace_back(start, m);
+    }
+    // a copy costs the host several microseconds: with more runs than max_copies, neighbours are joined across the
+    // smallest gaps of padding rows (which are then sent along) until max_copies runs are left
+    if (max_copies > 0 && runs.size() > (size_t)max_copies) {
+        std::vector<int64_t> gaps(runs.size() - 1);
+        for (size_t i = 0; i + 1 < runs.size(); i++) gaps[i] = runs[i + 1].first - (runs[i].first + runs[i].second);
+        std::vector<int64_t> sorted(gaps);
+        const size_t join = runs.size() - (size_t)max_copies;  // that many gaps go
+        std::nth_element(sorted.begin(), sorted.begin() + (join - 1), sorted.end());
+        const int64_t limit = sorted[join - 1];
+        size_t below = 0;
+        for (int64_t g : gaps) below += g < limit;
+        size_t at_limit = join - below;  // of the gaps equal to the limit, only this many are joined
+        std::vector<std::pair<int64_t, int64_t>> merged;
+        merged.reserve((size_t)max_copies);
+        merged.push_back(runs[0]);
+        for (size_t i = 0; i + 1 < runs.size(); i++) {
+            bool joined = gaps[i] < limit;
+            if (!joined && gaps[i] == limit && at_limit) joined = true, at_limit--;
+            if (joined) merged.back().second = runs[i + 1].first + runs[i + 1].second - merged.back().first;
+            else merged.push_back(runs[i + 1]);
+        }
+        runs.swap(merged);
+    }
+    for (const auto &r : runs) {
+        const size_t off = (size_t)r.first * row_bytes;
+        if (cudaMemcpyAsync(d + off, s + off, (size_t)r.second * row_bytes, cudaMemcpyDefault, st) != cudaSuccess)
+            return PCFGNAT_ERR_CUDA;
+        if (rows_sent) *rows_sent += r.second;
+    }
+    return PCFGNAT_OK;
+}
+
 int pcfgnat_stage_inputs(const void *hidden_src, void *hidden_dst, int row_bytes, const float *links_src,
                          float *links_dst, const int64_t *output_length, int B, int L, int max_left, void *stream) {
     if (max_left != 1) return PCFGNAT_ERR_UNSUPPORTED;
@@ -356,6 +411,21 @@ int pcfgnat_proj_dlogits(const void *hidden, const void *weight, const int64_t *
     if (target_length != nullptr && output_length == nullptr) return PCFGNAT_ERR_INVALID_ARGUMENT;
     return launch_proj_dlogits(hidden, weight, targets, output_length, target_length, lse, grad_match, B, L, T, V, H,
                                dlogits, workspace, workspace_bytes, status, static_cast<cudaStream_t>(stream));
+}
+
+int pcfgnat_proj_dlogits_compact(const void *hidden, const void *weight, const int64_t *targets,
+                                 const int64_t *output_length, const int64_t *target_length, const float *lse,
+                                 const float *grad_match, int B, int L, int T, int V, int H, int capacity, void *dlogits,
+                                 int64_t *row_index, int *n_rows, void *workspace, size_t workspace_bytes, int *status,
+                                 void *stream) {
+    if (B < 0 || L < 1 || T < 1 || V < 1 || H < 1 || capacity < 0) return PCFGNAT_ERR_INVALID_ARGUMENT;
+    if ((long long)B * L > (1ll << 30)) return PCFGNAT_ERR_TOO_LARGE;
+    if (B && (!hidden || !weight || !targets || !lse || !grad_match || !workspace || !row_index)) return PCFGNAT_ERR_INVALID_ARGUMENT;
+    if (B && capacity && !dlogits) return PCFGNAT_ERR_INVALID_ARGUMENT;
+    if (target_length != nullptr && output_length == nullptr) return PCFGNAT_ERR_INVALID_ARGUMENT;
+    return launch_proj_dlogits(hidden, weight, targets, output_length, target_length, lse, grad_match, B, L, T, V, H,
+                               dlogits, workspace, workspace_bytes, status, static_cast<cudaStream_t>(stream), capacity,
+                               row_index, n_rows);
 }
 
 int pcfgnat_links_gather_features(const void *q, const void *kl, const void *kr, int dtype, const int *nodes, int M,

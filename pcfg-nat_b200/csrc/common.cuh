@@ -196,6 +196,7 @@ int launch_links_from_scores(const float *ac, const float *bc, const float *qm, 
                              int D, float *links, cudaStream_t st);
 int launch_proj_dlogits(const void *hidden, const void *weight, const int64_t *targets, const int64_t *ol,
                         const int64_t *tl, const float *lse, const float *grad_match, int B, int L, int T, int V, int H,
-                        void *dlogits, void *workspace, size_t ws_bytes, int *status, cudaStream_t st);
+                        void *dlogits, void *workspace, size_t ws_bytes, int *status, cudaStream_t st, int capacity = 0,
+                        int64_t *row_index = nullptr, int *n_rows_out = nullptr);
 
 }  // namespace pcfgnat

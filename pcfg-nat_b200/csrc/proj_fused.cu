@@ -329,7 +329,9 @@ struct GradArgs {  // kGradLogits only
     const float *lse;        // [B*L] from the forward
     const float *gmatch;     // [B*L][T] gradient of the emissions
     const int64_t *ol, *tl;  // lengths (EOS masking), or null
-    __nv_bfloat16 *dlogits;  // [B*L][V]
+    __nv_bfloat16 *dlogits;  // [B*L][V], or [capacity][V] when compact
+    int compact;             // rows in compact order (row i = the i-th real node of the batch) instead of padded order
+    int capacity;            // compact: rows the buffer holds; a batch with more real nodes is flagged, not written
 };
 
 // PAIR: launched as clusters of two CTAs that share every W tile (tcgen05 cta_group::2).  A unit is then two
@@ -601,8 +603,8 @@ __global__ void __launch_bounds__(PROJ_THREADS, 1)
                             p++;
                             next_tok = p < T ? __ldg(my_tok + p) : INT_MAX;
                         }
-                        if (row_ok) {
-                            __nv_bfloat16 *dst = ga.dlogits + (size_t)row * V + col0;
+                        if (row_ok && (!ga.compact || cr < ga.capacity)) {
+                            __nv_bfloat16 *dst = ga.dlogits + (size_t)(ga.compact ? cr : row) * V + col0;
                             if (col0 + 32 <= V && (V & 7) == 0) {
                                 uint32_t pk[16];
 #pragma unroll
@@ -993,9 +995,23 @@ __global__ void proj_zero_padding_rows_kernel(const int *__restrict__ prefix, in
     }
 }
 
+// Compact order: the padded index b * L + l of every compact row for the caller's gather / scatter of the states and
+// their gradient, zero beyond the batch's real nodes; a batch with more real nodes than the buffer holds is flagged.
+__global__ void proj_row_index_kernel(const int *__restrict__ row_src, const int *__restrict__ n_rows, int capacity,
+                                      int64_t *row_index, int *n_rows_out, int *status) {
+    const int n = *n_rows;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < capacity; i += gridDim.x * blockDim.x)
+        row_index[i] = i < n ? row_src[i] : 0;
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        if (n_rows_out) *n_rows_out = n;
+        if (n > capacity) flag(status, PCFGNAT_STATUS_BAD_LENGTH);
+    }
+}
+
 int launch_proj_dlogits(const void *hidden, const void *weight, const int64_t *targets, const int64_t *ol,
                         const int64_t *tl, const float *lse, const float *grad_match, int B, int L, int T, int V, int H,
-                        void *dlogits, void *workspace, size_t ws_bytes, int *status, cudaStream_t st) {
+                        void *dlogits, void *workspace, size_t ws_bytes, int *status, cudaStream_t st, int capacity,
+                        int64_t *row_index, int *n_rows_out) {
     const int N = B * L;
     if (N == 0) return PCFGNAT_OK;
     if (H % BK != 0 || H > KC_MAX * BK) return PCFGNAT_ERR_UNSUPPORTED;
@@ -1009,9 +1025,14 @@ int launch_proj_dlogits(const void *hidden, const void *weight, const int64_t *t
     if (!make_map(&map_w, weight, (uint64_t)V, (uint64_t)H, geo.pair ? BN / 2 : BN)) return PCFGNAT_ERR_CUDA;
     proj_prepare_kernel<<<B, 128, 0, st>>>(ol, targets, B, L, T, V, w.prefix, w.row_src, w.n_rows, w.stok, w.sslot, status);
     __nv_bfloat16 *dl = static_cast<__nv_bfloat16 *>(dlogits);
-    if (ol) proj_zero_padding_rows_kernel<<<dim3(B, 8), 256, 0, st>>>(w.prefix, L, V, dl);
+    const int compact = row_index != nullptr;
+    if (compact)
+        proj_row_index_kernel<<<(capacity + 1023) / 1024 > 0 ? (capacity + 1023) / 1024 : 1, 1024, 0, st>>>(
+            w.row_src, w.n_rows, capacity, row_index, n_rows_out, status);
+    else if (ol)
+        proj_zero_padding_rows_kernel<<<dim3(B, 8), 256, 0, st>>>(w.prefix, L, V, dl);
     const size_t smem = (size_t)KC_MAX * A_CHUNK_BYTES + (size_t)NSTAGE * B_STAGE_BYTES + 1024;
-    const GradArgs ga = {lse, grad_match, ol, tl, dl};
+    const GradArgs ga = {lse, grad_match, ol, tl, dl, compact, capacity};
     return launch_proj_kernel<kGradLogits>(geo, smem, st, map_w, static_cast<const __half *>(hidden), w.row_src, w.n_rows, V,
                                            H / BK, L, T, w.stok, w.sslot, nullptr, w.partials, ga, status);
 }

@@ -319,10 +319,16 @@ class _Kernel:
         return out
 
     @staticmethod
-    def proj_dlogits(hidden, weight, targets, output_length, target_length, lse, grad_match):
+    def proj_dlogits(hidden, weight, targets, output_length, target_length, lse, grad_match, n_rows=None, out=None,
+                     row_index_out=None):
         """d loss / d logits of ``proj_logsoftmax_gather`` as bf16 [B * L, V], the logits recomputed on the
         tensor cores tile by tile (nothing of size [B, L, V] was kept from the forward).  ``lse`` [B, L] is the
-        forward's ``want_lse`` output, ``grad_match`` [B, L, T] the gradient of its ``match``."""
+        forward's ``want_lse`` output, ``grad_match`` [B, L, T] the gradient of its ``match``.
+
+        With ``n_rows`` (a host integer: the real graph nodes of the batch, sum of the output lengths) the result is
+        compact: (d-logits [n_rows, V] of the real nodes only, row_index [n_rows] int64 = their positions b * L + l),
+        so that the two GEMMs that follow skip the padding rows.  ``out`` / ``row_index_out``: buffers of at least
+        that many rows to write into (a step object's static ones)."""
         _require_cuda()
         if hidden.dtype != torch.float16 or weight.dtype != torch.float16 or not (hidden.is_cuda and weight.is_cuda):
             raise RuntimeError("hidden and weight must be float16 CUDA tensors")
@@ -345,7 +351,22 @@ class _Kernel:
         ptr = lambda t: t.data_ptr() if t is not None else None
         with torch.cuda.device(dev):
             ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=dev)
-            dl = torch.empty((B * L, V), dtype=torch.bfloat16, device=dev)
+            if n_rows is not None:
+                n = int(n_rows)
+                if n < 0 or n > B * L:
+                    raise RuntimeError("n_rows must be between 0 and batch * prelen")
+                dl = out if out is not None else torch.empty((n, V), dtype=torch.bfloat16, device=dev)
+                idx = row_index_out if row_index_out is not None else torch.empty((n,), dtype=torch.int64, device=dev)
+                if dl.dtype != torch.bfloat16 or dl.dim() != 2 or dl.shape[1] != V or dl.shape[0] < n or \
+                        not dl.is_contiguous() or idx.dtype != torch.int64 or idx.numel() < n:
+                    raise RuntimeError("out must be a contiguous bfloat16 [>= n_rows, V], row_index_out int64 [>= n_rows]")
+                rc = l.pcfgnat_proj_dlogits_compact(hidden.data_ptr(), weight.data_ptr(), targets.data_ptr(), ptr(ol),
+                                                    ptr(tl), lse.data_ptr(), g.data_ptr(), B, L, T, V, H, n,
+                                                    dl.data_ptr(), idx.data_ptr(), None, ws.data_ptr(), nbytes,
+                                                    _status_ptr(dev), _stream(dev))
+                _cabi.check(rc, "pcfgnat_proj_dlogits_compact")
+                return dl[:n], idx[:n]
+            dl = out if out is not None else torch.empty((B * L, V), dtype=torch.bfloat16, device=dev)
             rc = l.pcfgnat_proj_dlogits(hidden.data_ptr(), weight.data_ptr(), targets.data_ptr(), ptr(ol), ptr(tl),
                                         lse.data_ptr(), g.data_ptr(), B, L, T, V, H, dl.data_ptr(), ws.data_ptr(), nbytes,
                                         _status_ptr(dev), _stream(dev))
@@ -469,6 +490,34 @@ class _Kernel:
         with torch.cuda.device(dst.device):
             rc = _cabi.lib().pcfgnat_copy_links_main_rows(dst.data_ptr(), src.data_ptr(), B, L, 1, _stream(dst.device))
         _cabi.check(rc, "pcfgnat_copy_links_main_rows")
+
+    @staticmethod
+    def copy_real_rows(dst, src, host_lengths, b0=0, b1=None, max_copies=0):
+        """Copies the rows of the real graph nodes (l < length, clamped to [0, L]) of sentences [b0, b1) of ``src``
+        [B, L, ...] into ``dst`` of the same shape on the current stream with copy-engine copies, no kernel: one per
+        sentence, or at most ``max_copies`` (> 0), joined across the smallest gaps of padding rows.  Returns the
+        number of rows sent.  ``host_lengths`` [B] int64 lives in host memory.  Rows of ``dst`` that are not sent
+        keep what they held."""
+        _require_cuda()
+        if not dst.is_cuda or dst.dim() < 2 or tuple(src.shape) != tuple(dst.shape) or src.dtype != dst.dtype or \
+                not (dst.is_contiguous() and src.is_contiguous()):
+            raise RuntimeError("dst must be a contiguous CUDA tensor [batch, prelen, ...] and src of its shape and type")
+        if host_lengths.is_cuda or host_lengths.dtype != torch.int64 or tuple(host_lengths.shape) != (dst.shape[0],) or \
+                not host_lengths.is_contiguous():
+            raise RuntimeError("host_lengths must be a contiguous int64 host tensor [batch]")
+        B, L = dst.shape[0], dst.shape[1]
+        b1 = B if b1 is None else b1
+        if not 0 <= b0 <= b1 <= B:
+            raise RuntimeError("sentence range out of bounds")
+        row_bytes = dst[0, 0].numel() * dst.element_size()
+        import ctypes
+        sent = ctypes.c_int64(0)
+        with torch.cuda.device(dst.device):
+            rc = _cabi.lib().pcfgnat_copy_real_rows(dst.data_ptr(), src.data_ptr(), host_lengths.data_ptr(), b0, b1, L,
+                                                    row_bytes, int(max_copies), ctypes.addressof(sent),
+                                                    _stream(dst.device))
+        _cabi.check(rc, "pcfgnat_copy_real_rows")
+        return int(sent.value)
 
     @staticmethod
     def stage_inputs(output_length, hidden_dst=None, hidden_src=None, links_dst=None, links_src=None):
@@ -874,23 +923,35 @@ class ProjLogsoftmaxGatherFunc(Function):
     the softmax to keep them for the backward."""
 
     @staticmethod
-    def forward(ctx, hidden, weight, targets, output_length, target_length):
+    def forward(ctx, hidden, weight, targets, output_length, target_length, n_rows=None):
         out = get_pcfg_kernel().proj_logsoftmax_gather(hidden, weight, targets, output_length, target_length,
                                                        want_lse=True)
         ctx.save_for_backward(hidden, weight, targets, output_length, target_length, out["lse"])
+        ctx.n_rows = n_rows if output_length is not None else None
         return out["match"]
 
     @staticmethod
     def backward(ctx, grad_match):
         hidden, weight, targets, ol, tl, lse = ctx.saved_tensors
         B, L, H = hidden.shape
-        dl = get_pcfg_kernel().proj_dlogits(hidden, weight, targets, ol, tl, lse, grad_match.contiguous())
+        k = get_pcfg_kernel()
         d_hidden = d_weight = None
-        if ctx.needs_input_grad[0]:
-            d_hidden = (dl @ weight.to(torch.bfloat16)).view(B, L, H).to(hidden.dtype)
-        if ctx.needs_input_grad[1]:
-            d_weight = (dl.t() @ hidden.reshape(B * L, H).to(torch.bfloat16)).to(weight.dtype)
-        return d_hidden, d_weight, None, None, None
+        if ctx.n_rows is None:  # every row of the padded tensor
+            dl = k.proj_dlogits(hidden, weight, targets, ol, tl, lse, grad_match.contiguous())
+            if ctx.needs_input_grad[0]:
+                d_hidden = (dl @ weight.to(torch.bfloat16)).view(B, L, H).to(hidden.dtype)
+            if ctx.needs_input_grad[1]:
+                d_weight = (dl.t() @ hidden.reshape(B * L, H).to(torch.bfloat16)).to(weight.dtype)
+        else:  # the real graph nodes only
+            dl, idx = k.proj_dlogits(hidden, weight, targets, ol, tl, lse, grad_match.contiguous(), n_rows=ctx.n_rows)
+            if ctx.needs_input_grad[0]:
+                d_hidden = torch.zeros((B * L, H), dtype=hidden.dtype, device=hidden.device)
+                d_hidden.index_copy_(0, idx, (dl @ weight.to(torch.bfloat16)).to(hidden.dtype))
+                d_hidden = d_hidden.view(B, L, H)
+            if ctx.needs_input_grad[1]:
+                rows = hidden.reshape(B * L, H).index_select(0, idx).to(torch.bfloat16)
+                d_weight = (dl.t() @ rows).to(weight.dtype)
+        return d_hidden, d_weight, None, None, None, None
 
 
 class ExtractLinksFunc(Function):
@@ -937,9 +998,11 @@ def force_emit_mask(match_all_eos_masked, matchmask, keep_word_mask):
     return ForceEmitFunc.apply(match_all_eos_masked, matchmask, keep_word_mask)
 
 
-def proj_logsoftmax_gather_with_grad(hidden, weight, targets, output_length=None, target_length=None):
-    """``match`` [B, L, T] of ``proj_logsoftmax_gather``, differentiable with respect to hidden and weight."""
-    return ProjLogsoftmaxGatherFunc.apply(hidden, weight, targets, output_length, target_length)
+def proj_logsoftmax_gather_with_grad(hidden, weight, targets, output_length=None, target_length=None, n_rows=None):
+    """``match`` [B, L, T] of ``proj_logsoftmax_gather``, differentiable with respect to hidden and weight.
+    ``n_rows``: the number of real graph nodes of the batch (sum of ``output_length``) where the host knows it; the
+    backward then forms d-logits and runs its two GEMMs over those rows only instead of all B * L."""
+    return ProjLogsoftmaxGatherFunc.apply(hidden, weight, targets, output_length, target_length, n_rows)
 
 
 def proj_logsoftmax_gather(hidden, weight, targets=None, output_length=None, target_length=None, want_max=False,

@@ -667,10 +667,12 @@ def test_fused_projection_against_torch(proj_pair, ops, syn, B, L, T, V, H, std)
     assert torch.equal(out3["argmax"], out["argmax"]) and torch.equal(out3["max_lprob"], out["max_lprob"])
 
 
+@pytest.mark.parametrize("compact", [False, True])
 @pytest.mark.parametrize("V,H,std", [(1000, 64, 1.0), (4104, 128, 0.3), (997, 64, 1.0)])
-def test_fused_projection_backward_against_torch(proj_pair, ops, syn, V, H, std):
+def test_fused_projection_backward_against_torch(proj_pair, ops, syn, V, H, std, compact):
     """Gradients of the fused projection (logits recomputed on the tensor cores, bf16 d-logits, two GEMMs)
-    against float32 autograd of the same expression."""
+    against float32 autograd of the same expression; with the d-logits of every padded row and (compact) of the
+    real graph nodes only."""
     w = syn.Workload("pb", batch=5, vocab=V, hidden=H, src_min=8, src_max=40, hidden_std=std)
     b = syn.make_batch(w, seed=V)
     g = torch.Generator().manual_seed(1)
@@ -679,7 +681,8 @@ def test_fused_projection_backward_against_torch(proj_pair, ops, syn, V, H, std)
     hid = b.hidden.to(DEV).requires_grad_(True)
     wt = b.weight.to(DEV).requires_grad_(True)
     ol, tl = b.output_length.to(DEV), b.target_length.to(DEV)
-    match = ops.proj_logsoftmax_gather_with_grad(hid, wt, b.targets.to(DEV), ol, tl)
+    match = ops.proj_logsoftmax_gather_with_grad(hid, wt, b.targets.to(DEV), ol, tl,
+                                                 n_rows=int(b.output_length.sum()) if compact else None)
     fin = torch.isfinite(match)
     (match[fin] * gm.to(DEV)[fin]).sum().backward()
     # float32 reference of the same expression
@@ -699,6 +702,72 @@ def test_fused_projection_backward_against_torch(proj_pair, ops, syn, V, H, std)
         assert float((got - want).abs().max()) < 3e-2 * float(want.abs().max()) + 1e-3
     assert float(hid.grad[~rows].abs().sum()) == 0.0
     assert ops.read_status(DEV) == 0
+
+
+def test_loss_step_with_projection_backward_matches_autograd_path(pkg, ops, syn):
+    """LossStep(proj_backward=True): d hidden and d weight (compact d-logits in the graph, the two GEMMs after it)
+    against the differentiable operator fed with the step's own emission gradient; two batches with different
+    numbers of real nodes through the same step object."""
+    import importlib
+    runtime = importlib.import_module("pcfg_nat_b200.runtime")
+    w = syn.Workload("pbs", batch=6, vocab=1000, hidden=64, src_min=6, src_max=30, hidden_std=1.0)
+    batches = [syn.make_batch(w, seed=seed) for seed in (31, 32)]
+    B, L, T = batches[0].B, max(b.L for b in batches), max(b.T for b in batches)
+    weight = batches[0].weight.to(DEV)
+    step = runtime.LossStep(weight, B, L, T, DEV, use_graph=True, proj_backward=True)
+    assert int(batches[0].output_length.sum()) != int(batches[1].output_length.sum())
+    for b in batches:
+        hidden = torch.zeros(B, L, b.hidden.shape[2], dtype=b.hidden.dtype)
+        hidden[:, :b.L] = b.hidden
+        links = torch.full((B, L, 2, L), float("-inf"))
+        links[:, :b.L, :, :b.L] = b.links
+        targets = torch.ones(B, T, dtype=torch.int64)
+        targets[:, :b.T] = b.targets
+        step.load(hidden, links, b.output_length, targets, b.target_length)
+        stats, mg, lg, loss, d_hidden, d_weight = step.run()
+        torch.cuda.synchronize()
+        assert torch.isfinite(loss).all()
+        hid = hidden.to(DEV).requires_grad_(True)
+        wt = weight.clone().requires_grad_(True)
+        ol = b.output_length.to(DEV)
+        match = ops.proj_logsoftmax_gather_with_grad(hid, wt, targets.to(DEV), ol, b.target_length.to(DEV))
+        fin = torch.isfinite(match)
+        (match[fin] * mg[fin]).sum().backward()
+        for got, want in ((d_hidden.float(), hid.grad.float()), (d_weight.float(), wt.grad.float())):
+            assert float((got - want).norm() / want.norm()) < 2e-3
+        rows = torch.arange(L, device=DEV)[None, :] < ol[:, None]
+        assert float(d_hidden[~rows].abs().sum()) == 0.0
+    assert ops.read_status(DEV) == 0
+
+
+def test_copy_real_rows_sends_the_real_nodes_only(ops):
+    """pcfgnat_copy_real_rows: rows l < length arrive, the others keep what they held; lengths beyond the tensor
+    and below zero are clamped; full sentences next to each other go as one copy; a sentence range."""
+    k = ops.get_pcfg_kernel()
+    g = torch.Generator().manual_seed(3)
+    B, L, H = 7, 12, 40
+    src = torch.randn(B, L, H, generator=g).half().pin_memory()
+    lengths = torch.tensor([3, 12, 12, 0, 20, -4, 5])
+    dst = torch.full((B, L, H), 7.0, dtype=torch.float16, device=DEV)
+    assert k.copy_real_rows(dst, src, lengths) == 3 + 12 + 12 + 12 + 5
+    torch.cuda.synchronize()
+    m = lengths.clamp(0, L)
+    for b in range(B):
+        assert torch.equal(dst[b, :m[b]].cpu(), src[b, :m[b]])
+        assert (dst[b, m[b]:] == 7).all()
+    # at most 2 copies: runs are rows [0,3), [12,36), [48,60), [72,77); the gaps of 9 and 12 rows are closed first
+    dst.fill_(7.0)
+    sent = k.copy_real_rows(dst, src, lengths, max_copies=2)
+    torch.cuda.synchronize()
+    flat_d, flat_s = dst.view(B * L, H).cpu(), src.view(B * L, H)
+    assert sent == 60 + 5 and torch.equal(flat_d[:60], flat_s[:60]) and torch.equal(flat_d[72:77], flat_s[72:77])
+    assert (flat_d[60:72] == 7).all() and (flat_d[77:] == 7).all()
+    dst.fill_(7.0)
+    k.copy_real_rows(dst, src, lengths, 1, 3)
+    torch.cuda.synchronize()
+    assert torch.equal(dst[1:3].cpu(), src[1:3]) and (dst[0] == 7).all() and (dst[3:] == 7).all()
+    with pytest.raises(RuntimeError, match="host"):
+        k.copy_real_rows(dst, src, lengths.to(DEV))
 
 
 def test_fused_projection_flags_bad_targets(ops):
