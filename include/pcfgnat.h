@@ -216,6 +216,18 @@ int pcfgnat_proj_dlogits_compact(const void *hidden, const void *weight, const i
                                  int64_t *row_index, int *n_rows, void *workspace, size_t workspace_bytes, int *status,
                                  void *stream);
 
+/* The two matrix products that finish the backward of the projection, on the tcgen05 tensor cores (bf16 operands,
+ * float32 accumulation), in place of autograd's GEMMs of nn.Linear behind DagLogsoftmaxGatherFunc.backward
+ * (fs_plugins/custom_ops/pcfg_loss.py:168-180, models/glat_decomposed_with_link_two_hands_tri_pcfg.py:237):
+ *   d_rows   [n][H] f32 = dlogits [n][V] . weight_bf16 [V][H]
+ *   d_weight [V][H] f32 = dlogits^T . rows_bf16 [n][H]
+ * dlogits [n][V] bf16 as pcfgnat_proj_dlogits(_compact) writes it, rows_bf16 the decoder states of the same n rows.
+ * Either output may be NULL (that product is skipped).  V and H must be multiples of 8 and all pointers 16-byte
+ * aligned (PCFGNAT_ERR_UNSUPPORTED / _INVALID_ARGUMENT otherwise); n is a host value, so the call cannot be part
+ * of a captured graph that is replayed for batches with other row counts. */
+int pcfgnat_proj_backward_gemms(const void *dlogits, const void *weight_bf16, const void *rows_bf16, int n, int V, int H,
+                                float *d_rows, float *d_weight, int *status, void *stream);
+
 /* The three numbers the criterion's scalar loss is formed from, in one launch
  * (fs_plugins/criterions/nat_pcfg_loss.py:117-135: sentences whose loss is infinite or NaN are
  * counted and left out, the others are divided by their target length):

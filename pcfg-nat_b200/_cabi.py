@@ -29,6 +29,7 @@ SIGNATURES = {
     "pcfgnat_proj_logsoftmax_gather": (c_int, [c_void] * 5 + [c_int] * 5 + [c_void] * 5 + [c_size] + [c_void] * 2),
     "pcfgnat_proj_dlogits": (c_int, [c_void] * 7 + [c_int] * 5 + [c_void] * 2 + [c_size] + [c_void] * 2),
     "pcfgnat_proj_dlogits_compact": (c_int, [c_void] * 7 + [c_int] * 6 + [c_void] * 4 + [c_size] + [c_void] * 2),
+    "pcfgnat_proj_backward_gemms": (c_int, [c_void] * 3 + [c_int] * 3 + [c_void] * 4),
     "pcfgnat_links_gather_features": (c_int, [c_void] * 3 + [c_int] + [c_void] + [c_int] * 5 + [c_void] * 4),
     "pcfgnat_links_scores": (c_int, [c_void] * 3 + [c_int] * 4 + [c_void] * 3),
     "pcfgnat_links_backward": (c_int, [c_void] * 13 + [c_int] * 6 + [c_void] * 8),

@@ -15,7 +15,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libpcfgnat.so")
 OBJ_DIR = os.path.join(HERE, "build")
 
-SOURCES = ["cabi.cu", "loss_fwd.cu", "loss_bwd.cu", "loss_balanced.cu", "loss_cluster.cu", "loss_linear.cu", "best_tree.cu", "viterbi.cu", "lookahead.cu", "logsoftmax_gather.cu", "proj_fused.cu", "no_alloc.cu", "criterion_glue.cu", "extract_links.cu", "stage_inputs.cu"]
+SOURCES = ["cabi.cu", "loss_fwd.cu", "loss_bwd.cu", "loss_balanced.cu", "loss_cluster.cu", "loss_linear.cu", "best_tree.cu", "viterbi.cu", "lookahead.cu", "logsoftmax_gather.cu", "proj_fused.cu", "proj_bwd_gemm.cu", "no_alloc.cu", "criterion_glue.cu", "extract_links.cu", "stage_inputs.cu"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
 

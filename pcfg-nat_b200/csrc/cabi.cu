@@ -428,6 +428,15 @@ int pcfgnat_proj_dlogits_compact(const void *hidden, const void *weight, const i
                                row_index, n_rows);
 }
 
+int pcfgnat_proj_backward_gemms(const void *dlogits, const void *weight_bf16, const void *rows_bf16, int n, int V, int H,
+                                float *d_rows, float *d_weight, int *status, void *stream) {
+    if (n < 0 || V < 1 || H < 1) return PCFGNAT_ERR_INVALID_ARGUMENT;
+    if ((long long)n * V > (1ll << 40)) return PCFGNAT_ERR_TOO_LARGE;
+    if (n && (!dlogits || (d_rows && !weight_bf16) || (d_weight && !rows_bf16))) return PCFGNAT_ERR_INVALID_ARGUMENT;
+    return launch_proj_backward_gemms(dlogits, weight_bf16, rows_bf16, n, V, H, d_rows, d_weight, status,
+                                      static_cast<cudaStream_t>(stream));
+}
+
 int pcfgnat_links_gather_features(const void *q, const void *kl, const void *kr, int dtype, const int *nodes, int M,
                                   int B, int L, int heads, int head_dim, float *qm, float *klm, float *krm, void *stream) {
     if (dtype != PCFGNAT_DTYPE_F32 && dtype != PCFGNAT_DTYPE_F16) return PCFGNAT_ERR_UNSUPPORTED;

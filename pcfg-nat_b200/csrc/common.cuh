@@ -198,5 +198,7 @@ int launch_proj_dlogits(const void *hidden, const void *weight, const int64_t *t
                         const int64_t *tl, const float *lse, const float *grad_match, int B, int L, int T, int V, int H,
                         void *dlogits, void *workspace, size_t ws_bytes, int *status, cudaStream_t st, int capacity = 0,
                         int64_t *row_index = nullptr, int *n_rows_out = nullptr);
+int launch_proj_backward_gemms(const void *dlogits, const void *weight_bf16, const void *rows_bf16, int n, int V, int H,
+                               float *d_rows, float *d_weight, int *status, cudaStream_t st);
 
 }  // namespace pcfgnat

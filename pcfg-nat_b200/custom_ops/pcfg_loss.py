@@ -374,6 +374,33 @@ class _Kernel:
         return dl
 
     @staticmethod
+    def proj_backward_gemms(dlogits, weight_bf16, rows_bf16, want_rows=True, want_weight=True):
+        """The two products that finish the projection's backward, on the tensor cores: (d rows [n, H] float32 =
+        dlogits [n, V] @ weight_bf16 [V, H], d weight [V, H] float32 = dlogits.T @ rows_bf16 [n, H]); None for a
+        product not wanted.  All operands bfloat16 and contiguous; V and H multiples of 8."""
+        _require_cuda()
+        dev = dlogits.device
+        for t, name in ((dlogits, "dlogits"), (weight_bf16, "weight_bf16"), (rows_bf16, "rows_bf16")):
+            if t is None:
+                continue
+            if not t.is_cuda or t.dtype != torch.bfloat16 or t.dim() != 2 or not t.is_contiguous():
+                raise RuntimeError(f"{name} must be a contiguous bfloat16 CUDA matrix")
+        n, V = dlogits.shape
+        H = (weight_bf16 if weight_bf16 is not None else rows_bf16).shape[1]
+        if want_rows and (weight_bf16 is None or tuple(weight_bf16.shape) != (V, H)):
+            raise RuntimeError("weight_bf16 must be [V, H]")
+        if want_weight and (rows_bf16 is None or tuple(rows_bf16.shape) != (n, H)):
+            raise RuntimeError("rows_bf16 must be [n, H]")
+        ptr = lambda t: t.data_ptr() if t is not None else None
+        with torch.cuda.device(dev):
+            d_rows = torch.empty((n, H), dtype=torch.float32, device=dev) if want_rows else None
+            d_weight = torch.empty((V, H), dtype=torch.float32, device=dev) if want_weight else None
+            rc = _cabi.lib().pcfgnat_proj_backward_gemms(dlogits.data_ptr(), ptr(weight_bf16), ptr(rows_bf16), n, V, H,
+                                                         ptr(d_rows), ptr(d_weight), _status_ptr(dev), _stream(dev))
+        _cabi.check(rc, "pcfgnat_proj_backward_gemms")
+        return d_rows, d_weight
+
+    @staticmethod
     def viterbi_decoding_device(pred_length, output_length, L_trace, R_trace, M_trace, unreduced_tokens,
                                 left_tree_mask, pad_index):
         """Device back-trace: (tokens [B, L] int64 padded with pad_index, count [B] int64), no host sync."""
@@ -914,11 +941,28 @@ class DagLogsoftmaxGatherFunc(Function):
 dag_logsoftmax_gather_inplace = DagLogsoftmaxGatherFunc.apply
 
 
+def proj_backward_products(dlogits, weight, rows):
+    """(dlogits @ weight, dlogits.T @ rows) in float32 from bf16 d-logits [n, V], the projection weight [V, H] and the
+    decoder states of the same n rows [n, H] (either may be None: that product is skipped).  On this library's
+    tensor-core kernels (``pcfgnat_proj_backward_gemms``); shapes whose V or H is not a multiple of 8 cannot be
+    described to the tensor maps and go through torch's matmul instead."""
+    V = dlogits.shape[1]
+    H = (weight if weight is not None else rows).shape[1]
+    if V % 8 == 0 and H % 8 == 0:
+        return get_pcfg_kernel().proj_backward_gemms(
+            dlogits, weight.to(torch.bfloat16).contiguous() if weight is not None else None,
+            rows.to(torch.bfloat16).contiguous() if rows is not None else None,
+            want_rows=weight is not None, want_weight=rows is not None)
+    d_rows = (dlogits @ weight.to(torch.bfloat16)).float() if weight is not None else None
+    d_weight = (dlogits.t() @ rows.to(torch.bfloat16)).float() if rows is not None else None
+    return d_rows, d_weight
+
+
 class ProjLogsoftmaxGatherFunc(Function):
     """match = log_softmax(hidden @ weight.T)[targets] with a backward that never holds a [B, L, V] tensor of
     the forward: the forward keeps only the per-row log-sum-exp; the backward recomputes the logits on the
     tensor cores into d loss / d logits (bf16, the only [B * L, V] buffer, alive during the backward only) and
-    finishes with two library GEMMs.  Stands in for output_projection + DagLogsoftmaxGatherFunc
+    finishes with this library's two tensor-core products (``proj_backward_products``).  Stands in for output_projection + DagLogsoftmaxGatherFunc
     (models/...pcfg.py:237, custom_ops/pcfg_loss.py:160-180), whose forward overwrites the float32 logits with
     the softmax to keep them for the backward."""
 
@@ -936,21 +980,25 @@ class ProjLogsoftmaxGatherFunc(Function):
         B, L, H = hidden.shape
         k = get_pcfg_kernel()
         d_hidden = d_weight = None
+        need_h, need_w = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        V = weight.shape[0]
         if ctx.n_rows is None:  # every row of the padded tensor
             dl = k.proj_dlogits(hidden, weight, targets, ol, tl, lse, grad_match.contiguous())
-            if ctx.needs_input_grad[0]:
-                d_hidden = (dl @ weight.to(torch.bfloat16)).view(B, L, H).to(hidden.dtype)
-            if ctx.needs_input_grad[1]:
-                d_weight = (dl.t() @ hidden.reshape(B * L, H).to(torch.bfloat16)).to(weight.dtype)
+            rows = hidden.reshape(B * L, H)
+            idx = None
         else:  # the real graph nodes only
             dl, idx = k.proj_dlogits(hidden, weight, targets, ol, tl, lse, grad_match.contiguous(), n_rows=ctx.n_rows)
-            if ctx.needs_input_grad[0]:
+            rows = hidden.reshape(B * L, H).index_select(0, idx) if need_w else None
+        d_rows, d_weight = proj_backward_products(dl, weight if need_h else None, rows if need_w else None)
+        if need_h:
+            if idx is None:
+                d_hidden = d_rows.to(hidden.dtype).view(B, L, H)
+            else:
                 d_hidden = torch.zeros((B * L, H), dtype=hidden.dtype, device=hidden.device)
-                d_hidden.index_copy_(0, idx, (dl @ weight.to(torch.bfloat16)).to(hidden.dtype))
+                d_hidden.index_copy_(0, idx, d_rows.to(hidden.dtype))
                 d_hidden = d_hidden.view(B, L, H)
-            if ctx.needs_input_grad[1]:
-                rows = hidden.reshape(B * L, H).index_select(0, idx).to(torch.bfloat16)
-                d_weight = (dl.t() @ rows).to(weight.dtype)
+        if need_w:
+            d_weight = d_weight.to(weight.dtype)
         return d_hidden, d_weight, None, None, None, None
 
 

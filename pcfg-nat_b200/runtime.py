@@ -339,7 +339,7 @@ class LossStep(_GraphedStep):
             self.kernels_per_step = 4 + (dp if dp > 0 else 3) + (2 if self.force_emit else 0) + (5 if link_features else 0)
         self.proj_backward_note = None
         if self.proj_backward:
-            self.kernels_per_step += 3  # proj_prepare, row index, proj (grad mode)
+            self.kernels_per_step += 5  # proj_prepare, row index, proj (grad mode), the two products of the backward
             self.weight_bf16 = self.weight.to(torch.bfloat16)
             V = int(self.weight.shape[0])
             # d-logits of the real graph nodes only, compact; the two GEMMs run after the graph, over as many rows
@@ -350,8 +350,8 @@ class LossStep(_GraphedStep):
             self.n_rows = None
             self.proj_backward_note = ("the step plus d hidden and d weight of the projection: logits recomputed into "
                                        "bf16 d-logits of the real graph nodes by proj_kernel's gradient mode (in the "
-                                       "graph), then two library bf16 GEMMs over those rows (launched after the graph: "
-                                       "their row count changes from batch to batch)")
+                                       "graph), then this library's two tcgen05 products over those rows (launched "
+                                       "after the graph: their row count changes from batch to batch)")
 
     def _inputs(self):
         if self.link_features is not None:
@@ -405,10 +405,11 @@ class LossStep(_GraphedStep):
             return out
         n = self.n_rows if self.n_rows is not None else int(self.output_length.clamp(min=0, max=self.L).sum())
         dl, idx = self.dlogits[:n], self.row_index[:n]
+        rows = self.hidden.view(self.B * self.L, self.H).index_select(0, idx)
+        d_rows, d_weight = ops.proj_backward_products(dl, self.weight_bf16, rows)
         self.d_hidden.zero_()
-        self.d_hidden.index_copy_(0, idx, (dl @ self.weight_bf16).to(torch.float16))
-        rows = self.hidden.view(self.B * self.L, self.H).index_select(0, idx).to(torch.bfloat16)
-        d_weight = (dl.t() @ rows).to(torch.float16)
+        self.d_hidden.index_copy_(0, idx, d_rows.to(torch.float16))
+        d_weight = d_weight.to(torch.float16)
         self._ev_ran.record(torch.cuda.current_stream(self.device))  # the GEMMs still read the step's buffers
         return (*out, self.d_hidden.view(self.B, self.L, self.H), d_weight)
 

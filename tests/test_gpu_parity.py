@@ -740,6 +740,26 @@ def test_loss_step_with_projection_backward_matches_autograd_path(pkg, ops, syn)
     assert ops.read_status(DEV) == 0
 
 
+@pytest.mark.parametrize("n,V,H", [(300, 1024, 64), (1000, 4104, 512), (129, 40000, 128), (70, 200, 8)])
+def test_projection_backward_gemms_against_torch(ops, n, V, H):
+    """pcfgnat_proj_backward_gemms (tcgen05, dlogits read K-major for one product and MN-major for the other)
+    against float32 matmul of the same bf16 operands; shapes with row, column and K tails, one tile and many."""
+    g = torch.Generator().manual_seed(n)
+    dl = (torch.randn(n, V, generator=g) * 0.1).to(torch.bfloat16).to(DEV)
+    w = torch.randn(V, H, generator=g).to(torch.bfloat16).to(DEV)
+    rows = torch.randn(n, H, generator=g).to(torch.bfloat16).to(DEV)
+    k = ops.get_pcfg_kernel()
+    d_rows, d_weight = k.proj_backward_gemms(dl, w, rows)
+    want_rows = dl.float() @ w.float()
+    want_weight = dl.float().t() @ rows.float()
+    torch.testing.assert_close(d_rows, want_rows, rtol=2e-3, atol=2e-3 * float(want_rows.abs().max()))
+    torch.testing.assert_close(d_weight, want_weight, rtol=2e-3, atol=2e-3 * float(want_weight.abs().max()))
+    only_rows, none = k.proj_backward_gemms(dl, w, None, want_weight=False)
+    assert none is None
+    torch.testing.assert_close(only_rows, d_rows, rtol=1e-5, atol=1e-5 * float(want_rows.abs().max()))
+    assert ops.read_status(DEV) == 0
+
+
 def test_copy_real_rows_sends_the_real_nodes_only(ops):
     """pcfgnat_copy_real_rows: rows l < length arrive, the others keep what they held; lengths beyond the tensor
     and below zero are clamped; full sentences next to each other go as one copy; a sentence range."""
