@@ -177,7 +177,6 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
         "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
         : "memory");
 }
-
 // K-major, 128-byte-swizzled operand tile: rows at 128 B pitch, 8-row groups 1024 B apart.
 __device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
     return (uint64_t)((saddr >> 4) & 0x3FFFu) | (1ull << 16) /* leading byte offset (unused with swizzle) */
@@ -332,6 +331,7 @@ struct GradArgs {  // kGradLogits only
     __nv_bfloat16 *dlogits;  // [B*L][V], or [capacity][V] when compact
     int compact;             // rows in compact order (row i = the i-th real node of the batch) instead of padded order
     int capacity;            // compact: rows the buffer holds; a batch with more real nodes is flagged, not written
+    int tma_store;           // compact and V % 8 == 0: tiles leave through shared memory and TMA stores (map_dl)
 };
 
 // PAIR: launched as clusters of two CTAs that share every W tile (tcgen05 cta_group::2).  A unit is then two
@@ -339,13 +339,16 @@ struct GradArgs {  // kGradLogits only
 // traffic per SM and lets the same shared memory hold a ring twice as deep; the first CTA issues the MMAs for both.
 template <int MODE, bool PAIR>
 __global__ void __launch_bounds__(PROJ_THREADS, 1)
-    proj_kernel(const __grid_constant__ CUtensorMap map_w, const __half *__restrict__ hidden,
+    proj_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_dl,
+                const __half *__restrict__ hidden,
                 const int *__restrict__ row_src, const int *__restrict__ n_rows_ptr, int max_seg, int V, int KC, int L,
                 int T, const int *__restrict__ stok, const int *__restrict__ sslot, float *match, Partial *partials,
                 GradArgs ga, int *status) {
     constexpr bool WANT_ARGMAX = MODE == kForwardArgmax;
     extern __shared__ uint8_t smem_raw[];
-    constexpr int NST = PAIR ? NSTAGE_PAIR : NSTAGE;
+    // the gradient mode gives 32 KB of the W ring to the staging buffers of its TMA stores
+    constexpr bool GRAD = MODE == kGradLogits;
+    constexpr int NST = PAIR ? (GRAD ? NSTAGE_PAIR - 2 : NSTAGE_PAIR) : (GRAD ? NSTAGE - 1 : NSTAGE);
     constexpr int STAGE_BYTES = PAIR ? B_STAGE_BYTES_PAIR : B_STAGE_BYTES;
     __shared__ __align__(8) uint64_t bars[2 * NST + 2 + 4];
     __shared__ uint32_t tmem_base_slot;
@@ -363,6 +366,7 @@ __global__ void __launch_bounds__(PROJ_THREADS, 1)
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const uint32_t smem_a = smem_u32(smem);
     const uint32_t smem_b = smem_a + KC_MAX * A_CHUNK_BYTES;
+    const uint32_t smem_store = smem_b + NST * STAGE_BYTES;  // GRAD: two 2 KB buffers per epilogue warp
     // In a pair, `full`, `a` and `tempty` are used in the first CTA only (both CTAs report to them); `empty`,
     // `a_free` and `tfull` exist in both and are signalled in both by the first CTA's commits.
     const uint32_t bar_full = smem_u32(&bars[0]);              // [NST] W stage landed
@@ -488,6 +492,7 @@ __global__ void __launch_bounds__(PROJ_THREADS, 1)
         const int sub = warp & 3;       // TMEM sub-partition (lanes 32*sub ..) this warp may read
         const int half = ew >> 2;       // which 128 columns of each 256-wide tile
         uint32_t tile = 0, seg = 0;
+        uint32_t store_buf = 0;  // GRAD: which of the warp's two staging buffers the next TMA store uses
         bool ok = true;
         long long u = u_begin;
         while (u < u_end && ok) {
@@ -603,7 +608,36 @@ __global__ void __launch_bounds__(PROJ_THREADS, 1)
                             p++;
                             next_tok = p < T ? __ldg(my_tok + p) : INT_MAX;
                         }
-                        if (row_ok && (!ga.compact || cr < ga.capacity)) {
+                        if (ga.tma_store) {
+                            // the warp's 32 rows x 32 columns as bf16 into its staging buffer (rows of 64 B in the
+                            // 64-byte swizzle: no bank conflicts), then one TMA store: whole 64-byte row segments
+                            // instead of 32 scattered 16-byte stores per instruction.  Rows past the batch's real
+                            // nodes hold zeros here and the store clips at the buffer's rows and at column V.
+                            uint32_t pk[16];
+#pragma unroll
+                            for (int i = 0; i < 16; i++) {
+                                const __nv_bfloat162 two = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+                                pk[i] = *reinterpret_cast<const uint32_t *>(&two);
+                            }
+                            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");  // this buffer's last store has read it
+                            __syncwarp();
+                            const uint32_t sbuf = smem_store + (uint32_t)ew * 4096u + store_buf * 2048u;
+#pragma unroll
+                            for (int i = 0; i < 4; i++)
+                                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sbuf + lane * 64 + ((i ^ ((lane >> 1) & 3)) << 4)),
+                                             "r"(pk[4 * i]), "r"(pk[4 * i + 1]), "r"(pk[4 * i + 2]), "r"(pk[4 * i + 3])
+                                             : "memory");
+                            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                            __syncwarp();
+                            if (lane == 0) {
+                                asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                                                 reinterpret_cast<uint64_t>(&map_dl)),
+                                             "r"(sbuf), "r"(col0), "r"(cr - lane)
+                                             : "memory");
+                                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                            }
+                            store_buf ^= 1u;
+                        } else if (row_ok && (!ga.compact || cr < ga.capacity)) {
                             __nv_bfloat16 *dst = ga.dlogits + (size_t)(ga.compact ? cr : row) * V + col0;
                             if (col0 + 32 <= V && (V & 7) == 0) {
                                 uint32_t pk[16];
@@ -696,6 +730,8 @@ __global__ void __launch_bounds__(PROJ_THREADS, 1)
             }
             seg++;
         }
+        // the staging buffers are read by stores still in flight: they are done before the CTA gives up its memory
+        if (GRAD && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     }
     if (*abort_flag && threadIdx.x == 0) flag(status, PCFGNAT_STATUS_TIMEOUT);
     tc_fence_before();
@@ -849,6 +885,20 @@ bool make_map(CUtensorMap *map, const void *base, uint64_t rows, uint64_t K, uin
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// d-logits [rows][V] bf16 row-major for the gradient mode's stores: boxes of 32 rows x 32 columns (64 B per row,
+// 64-byte swizzle in shared memory); a store clips at the tensor's bounds.
+bool make_store_map(CUtensorMap *map, const void *base, uint64_t rows, uint64_t V) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {V, rows};
+    cuuint64_t strides[1] = {V * 2};
+    cuuint32_t box[2] = {32, 32};
+    cuuint32_t estr[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 // Launch geometry from the PADDED row count (an upper bound of the compact one, which only the
 // device knows): number of CTAs and the most segments a CTA's range can touch.
 struct Geometry {
@@ -885,14 +935,15 @@ Geometry make_geometry(int N, int V) {
 
 // Launches proj_kernel<MODE, PAIR>: plain launch, or clusters of two CTAs.
 template <int MODE>
-int launch_proj_kernel(const Geometry &geo, size_t smem, cudaStream_t st, const CUtensorMap &map_w, const __half *hidden,
+int launch_proj_kernel(const Geometry &geo, size_t smem, cudaStream_t st, const CUtensorMap &map_w,
+                       const CUtensorMap &map_dl, const __half *hidden,
                        const int *row_src, const int *n_rows, int V, int KC, int L, int T, const int *stok,
                        const int *sslot, float *match, Partial *partials, GradArgs ga, int *status) {
     if (!geo.pair) {
         auto k = proj_kernel<MODE, false>;
         if (ensure_dynamic_smem(k, smem) != cudaSuccess) return PCFGNAT_ERR_CUDA;
-        k<<<geo.ctas, PROJ_THREADS, smem, st>>>(map_w, hidden, row_src, n_rows, geo.max_seg, V, KC, L, T, stok, sslot, match,
-                                                partials, ga, status);
+        k<<<geo.ctas, PROJ_THREADS, smem, st>>>(map_w, map_dl, hidden, row_src, n_rows, geo.max_seg, V, KC, L, T, stok, sslot,
+                                                match, partials, ga, status);
         return cuda_rc(cudaGetLastError());
     }
     auto k = proj_kernel<MODE, true>;
@@ -909,8 +960,8 @@ int launch_proj_kernel(const Geometry &geo, size_t smem, cudaStream_t st, const 
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cuda_rc(cudaLaunchKernelEx(&cfg, k, map_w, hidden, row_src, n_rows, geo.max_seg, V, KC, L, T, stok, sslot, match,
-                                      partials, ga, status));
+    return cuda_rc(cudaLaunchKernelEx(&cfg, k, map_w, map_dl, hidden, row_src, n_rows, geo.max_seg, V, KC, L, T, stok, sslot,
+                                      match, partials, ga, status));
 }
 
 struct Workspace {
@@ -967,10 +1018,10 @@ int launch_proj(const void *hidden, const void *weight, const int64_t *targets, 
     const bool want_arg = max_lprob != nullptr || argmax != nullptr;
     const __half *hid = static_cast<const __half *>(hidden);
     const GradArgs none = {nullptr, nullptr, nullptr, nullptr, nullptr};
-    const int rc = want_arg ? launch_proj_kernel<kForwardArgmax>(geo, smem, st, map_w, hid, w.row_src, w.n_rows, V, H / BK, L, T,
+    const int rc = want_arg ? launch_proj_kernel<kForwardArgmax>(geo, smem, st, map_w, map_w, hid, w.row_src, w.n_rows, V, H / BK, L, T,
                                                                  gather ? w.stok : nullptr, gather ? w.sslot : nullptr,
                                                                  gather ? match : nullptr, w.partials, none, status)
-                            : launch_proj_kernel<kForward>(geo, smem, st, map_w, hid, w.row_src, w.n_rows, V, H / BK, L, T,
+                            : launch_proj_kernel<kForward>(geo, smem, st, map_w, map_w, hid, w.row_src, w.n_rows, V, H / BK, L, T,
                                                            gather ? w.stok : nullptr, gather ? w.sslot : nullptr,
                                                            gather ? match : nullptr, w.partials, none, status);
     if (rc != PCFGNAT_OK) return rc;
@@ -1032,9 +1083,12 @@ int launch_proj_dlogits(const void *hidden, const void *weight, const int64_t *t
     else if (ol)
         proj_zero_padding_rows_kernel<<<dim3(B, 8), 256, 0, st>>>(w.prefix, L, V, dl);
     const size_t smem = (size_t)KC_MAX * A_CHUNK_BYTES + (size_t)NSTAGE * B_STAGE_BYTES + 1024;
-    const GradArgs ga = {lse, grad_match, ol, tl, dl, compact, capacity};
-    return launch_proj_kernel<kGradLogits>(geo, smem, st, map_w, static_cast<const __half *>(hidden), w.row_src, w.n_rows, V,
-                                           H / BK, L, T, w.stok, w.sslot, nullptr, w.partials, ga, status);
+    // compact rows are consecutive in the buffer, so a warp's 32 rows x 32 columns can leave as one TMA store
+    CUtensorMap map_dl = map_w;
+    const int tma_store = compact && capacity > 0 && V % 8 == 0 && make_store_map(&map_dl, dl, (uint64_t)capacity, (uint64_t)V);
+    const GradArgs ga = {lse, grad_match, ol, tl, dl, compact, capacity, tma_store};
+    return launch_proj_kernel<kGradLogits>(geo, smem, st, map_w, map_dl, static_cast<const __half *>(hidden), w.row_src,
+                                           w.n_rows, V, H / BK, L, T, w.stok, w.sslot, nullptr, w.partials, ga, status);
 }
 
 }  // namespace pcfgnat
