@@ -201,28 +201,11 @@ __global__ void __launch_bounds__(G_THREADS, 1)
     }
 }
 
-using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
-                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn gemm_encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    if (!fn) {
-        void *p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
-            q != cudaDriverEntryPointSuccess)
-            return nullptr;
-        fn = reinterpret_cast<EncodeTiledFn>(p);
-    }
-    return fn;
-}
-
 // bf16 matrix [outer][inner] row-major with a row pitch of ld elements; tiles of box_outer rows x box_inner elements
 // (64: 128-byte swizzle, 32: 64-byte swizzle), zeros outside.
 bool gemm_map(CUtensorMap *map, const void *base, uint64_t inner, uint64_t outer, uint64_t ld, uint32_t box_inner,
               uint32_t box_outer) {
-    EncodeTiledFn fn = gemm_encode_fn();
+    EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return false;
     cuuint64_t dims[2] = {inner, outer};
     cuuint64_t strides[1] = {ld * 2};

@@ -33,10 +33,23 @@
 #include <cuda_fp16.h>
 
 #include "common.cuh"
+#include "tcgen05.cuh"
 
 namespace pcfgnat {
 
 namespace {
+
+using tc::elect_one;
+using tc::kSpinLimit;
+using tc::mbar_arrive;
+using tc::mbar_expect_tx;
+using tc::mbar_init;
+using tc::mbar_wait;
+using tc::smem_u32;
+using tc::tma_load_2d;
+using tc::tmem_ld32_issue;
+using tc::tmem_ld_wait;
+using tc::umma_commit;
 
 constexpr int BM = 128;        // rows per CTA (TMEM lanes)
 constexpr int BN = 256;        // vocabulary columns per MMA tile (TMEM columns per accumulator)
@@ -54,7 +67,6 @@ constexpr int EPI_WARPS = 8;                // two per TMEM sub-partition
 constexpr int PROJ_THREADS = 32 * (2 + EPI_WARPS);
 constexpr int TMEM_BUF_COLS = 256;         // column pitch of the two accumulators (512 columns allocated)
 constexpr int HALF_COLS = BN / 2;           // columns of a tile owned by one epilogue thread
-constexpr uint32_t kSpinLimit = 1u << 22;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
@@ -92,35 +104,6 @@ struct Plan {
         return u < big ? (int)(u / (q + 1)) : (int)(rem + (u - big) / q);
     }
 };
-
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("{ .reg .b64 st; mbarrier.arrive.shared::cta.b64 st, [%0]; }" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("{ .reg .b64 st; mbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1; }" ::"r"(bar), "r"(bytes)
-                 : "memory");
-}
-// Bounded wait: returns false when the limit ran out or another role already gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
-    for (uint32_t it = 0; it < kSpinLimit; ++it) {
-        uint32_t ok;
-        asm volatile(
-            "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.b32 %0, 1, 0, p; }"
-            : "=r"(ok)
-            : "r"(bar), "r"(parity)
-            : "memory");
-        if (ok) return true;
-        if (it > 32) __nanosleep(128);
-        if ((it & 255u) == 255u && *abort_flag) return false;
-    }
-    *abort_flag = 1;
-    return false;
-}
 
 // ---- CTA pair (cluster of 2) variants: barriers that live in the pair's first CTA, loads that signal them ----
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -164,19 +147,6 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap
         : "memory");
 }
 
-// True in exactly one lane of a fully converged warp (the same lane on every call).
-__device__ __forceinline__ bool elect_one() {
-    uint32_t chosen;
-    asm volatile("{ .reg .pred p; elect.sync _|p, 0xffffffff; selp.b32 %0, 1, 0, p; }" : "=r"(chosen));
-    return chosen != 0;
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int x, int y) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
-        "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
-        : "memory");
-}
 // K-major, 128-byte-swizzled operand tile: rows at 128 B pitch, 8-row groups 1024 B apart.
 __device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
     return (uint64_t)((saddr >> 4) & 0x3FFFu) | (1ull << 16) /* leading byte offset (unused with swizzle) */
@@ -215,37 +185,8 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
                  "h"((uint16_t)3)
                  : "memory");
 }
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-// Issues the load of 32 accumulator columns of this thread's row; the registers are valid only after
-// tmem_ld_wait(r) on the same array.
-__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t *r) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr));
-}
-// Waits for the outstanding tcgen05.ld; the registers are listed as in/out operands so that the compiler
-// cannot move any use of them above the wait.
-__device__ __forceinline__ void tmem_ld_wait(uint32_t *r) {
-    asm volatile("tcgen05.wait::ld.sync.aligned;"
-                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
-                   "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]),
-                   "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]),
-                   "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]),
-                   "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
-                 :
-                 : "memory");
-}
+__device__ __forceinline__ void tc_fence_before() { tc::fence_before(); }
+__device__ __forceinline__ void tc_fence_after() { tc::fence_after(); }
 
 __device__ __forceinline__ float ex2(float x) {
     float y;
@@ -854,26 +795,9 @@ __global__ void proj_merge_kernel(const Partial *__restrict__ partials, const in
     }
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
-                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    if (!fn) {
-        void *p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
-            q != cudaDriverEntryPointSuccess)
-            return nullptr;
-        fn = reinterpret_cast<EncodeTiledFn>(p);
-    }
-    return fn;
-}
-
 // [rows][K] fp16 row-major, box = 64 (K) x box_rows, 128-byte swizzle, out-of-bounds reads give zeros.
 bool make_map(CUtensorMap *map, const void *base, uint64_t rows, uint64_t K, uint32_t box_rows) {
-    EncodeTiledFn fn = encode_fn();
+    tc::EncodeTiledFn fn = tc::encode_tiled_fn();
     if (!fn) return false;
     cuuint64_t dims[2] = {K, rows};
     cuuint64_t strides[1] = {K * 2};
@@ -888,7 +812,7 @@ bool make_map(CUtensorMap *map, const void *base, uint64_t rows, uint64_t K, uin
 // d-logits [rows][V] bf16 row-major for the gradient mode's stores: boxes of 32 rows x 32 columns (64 B per row,
 // 64-byte swizzle in shared memory); a store clips at the tensor's bounds.
 bool make_store_map(CUtensorMap *map, const void *base, uint64_t rows, uint64_t V) {
-    EncodeTiledFn fn = encode_fn();
+    tc::EncodeTiledFn fn = tc::encode_tiled_fn();
     if (!fn) return false;
     cuuint64_t dims[2] = {V, rows};
     cuuint64_t strides[1] = {V * 2};

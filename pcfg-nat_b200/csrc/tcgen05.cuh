@@ -1,8 +1,9 @@
 // Small wrappers around the sm_100a instructions the tensor-core kernels are built from: mbarriers with bounded
 // waits, TMA tile loads (this CTA only, no multicast), tcgen05 shared-memory and instruction descriptors, MMA
-// issue and commit, tensor-memory loads.  Shared by the kernels of proj_bwd_gemm.cu.
+// issue and commit, tensor-memory loads.  Shared by proj_fused.cu and proj_bwd_gemm.cu.
 #pragma once
 #include <cuda.h>
+#include <cuda_runtime.h>
 
 #include <cstdint>
 
@@ -124,6 +125,23 @@ __device__ __forceinline__ void tmem_ld_wait(uint32_t *r) {
                    "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
                  :
                  : "memory");
+}
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point (no link against libcuda); null when unavailable.
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+inline EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            return nullptr;
+        fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
 }
 
 }  // namespace tc
