@@ -83,6 +83,8 @@ def parse():
                     help="sentence groups the end-to-end leg sends (and projects) the decoder states in")
     ap.add_argument("--fetch", default="auto", choices=["auto", "none", "links", "all"],
                     help="what the end-to-end leg fetches from the host buffers by kernel instead of by copy engine")
+    ap.add_argument("--pipeline-depth", type=int, default=2,
+                    help="step objects the end-to-end leg uses in turn (batches in flight)")
     ap.add_argument("--cpu-sample", type=int, default=0,
                     help="sentences per pass of the CPU baseline (0 = the whole batch of the workload)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -366,7 +368,8 @@ def measure(ctx, name, batch, global_sentences, steps, warm, blocks=None, exchan
     fetch = a.fetch if a.fetch != "auto" else ("links" if ctx.world > 4 else "none")
     pipe = ctx.runtime.PipelinedStep(lambda: make_step(ctx.runtime, batch, weight, dev, not a.no_graph, a.copy_chunks,
                                                        exchange, **shape)[0],
-                                     fetch_from_host=None if fetch == "none" else fetch) if not a.no_graph else None
+                                     fetch_from_host=None if fetch == "none" else fetch,
+                                     depth=a.pipeline_depth) if not a.no_graph else None
     if pipe is not None:
         step_single = step
         step = pipe

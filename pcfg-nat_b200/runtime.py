@@ -255,13 +255,15 @@ class _GraphedStep:
 
 
 class PipelinedStep:
-    """Two step objects of the same shape used in turn, so that the host-to-device copies of batch i + 1 run while
-    batch i is computed (each object has its own static buffers and graphs): ``load`` always goes over the copy
-    stream of the object whose turn it is and waits only for that object's previous run, two batches back.
-    ``run`` returns that object's static outputs, which stay valid until the run after next."""
+    """Several step objects of the same shape (two by default) used in turn, so that the host-to-device copies of the
+    next batches run while batch i is computed (each object has its own static buffers and graphs): ``load`` always
+    goes over the copy stream of the object whose turn it is and waits only for that object's previous run, ``depth``
+    batches back.  ``run`` returns that object's static outputs, which stay valid until ``depth`` - 1 more runs."""
 
-    def __init__(self, make_step, fetch_from_host=None):
-        self.steps = [make_step(), make_step()]
+    def __init__(self, make_step, fetch_from_host=None, depth=2):
+        if depth < 2:
+            raise ValueError("a pipeline needs at least two step objects")
+        self.steps = [make_step() for _ in range(depth)]
         for st in self.steps:
             st.fetch_from_host = fetch_from_host
         self.turn = 0
@@ -271,11 +273,11 @@ class PipelinedStep:
 
     def run(self):
         out = self.steps[self.turn].run()
-        self.turn ^= 1
+        self.turn = (self.turn + 1) % len(self.steps)
         return out
 
     def input_bytes(self):
-        return self.steps[self.turn ^ 1].input_bytes()  # of the batch loaded last
+        return self.steps[self.turn - 1].input_bytes()  # of the batch loaded last
 
     @property
     def kernels_per_step(self):

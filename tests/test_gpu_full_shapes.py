@@ -249,3 +249,34 @@ def test_full_shape_live_against_reference_kernels(pkg, ops, syn, wname):
     torch.testing.assert_close(loss, Sr[:, 0, 0], rtol=1e-5, atol=0)
     torch.testing.assert_close(mg, mgr, rtol=1e-3, atol=2e-6)
     torch.testing.assert_close(lg, lgr, rtol=1e-3, atol=2e-6)
+
+
+def test_projection_backward_full_shape_against_float32_autograd(pkg, ops, syn):
+    """train_batch through LossStep(proj_backward=True): d-logits of the 10 804 real nodes, then the two tensor-core
+    products, against float32 autograd of log_softmax(hidden @ weight.T) fed the step's own emission gradient
+    (1.5e-2 of the Frobenius norm: bf16 d-logits and operands); padding rows of d hidden exactly zero."""
+    batch = syn.make_batch("train_batch", seed=0)
+    weight = batch.weight.to(DEV)
+    step = _runtime().LossStep(weight, batch.B, batch.L, batch.T, DEV, use_graph=True, proj_backward=True)
+    step.load(batch.hidden, batch.links, batch.output_length, batch.targets, batch.target_length)
+    stats, mg, lg, loss, d_hidden, d_weight = step.run()
+    torch.cuda.synchronize()
+    assert ops.read_status(DEV) == 0 and torch.isfinite(loss).all()
+    rows = _real_rows(batch)
+    assert float(d_hidden[~rows].abs().sum()) == 0.0
+    h32 = batch.hidden.float().to(DEV).requires_grad_(True)
+    w32 = batch.weight.float().to(DEV).requires_grad_(True)
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        lp = torch.log_softmax(h32 @ w32.t(), -1)
+        ref = lp.gather(2, batch.targets.to(DEV)[:, None, :].expand(-1, batch.L, -1))
+        g = torch.where(torch.isfinite(mg) & rows[:, :, None], mg, torch.zeros_like(mg))
+        # entries the forward masked (EOS) or did not project get no gradient
+        syn.eos_mask_(ref, batch.output_length.to(DEV), batch.target_length.to(DEV))
+        g = torch.where(torch.isfinite(ref), g, torch.zeros_like(g))
+        (torch.where(torch.isfinite(ref), ref, torch.zeros_like(ref)) * g).sum().backward()
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+    for got, want in ((d_hidden.float(), h32.grad), (d_weight.float(), w32.grad)):
+        assert float((got - want).norm() / want.norm()) < 1.5e-2
