@@ -352,7 +352,7 @@ __global__ void __launch_bounds__(PROJ_THREADS, 1)
     const uint32_t tmem_base = tmem_base_slot;
 
     // The two issuing warps run their loops with all 32 lanes (every lane waits on the barriers, the
-    // verdict is made warp-uniform) and elect one lane for the asynchronous instructions, so that loop
+    // outcome is made warp-uniform) and elect one lane for the asynchronous instructions, so that loop
     // state, descriptors and addresses stay warp-uniform values.
     if (warp == 0) {
         // ------------------------------ TMA producer: streams W, segment after segment ------------
