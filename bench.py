@@ -795,7 +795,9 @@ def run_ours(a):
         line["workloads"] = {}
         for name in SUB_WORKLOADS:
             b = syn.make_batch(name, seed=a.seed + rank)
-            r, st, _, _ = measure(ctx, name, b, b.B * world, sub_steps, 3, blocks=5)
+            # 40 warm-up steps: the GPU sat idle while the previous workload's CPU baseline ran, and its clocks
+            # take some tens of milliseconds to come back
+            r, st, _, _ = measure(ctx, name, b, b.B * world, sub_steps, 40, blocks=7)
             r["steps"] = sub_steps
             r["scaling"] = "weak"
             if name == "viterbi_b1":

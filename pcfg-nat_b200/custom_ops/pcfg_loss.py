@@ -27,6 +27,8 @@ Known, deliberate differences from the reference:
 * outputs are produced on the tensors' own device and current stream (the reference
   always launches on the legacy default stream 0, pcfg_loss.cu:395).
 """
+import ctypes
+
 import torch
 from torch.autograd import Function
 
@@ -537,7 +539,6 @@ class _Kernel:
         if not 0 <= b0 <= b1 <= B:
             raise RuntimeError("sentence range out of bounds")
         row_bytes = dst[0, 0].numel() * dst.element_size()
-        import ctypes
         sent = ctypes.c_int64(0)
         with torch.cuda.device(dst.device):
             rc = _cabi.lib().pcfgnat_copy_real_rows(dst.data_ptr(), src.data_ptr(), host_lengths.data_ptr(), b0, b1, L,
