@@ -116,7 +116,7 @@ const char *pcfgnat_error_string(int code) {
     switch (code) {
         case PCFGNAT_OK: return "ok";
         case PCFGNAT_ERR_INVALID_ARGUMENT: return "invalid argument (null pointer, negative or inconsistent size)";
-        case PCFGNAT_ERR_UNSUPPORTED: return "unsupported configuration (only max_left == 1; dtypes f32/f16)";
+        case PCFGNAT_ERR_UNSUPPORTED: return "unsupported configuration (max_left other than 1, a dtype other than f32/f16, or a shape this kernel cannot take)";
         case PCFGNAT_ERR_CUDA: return "a CUDA runtime call or kernel launch failed";
         case PCFGNAT_ERR_WORKSPACE: return "workspace too small";
         case PCFGNAT_ERR_TOO_LARGE: return "shape too large for the kernels";

@@ -760,6 +760,20 @@ def test_projection_backward_gemms_against_torch(ops, n, V, H):
     assert ops.read_status(DEV) == 0
 
 
+def test_projection_backward_gemms_with_no_rows(ops):
+    """A batch without real nodes: d rows is empty and d weight exactly zero."""
+    k = ops.get_pcfg_kernel()
+    dl = torch.empty((0, 1024), dtype=torch.bfloat16, device=DEV)
+    w = torch.ones((1024, 64), dtype=torch.bfloat16, device=DEV)
+    rows = torch.empty((0, 64), dtype=torch.bfloat16, device=DEV)
+    d_rows, d_weight = k.proj_backward_gemms(dl, w, rows)
+    assert tuple(d_rows.shape) == (0, 64) and tuple(d_weight.shape) == (1024, 64)
+    assert float(d_weight.abs().sum()) == 0.0
+    with pytest.raises(RuntimeError, match="unsupported"):
+        k.proj_backward_gemms(torch.zeros((8, 1001), dtype=torch.bfloat16, device=DEV),
+                              torch.zeros((1001, 64), dtype=torch.bfloat16, device=DEV), None, want_weight=False)
+
+
 def test_copy_real_rows_sends_the_real_nodes_only(ops):
     """pcfgnat_copy_real_rows: rows l < length arrive, the others keep what they held; lengths beyond the tensor
     and below zero are clamped; full sentences next to each other go as one copy; a sentence range."""
