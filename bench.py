@@ -741,20 +741,41 @@ def run_ours(a):
     if is_loss and world == 1 and not a.no_proj_backward:
         full = runtime.LossStep(ctx.weight(batch), batch.B, batch.L, batch.T, dev, use_graph=not a.no_graph,
                                 proj_backward=True)
-        full.load(*[t.to(dev) for t in host])
-        times = []
-        for i in range(3 + a.steps):
-            ctx.flush.fill_(1)
-            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            s.record()
-            full.run()
-            e.record()
-            times.append((s, e))
+        full.load(*host)  # lengths from host memory: the row count of the two products needs no device read
         torch.cuda.synchronize()
-        full_ms = sum(s.elapsed_time(e) for s, e in times[3:]) / a.steps
+
+        def timed(fn, n):
+            ev = []
+            for i in range(3 + n):
+                ctx.flush.fill_(1)
+                s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                s.record()
+                fn()
+                e.record()
+                ev.append((s, e))
+            torch.cuda.synchronize()
+            return sum(s.elapsed_time(e) for s, e in ev[3:]) / n
+
+        full_ms = timed(full.run, a.steps)
         line["with_projection_backward"] = {
             "ms_per_step": full_ms, "value": batch.B / (full_ms / 1e3), "unit": UNIT,
             "gpu_launches_per_step": full.kernels_per_step, "what": full.proj_backward_note}
+        # the two tensor-core products of the backward alone, on the d-logits the last run left behind
+        n_rows = full.n_rows
+        V, H = int(full.weight.shape[0]), full.H
+        if n_rows and V % 8 == 0 and H % 8 == 0:
+            dl = full.dlogits[:n_rows]
+            rows = full.hidden.view(-1, H).index_select(0, full.row_index[:n_rows]).to(torch.bfloat16)
+            flops = 2.0 * n_rows * V * H
+            prods = {}
+            for key, fn in (("d_rows", lambda: ctx.kernel.proj_backward_gemms(dl, full.weight_bf16, None, want_weight=False)),
+                            ("d_weight", lambda: ctx.kernel.proj_backward_gemms(dl, None, rows, want_rows=False))):
+                ms = timed(fn, min(a.steps, 10))
+                prods[key] = {"ms_per_launch": ms, "achieved": flops / (ms / 1e3) / 1e12, "peak": ctx.pk["tflops"],
+                              "unit": "TFLOP/s", "frac": flops / (ms / 1e3) / 1e12 / ctx.pk["tflops"]}
+            line["with_projection_backward"]["products"] = {
+                "bound": "tensor", "kernel": "gemm_bf16_kernel", "flops_per_launch": flops,
+                "peak_source": ctx.pk["source"] + " (burst bf16 GEMM)", **prods}
         del full
     # the same step fed with the projected link features instead of the transition matrix: the transitions are formed
     # inside the step (the model's extract_links) and the loss gradient is carried back to the features

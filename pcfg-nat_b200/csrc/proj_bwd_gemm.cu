@@ -7,16 +7,18 @@
 //
 // One kernel, C [M][N] += A . B with either operand K-major ([rows][K] in memory) or MN-major ([K][rows]), so that
 // neither product needs a transposed copy of the 0.9 GB dlogits: the first reads dlogits K-major and W MN-major,
-// the second reads dlogits and the rows both MN-major.  Tiles of 256 x 256 x 64 per CTA (64 KB of operands per
-// 8.4 MFLOP: a 128-row tile moves half as much again per FLOP and was bound by the L2 at 0.6 of the tensor peak),
-// both operands brought in by TMA (this CTA only) through a ring of six 32 KB stages of 32 K each; warp 0
-// issues the loads, warp 1 two tcgen05.mma 128 x 256 x 16 per 16 K (rows 0-127 and 128-255 of the tile, each into
-// its own 256-column accumulator: all 512 columns of tensor memory), eight warps drain the accumulators with
-// tcgen05.ld and add them to C with float4 reductions.  The work is the list of (tile, K step) pairs cut into
-// equal contiguous ranges, one per SM (a tile cut by a range boundary is summed up in C by the reductions), so
-// every SM runs the same number of K steps whatever the shape; a range is hundreds of K steps long, so the one
-// accumulator set (no second one to overlap the drain with) costs a few microseconds per range.  Every wait on an mbarrier is
-// bounded; on expiry the CTA records PCFGNAT_STATUS_TIMEOUT, stops issuing work and still frees its tensor memory.
+// the second reads dlogits and the rows both MN-major.  Tiles of 256 x 256 per CTA in K steps of 32 (32 KB of
+// operands per 4.2 MFLOP; a 128-row tile moves half as much again per FLOP), both operands brought in by TMA (this
+// CTA only) through a ring of six 32 KB stages; warp 0 issues the loads, warp 1 two tcgen05.mma 128 x 256 x 16 per
+// 16 K (rows 0-127 and 128-255 of the tile, each into its own 256-column accumulator: all 512 columns of tensor
+// memory), eight warps drain the accumulators with tcgen05.ld and add them to C with float4 reductions.  The work is
+// a list of (tile, K step) pairs cut into equal contiguous ranges, one per SM (a tile cut by a range boundary is
+// summed up in C by the reductions), so every SM runs the same number of K steps whatever the shape; a range is
+// hundreds of K steps long, so the one accumulator set (no second one to overlap the drain with) costs a few
+// microseconds per range.  The SMs form one group per column tile, and the members of equal rank walk the same
+// (row tile, K step) list side by side, so that dlogits comes from HBM once and from L2 for the other group.
+// Every wait on an mbarrier is bounded; on expiry the CTA records PCFGNAT_STATUS_TIMEOUT, stops issuing work and
+// still frees its tensor memory.
 #include <cuda.h>
 #include <cuda_bf16.h>
 

@@ -70,6 +70,9 @@ class _GraphedStep:
         self.chunks = [(B * i // n, B * (i + 1) // n) for i in range(n)]
         self.chunk_graphs = None
         self._ev_chunk = None
+        # after an overlapped load: project sentence group by sentence group as the groups arrive (pays when the step
+        # waits for its own copies), or the whole batch at once when the copies are long done (a pipeline of steps)
+        self.project_by_group = True
 
     def _inputs(self):
         return [self.hidden, self.links, self.output_length]
@@ -231,7 +234,7 @@ class _GraphedStep:
                 cur.wait_event(self._ev_stage2)
                 pending = False
             self._capture()
-        if pending and self.chunk_graphs and self._pending_chunked:
+        if pending and self.chunk_graphs and self._pending_chunked and self.project_by_group:
             for ev, g in zip(self._ev_chunk, self.chunk_graphs):
                 cur.wait_event(ev)
                 g.replay()
@@ -266,6 +269,7 @@ class PipelinedStep:
         self.steps = [make_step() for _ in range(depth)]
         for st in self.steps:
             st.fetch_from_host = fetch_from_host
+            st.project_by_group = False  # a batch's copies ran under the previous batch's kernels: nothing to wait for
         self.turn = 0
 
     def load(self, *tensors):
