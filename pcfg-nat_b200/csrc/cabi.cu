@@ -8,6 +8,8 @@
 #include <cstdlib>
 #include <mutex>
 
+#include <nvtx3/nvToolsExt.h>
+
 using namespace pcfgnat;
 
 namespace pcfgnat {
@@ -108,6 +110,35 @@ inline size_t align256(size_t x) { return (x + 255) / 256 * 256; }
 
 }  // namespace
 
+namespace {
+
+// NVTX range around an entry point (its host side: argument checks and launches) when PCFGNAT_NVTX=1 was set when
+// the library was first called; free otherwise.  The ranges carry the entry point's name, so that a timeline of the
+// host application shows which of its calls the kernels belong to.
+struct ApiRange {
+    static bool enabled() {
+        static const bool on = [] {
+            const char *v = getenv("PCFGNAT_NVTX");
+            return v && v[0] == '1';
+        }();
+        return on;
+    }
+    explicit ApiRange(const char *name) : on_(enabled()) {
+        if (on_) nvtxRangePushA(name);
+    }
+    ~ApiRange() {
+        if (on_) nvtxRangePop();
+    }
+    ApiRange(const ApiRange &) = delete;
+    ApiRange &operator=(const ApiRange &) = delete;
+
+private:
+    bool on_;
+};
+#define PCFGNAT_API_RANGE() ApiRange api_range_(__func__)
+
+}  // namespace
+
 extern "C" {
 
 int pcfgnat_version(void) { return 100; }
@@ -127,6 +158,7 @@ const char *pcfgnat_error_string(int code) {
 int pcfgnat_loss_fwd(const float *match_all, const float *links, const int64_t *output_length,
                      const int64_t *target_length, int B, int L, int T, int max_left, float *S, float *C, int *status,
                      void *stream) {
+    PCFGNAT_API_RANGE();
     if (max_left != 1) return PCFGNAT_ERR_UNSUPPORTED;
     if (bad_dims(B, L, T)) return PCFGNAT_ERR_INVALID_ARGUMENT;
     if (B && (!match_all || !links || !output_length || !target_length || !S)) return PCFGNAT_ERR_INVALID_ARGUMENT;
@@ -137,6 +169,7 @@ int pcfgnat_loss_fwd(const float *match_all, const float *links, const int64_t *
 int pcfgnat_loss_bwd(const float *grad_output, const float *S, const float *match_all, const float *links,
                      const int64_t *output_length, const int64_t *target_length, int B, int L, int T, int max_left,
                      float *S_grad, float *match_all_grad, float *links_grad, int *status, void *stream) {
+    PCFGNAT_API_RANGE();
     if (max_left != 1) return PCFGNAT_ERR_UNSUPPORTED;
     if (bad_dims(B, L, T)) return PCFGNAT_ERR_INVALID_ARGUMENT;
     if (B && (!grad_output || !S || !match_all || !links || !output_length || !target_length || !S_grad ||
@@ -166,6 +199,7 @@ int pcfgnat_loss_fwd_bwd(const float *match_all, const float *links, const int64
                          const int64_t *target_length, int B, int L, int T, int max_left, void *workspace,
                          size_t workspace_bytes, float *loss, float *match_all_grad, float *links_grad, int *status,
                          void *stream) {
+    PCFGNAT_API_RANGE();
     if (max_left != 1) return PCFGNAT_ERR_UNSUPPORTED;
     if (bad_dims(B, L, T)) return PCFGNAT_ERR_INVALID_ARGUMENT;
     if (B && (!match_all || !links || !output_length || !target_length || !workspace || !loss || !match_all_grad ||
@@ -182,6 +216,7 @@ int pcfgnat_loss_fwd_bwd(const float *match_all, const float *links, const int64
 int pcfgnat_best_tree(const float *S, const float *match_all, const float *links, const int64_t *output_length,
                       const int64_t *target_length, int B, int L, int T, int max_left, int64_t *tree, int *status,
                       void *stream) {
+    PCFGNAT_API_RANGE();
     if (max_left != 1) return PCFGNAT_ERR_UNSUPPORTED;
     if (bad_dims(B, L, T)) return PCFGNAT_ERR_INVALID_ARGUMENT;
     if (B && (!S || !match_all || !links || !output_length || !target_length || !tree))
@@ -192,6 +227,7 @@ int pcfgnat_best_tree(const float *S, const float *match_all, const float *links
 
 int pcfgnat_viterbi(const float *ob_lprob, const float *links, const int64_t *output_length, int B, int L,
                     int max_left, float *S, int64_t *R, int64_t *Lt, int64_t *Mt, int *status, void *stream) {
+    PCFGNAT_API_RANGE();
     if (max_left != 1) return PCFGNAT_ERR_UNSUPPORTED;
     if (B < 0 || L < 8) return PCFGNAT_ERR_INVALID_ARGUMENT;
     if (B && (!ob_lprob || !links || !output_length || !S || !R || !Lt || !Mt)) return PCFGNAT_ERR_INVALID_ARGUMENT;
@@ -203,6 +239,7 @@ int pcfgnat_viterbi_backtrace(const int64_t *pred_length, const int64_t *output_
                               const int64_t *R, const int64_t *Mt, const int64_t *tokens,
                               const int64_t *left_tree_mask, int mask_dim, int64_t pad_index, int B, int L, int Q,
                               int cap, int64_t *out_tokens, int64_t *out_count, int *status, void *stream) {
+    PCFGNAT_API_RANGE();
     if (B < 0 || L < 1 || Q < 1 || cap < 0 || mask_dim < 1) return PCFGNAT_ERR_INVALID_ARGUMENT;
     if (B && (!pred_length || !output_length || !Lt || !R || !Mt || !tokens || !left_tree_mask || !out_count ||
               (cap && !out_tokens)))
@@ -215,6 +252,7 @@ int pcfgnat_viterbi_decode(const float *S, const float *penalty, const int64_t *
                            const int64_t *R, const int64_t *Mt, const int64_t *tokens, const int64_t *left_tree_mask,
                            int mask_dim, int64_t pad_index, int B, int L, int Q, int cap, int64_t *pred_length,
                            int64_t *out_tokens, int64_t *out_count, int *status, void *stream) {
+    PCFGNAT_API_RANGE();
     if (B < 0 || L < 2 || Q < 2 || cap < 0 || mask_dim < 1) return PCFGNAT_ERR_INVALID_ARGUMENT;
     if (B && (!S || !penalty || !output_length || !Lt || !R || !Mt || !tokens || !left_tree_mask || !pred_length ||
               !out_count || (cap && !out_tokens)))
@@ -227,6 +265,7 @@ int pcfgnat_lookahead_decode(const float *links, const float *ob_lprob, const in
                              const int64_t *output_length, const int64_t *left_tree_mask, int mask_dim, float beta,
                              int lookahead, int64_t pad_index, int B, int L, int max_left, int cap, int64_t *out_tokens,
                              int64_t *out_count, int *status, void *stream) {
+    PCFGNAT_API_RANGE();
     if (max_left != 1) return PCFGNAT_ERR_UNSUPPORTED;
     if (B < 0 || L < 2 || cap < 0 || mask_dim < 1) return PCFGNAT_ERR_INVALID_ARGUMENT;
     if (B && (!links || !tokens || !output_length || !left_tree_mask || !out_count || (cap && !out_tokens) ||
@@ -239,6 +278,7 @@ int pcfgnat_lookahead_decode(const float *links, const float *ob_lprob, const in
 int pcfgnat_logsoftmax_gather(void *logits, int dtype, const int64_t *select_idx, int64_t stride_b, int64_t stride_l,
                               int64_t stride_s, int64_t rows, int64_t rows_per_batch, int V, int slen,
                               int require_gradient, float *selected, int *status, void *stream) {
+    PCFGNAT_API_RANGE();
     if (rows < 0 || rows_per_batch < 1 || V < 1 || slen < 0) return PCFGNAT_ERR_INVALID_ARGUMENT;
     if (rows && (!logits || (slen && (!select_idx || !selected)))) return PCFGNAT_ERR_INVALID_ARGUMENT;
     return launch_logsoftmax_gather(logits, dtype, select_idx, stride_b, stride_l, stride_s, rows, rows_per_batch, V,
@@ -254,6 +294,7 @@ int pcfgnat_proj_logsoftmax_gather(const void *hidden, const void *weight, const
                                    const int64_t *output_length, const int64_t *target_length, int B, int L, int T,
                                    int V, int H, float *match, float *max_lprob, int64_t *argmax, float *lse,
                                    void *workspace, size_t workspace_bytes, int *status, void *stream) {
+    PCFGNAT_API_RANGE();
     if (B < 0 || L < 1 || T < 0 || V < 1 || H < 1) return PCFGNAT_ERR_INVALID_ARGUMENT;
     if ((long long)B * L > (1ll << 30)) return PCFGNAT_ERR_TOO_LARGE;
     if (B && (!hidden || !weight || !workspace)) return PCFGNAT_ERR_INVALID_ARGUMENT;
@@ -264,6 +305,7 @@ int pcfgnat_proj_logsoftmax_gather(const void *hidden, const void *weight, const
 }
 
 int pcfgnat_loss_stats(const float *sentence_loss, const int64_t *target_length, int B, float *stats, void *stream) {
+    PCFGNAT_API_RANGE();
     if (B < 0 || !stats || (B && (!sentence_loss || !target_length))) return PCFGNAT_ERR_INVALID_ARGUMENT;
     return launch_loss_stats(sentence_loss, target_length, B, stats, static_cast<cudaStream_t>(stream));
 }
@@ -271,6 +313,7 @@ int pcfgnat_loss_stats(const float *sentence_loss, const int64_t *target_length,
 int pcfgnat_loss_stats_exchange(const float *sentence_loss, const int64_t *target_length, int B,
                                 const uint64_t *peer_buffers, int rank, int world, float *stats, int *status,
                                 void *stream) {
+    PCFGNAT_API_RANGE();
     if (B < 0 || !stats || !peer_buffers || world < 1 || world > PCFGNAT_EXCHANGE_MAX_WORLD || rank < 0 || rank >= world ||
         (B && (!sentence_loss || !target_length)))
         return PCFGNAT_ERR_INVALID_ARGUMENT;
@@ -283,6 +326,7 @@ int pcfgnat_glance_select(const int64_t *path, const int64_t *pred_tokens, const
                           const float *uniform, int strategy, float context_p, int B, int L, int T, uint8_t *matchmask,
                           int64_t *oracle, int64_t *same_num, int64_t *glance_num, uint8_t *keep, int64_t *glat_prev,
                           void *stream) {
+    PCFGNAT_API_RANGE();
     if (B < 0 || L < 1 || T < 1) return PCFGNAT_ERR_INVALID_ARGUMENT;
     if (strategy != PCFGNAT_GLANCE_NUMBER_RANDOM && strategy != PCFGNAT_GLANCE_CMLM && strategy != PCFGNAT_GLANCE_FRACTION)
         return PCFGNAT_ERR_UNSUPPORTED;
@@ -298,18 +342,21 @@ int pcfgnat_glance_select(const int64_t *path, const int64_t *pred_tokens, const
 
 int pcfgnat_force_emit(const float *match, const uint8_t *matchmask, const uint8_t *keep, int B, int L, int T,
                        float *out, void *stream) {
+    PCFGNAT_API_RANGE();
     if (B < 0 || L < 1 || T < 1) return PCFGNAT_ERR_INVALID_ARGUMENT;
     if (B && (!match || !matchmask || !keep || !out)) return PCFGNAT_ERR_INVALID_ARGUMENT;
     return launch_force_emit(match, matchmask, keep, B, L, T, out, static_cast<cudaStream_t>(stream));
 }
 
 int pcfgnat_force_emit_grad(const float *grad, const uint8_t *keep, int B, int L, int T, float *out, void *stream) {
+    PCFGNAT_API_RANGE();
     if (B < 0 || L < 1 || T < 1) return PCFGNAT_ERR_INVALID_ARGUMENT;
     if (B && (!grad || !keep || !out)) return PCFGNAT_ERR_INVALID_ARGUMENT;
     return launch_force_emit_grad(grad, keep, B, L, T, out, static_cast<cudaStream_t>(stream));
 }
 
 int pcfgnat_copy_links_main_rows(void *dst, const void *src, int B, int L, int max_left, void *stream) {
+    PCFGNAT_API_RANGE();
     if (max_left != 1) return PCFGNAT_ERR_UNSUPPORTED;
     if (B < 0 || L < 1 || (B && (!dst || !src))) return PCFGNAT_ERR_INVALID_ARGUMENT;
     if (B == 0) return PCFGNAT_OK;
@@ -329,6 +376,7 @@ int pcfgnat_copy_links_main_rows(void *dst, const void *src, int B, int L, int m
 
 int pcfgnat_copy_real_rows(void *dst, const void *src, const int64_t *host_lengths, int b0, int b1, int L,
                            size_t row_bytes, int max_copies, int64_t *rows_sent, void *stream) {
+    PCFGNAT_API_RANGE();
     if (rows_sent) *rows_sent = 0;
     if (b0 < 0 || b1 < b0 || L < 1 || row_bytes == 0 || max_copies < 0) return PCFGNAT_ERR_INVALID_ARGUMENT;
     if (b1 > b0 && (!dst || !src || !host_lengths)) return PCFGNAT_ERR_INVALID_ARGUMENT;
@@ -380,6 +428,7 @@ int pcfgnat_copy_real_rows(void *dst, const void *src, const int64_t *host_lengt
 
 int pcfgnat_stage_inputs(const void *hidden_src, void *hidden_dst, int row_bytes, const float *links_src,
                          float *links_dst, const int64_t *output_length, int B, int L, int max_left, void *stream) {
+    PCFGNAT_API_RANGE();
     if (max_left != 1) return PCFGNAT_ERR_UNSUPPORTED;
     if (B < 0 || L < 2 || row_bytes < 0 || row_bytes % 16) return PCFGNAT_ERR_INVALID_ARGUMENT;
     if (B && (!output_length || (hidden_src && !hidden_dst) || (links_src && !links_dst))) return PCFGNAT_ERR_INVALID_ARGUMENT;
@@ -404,6 +453,7 @@ int pcfgnat_stage_inputs(const void *hidden_src, void *hidden_dst, int row_bytes
 int pcfgnat_proj_dlogits(const void *hidden, const void *weight, const int64_t *targets, const int64_t *output_length,
                          const int64_t *target_length, const float *lse, const float *grad_match, int B, int L, int T, int V,
                          int H, void *dlogits, void *workspace, size_t workspace_bytes, int *status, void *stream) {
+    PCFGNAT_API_RANGE();
     if (B < 0 || L < 1 || T < 1 || V < 1 || H < 1) return PCFGNAT_ERR_INVALID_ARGUMENT;
     if ((long long)B * L > (1ll << 30)) return PCFGNAT_ERR_TOO_LARGE;
     if (B && (!hidden || !weight || !targets || !lse || !grad_match || !dlogits || !workspace))
@@ -418,6 +468,7 @@ int pcfgnat_proj_dlogits_compact(const void *hidden, const void *weight, const i
                                  const float *grad_match, int B, int L, int T, int V, int H, int capacity, void *dlogits,
                                  int64_t *row_index, int *n_rows, void *workspace, size_t workspace_bytes, int *status,
                                  void *stream) {
+    PCFGNAT_API_RANGE();
     if (B < 0 || L < 1 || T < 1 || V < 1 || H < 1 || capacity < 0) return PCFGNAT_ERR_INVALID_ARGUMENT;
     if ((long long)B * L > (1ll << 30)) return PCFGNAT_ERR_TOO_LARGE;
     if (B && (!hidden || !weight || !targets || !lse || !grad_match || !workspace || !row_index)) return PCFGNAT_ERR_INVALID_ARGUMENT;
@@ -430,6 +481,7 @@ int pcfgnat_proj_dlogits_compact(const void *hidden, const void *weight, const i
 
 int pcfgnat_proj_backward_gemms(const void *dlogits, const void *weight_bf16, const void *rows_bf16, int n, int V, int H,
                                 float *d_rows, float *d_weight, int *status, void *stream) {
+    PCFGNAT_API_RANGE();
     if (n < 0 || V < 1 || H < 1) return PCFGNAT_ERR_INVALID_ARGUMENT;
     if ((long long)n * V > (1ll << 40)) return PCFGNAT_ERR_TOO_LARGE;
     if (n && (!dlogits || (d_rows && !weight_bf16) || (d_weight && !rows_bf16))) return PCFGNAT_ERR_INVALID_ARGUMENT;
@@ -439,6 +491,7 @@ int pcfgnat_proj_backward_gemms(const void *dlogits, const void *weight_bf16, co
 
 int pcfgnat_links_gather_features(const void *q, const void *kl, const void *kr, int dtype, const int *nodes, int M,
                                   int B, int L, int heads, int head_dim, float *qm, float *klm, float *krm, void *stream) {
+    PCFGNAT_API_RANGE();
     if (dtype != PCFGNAT_DTYPE_F32 && dtype != PCFGNAT_DTYPE_F16) return PCFGNAT_ERR_UNSUPPORTED;
     if (B < 0 || L < 1 || M < 0 || M > L || heads < 1 || head_dim < 1) return PCFGNAT_ERR_INVALID_ARGUMENT;
     if (B && (!q || !kl || !kr || !nodes || !qm || !klm || !krm)) return PCFGNAT_ERR_INVALID_ARGUMENT;
@@ -448,6 +501,7 @@ int pcfgnat_links_gather_features(const void *q, const void *kl, const void *kr,
 
 int pcfgnat_links_scores(const float *qm, const float *klm, const float *krm, int M, int B, int heads, int head_dim,
                          float *ac, float *bc, void *stream) {
+    PCFGNAT_API_RANGE();
     if (B < 0 || M < 0 || heads < 1 || head_dim < 1) return PCFGNAT_ERR_INVALID_ARGUMENT;
     if (B && M && (!qm || !klm || !krm || !ac || !bc)) return PCFGNAT_ERR_INVALID_ARGUMENT;
     return launch_links_scores(qm, klm, krm, M, B, heads, head_dim, ac, bc, static_cast<cudaStream_t>(stream));
@@ -459,6 +513,7 @@ int pcfgnat_links_backward(const float *links_grad, const float *ac, const float
                            const int *slot_of, const int *nodes, int M, int B, int L, int heads, int head_dim, int max_left,
                            float *X0, float *X1, float *dab, float *dq, float *dkl, float *dkr, float *dgates,
                            void *stream) {
+    PCFGNAT_API_RANGE();
     if (max_left != 1) return PCFGNAT_ERR_UNSUPPORTED;
     if (B < 0 || L < 1 || M < 0 || M > L || heads < 1 || head_dim < 1) return PCFGNAT_ERR_INVALID_ARGUMENT;
     if (B && (!links_grad || !ac || !bc || !qm || !klm || !krm || !gate_logits || !nonpad || !left_tree_mask ||
@@ -474,6 +529,7 @@ int pcfgnat_links_from_scores(const float *ac, const float *bc, const float *qm,
                               const uint8_t *right_tree_mask, const uint8_t *main_chain, const int *slot_of,
                               const int *nodes, int M, int B, int L, int heads, int head_dim, int max_left, float *links,
                               void *stream) {
+    PCFGNAT_API_RANGE();
     if (max_left != 1) return PCFGNAT_ERR_UNSUPPORTED;
     if (B < 0 || L < 1 || M < 0 || M > L || heads < 1 || head_dim < 1) return PCFGNAT_ERR_INVALID_ARGUMENT;
     if (B && (!ac || !bc || !qm || !klm || !gate_logits || !nonpad || !left_tree_mask || !right_tree_mask || !main_chain ||
