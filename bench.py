@@ -362,10 +362,10 @@ def measure(ctx, name, batch, global_sentences, steps, warm, blocks=None, exchan
     block(3, True)
     serial_ms = [block(steps, True) for _ in range(min(nb, 5))]  # load -> run -> read-back, one batch at a time
     # the end-to-end figure: two step objects in turn, so that batch i + 1 is copied while batch i is computed
-    # eight GPUs pulling from one host: the bus is the bottleneck (24 GB/s per rank against 44 alone), so the
+    # several GPUs pulling from one host share its bus (24 GB/s per rank at N = 8 against 44-49 alone), so there the
     # transitions are fetched by the kernel that moves only the entries the kernels read (measured at N = 8: 984k
-    # sentences/s against 761k with copies alone); up to four GPUs the copy engines alone are as fast or faster
-    fetch = a.fetch if a.fetch != "auto" else ("links" if ctx.world > 4 else "none")
+    # sentences/s against 761k with copies alone; on one GPU both give the same 175k)
+    fetch = a.fetch if a.fetch != "auto" else ("links" if ctx.world > 1 else "none")
     pipe = ctx.runtime.PipelinedStep(lambda: make_step(ctx.runtime, batch, weight, dev, not a.no_graph, a.copy_chunks,
                                                        exchange, **shape)[0],
                                      fetch_from_host=None if fetch == "none" else fetch,
