@@ -33,7 +33,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
                      : "r"(bar), "r"(parity)
                      : "memory");
         if (ok) return true;
-        if (it > 32) __nanosleep(128);
+        if (it > 4096) __nanosleep(128);  // long waits only: a sleeping warp wakes up to 128 ns late
         if ((it & 255u) == 255u && *abort_flag) return false;
     }
     *abort_flag = 1;
