@@ -23,7 +23,8 @@
 //                              gradient of every logit (k, c, head) as X0, X1 [B][H][M][M] (left option 0 / 1,
 //                              scaled), their row sums (gradient of ab) and the gradient of the gate logits;
 //   links_features_grad_kernel one block per (sentence, head): the five small products that turn X0, X1 into the
-//                              gradients of q, kl, kr at the main-chain nodes and their left options.
+//                              gradients of q, kl, kr at the main-chain nodes and their left options (operands in
+//                              shared memory, 4 x 4 outputs per thread; a plain version for odd shapes).
 #include <cuda_fp16.h>
 
 #include "common.cuh"
@@ -433,7 +434,7 @@ __global__ void __launch_bounds__(kLinkThreads)
 // and scattered to the nodes: dq[nodes[a]], dkr[nodes[s]], dkl[nodes[a] - 1] and dkl[0] (which also takes row 1 of the
 // first main-chain node, whose left option 1 is node 0 again).  dq, dkl, dkr [B][L][H][D] f32 were zero-filled.
 __global__ void __launch_bounds__(256)
-    links_features_grad_kernel(const float *__restrict__ X0, const float *__restrict__ X1, const float *__restrict__ dab,
+    links_features_grad_simple_kernel(const float *__restrict__ X0, const float *__restrict__ X1, const float *__restrict__ dab,
                                const float *__restrict__ qm, const float *__restrict__ klm, const float *__restrict__ krm,
                                const int *__restrict__ nodes, int M, int L, int H, int D, float *__restrict__ dq,
                                float *__restrict__ dkl, float *__restrict__ dkr) {
@@ -475,6 +476,126 @@ __global__ void __launch_bounds__(256)
     }
 }
 
+// The same with every operand staged in shared memory once and 4 x 4 outputs per thread (D a multiple of 4): the five
+// products are small matrix products, M x M x D each, and a thread that computes one output from global memory
+// re-reads every operand M or D times.  The contributions to the "no left child" row of kl are summed in shared
+// memory and leave as one atomic per column (all M parents share that row).  xs = row pitch of X0 / X1 in shared
+// memory, M rounded up to a multiple of 4 with the padding zero.
+constexpr int kFeatThreads = 320;
+__global__ void __launch_bounds__(kFeatThreads)
+    links_features_grad_kernel(const float *__restrict__ X0, const float *__restrict__ X1, const float *__restrict__ dab,
+                               const float *__restrict__ qm, const float *__restrict__ klm, const float *__restrict__ krm,
+                               const int *__restrict__ nodes, int M, int L, int H, int D, int xs, float *__restrict__ dq,
+                               float *__restrict__ dkl, float *__restrict__ dkr) {
+    extern __shared__ __align__(16) float s_feat[];
+    const int h = blockIdx.x, b = blockIdx.y, tid = threadIdx.x;
+    const size_t bh = (size_t)b * H + h;
+    const float *da = dab + bh * M * 2;
+    const int HD = H * D;
+    float *sx0 = s_feat, *sx1 = sx0 + (size_t)M * xs, *sq = sx1 + (size_t)M * xs, *skr = sq + (size_t)M * D;
+    float *skl = skr + (size_t)M * D, *skl0 = skl + (size_t)(M + 1) * D;  // skl0 [D]: sum for row 0 of kl
+    {
+        const float *x0 = X0 + bh * M * M, *x1 = X1 + bh * M * M;
+        for (int i = tid; i < M * xs; i += kFeatThreads) {
+            const int r = i / xs, c = i - r * xs;
+            sx0[i] = c < M ? x0[(size_t)r * M + c] : 0.f;
+            sx1[i] = c < M ? x1[(size_t)r * M + c] : 0.f;
+        }
+        const float *q = qm + bh * M * D, *kr = krm + bh * M * D, *kl = klm + bh * (M + 1) * D;
+        for (int i = tid; i < M * D; i += kFeatThreads) sq[i] = q[i], skr[i] = kr[i];
+        for (int i = tid; i < (M + 1) * D; i += kFeatThreads) skl[i] = kl[i];
+        for (int i = tid; i < D; i += kFeatThreads) skl0[i] = 0.f;
+    }
+    __syncthreads();
+    const int CG = D / 4, micro = ((M + 3) / 4) * CG;
+    for (int mt = tid; mt < micro; mt += kFeatThreads) {
+        const int r0 = (mt / CG) * 4, d0 = (mt % CG) * 4;
+        int rr[4];  // rows of this tile, clamped: a row past the end repeats the last one and is not written
+#pragma unroll
+        for (int i = 0; i < 4; i++) rr[i] = r0 + i < M ? r0 + i : M - 1;
+        // rows as parents a: s0 = sum_s X0[a][s] krm[s], s1 = sum_s X1[a][s] krm[s]
+        float a0[4][4], a1[4][4];
+#pragma unroll
+        for (int i = 0; i < 4; i++)
+#pragma unroll
+            for (int c = 0; c < 4; c++) a0[i][c] = a1[i][c] = 0.f;
+        for (int s = 0; s < xs; s += 4) {
+            float4 x0v[4], x1v[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                x0v[i] = *reinterpret_cast<const float4 *>(sx0 + (size_t)rr[i] * xs + s);
+                x1v[i] = *reinterpret_cast<const float4 *>(sx1 + (size_t)rr[i] * xs + s);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const int sr = s + j < M ? s + j : M - 1;  // padding columns of X are zero
+                const float4 kv = *reinterpret_cast<const float4 *>(skr + (size_t)sr * D + d0);
+                const float kc[4] = {kv.x, kv.y, kv.z, kv.w};
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const float v0 = j == 0 ? x0v[i].x : j == 1 ? x0v[i].y : j == 2 ? x0v[i].z : x0v[i].w;
+                    const float v1 = j == 0 ? x1v[i].x : j == 1 ? x1v[i].y : j == 2 ? x1v[i].z : x1v[i].w;
+#pragma unroll
+                    for (int c = 0; c < 4; c++) {
+                        a0[i][c] = fmaf(v0, kc[c], a0[i][c]);
+                        a1[i][c] = fmaf(v1, kc[c], a1[i][c]);
+                    }
+                }
+            }
+        }
+        float kl0_part[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int r = r0 + i;
+            if (r >= M) continue;
+            const float w0 = da[r * 2 + 0], w1 = da[r * 2 + 1];
+            const int node = nodes[r];
+            const size_t at = ((size_t)b * L + node) * HD + (size_t)h * D + d0;
+            const int left = node - 1 > 0 ? node - 1 : 0;
+            float *dkl_row = dkl + ((size_t)b * L + left) * HD + (size_t)h * D + d0;
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                const float qv = sq[(size_t)r * D + d0 + c];
+                dq[at + c] = w0 * skl[d0 + c] + w1 * skl[(size_t)(1 + r) * D + d0 + c] + (a0[i][c] + a1[i][c]);
+                atomicAdd(dkl_row + c, w1 * qv + a1[i][c]);  // left option 1 of node r
+                kl0_part[c] += w0 * qv + a0[i][c];         // this node's part of the "no left child" row
+            }
+        }
+#pragma unroll
+        for (int c = 0; c < 4; c++) atomicAdd(skl0 + d0 + c, kl0_part[c]);
+        // rows as children s: sum_a ( (X0 + X1)[a][s] qm[a] + X0[a][s] klm[0] + X1[a][s] klm[1 + a] )
+        float t[4][4], x0sum[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int i = 0; i < 4; i++)
+#pragma unroll
+            for (int c = 0; c < 4; c++) t[i][c] = 0.f;
+        for (int a = 0; a < M; a++) {
+            const float4 xa0 = *reinterpret_cast<const float4 *>(sx0 + (size_t)a * xs + r0);
+            const float4 xa1 = *reinterpret_cast<const float4 *>(sx1 + (size_t)a * xs + r0);
+            const float4 qv = *reinterpret_cast<const float4 *>(sq + (size_t)a * D + d0);
+            const float4 k1 = *reinterpret_cast<const float4 *>(skl + (size_t)(1 + a) * D + d0);
+            const float v0[4] = {xa0.x, xa0.y, xa0.z, xa0.w}, v1[4] = {xa1.x, xa1.y, xa1.z, xa1.w};
+            const float qc[4] = {qv.x, qv.y, qv.z, qv.w}, kc[4] = {k1.x, k1.y, k1.z, k1.w};
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                x0sum[i] += v0[i];
+#pragma unroll
+                for (int c = 0; c < 4; c++) t[i][c] = fmaf(v1[i], kc[c], fmaf(v0[i] + v1[i], qc[c], t[i][c]));
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int r = r0 + i;
+            if (r >= M) continue;
+            const size_t at = ((size_t)b * L + nodes[r]) * HD + (size_t)h * D + d0;
+#pragma unroll
+            for (int c = 0; c < 4; c++) dkr[at + c] = fmaf(x0sum[i], skl[d0 + c], t[i][c]);
+        }
+    }
+    __syncthreads();
+    for (int d = tid; d < D; d += kFeatThreads) atomicAdd(dkl + ((size_t)b * L + 0) * HD + (size_t)h * D + d, skl0[d]);
+}
+
 }  // namespace
 
 int launch_links_scores(const float *qm, const float *klm, const float *krm, int M, int B, int H, int D, float *ac,
@@ -500,7 +621,16 @@ int launch_links_backward(const float *links_grad, const float *ac, const float 
                                                                      X0, X1, dab, dgates);
     if (cudaGetLastError() != cudaSuccess) return PCFGNAT_ERR_CUDA;
     if (M == 0) return PCFGNAT_OK;
-    links_features_grad_kernel<<<dim3(H, B), 256, 0, st>>>(X0, X1, dab, qm, klm, krm, nodes, M, L, H, D, dq, dkl, dkr);
+    // operands in shared memory and 4 x 4 outputs per thread where D allows it and they fit (M = 80, D = 64: 113 KB)
+    const int xs = (M + 3) / 4 * 4;
+    const size_t feat_smem = ((size_t)2 * M * xs + (size_t)(3 * M + 1) * D + D) * sizeof(float);
+    if (D % 4 == 0 && feat_smem <= (size_t)kSmemLimit - 1024 &&
+        ensure_dynamic_smem(links_features_grad_kernel, feat_smem) == cudaSuccess)
+        links_features_grad_kernel<<<dim3(H, B), kFeatThreads, feat_smem, st>>>(X0, X1, dab, qm, klm, krm, nodes, M, L, H, D,
+                                                                              xs, dq, dkl, dkr);
+    else
+        links_features_grad_simple_kernel<<<dim3(H, B), 256, 0, st>>>(X0, X1, dab, qm, klm, krm, nodes, M, L, H, D, dq, dkl,
+                                                                      dkr);
     return cuda_rc(cudaGetLastError());
 }
 
