@@ -348,6 +348,13 @@ int pcfgnat_copy_links_main_rows(void *dst, const void *src, int B, int L, int m
 int pcfgnat_copy_real_rows(void *dst, const void *src, const int64_t *host_lengths, int b0, int b1, int L,
                            size_t row_bytes, int max_copies, int64_t *rows_sent, void *stream);
 
+/* The copies pcfgnat_copy_real_rows would issue for the same arguments, without issuing them (host arithmetic only, no
+ * CUDA call): runs [2 * i] = first row and runs [2 * i + 1] = number of rows of copy i, in rows of the [B * L] view.
+ * Returns the number of copies (at most min(b1 - b0, max_copies if > 0)), or a negative error when `capacity` pairs
+ * do not hold them.  For callers that size pinned staging or account for the bytes beforehand, and for tests. */
+int pcfgnat_plan_real_rows(const int64_t *host_lengths, int b0, int b1, int L, int max_copies, int64_t *runs,
+                           int capacity);
+
 /* Fetches a batch's large inputs from HOST memory with one kernel that reads the host buffers itself (mapped pinned
  * memory, e.g. cudaHostAlloc / torch pin_memory; device memory works too), and only what the kernels of this library
  * read: the decoder states of the real graph nodes, hidden[b][l][.] for l < m_b (row_bytes per node, a multiple of

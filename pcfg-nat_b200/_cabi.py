@@ -35,6 +35,7 @@ SIGNATURES = {
     "pcfgnat_links_backward": (c_int, [c_void] * 13 + [c_int] * 6 + [c_void] * 8),
     "pcfgnat_links_from_scores": (c_int, [c_void] * 11 + [c_int] * 6 + [c_void] * 2),
     "pcfgnat_copy_links_main_rows": (c_int, [c_void] * 2 + [c_int] * 3 + [c_void]),
+    "pcfgnat_plan_real_rows": (c_int, [c_void] + [c_int] * 4 + [c_void] + [c_int]),
     "pcfgnat_copy_real_rows": (c_int, [c_void] * 3 + [c_int] * 3 + [c_size] + [c_int] + [c_void] * 2),
     "pcfgnat_stage_inputs": (c_int, [c_void] * 2 + [c_int] + [c_void] * 3 + [c_int] * 3 + [c_void]),
     "pcfgnat_loss_stats": (c_int, [c_void] * 2 + [c_int] + [c_void] * 2),

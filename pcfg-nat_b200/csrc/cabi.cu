@@ -112,6 +112,46 @@ inline size_t align256(size_t x) { return (x + 255) / 256 * 256; }
 
 namespace {
 
+// The runs of rows (first row, rows; in rows of the [B * L] view) that send the real graph nodes of sentences
+// [b0, b1): one per non-empty sentence, adjacent ones joined; with more runs than max_copies (> 0), neighbours are
+// joined across the smallest gaps of padding rows (which are then sent along) until max_copies runs are left.
+std::vector<std::pair<int64_t, int64_t>> plan_real_rows(const int64_t *host_lengths, int b0, int b1, int L, int max_copies) {
+    std::vector<std::pair<int64_t, int64_t>> runs;
+    runs.reserve((size_t)(b1 - b0));
+    for (int b = b0; b < b1; b++) {
+        int64_t m = host_lengths[b];
+        m = m < 0 ? 0 : (m > L ? L : m);
+        if (m == 0) continue;
+        const int64_t start = (int64_t)b * L;
+        if (!runs.empty() && runs.back().first + runs.back().second == start) runs.back().second += m;
+        else runs.emplace_back(start, m);
+    }
+    // a copy costs the host several microseconds: with more runs than max_copies, neighbours are joined across the
+    // smallest gaps of padding rows (which are then sent along) until max_copies runs are left
+    if (max_copies > 0 && runs.size() > (size_t)max_copies) {
+        std::vector<int64_t> gaps(runs.size() - 1);
+        for (size_t i = 0; i + 1 < runs.size(); i++) gaps[i] = runs[i + 1].first - (runs[i].first + runs[i].second);
+        std::vector<int64_t> sorted(gaps);
+        const size_t join = runs.size() - (size_t)max_copies;  // that many gaps go
+        std::nth_element(sorted.begin(), sorted.begin() + (join - 1), sorted.end());
+        const int64_t limit = sorted[join - 1];
+        size_t below = 0;
+        for (int64_t g : gaps) below += g < limit;
+        size_t at_limit = join - below;  // of the gaps equal to the limit, only this many are joined
+        std::vector<std::pair<int64_t, int64_t>> merged;
+        merged.reserve((size_t)max_copies);
+        merged.push_back(runs[0]);
+        for (size_t i = 0; i + 1 < runs.size(); i++) {
+            bool joined = gaps[i] < limit;
+            if (!joined && gaps[i] == limit && at_limit) joined = true, at_limit--;
+            if (joined) merged.back().second = runs[i + 1].first + runs[i + 1].second - merged.back().first;
+            else merged.push_back(runs[i + 1]);
+        }
+        runs.swap(merged);
+    }
+    return runs;
+}
+
 // NVTX range around an entry point (its host side: argument checks and launches) when PCFGNAT_NVTX=1 was set when
 // the library was first called; free otherwise.  The ranges carry the entry point's name, so that a timeline of the
 // host application shows which of its calls the kernels belong to.
@@ -374,6 +414,16 @@ int pcfgnat_copy_links_main_rows(void *dst, const void *src, int B, int L, int m
     return PCFGNAT_OK;
 }
 
+int pcfgnat_plan_real_rows(const int64_t *host_lengths, int b0, int b1, int L, int max_copies, int64_t *runs,
+                           int capacity) {
+    if (b0 < 0 || b1 < b0 || L < 1 || max_copies < 0 || capacity < 0) return PCFGNAT_ERR_INVALID_ARGUMENT;
+    if (b1 > b0 && !host_lengths) return PCFGNAT_ERR_INVALID_ARGUMENT;
+    const std::vector<std::pair<int64_t, int64_t>> plan = plan_real_rows(host_lengths, b0, b1, L, max_copies);
+    if ((size_t)capacity < plan.size() || (plan.size() && !runs)) return PCFGNAT_ERR_INVALID_ARGUMENT;
+    for (size_t i = 0; i < plan.size(); i++) runs[2 * i] = plan[i].first, runs[2 * i + 1] = plan[i].second;
+    return (int)plan.size();
+}
+
 int pcfgnat_copy_real_rows(void *dst, const void *src, const int64_t *host_lengths, int b0, int b1, int L,
                            size_t row_bytes, int max_copies, int64_t *rows_sent, void *stream) {
     PCFGNAT_API_RANGE();
@@ -383,40 +433,7 @@ int pcfgnat_copy_real_rows(void *dst, const void *src, const int64_t *host_lengt
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     unsigned char *d = static_cast<unsigned char *>(dst);
     const unsigned char *s = static_cast<const unsigned char *>(src);
-    // runs of rows to send: one per non-empty sentence, as (first row, rows), in rows of the [B * L] view
-    std::vector<std::pair<int64_t, int64_t>> runs;
-    runs.reserve((size_t)(b1 - b0));
-    for (int b = b0; b < b1; b++) {
-        int64_t m = host_lengths[b];
-        m = m < 0 ? 0 : (m > L ? L : m);
-        if (m == 0) continue;
-        const int64_t start = (int64_t)b * L;
-        if (!runs.empty() && runs.back().first + runs.back().second == start) runs.back().second += m;
-        else runs.emplace_back(start, m);
-    }
-    // a copy costs the host several microseconds: with more runs than max_copies, neighbours are joined across the
-    // smallest gaps of padding rows (which are then sent along) until max_copies runs are left
-    if (max_copies > 0 && runs.size() > (size_t)max_copies) {
-        std::vector<int64_t> gaps(runs.size() - 1);
-        for (size_t i = 0; i + 1 < runs.size(); i++) gaps[i] = runs[i + 1].first - (runs[i].first + runs[i].second);
-        std::vector<int64_t> sorted(gaps);
-        const size_t join = runs.size() - (size_t)max_copies;  // that many gaps go
-        std::nth_element(sorted.begin(), sorted.begin() + (join - 1), sorted.end());
-        const int64_t limit = sorted[join - 1];
-        size_t below = 0;
-        for (int64_t g : gaps) below += g < limit;
-        size_t at_limit = join - below;  // of the gaps equal to the limit, only this many are joined
-        std::vector<std::pair<int64_t, int64_t>> merged;
-        merged.reserve((size_t)max_copies);
-        merged.push_back(runs[0]);
-        for (size_t i = 0; i + 1 < runs.size(); i++) {
-            bool joined = gaps[i] < limit;
-            if (!joined && gaps[i] == limit && at_limit) joined = true, at_limit--;
-            if (joined) merged.back().second = runs[i + 1].first + runs[i + 1].second - merged.back().first;
-            else merged.push_back(runs[i + 1]);
-        }
-        runs.swap(merged);
-    }
+    const std::vector<std::pair<int64_t, int64_t>> runs = plan_real_rows(host_lengths, b0, b1, L, max_copies);
     for (const auto &r : runs) {
         const size_t off = (size_t)r.first * row_bytes;
         if (cudaMemcpyAsync(d + off, s + off, (size_t)r.second * row_bytes, cudaMemcpyDefault, st) != cudaSuccess)

@@ -155,3 +155,49 @@ def test_reduce_loss_across_two_gloo_ranks(tmp_path):
     for p in procs:
         out, _ = p.communicate(timeout=180)
         assert p.returncode == 0 and "ok" in out, out
+
+
+def _plan(l, lengths, b0, b1, L, max_copies):
+    lengths = np.ascontiguousarray(lengths, dtype=np.int64)
+    runs = np.zeros((max(b1 - b0, 1), 2), dtype=np.int64)
+    n = l.pcfgnat_plan_real_rows(lengths.ctypes.data, b0, b1, L, max_copies, runs.ctypes.data, runs.shape[0])
+    assert n >= 0, n
+    return [(int(a), int(c)) for a, c in runs[:n]]
+
+
+def test_plan_of_the_real_row_copies(pkg):
+    """pcfgnat_plan_real_rows (the host arithmetic behind pcfgnat_copy_real_rows): every real row is covered exactly
+    once, runs are disjoint and ascending, at most max_copies of them, and joining costs no more padding rows than
+    the cheapest choice of gaps."""
+    import importlib
+
+    l = importlib.import_module("pcfg_nat_b200._cabi").lib()
+    # a worked case: runs [0,3) [12,36) [48,60) [72,77); two copies close the gaps of 9 and one of the 12s
+    lengths = [3, 12, 12, 0, 20, -4, 5]
+    assert _plan(l, lengths, 0, 7, 12, 0) == [(0, 3), (12, 24), (48, 12), (72, 5)]
+    assert _plan(l, lengths, 0, 7, 12, 2) == [(0, 60), (72, 5)]
+    assert _plan(l, lengths, 1, 3, 12, 0) == [(12, 24)]
+    assert _plan(l, [0, 0, 0], 0, 3, 8, 4) == []
+    assert l.pcfgnat_plan_real_rows(None, 0, 2, 8, 0, None, 0) == -1
+    rng = np.random.default_rng(0)
+    for _ in range(200):
+        B, L = int(rng.integers(1, 40)), int(rng.integers(1, 30))
+        lengths = rng.integers(-2, L + 3, size=B)
+        k = int(rng.integers(0, 12))
+        free = _plan(l, lengths, 0, B, L, 0)
+        runs = _plan(l, lengths, 0, B, L, k)
+        real = np.zeros(B * L, dtype=bool)
+        for b in range(B):
+            real[b * L: b * L + int(np.clip(lengths[b], 0, L))] = True
+        sent = np.zeros(B * L, dtype=int)
+        for first, rows in runs:
+            assert rows > 0
+            sent[first: first + rows] += 1
+        assert sent.max(initial=0) <= 1 and (sent[real] == 1).all()
+        assert all(runs[i][0] + runs[i][1] < runs[i + 1][0] for i in range(len(runs) - 1))
+        assert len(runs) <= len(free) and (k == 0 or len(runs) <= max(k, 0) or len(free) <= k)
+        if k and len(free) > k:  # the joined gaps are the smallest ones
+            gaps = sorted(free[i + 1][0] - (free[i][0] + free[i][1]) for i in range(len(free) - 1))
+            assert len(runs) == k and int(sent.sum() - real.sum()) == sum(gaps[: len(free) - k])
+        else:
+            assert runs == free
