@@ -110,6 +110,16 @@ inline size_t align256(size_t x) { return (x + 255) / 256 * 256; }
 
 }  // namespace
 
+namespace pcfgnat {
+bool pdl_enabled() {
+    static const bool on = [] {
+        const char *v = getenv("PCFGNAT_PDL");
+        return v && v[0] == '1';
+    }();
+    return on;
+}
+}  // namespace pcfgnat
+
 namespace {
 
 // The runs of rows (first row, rows; in rows of the [B * L] view) that send the real graph nodes of sentences

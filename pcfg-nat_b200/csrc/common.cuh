@@ -77,6 +77,32 @@ __device__ __forceinline__ bool dsm_wait_column(uint32_t bar, uint32_t parity) {
 
 inline int cuda_rc(cudaError_t e) { return e == cudaSuccess ? PCFGNAT_OK : PCFGNAT_ERR_CUDA; }
 
+// ---- programmatic dependent launch for the chains of short kernels a step is made of.  A kernel launched with
+// launch_chain() may be scheduled while the kernel before it in the stream is still running (PCFGNAT_PDL=1); it
+// therefore starts with chain_begin(): wait until that kernel has finished and its memory is visible, then let the
+// next kernel of the chain be scheduled in turn.  What is saved is the launch latency between the kernels.  Without
+// the launch attribute both instructions do nothing.
+__device__ __forceinline__ void chain_begin() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+bool pdl_enabled();  // cabi.cu: PCFGNAT_PDL=1, read once
+template <class... KArgs, class... Args>
+inline cudaError_t launch_chain(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 // Raises a kernel's dynamic shared-memory limit, remembering per device the largest value already
 // set so that the steady state costs no driver call (the attribute is sticky per function and device).
 cudaError_t ensure_dynamic_smem_for(const void *kernel, size_t bytes);  // cabi.cu; keyed by (function, device)

@@ -38,6 +38,7 @@ __device__ __forceinline__ float block_sum(float v, float *scratch) {
 // (loss_b infinite or NaN).
 __global__ void loss_stats_kernel(const float *__restrict__ loss, const int64_t *__restrict__ tl, int B, float *stats) {
     __shared__ float scratch[32];
+    chain_begin();
     float s = 0.f, bad = 0.f;
     for (int b = threadIdx.x; b < B; b += blockDim.x) {
         const float v = loss[b];
@@ -68,6 +69,7 @@ __global__ void loss_stats_exchange_kernel(const float *__restrict__ loss, const
     __shared__ float scratch[32];
     __shared__ float part[PCFGNAT_EXCHANGE_MAX_WORLD][3];
     __shared__ unsigned epoch_s;
+    chain_begin();
     float s = 0.f, bad = 0.f;
     bool arrived = true;
     for (int b = threadIdx.x; b < B; b += blockDim.x) {
@@ -229,13 +231,13 @@ __global__ void force_emit_grad_kernel(const float *grad, const uint8_t *__restr
 }  // namespace
 
 int launch_loss_stats(const float *loss, const int64_t *tl, int B, float *stats, cudaStream_t st) {
-    loss_stats_kernel<<<1, 256, 0, st>>>(loss, tl, B, stats);
+    launch_chain(loss_stats_kernel, dim3(1), dim3(256), 0, st, loss, tl, B, stats);
     return cuda_rc(cudaGetLastError());
 }
 
 int launch_loss_stats_exchange(const float *loss, const int64_t *tl, int B, const uint64_t *peer_bufs, int rank, int world,
                                float *stats, int *status, cudaStream_t st) {
-    loss_stats_exchange_kernel<<<1, 256, 0, st>>>(loss, tl, B, peer_bufs, rank, world, stats, status);
+    launch_chain(loss_stats_exchange_kernel, dim3(1), dim3(256), 0, st, loss, tl, B, peer_bufs, rank, world, stats, status);
     return cuda_rc(cudaGetLastError());
 }
 

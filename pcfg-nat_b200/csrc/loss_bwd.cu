@@ -34,6 +34,7 @@ __global__ void __launch_bounds__(kMaxRows *kLanes)
                    const int64_t *__restrict__ ol, const int64_t *__restrict__ tl, int L, int T, float *G, int *status,
                    int Mc, int col_stride, int lk_stride, const float *redo) {
     extern __shared__ float smem[];
+    chain_begin();
     const int b = blockIdx.x;
     // redo: only the sentences the linear-space kernels left marked (loss_linear.cu)
     if (redo && !linear_needs_redo(redo + (size_t)b * (kLinearFrameHead + T + 2), (int)tl[b])) return;
@@ -157,6 +158,7 @@ __global__ void __launch_bounds__(kGradWarps * 32)
                 const float *__restrict__ links, const int64_t *__restrict__ ol, const int64_t *__restrict__ tl, int L,
                 int T, float *mg, float *lg, int Mc, const float *redo) {
     extern __shared__ float smem[];  // per warp: 2 rows of T floats (emission gradients of a and a-1)
+    chain_begin();
     const int b = blockIdx.y;
     if (redo && !linear_needs_redo(redo + (size_t)b * (kLinearFrameHead + T + 2), (int)tl[b])) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -323,8 +325,8 @@ int launch_grad_rows(const float *S, const float *S_grad, const float *match_all
     dim3 ggrid((npairs + kGradWarps - 1) / kGradWarps, B);
     auto launch = [&](auto kernel) {
         if (ensure_dynamic_smem(kernel, gsm) != cudaSuccess) return PCFGNAT_ERR_CUDA;
-        kernel<<<ggrid, kGradWarps * 32, gsm, st>>>(S, S_grad, match_all, links, ol, tl, L, T, mg, lg, Mc, redo);
-        return cuda_rc(cudaGetLastError());
+        return cuda_rc(launch_chain(kernel, ggrid, dim3(kGradWarps * 32), gsm, st, S, S_grad, match_all, links, ol, tl, L, T,
+                                    mg, lg, Mc, redo));
     };
     if (Mc <= 64) return launch(grad_kernel<2>);
     if (Mc <= 96) return launch(grad_kernel<3>);
@@ -353,15 +355,15 @@ int launch_loss_bwd_rows(const float *grad_output, const float *S, const float *
         auto k = outside_kernel<true>;
         e = ensure_dynamic_smem(k, smem_cols + smem_links);
         if (e != cudaSuccess) return PCFGNAT_ERR_CUDA;
-        k<<<grid, block, smem_cols + smem_links, st>>>(grad_output, S, match_all, links, ol, tl, L, T, S_grad, status,
-                                                       Mc, col_stride, lk_stride, redo);
+        launch_chain(k, grid, block, smem_cols + smem_links, st, grad_output, S, match_all, links, ol, tl, L, T, S_grad,
+                     status, Mc, col_stride, lk_stride, redo);
     } else {
         if (smem_cols > (size_t)kSmemLimit - 1024) return PCFGNAT_ERR_TOO_LARGE;
         auto k = outside_kernel<false>;
         e = ensure_dynamic_smem(k, smem_cols);
         if (e != cudaSuccess) return PCFGNAT_ERR_CUDA;
-        k<<<grid, block, smem_cols, st>>>(grad_output, S, match_all, links, ol, tl, L, T, S_grad, status, Mc,
-                                          col_stride, lk_stride, redo);
+        launch_chain(k, grid, block, smem_cols, st, grad_output, S, match_all, links, ol, tl, L, T, S_grad, status, Mc,
+                     col_stride, lk_stride, redo);
     }
     if (cudaGetLastError() != cudaSuccess) return PCFGNAT_ERR_CUDA;
     return launch_grad_rows(S, S_grad, match_all, links, ol, tl, B, L, T, mg, lg, st, redo);

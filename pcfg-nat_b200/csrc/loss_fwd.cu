@@ -106,6 +106,7 @@ __global__ void __launch_bounds__(kMaxRows *kLanes)
                     const int64_t *__restrict__ ol, const int64_t *__restrict__ tl, int L, int T, float *S, float *C,
                     float *loss, int *status, int Mc, int Lt, int col_stride, int lk_stride, const float *redo) {
     extern __shared__ float smem[];
+    chain_begin();
     const int b = blockIdx.x;
     // redo: only the sentences the linear-space kernels left marked (loss_linear.cu)
     if (redo) {
@@ -251,15 +252,15 @@ int launch_loss_fwd_rows(const float *match_all, const float *links, const int64
         auto k = loss_fwd_kernel<true>;
         e = ensure_dynamic_smem(k, smem_cols + smem_links);
         if (e != cudaSuccess) return PCFGNAT_ERR_CUDA;
-        k<<<grid, block, smem_cols + smem_links, st>>>(match_all, links, ol, tl, L, T, S, C, loss, status, Mc, Lt,
-                                                       col_stride, lk_stride, redo);
+        launch_chain(k, grid, block, smem_cols + smem_links, st, match_all, links, ol, tl, L, T, S, C, loss, status, Mc, Lt,
+                     col_stride, lk_stride, redo);
     } else {
         if (smem_cols > (size_t)kSmemLimit - 1024) return PCFGNAT_ERR_TOO_LARGE;
         auto k = loss_fwd_kernel<false>;
         e = ensure_dynamic_smem(k, smem_cols);
         if (e != cudaSuccess) return PCFGNAT_ERR_CUDA;
-        k<<<grid, block, smem_cols, st>>>(match_all, links, ol, tl, L, T, S, C, loss, status, Mc, Lt, col_stride,
-                                          lk_stride, redo);
+        launch_chain(k, grid, block, smem_cols, st, match_all, links, ol, tl, L, T, S, C, loss, status, Mc, Lt, col_stride,
+                     lk_stride, redo);
     }
     return cuda_rc(cudaGetLastError());
 }

@@ -208,6 +208,7 @@ __global__ void __launch_bounds__(kLThreads, 1)
                          int wide) {
     extern __shared__ float4 smem4[];
     float *smem = reinterpret_cast<float *>(smem4);
+    chain_begin();
     cg::cluster_group cluster = cg::this_cluster();
     const int crank = (int)cluster.block_rank();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -498,6 +499,7 @@ __global__ void __launch_bounds__(kLThreads, 1)
     constexpr int kGradChunk = 2;
     extern __shared__ float4 smem4[];
     float *smem = reinterpret_cast<float *>(smem4);
+    chain_begin();
     cg::cluster_group cluster = cg::this_cluster();
     const int crank = (int)cluster.block_rank();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -852,11 +854,13 @@ int launch_linear_cluster(Kernel kernel, int B, int nc, size_t smem, cudaStream_
     cfg.blockDim = dim3(kLThreads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = (unsigned)nc;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // the kernels start with chain_begin()
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     int max_clusters = 0;
@@ -864,6 +868,7 @@ int launch_linear_cluster(Kernel kernel, int B, int nc, size_t smem, cudaStream_
         cudaGetLastError();
         return PCFGNAT_ERR_UNSUPPORTED;
     }
+    cfg.numAttrs = pdl_enabled() ? 2 : 1;
     return cuda_rc(cudaLaunchKernelEx(&cfg, kernel, args...));
 }
 

@@ -209,6 +209,7 @@ __global__ void proj_prepare_kernel(const int64_t *__restrict__ ol, const int64_
                                     int *status) {
     __shared__ int warp_sum[32];
     __shared__ int before_s;
+    chain_begin();
     const int b = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     auto length = [&](int i) {
         int m = ol ? (int)ol[i] : L;
@@ -295,6 +296,7 @@ __global__ void __launch_bounds__(PROJ_THREADS, 1)
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag_s;
 
+    chain_begin();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = blockIdx.x;  // owner of a partial slot
     const uint32_t rank = PAIR ? cluster_ctarank() : 0;  // 0: the CTA that owns the pair's barriers and issues its MMAs
@@ -698,6 +700,7 @@ __global__ void proj_merge_kernel(const Partial *__restrict__ partials, const in
                                   int max_seg, int row_tiles, int pair, int V, int L, int T, const int64_t *__restrict__ ol,
                                   const int64_t *__restrict__ tl, const int64_t *__restrict__ targets, float *match,
                                   float *max_lprob, int64_t *argmax, float *lse_out) {
+    chain_begin();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
     if ((int)blockIdx.x >= kMergeSplit * row_tiles) {  // padding rows of sentence b: not projected
         const int b = blockIdx.x - kMergeSplit * row_tiles;
@@ -866,9 +869,8 @@ int launch_proj_kernel(const Geometry &geo, size_t smem, cudaStream_t st, const 
     if (!geo.pair) {
         auto k = proj_kernel<MODE, false>;
         if (ensure_dynamic_smem(k, smem) != cudaSuccess) return PCFGNAT_ERR_CUDA;
-        k<<<geo.ctas, PROJ_THREADS, smem, st>>>(map_w, map_dl, hidden, row_src, n_rows, geo.max_seg, V, KC, L, T, stok, sslot,
-                                                match, partials, ga, status);
-        return cuda_rc(cudaGetLastError());
+        return cuda_rc(launch_chain(k, dim3(geo.ctas), dim3(PROJ_THREADS), smem, st, map_w, map_dl, hidden, row_src, n_rows,
+                                    geo.max_seg, V, KC, L, T, stok, sslot, match, partials, ga, status));
     }
     auto k = proj_kernel<MODE, true>;
     if (ensure_dynamic_smem(k, smem) != cudaSuccess) return PCFGNAT_ERR_CUDA;
@@ -936,8 +938,9 @@ int launch_proj(const void *hidden, const void *weight, const int64_t *targets, 
 
     CUtensorMap map_w;
     if (!make_map(&map_w, weight, (uint64_t)V, (uint64_t)H, geo.pair ? BN / 2 : BN)) return PCFGNAT_ERR_CUDA;
-    proj_prepare_kernel<<<B, 128, 0, st>>>(ol, gather ? targets : nullptr, B, L, T, V, w.prefix, w.row_src, w.n_rows,
-                                           w.stok, w.sslot, status);
+    if (launch_chain(proj_prepare_kernel, dim3(B), dim3(128), 0, st, ol, gather ? targets : nullptr, B, L, T, V, w.prefix,
+                     w.row_src, w.n_rows, w.stok, w.sslot, status) != cudaSuccess)
+        return PCFGNAT_ERR_CUDA;
     const size_t smem = (size_t)KC_MAX * A_CHUNK_BYTES + (size_t)NSTAGE * B_STAGE_BYTES + 1024;
     const bool want_arg = max_lprob != nullptr || argmax != nullptr;
     const __half *hid = static_cast<const __half *>(hidden);
@@ -950,10 +953,10 @@ int launch_proj(const void *hidden, const void *weight, const int64_t *targets, 
                                                            gather ? match : nullptr, w.partials, none, status);
     if (rc != PCFGNAT_OK) return rc;
     const int row_tiles = (N + BM - 1) / BM;
-    proj_merge_kernel<<<kMergeSplit * row_tiles + B, kMergeThreads, 0, st>>>(w.partials, w.prefix, w.row_src, w.n_rows, geo.owners, geo.max_seg,
-                                                     row_tiles, geo.pair ? 1 : 0, V, L, T, ol, tl, targets, gather ? match : nullptr,
-                                                     max_lprob, argmax, lse);
-    return cuda_rc(cudaGetLastError());
+    return cuda_rc(launch_chain(proj_merge_kernel, dim3(kMergeSplit * row_tiles + B), dim3(kMergeThreads), 0, st,
+                                (const Partial *)w.partials, (const int *)w.prefix, (const int *)w.row_src,
+                                (const int *)w.n_rows, geo.owners, geo.max_seg, row_tiles, geo.pair ? 1 : 0, V, L, T, ol, tl,
+                                targets, gather ? match : nullptr, max_lprob, argmax, lse));
 }
 
 // Rows of padding (l >= m_b) are not projected: their gradient rows are zero.
@@ -998,7 +1001,9 @@ int launch_proj_dlogits(const void *hidden, const void *weight, const int64_t *t
     const Workspace w = carve(workspace, B, L, T, V);
     CUtensorMap map_w;
     if (!make_map(&map_w, weight, (uint64_t)V, (uint64_t)H, geo.pair ? BN / 2 : BN)) return PCFGNAT_ERR_CUDA;
-    proj_prepare_kernel<<<B, 128, 0, st>>>(ol, targets, B, L, T, V, w.prefix, w.row_src, w.n_rows, w.stok, w.sslot, status);
+    if (launch_chain(proj_prepare_kernel, dim3(B), dim3(128), 0, st, ol, targets, B, L, T, V, w.prefix, w.row_src, w.n_rows,
+                     w.stok, w.sslot, status) != cudaSuccess)
+        return PCFGNAT_ERR_CUDA;
     __nv_bfloat16 *dl = static_cast<__nv_bfloat16 *>(dlogits);
     const int compact = row_index != nullptr;
     if (compact)
