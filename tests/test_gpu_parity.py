@@ -1430,3 +1430,18 @@ def test_overlapped_load_fetching_from_host_buffers(pkg, ops, syn, mode):
         assert fetched.input_bytes() < plain.input_bytes()
         kernel_links = fetched.links.cpu()
         assert torch.equal(kernel_links, args[1])  # the model's masks leave nothing finite outside what was fetched
+
+
+def test_smoke_with_dependent_launches_and_ranges_switched_on():
+    """PCFGNAT_PDL=1 (programmatic dependent launch along the kernel chain) and PCFGNAT_NVTX=1 are read once per
+    process: a fresh interpreter runs the package's smoke check, which compares a step with the oracle, with both on."""
+    import subprocess
+    import sys
+
+    from conftest import ROOT
+
+    env = dict(os.environ, PCFGNAT_PDL="1", PCFGNAT_NVTX="1")
+    r = subprocess.run([sys.executable, "-c", "import __graft_entry__ as g; g.smoke()"], cwd=ROOT, env=env,
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert "smoke ok" in r.stdout
