@@ -270,8 +270,10 @@ __global__ void __launch_bounds__(kCThreads, 1)
     }
     // columns are exchanged with st.async counted on two alternating barriers (common.cuh), not a cluster barrier
     __shared__ __align__(8) uint64_t col_bar[2];
+    __shared__ int s_timeout;
     for (int i = tid; i < 4 * cs; i += kCThreads) col[i] = neg_inf();
     if (tid == 0) {
+        s_timeout = 0;
         for (int i = 0; i < 2; i++)
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(dsm_smem_u32(&col_bar[i])) : "memory");
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -286,7 +288,6 @@ __global__ void __launch_bounds__(kCThreads, 1)
     if (NC > 1) cluster.sync(); else __syncthreads();
     if (ctid == 0) Sb[(size_t)last * W + (n - 1)] = __ldg(mat + (size_t)(m - 1) * T + (n - 1));
 
-    bool arrived = true;
     for (int start = n - 2; start >= 0; start--) {
         const float *S1 = col + ((start + 1) & 3) * cs;
         const float *S2 = col + ((start + 2) & 3) * cs;
@@ -376,10 +377,11 @@ __global__ void __launch_bounds__(kCThreads, 1)
             }
             if (lane == 0) own[r * W + start] = res;
         }
-        if (NC > 1) arrived = dsm_wait_column(bar, (((n - 2) - start) >> 1) & 1) && arrived;
-        else __syncthreads();
+        // one warp waits for the column on the byte-counting barrier, the block barrier releases the others
+        if (NC > 1 && warp == kCWarps - 1 && !dsm_wait_column(bar, (((n - 2) - start) >> 1) & 1)) s_timeout = 1;
+        __syncthreads();
     }
-    if (!arrived) flag(status, PCFGNAT_STATUS_TIMEOUT);
+    if (s_timeout && tid == 0) flag(status, PCFGNAT_STATUS_TIMEOUT);
     // no CTA leaves (its shared memory with it) while a peer may still send to it; every wait above is bounded,
     // so every CTA gets here
     if (NC > 1) cluster.sync();

@@ -166,8 +166,10 @@ __global__ void __launch_bounds__(kVitThreads, 1)
         }
     }
     __shared__ __align__(8) uint64_t col_bar[2];
+    __shared__ int s_timeout;
     for (int i = tid; i < 4 * cs; i += kVitThreads) col[i] = neg_inf();  // lengths 0 and 1; slots >= Mb for good
     if (tid == 0) {
+        s_timeout = 0;
         for (int i = 0; i < 2; i++)
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(dsm_smem_u32(&col_bar[i])) : "memory");
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -183,7 +185,6 @@ __global__ void __launch_bounds__(kVitThreads, 1)
     const int x = lane & 3;
     const int prio = ((x & 1) << 1) | (x >> 1);  // reference thread 0 wins ties, then 2, 1, 3
     const int n_len = m / 4;
-    bool arrived = true;
     for (int len = 2; len < n_len; len++) {
         const float *S1 = col + ((len - 1) & 3) * cs;
         const float *S2 = col + ((len - 2) & 3) * cs;
@@ -209,10 +210,12 @@ __global__ void __launch_bounds__(kVitThreads, 1)
                 own_k[r * Q + len] = key;
             }
         }
-        if (NC > 1) arrived = dsm_wait_column(bar, ((len - 2) >> 1) & 1) && arrived;
-        else __syncthreads();
+        // one warp waits for the column on the byte-counting barrier, the block barrier releases the others: 32 warps
+        // polling the same barrier get in each other's way
+        if (NC > 1 && warp == kVitWarps - 1 && !dsm_wait_column(bar, ((len - 2) >> 1) & 1)) s_timeout = 1;
+        __syncthreads();
     }
-    if (!arrived) flag(status, PCFGNAT_STATUS_TIMEOUT);
+    if (s_timeout && tid == 0) flag(status, PCFGNAT_STATUS_TIMEOUT);
     // no CTA leaves (its shared memory with it) while a peer may still send to it: the last column has arrived
     // everywhere once every CTA has passed its last wait
     if (NC > 1) cluster.sync();
