@@ -86,6 +86,41 @@ __device__ __forceinline__ void viterbi_node(int id, int Mb, int lane, int prio,
     warp_argmax(best, key, lane);
 }
 
+// The same for a group of G lanes (G = 4, 8, 16 or 32, the groups of a warp side by side): lane q of the group scans
+// children ci = id + q + G i, so that its reference thread (ci - id) & 3 = q & 3 is still one per lane, and the group
+// settles on (largest value, smallest key) with a butterfly of shuffles.  The lanes of a group without a node
+// (live = false) go through the shuffles with -inf.
+template <class K0, class K1>
+__device__ __forceinline__ void viterbi_node_group(bool live, int id, int Mb, int q, int G, float oa, const float *S1,
+                                                   const float *S2, K0 k0, K1 k1, float &best, int &key) {
+    best = neg_inf();
+    key = INT_MAX;
+    if (live) {
+        const int x = q & 3, prio = ((x & 1) << 1) | (x >> 1);
+        for (int ci = id + q; ci < Mb; ci += G) {
+            const int kk = (prio << 24) | (ci << 1);
+            const float t0 = (k0(ci) + S1[ci]) + oa;
+            if (t0 > best) {
+                best = t0;
+                key = kk;
+            }
+            const float t1 = (k1(ci) + S2[ci]) + oa;
+            if (t1 > best) {
+                best = t1;
+                key = kk | 1;
+            }
+        }
+    }
+    for (int o = G >> 1; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int ok = __shfl_xor_sync(0xffffffffu, key, o);
+        if (ov > best || (ov == best && ok < key)) {  // -0 and +0 compare equal, as under the reference's '>'
+            best = ov;
+            key = ok;
+        }
+    }
+}
+
 __device__ __forceinline__ void viterbi_store(float best, int key, int a, int Q, int len, float *Sb, int64_t *Rb,
                                               int64_t *Lb, int64_t *Mtb) {
     if (isinf(best)) return;  // cell stays at its initial value (pcfg_viterbi.cu:113-121)
@@ -182,8 +217,14 @@ __global__ void __launch_bounds__(kVitThreads, 1)
     if (NC > 1) cluster.sync(); else __syncthreads();
     if (ctid == 0) Sb[(size_t)(m - 1) * Q + 1] = __ldg(ob + (m - 1));
 
-    const int x = lane & 3;
-    const int prio = ((x & 1) << 1) | (x >> 1);  // reference thread 0 wins ties, then 2, 1, 3
+    // G lanes share a node, as few as still let the warps take all of this CTA's nodes in one pass (a second pass
+    // costs a step more than the longer scan per lane does); lane q < NC of a group also sends the result to CTA q
+    int G = 32;
+    while ((32 / G) * kVitWarps < my_rows && (G >> 1) >= 4 && (G >> 1) >= NC) G >>= 1;
+    const int RW = 32 / G, q = lane % G, sub = lane / G;  // RW nodes per warp
+    const uint32_t rcol = NC > 1 && q < NC ? dsm_map_to_cta(dsm_smem_u32(col), q) : 0;  // this CTA's columns as CTA q maps them
+    const uint32_t rbar0 = NC > 1 && q < NC ? dsm_map_to_cta(dsm_smem_u32(&col_bar[0]), q) : 0;
+    const uint32_t rbar1 = NC > 1 && q < NC ? dsm_map_to_cta(dsm_smem_u32(&col_bar[1]), q) : 0;
     const int n_len = m / 4;
     for (int len = 2; len < n_len; len++) {
         const float *S1 = col + ((len - 1) & 3) * cs;
@@ -193,21 +234,25 @@ __global__ void __launch_bounds__(kVitThreads, 1)
         if (NC > 1 && tid == 0)  // this CTA expects the whole column of this length: one value per node of the chain
             asm volatile("{ .reg .b64 st; mbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1; }" ::"r"(bar), "r"(4 * Mb)
                          : "memory");
-        for (int r = warp; r < my_rows; r += kVitWarps) {
-            const int id = crank + NC * r;
-            const float *r0 = lk0 + r * lk_stride, *r1 = lk1 + r * lk_stride;
+        for (int r0w = warp * RW; r0w < my_rows; r0w += kVitWarps * RW) {
+            const int r = r0w + sub;
+            const bool live = r < my_rows;
+            const int rr = live ? r : 0, id = crank + NC * rr;
+            const float *r0 = lk0 + rr * lk_stride, *r1 = lk1 + rr * lk_stride;
             float best;
             int key;
-            viterbi_node(id, Mb, lane, prio, __ldg(ob + 2 * id + 1), S1, S2, [&](int ci) { return r0[ci]; },
-                         [&](int ci) { return r1[ci]; }, best, key);
-            if (NC > 1) {  // into every CTA's column, counted on that CTA's barrier of this length
-                if (lane < NC) dsm_store_async(dsm_map_to_cta(dsm_smem_u32(S0 + id), lane), best, dsm_map_to_cta(bar, lane));
-            } else if (lane == 0) {
-                S0[id] = best;
-            }
-            if (lane == 0) {
-                own_v[r * Q + len] = best;
-                own_k[r * Q + len] = key;
+            viterbi_node_group(live, id, Mb, q, G, __ldg(ob + 2 * id + 1), S1, S2, [&](int ci) { return r0[ci]; },
+                               [&](int ci) { return r1[ci]; }, best, key);
+            if (live) {
+                if (NC > 1) {  // into every CTA's column, counted on that CTA's barrier of this length
+                    if (q < NC) dsm_store_async(rcol + 4u * ((len & 3) * cs + id), best, (len & 1) ? rbar1 : rbar0);
+                } else if (q == 0) {
+                    S0[id] = best;
+                }
+                if (q == 0) {
+                    own_v[r * Q + len] = best;
+                    own_k[r * Q + len] = key;
+                }
             }
         }
         // one warp waits for the column on the byte-counting barrier, the block barrier releases the others: 32 warps
