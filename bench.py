@@ -85,6 +85,9 @@ def parse():
                     help="sentence groups the end-to-end leg sends (and projects) the decoder states in")
     ap.add_argument("--fetch", default="auto", choices=["auto", "none", "links", "all"],
                     help="what the end-to-end leg fetches from the host buffers by kernel instead of by copy engine")
+    ap.add_argument("--copy-real-rows", type=int, default=-1,
+                    help="copies per sentence group that send the decoder states without most padding rows "
+                         "(-1 = the step objects' default, 0 = the whole padded tensor)")
     ap.add_argument("--pipeline-depth", type=int, default=2,
                     help="step objects the end-to-end leg uses in turn (batches in flight)")
     ap.add_argument("--cpu-sample", type=int, default=0,
@@ -377,6 +380,9 @@ def measure(ctx, name, batch, global_sentences, steps, warm, blocks=None, exchan
                                      fetch_from_host=None if fetch == "none" else fetch,
                                      depth=a.pipeline_depth) if not a.no_graph else None
     if pipe is not None:
+        if a.copy_real_rows >= 0:
+            for st in pipe.steps:
+                st.copy_real_rows = a.copy_real_rows
         step_single = step
         step = pipe
         pipe.load(*host)
