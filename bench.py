@@ -418,11 +418,13 @@ def measure(ctx, name, batch, global_sentences, steps, warm, blocks=None, exchan
         block_piped(3)
         e2e_ms = [block_piped(steps) for _ in range(nb)]
         h2d = pipe.input_bytes()
+        copies_per_group = pipe.steps[0].copy_real_rows
         step = step_single
         del pipe
         pipe_used = True
     else:
         e2e_ms = serial_ms
+        copies_per_group = None
         pipe_used = False
     copy_block(2)
     copy_ms = copy_block(min(steps, 10)) / min(steps, 10)
