@@ -454,6 +454,7 @@ def measure(ctx, name, batch, global_sentences, steps, warm, blocks=None, exchan
                 "how": "every step copies its inputs from pinned host memory and reads its result back; two step "
                        "objects in turn, so that the copies of batch i + 1 run while batch i is computed",
                 "fetch_by_kernel": fetch if pipe_used else "none",
+                "copies_per_sentence_group": copies_per_group,
                 "one_batch_at_a_time": {"value": per_s(statistics.median(serial_ms)),
                                         "ms_per_step": statistics.median(serial_ms) / steps},
                 "bound": "host-to-device copies (PCIe)" if copy_max > e2e_med / steps * 0.95 else "device time"},
