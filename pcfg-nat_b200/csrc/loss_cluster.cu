@@ -181,17 +181,24 @@ __global__ void __launch_bounds__(kCThreads, 1)
                           int B, int wide, float *shares) {
     extern __shared__ float smem[];
     cg::cluster_group cluster = cg::this_cluster();
-    const int crank = (int)cluster.block_rank();
+    int crank = (int)cluster.block_rank();  // below: the rank among the CTAs that work on this sentence
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     // wide < 0: every sentence gets the whole cluster.  wide >= 0 (batches with more sentences than half the
-    // SMs): the clusters take the sentences in order of decreasing cost m * n, the `wide` costliest get the whole
-    // cluster and for the others only the first CTA works (the second leaves at once and frees its SM), so that
-    // the long sentences, which set the kernel's time, run on two SMs while every sentence still starts at once.
+    // SMs; clusters of two): the sentences are taken in order of decreasing cost m * n, the `wide` costliest get a
+    // cluster each and the others share clusters, one CTA per sentence, so that the grid is one CTA per SM: the
+    // long sentences, which set the kernel's time, run on two SMs while every sentence still starts at once.
+    // (A second CTA that merely left would not make room for clusters still waiting: a new cluster needs both of
+    // its SMs free together.)
     int NC = (int)cluster.num_blocks();
     int b = blockIdx.x / NC;
     if (wide >= 0) {
         __shared__ int s_b;
-        const int want = b;  // this cluster takes the sentence of this cost rank
+        const int want = b < wide ? b : wide + 2 * (b - wide) + crank;  // the cost rank this CTA serves
+        if (want >= B) return;  // the odd CTA of the last shared cluster
+        if (b >= wide) {
+            NC = 1;
+            crank = 0;
+        }
         for (int i = tid; i < B; i += kCThreads) {
             const long long mi = ol[i], ni = tl[i];
             const long long ci = lengths_ok((int)mi, (int)ni, L, T) ? mi * ni : 0;
@@ -205,10 +212,6 @@ __global__ void __launch_bounds__(kCThreads, 1)
         }
         __syncthreads();
         b = s_b;
-        if (want >= wide) {
-            if (crank > 0) return;  // before any cluster barrier; nothing of this CTA is touched by the first one
-            NC = 1;
-        }
     }
     const int ctid = crank * kCThreads + tid, cthreads = NC * kCThreads;  // thread index inside the cluster
     const int W = T + 2;
@@ -687,9 +690,14 @@ int launch_cluster(Kernel kernel, int B, int nc, size_t smem, cudaStream_t st, A
 // Number of sentences that get both CTAs of a cluster of two when the batch has more sentences than half the
 // SMs (so that one cluster size for all would leave SMs idle or sentences waiting), or 0 when that mode does not
 // apply: the SMs left over once every sentence has one.
-int mixed_width_count(int B, int Mc) {
+static int sm_count() {
     int dev = 0, sms = 148;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    return sms;
+}
+
+int mixed_width_count(int B, int Mc) {
+    const int sms = sm_count();
     if (B * 2 <= sms || B >= sms || B > 256 || Mc <= 16 || getenv("PCFGNAT_DP_CLUSTER_SIZE")) return 0;
     return sms - B;
 }
@@ -723,17 +731,19 @@ int launch_inside(const float *match_all, const float *links, const int64_t *ol,
                     sizeof(float);
         if (g.smem_in > (size_t)kSmemLimit - 1024) break;
         if (g.nc == 1) {
-            // more sentences than half the SMs: clusters of two, of which only the costliest sentences use both
-            // CTAs (see the kernel); every CTA can hold a whole chain, so the shared memory is that of one CTA
+            // more sentences than half the SMs: clusters of two, which the costliest sentences have to themselves
+            // and the others share (see the kernel); every CTA can hold a whole chain, so the shared memory is that of one CTA
             const int wide = mixed_width_count(B, Mc);
             if (wide > 0) {
-                int rc = launch_cluster(inside_cluster_kernel<TRIPS, SHARES>, B, 2, g.smem_in, st, match_all, links, ol, tl,
+                int rc = launch_cluster(inside_cluster_kernel<TRIPS, SHARES>, wide + (B - wide + 1) / 2, 2, g.smem_in, st, match_all, links, ol, tl,
                                         L, T, S, C, loss, status, Mc, Lt, g.cs, g.rows_cap, g.lk_stride, B, wide, shares);
                 if (rc != PCFGNAT_ERR_UNSUPPORTED) return rc;
             }
         }
+        // more CTAs than SMs: sentences by decreasing cost, so that the clusters that wait for a place get the cheapest
+        const int ranked = (long long)B * g.nc > sm_count() && B <= 256 ? B : -1;
         int rc = launch_cluster(inside_cluster_kernel<TRIPS, SHARES>, B, g.nc, g.smem_in, st, match_all, links, ol, tl, L,
-                                T, S, C, loss, status, Mc, Lt, g.cs, g.rows_cap, g.lk_stride, B, -1, shares);
+                                T, S, C, loss, status, Mc, Lt, g.cs, g.rows_cap, g.lk_stride, B, ranked, shares);
         if (rc != PCFGNAT_ERR_UNSUPPORTED) return rc;
     }
     return PCFGNAT_ERR_UNSUPPORTED;

@@ -113,17 +113,26 @@ __device__ __forceinline__ float dot4(const float4 &a, const float4 &b) {
 // Floats the outside kernel keeps in front of its step-loop memory (E0, E1 and the column scales), a multiple of 4.
 __host__ __device__ inline int linear_outside_head(int rows_cap, int W) { return (2 * rows_cap * W + W + 3) & ~3; }
 
-// The sentence of this cluster and the number of its CTAs that work on it (the mixed-width rule of
-// loss_cluster.cu: with `wide` >= 0 the clusters take the sentences by decreasing cost and only the `wide`
-// costliest use every CTA).  False: this CTA has nothing to do and must return at once.
+// The sentence of this CTA, the number of CTAs that work on it and this CTA's rank among them.  wide < 0: cluster
+// k takes sentence k with all its CTAs.  wide >= 0: the sentences are taken by decreasing cost; the `wide`
+// costliest get a cluster each, the others (clusters of two only) share clusters, one CTA per sentence, so that
+// the grid is one CTA per SM and every sentence starts at once.  (A second CTA that merely left would not make
+// room for the clusters still waiting: a new cluster needs both of its SMs free together.)  wide = B is the plain
+// ranking for grids larger than the GPU: the clusters that wait for a place get the cheapest sentences.  False:
+// nothing for this CTA.
 __device__ __forceinline__ bool pick_sentence(const int64_t *ol, const int64_t *tl, int B, int L, int T, int wide,
-                                              int cluster_blocks, int crank, int &b, int &NC) {
+                                              int cluster_blocks, int &crank, int &b, int &NC) {
     NC = cluster_blocks;
     b = blockIdx.x / cluster_blocks;
     if (wide < 0) return true;
+    const int want = b < wide ? b : wide + 2 * (b - wide) + crank;  // the cost rank this CTA serves
+    if (want >= B) return false;
+    if (b >= wide) {
+        NC = 1;
+        crank = 0;
+    }
     __shared__ int s_b;
     __shared__ int s_cost[kMaxMixedBatch];  // m n of every sentence (0: lengths out of range)
-    const int want = b;
     for (int i = threadIdx.x; i < B; i += kLThreads) {
         const long long mi = ol[i], ni = tl[i];
         s_cost[i] = lengths_ok((int)mi, (int)ni, L, T) ? (int)(mi * ni) : 0;
@@ -140,10 +149,6 @@ __device__ __forceinline__ bool pick_sentence(const int64_t *ol, const int64_t *
     }
     __syncthreads();
     b = s_b;
-    if (want >= wide) {
-        if (crank > 0) return false;
-        NC = 1;
-    }
     return true;
 }
 
@@ -210,7 +215,7 @@ __global__ void __launch_bounds__(kLThreads, 1)
     float *smem = reinterpret_cast<float *>(smem4);
     chain_begin();
     cg::cluster_group cluster = cg::this_cluster();
-    const int crank = (int)cluster.block_rank();
+    int crank = (int)cluster.block_rank();  // from pick_sentence on: the rank among the CTAs of this sentence
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 #ifdef PCFGNAT_TIMING
     const long long t_start = clock64();
@@ -501,7 +506,7 @@ __global__ void __launch_bounds__(kLThreads, 1)
     float *smem = reinterpret_cast<float *>(smem4);
     chain_begin();
     cg::cluster_group cluster = cg::this_cluster();
-    const int crank = (int)cluster.block_rank();
+    int crank = (int)cluster.block_rank();  // from pick_sentence on: the rank among the CTAs of this sentence
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 #ifdef PCFGNAT_TIMING
     const long long t_start = clock64();
@@ -805,7 +810,9 @@ __global__ void __launch_bounds__(kLThreads, 1)
 }
 
 struct LinearGeometry {
-    int nc, cs, rows_cap, wide;
+    int nc, cs, rows_cap;
+    int wide;                 // -1: cluster k takes sentence k; else the sentences are taken by cost (pick_sentence)
+    int launch_nc, clusters;  // cluster size and number of clusters of the launch
     size_t smem_in, smem_out;
 };
 
@@ -837,20 +844,29 @@ LinearGeometry linear_geometry(int B, int Mc, int W) {
             break;
         }
     }
+    g.launch_nc = g.nc;
+    g.clusters = B;
     if (g.nc == 1) {
+        // mixed widths: clusters of two; the costliest sentences have one to themselves, the others share them in pairs
         const int wide = mixed_width_count(B, Mc);
-        if (wide > 0) g.wide = wide;
+        if (wide > 0) {
+            g.wide = wide;
+            g.launch_nc = 2;
+            g.clusters = wide + (B - wide + 1) / 2;
+        }
     }
+    // more CTAs than SMs: the clusters that have to wait for a place take the cheapest sentences
+    if (g.wide < 0 && g.nc >= 1 && (long long)B * g.nc > sms && B <= kMaxMixedBatch) g.wide = B;
     return g;
 }
 
 template <class Kernel, class... Args>
-int launch_linear_cluster(Kernel kernel, int B, int nc, size_t smem, cudaStream_t st, Args... args) {
+int launch_linear_cluster(Kernel kernel, int clusters, int nc, size_t smem, cudaStream_t st, Args... args) {
     if (ensure_dynamic_smem(kernel, smem) != cudaSuccess) return PCFGNAT_ERR_CUDA;
     if (nc > 8 && cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess)
         return PCFGNAT_ERR_UNSUPPORTED;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)(B * nc));
+    cfg.gridDim = dim3((unsigned)(clusters * nc));
     cfg.blockDim = dim3(kLThreads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
@@ -877,11 +893,11 @@ int launch_linear(const LinearGeometry &g, const float *match_all, const float *
                   int B, int L, int T, float *Y, float *O, float *frames, float *loss, float *mg, float *lg, int *status,
                   cudaStream_t st) {
     const int Mc = main_slots(L, 1);
-    const int nc = g.wide >= 0 ? 2 : g.nc;  // mixed widths: clusters of two of which only the costliest use both CTAs
-    int rc = launch_linear_cluster(inside_linear_kernel<G, TRIPS>, B, nc, g.smem_in, st, match_all, links, ol, tl, L, T, Y,
-                                   frames, loss, mg, status, Mc, g.cs, g.rows_cap, B, g.wide);
+    const int nc = g.launch_nc, clusters = g.clusters;
+    int rc = launch_linear_cluster(inside_linear_kernel<G, TRIPS>, clusters, nc, g.smem_in, st, match_all, links, ol, tl, L, T,
+                                   Y, frames, loss, mg, status, Mc, g.cs, g.rows_cap, B, g.wide);
     if (rc) return rc;
-    return launch_linear_cluster(outside_linear_kernel<G, TRIPS>, B, nc, g.smem_out, st, match_all, links, ol, tl, L, T,
+    return launch_linear_cluster(outside_linear_kernel<G, TRIPS>, clusters, nc, g.smem_out, st, match_all, links, ol, tl, L, T,
                                  (const float *)Y, O, frames, mg, lg, status, Mc, g.cs, g.rows_cap, B, g.wide);
 }
 

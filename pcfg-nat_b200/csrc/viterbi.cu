@@ -138,16 +138,23 @@ __global__ void __launch_bounds__(kVitThreads, 1)
                            int *status, int Mc, int cs, int rows_cap, int lk_stride, int B, int wide) {
     extern __shared__ float smem[];
     cg::cluster_group cluster = cg::this_cluster();
-    const int crank = (int)cluster.block_rank();
+    int crank = (int)cluster.block_rank();  // below: the rank among the CTAs that work on this sentence
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    // wide < 0: every sentence gets the whole cluster.  wide >= 0 (more sentences than half the SMs): the clusters
-    // take the sentences in order of decreasing graph length, the `wide` longest get both CTAs of a cluster of
-    // two and for the others only the first CTA works (the second leaves at once and frees its SM).
+    // wide < 0: every sentence gets the whole cluster.  wide >= 0 (more sentences than half the SMs; clusters of
+    // two): the sentences are taken in order of decreasing graph length, the `wide` longest get a cluster each and
+    // the others share clusters, one CTA per sentence, so that the grid is one CTA per SM and every sentence
+    // starts at once (a second CTA that merely left would not make room for clusters still waiting: a new cluster
+    // needs both of its SMs free together).
     int NC = (int)cluster.num_blocks();
     int b = blockIdx.x / NC;
     if (wide >= 0) {
         __shared__ int s_b;
-        const int want = b;  // this cluster takes the sentence of this length rank
+        const int want = b < wide ? b : wide + 2 * (b - wide) + crank;  // the length rank this CTA serves
+        if (want >= B) return;  // the odd CTA of the last shared cluster
+        if (b >= wide) {
+            NC = 1;
+            crank = 0;
+        }
         for (int i = tid; i < B; i += kVitThreads) {
             const long long mi = ol[i], ci = (mi >= 2 && mi <= L) ? mi : 0;
             int before = 0;
@@ -159,10 +166,6 @@ __global__ void __launch_bounds__(kVitThreads, 1)
         }
         __syncthreads();
         b = s_b;
-        if (want >= wide) {
-            if (crank > 0) return;  // before any cluster barrier; nothing of this CTA is touched by the first one
-            NC = 1;
-        }
     }
     const int ctid = crank * kVitThreads + tid, cthreads = NC * kVitThreads;  // thread index inside the cluster
     const int Q = L / 4;
@@ -428,8 +431,8 @@ int launch_viterbi(const float *ob, const float *links, const int64_t *ol, int B
         const int want = atoi(v);
         if (want == 1 || want == 2 || want == 4 || want == 8 || want == 16) nc = want;
     }
-    // more sentences than half the SMs but fewer than SMs: clusters of two of which only the longest sentences
-    // use both CTAs (see the kernel); `wide` = the SMs left over once every sentence has one
+    // more sentences than half the SMs but fewer than SMs: clusters of two, which the longest sentences have to
+    // themselves and the others share (see the kernel); `wide` = the SMs left over once every sentence has one
     int wide = -1;
     if (nc == 1 && B * 2 > sms && B < sms && B <= 256 && Mc > 16 && !getenv("PCFGNAT_DP_CLUSTER_SIZE")) wide = sms - B;
     if (dp_kernel_choice() == kDpRows) nc = 32;  // skips the loop below
@@ -444,8 +447,12 @@ int launch_viterbi(const float *ob, const float *links, const int64_t *ol, int B
             break;
         }
         cudaLaunchConfig_t cfg = {};
-        const int launch_nc = wide >= 0 ? 2 : nc;
-        cfg.gridDim = dim3((unsigned)(B * launch_nc));
+        // mixed widths only while one CTA holds a chain; a grid larger than the GPU takes the sentences by
+        // decreasing length (wide = B), so that the clusters that wait for a place get the shortest
+        const bool mixed = wide >= 0 && nc == 1;
+        const int order = mixed ? wide : ((long long)B * nc > sms && B <= 256 ? B : -1);
+        const int launch_nc = mixed ? 2 : nc;
+        cfg.gridDim = dim3((unsigned)((mixed ? wide + (B - wide + 1) / 2 : B) * launch_nc));
         cfg.blockDim = dim3(kVitThreads);
         cfg.dynamicSmemBytes = smem;
         cfg.stream = st;
@@ -462,7 +469,7 @@ int launch_viterbi(const float *ob, const float *links, const int64_t *ol, int B
             continue;  // this cluster size cannot be scheduled here: try the next one
         }
         return cuda_rc(cudaLaunchKernelEx(&cfg, viterbi_cluster_kernel, ob, links, ol, L, S, R, Lt, Mt, status, Mc, cs,
-                                          rows_cap, lk_stride, B, wide));
+                                          rows_cap, lk_stride, B, order));
     }
     const size_t smem_cols = (size_t)3 * cs * sizeof(float);
     if (smem_cols > (size_t)kSmemLimit - 1024) return PCFGNAT_ERR_TOO_LARGE;

@@ -354,8 +354,8 @@ def test_logsoftmax_gather_reference_golden_and_autograd(ops):
 
 
 def test_fused_loss_many_sentences_mixed_cluster_widths(ops, syn, monkeypatch):
-    """More sentences than half the SMs: the fused forward + backward runs its inside pass as cost-ordered clusters
-    of two in which only the costliest sentences use both CTAs.  Loss and gradients against the oracle, with an
+    """More sentences than half the SMs: the fused forward + backward runs its passes as cost-ordered clusters
+    of two, which the costliest sentences have to themselves and the others share, one CTA each.  Loss and gradients against the oracle, with an
     invalid sentence and wildly different lengths in the batch."""
     monkeypatch.delenv("PCFGNAT_DP_KERNEL", raising=False)
     monkeypatch.delenv("PCFGNAT_DP_CLUSTER_SIZE", raising=False)
@@ -387,15 +387,19 @@ def test_fused_loss_many_sentences_mixed_cluster_widths(ops, syn, monkeypatch):
     ops.read_status(DEV)
 
 
-def test_fused_loss_model_graph_size(ops, syn, monkeypatch):
+@pytest.mark.parametrize("batch", [24, 90])
+def test_fused_loss_model_graph_size(ops, syn, monkeypatch, batch):
     """Graphs of 8 * source + 2 nodes, the size the reference model builds at left_tree_layer 1
     (models/glat_decomposed_with_link_two_hands_tri_pcfg.py:322), on the sentence lengths of the training batch:
-    up to 161 main-chain nodes per sentence.  Loss and gradients against the oracle, Viterbi tables bit for bit."""
+    up to 161 main-chain nodes per sentence.  Loss and gradients against the oracle, Viterbi tables bit for bit.
+    With 90 sentences a chain needs two CTAs and the grid is larger than the GPU: the clusters take the sentences
+    by decreasing cost; the inside table in the reference's order must not notice (bit for bit the table of the
+    kernel that takes them in batch order)."""
     monkeypatch.delenv("PCFGNAT_DP_KERNEL", raising=False)
     monkeypatch.delenv("PCFGNAT_DP_CLUSTER_SIZE", raising=False)
     monkeypatch.delenv("PCFGNAT_EXACT_ORDER", raising=False)
     w = syn.WORKLOADS["train_batch_model_graph"]
-    b, ma = _loss_inputs(syn, syn.Workload("model_graph", batch=24, vocab=40, hidden=8, src_min=w.src_min,
+    b, ma = _loss_inputs(syn, syn.Workload("model_graph", batch=batch, vocab=40, hidden=8, src_min=w.src_min,
                                            src_max=w.src_max, upsample=w.upsample, graph_offset=w.graph_offset,
                                            emissions="logits"), 33)
     assert int(b.output_length.max()) > 256 and (b.output_length % 8 == 2).all()
@@ -417,6 +421,10 @@ def test_fused_loss_model_graph_size(ops, syn, monkeypatch):
     np.testing.assert_array_equal(R2.cpu().numpy(), Ro)
     np.testing.assert_array_equal(L2.cpu().numpy(), Lo)
     np.testing.assert_array_equal(M2.cpu().numpy(), Mo)
+    S_ranked, _ = k.pcfg_loss(ma.to(DEV), b.links.to(DEV), ol.to(DEV), tl.to(DEV), 1)
+    monkeypatch.setenv("PCFGNAT_DP_KERNEL", "rows")
+    S_rows, _ = k.pcfg_loss(ma.to(DEV), b.links.to(DEV), ol.to(DEV), tl.to(DEV), 1)
+    assert np.array_equal(_bits(S_ranked.cpu().numpy()), _bits(S_rows.cpu().numpy()))
     assert ops.read_status(DEV) == 0
 
 
