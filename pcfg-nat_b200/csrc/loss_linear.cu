@@ -284,6 +284,7 @@ __global__ void __launch_bounds__(kLThreads, 1)
     for (int r = warp; r < my_rows; r += kLWarps) {
         const int ai = crank + NC * r;
         const float *row = lkb + (size_t)(2 * ai + 1) * 2 * L;
+#pragma unroll 4
         for (int ci = lane; ci < cs; ci += 32) {
             float p0 = 0.f, p1 = 0.f;
             if (ci > ai && ci < Mb) {
@@ -494,14 +495,69 @@ __global__ void __launch_bounds__(kLThreads, 1)
 // ---------------------------------------------------------------------------------------
 // outside pass + gradients
 // ---------------------------------------------------------------------------------------
-// J = children per lane in the links-gradient sums (32 J >= main-chain nodes).
+// Sums of the links gradient of one node over the steps: acc0[j] = sum_tc x0[tc - 1] y_tc[c], acc1[j] = sum_tc
+// x1[tc - 2] y_tc[c] for the children c = lane + 32 j of C groups, of which the first D are skipped (all at or
+// below the node).  Column tc of y meets x0 of step tc - 1 and x1 of step tc - 2: one load per column and child.
+// Four columns at a time, all their loads issued before the sums: a warp has few neighbours on its scheduler
+// here, so it has to cover the shared-memory latency itself; the phase is bound by instruction issue.
+template <int C, int D>
+__device__ __forceinline__ void links_grad_sums(const float *x0r, const float *x1r, const float *ycol, int cs, int n,
+                                                const bool (&in)[C], float (&acc0)[C], float (&acc1)[C]) {
+    {  // column 1 has no x1 partner
+        const float xa = x0r[0];
+#pragma unroll
+        for (int j = D; j < C; j++) acc0[j] = xa * (in[j] ? ycol[32 * j] : 0.f);
+    }
+    int tc = 2;
+    for (; tc + 3 <= n - 1; tc += 4) {
+        float xa[4], xb[4], y[4][C];
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            xa[u] = x0r[tc + u - 1];
+            xb[u] = x1r[tc + u - 2];
+#pragma unroll
+            for (int j = D; j < C; j++) y[u][j] = in[j] ? ycol[(tc + u - 1) * cs + 32 * j] : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; u++)
+#pragma unroll
+            for (int j = D; j < C; j++) {
+                acc0[j] = fmaf(xa[u], y[u][j], acc0[j]);
+                acc1[j] = fmaf(xb[u], y[u][j], acc1[j]);
+            }
+    }
+    for (; tc <= n - 1; tc++) {
+        const float xa = x0r[tc - 1], xb = x1r[tc - 2];
+#pragma unroll
+        for (int j = D; j < C; j++) {
+            const float y = in[j] ? ycol[(tc - 1) * cs + 32 * j] : 0.f;
+            acc0[j] = fmaf(xa, y, acc0[j]);
+            acc1[j] = fmaf(xb, y, acc1[j]);
+        }
+    }
+}
+// the instance for `dead` skipped groups (warp-uniform); dead = C: nothing to sum
+template <int C, int D>
+__device__ __forceinline__ void links_grad_dispatch(int dead, const float *x0r, const float *x1r, const float *ycol, int cs,
+                                                    int n, const bool (&in)[C], float (&acc0)[C], float (&acc1)[C]) {
+    if constexpr (D < C) {
+        if (dead == D)
+            links_grad_sums<C, D>(x0r, x1r, ycol, cs, n, in, acc0, acc1);
+        else
+            links_grad_dispatch<C, D + 1>(dead, x0r, x1r, ycol, cs, n, in, acc0, acc1);
+    }
+}
+
 template <int G, int TRIPS>
 __global__ void __launch_bounds__(kLThreads, 1)
     outside_linear_kernel(const float *__restrict__ match_all, const float *__restrict__ links,
                           const int64_t *__restrict__ ol, const int64_t *__restrict__ tl, int L, int T,
                           const float *__restrict__ Y, float *O, float *frames, float *mg, float *lg, int *status, int Mc,
                           int cs, int rows_cap, int B, int wide) {
-    constexpr int kGradChunk = 2;
+    // groups of 32 children a lane sums in one pass over the steps of the links gradient: all the kernel's row
+    // width allows (4 G TRIPS children), in two passes when that is more than four
+    constexpr int kChunksMax = (4 * G * TRIPS + 31) / 32;
+    constexpr int kGradChunk = kChunksMax <= 4 ? kChunksMax : (kChunksMax + 1) / 2;
     extern __shared__ float4 smem4[];
     float *smem = reinterpret_cast<float *>(smem4);
     chain_begin();
@@ -561,6 +617,7 @@ __global__ void __launch_bounds__(kLThreads, 1)
     __syncthreads();  // the maxima are used up: invs takes the scales below
     for (int r = warp; r < my_rows; r += kLWarps) {
         const int ci = crank + NC * r;
+#pragma unroll 4
         for (int ai = lane; ai < cs; ai += 32) {
             float p0 = 0.f, p1 = 0.f;
             if (ai < ci) {
@@ -704,17 +761,21 @@ __global__ void __launch_bounds__(kLThreads, 1)
         e1[i] = (e1[i] * o) * (t + 1 < W ? invs[t + 1] : 0.f);
     }
     __syncthreads();
+    PCFGNAT_STAMP(1, 11)
 
     // ---- links_grad rows of this CTA's nodes: sums over the steps.  The y table of the whole chain is staged in
     // the shared memory the matrices and columns no longer need (the launcher sizes the kernel for it).
     const float *Yb = Y + (size_t)b * W * Mc;
     float *ys = loop_mem;  // [n - 1][cs]: y_t[c] in row t - 1, over the columns and matrices of the step loop
     float *lgb = lg + (size_t)b * L * 2 * L;
+    const bool pairs_ok = !(L & 1) && !(reinterpret_cast<uintptr_t>(lg) & 7);  // rows and half rows start on 8 bytes
+#pragma unroll 4
     for (int i = tid; i < (n - 1) * cs; i += kLThreads) {
         const int tc = 1 + i / cs, c = i - (tc - 1) * cs;
         ys[i] = c < Mb ? __ldg(Yb + (size_t)tc * Mc + c) : 0.f;
     }
     __syncthreads();
+    PCFGNAT_STAMP(1, 12)
     for (int r = warp; r < my_rows; r += kLWarps) {
         const int ai = crank + NC * r, a = 2 * ai + 1;
         const float *x0r = e0 + r * W, *x1r = e1 + r * W;
@@ -732,29 +793,29 @@ __global__ void __launch_bounds__(kLThreads, 1)
                     if (ai >= 1) l1[j] = __ldg(lrow + L + 2 * ci + 1);
                 }
             }
-            if ((j0 + kGradChunk) * 32 > ai + 1) {  // else: all of these children are at or below the node itself
-                // column tc of y meets x0 of step tc - 1 and x1 of step tc - 2: one load per column and child
-                for (int tc = 1; tc <= n - 1; tc++) {
-                    const float xa = x0r[tc - 1], xb = tc >= 2 ? x1r[tc - 2] : 0.f;
-                    const float *ycol = ys + (tc - 1) * cs + 32 * j0 + lane;
+            // groups of 32 children that lie at or below the node itself have no pair with it: skipped as a whole
+            const int dead = min(max((ai + 1) / 32 - j0, 0), kGradChunk);
+            bool in[kGradChunk];
 #pragma unroll
-                    for (int j = 0; j < kGradChunk; j++) {
-                        const float y = 32 * (j0 + j) + lane < cs ? ycol[32 * j] : 0.f;
-                        acc0[j] = fmaf(xa, y, acc0[j]);
-                        acc1[j] = fmaf(xb, y, acc1[j]);
-                    }
-                }
-            }
+            for (int j = 0; j < kGradChunk; j++) in[j] = 32 * (j0 + j) + lane < cs;
+            links_grad_dispatch<kGradChunk, 0>(dead, x0r, x1r, ys + 32 * j0 + lane, cs, n, in, acc0, acc1);
 #pragma unroll
             for (int j = 0; j < kGradChunk; j++) {
                 const int ci = lane + 32 * (j0 + j);
-                if (2 * ci < L) {
-                    row[2 * ci] = 0.f;
-                    row[L + 2 * ci] = 0.f;
-                }
-                if (2 * ci + 1 < L) {
-                    row[2 * ci + 1] = exp_clean(l0[j]) * acc0[j];  // exp(-inf) = 0 where there is no pair
-                    row[L + 2 * ci + 1] = exp_clean(l1[j]) * acc1[j];
+                const float g0 = exp_clean(l0[j]) * acc0[j];  // exp(-inf) = 0 where there is no pair
+                const float g1 = exp_clean(l1[j]) * acc1[j];
+                if (pairs_ok && 2 * ci + 1 < L) {  // the leaf's zero and the child's value in one 8-byte store
+                    *reinterpret_cast<float2 *>(row + 2 * ci) = make_float2(0.f, g0);
+                    *reinterpret_cast<float2 *>(row + L + 2 * ci) = make_float2(0.f, g1);
+                } else {
+                    if (2 * ci < L) {
+                        row[2 * ci] = 0.f;
+                        row[L + 2 * ci] = 0.f;
+                    }
+                    if (2 * ci + 1 < L) {
+                        row[2 * ci + 1] = g0;
+                        row[L + 2 * ci + 1] = g1;
+                    }
                 }
             }
         }
@@ -763,11 +824,18 @@ __global__ void __launch_bounds__(kLThreads, 1)
             row[L + c] = 0.f;
         }
     }
+    PCFGNAT_STAMP(1, 13)
     // rows of links_grad that belong to no main-chain node in use
+    const bool quads_ok = !(L & 1) && !(reinterpret_cast<uintptr_t>(lg) & 15);  // rows of 2 L floats start on 16 bytes
     for (int a = crank * kLWarps + warp; a < L; a += NC * kLWarps) {
         if ((a & 1) && a < m) continue;
         float *row = lgb + (size_t)a * 2 * L;
-        for (int c = lane; c < 2 * L; c += 32) row[c] = 0.f;
+        if (quads_ok) {
+            float4 *row4 = reinterpret_cast<float4 *>(row);
+            for (int c = lane; c < L / 2; c += 32) row4[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+        } else {
+            for (int c = lane; c < 2 * L; c += 32) row[c] = 0.f;
+        }
     }
 
     // ---- emission gradients, pass 1: every cell times the o of its main-chain node (cells without a share: 0)
@@ -775,27 +843,55 @@ __global__ void __launch_bounds__(kLThreads, 1)
     if (NC > 1) cluster.sync(); else __syncthreads();  // the o table is complete
     PCFGNAT_STAMP(1, 7)
     float *mgb = mg + (size_t)b * L * T;
-    for (int i = ctid; i < L * T; i += cthreads) {
-        const int node = i / T, t = i - node * T;
-        float v = 0.f;
-        if (node >= 1 && node < m && t <= n - 2) {
-            const int a = node | 1;  // the main-chain node of the cell: itself, or the parent of the leaf
-            if (a < m && (node & 1 || node >= 2)) v = mgb[i] * Ob[(size_t)((a - 1) / 2) * W + t];
+    constexpr int kCells = 4;  // cells per thread and trip: their loads are in flight together
+    for (int i0 = ctid; i0 < L * T; i0 += kCells * cthreads) {
+        float share[kCells], o[kCells];
+#pragma unroll
+        for (int u = 0; u < kCells; u++) {
+            const int i = i0 + u * cthreads;
+            const int node = i / T, t = i - node * T;
+            share[u] = o[u] = 0.f;
+            if (i < L * T && node >= 1 && node < m && t <= n - 2) {
+                const int a = node | 1;  // the main-chain node of the cell: itself, or the parent of the leaf
+                if (a < m && (node & 1 || node >= 2)) {
+                    share[u] = mgb[i];
+                    o[u] = Ob[(size_t)((a - 1) / 2) * W + t];
+                }
+            }
         }
-        mgb[i] = v;
+#pragma unroll
+        for (int u = 0; u < kCells; u++) {
+            const int i = i0 + u * cthreads;
+            if (i < L * T) mgb[i] = share[u] * o[u];
+        }
     }
     if (NC > 1) cluster.sync(); else __syncthreads();
     // pass 2: a node that emitted y_t after its leaf emitted y_{t-1} (the same posterior), the terminal cell, and
     // the total mass of the sentence's emission gradients (= n when nothing was lost)
+    // (the cells a thread adds in, those of the leaves, are not written in this pass)
     float mass = 0.f;
-    for (int i = ctid; i < L * T; i += cthreads) {
-        const int node = i / T, t = i - node * T;
-        if (node >= m || t >= n) continue;
-        float v = mgb[i];
-        if ((node & 1) && node >= 3 && t >= 1) v += mgb[(size_t)(node - 1) * T + t - 1];
-        if (node == m - 1 && t == n - 1) v += Ob[(size_t)last * W + n - 1] * e_term;  // o u of the terminal cell
-        if ((node & 1) && t >= 1) mgb[i] = v;
-        mass += v;
+    for (int i0 = ctid; i0 < m * T; i0 += kCells * cthreads) {
+        float own[kCells], leaf[kCells];
+#pragma unroll
+        for (int u = 0; u < kCells; u++) {
+            const int i = i0 + u * cthreads;
+            const int node = i / T, t = i - node * T;
+            own[u] = leaf[u] = 0.f;
+            if (node < m && t < n) {
+                own[u] = mgb[i];
+                if ((node & 1) && node >= 3 && t >= 1) leaf[u] = mgb[(size_t)(node - 1) * T + t - 1];
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kCells; u++) {
+            const int i = i0 + u * cthreads;
+            const int node = i / T, t = i - node * T;
+            if (node >= m || t >= n) continue;
+            float v = own[u] + leaf[u];
+            if (node == m - 1 && t == n - 1) v += Ob[(size_t)last * W + n - 1] * e_term;  // o u of the terminal cell
+            if ((node & 1) && t >= 1) mgb[i] = v;
+            mass += v;
+        }
     }
     mass = warp_sum(mass);
     if (lane == 0) red[warp] = mass;
