@@ -572,7 +572,6 @@ __global__ void __launch_bounds__(kLThreads, 1)
 #ifdef PCFGNAT_TIMING
     if (tid == 0 && crank == 0 && b < 256) g_linear_timing[1][b][0] = t_start;
 #endif
-    const int ctid = crank * kLThreads + tid, cthreads = NC * kLThreads;
     const int W = T + 2, F = kLinearFrameHead + W;
     const int m = (int)ol[b], n = (int)tl[b];
     float *fr = frames + (size_t)b * F;
@@ -838,61 +837,56 @@ __global__ void __launch_bounds__(kLThreads, 1)
         }
     }
 
-    // ---- emission gradients, pass 1: every cell times the o of its main-chain node (cells without a share: 0)
+    // ---- emission gradients: a warp per main-chain node a takes the rows of a and of its leaf a - 1, lanes over the
+    // tokens.  The inside pass left the shares p0_t[a] in cell [a][t] and p1_t[a] in cell [a-1][t]; with o = o_t[a]
+    // the leaf's gradient is p1 o, and the node's p0 o plus the leaf's of token t - 1 (a node that emitted y_t after
+    // its leaf emitted y_{t-1}: the same posterior), which comes from the neighbouring lane: no cell is read
+    // that another thread writes.  The terminal cell gets o u on top; everything else is zero.  `mass` = the total
+    // of the sentence's emission gradients (= n when nothing was lost).
     PCFGNAT_STAMP(1, 6)
     if (NC > 1) cluster.sync(); else __syncthreads();  // the o table is complete
     PCFGNAT_STAMP(1, 7)
     float *mgb = mg + (size_t)b * L * T;
-    constexpr int kCells = 4;  // cells per thread and trip: their loads are in flight together
-    for (int i0 = ctid; i0 < L * T; i0 += kCells * cthreads) {
-        float share[kCells], o[kCells];
+    const int cwarp = crank * kLWarps + warp, cwarps = NC * kLWarps;
+    float mass = 0.f;
+    for (int ai = cwarp; ai < Mb; ai += cwarps) {
+        const int a = 2 * ai + 1;
+        float *rown = mgb + (size_t)a * T, *rowl = rown - T;
+        const float *orow = Ob + (size_t)ai * W;
+        const float term = ai == last ? orow[n - 1] * e_term : 0.f;
+        float carry = 0.f;  // the leaf's gradient at the token before this group of 64
+        for (int t0 = 0; t0 < T; t0 += 64) {
+            float p0[2], p1[2], o[2];
 #pragma unroll
-        for (int u = 0; u < kCells; u++) {
-            const int i = i0 + u * cthreads;
-            const int node = i / T, t = i - node * T;
-            share[u] = o[u] = 0.f;
-            if (i < L * T && node >= 1 && node < m && t <= n - 2) {
-                const int a = node | 1;  // the main-chain node of the cell: itself, or the parent of the leaf
-                if (a < m && (node & 1 || node >= 2)) {
-                    share[u] = mgb[i];
-                    o[u] = Ob[(size_t)((a - 1) / 2) * W + t];
+            for (int u = 0; u < 2; u++) {  // both halves' loads before any use
+                const int t = t0 + 32 * u + lane;
+                p0[u] = p1[u] = o[u] = 0.f;
+                if (t <= n - 2) {
+                    o[u] = orow[t];
+                    p0[u] = rown[t];
+                    if (a >= 3) p1[u] = rowl[t];
                 }
             }
-        }
 #pragma unroll
-        for (int u = 0; u < kCells; u++) {
-            const int i = i0 + u * cthreads;
-            if (i < L * T) mgb[i] = share[u] * o[u];
-        }
-    }
-    if (NC > 1) cluster.sync(); else __syncthreads();
-    // pass 2: a node that emitted y_t after its leaf emitted y_{t-1} (the same posterior), the terminal cell, and
-    // the total mass of the sentence's emission gradients (= n when nothing was lost)
-    // (the cells a thread adds in, those of the leaves, are not written in this pass)
-    float mass = 0.f;
-    for (int i0 = ctid; i0 < m * T; i0 += kCells * cthreads) {
-        float own[kCells], leaf[kCells];
-#pragma unroll
-        for (int u = 0; u < kCells; u++) {
-            const int i = i0 + u * cthreads;
-            const int node = i / T, t = i - node * T;
-            own[u] = leaf[u] = 0.f;
-            if (node < m && t < n) {
-                own[u] = mgb[i];
-                if ((node & 1) && node >= 3 && t >= 1) leaf[u] = mgb[(size_t)(node - 1) * T + t - 1];
+            for (int u = 0; u < 2; u++) {
+                const int t = t0 + 32 * u + lane;
+                const float leafv = p1[u] * o[u];
+                float nodev = p0[u] * o[u];
+                float prev = __shfl_up_sync(0xffffffffu, leafv, 1);
+                if (lane == 0) prev = carry;
+                carry = __shfl_sync(0xffffffffu, leafv, 31);
+                if (a >= 3 && t >= 1) nodev += prev;
+                if (t == n - 1) nodev += term;
+                if (t < T) {
+                    rown[t] = t < n ? nodev : 0.f;
+                    rowl[t] = t < n ? leafv : 0.f;
+                }
+                if (t < n) mass += nodev + leafv;
             }
         }
-#pragma unroll
-        for (int u = 0; u < kCells; u++) {
-            const int i = i0 + u * cthreads;
-            const int node = i / T, t = i - node * T;
-            if (node >= m || t >= n) continue;
-            float v = own[u] + leaf[u];
-            if (node == m - 1 && t == n - 1) v += Ob[(size_t)last * W + n - 1] * e_term;  // o u of the terminal cell
-            if ((node & 1) && t >= 1) mgb[i] = v;
-            mass += v;
-        }
     }
+    for (int node = m + cwarp; node < L; node += cwarps)  // rows beyond the graph
+        for (int t = lane; t < T; t += 32) mgb[(size_t)node * T + t] = 0.f;
     mass = warp_sum(mass);
     if (lane == 0) red[warp] = mass;
     __syncthreads();
