@@ -18,6 +18,8 @@
 // The threads of a block (one block per sentence) each scan a subset of one virtual lane and the
 // reduction orders candidates by (value desc, lane rank, c, j), which is the same order.  All loads of a
 // step are independent, so a step costs one round trip to L2, a hardware warp reduction and one block barrier.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace pcfgnat {
@@ -123,6 +125,143 @@ __global__ void __launch_bounds__(kTreeWarps * 32)
     }
 }
 
+// The same walk with everything it reads staged in shared memory first: the triangle links[a][k][c], c > a, of the
+// main-chain nodes (packed row after row), the inside table and the emissions.  A step of the walk above is one
+// round trip to L2 (about 1 300 cycles with the reduction and the barrier) and there are up to n + 1 of them in a
+// row; from shared memory a step is about 250 cycles, and the staging is one coalesced pass with every load of
+// the block in flight.  Same arithmetic, same keys: the result is bit for bit the same.
+constexpr int kStagedTreeWarps = 32;
+
+__host__ __device__ inline size_t tri_rows_before(int ai, int Mb) {  // pairs (a, c > a) of the rows before ai
+    return (size_t)ai * (Mb - 1) - (size_t)ai * (ai - 1) / 2;
+}
+
+__global__ void __launch_bounds__(kStagedTreeWarps * 32)
+    best_tree_staged_kernel(const float *__restrict__ S, const float *__restrict__ match_all,
+                            const float *__restrict__ links, const int64_t *__restrict__ ol,
+                            const int64_t *__restrict__ tl, int B, int L, int T, int64_t *tree, int *status, int Mc) {
+    extern __shared__ float tree_smem[];
+    __shared__ unsigned s_ord[2][kStagedTreeWarps];
+    __shared__ int s_key[2][kStagedTreeWarps];
+    constexpr int kThreads = kStagedTreeWarps * 32;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int b = blockIdx.x;
+    const int W = T + 2;
+    const int m = (int)ol[b], n = (int)tl[b];
+    int64_t *tr = tree + (size_t)b * L;
+    for (int i = tid; i < L; i += kThreads) tr[i] = -1;
+    if (!lengths_ok(m, n, L, T)) {
+        if (tid == 0) flag(status, PCFGNAT_STATUS_BAD_LENGTH);
+        return;
+    }
+    const float *mat = match_all + (size_t)b * L * T;
+    const float *lkb = links + (size_t)b * L * 2 * L;
+    const float *Sb = S + (size_t)b * Mc * W;
+    const int Mb = main_nodes_below(m);
+    const size_t tri = tri_rows_before(Mb > 0 ? Mb - 1 : 0, Mb);  // pairs in all
+    float *tri0 = tree_smem, *tri1 = tri0 + tri;  // [pairs] links[a][0][c], links[a][1][c]
+    float *Ss = tri1 + tri;                       // [Mb][W]
+    float *ms = Ss + (size_t)Mb * W;              // [m][T]
+    // eight elements per thread and trip, all their loads issued before the first store: the staging is a handful
+    // of round trips to L2
+    constexpr int kBatch = 8;
+    for (int i0 = tid; i0 < (Mb - 1) * Mb; i0 += kBatch * kThreads) {  // (ai, ci) over the square; pairs ci > ai only
+        float v0[kBatch], v1[kBatch];
+#pragma unroll
+        for (int u = 0; u < kBatch; u++) {
+            const int i = i0 + u * kThreads, ai = i / Mb, ci = i - ai * Mb;
+            v0[u] = v1[u] = 0.f;
+            if (i < (Mb - 1) * Mb && ci > ai) {
+                const float *row = lkb + (size_t)(2 * ai + 1) * 2 * L + 2 * ci + 1;
+                v0[u] = __ldg(row);
+                v1[u] = __ldg(row + L);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kBatch; u++) {
+            const int i = i0 + u * kThreads, ai = i / Mb, ci = i - ai * Mb;
+            if (i < (Mb - 1) * Mb && ci > ai) {
+                const size_t at = tri_rows_before(ai, Mb) + (ci - ai - 1);
+                tri0[at] = v0[u];
+                tri1[at] = v1[u];
+            }
+        }
+    }
+    auto stage = [&](float *dst, const float *src, int count) {
+        for (int i0 = tid; i0 < count; i0 += kBatch * kThreads) {
+            float v[kBatch];
+#pragma unroll
+            for (int u = 0; u < kBatch; u++) v[u] = i0 + u * kThreads < count ? __ldg(src + i0 + u * kThreads) : 0.f;
+#pragma unroll
+            for (int u = 0; u < kBatch; u++)
+                if (i0 + u * kThreads < count) dst[i0 + u * kThreads] = v[u];
+        }
+    };
+    stage(Ss, Sb, Mb * W);
+    stage(ms, mat, m * T);
+    __syncthreads();
+    // the walk needs a thread per right child at most: the other warps are done, the walkers meet on a barrier of
+    // their own
+    const int walkers = max(1, (Mb - 1 + 31) / 32);
+    if (warp >= walkers) return;
+    const int walk_threads = walkers * 32;
+
+    int ai = 0, start = 0;
+    for (int step = 0; step <= n && start <= n; step++) {
+        const int a = 2 * ai + 1;
+        const int jmax = min(n - start, 2);
+        float best = neg_inf();
+        int key = 0x7fffffff;
+        if (jmax >= 1) {
+            const float ma0 = ms[(size_t)a * T + start];
+            const bool leaf = jmax >= 2 && a >= 3;
+            const float ma1 = leaf ? ms[(size_t)a * T + start + 1] : 0.f;
+            const float ml = leaf ? ms[(size_t)(a - 1) * T + start] : 0.f;
+            const size_t off = tri_rows_before(ai, Mb);
+            for (int ci = ai + 1 + tid; ci < Mb; ci += walk_threads) {
+                const int rank_of_lane = (0x3120 >> (4 * ((ci - ai - 1) & 3))) & 0xf;
+                const float l0 = tri0[off + (ci - ai - 1)], s1 = Ss[(size_t)ci * W + start + 1];
+                const float t0 = ((l0 + s1) + 0.f) + ma0;
+                if (t0 > best) {
+                    best = t0;
+                    key = (rank_of_lane << 24) | (ci << 1);
+                }
+                if (leaf) {
+                    const float l1 = tri1[off + (ci - ai - 1)], s2 = Ss[(size_t)ci * W + start + 2];
+                    const float t1 = ((l1 + s2) + ml) + ma1;
+                    if (t1 > best) {
+                        best = t1;
+                        key = (rank_of_lane << 24) | (ci << 1) | 1;
+                    }
+                }
+            }
+        }
+        unsigned ord = ordered_bits(best);
+        const unsigned top = __reduce_max_sync(0xffffffffu, ord);
+        const unsigned kmin = __reduce_min_sync(0xffffffffu, ord == top ? (unsigned)key : 0xffffffffu);
+        if (lane == 0) {
+            s_ord[step & 1][warp] = top;
+            s_key[step & 1][warp] = (int)kmin;
+        }
+        asm volatile("bar.sync 1, %0;" ::"r"(walk_threads) : "memory");
+        // every walking warp reduces the winners of all of them (one per lane) the same way
+        static_assert(kStagedTreeWarps <= 32, "one lane per warp's winner");
+        const unsigned my_ord = lane < walkers ? s_ord[step & 1][lane] : 0u;
+        const int my_key = lane < walkers ? s_key[step & 1][lane] : 0x7fffffff;
+        const unsigned w_ord = __reduce_max_sync(0xffffffffu, my_ord);
+        const int w_key = (int)__reduce_min_sync(0xffffffffu, my_ord == w_ord ? (unsigned)my_key : 0xffffffffu);
+        const bool found = w_key != 0x7fffffff;
+        const int j = found ? (w_key & 1) : 0;
+        if (tid == 0) {
+            tr[a] = start + j;
+            if (found && j == 1) tr[a - 1] = start;
+        }
+        if (!found) break;
+        ai = (w_key >> 1) & 0x7fffff;
+        start = start + j + 1;
+    }
+}
+
 }  // namespace
 
 int launch_best_tree(const float *S, const float *match_all, const float *links, const int64_t *ol, const int64_t *tl,
@@ -130,6 +269,14 @@ int launch_best_tree(const float *S, const float *match_all, const float *links,
     if (B == 0) return PCFGNAT_OK;
     const int Mc = main_slots(L, 1);
     if (Mc >= (1 << 22)) return PCFGNAT_ERR_TOO_LARGE;
+    // everything the walk reads in shared memory, where the largest sentence the shapes allow fits
+    const size_t staged = (2 * tri_rows_before(Mc > 0 ? Mc - 1 : 0, Mc) + (size_t)Mc * (T + 2) + (size_t)L * T) * sizeof(float);
+    const char *env = getenv("PCFGNAT_TREE_STAGED");  // "0": the walk over global memory
+    if (staged <= (size_t)kSmemLimit - 1024 && !(env && env[0] == '0')) {
+        if (ensure_dynamic_smem(best_tree_staged_kernel, staged) != cudaSuccess) return PCFGNAT_ERR_CUDA;
+        best_tree_staged_kernel<<<B, kStagedTreeWarps * 32, staged, st>>>(S, match_all, links, ol, tl, B, L, T, tree, status, Mc);
+        return cuda_rc(cudaGetLastError());
+    }
     best_tree_kernel<<<B, kTreeWarps * 32, 0, st>>>(S, match_all, links, ol, tl, B, L, T, tree, status, Mc);
     return cuda_rc(cudaGetLastError());
 }

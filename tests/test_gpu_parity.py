@@ -127,8 +127,19 @@ def test_loss_backward_against_oracle(dp_kernel, ops, syn, name, kw, seed):
     np.testing.assert_allclose(lkt.grad.cpu().numpy()[fin_np], lgo[fin_np], rtol=1e-3, atol=2e-6)
 
 
+@pytest.fixture(params=["staged", "global"])
+def tree_walk(request, monkeypatch):
+    """Both best-tree kernels: the walk over a copy of its inputs in shared memory (default where it fits) and the
+    walk over global memory (PCFGNAT_TREE_STAGED=0, and shapes too large for shared memory)."""
+    if request.param == "global":
+        monkeypatch.setenv("PCFGNAT_TREE_STAGED", "0")
+    else:
+        monkeypatch.delenv("PCFGNAT_TREE_STAGED", raising=False)
+    return request.param
+
+
 @pytest.mark.parametrize("name,kw,seed", CASES)
-def test_best_tree_bit_exact_on_shared_tables(ops, syn, name, kw, seed):
+def test_best_tree_bit_exact_on_shared_tables(ops, syn, tree_walk, name, kw, seed):
     b, ma = _loss_inputs(syn, syn.Workload(name, emissions="logits", **kw), seed)
     ol, tl = b.output_length.numpy(), b.target_length.numpy()
     So, Co = oracle.pcfg_loss(ma.numpy(), b.links.numpy(), ol, tl)
@@ -138,7 +149,7 @@ def test_best_tree_bit_exact_on_shared_tables(ops, syn, name, kw, seed):
     np.testing.assert_array_equal(got.cpu().numpy(), want)
 
 
-def test_best_tree_tie_breaking(ops):
+def test_best_tree_tie_breaking(ops, tree_walk):
     # all transitions and emissions equal: every arg-max is a tie, so the result is decided by the
     # reference's lane order (0, 2, 1, 3), then smallest right child, then "no left child" first
     B, L, T = 1, 40, 9
