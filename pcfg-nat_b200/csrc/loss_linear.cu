@@ -37,9 +37,11 @@
 // target token, out of range), the sentence is marked and recomputed by the log-space kernels in the same call
 // (loss_fwd.cu / loss_bwd.cu, which skip unmarked sentences).
 //
-// Layout: one WARP per node, one thread-block CLUSTER per sentence, nodes dealt round-robin to the CTAs; the
-// columns are exchanged with st.async counted on alternating mbarriers exactly as in loss_cluster.cu; a lane
-// covers four consecutive children with 16-byte shared-memory loads.
+// Layout: G = 8 or 16 lanes per node (a lane covers groups of four consecutive children, its part of the node's
+// matrix rows in registers), one thread-block CLUSTER per sentence, nodes dealt round-robin to the CTAs; the
+// columns are exchanged with st.async counted on alternating mbarriers exactly as in loss_cluster.cu.  Batches
+// between half and all of the SMs run clusters of two, which the costliest sentences have to themselves and the
+// others share, one CTA per sentence (pick_sentence).
 #include <cooperative_groups.h>
 
 #include <cstdlib>
